@@ -1,0 +1,343 @@
+/*
+ * wgml_b200.h -- C ABI of the B200-native token-loop path behind wgml's operator surface.
+ *
+ * wgml has no FFI of its own: its operators are Rust structs that record WGSL dispatches into a
+ * wgpu compute pass.  Each entry point below replaces one of those Rust interfaces (cited as
+ * file:line inside the wgml repository) with a call that enqueues hand-written sm_100a CUDA
+ * kernels on a caller-supplied CUDA stream.
+ *
+ * Conventions
+ *  - Every function returns a wgb_status; 0 is success.  Nothing aborts: where the Rust code
+ *    panics on an `assert!`, the call returns WGB_ERR_INVALID.  wgb_last_error() gives the
+ *    message of the calling thread's last failure.
+ *  - `stream` is a `cudaStream_t` passed as `void *` (NULL = the legacy default stream).  Work is
+ *    enqueued and the call returns: the counterpart of wgml's "record, then queue.submit".
+ *  - Pointers named d_* are device addresses of the current CUDA device, owned by the caller,
+ *    as wgml's ops borrow the caller's GpuVector / GpuMatrix buffers.  Vector views are
+ *    contiguous: pass `base + offset` for `column(pos)` / `rows(start, n)` views.
+ *  - Matrices are row-major with the input dimension contiguous, exactly the byte order of a
+ *    GGUF tensor (crates/wgml/src/gguf.rs:148-155).
+ *  - There is no CPU fallback: on a machine without a CUDA device every compute entry point
+ *    fails with WGB_ERR_CUDA.
+ */
+#ifndef WGML_B200_H
+#define WGML_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    WGB_OK = 0,
+    WGB_ERR_INVALID = 1,     /* shape / argument mismatch (a Rust `assert!` in the reference) */
+    WGB_ERR_UNSUPPORTED = 2, /* tensor or metadata type the reference does not support either */
+    WGB_ERR_CUDA = 3,        /* a CUDA runtime call failed, or no device */
+    WGB_ERR_PARSE = 4,       /* malformed GGUF (GgufParseError, gguf.rs:23-37) */
+    WGB_ERR_NOT_FOUND = 5,   /* missing GGUF key / tensor (a panic in the reference) */
+    WGB_ERR_TIMEOUT = 6      /* a bounded device-side wait gave up */
+} wgb_status;
+
+/* ggml tensor type ids (crates/wgml/src/gguf.rs:73-105); the variants of GpuQuantMatrix
+ * (crates/wgml/src/quantized_matrix.rs:9-20) plus F16. */
+typedef enum {
+    WGB_F32 = 0, WGB_F16 = 1, WGB_Q4_0 = 2, WGB_Q4_1 = 3, WGB_Q5_0 = 6, WGB_Q5_1 = 7,
+    WGB_Q8_0 = 8, WGB_Q4_K = 12, WGB_Q5_K = 13, WGB_Q6_K = 14, WGB_Q8_K = 15
+} wgb_qtype;
+
+const char *wgb_last_error(void);
+/* Library version string and the compute capability the kernels were built for ("sm_100a"). */
+const char *wgb_version(void);
+/* Bytes per block / weights per block of a format (block structs, quantization.rs:13-327). */
+int wgb_block_bytes(int qtype);
+int wgb_block_len(int qtype);
+
+/* ---- device memory helpers (what wgcore's GpuVector::init / read do for the Rust caller) ---- */
+int wgb_malloc(void **d_ptr, size_t bytes);
+int wgb_free(void *d_ptr);
+int wgb_memcpy_h2d(void *d_dst, const void *h_src, size_t bytes, void *stream);
+int wgb_memcpy_d2h(void *h_dst, const void *d_src, size_t bytes, void *stream);
+int wgb_memset(void *d_dst, int value, size_t bytes, void *stream);
+int wgb_stream_synchronize(void *stream);
+
+/* ---- quantisation ---- */
+
+/* Block*::dequantize for every block of a tensor (quantization.rs:21-378,
+ * GgufTensorData::dequantize gguf.rs:114-129; GPU twin ops/quantization_test.wgsl:45-146).
+ * d_blocks: raw GGUF blocks; d_out: nblocks * wgb_block_len(qtype) floats.  Bit-exact with the
+ * Rust CPU code (every multiply, add and subtract individually rounded). */
+int wgb_dequantize(int qtype, const void *d_blocks, size_t nblocks, float *d_out, void *stream);
+
+/* GpuQuantMatrix (quantized_matrix.rs:9-75) as built by GgufTensorData::to_gpu_matrix
+ * (gguf.rs:131-184): an nrows x ncols matrix kept in its GGUF blocks on the device.  Unlike the
+ * reference there is no dense-f32 fallback when ncols is not a multiple of 64 / 512: any ncols
+ * that is a multiple of the format's block length is accepted.  Q8_0 and Q6_K blocks (34 and
+ * 210 bytes, only 2-byte aligned) are split into 16-byte aligned planes once, here; the weights
+ * they decode to are unchanged. */
+typedef struct wgb_quant_matrix wgb_quant_matrix;
+int wgb_quant_matrix_create(int qtype, const void *h_blocks, size_t nrows, size_t ncols,
+                            void *stream, wgb_quant_matrix **out);
+/* Same, from blocks that are already on the device (raw GGUF order). */
+int wgb_quant_matrix_create_from_device(int qtype, const void *d_blocks, size_t nrows, size_t ncols,
+                                        void *stream, wgb_quant_matrix **out);
+int wgb_quant_matrix_destroy(wgb_quant_matrix *m);
+/* GpuQuantMatrix::shape (quantized_matrix.rs:37-52) in weights, and the format. */
+int wgb_quant_matrix_shape(const wgb_quant_matrix *m, size_t *nrows, size_t *ncols, int *qtype);
+/* Dequantise rows [row0, row0+n) to d_out (n * ncols floats), bit-exact as wgb_dequantize. */
+int wgb_quant_matrix_dequantize_rows(const wgb_quant_matrix *m, size_t row0, size_t n, float *d_out,
+                                     void *stream);
+
+/* GemvQuant::dispatch (ops/gemv_quant.rs:241-348): d_out[nrows] = m * d_v[ncols], f32 in and
+ * out, f32 accumulation.  Any nrows (the reference needs nrows % 4 == 0). */
+int wgb_gemv_quant(const wgb_quant_matrix *m, const float *d_v, float *d_out, void *stream);
+/* The same product over raw GGUF blocks in device memory (no wgb_quant_matrix). */
+int wgb_gemv_quant_raw(int qtype, const void *d_blocks, size_t nrows, size_t ncols, const float *d_v,
+                       float *d_out, void *stream);
+
+/* ---- normalisation, activations, elementwise ---- */
+
+/* RmsNorm::dispatch (ops/rms_norm.rs:24-53, rms_norm.wgsl:58-67), RmsNormConfig::nudge_factor
+ * (rms_norm.rs:17-21) passed as eps: out = (v * 1/sqrt(mean(v^2) + eps)) * w. */
+int wgb_rms_norm(float *d_out, const float *d_v, const float *d_w, size_t n, float eps, void *stream);
+/* LayerNorm::dispatch (ops/layernorm.rs:18-41, layernorm.wgsl:28-80): (x - mean)/sqrt(var+1e-5),
+ * no gain or bias. */
+int wgb_layernorm(float *d_out, const float *d_in, size_t n, void *stream);
+
+/* RoPEConfig (ops/rope.rs:26-35); field order and types as the Rust / WGSL struct. */
+typedef struct {
+    uint32_t head_size;
+    uint32_t kv_dim;
+    uint32_t pos;
+    float base_freq;
+} wgb_rope_config;
+/* RoPEVariant (ops/rope.rs:10-16) */
+typedef enum { WGB_ROPE_ORIGINAL = 0, WGB_ROPE_NEOX = 1 } wgb_rope_variant;
+/* RoPE::dispatch (ops/rope.rs:37-76, rope.wgsl:36-77): rotates q and the first kv_dim entries
+ * of k in place.  q_len and k_len must be even and q_len >= k_len (rope.rs:51-56). */
+int wgb_rope(int variant, const wgb_rope_config *cfg, float *d_q, size_t q_len, float *d_k,
+             size_t k_len, void *stream);
+
+/* BatchedMultiqueryAttentionParams (ops/batched_multiquery_attention.rs:26-37). */
+typedef struct {
+    uint32_t seq_len;
+    uint32_t kv_dim;
+    uint32_t kv_mul;
+    uint32_t n_heads;
+    uint32_t head_size;
+    uint32_t pos;
+} wgb_attn_params;
+/* BatchedMultiqueryAttention::dispatch / dispatch_multi (ops/batched_multiquery_attention.rs:
+ * 55-139): xb_h = softmax(q_h . K_t / sqrt(head_size), t = 0..=pos) . V_t for every query head.
+ * Caches are [seq_len][kv_dim] floats (time step t is the t-th run of kv_dim floats).  d_attn
+ * may be NULL; otherwise it receives the attention weights as [n_heads][seq_len] (the layout of
+ * the reference's single-kernel path, batched_multiquery_attention.wgsl:48,66). */
+int wgb_attention(const wgb_attn_params *p, const float *d_q, const float *d_key_cache,
+                  const float *d_value_cache, float *d_attn, float *d_xb, void *stream);
+/* SoftMax::dispatch (ops/softmax.rs:18-30, softmax.wgsl:31-92): every column of a column-major
+ * nrows x ncols matrix (column j starts at d_mat + j * col_stride) replaced by its softmax. */
+int wgb_softmax(float *d_mat, size_t nrows, size_t ncols, size_t col_stride, void *stream);
+/* Silu::dispatch (ops/silu.rs:18-34, silu.wgsl:19-27): h1 = h2 * h1 / (1 + exp(-h1)). */
+int wgb_silu(float *d_h1, const float *d_h2, size_t n, void *stream);
+
+/* UnaryOp (ops/unary.rs:16-38), numbered in declaration order. */
+typedef enum {
+    WGB_UNARY_ABS = 0, WGB_UNARY_SGN, WGB_UNARY_NEG, WGB_UNARY_STEP, WGB_UNARY_ELU, WGB_UNARY_GELU,
+    WGB_UNARY_GELU_QUICK, WGB_UNARY_SILU, WGB_UNARY_TANH, WGB_UNARY_RELU, WGB_UNARY_SIGMOID,
+    WGB_UNARY_HARD_SIGMOID, WGB_UNARY_HARD_SWISH, WGB_UNARY_SQR, WGB_UNARY_SQRT, WGB_UNARY_LOG,
+    WGB_UNARY_LEAKY_RELU, WGB_UNARY_CLAMP, WGB_UNARY_SCALE, WGB_UNARY_ADD_SCALAR
+} wgb_unary_op;
+/* Unary::dispatch / UnaryInplace::dispatch (ops/unary.rs:158-193, 229-256; unary.wgsl:116-130).
+ * args4 (host pointer to 4 floats) must be given exactly for the ops that take arguments
+ * (LeakyRelu, Clamp, Scale, AddScalar), else NULL (unary.rs:172-175). */
+int wgb_unary(int op, float *d_dst, const float *d_src, size_t n, const float *args4, void *stream);
+int wgb_unary_inplace(int op, float *d_src, size_t n, const float *args4, void *stream);
+
+/* wgebra OpAssign{Add,Mul,Copy} as wgml calls it (models/llama2/transformer.rs:293,343-354,
+ * 383-384; models/gpt2/transformer.rs:259-261,277-290): lhs += rhs, lhs *= rhs, lhs = rhs. */
+typedef enum { WGB_ASSIGN_ADD = 0, WGB_ASSIGN_MUL = 1, WGB_ASSIGN_COPY = 2 } wgb_assign_kind;
+int wgb_op_assign(int kind, float *d_lhs, const float *d_rhs, size_t n, void *stream);
+
+/* Sampler::sample_argmax (models/sampler.rs:54-56) on the device: index of the first maximum
+ * of d_v[0..n) written to *d_index. */
+int wgb_argmax(const float *d_v, size_t n, uint32_t *d_index, void *stream);
+
+/* ---- GGUF ---- */
+
+/* Gguf (gguf.rs:317-322) parsed by Gguf::from_bytes (gguf.rs:452-623).  The file is mapped, not
+ * copied: tensor data pointers point into the mapping (or into `bytes`, which must then outlive
+ * the handle). */
+typedef struct wgb_gguf wgb_gguf;
+int wgb_gguf_open(const char *path, wgb_gguf **out);
+int wgb_gguf_from_bytes(const void *bytes, size_t len, wgb_gguf **out);
+int wgb_gguf_close(wgb_gguf *g);
+uint32_t wgb_gguf_version(const wgb_gguf *g);
+uint64_t wgb_gguf_tensor_count(const wgb_gguf *g);
+uint64_t wgb_gguf_metadata_count(const wgb_gguf *g);
+uint32_t wgb_gguf_alignment(const wgb_gguf *g);
+
+/* GgufMetadataValue (gguf.rs:230-245); type ids of MetadataValueType (gguf.rs:332-364). */
+typedef enum {
+    WGB_META_U8 = 0, WGB_META_I8 = 1, WGB_META_U16 = 2, WGB_META_I16 = 3, WGB_META_U32 = 4,
+    WGB_META_I32 = 5, WGB_META_F32 = 6, WGB_META_BOOL = 7, WGB_META_STRING = 8, WGB_META_ARRAY = 9,
+    WGB_META_U64 = 10, WGB_META_I64 = 11, WGB_META_F64 = 12
+} wgb_meta_type;
+/* Index of a key, or -1.  Keys are listed in file order by wgb_gguf_meta_key. */
+int64_t wgb_gguf_meta_find(const wgb_gguf *g, const char *key);
+const char *wgb_gguf_meta_key(const wgb_gguf *g, uint64_t index);
+/* Value type; for arrays *elem_type and *len describe the elements (elem_type WGB_META_ARRAY
+ * for nested arrays, whose elements are not exposed). */
+int wgb_gguf_meta_type(const wgb_gguf *g, uint64_t index, int *type, int *elem_type, uint64_t *len);
+/* Scalar getters: integers and bool widen to 64 bits, floats to double.  WGB_ERR_INVALID when
+ * the stored type is of another kind (the reference's unwrap_* accessors panic, gguf.rs:247-295). */
+int wgb_gguf_meta_u64(const wgb_gguf *g, uint64_t index, uint64_t *out);
+int wgb_gguf_meta_i64(const wgb_gguf *g, uint64_t index, int64_t *out);
+int wgb_gguf_meta_f64(const wgb_gguf *g, uint64_t index, double *out);
+/* String value: pointer into the file (not NUL-terminated) and its length. */
+int wgb_gguf_meta_str(const wgb_gguf *g, uint64_t index, const char **ptr, uint64_t *len);
+/* Array element i as integer / double / string. */
+int wgb_gguf_meta_arr_u64(const wgb_gguf *g, uint64_t index, uint64_t i, uint64_t *out);
+int wgb_gguf_meta_arr_i64(const wgb_gguf *g, uint64_t index, uint64_t i, int64_t *out);
+int wgb_gguf_meta_arr_f64(const wgb_gguf *g, uint64_t index, uint64_t i, double *out);
+int wgb_gguf_meta_arr_str(const wgb_gguf *g, uint64_t index, uint64_t i, const char **ptr, uint64_t *len);
+
+/* GgufTensor (gguf.rs:297-315). */
+typedef struct {
+    const char *name;      /* NUL-terminated copy owned by the handle */
+    uint32_t n_dims;
+    uint64_t dims[4];      /* unused trailing dims are 1, as in the reference (gguf.rs:516) */
+    uint32_t type;         /* ggml type id */
+    uint64_t offset;       /* absolute offset of the data in the file (gguf.rs:540-542) */
+    uint64_t n_bytes;      /* 0 for the block formats the reference leaves unread (gguf.rs:618) */
+    const void *data;      /* host pointer to the tensor bytes */
+} wgb_gguf_tensor;
+int64_t wgb_gguf_tensor_find(const wgb_gguf *g, const char *name);
+int wgb_gguf_tensor_info(const wgb_gguf *g, uint64_t index, wgb_gguf_tensor *out);
+
+/* ---- Llama-2 family ---- */
+
+/* Llama2Config (models/llama2/cpu.rs:46-67); usize fields are u32 here. */
+typedef struct {
+    uint32_t dim;
+    uint32_t hidden_dim;
+    uint32_t n_layers;
+    uint32_t n_q_heads;
+    uint32_t n_kv_heads;
+    uint32_t vocab_size;
+    uint32_t seq_len;
+    float rope_base_freq;
+    float rms_norm_eps;
+} wgb_llama2_config;
+/* LlamaModelType (models/llama2/mod.rs:14-32): Qwen2 = q/k/v biases + Neox RoPE. */
+typedef enum { WGB_LLAMA = 0, WGB_QWEN2 = 1 } wgb_llama_model_type;
+/* Llama2Config::from_gguf_with_model_type (cpu.rs:79-109), same keys and defaults. */
+int wgb_llama2_config_from_gguf(const wgb_gguf *g, int model_type, wgb_llama2_config *out);
+
+/* Per-layer matrices / vectors of Llama2LayerWeights (models/llama2/transformer.rs:128-141). */
+typedef enum {
+    WGB_L_ATTN_Q = 0, WGB_L_ATTN_K, WGB_L_ATTN_V, WGB_L_ATTN_OUTPUT, WGB_L_FFN_GATE, WGB_L_FFN_UP,
+    WGB_L_FFN_DOWN
+} wgb_llama2_matrix;
+typedef enum {
+    WGB_L_ATTN_NORM = 0, WGB_L_FFN_NORM, WGB_L_ATTN_Q_BIAS, WGB_L_ATTN_K_BIAS, WGB_L_ATTN_V_BIAS
+} wgb_llama2_vector;
+/* Model-level tensors of Llama2Weights (transformer.rs:143-148), used with layer = -1. */
+typedef enum { WGB_L_TOKEN_EMBD = 0, WGB_L_OUTPUT = 1 } wgb_llama2_model_matrix;
+
+/* Llama2 + Llama2Weights + Llama2State (models/llama2/transformer.rs:17-126,143-148,271-296)
+ * for tensor-parallel rank `tp_rank` of `tp_size` (1 GPU: 0 of 1).  The model owns its weights,
+ * activations and KV cache on the current device. */
+typedef struct wgb_llama2 wgb_llama2;
+int wgb_llama2_create(const wgb_llama2_config *cfg, int model_type, int tp_rank, int tp_size,
+                      wgb_llama2 **out);
+int wgb_llama2_destroy(wgb_llama2 *m);
+/* Upload one tensor from host memory (raw GGUF blocks or f32).  Under tensor parallelism the
+ * full tensor is passed and the rank keeps its slice.  layer = -1 addresses token_embd / output
+ * / output_norm; output defaults to token_embd when never set (transformer.rs:244-257). */
+int wgb_llama2_set_matrix(wgb_llama2 *m, int layer, int which, int qtype, const void *h_blocks,
+                          size_t nrows, size_t ncols);
+int wgb_llama2_set_vector(wgb_llama2 *m, int layer, int which, const float *h_data, size_t n);
+/* Llama2Weights::from_gguf (transformer.rs:151-268): same tensor names. */
+int wgb_llama2_load_gguf(wgb_llama2 *m, const wgb_gguf *g);
+/* Optional: share an NCCL communicator (an `ncclComm_t` passed as void *) for tp_size > 1. */
+int wgb_llama2_set_comm(wgb_llama2 *m, void *nccl_comm);
+/* 1 (default): fused kernels (norm + matrix product + RoPE / KV append / SiLU / residual in one
+ * launch each).  0: one launch per reference dispatch, in the order of Llama2::dispatch
+ * (transformer.rs:310-427); also what is used when a layer mixes block formats that have no fused
+ * kernel. */
+int wgb_llama2_set_fused(wgb_llama2 *m, int enable);
+/* Llama2::dispatch + the embedding copy of ChatLlama2::forward_logits (transformer.rs:298-431,
+ * crates/wgml-chat/src/chat_llama2.rs:155-213): one token at position pos; logits stay on the
+ * device (wgb_llama2_logits). */
+int wgb_llama2_forward(wgb_llama2 *m, uint32_t token, uint32_t pos, void *stream);
+/* Device pointers into Llama2State (transformer.rs:17-45): logits [vocab_size], x [dim],
+ * key / value cache of a layer [seq_len][kv_dim / tp_size]. */
+const float *wgb_llama2_logits(const wgb_llama2 *m);
+const float *wgb_llama2_x(const wgb_llama2 *m);
+float *wgb_llama2_key_cache(wgb_llama2 *m, uint32_t layer);
+float *wgb_llama2_value_cache(wgb_llama2 *m, uint32_t layer);
+/* The token loop of ChatLlama2::forward (chat_llama2.rs:102-121) with the forced-token rule of
+ * sample_next_token (crates/wgml-chat/src/sampler.rs:102-107) and greedy sampling
+ * (Sampler::sample with temperature 0, models/sampler.rs:33-35), kept on the device: token ids,
+ * position, logits, argmax and the KV cache never leave the GPU and every step replays one CUDA
+ * graph.  h_prompt: n_prompt >= 1 host token ids, the first fed at position start_pos.
+ * h_out_tokens receives n_prompt - 1 + n_gen ids: the token fed at each following position. */
+int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t n_prompt, size_t n_gen,
+                      uint32_t start_pos, uint32_t *h_out_tokens, void *stream);
+/* Number of kernels one decode step launches (for launch accounting). */
+int wgb_llama2_kernels_per_token(const wgb_llama2 *m);
+
+/* ---- GPT-2 ---- */
+
+/* Gpt2Params (models/gpt2/cpu.rs:18-33); usize fields are u32 here. */
+typedef struct {
+    uint32_t n_vocab;
+    uint32_t n_seq;
+    uint32_t n_embd;
+    uint32_t n_head;
+    uint32_t n_layer;
+    uint32_t ff_len;
+    uint32_t attn_b;
+    uint32_t ftype;
+} wgb_gpt2_params;
+/* Gpt2Params::from_gguf (gpt2/cpu.rs:36-47). */
+int wgb_gpt2_params_from_gguf(const wgb_gguf *g, wgb_gpt2_params *out);
+
+/* Gpt2LayerWeights (models/gpt2/transformer.rs:70-94). */
+typedef enum { WGB_G_ATTN_QKV = 0, WGB_G_ATTN_PROJ, WGB_G_MLP_FC, WGB_G_MLP_PROJ } wgb_gpt2_matrix;
+typedef enum {
+    WGB_G_LN_1_G = 0, WGB_G_LN_1_B, WGB_G_LN_2_G, WGB_G_LN_2_B, WGB_G_ATTN_QKV_B, WGB_G_ATTN_PROJ_B,
+    WGB_G_MLP_FC_B, WGB_G_MLP_PROJ_B
+} wgb_gpt2_vector;
+/* Gpt2Weights (transformer.rs:96-106), with layer = -1: matrices WTE / WPE (lm_head is WTE,
+ * transformer.rs:194-195), vectors LN_F_G / LN_F_B. */
+typedef enum { WGB_G_WTE = 0, WGB_G_WPE = 1 } wgb_gpt2_model_matrix;
+typedef enum { WGB_G_LN_F_G = 0, WGB_G_LN_F_B = 1 } wgb_gpt2_model_vector;
+
+/* Gpt2 + Gpt2Weights + Gpt2State (models/gpt2/transformer.rs:14-68,96-106,240-263). */
+typedef struct wgb_gpt2 wgb_gpt2;
+int wgb_gpt2_create(const wgb_gpt2_params *params, wgb_gpt2 **out);
+int wgb_gpt2_destroy(wgb_gpt2 *m);
+int wgb_gpt2_set_matrix(wgb_gpt2 *m, int layer, int which, int qtype, const void *h_blocks,
+                        size_t nrows, size_t ncols);
+int wgb_gpt2_set_vector(wgb_gpt2 *m, int layer, int which, const float *h_data, size_t n);
+/* Gpt2Weights::from_gguf (transformer.rs:109-205).  Matrices stay quantised (the reference
+ * dequantises them to f32 first, transformer.rs:133-140; the products are the same). */
+int wgb_gpt2_load_gguf(wgb_gpt2 *m, const wgb_gguf *g);
+/* As wgb_llama2_set_fused. */
+int wgb_gpt2_set_fused(wgb_gpt2 *m, int enable);
+/* Gpt2::dispatch (transformer.rs:265-477). */
+int wgb_gpt2_forward(wgb_gpt2 *m, uint32_t token, uint32_t pos, void *stream);
+const float *wgb_gpt2_logits(const wgb_gpt2 *m);
+float *wgb_gpt2_key_cache(wgb_gpt2 *m, uint32_t layer);
+float *wgb_gpt2_value_cache(wgb_gpt2 *m, uint32_t layer);
+/* ChatGpt2::forward's loop (crates/wgml-chat/src/chat_gpt2.rs:43-151), greedy, device-resident. */
+int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_prompt, size_t n_gen,
+                    uint32_t start_pos, uint32_t *h_out_tokens, void *stream);
+int wgb_gpt2_kernels_per_token(const wgb_gpt2 *m);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WGML_B200_H */

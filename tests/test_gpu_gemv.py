@@ -1,0 +1,96 @@
+"""GemvQuant parity: CUDA (through the C ABI) against the oracle's dequantise-then-dot.
+
+Tolerance: 1e-3 relative / 1e-4 absolute against the oracle's double-precision accumulation of the
+same bit-exact weights.  The oracle's f32 result (sequential summation, as nalgebra does) carries its
+own rounding error of up to about K * 2^-24 * sum|w x|, so against it the absolute term is widened
+by that bound."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import ATOL, RTOL, assert_close
+from wgml_b200 import ops, synth
+
+pytestmark = pytest.mark.gpu
+ALL = [ops.F32, ops.F16, ops.Q4_0, ops.Q4_1, ops.Q5_0, ops.Q5_1, ops.Q8_0, ops.Q4_K, ops.Q5_K, ops.Q6_K, ops.Q8_K]
+
+
+def make(qtype, nrows, ncols, seed):
+    qt, arr = synth.matrix(qtype, nrows, ncols, seed, f"m{qtype}")
+    x = np.random.default_rng(seed + 1).standard_normal(ncols).astype(np.float32)
+    return np.ascontiguousarray(arr).view(np.uint8), x
+
+
+def check(qtype, raw, nrows, ncols, x, out):
+    o32, o64 = oracle.gemv_quant(qtype, raw, nrows, ncols, x, want_f64=True)
+    assert_close(out, o64, RTOL, ATOL, f"qtype {qtype} {nrows}x{ncols} vs f64 oracle")
+    w = oracle.dequantize(qtype, raw).reshape(nrows, ncols)
+    bound = ncols * 2.0 ** -24 * (np.abs(w.astype(np.float64)) @ np.abs(x.astype(np.float64)))
+    err = np.abs(out.astype(np.float64) - o32)
+    assert (err <= ATOL + RTOL * np.abs(o32) + bound).all(), f"qtype {qtype}: vs f32 oracle, worst {err.max()}"
+
+
+@pytest.mark.parametrize("qtype", ALL)
+@pytest.mark.parametrize("shape", [(4, 256), (37, 512), (1757, 768), (1024, 2816)])
+def test_gemv_small(qtype, shape):
+    nrows, ncols = shape
+    raw, x = make(qtype, nrows, ncols, 7)
+    m = ops.GpuQuantMatrix(qtype, raw, nrows, ncols)
+    out = torch.full((nrows,), float("nan"), device="cuda")
+    ops.GemvQuant.from_device().dispatch(out, m, torch.from_numpy(x).cuda())
+    check(qtype, raw, nrows, ncols, x, out.cpu().numpy())
+
+
+@pytest.mark.parametrize("qtype", [ops.Q4_K, ops.Q8_0, ops.Q6_K, ops.Q5_0, ops.F32])
+def test_gemv_raw_blocks_on_device(qtype):
+    nrows, ncols = 130, 1024
+    raw, x = make(qtype, nrows, ncols, 11)
+    out = torch.zeros(nrows, device="cuda")
+    ops.GemvQuant.from_device().dispatch_raw(out, qtype, torch.from_numpy(raw).cuda(), nrows, ncols, torch.from_numpy(x).cuda())
+    check(qtype, raw, nrows, ncols, x, out.cpu().numpy())
+
+
+@pytest.mark.parametrize("qtype", [ops.Q8_0, ops.Q4_K, ops.Q6_K])
+@pytest.mark.parametrize("shape", [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)])
+def test_gemv_microbench_shapes_vs_oracle(qtype, shape):
+    """The GEMV microbench configurations at full size."""
+    nrows, ncols = shape
+    raw, x = make(qtype, nrows, ncols, 13)
+    m = ops.GpuQuantMatrix(qtype, raw, nrows, ncols)
+    out = torch.zeros(nrows, device="cuda")
+    g = ops.GemvQuant.from_device()
+    xd = torch.from_numpy(x).cuda()
+    g.dispatch(out, m, xd)
+    o = out.cpu().numpy()
+    check(qtype, raw, nrows, ncols, x, o)
+    # linearity: W(2x - 3y) = 2Wx - 3Wy (size-independent property)
+    y = torch.randn(ncols, device="cuda", generator=torch.Generator("cuda").manual_seed(3))
+    out_y, out_c = torch.zeros_like(out), torch.zeros_like(out)
+    g.dispatch(out_y, m, y)
+    g.dispatch(out_c, m, (2 * xd - 3 * y).contiguous())
+    lin = (2 * out - 3 * out_y).cpu().numpy()
+    scale = float(np.abs(lin).max())
+    assert np.abs(out_c.cpu().numpy() - lin).max() <= 1e-5 * scale
+
+
+def test_gemv_70b_and_gpt2_shapes():
+    for qtype, (nrows, ncols) in [(ops.Q4_K, (1024, 8192)), (ops.Q4_K, (8192, 28672)), (ops.Q8_0, (2304, 768)),
+                                  (ops.Q8_0, (50257, 768)), (ops.Q8_0, (768, 3072))]:
+        raw, x = make(qtype, nrows, ncols, 17)
+        m = ops.GpuQuantMatrix(qtype, raw, nrows, ncols)
+        out = torch.zeros(nrows, device="cuda")
+        ops.GemvQuant.from_device().dispatch(out, m, torch.from_numpy(x).cuda())
+        check(qtype, raw, nrows, ncols, x, out.cpu().numpy())
+
+
+def test_gemv_dimension_mismatch_is_an_error():
+    raw, x = make(ops.Q4_K, 8, 256, 1)
+    m = ops.GpuQuantMatrix(ops.Q4_K, raw, 8, 256)
+    g = ops.GemvQuant.from_device()
+    with pytest.raises(ops.WgbError):
+        g.dispatch(torch.zeros(8, device="cuda"), m, torch.zeros(255, device="cuda"))
+    with pytest.raises(ops.WgbError):
+        ops.GpuQuantMatrix(ops.Q4_K, raw, 8, 250)
+    with pytest.raises(ops.WgbError):
+        ops.GpuQuantMatrix(9, raw, 8, 256)  # Q8_1: unsupported by the reference as well

@@ -1,0 +1,336 @@
+// Decode attention over the KV cache: one query position against keys / values 0..=pos.
+//
+// Semantics: BatchedMultiqueryAttention (crates/wgml/src/ops/batched_multiquery_attention.rs:141-195,
+// batched_multiquery_attention.wgsl:38-99): score_t = (q_h . k_t) / sqrt(head_size), softmax with
+// the maximum subtracted, xb_h = sum_t p_t v_t; query head h reads KV head h / kv_mul.
+//
+// Split kernel (the hot path): grid (time chunks of 64, KV heads).  A block computes, for every
+// query head of its KV head, the scores of its chunk, the chunk maximum, the exponentials and the
+// weighted sum of its 64 value rows; (max, sum, vector) go to a scratch buffer.  The block that
+// finishes last for a KV head (an atomic ticket, nobody waits) merges the chunks.  K and V rows
+// are read once for all kv_mul query heads.
+//
+// Full kernel (API path that returns the attention weights): one block per query head, the
+// probabilities are materialised in the caller's [n_heads][seq_len] buffer.
+#include "kernels.h"
+
+namespace wgb {
+
+constexpr int ATT_NT = 256;
+constexpr int ATT_WARPS = ATT_NT / 32;
+constexpr int ATT_CHUNK = 64;
+
+uint32_t attn_num_splits(uint32_t seq_len) { return (seq_len + ATT_CHUNK - 1) / ATT_CHUNK; }
+
+size_t attn_scratch_floats(uint32_t n_heads, uint32_t head_size, uint32_t seq_len)
+{
+    return (size_t)n_heads * attn_num_splits(seq_len) * (head_size + 4);
+}
+
+// QH = query heads per KV head handled at once; VC = float4 chunks of a head per lane (1: head
+// sizes up to 128, 2: up to 256).
+template <int QH, int VC>
+__global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constant__ AttnArgs a)
+{
+    __shared__ float s_score[QH][ATT_CHUNK];
+    __shared__ float s_red[QH][ATT_WARPS];
+    __shared__ float s_acc[ATT_WARPS][QH][VC * 128 + 4];
+    __shared__ uint32_t s_last;
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    const uint32_t pos = a.pos ? *a.pos : a.p.pos;
+    const uint32_t hs = a.p.head_size, kv_dim = a.p.kv_dim, kv_mul = a.p.kv_mul;
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y;
+    const uint32_t t0 = split * ATT_CHUNK;
+    if (t0 > pos) return;
+    const uint32_t nt = min((uint32_t)ATT_CHUNK, pos + 1 - t0);
+    const uint32_t nsplit_active = pos / ATT_CHUNK + 1;
+    const uint32_t max_splits = gridDim.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t nchunk = hs / 4;  // float4 chunks per head
+    const float inv_sqrt = sqrtf((float)hs);
+
+    // query heads of this KV head: h = kvh * kv_mul + j, j = hq0 .. hq0 + QH - 1 (looped by caller grid.z)
+    const uint32_t hq0 = blockIdx.z * QH;
+    float4 q[QH][VC];
+#pragma unroll
+    for (int j = 0; j < QH; j++)
+#pragma unroll
+        for (int c = 0; c < VC; c++) {
+            const uint32_t ch = lane + 32 * c;
+            q[j][c] = (ch < nchunk && hq0 + j < kv_mul)
+                          ? __ldcg(reinterpret_cast<const float4 *>(a.q + (size_t)(kvh * kv_mul + hq0 + j) * hs) + ch)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+
+    // Pass 1: scores of the chunk.
+    const float *kbase = a.k_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
+    for (uint32_t tl = warp; tl < nt; tl += ATT_WARPS) {
+        float part[QH];
+#pragma unroll
+        for (int j = 0; j < QH; j++) part[j] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < VC; c++) {
+            const uint32_t ch = lane + 32 * c;
+            if (ch < nchunk) {
+                const float4 k = __ldcs(reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch);
+#pragma unroll
+                for (int j = 0; j < QH; j++)
+                    part[j] += q[j][c].x * k.x + q[j][c].y * k.y + q[j][c].z * k.z + q[j][c].w * k.w;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < QH; j++) {
+            const float s = warp_sum(part[j]) / inv_sqrt;
+            if (lane == 0) s_score[j][tl] = s;
+        }
+    }
+    __syncthreads();
+
+    // Chunk maximum per query head, then exponentials and their sum.
+    float mx[QH], sum[QH];
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        float m = -INFINITY;
+        for (uint32_t tl = threadIdx.x; tl < nt; tl += ATT_NT) m = fmaxf(m, s_score[j][tl]);
+        m = warp_max(m);
+        if (lane == 0) s_red[j][warp] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        float m = s_red[j][0];
+#pragma unroll
+        for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, s_red[j][w]);
+        mx[j] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        float s = 0.0f;
+        for (uint32_t tl = threadIdx.x; tl < nt; tl += ATT_NT) {
+            const float e = expf(s_score[j][tl] - mx[j]);
+            s_score[j][tl] = e;
+            s += e;
+        }
+        s = warp_sum(s);
+        if (lane == 0) s_red[j][warp] = s;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) s += s_red[j][w];
+        sum[j] = s;
+    }
+
+    // Pass 2: weighted sum of the value rows.
+    float4 acc[QH][VC];
+#pragma unroll
+    for (int j = 0; j < QH; j++)
+#pragma unroll
+        for (int c = 0; c < VC; c++) acc[j][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float *vbase = a.v_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
+    for (uint32_t tl = warp; tl < nt; tl += ATT_WARPS) {
+#pragma unroll
+        for (int c = 0; c < VC; c++) {
+            const uint32_t ch = lane + 32 * c;
+            if (ch < nchunk) {
+                const float4 v = __ldcs(reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch);
+#pragma unroll
+                for (int j = 0; j < QH; j++) {
+                    const float p = s_score[j][tl];
+                    acc[j][c].x = fmaf(p, v.x, acc[j][c].x);
+                    acc[j][c].y = fmaf(p, v.y, acc[j][c].y);
+                    acc[j][c].z = fmaf(p, v.z, acc[j][c].z);
+                    acc[j][c].w = fmaf(p, v.w, acc[j][c].w);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < QH; j++)
+#pragma unroll
+        for (int c = 0; c < VC; c++) {
+            const uint32_t ch = lane + 32 * c;
+            if (ch < nchunk) reinterpret_cast<float4 *>(&s_acc[warp][j][0])[ch] = acc[j][c];
+        }
+    __syncthreads();
+
+    // Partial result of this chunk -> scratch [head][split][hs + 4] = {vector, max, sum}.
+    for (uint32_t e = threadIdx.x; e < QH * hs; e += ATT_NT) {
+        const uint32_t j = e / hs, i = e % hs;
+        if (hq0 + j >= kv_mul) continue;
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) s += s_acc[w][j][i];
+        const uint32_t h = kvh * kv_mul + hq0 + j;
+        a.scratch[((size_t)h * max_splits + split) * (hs + 4) + i] = s;
+    }
+    if (threadIdx.x < QH && hq0 + threadIdx.x < kv_mul) {
+        const uint32_t h = kvh * kv_mul + hq0 + threadIdx.x;
+        float *dst = a.scratch + ((size_t)h * max_splits + split) * (hs + 4) + hs;
+        float m = mx[0], s = sum[0];
+#pragma unroll
+        for (int j = 1; j < QH; j++) { m = (threadIdx.x == j) ? mx[j] : m; s = (threadIdx.x == j) ? sum[j] : s; }
+        dst[0] = m;
+        dst[1] = s;
+    }
+
+    // Ticket: the last block of this (KV head, query-head group) merges all chunks.
+    __threadfence();
+    __syncthreads();
+    uint32_t *counter = a.counters + kvh * gridDim.z + blockIdx.z;
+    if (threadIdx.x == 0) {
+        const uint32_t ticket = atomicAdd(counter, 1u);
+        s_last = (ticket == nsplit_active - 1);
+        if (s_last) *counter = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (uint32_t e = threadIdx.x; e < QH * hs; e += ATT_NT) {
+        const uint32_t j = e / hs, i = e % hs;
+        if (hq0 + j >= kv_mul) continue;
+        const uint32_t h = kvh * kv_mul + hq0 + j;
+        const float *base = a.scratch + (size_t)h * max_splits * (hs + 4);
+        float M = -INFINITY;
+        for (uint32_t s = 0; s < nsplit_active; s++) M = fmaxf(M, __ldcg(base + (size_t)s * (hs + 4) + hs));
+        float L = 0.0f, o = 0.0f;
+        for (uint32_t s = 0; s < nsplit_active; s++) {
+            const float w = expf(__ldcg(base + (size_t)s * (hs + 4) + hs) - M);
+            L = fmaf(__ldcg(base + (size_t)s * (hs + 4) + hs + 1), w, L);
+            o = fmaf(__ldcg(base + (size_t)s * (hs + 4) + i), w, o);
+        }
+        a.xb[(size_t)h * hs + i] = o / L;
+    }
+}
+
+// One block per query head; writes the attention weights.
+__global__ void __launch_bounds__(ATT_NT) attn_full_kernel(const __grid_constant__ AttnArgs a, float *__restrict__ attn)
+{
+    __shared__ float red[32];
+    const uint32_t pos = a.pos ? *a.pos : a.p.pos;
+    const uint32_t hs = a.p.head_size, kv_dim = a.p.kv_dim;
+    const uint32_t h = blockIdx.x, kvh = h / a.p.kv_mul;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float *att = attn + (size_t)h * a.p.seq_len;
+    const float *qh = a.q + (size_t)h * hs;
+    const float sq = sqrtf((float)hs);
+    for (uint32_t t = warp; t <= pos; t += ATT_WARPS) {
+        const float *k = a.k_cache + (size_t)t * kv_dim + (size_t)kvh * hs;
+        float s = 0.0f;
+        for (uint32_t i = lane; i < hs; i += 32) s = fmaf(qh[i], k[i], s);
+        s = warp_sum(s);
+        if (lane == 0) att[t] = s / sq;
+    }
+    __syncthreads();
+    float m = -INFINITY;
+    for (uint32_t t = threadIdx.x; t <= pos; t += ATT_NT) m = fmaxf(m, att[t]);
+    m = block_max<ATT_NT>(m, red);
+    float sum = 0.0f;
+    for (uint32_t t = threadIdx.x; t <= pos; t += ATT_NT) {
+        const float e = expf(att[t] - m);
+        att[t] = e;
+        sum += e;
+    }
+    sum = block_sum<ATT_NT>(sum, red);
+    for (uint32_t t = threadIdx.x; t <= pos; t += ATT_NT) att[t] = att[t] / sum;
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < hs; i += ATT_NT) {
+        float o = 0.0f;
+        for (uint32_t t = 0; t <= pos; t++) o = fmaf(att[t], a.v_cache[(size_t)t * kv_dim + (size_t)kvh * hs + i], o);
+        a.xb[(size_t)h * hs + i] = o;
+    }
+}
+
+template <int QH, int VC>
+static int launch_split(const AttnArgs &a, uint32_t nsplits, uint32_t n_kv, uint32_t zgroups, cudaStream_t stream, bool pdl)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nsplits, n_kv, zgroups);
+    cfg.blockDim = dim3(ATT_NT);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    WGB_CUDA(cudaLaunchKernelEx(&cfg, attn_split_kernel<QH, VC>, a));
+    return WGB_OK;
+}
+
+// `a.counters` must hold n_kv_heads * ceil(kv_mul / QH) zeroed words (QH as chosen below).
+int launch_attention(const AttnArgs &a, cudaStream_t stream, bool pdl)
+{
+    const wgb_attn_params &p = a.p;
+    WGB_REQUIRE(p.head_size % 4 == 0 && p.head_size <= 256 && p.head_size > 0, "head_size %u unsupported", p.head_size);
+    WGB_REQUIRE(p.kv_mul > 0 && p.n_heads % p.kv_mul == 0, "n_heads %u not a multiple of kv_mul %u", p.n_heads, p.kv_mul);
+    const uint32_t n_kv = p.n_heads / p.kv_mul;
+    const uint32_t nsplits = attn_num_splits(p.seq_len);
+    const bool big = p.head_size > 128;
+    // query heads per block: the largest of 4 / 2 / 1 that divides nothing away (tail heads masked)
+    const uint32_t qh = p.kv_mul >= 4 ? 4 : (p.kv_mul >= 2 ? 2 : 1);
+    const uint32_t zg = (p.kv_mul + qh - 1) / qh;
+    if (qh == 4) return big ? launch_split<4, 2>(a, nsplits, n_kv, zg, stream, pdl) : launch_split<4, 1>(a, nsplits, n_kv, zg, stream, pdl);
+    if (qh == 2) return big ? launch_split<2, 2>(a, nsplits, n_kv, zg, stream, pdl) : launch_split<2, 1>(a, nsplits, n_kv, zg, stream, pdl);
+    return big ? launch_split<1, 2>(a, nsplits, n_kv, zg, stream, pdl) : launch_split<1, 1>(a, nsplits, n_kv, zg, stream, pdl);
+}
+
+}  // namespace wgb
+
+using namespace wgb;
+
+// Scratch of the stand-alone op, grown on demand and kept for the life of the process.
+static float *g_scratch = nullptr;
+static size_t g_scratch_floats = 0;
+static uint32_t *g_counters = nullptr;
+static size_t g_ncounters = 0;
+
+WGB_EXPORT int wgb_attention(const wgb_attn_params *p, const float *d_q, const float *d_key_cache,
+                             const float *d_value_cache, float *d_attn, float *d_xb, void *stream)
+{
+    WGB_REQUIRE(p && d_q && d_key_cache && d_value_cache && d_xb, "null argument");
+    WGB_REQUIRE(p->pos < p->seq_len, "pos %u outside a cache of %u positions", p->pos, p->seq_len);
+    WGB_REQUIRE(p->kv_mul > 0 && p->n_heads % p->kv_mul == 0 && p->kv_dim == (p->n_heads / p->kv_mul) * p->head_size,
+                "inconsistent attention parameters");
+    AttnArgs a = {};
+    a.p = *p;
+    a.pos = nullptr;
+    a.q = d_q;
+    a.k_cache = d_key_cache;
+    a.v_cache = d_value_cache;
+    a.xb = d_xb;
+    if (d_attn) {
+        attn_full_kernel<<<p->n_heads, ATT_NT, 0, as_stream(stream)>>>(a, d_attn);
+        WGB_LAUNCH_CHECK("attn_full_kernel");
+        return WGB_OK;
+    }
+    WGB_REQUIRE(p->head_size % 4 == 0 && p->head_size <= 256, "head_size %u unsupported", p->head_size);
+    const size_t need = attn_scratch_floats(p->n_heads, p->head_size, p->seq_len);
+    if (need > g_scratch_floats) {
+        WGB_CUDA(cudaStreamSynchronize(as_stream(stream)));
+        if (g_scratch) cudaFree(g_scratch);
+        g_scratch = nullptr;
+        g_scratch_floats = 0;
+        WGB_CUDA(cudaMalloc((void **)&g_scratch, need * sizeof(float)));
+        g_scratch_floats = need;
+    }
+    if (p->n_heads > g_ncounters) {
+        WGB_CUDA(cudaStreamSynchronize(as_stream(stream)));
+        if (g_counters) cudaFree(g_counters);
+        g_counters = nullptr;
+        g_ncounters = 0;
+        WGB_CUDA(cudaMalloc((void **)&g_counters, p->n_heads * sizeof(uint32_t)));
+        WGB_CUDA(cudaMemset(g_counters, 0, p->n_heads * sizeof(uint32_t)));
+        g_ncounters = p->n_heads;
+    }
+    a.scratch = g_scratch;
+    a.counters = g_counters;
+    return launch_attention(a, as_stream(stream), false);
+}

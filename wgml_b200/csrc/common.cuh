@@ -1,0 +1,108 @@
+// Shared declarations of the wgml_b200 library: status handling, block geometry, warp helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <string>
+
+#include "../../include/wgml_b200.h"
+
+#define WGB_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace wgb {
+
+// Records the message returned by wgb_last_error() for the calling thread and returns `code`.
+int fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+int cuda_fail(cudaError_t e, const char *what);
+
+#define WGB_CUDA(call)                                                     \
+    do {                                                                   \
+        cudaError_t e__ = (call);                                          \
+        if (e__ != cudaSuccess) return ::wgb::cuda_fail(e__, #call);       \
+    } while (0)
+
+// After a kernel launch: launch-configuration errors surface here, not at the next sync.
+#define WGB_LAUNCH_CHECK(what)                                             \
+    do {                                                                   \
+        cudaError_t e__ = cudaGetLastError();                              \
+        if (e__ != cudaSuccess) return ::wgb::cuda_fail(e__, what);        \
+    } while (0)
+
+#define WGB_REQUIRE(cond, ...)                                             \
+    do {                                                                   \
+        if (!(cond)) return ::wgb::fail(WGB_ERR_INVALID, __VA_ARGS__);     \
+    } while (0)
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Number of SMs of the current device (148 on B200); cached per process.
+int sm_count();
+
+__host__ __device__ constexpr int block_bytes(int qtype)
+{
+    return qtype == WGB_F32 ? 4 : qtype == WGB_F16 ? 2 : qtype == WGB_Q4_0 ? 18 : qtype == WGB_Q4_1 ? 20
+         : qtype == WGB_Q5_0 ? 22 : qtype == WGB_Q5_1 ? 24 : qtype == WGB_Q8_0 ? 34 : qtype == WGB_Q4_K ? 144
+         : qtype == WGB_Q5_K ? 176 : qtype == WGB_Q6_K ? 210 : qtype == WGB_Q8_K ? 292 : 0;
+}
+
+__host__ __device__ constexpr int block_len(int qtype)
+{
+    return (qtype == WGB_F32 || qtype == WGB_F16) ? 1
+         : (qtype == WGB_Q4_0 || qtype == WGB_Q4_1 || qtype == WGB_Q5_0 || qtype == WGB_Q5_1 || qtype == WGB_Q8_0) ? 32
+         : (qtype == WGB_Q4_K || qtype == WGB_Q5_K || qtype == WGB_Q6_K || qtype == WGB_Q8_K) ? 256 : 0;
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a thread block of NT threads (NT a multiple of 32, <= 1024); every thread gets the
+// result.  `red` is shared scratch of at least 32 floats; safe to call repeatedly.
+template <int NT>
+__device__ __forceinline__ float block_sum(float v, float *red)
+{
+    v = warp_sum(v);
+    if (NT == 32) return v;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < NT / 32) ? red[lane] : 0.0f;
+    return warp_sum(t);
+}
+
+template <int NT>
+__device__ __forceinline__ float block_max(float v, float *red)
+{
+    v = warp_max(v);
+    if (NT == 32) return v;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < NT / 32) ? red[lane] : -INFINITY;
+    return warp_max(t);
+}
+
+// Programmatic dependent launch (sm_90+): `pdl_wait` blocks until the preceding kernel in the
+// stream has completed and its writes are visible; `pdl_launch_dependents` lets the following
+// kernel start its independent prologue.  Both are no-ops for a kernel launched without the
+// programmatic-serialization attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+#endif
+
+}  // namespace wgb

@@ -1,0 +1,88 @@
+// Internal C++ interface between the kernel files and the model / API files of the library.
+#pragma once
+
+#include "common.cuh"
+#include "qmatrix.cuh"
+
+namespace wgb {
+
+// ---- fused matrix-vector kernel ------------------------------------------------------------
+
+enum Prologue {
+    PRO_NONE = 0,  // x used as is
+    PRO_RMS = 1,   // x <- (x * 1/sqrt(mean(x^2) + eps)) * norm_w          (RmsNorm, ops/rms_norm.wgsl:58-67)
+    PRO_LN = 2     // x <- ((x - mean) * 1/sqrt(var + 1e-5)) * norm_w + norm_b (LayerNorm + Mul + Add)
+};
+
+enum Epilogue {
+    EPI_STORE = 0,     // out[r] = y (+ bias[r])
+    EPI_RESIDUAL = 1,  // out[r] = residual[r] + y (+ bias[r]); out may alias residual
+    EPI_SILU_PAIR = 2, // matrices {gate, up}: out[r] = up_r * gate_r / (1 + exp(-gate_r))   (Silu, ops/silu.wgsl:19-27)
+    EPI_GELU = 3,      // out[r] = gelu(y + bias[r])                                       (unary.wgsl:50-52)
+    EPI_QKV_ROPE = 4,  // matrices {q, k, v}: (+bias), rotate q and k (RoPE), q -> out, k/v -> cache row *pos
+    EPI_QKV_SPLIT = 5  // one fused qkv matrix (+bias): rows [0,n) -> out, [n,2n) -> k cache, [2n,3n) -> v cache
+};
+
+struct GemvArgs {
+    QMat mat[3];
+    int nmat;
+    const float *x;          // input vector, mat[0].ncols floats
+    // prologue
+    int prologue;
+    const float *norm_w, *norm_b;
+    float eps;
+    // epilogue
+    int epilogue;
+    float *out;
+    const float *bias;       // optional; for EPI_QKV_ROPE: bias of q
+    const float *bias_k, *bias_v;
+    const float *residual;
+    // EPI_QKV_*: KV cache rows and the position, read on the device
+    float *k_cache, *v_cache;   // [seq_len][kv_dim]
+    const uint32_t *pos;        // device scalar
+    uint32_t kv_dim, head_size;
+    int rope_variant;
+    const float *rope_freq;     // head_size/2 inverse frequencies base^(-2j/head_size)
+    // optional copy of the normalised input (first block writes it); NULL to skip
+    float *x_norm_out;
+};
+
+// Enqueues one fused kernel.  All matrices must share format and ncols and have a fast path;
+// returns WGB_ERR_UNSUPPORTED otherwise so that the caller can fall back to separate ops.
+// `pdl` launches with programmatic stream serialization (the kernel prefetches its first
+// weights before waiting for its predecessor).
+int launch_gemv(const GemvArgs &a, cudaStream_t stream, bool pdl);
+bool gemv_fast_supported(const QMat &m);
+
+// Slow path for any format: one warp per row, dequantising with the exact block formulas.
+int launch_gemv_generic(const QMat &m, const float *x, float *out, cudaStream_t stream);
+
+// ---- attention ------------------------------------------------------------------------------
+struct AttnArgs {
+    wgb_attn_params p;          // p.pos is ignored when pos != NULL
+    const uint32_t *pos;        // device scalar or NULL
+    const float *q, *k_cache, *v_cache;
+    float *xb;
+    float *scratch;             // attn_scratch_floats() floats
+    uint32_t *counters;         // n_kv_heads counters, zero before the first launch
+};
+size_t attn_scratch_floats(uint32_t n_heads, uint32_t head_size, uint32_t seq_len);
+uint32_t attn_num_splits(uint32_t seq_len);
+int launch_attention(const AttnArgs &a, cudaStream_t stream, bool pdl);
+
+// ---- small ops used by the models -------------------------------------------------------------
+// x[0..n) = row *d_token of the embedding matrix (+ row *d_pos of `pos_embd` when given).
+int launch_embed(const QMat &embd, const QMat *pos_embd, const uint32_t *d_token, const uint32_t *d_pos,
+                 float *x, cudaStream_t stream);
+// Greedy sampling step kept on the device: next = step+1 < n_prompt ? prompt[step+1] : argmax(logits);
+// token <- next, pos <- pos+1, out_tokens[step] <- next, step <- step+1.
+struct LoopState {
+    uint32_t *token, *pos, *step;       // device scalars
+    const uint32_t *prompt;             // device, n_prompt ids
+    uint32_t n_prompt;
+    uint32_t *out_tokens;               // device
+};
+int launch_argmax_advance(const float *logits, uint32_t n, const LoopState &ls, uint32_t *scratch,
+                          cudaStream_t stream);
+
+}  // namespace wgb

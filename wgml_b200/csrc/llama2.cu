@@ -1,0 +1,645 @@
+// Llama-2 family decoder: weights, state, one-token forward and the device-resident greedy loop.
+//
+// Follows Llama2::dispatch (crates/wgml/src/models/llama2/transformer.rs:298-431) and the token
+// loop of ChatLlama2::forward (crates/wgml-chat/src/chat_llama2.rs:102-228).  Two schedules:
+//   fused    5 launches per layer:  [RMSNorm + Q/K/V products + bias + RoPE + KV append]
+//            [split attention]  [O product + residual]  [RMSNorm + gate/up products + SiLU]
+//            [down product + residual], then [RMSNorm + output product], argmax.
+//   unfused  one launch per reference dispatch, in the reference's order.
+// Token id, position, logits and the KV cache live on the device; a decode step is captured
+// once into a CUDA graph and replayed per token.
+#include "kernels.h"
+
+#include <cmath>
+#include <cstdlib>
+#include <new>
+#include <vector>
+
+namespace wgb {
+void rope_inv_freq(uint32_t head_size, float base, float *out);
+}
+
+using namespace wgb;
+
+struct wgb_llama2 {
+    wgb_llama2_config cfg;
+    int model_type, tp_rank, tp_size;
+    uint32_t head_size, kv_mul;
+    // per-rank sizes
+    uint32_t n_q_local, n_kv_local, q_dim, kv_dim, hidden;
+    uint32_t hidden_blk0, hidden_blks;   // this rank's slice of the FFN dimension in 256-column blocks
+    struct Layer {
+        wgb_quant_matrix *m[7] = {};
+        float *v[5] = {};
+    };
+    std::vector<Layer> layers;
+    wgb_quant_matrix *token_embd = nullptr, *output = nullptr;
+    float *output_norm = nullptr;
+    // state (Llama2State, transformer.rs:17-45)
+    float *x = nullptr, *xb = nullptr, *xb2 = nullptr, *hb = nullptr, *hb2 = nullptr, *q = nullptr, *logits = nullptr;
+    float *tk = nullptr, *tv = nullptr;      // unfused path: K / V projections before RoPE + append
+    float *key_cache = nullptr, *value_cache = nullptr;  // [n_layers][seq_len][kv_dim]
+    float *attn_scratch = nullptr;
+    uint32_t *attn_counters = nullptr;
+    float *rope_freq = nullptr;
+    uint32_t *scalars = nullptr;             // token, pos, step
+    uint32_t *argmax_scratch = nullptr;
+    uint32_t *d_prompt = nullptr, *d_out = nullptr;
+    size_t prompt_cap = 0, out_cap = 0;
+    bool fused = true, use_pdl = true;
+    cudaGraphExec_t graph = nullptr;
+    uint32_t graph_n_prompt = 0;
+    void *comm = nullptr;
+    int kernels_per_token = 0;
+};
+
+namespace {
+
+__global__ void set_scalars_kernel(uint32_t *s, uint32_t token, uint32_t pos, uint32_t step)
+{
+    s[0] = token;
+    s[1] = pos;
+    s[2] = step;
+}
+
+// Unfused path: bias, RoPE and KV append for one position (the work of the OpAssign / RoPE
+// dispatches of transformer.rs:343-365, plus the write into cache column `pos`).
+__global__ void qkv_finish_kernel(float *__restrict__ q, const float *__restrict__ tk, const float *__restrict__ tv,
+                                  const float *__restrict__ bq, const float *__restrict__ bk, const float *__restrict__ bv,
+                                  float *__restrict__ k_cache, float *__restrict__ v_cache, const uint32_t *__restrict__ d_pos,
+                                  uint32_t q_dim, uint32_t kv_dim, uint32_t head_size, int variant,
+                                  const float *__restrict__ freq)
+{
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;  // pair index over q
+    if (2 * i >= q_dim) return;
+    const uint32_t pos = *d_pos;
+    const uint32_t half = head_size / 2;
+    float sn, cs;
+    sincosf((float)pos * freq[i % half], &sn, &cs);
+    uint32_t ia, ib;
+    if (variant == WGB_ROPE_ORIGINAL) { ia = 2 * i; ib = ia + 1; }
+    else { ia = i + ((2 * i) / head_size) * half; ib = ia + half; }
+    float x = q[ia] + (bq ? bq[ia] : 0.0f), y = q[ib] + (bq ? bq[ib] : 0.0f);
+    q[ia] = cs * x - sn * y;
+    q[ib] = sn * x + cs * y;
+    if (2 * i < kv_dim) {
+        float *kc = k_cache + (size_t)pos * kv_dim, *vc = v_cache + (size_t)pos * kv_dim;
+        x = tk[ia] + (bk ? bk[ia] : 0.0f);
+        y = tk[ib] + (bk ? bk[ib] : 0.0f);
+        kc[ia] = cs * x - sn * y;
+        kc[ib] = sn * x + cs * y;
+        vc[ia] = tv[ia] + (bv ? bv[ia] : 0.0f);
+        vc[ib] = tv[ib] + (bv ? bv[ib] : 0.0f);
+    }
+}
+
+int dalloc(float **p, size_t n)
+{
+    WGB_CUDA(cudaMalloc((void **)p, n * sizeof(float)));
+    WGB_CUDA(cudaMemset(*p, 0, n * sizeof(float)));
+    return WGB_OK;
+}
+
+bool fusable(const wgb_llama2 *m)
+{
+    for (const auto &l : m->layers) {
+        for (int i = 0; i < 7; i++)
+            if (!l.m[i] || !gemv_fast_supported(l.m[i]->view)) return false;
+        const QMat &q = l.m[WGB_L_ATTN_Q]->view, &k = l.m[WGB_L_ATTN_K]->view, &v = l.m[WGB_L_ATTN_V]->view;
+        if (q.qtype != k.qtype || q.qtype != v.qtype) return false;
+        if (l.m[WGB_L_FFN_GATE]->view.qtype != l.m[WGB_L_FFN_UP]->view.qtype) return false;
+    }
+    const wgb_quant_matrix *out = m->output ? m->output : m->token_embd;
+    return out && gemv_fast_supported(out->view);
+}
+
+int check_complete(const wgb_llama2 *m)
+{
+    for (size_t l = 0; l < m->layers.size(); l++) {
+        for (int i = 0; i < 7; i++)
+            if (!m->layers[l].m[i]) return fail(WGB_ERR_NOT_FOUND, "layer %zu: matrix %d was never set", l, i);
+        for (int i = 0; i < 2; i++)
+            if (!m->layers[l].v[i]) return fail(WGB_ERR_NOT_FOUND, "layer %zu: norm vector %d was never set", l, i);
+    }
+    if (!m->token_embd) return fail(WGB_ERR_NOT_FOUND, "token_embd.weight was never set");
+    if (!m->output_norm) return fail(WGB_ERR_NOT_FOUND, "output_norm.weight was never set");
+    return WGB_OK;
+}
+
+// Plain product out = W . x through the fast kernel when there is one.
+int mat_vec(const QMat &w, const float *x, float *out, cudaStream_t s)
+{
+    if (gemv_fast_supported(w)) {
+        GemvArgs a = {};
+        a.mat[0] = w;
+        a.nmat = 1;
+        a.x = x;
+        a.epilogue = EPI_STORE;
+        a.out = out;
+        return launch_gemv(a, s, false);
+    }
+    return launch_gemv_generic(w, x, out, s);
+}
+
+// Enqueues one token forward reading token / position from the device scalars.
+int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
+{
+    const wgb_llama2_config &c = m->cfg;
+    const uint32_t *d_token = m->scalars, *d_pos = m->scalars + 1;
+    const bool fused = m->fused && fusable(m);
+    const bool pdl = m->use_pdl;
+    const int variant = m->model_type == WGB_QWEN2 ? WGB_ROPE_NEOX : WGB_ROPE_ORIGINAL;
+    int n = 0;
+    int rc = launch_embed(m->token_embd->view, nullptr, d_token, d_pos, m->x, s);
+    if (rc) return rc;
+    n++;
+    const size_t cache_stride = (size_t)c.seq_len * m->kv_dim;
+    AttnArgs at = {};
+    at.p.seq_len = c.seq_len;
+    at.p.kv_dim = m->kv_dim;
+    at.p.kv_mul = m->kv_mul;
+    at.p.n_heads = m->n_q_local;
+    at.p.head_size = m->head_size;
+    at.pos = d_pos;
+    at.q = m->q;
+    at.xb = m->xb;
+    at.scratch = m->attn_scratch;
+    at.counters = m->attn_counters;
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        const wgb_llama2::Layer &w = m->layers[l];
+        float *kc = m->key_cache + l * cache_stride, *vc = m->value_cache + l * cache_stride;
+        at.k_cache = kc;
+        at.v_cache = vc;
+        if (fused) {
+            GemvArgs a = {};
+            a.mat[0] = w.m[WGB_L_ATTN_Q]->view;
+            a.mat[1] = w.m[WGB_L_ATTN_K]->view;
+            a.mat[2] = w.m[WGB_L_ATTN_V]->view;
+            a.nmat = 3;
+            a.x = m->x;
+            a.prologue = PRO_RMS;
+            a.norm_w = w.v[WGB_L_ATTN_NORM];
+            a.eps = c.rms_norm_eps;
+            a.epilogue = EPI_QKV_ROPE;
+            a.out = m->q;
+            a.bias = w.v[WGB_L_ATTN_Q_BIAS];
+            a.bias_k = w.v[WGB_L_ATTN_K_BIAS];
+            a.bias_v = w.v[WGB_L_ATTN_V_BIAS];
+            a.k_cache = kc;
+            a.v_cache = vc;
+            a.pos = d_pos;
+            a.kv_dim = m->kv_dim;
+            a.head_size = m->head_size;
+            a.rope_variant = variant;
+            a.rope_freq = m->rope_freq;
+            if ((rc = launch_gemv(a, s, pdl))) return rc;
+            if ((rc = launch_attention(at, s, pdl))) return rc;
+            GemvArgs o = {};
+            o.mat[0] = w.m[WGB_L_ATTN_OUTPUT]->view;
+            o.nmat = 1;
+            o.x = m->xb;
+            o.epilogue = EPI_RESIDUAL;
+            o.residual = m->x;
+            o.out = m->x;
+            if ((rc = launch_gemv(o, s, pdl))) return rc;
+            GemvArgs f = {};
+            f.mat[0] = w.m[WGB_L_FFN_GATE]->view;
+            f.mat[1] = w.m[WGB_L_FFN_UP]->view;
+            f.nmat = 2;
+            f.x = m->x;
+            f.prologue = PRO_RMS;
+            f.norm_w = w.v[WGB_L_FFN_NORM];
+            f.eps = c.rms_norm_eps;
+            f.epilogue = EPI_SILU_PAIR;
+            f.out = m->hb;
+            if ((rc = launch_gemv(f, s, pdl))) return rc;
+            GemvArgs d = {};
+            d.mat[0] = w.m[WGB_L_FFN_DOWN]->view;
+            d.nmat = 1;
+            d.x = m->hb;
+            d.epilogue = EPI_RESIDUAL;
+            d.residual = m->x;
+            d.out = m->x;
+            if ((rc = launch_gemv(d, s, pdl))) return rc;
+            n += 5;
+        } else {
+            // transformer.rs:312-407, dispatch by dispatch
+            if ((rc = wgb_rms_norm(m->xb, m->x, w.v[WGB_L_ATTN_NORM], c.dim, c.rms_norm_eps, s))) return rc;
+            if ((rc = mat_vec(w.m[WGB_L_ATTN_Q]->view, m->xb, m->q, s))) return rc;
+            if ((rc = mat_vec(w.m[WGB_L_ATTN_K]->view, m->xb, m->tk, s))) return rc;
+            if ((rc = mat_vec(w.m[WGB_L_ATTN_V]->view, m->xb, m->tv, s))) return rc;
+            qkv_finish_kernel<<<(m->q_dim / 2 + 127) / 128, 128, 0, s>>>(
+                m->q, m->tk, m->tv, w.v[WGB_L_ATTN_Q_BIAS], w.v[WGB_L_ATTN_K_BIAS], w.v[WGB_L_ATTN_V_BIAS], kc, vc, d_pos,
+                m->q_dim, m->kv_dim, m->head_size, variant, m->rope_freq);
+            WGB_LAUNCH_CHECK("qkv_finish_kernel");
+            if ((rc = launch_attention(at, s, false))) return rc;
+            if ((rc = mat_vec(w.m[WGB_L_ATTN_OUTPUT]->view, m->xb, m->xb2, s))) return rc;
+            if ((rc = wgb_op_assign(WGB_ASSIGN_ADD, m->x, m->xb2, c.dim, s))) return rc;
+            if ((rc = wgb_rms_norm(m->xb, m->x, w.v[WGB_L_FFN_NORM], c.dim, c.rms_norm_eps, s))) return rc;
+            if ((rc = mat_vec(w.m[WGB_L_FFN_GATE]->view, m->xb, m->hb, s))) return rc;
+            if ((rc = mat_vec(w.m[WGB_L_FFN_UP]->view, m->xb, m->hb2, s))) return rc;
+            if ((rc = wgb_silu(m->hb, m->hb2, m->hidden, s))) return rc;
+            if ((rc = mat_vec(w.m[WGB_L_FFN_DOWN]->view, m->hb, m->xb2, s))) return rc;
+            if ((rc = wgb_op_assign(WGB_ASSIGN_ADD, m->x, m->xb2, c.dim, s))) return rc;
+            n += 14;
+        }
+    }
+    const QMat &outw = (m->output ? m->output : m->token_embd)->view;
+    if (fused) {
+        GemvArgs a = {};
+        a.mat[0] = outw;
+        a.nmat = 1;
+        a.x = m->x;
+        a.prologue = PRO_RMS;
+        a.norm_w = m->output_norm;
+        a.eps = c.rms_norm_eps;
+        a.epilogue = EPI_STORE;
+        a.out = m->logits;
+        if ((rc = launch_gemv(a, s, pdl))) return rc;
+        n += 1;
+    } else {
+        if ((rc = wgb_rms_norm(m->xb, m->x, m->output_norm, c.dim, c.rms_norm_eps, s))) return rc;
+        if ((rc = mat_vec(outw, m->xb, m->logits, s))) return rc;
+        n += 2;
+    }
+    if (nkernels) *nkernels = n;
+    return WGB_OK;
+}
+
+void drop_graph(wgb_llama2 *m)
+{
+    if (m->graph) cudaGraphExecDestroy(m->graph);
+    m->graph = nullptr;
+}
+
+}  // namespace
+
+WGB_EXPORT int wgb_llama2_create(const wgb_llama2_config *cfg, int model_type, int tp_rank, int tp_size, wgb_llama2 **out)
+{
+    WGB_REQUIRE(cfg && out, "null argument");
+    WGB_REQUIRE(model_type == WGB_LLAMA || model_type == WGB_QWEN2, "unknown model type %d", model_type);
+    WGB_REQUIRE(tp_size >= 1 && tp_rank >= 0 && tp_rank < tp_size, "bad tensor-parallel rank %d of %d", tp_rank, tp_size);
+    const wgb_llama2_config &c = *cfg;
+    WGB_REQUIRE(c.dim && c.hidden_dim && c.n_layers && c.n_q_heads && c.n_kv_heads && c.vocab_size && c.seq_len, "zero-sized config");
+    WGB_REQUIRE(c.dim % c.n_q_heads == 0 && c.n_q_heads % c.n_kv_heads == 0, "head counts do not divide the model dimension");
+    const uint32_t hs = c.dim / c.n_q_heads;
+    WGB_REQUIRE(hs % 4 == 0 && hs <= 256, "head size %u unsupported (multiple of 4, at most 256)", hs);
+    WGB_REQUIRE(c.dim % 4 == 0 && c.hidden_dim % 4 == 0, "dimensions must be multiples of 4");
+    WGB_REQUIRE(c.n_kv_heads % tp_size == 0, "n_kv_heads %u is not a multiple of the tensor-parallel size %d", c.n_kv_heads, tp_size);
+    wgb_llama2 *m = new (std::nothrow) wgb_llama2();
+    if (!m) return fail(WGB_ERR_INVALID, "out of host memory");
+    m->cfg = c;
+    m->model_type = model_type;
+    m->tp_rank = tp_rank;
+    m->tp_size = tp_size;
+    m->head_size = hs;
+    m->kv_mul = c.n_q_heads / c.n_kv_heads;
+    m->n_kv_local = c.n_kv_heads / tp_size;
+    m->n_q_local = m->n_kv_local * m->kv_mul;
+    m->q_dim = m->n_q_local * hs;
+    m->kv_dim = m->n_kv_local * hs;
+    if (tp_size == 1) {
+        m->hidden_blk0 = 0;
+        m->hidden_blks = 0;
+        m->hidden = c.hidden_dim;
+    } else {
+        if (c.hidden_dim % 256 != 0) { delete m; return fail(WGB_ERR_INVALID, "tensor parallelism needs hidden_dim %% 256 == 0"); }
+        const uint32_t nb = c.hidden_dim / 256;
+        m->hidden_blk0 = (uint32_t)((uint64_t)nb * tp_rank / tp_size);
+        m->hidden_blks = (uint32_t)((uint64_t)nb * (tp_rank + 1) / tp_size) - m->hidden_blk0;
+        m->hidden = m->hidden_blks * 256;
+        if (m->hidden == 0) { delete m; return fail(WGB_ERR_INVALID, "more ranks than 256-column FFN blocks"); }
+    }
+    m->layers.resize(c.n_layers);
+    int rc = WGB_OK;
+    const size_t cache = (size_t)c.n_layers * c.seq_len * m->kv_dim;
+    if ((rc = dalloc(&m->x, c.dim)) || (rc = dalloc(&m->xb, c.dim)) || (rc = dalloc(&m->xb2, c.dim)) ||
+        (rc = dalloc(&m->hb, m->hidden)) || (rc = dalloc(&m->hb2, m->hidden)) || (rc = dalloc(&m->q, m->q_dim)) ||
+        (rc = dalloc(&m->tk, m->kv_dim)) || (rc = dalloc(&m->tv, m->kv_dim)) || (rc = dalloc(&m->logits, c.vocab_size)) ||
+        (rc = dalloc(&m->key_cache, cache)) || (rc = dalloc(&m->value_cache, cache)) ||
+        (rc = dalloc(&m->attn_scratch, attn_scratch_floats(m->n_q_local, hs, c.seq_len))) ||
+        (rc = dalloc(&m->rope_freq, hs / 2 + 4))) {
+        wgb_llama2_destroy(m);
+        return rc;
+    }
+    cudaError_t e;
+    if ((e = cudaMalloc((void **)&m->attn_counters, (size_t)m->n_q_local * 4)) != cudaSuccess ||
+        (e = cudaMemset(m->attn_counters, 0, (size_t)m->n_q_local * 4)) != cudaSuccess ||
+        (e = cudaMalloc((void **)&m->scalars, 16)) != cudaSuccess || (e = cudaMemset(m->scalars, 0, 16)) != cudaSuccess ||
+        (e = cudaMalloc((void **)&m->argmax_scratch, 64 * 8)) != cudaSuccess) {
+        wgb_llama2_destroy(m);
+        return cuda_fail(e, "cudaMalloc(model state)");
+    }
+    std::vector<float> freq(hs / 2);
+    rope_inv_freq(hs, c.rope_base_freq, freq.data());
+    if ((e = cudaMemcpy(m->rope_freq, freq.data(), freq.size() * 4, cudaMemcpyHostToDevice)) != cudaSuccess) {
+        wgb_llama2_destroy(m);
+        return cuda_fail(e, "cudaMemcpy(rope table)");
+    }
+    const char *env = getenv("WGB_NO_PDL");
+    if (env && env[0] == '1') m->use_pdl = false;
+    *out = m;
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_destroy(wgb_llama2 *m)
+{
+    if (!m) return WGB_OK;
+    drop_graph(m);
+    for (auto &l : m->layers) {
+        for (auto *q : l.m) wgb_quant_matrix_destroy(q);
+        for (auto *v : l.v) if (v) cudaFree(v);
+    }
+    wgb_quant_matrix_destroy(m->token_embd);
+    wgb_quant_matrix_destroy(m->output);
+    float *bufs[] = { m->output_norm, m->x, m->xb, m->xb2, m->hb, m->hb2, m->q, m->tk, m->tv, m->logits, m->key_cache,
+                      m->value_cache, m->attn_scratch, m->rope_freq };
+    for (float *b : bufs) if (b) cudaFree(b);
+    uint32_t *ubufs[] = { m->attn_counters, m->scalars, m->argmax_scratch, m->d_prompt, m->d_out };
+    for (uint32_t *b : ubufs) if (b) cudaFree(b);
+    delete m;
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_set_matrix(wgb_llama2 *m, int layer, int which, int qtype, const void *h_blocks, size_t nrows,
+                                     size_t ncols)
+{
+    WGB_REQUIRE(m && h_blocks, "null argument");
+    const wgb_llama2_config &c = m->cfg;
+    const int bl = block_len(qtype);
+    if (!bl) return fail(WGB_ERR_UNSUPPORTED, "unsupported tensor type %d", qtype);
+    const uint32_t hs = m->head_size, full_kv = c.n_kv_heads * hs;
+    size_t exp_rows, exp_cols, row0 = 0, rows_keep, kb0 = 0, kb_keep;
+    wgb_quant_matrix **slot;
+    if (layer < 0) {
+        WGB_REQUIRE(which == WGB_L_TOKEN_EMBD || which == WGB_L_OUTPUT, "unknown model matrix %d", which);
+        exp_rows = c.vocab_size; exp_cols = c.dim; rows_keep = exp_rows; kb_keep = exp_cols / bl;
+        slot = which == WGB_L_TOKEN_EMBD ? &m->token_embd : &m->output;
+    } else {
+        WGB_REQUIRE((uint32_t)layer < c.n_layers && which >= 0 && which < 7, "layer %d / matrix %d out of range", layer, which);
+        slot = &m->layers[layer].m[which];
+        switch (which) {
+        case WGB_L_ATTN_Q: exp_rows = c.dim; exp_cols = c.dim; row0 = (size_t)m->tp_rank * m->q_dim; rows_keep = m->q_dim; kb_keep = exp_cols / bl; break;
+        case WGB_L_ATTN_K: case WGB_L_ATTN_V:
+            exp_rows = full_kv; exp_cols = c.dim; row0 = (size_t)m->tp_rank * m->kv_dim; rows_keep = m->kv_dim; kb_keep = exp_cols / bl; break;
+        case WGB_L_ATTN_OUTPUT:
+            exp_rows = c.dim; exp_cols = c.dim; rows_keep = exp_rows;
+            WGB_REQUIRE(m->q_dim % bl == 0, "attention slice of %u columns is not a multiple of the block length %d", m->q_dim, bl);
+            kb0 = (size_t)m->tp_rank * m->q_dim / bl; kb_keep = m->q_dim / bl; break;
+        case WGB_L_FFN_GATE: case WGB_L_FFN_UP:
+            exp_rows = c.hidden_dim; exp_cols = c.dim; kb_keep = exp_cols / bl;
+            row0 = m->tp_size == 1 ? 0 : (size_t)m->hidden_blk0 * 256; rows_keep = m->hidden; break;
+        default:  // WGB_L_FFN_DOWN
+            exp_rows = c.dim; exp_cols = c.hidden_dim; rows_keep = exp_rows;
+            kb0 = m->tp_size == 1 ? 0 : (size_t)m->hidden_blk0 * 256 / bl; kb_keep = m->hidden / bl; break;
+        }
+    }
+    WGB_REQUIRE(nrows == exp_rows && ncols == exp_cols, "matrix is %zu x %zu, the model expects %zu x %zu", nrows, ncols, exp_rows, exp_cols);
+    WGB_REQUIRE(ncols % bl == 0, "ncols %zu is not a multiple of the block length %d", ncols, bl);
+    wgb_quant_matrix *q = nullptr;
+    const int rc = qmat_create_slice(qtype, h_blocks, nrows, ncols, row0, rows_keep, kb0, kb_keep, nullptr, &q);
+    if (rc) return rc;
+    WGB_CUDA(cudaStreamSynchronize(nullptr));
+    wgb_quant_matrix_destroy(*slot);
+    *slot = q;
+    drop_graph(m);
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_set_vector(wgb_llama2 *m, int layer, int which, const float *h_data, size_t n)
+{
+    WGB_REQUIRE(m && h_data, "null argument");
+    const wgb_llama2_config &c = m->cfg;
+    float **slot;
+    size_t expect, off = 0, keep;
+    if (layer < 0) {
+        slot = &m->output_norm;
+        expect = keep = c.dim;
+    } else {
+        WGB_REQUIRE((uint32_t)layer < c.n_layers && which >= 0 && which < 5, "layer %d / vector %d out of range", layer, which);
+        slot = &m->layers[layer].v[which];
+        if (which == WGB_L_ATTN_NORM || which == WGB_L_FFN_NORM) { expect = keep = c.dim; }
+        else if (which == WGB_L_ATTN_Q_BIAS) { expect = c.dim; keep = m->q_dim; off = (size_t)m->tp_rank * m->q_dim; }
+        else { expect = (size_t)c.n_kv_heads * m->head_size; keep = m->kv_dim; off = (size_t)m->tp_rank * m->kv_dim; }
+    }
+    WGB_REQUIRE(n == expect, "vector has %zu entries, the model expects %zu", n, expect);
+    if (!*slot) WGB_CUDA(cudaMalloc((void **)slot, keep * sizeof(float)));
+    WGB_CUDA(cudaMemcpy(*slot, h_data + off, keep * sizeof(float), cudaMemcpyHostToDevice));
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_config_from_gguf(const wgb_gguf *g, int model_type, wgb_llama2_config *out)
+{
+    WGB_REQUIRE(g && out, "null argument");
+    const char *name = model_type == WGB_QWEN2 ? "qwen2" : "llama";  // models/llama2/mod.rs:19-24
+    auto key = [&](const char *suffix) { return std::string(name) + "." + suffix; };
+    auto get_u32 = [&](const std::string &k, uint32_t *v) -> int {
+        const int64_t i = wgb_gguf_meta_find(g, k.c_str());
+        if (i < 0) return fail(WGB_ERR_NOT_FOUND, "missing GGUF key '%s'", k.c_str());
+        int type = 0;
+        wgb_gguf_meta_type(g, (uint64_t)i, &type, nullptr, nullptr);
+        if (type != WGB_META_U32) return fail(WGB_ERR_INVALID, "unwrap: unexpected GGUF attribute type for '%s'.", k.c_str());
+        uint64_t u = 0;
+        wgb_gguf_meta_u64(g, (uint64_t)i, &u);
+        *v = (uint32_t)u;
+        return WGB_OK;
+    };
+    auto get_f32 = [&](const std::string &k, float dflt, float *v) -> int {
+        const int64_t i = wgb_gguf_meta_find(g, k.c_str());
+        if (i < 0) { *v = dflt; return WGB_OK; }
+        int type = 0;
+        wgb_gguf_meta_type(g, (uint64_t)i, &type, nullptr, nullptr);
+        if (type != WGB_META_F32) return fail(WGB_ERR_INVALID, "unwrap: unexpected GGUF attribute type for '%s'.", k.c_str());
+        double d = 0;
+        wgb_gguf_meta_f64(g, (uint64_t)i, &d);
+        *v = (float)d;
+        return WGB_OK;
+    };
+    int rc;
+    // cpu.rs:79-109
+    if ((rc = get_u32(key("embedding_length"), &out->dim)) || (rc = get_u32(key("feed_forward_length"), &out->hidden_dim)) ||
+        (rc = get_u32(key("block_count"), &out->n_layers)) || (rc = get_u32(key("attention.head_count"), &out->n_q_heads)) ||
+        (rc = get_u32(key("attention.head_count_kv"), &out->n_kv_heads)) || (rc = get_u32(key("context_length"), &out->seq_len)))
+        return rc;
+    const int64_t ti = wgb_gguf_meta_find(g, "tokenizer.ggml.tokens");
+    if (ti < 0) return fail(WGB_ERR_NOT_FOUND, "missing GGUF key 'tokenizer.ggml.tokens'");
+    int type = 0;
+    uint64_t len = 0;
+    wgb_gguf_meta_type(g, (uint64_t)ti, &type, nullptr, &len);
+    if (type != WGB_META_ARRAY) return fail(WGB_ERR_INVALID, "unwrap: unexpected GGUF attribute type for 'tokenizer.ggml.tokens'.");
+    out->vocab_size = (uint32_t)len;
+    if ((rc = get_f32(key("rope.freq_base"), 10000.0f, &out->rope_base_freq)) ||
+        (rc = get_f32(key("attention.layer_norm_rms_epsilon"), 1.0e-6f, &out->rms_norm_eps)))
+        return rc;
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_load_gguf(wgb_llama2 *m, const wgb_gguf *g)
+{
+    WGB_REQUIRE(m && g, "null argument");
+    const wgb_llama2_config &c = m->cfg;
+    const uint32_t full_kv = c.n_kv_heads * m->head_size;
+    auto find = [&](const std::string &name, bool required, wgb_gguf_tensor *t) -> int {
+        const int64_t i = wgb_gguf_tensor_find(g, name.c_str());
+        if (i < 0) return required ? fail(WGB_ERR_NOT_FOUND, "missing GGUF tensor '%s'", name.c_str()) : -1;
+        const int rc = wgb_gguf_tensor_info(g, (uint64_t)i, t);
+        if (rc) return rc;
+        if (!t->data) return fail(WGB_ERR_UNSUPPORTED, "tensor '%s' has unsupported type %u", name.c_str(), t->type);
+        return WGB_OK;
+    };
+    auto mat = [&](int layer, int which, const std::string &name, size_t nrows, size_t ncols, bool required) -> int {
+        wgb_gguf_tensor t;
+        int rc = find(name, required, &t);
+        if (rc == -1) return WGB_OK;
+        if (rc) return rc;
+        if (t.dims[0] * t.dims[1] * t.dims[2] * t.dims[3] != nrows * ncols)
+            return fail(WGB_ERR_INVALID, "tensor '%s' has %llu elements, expected %zu x %zu", name.c_str(),
+                        (unsigned long long)(t.dims[0] * t.dims[1] * t.dims[2] * t.dims[3]), nrows, ncols);
+        return wgb_llama2_set_matrix(m, layer, which, (int)t.type, t.data, nrows, ncols);
+    };
+    auto vec = [&](int layer, int which, const std::string &name, size_t n, bool required) -> int {
+        wgb_gguf_tensor t;
+        int rc = find(name, required, &t);
+        if (rc == -1) return WGB_OK;
+        if (rc) return rc;
+        if (t.type != WGB_F32) return fail(WGB_ERR_INVALID, "tensor '%s' must be f32", name.c_str());  // as_f32().unwrap()
+        if (t.n_bytes != n * 4) return fail(WGB_ERR_INVALID, "tensor '%s' has %llu bytes, expected %zu", name.c_str(), (unsigned long long)t.n_bytes, n * 4);
+        return wgb_llama2_set_vector(m, layer, which, (const float *)t.data, n);
+    };
+    int rc;
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        const std::string p = "blk." + std::to_string(l) + ".";
+        // transformer.rs:161-216
+        if ((rc = mat(l, WGB_L_ATTN_Q, p + "attn_q.weight", c.dim, c.dim, true)) ||
+            (rc = mat(l, WGB_L_ATTN_K, p + "attn_k.weight", full_kv, c.dim, true)) ||
+            (rc = mat(l, WGB_L_ATTN_V, p + "attn_v.weight", full_kv, c.dim, true)) ||
+            (rc = mat(l, WGB_L_ATTN_OUTPUT, p + "attn_output.weight", c.dim, c.dim, true)) ||
+            (rc = mat(l, WGB_L_FFN_DOWN, p + "ffn_down.weight", c.dim, c.hidden_dim, true)) ||
+            (rc = mat(l, WGB_L_FFN_GATE, p + "ffn_gate.weight", c.hidden_dim, c.dim, true)) ||
+            (rc = mat(l, WGB_L_FFN_UP, p + "ffn_up.weight", c.hidden_dim, c.dim, true)) ||
+            (rc = vec(l, WGB_L_ATTN_NORM, p + "attn_norm.weight", c.dim, true)) ||
+            (rc = vec(l, WGB_L_FFN_NORM, p + "ffn_norm.weight", c.dim, true)) ||
+            (rc = vec(l, WGB_L_ATTN_Q_BIAS, p + "attn_q.bias", c.dim, false)) ||
+            (rc = vec(l, WGB_L_ATTN_K_BIAS, p + "attn_k.bias", full_kv, false)) ||
+            (rc = vec(l, WGB_L_ATTN_V_BIAS, p + "attn_v.bias", full_kv, false)))
+            return rc;
+    }
+    // transformer.rs:235-260
+    if ((rc = mat(-1, WGB_L_TOKEN_EMBD, "token_embd.weight", c.vocab_size, c.dim, true)) ||
+        (rc = mat(-1, WGB_L_OUTPUT, "output.weight", c.vocab_size, c.dim, false)) ||
+        (rc = vec(-1, 0, "output_norm.weight", c.dim, true)))
+        return rc;
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_set_comm(wgb_llama2 *m, void *nccl_comm)
+{
+    WGB_REQUIRE(m, "null argument");
+    m->comm = nccl_comm;
+    drop_graph(m);
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_set_fused(wgb_llama2 *m, int enable)
+{
+    WGB_REQUIRE(m, "null argument");
+    m->fused = enable != 0;
+    drop_graph(m);
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_forward(wgb_llama2 *m, uint32_t token, uint32_t pos, void *stream)
+{
+    WGB_REQUIRE(m, "null argument");
+    int rc = check_complete(m);
+    if (rc) return rc;
+    WGB_REQUIRE(token < m->cfg.vocab_size, "token %u outside a vocabulary of %u", token, m->cfg.vocab_size);
+    WGB_REQUIRE(pos < m->cfg.seq_len, "position %u outside a context of %u", pos, m->cfg.seq_len);
+    WGB_REQUIRE(m->tp_size == 1 || m->comm, "tensor-parallel model without a communicator");
+    cudaStream_t s = as_stream(stream);
+    set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
+    WGB_LAUNCH_CHECK("set_scalars_kernel");
+    return enqueue_forward(m, s, &m->kernels_per_token);
+}
+
+WGB_EXPORT const float *wgb_llama2_logits(const wgb_llama2 *m) { return m ? m->logits : nullptr; }
+WGB_EXPORT const float *wgb_llama2_x(const wgb_llama2 *m) { return m ? m->x : nullptr; }
+WGB_EXPORT float *wgb_llama2_key_cache(wgb_llama2 *m, uint32_t layer)
+{
+    return (m && layer < m->cfg.n_layers) ? m->key_cache + (size_t)layer * m->cfg.seq_len * m->kv_dim : nullptr;
+}
+WGB_EXPORT float *wgb_llama2_value_cache(wgb_llama2 *m, uint32_t layer)
+{
+    return (m && layer < m->cfg.n_layers) ? m->value_cache + (size_t)layer * m->cfg.seq_len * m->kv_dim : nullptr;
+}
+WGB_EXPORT int wgb_llama2_kernels_per_token(const wgb_llama2 *m) { return m ? m->kernels_per_token : 0; }
+
+WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t n_prompt, size_t n_gen, uint32_t start_pos,
+                                 uint32_t *h_out_tokens, void *stream)
+{
+    WGB_REQUIRE(m && h_prompt && n_prompt >= 1, "null or empty prompt");
+    int rc = check_complete(m);
+    if (rc) return rc;
+    const size_t total = n_prompt - 1 + n_gen;
+    if (total == 0) return WGB_OK;
+    WGB_REQUIRE(h_out_tokens, "null output");
+    WGB_REQUIRE((size_t)start_pos + total <= m->cfg.seq_len, "%zu steps from position %u overrun a context of %u", total, start_pos,
+                m->cfg.seq_len);
+    for (size_t i = 0; i < n_prompt; i++)
+        WGB_REQUIRE(h_prompt[i] < m->cfg.vocab_size, "prompt token %u outside a vocabulary of %u", h_prompt[i], m->cfg.vocab_size);
+    WGB_REQUIRE(m->tp_size == 1 || m->comm, "tensor-parallel model without a communicator");
+    cudaStream_t s = as_stream(stream);
+    if (n_prompt > m->prompt_cap) {
+        if (m->d_prompt) cudaFree(m->d_prompt);
+        m->d_prompt = nullptr;
+        m->prompt_cap = 0;
+        drop_graph(m);
+        WGB_CUDA(cudaMalloc((void **)&m->d_prompt, n_prompt * 4));
+        m->prompt_cap = n_prompt;
+    }
+    if (total > m->out_cap) {
+        if (m->d_out) cudaFree(m->d_out);
+        m->d_out = nullptr;
+        m->out_cap = 0;
+        drop_graph(m);
+        WGB_CUDA(cudaMalloc((void **)&m->d_out, total * 4));
+        m->out_cap = total;
+    }
+    WGB_CUDA(cudaMemcpyAsync(m->d_prompt, h_prompt, n_prompt * 4, cudaMemcpyHostToDevice, s));
+    set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, h_prompt[0], start_pos, 0);
+    WGB_LAUNCH_CHECK("set_scalars_kernel");
+
+    LoopState ls = {};
+    ls.token = m->scalars;
+    ls.pos = m->scalars + 1;
+    ls.step = m->scalars + 2;
+    ls.prompt = m->d_prompt;
+    ls.n_prompt = (uint32_t)n_prompt;
+    ls.out_tokens = m->d_out;
+
+    if (m->graph && m->graph_n_prompt != (uint32_t)n_prompt) drop_graph(m);
+    if (!m->graph) {
+        // Capture one step on a private stream (capturing on the legacy default stream is not allowed).
+        cudaStream_t cs;
+        WGB_CUDA(cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking));
+        cudaGraph_t graph = nullptr;
+        cudaError_t e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal);
+        if (e == cudaSuccess) {
+            int nk = 0;
+            rc = enqueue_forward(m, cs, &nk);
+            if (!rc) rc = launch_argmax_advance(m->logits, m->cfg.vocab_size, ls, m->argmax_scratch, cs);
+            m->kernels_per_token = nk + 2;
+            e = cudaStreamEndCapture(cs, &graph);
+            if (rc) { if (graph) cudaGraphDestroy(graph); cudaStreamDestroy(cs); return rc; }
+        }
+        if (e == cudaSuccess) e = cudaGraphInstantiate(&m->graph, graph, 0);
+        if (graph) cudaGraphDestroy(graph);
+        cudaStreamDestroy(cs);
+        if (e != cudaSuccess) { m->graph = nullptr; return cuda_fail(e, "CUDA graph capture of a decode step"); }
+        m->graph_n_prompt = (uint32_t)n_prompt;
+    }
+    for (size_t i = 0; i < total; i++) WGB_CUDA(cudaGraphLaunch(m->graph, s));
+    WGB_CUDA(cudaMemcpyAsync(h_out_tokens, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
+    WGB_CUDA(cudaStreamSynchronize(s));
+    return WGB_OK;
+}

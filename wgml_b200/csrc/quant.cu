@@ -1,0 +1,310 @@
+// Dequantisation kernels and the quantised-matrix object (upload, planar repack, row dequant).
+#include "dequant.cuh"
+#include "qmatrix.cuh"
+
+#include <new>
+
+namespace wgb {
+
+// ---------------------------------------------------------------------------------------------
+// Kernels
+// ---------------------------------------------------------------------------------------------
+
+// One thread per weight of a raw block stream (the role of ops/quantization_test.wgsl:45-146).
+template <int QT>
+__global__ void dequant_raw_kernel(const uint8_t *__restrict__ blocks, size_t nweights, float *__restrict__ out)
+{
+    constexpr int BL = block_len(QT), BB = block_bytes(QT);
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < nweights;
+         e += (size_t)gridDim.x * blockDim.x) {
+        size_t blk = e / BL;
+        int r = (int)(e % BL);
+        out[e] = dequant_one<QT>(blocks + blk * BB, r >> 5, r & 31);
+    }
+}
+
+// Weight (row, col) of a matrix in either layout.
+template <int QT>
+__device__ __forceinline__ float qmat_weight(const QMat &m, size_t row, uint32_t col)
+{
+    constexpr int BL = block_len(QT), BB = block_bytes(QT);
+    const uint32_t kb = col / BL, r = col % BL;
+    const size_t blk = row * m.bpr + kb;
+    if (QT == WGB_Q8_0) {
+        if (m.planar) {
+            uint16_t s = ((const uint16_t *)m.p1)[blk];
+            return q8_0_value(s, (int8_t)m.p0[row * (size_t)m.ncols + col]);
+        }
+    } else if (QT == WGB_Q6_K) {
+        if (m.planar)
+            return q6_k_value(m.p0 + blk * 128, m.p1 + blk * 64, (const int8_t *)(m.p2 + blk * 16),
+                              ((const uint16_t *)m.p3)[blk], r >> 5, r & 31);
+    }
+    return dequant_one<QT>(m.p0 + blk * BB, r >> 5, r & 31);
+}
+
+// Rows [row0, row0+n) (or the single row *d_row when d_row != NULL) to dense f32.
+template <int QT>
+__global__ void dequant_rows_kernel(QMat m, size_t row0, size_t n, const uint32_t *d_row, float *__restrict__ out)
+{
+    if (d_row) row0 = *d_row;
+    const size_t total = n * (size_t)m.ncols;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total;
+         e += (size_t)gridDim.x * blockDim.x) {
+        size_t r = e / m.ncols;
+        uint32_t c = (uint32_t)(e % m.ncols);
+        size_t row = row0 + r;
+        out[e] = row < m.nrows ? qmat_weight<QT>(m, row, c) : 0.0f;
+    }
+}
+
+// Raw Q8_0 blocks -> planes.  One thread per block.
+__global__ void repack_q8_0_kernel(const uint8_t *__restrict__ raw, size_t nblocks, uint8_t *__restrict__ qs,
+                                   uint16_t *__restrict__ d)
+{
+    for (size_t b = blockIdx.x * (size_t)blockDim.x + threadIdx.x; b < nblocks;
+         b += (size_t)gridDim.x * blockDim.x) {
+        const uint8_t *s = raw + b * 34;
+        d[b] = ld16(s);
+        uint32_t *dst = (uint32_t *)(qs + b * 32);
+#pragma unroll
+        for (int i = 0; i < 8; i++) dst[i] = ld32(s + 2 + 4 * i);
+    }
+}
+
+// Raw Q6_K blocks -> planes.  One thread per 4 bytes of a block's 208 data bytes + its d.
+__global__ void repack_q6_k_kernel(const uint8_t *__restrict__ raw, size_t nblocks, uint8_t *__restrict__ ql,
+                                   uint8_t *__restrict__ qh, uint8_t *__restrict__ sc, uint16_t *__restrict__ d)
+{
+    const size_t total = nblocks * 53;  // 52 words of ql/qh/scales + one slot for d
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total;
+         e += (size_t)gridDim.x * blockDim.x) {
+        size_t b = e / 53;
+        int w = (int)(e % 53);
+        const uint8_t *s = raw + b * 210;
+        if (w < 32) ((uint32_t *)(ql + b * 128))[w] = ld32(s + 4 * w);
+        else if (w < 48) ((uint32_t *)(qh + b * 64))[w - 32] = ld32(s + 4 * w);
+        else if (w < 52) ((uint32_t *)(sc + b * 16))[w - 48] = ld32(s + 4 * w);
+        else d[b] = ld16(s + 208);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+
+static inline int grid_for(size_t n, int threads)
+{
+    size_t g = (n + threads - 1) / threads;
+    size_t cap = (size_t)sm_count() * 16;
+    return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+static bool is_supported(int qtype) { return block_bytes(qtype) != 0; }
+
+#define WGB_QT_SWITCH(qtype, CALL)                                                        \
+    switch (qtype) {                                                                      \
+    case WGB_F32: { constexpr int QT = WGB_F32; CALL; } break;                            \
+    case WGB_F16: { constexpr int QT = WGB_F16; CALL; } break;                            \
+    case WGB_Q4_0: { constexpr int QT = WGB_Q4_0; CALL; } break;                          \
+    case WGB_Q4_1: { constexpr int QT = WGB_Q4_1; CALL; } break;                          \
+    case WGB_Q5_0: { constexpr int QT = WGB_Q5_0; CALL; } break;                          \
+    case WGB_Q5_1: { constexpr int QT = WGB_Q5_1; CALL; } break;                          \
+    case WGB_Q8_0: { constexpr int QT = WGB_Q8_0; CALL; } break;                          \
+    case WGB_Q4_K: { constexpr int QT = WGB_Q4_K; CALL; } break;                          \
+    case WGB_Q5_K: { constexpr int QT = WGB_Q5_K; CALL; } break;                          \
+    case WGB_Q6_K: { constexpr int QT = WGB_Q6_K; CALL; } break;                          \
+    case WGB_Q8_K: { constexpr int QT = WGB_Q8_K; CALL; } break;                          \
+    default: return fail(WGB_ERR_UNSUPPORTED, "unsupported tensor type %d", qtype);       \
+    }
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Fills `view` plane pointers for a matrix of nrows x bpr blocks stored at `base`; returns bytes.
+static size_t layout_planes(int qtype, bool planar, size_t nrows, size_t bpr, uint8_t *base, QMat &v)
+{
+    const size_t nb = nrows * bpr;
+    v.p1 = v.p2 = v.p3 = nullptr;
+    v.p0 = base;
+    if (!planar) return align_up(nb * block_bytes(qtype), 256);
+    size_t off = 0;
+    if (qtype == WGB_Q8_0) {
+        off = align_up(nb * 32, 256);
+        v.p1 = base + off;
+        off += align_up(nb * 2, 256);
+    } else {  // Q6_K
+        off = align_up(nb * 128, 256);
+        v.p1 = base + off;
+        off += align_up(nb * 64, 256);
+        v.p2 = base + off;
+        off += align_up(nb * 16, 256);
+        v.p3 = base + off;
+        off += align_up(nb * 2, 256);
+    }
+    return off;
+}
+
+static int repack_from_device_raw(int qtype, const uint8_t *d_raw, size_t nb, const QMat &v, cudaStream_t stream)
+{
+    if (qtype == WGB_Q8_0) {
+        repack_q8_0_kernel<<<grid_for(nb, 256), 256, 0, stream>>>(d_raw, nb, (uint8_t *)v.p0, (uint16_t *)v.p1);
+    } else {
+        repack_q6_k_kernel<<<grid_for(nb * 53, 256), 256, 0, stream>>>(d_raw, nb, (uint8_t *)v.p0, (uint8_t *)v.p1,
+                                                                         (uint8_t *)v.p2, (uint16_t *)v.p3);
+    }
+    WGB_LAUNCH_CHECK("repack kernel");
+    return WGB_OK;
+}
+
+int qmat_create_slice(int qtype, const void *h_blocks, size_t nrows, size_t ncols, size_t row0,
+                      size_t nrows_keep, size_t kb0, size_t bpr_keep, cudaStream_t stream,
+                      wgb_quant_matrix **out)
+{
+    if (!is_supported(qtype)) return fail(WGB_ERR_UNSUPPORTED, "unsupported tensor type %d", qtype);
+    const int bl = block_len(qtype), bb = block_bytes(qtype);
+    WGB_REQUIRE(out && h_blocks, "null argument");
+    WGB_REQUIRE(ncols % bl == 0, "ncols %zu is not a multiple of the block length %d", ncols, bl);
+    const size_t bpr = ncols / bl;
+    WGB_REQUIRE(row0 + nrows_keep <= nrows && kb0 + bpr_keep <= bpr && nrows_keep > 0 && bpr_keep > 0,
+                "slice outside the matrix");
+    const bool planar = (qtype == WGB_Q8_0 || qtype == WGB_Q6_K);
+    wgb_quant_matrix *m = new (std::nothrow) wgb_quant_matrix();
+    if (!m) return fail(WGB_ERR_INVALID, "out of host memory");
+    m->view.qtype = qtype;
+    m->view.planar = planar;
+    m->view.nrows = (uint32_t)nrows_keep;
+    m->view.bpr = (uint32_t)bpr_keep;
+    m->view.ncols = (uint32_t)(bpr_keep * bl);
+    QMat tmp = m->view;
+    m->bytes = layout_planes(qtype, planar, nrows_keep, bpr_keep, nullptr, tmp);
+    cudaError_t e = cudaMalloc(&m->storage, m->bytes);
+    if (e != cudaSuccess) { delete m; return cuda_fail(e, "cudaMalloc(quant matrix)"); }
+    layout_planes(qtype, planar, nrows_keep, bpr_keep, (uint8_t *)m->storage, m->view);
+
+    const size_t raw_bytes = nrows_keep * bpr_keep * bb;
+    uint8_t *d_raw = planar ? nullptr : (uint8_t *)m->storage;
+    int rc = WGB_OK;
+    if (planar) {
+        e = cudaMalloc((void **)&d_raw, raw_bytes);
+        if (e != cudaSuccess) { cudaFree(m->storage); delete m; return cuda_fail(e, "cudaMalloc(repack staging)"); }
+    }
+    const uint8_t *src = (const uint8_t *)h_blocks + (row0 * bpr + kb0) * bb;
+    if (bpr_keep == bpr) e = cudaMemcpyAsync(d_raw, src, raw_bytes, cudaMemcpyHostToDevice, stream);
+    else e = cudaMemcpy2DAsync(d_raw, bpr_keep * bb, src, bpr * bb, bpr_keep * bb, nrows_keep,
+                               cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) rc = cuda_fail(e, "cudaMemcpy(quant matrix upload)");
+    if (rc == WGB_OK && planar) rc = repack_from_device_raw(qtype, d_raw, nrows_keep * bpr_keep, m->view, stream);
+    if (planar) {
+        cudaError_t e2 = cudaStreamSynchronize(stream);
+        if (rc == WGB_OK && e2 != cudaSuccess) rc = cuda_fail(e2, "repack");
+        cudaFree(d_raw);
+    }
+    if (rc != WGB_OK) { cudaFree(m->storage); delete m; return rc; }
+    *out = m;
+    return WGB_OK;
+}
+
+int qmat_create(int qtype, const void *blocks, bool src_on_device, size_t nrows, size_t ncols,
+                cudaStream_t stream, wgb_quant_matrix **out)
+{
+    if (!src_on_device) return qmat_create_slice(qtype, blocks, nrows, ncols, 0, nrows, 0,
+                                                 block_len(qtype) ? ncols / block_len(qtype) : 0, stream, out);
+    if (!is_supported(qtype)) return fail(WGB_ERR_UNSUPPORTED, "unsupported tensor type %d", qtype);
+    const int bl = block_len(qtype), bb = block_bytes(qtype);
+    WGB_REQUIRE(out && blocks, "null argument");
+    WGB_REQUIRE(ncols % bl == 0 && nrows > 0 && ncols > 0, "ncols %zu is not a multiple of the block length %d", ncols, bl);
+    const size_t bpr = ncols / bl;
+    const bool planar = (qtype == WGB_Q8_0 || qtype == WGB_Q6_K);
+    wgb_quant_matrix *m = new (std::nothrow) wgb_quant_matrix();
+    if (!m) return fail(WGB_ERR_INVALID, "out of host memory");
+    m->view.qtype = qtype;
+    m->view.planar = planar;
+    m->view.nrows = (uint32_t)nrows;
+    m->view.bpr = (uint32_t)bpr;
+    m->view.ncols = (uint32_t)ncols;
+    QMat tmp = m->view;
+    m->bytes = layout_planes(qtype, planar, nrows, bpr, nullptr, tmp);
+    cudaError_t e = cudaMalloc(&m->storage, m->bytes);
+    if (e != cudaSuccess) { delete m; return cuda_fail(e, "cudaMalloc(quant matrix)"); }
+    layout_planes(qtype, planar, nrows, bpr, (uint8_t *)m->storage, m->view);
+    int rc = WGB_OK;
+    if (planar) rc = repack_from_device_raw(qtype, (const uint8_t *)blocks, nrows * bpr, m->view, stream);
+    else {
+        e = cudaMemcpyAsync(m->storage, blocks, nrows * bpr * bb, cudaMemcpyDeviceToDevice, stream);
+        if (e != cudaSuccess) rc = cuda_fail(e, "cudaMemcpy(quant matrix)");
+    }
+    if (rc != WGB_OK) { cudaFree(m->storage); delete m; return rc; }
+    *out = m;
+    return WGB_OK;
+}
+
+int qmat_dequantize_rows(const QMat &m, size_t row0, size_t n, float *d_out, cudaStream_t stream)
+{
+    WGB_REQUIRE(row0 + n <= m.nrows, "rows [%zu, %zu) outside a matrix of %u rows", row0, row0 + n, m.nrows);
+    if (n == 0) return WGB_OK;
+    const size_t total = n * (size_t)m.ncols;
+    WGB_QT_SWITCH(m.qtype, (dequant_rows_kernel<QT><<<grid_for(total, 256), 256, 0, stream>>>(m, row0, n, nullptr, d_out)));
+    WGB_LAUNCH_CHECK("dequant_rows_kernel");
+    return WGB_OK;
+}
+
+int qmat_dequantize_row_indirect(const QMat &m, const uint32_t *d_row, float *d_out, cudaStream_t stream)
+{
+    WGB_QT_SWITCH(m.qtype, (dequant_rows_kernel<QT><<<grid_for(m.ncols, 256), 256, 0, stream>>>(m, 0, 1, d_row, d_out)));
+    WGB_LAUNCH_CHECK("dequant_rows_kernel");
+    return WGB_OK;
+}
+
+}  // namespace wgb
+
+using namespace wgb;
+
+WGB_EXPORT int wgb_block_bytes(int qtype) { return block_bytes(qtype); }
+WGB_EXPORT int wgb_block_len(int qtype) { return block_len(qtype); }
+
+WGB_EXPORT int wgb_dequantize(int qtype, const void *d_blocks, size_t nblocks, float *d_out, void *stream)
+{
+    if (nblocks == 0) return WGB_OK;
+    WGB_REQUIRE(d_blocks && d_out, "null argument");
+    const size_t nweights = nblocks * (size_t)block_len(qtype);
+    WGB_QT_SWITCH(qtype, (dequant_raw_kernel<QT><<<grid_for(nweights, 256), 256, 0, as_stream(stream)>>>(
+                             (const uint8_t *)d_blocks, nweights, d_out)));
+    WGB_LAUNCH_CHECK("dequant_raw_kernel");
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_quant_matrix_create(int qtype, const void *h_blocks, size_t nrows, size_t ncols,
+                                       void *stream, wgb_quant_matrix **out)
+{
+    return qmat_create(qtype, h_blocks, false, nrows, ncols, as_stream(stream), out);
+}
+
+WGB_EXPORT int wgb_quant_matrix_create_from_device(int qtype, const void *d_blocks, size_t nrows, size_t ncols,
+                                                   void *stream, wgb_quant_matrix **out)
+{
+    return qmat_create(qtype, d_blocks, true, nrows, ncols, as_stream(stream), out);
+}
+
+WGB_EXPORT int wgb_quant_matrix_destroy(wgb_quant_matrix *m)
+{
+    if (!m) return WGB_OK;
+    if (m->storage) cudaFree(m->storage);
+    delete m;
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_quant_matrix_shape(const wgb_quant_matrix *m, size_t *nrows, size_t *ncols, int *qtype)
+{
+    WGB_REQUIRE(m, "null matrix");
+    if (nrows) *nrows = m->view.nrows;
+    if (ncols) *ncols = m->view.ncols;
+    if (qtype) *qtype = m->view.qtype;
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_quant_matrix_dequantize_rows(const wgb_quant_matrix *m, size_t row0, size_t n, float *d_out,
+                                                void *stream)
+{
+    WGB_REQUIRE(m && d_out, "null argument");
+    return qmat_dequantize_rows(m->view, row0, n, d_out, as_stream(stream));
+}
