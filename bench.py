@@ -1,0 +1,392 @@
+#!/usr/bin/env python
+"""Decode throughput of the B200-native token loop, one JSON line.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+
+N = 1 (default): the configuration the headline metric is quoted on, a Llama-2-7B-architecture model
+in a Q4_K_M-style mix (Q4_K, Q6_K for the output matrix and every other ffn_down), synthetic weights,
+512 forced prompt tokens, then greedy decoding at batch 1.  A step is one decoded token.
+N > 1: the Llama-2-70B-architecture Q4_K model, tensor-parallel over the N GPUs (one process per GPU,
+launched by torchrun), 4096 forced prompt tokens.
+
+`value`  tokens/s with everything resident on the device (one C-ABI call decodes K tokens).
+`e2e`    tokens/s through the C ABI with host buffers, one call per token: the token id goes host ->
+         device, the sampled id comes back device -> host and the host waits for it, every step.
+`--impl reference` times the reference's CPU transformer (the C restatement in oracle/, all host
+threads) on a bounded sample of the same workload and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode_tokens_per_s"
+UNIT = "tok/s"
+BPE = {0: 4.0, 8: 34 / 32, 12: 144 / 256, 14: 210 / 256}  # algorithmic bytes per weight
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (earlier pool measurement)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_cfg(workload: str, seq_len: int) -> dict:
+    from wgml_b200 import synth
+    cfg = dict(synth.CONFIGS[workload])
+    cfg["seq_len"] = seq_len
+    return cfg
+
+
+def matrix_bytes(cfg: dict, layer: int, name: str) -> float:
+    """Algorithmic bytes of one weight matrix (GGUF block sizes, whatever the device layout)."""
+    from wgml_b200 import synth
+    dim, hid = cfg["dim"], cfg["hidden_dim"]
+    kv = dim * cfg["n_kv_heads"] // cfg["n_q_heads"]
+    shapes = {"attn_q": (dim, dim), "attn_k": (kv, dim), "attn_v": (kv, dim), "attn_output": (dim, dim),
+              "ffn_gate": (hid, dim), "ffn_up": (hid, dim), "ffn_down": (dim, hid), "output": (cfg["vocab_size"], dim)}
+    qt = cfg["default_qtype"]
+    if cfg.get("mix") == "q4_k_m" and (name == "output" or (name == "ffn_down" and layer % 2 == 0)):
+        qt = synth.Q6_K
+    r, c = shapes[name]
+    return r * c * BPE[qt], qt
+
+
+def launch_bytes(cfg: dict, kind: str, layer: int, pos: int, tp: int = 1):
+    """Algorithmic bytes one launch of `kind` must move: weights + input and output vectors (+ KV rows)."""
+    dim, hid = cfg["dim"], cfg["hidden_dim"]
+    kv = dim * cfg["n_kv_heads"] // cfg["n_q_heads"]
+    if kind == "qkv_rope":
+        b = sum(matrix_bytes(cfg, layer, n)[0] for n in ("attn_q", "attn_k", "attn_v")) / tp
+        return b + 4 * dim * 2 + 4 * (dim + 2 * kv) / tp, matrix_bytes(cfg, layer, "attn_q")[1]
+    if kind == "attn_output":
+        w, qt = matrix_bytes(cfg, layer, "attn_output")
+        return w / tp + 4 * dim / tp + 8 * dim, qt
+    if kind == "gate_up_silu":
+        w, qt = matrix_bytes(cfg, layer, "ffn_gate")
+        return 2 * w / tp + 4 * dim * 2 + 4 * hid / tp, qt
+    if kind == "ffn_down":
+        w, qt = matrix_bytes(cfg, layer, "ffn_down")
+        return w / tp + 4 * hid / tp + 8 * dim, qt
+    if kind == "logits":
+        w, qt = matrix_bytes(cfg, -1, "output")
+        return w + 4 * dim * 2 + 4 * cfg["vocab_size"], qt
+    if kind == "attention":
+        return 2.0 * (pos + 1) * kv * 4 / tp + 8 * dim / tp, 0
+    return 0.0, 0
+
+
+def token_bytes(cfg: dict, pos: int, tp: int = 1) -> float:
+    total = 0.0
+    for l in range(cfg["n_layers"]):
+        for k in ("qkv_rope", "attention", "attn_output", "gate_up_silu", "ffn_down"):
+            total += launch_bytes(cfg, k, l, pos, tp)[0]
+    return total + launch_bytes(cfg, "logits", -1, pos, tp)[0]
+
+
+def build_gpu_model(cfg: dict, seed: int, tp_rank: int = 0, tp_size: int = 1):
+    """Generates the tensors layer by layer (host memory stays bounded) and uploads them."""
+    import ctypes as C
+
+    from wgml_b200 import _lib, synth
+    from wgml_b200.models import LLAMA_MATS, Llama2, Llama2Config
+    c = Llama2Config(cfg["dim"], cfg["hidden_dim"], cfg["n_layers"], cfg["n_q_heads"], cfg["n_kv_heads"], cfg["vocab_size"],
+                     cfg["seq_len"], cfg["rope_base_freq"], cfg["rms_norm_eps"])
+    m = Llama2(c, tp_rank=tp_rank, tp_size=tp_size)
+    lib = _lib.load()
+    kv = c.kv_dim
+    shapes = {"attn_q": (c.dim, c.dim), "attn_k": (kv, c.dim), "attn_v": (kv, c.dim), "attn_output": (c.dim, c.dim),
+              "ffn_gate": (c.hidden_dim, c.dim), "ffn_up": (c.hidden_dim, c.dim), "ffn_down": (c.dim, c.hidden_dim)}
+    for l in range(c.n_layers):
+        t = synth.llama_tensors(cfg, seed, layers=[l])
+        for i, nm in enumerate(LLAMA_MATS):
+            qt, arr = t[f"blk.{l}.{nm}.weight"]
+            raw = np.ascontiguousarray(arr).view(np.uint8).reshape(-1)
+            _lib.check(lib.wgb_llama2_set_matrix(m._h, l, i, qt, raw.ctypes.data, *shapes[nm]))
+        for i, nm in enumerate(("attn_norm.weight", "ffn_norm.weight")):
+            v = np.ascontiguousarray(t[f"blk.{l}.{nm}"][1], dtype=np.float32)
+            _lib.check(lib.wgb_llama2_set_vector(m._h, l, i, v.ctypes.data, v.size))
+        if l == 0:
+            for which, key in ((0, "token_embd.weight"), (1, "output.weight")):
+                qt, arr = t[key]
+                raw = np.ascontiguousarray(arr).view(np.uint8).reshape(-1)
+                _lib.check(lib.wgb_llama2_set_matrix(m._h, -1, which, qt, raw.ctypes.data, c.vocab_size, c.dim))
+            v = np.ascontiguousarray(t["output_norm.weight"][1], dtype=np.float32)
+            _lib.check(lib.wgb_llama2_set_vector(m._h, -1, 0, v.ctypes.data, v.size))
+        del t
+    return m
+
+
+def cpu_sample(cfg: dict, seed: int, pos: int, budget_s: float, steps: int | None = None, warmup: int = 1):
+    """Times the CPU oracle on a bounded sample: single layers (three resident, rotating) and the
+    classifier head of the model, extrapolated to a whole token.  Returns (tok/s, description,
+    threads, per-step seconds)."""
+    import oracle
+    from wgml_b200 import synth
+    n_res = min(3, cfg["n_layers"])
+    small = dict(cfg, n_layers=n_res, seq_len=pos + 2)
+    t = synth.llama_tensors(dict(cfg), seed, layers=range(n_res))
+    m = oracle.Llama2Oracle(small, t)
+    threads = oracle.num_threads()
+    x0 = np.random.default_rng(0).standard_normal(cfg["dim"]).astype(np.float32)
+
+    def reset():
+        np.ctypeslib.as_array(oracle.lib().wgo_llama2_x(m.h), (cfg["dim"],))[:] = x0
+
+    reset()
+    t0 = time.perf_counter()
+    m.head_forward()
+    t_head = time.perf_counter() - t0
+    for i in range(warmup):
+        reset()
+        m.layer_forward(i % n_res, pos)
+    times = []
+    i = 0
+    t_start = time.perf_counter()
+    while True:
+        reset()
+        t0 = time.perf_counter()
+        m.layer_forward(i % n_res, pos)
+        times.append(time.perf_counter() - t0)
+        i += 1
+        if steps is not None:
+            if i >= steps:
+                break
+        elif time.perf_counter() - t_start > budget_s or i >= 64:
+            break
+    t_layer = float(np.mean(times))
+    tok_s = 1.0 / (cfg["n_layers"] * t_layer + t_head)
+    desc = (f"{len(times)} single-layer forwards (layers 0..{n_res - 1} rotating, KV position {pos}) + 1 classifier head of the "
+            f"{cfg['n_layers']}-layer model; token time = {cfg['n_layers']} x mean layer time + head time")
+    return tok_s, desc, threads, times, t_head
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    workload = args.workload or ("llama2-7b" if args.gpus == 1 else "llama2-70b")
+    prompt_len = args.prompt_len or (512 if workload == "llama2-7b" else 4096)
+    cfg = model_cfg(workload, prompt_len + args.warmup + args.steps)
+    pos = min(prompt_len, 64)  # the CPU attention cost is negligible beside the matrix products
+    t0 = time.perf_counter()
+    tok_s, desc, threads, times, t_head = cpu_sample(cfg, args.seed, pos, 0.0, steps=args.steps, warmup=max(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1000.0 / tok_s, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "prompt_len": prompt_len, "decode_steps": args.steps, "batch": 1,
+                   "note": "wgml's CPU transformer (models/llama2/cpu.rs) restated in C (oracle/), on-the-fly dequantisation, "
+                           "OpenMP over matrix rows; the Rust original and its wgpu path cannot be built or run here"},
+        "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_b200(args):
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}"
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    workload = args.workload or ("llama2-7b" if world == 1 else "llama2-70b")
+    prompt_len = args.prompt_len or (512 if workload == "llama2-7b" else 4096)
+    K, W = args.steps, args.warmup
+    cfg = model_cfg(workload, prompt_len + W + 2 * K + 8)
+    from wgml_b200 import synth
+    model = build_gpu_model(cfg, args.seed, rank, world)
+    if world > 1:
+        from wgml_b200 import tp
+        tp.attach(model)
+    prompt = synth.prompt(prompt_len, cfg["vocab_size"], args.seed)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # prefill: the prompt goes through the decode path token by token, as the reference does
+    toks = model.decode(prompt, 0) if prompt_len > 1 else np.zeros(0, np.uint32)
+    pos = prompt_len - 1
+    last = np.array([prompt[-1]], np.uint32)
+    # warm-up decode steps (also builds the n_prompt=1 graph)
+    for _ in range(max(W, 1)):
+        last = model.decode(last, 1, start_pos=pos)
+        pos += 1
+    stream = torch.cuda.current_stream()
+    index = int(os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[local]) if os.environ.get("CUDA_VISIBLE_DEVICES") else local
+
+    # ---- device-resident: one call decodes K tokens --------------------------------------------
+    barrier()
+    with ClockSampler(index) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        out = model.decode(last, K, start_pos=pos)
+        e1.record(stream)
+        barrier()
+    ms_dev = e0.elapsed_time(e1)
+    pos_mid = pos + K // 2
+    pos += K
+    last = out[-1:]
+    # ---- end to end: one C-ABI call per token, host ids in and out -------------------------------
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record(stream)
+    for _ in range(K):
+        last = model.decode(last, 1, start_pos=pos)
+        pos += 1
+    e1.record(stream)
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    wall_e2e = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([ms_dev, ms_e2e], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_dev, ms_e2e = float(t[0]), float(t[1])
+
+    # ---- per-launch breakdown (eager, events after every launch) ----------------------------------
+    peak, peak_src = measured_peaks()
+    classes = {}
+    for rep in range(6):
+        for kind, layer, ms in model.profile_step(int(last[0]), pos_mid):
+            if rep == 0:
+                continue  # first eager pass warms the instruction caches
+            b, qt = launch_bytes(cfg, kind, layer, pos_mid, world)
+            key = kind if kind in ("attention", "embed") else f"{kind}/{ {0: 'f32', 8: 'q8_0', 12: 'q4_k', 14: 'q6_k'}.get(qt, qt) }"
+            c = classes.setdefault(key, {"launches": 0, "ms": 0.0, "bytes": 0.0})
+            c["launches"] += 1
+            c["ms"] += ms
+            c["bytes"] += b
+    for c in classes.values():
+        c["gbs"] = c["bytes"] / (c["ms"] * 1e-3) / 1e9 if c["ms"] > 0 else 0.0
+        c["us_per_launch"] = 1e3 * c["ms"] / max(c["launches"], 1)
+    gemv = {k: v for k, v in classes.items() if "/" in k}
+    dom = max(gemv, key=lambda k: gemv[k]["ms"]) if gemv else None
+    tok_s = K / (ms_dev * 1e-3)
+    bytes_tok = token_bytes(cfg, pos_mid, world)
+    roofline = None
+    if dom:
+        d = classes[dom]
+        roofline = {"bound": "hbm", "kernel": f"gemv_kernel [{dom}]", "achieved": d["gbs"], "peak": peak, "unit": "GB/s",
+                    "frac": d["gbs"] / peak, "traffic": None, "peak_source": peak_src,
+                    "bytes_per_launch": d["bytes"] / d["launches"], "us_per_launch": d["us_per_launch"],
+                    "how": "algorithmic bytes / CUDA-event time per launch, eager replay of the step with an event after every launch",
+                    "whole_step": {"bytes_per_token": bytes_tok, "achieved": bytes_tok * tok_s / 1e9,
+                                   "frac": bytes_tok * tok_s / 1e9 / peak, "frac_of_8TBs": bytes_tok * tok_s / 8e12}}
+    line = {
+        "metric": METRIC, "value": tok_s * (1 if world == 1 else 1), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "prompt_len": prompt_len, "decode_steps": K, "batch": 1,
+                   "parallelism": f"tp{world}" if world > 1 else "single GPU", "weights_gb": None,
+                   "timing": "CUDA events on the launch stream; the weights (far larger than the 126 MB L2) are re-read every token"},
+        "e2e": {"value": K / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
+                "ms_per_step": ms_e2e / K, "wall_ms_per_step": 1e3 * wall_e2e / K,
+                "how": "wgb_llama2_decode called once per token with host token ids; includes the copies and the host wait"},
+        "gpu_launches": int(model.kernels_per_token()) * 2 * K + 2 * K,
+        "kernels_per_token": int(model.kernels_per_token()),
+        "clocks": clocks.summary(), "roofline": roofline, "breakdown": classes,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tok_cpu, desc, threads, _, _ = cpu_sample(cfg, args.seed, 64, args.cpu_budget)
+        line["cpu_baseline"] = {"value": tok_cpu, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=None, choices=[None, "llama2-7b", "llama2-70b", "tiny-llama"])
+    ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU oracle work for cpu_baseline")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

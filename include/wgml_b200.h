@@ -287,6 +287,14 @@ int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t n_prompt, 
                       uint32_t start_pos, uint32_t *h_out_tokens, void *stream);
 /* Number of kernels one decode step launches (for launch accounting). */
 int wgb_llama2_kernels_per_token(const wgb_llama2 *m);
+/* Measurement aid, the counterpart of wgcore's GpuTimestamps around a pass
+ * (crates/wgml-bench/src/main.rs:201,226-241): runs one forward outside any graph with a CUDA event
+ * after every launch, waits, and reports per launch its kind (0 embedding, 1 norm+QKV+RoPE,
+ * 2 attention, 3 output projection, 4 norm+gate/up+SiLU, 5 down projection, 6 norm+logits,
+ * 7 unfused layer), its layer (-1 outside layers) and the milliseconds since the previous event.
+ * At most `cap` entries are written; *n_out is their number. */
+int wgb_llama2_profile_step(wgb_llama2 *m, uint32_t token, uint32_t pos, void *stream, int cap,
+                            int *kinds, int *layers, float *ms, int *n_out);
 
 /* ---- GPT-2 ---- */
 

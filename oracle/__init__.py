@@ -70,6 +70,8 @@ def lib() -> C.CDLL:
             fn = getattr(L, "wgo_llama2_" + name)
             fn.restype, fn.argtypes = f32p, [vp]
         L.wgo_llama2_forward.argtypes = [vp, C.c_uint32, C.c_uint32]
+        L.wgo_llama2_layer_forward.argtypes = [vp, C.c_uint32, C.c_uint32]
+        L.wgo_llama2_head_forward.argtypes = [vp]
         L.wgo_llama2_decode.argtypes = [vp, vp, sz, sz, C.c_uint32, vp, vp]
         L.wgo_gpt2_new.restype = vp
         L.wgo_gpt2_new.argtypes = [C.c_uint32] * 6
@@ -237,6 +239,13 @@ class Llama2Oracle:
     def forward(self, token: int, pos: int) -> np.ndarray:
         lib().wgo_llama2_forward(self.h, token, pos)
         return self.logits()
+
+    def layer_forward(self, layer: int, pos: int) -> None:
+        """One layer on the running activation (timing samples of large models)."""
+        lib().wgo_llama2_layer_forward(self.h, layer, pos)
+
+    def head_forward(self) -> None:
+        lib().wgo_llama2_head_forward(self.h)
 
     def logits(self) -> np.ndarray:
         return np.ctypeslib.as_array(lib().wgo_llama2_logits(self.h), (self.cfg["vocab_size"],)).copy()

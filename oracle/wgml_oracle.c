@@ -632,14 +632,15 @@ static void embedding_row(const wgo_mat *w, size_t row, float *out)
     for (size_t k = 0; k < bpr; k++) deq_block(w->qtype, rb + k * (size_t)bb, out + k * (size_t)bl);
 }
 
-/* Transformer::forward -- cpu.rs:377-444 */
-WGO_API void wgo_llama2_forward(wgo_llama2 *m, uint32_t token, uint32_t pos)
+/* One iteration of the layer loop of Transformer::forward -- cpu.rs:392-434 -- on the running
+ * activation `x`.  Exposed on its own so that the CPU baseline can time a bounded sample of a
+ * model that is too slow to run whole. */
+WGO_API void wgo_llama2_layer_forward(wgo_llama2 *m, uint32_t l, uint32_t pos)
 {
     size_t dim = m->dim, hidden = m->hidden_dim;
     size_t kv_dim = dim * m->n_kv_heads / m->n_q_heads;
     uint32_t head_size = (uint32_t)(dim / m->n_q_heads);
-    embedding_row(&m->token_embd, token, m->x);
-    for (uint32_t l = 0; l < m->n_layers; l++) {
+    {
         wgo_llama2_layer *wl = &m->layers[l];
         float *kc_l = m->key_cache + (size_t)l * kv_dim * m->seq_len;
         float *vc_l = m->value_cache + (size_t)l * kv_dim * m->seq_len;
@@ -667,8 +668,21 @@ WGO_API void wgo_llama2_forward(wgo_llama2 *m, uint32_t token, uint32_t pos)
         mat_vec(&wl->m[WGO_FFN_DOWN], m->hb, m->xb2);
         for (size_t i = 0; i < dim; i++) m->x[i] += m->xb2[i];
     }
-    wgo_rms_norm(m->xb, m->x, m->output_norm, dim, m->rms_norm_eps);
+}
+
+/* Final norm and classifier -- cpu.rs:436-443. */
+WGO_API void wgo_llama2_head_forward(wgo_llama2 *m)
+{
+    wgo_rms_norm(m->xb, m->x, m->output_norm, m->dim, m->rms_norm_eps);
     mat_vec(&m->output, m->xb, m->logits);
+}
+
+/* Transformer::forward -- cpu.rs:377-444 */
+WGO_API void wgo_llama2_forward(wgo_llama2 *m, uint32_t token, uint32_t pos)
+{
+    embedding_row(&m->token_embd, token, m->x);
+    for (uint32_t l = 0; l < m->n_layers; l++) wgo_llama2_layer_forward(m, l, pos);
+    wgo_llama2_head_forward(m);
 }
 
 /* The token loop of crates/wgml-chat/src/chat_llama2.rs:102-121 with the forced-token rule of

@@ -51,6 +51,10 @@ struct wgb_llama2 {
     uint32_t graph_n_prompt = 0;
     void *comm = nullptr;
     int kernels_per_token = 0;
+    // per-launch timing of wgb_llama2_profile_step: one event after every launch
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events;
+    std::vector<int> prof_kind, prof_layer;
 };
 
 namespace {
@@ -141,18 +145,33 @@ int mat_vec(const QMat &w, const float *x, float *out, cudaStream_t s)
     return launch_gemv_generic(w, x, out, s);
 }
 
+// Profiling: an event after the launch just enqueued, tagged with its kind and layer.
+enum { K_EMBED = 0, K_QKV, K_ATTN, K_OPROJ, K_GATE_UP, K_DOWN, K_HEAD, K_OTHER };
+int mark(wgb_llama2 *m, cudaStream_t s, int kind, int layer)
+{
+    if (!m->profiling) return WGB_OK;
+    cudaEvent_t e;
+    WGB_CUDA(cudaEventCreate(&e));
+    WGB_CUDA(cudaEventRecord(e, s));
+    m->prof_events.push_back(e);
+    m->prof_kind.push_back(kind);
+    m->prof_layer.push_back(layer);
+    return WGB_OK;
+}
+
 // Enqueues one token forward reading token / position from the device scalars.
 int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
 {
     const wgb_llama2_config &c = m->cfg;
     const uint32_t *d_token = m->scalars, *d_pos = m->scalars + 1;
     const bool fused = m->fused && fusable(m);
-    const bool pdl = m->use_pdl;
+    const bool pdl = m->use_pdl && !m->profiling;
     const int variant = m->model_type == WGB_QWEN2 ? WGB_ROPE_NEOX : WGB_ROPE_ORIGINAL;
     int n = 0;
     int rc = launch_embed(m->token_embd->view, nullptr, d_token, d_pos, m->x, s);
     if (rc) return rc;
     n++;
+    mark(m, s, K_EMBED, -1);
     const size_t cache_stride = (size_t)c.seq_len * m->kv_dim;
     AttnArgs at = {};
     at.p.seq_len = c.seq_len;
@@ -193,7 +212,9 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             a.rope_variant = variant;
             a.rope_freq = m->rope_freq;
             if ((rc = launch_gemv(a, s, pdl))) return rc;
+            mark(m, s, K_QKV, l);
             if ((rc = launch_attention(at, s, pdl))) return rc;
+            mark(m, s, K_ATTN, l);
             GemvArgs o = {};
             o.mat[0] = w.m[WGB_L_ATTN_OUTPUT]->view;
             o.nmat = 1;
@@ -202,6 +223,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             o.residual = m->x;
             o.out = m->x;
             if ((rc = launch_gemv(o, s, pdl))) return rc;
+            mark(m, s, K_OPROJ, l);
             GemvArgs f = {};
             f.mat[0] = w.m[WGB_L_FFN_GATE]->view;
             f.mat[1] = w.m[WGB_L_FFN_UP]->view;
@@ -213,6 +235,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             f.epilogue = EPI_SILU_PAIR;
             f.out = m->hb;
             if ((rc = launch_gemv(f, s, pdl))) return rc;
+            mark(m, s, K_GATE_UP, l);
             GemvArgs d = {};
             d.mat[0] = w.m[WGB_L_FFN_DOWN]->view;
             d.nmat = 1;
@@ -221,6 +244,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             d.residual = m->x;
             d.out = m->x;
             if ((rc = launch_gemv(d, s, pdl))) return rc;
+            mark(m, s, K_DOWN, l);
             n += 5;
         } else {
             // transformer.rs:312-407, dispatch by dispatch
@@ -241,6 +265,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             if ((rc = wgb_silu(m->hb, m->hb2, m->hidden, s))) return rc;
             if ((rc = mat_vec(w.m[WGB_L_FFN_DOWN]->view, m->hb, m->xb2, s))) return rc;
             if ((rc = wgb_op_assign(WGB_ASSIGN_ADD, m->x, m->xb2, c.dim, s))) return rc;
+            mark(m, s, K_OTHER, l);
             n += 14;
         }
     }
@@ -256,10 +281,12 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
         a.epilogue = EPI_STORE;
         a.out = m->logits;
         if ((rc = launch_gemv(a, s, pdl))) return rc;
+        mark(m, s, K_HEAD, -1);
         n += 1;
     } else {
         if ((rc = wgb_rms_norm(m->xb, m->x, m->output_norm, c.dim, c.rms_norm_eps, s))) return rc;
         if ((rc = mat_vec(outw, m->xb, m->logits, s))) return rc;
+        mark(m, s, K_HEAD, -1);
         n += 2;
     }
     if (nkernels) *nkernels = n;
@@ -560,6 +587,49 @@ WGB_EXPORT int wgb_llama2_forward(wgb_llama2 *m, uint32_t token, uint32_t pos, v
     set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
     return enqueue_forward(m, s, &m->kernels_per_token);
+}
+
+WGB_EXPORT int wgb_llama2_profile_step(wgb_llama2 *m, uint32_t token, uint32_t pos, void *stream, int cap, int *kinds,
+                                       int *layers, float *ms, int *n_out)
+{
+    WGB_REQUIRE(m && kinds && layers && ms && n_out, "null argument");
+    int rc = check_complete(m);
+    if (rc) return rc;
+    WGB_REQUIRE(token < m->cfg.vocab_size && pos < m->cfg.seq_len, "token / position out of range");
+    cudaStream_t s = as_stream(stream);
+    set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
+    WGB_LAUNCH_CHECK("set_scalars_kernel");
+    m->profiling = true;
+    m->prof_events.clear();
+    m->prof_kind.clear();
+    m->prof_layer.clear();
+    cudaEvent_t start;
+    WGB_CUDA(cudaEventCreate(&start));
+    WGB_CUDA(cudaEventRecord(start, s));
+    rc = enqueue_forward(m, s, nullptr);
+    m->profiling = false;
+    cudaError_t e = cudaStreamSynchronize(s);
+    int n = 0;
+    cudaEvent_t prev = start;
+    for (size_t i = 0; i < m->prof_events.size(); i++) {
+        if (rc == WGB_OK && e == cudaSuccess && n < cap) {
+            float t = 0.0f;
+            cudaEventElapsedTime(&t, prev, m->prof_events[i]);
+            kinds[n] = m->prof_kind[i];
+            layers[n] = m->prof_layer[i];
+            ms[n] = t;
+            n++;
+        }
+        if (prev != start) cudaEventDestroy(prev);
+        prev = m->prof_events[i];
+    }
+    if (prev != start) cudaEventDestroy(prev);
+    cudaEventDestroy(start);
+    m->prof_events.clear();
+    *n_out = n;
+    if (rc) return rc;
+    if (e != cudaSuccess) return cuda_fail(e, "profile step");
+    return WGB_OK;
 }
 
 WGB_EXPORT const float *wgb_llama2_logits(const wgb_llama2 *m) { return m ? m->logits : nullptr; }

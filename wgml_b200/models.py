@@ -150,6 +150,16 @@ class Llama2:
     def kernels_per_token(self) -> int:
         return _lib.load().wgb_llama2_kernels_per_token(self._h)
 
+    PROFILE_KINDS = ["embed", "qkv_rope", "attention", "attn_output", "gate_up_silu", "ffn_down", "logits", "unfused_layer"]
+
+    def profile_step(self, token: int, pos: int):
+        """One eager forward with an event after every launch: list of (kind name, layer, milliseconds)."""
+        cap = 32 * self.config.n_layers + 16
+        kinds, layers, ms, n = (C.c_int * cap)(), (C.c_int * cap)(), (C.c_float * cap)(), C.c_int()
+        check(_lib.load().wgb_llama2_profile_step(self._h, token, pos, torch.cuda.current_stream().cuda_stream, cap,
+                                                  kinds, layers, ms, C.byref(n)))
+        return [(self.PROFILE_KINDS[kinds[i]], layers[i], ms[i]) for i in range(n.value)]
+
     def close(self):
         if self._h is not None and self._h.value:
             _lib.load().wgb_llama2_destroy(self._h)
