@@ -2,16 +2,25 @@
 // memory.  These are the inner loops of every matrix-vector kernel of the library.
 //
 // A warp owns R rows and walks the K dimension in steps; in each step every lane owns a fixed
-// slice of the columns (a run of codes that shares its sub-block scale), keeps the matching x
-// values in registers and reuses them for all R rows.  Weight bytes are fetched with 128-bit
-// loads straight from HBM (each byte is used once, so nothing is staged); x comes from shared
-// memory through a bank-conflict-free swizzle.  Codes are unpacked in registers, accumulated in
-// f32 and folded across the warp with shuffles.
+// slice of the columns (a run of codes that shares its sub-block scale), keeps the matching part
+// of x in registers and reuses it for all R rows.  Weight bytes are fetched with 128-bit loads
+// straight from HBM (each byte is used once, so nothing is staged); x comes from shared memory
+// through a bank-conflict-free swizzle.  Partial sums are f32 and are folded across the warp
+// with shuffles.
 //
-// Algebra used instead of materialising every weight:
-//   Q4_K  sum_l (d*sc*q_l - dmin*m) x_l = d*sc * sum_l q_l x_l  -  dmin*m * sum_l x_l
-//   Q6_K  sum_l d*sc*(q_l - 32) x_l     = d*sc * (sum_l q_l x_l - 32 * sum_l x_l)
-// with the per-16-column sums of x precomputed once per thread block.
+// Arithmetic.  At 7.7 TB/s a B200 streams ~1.4e13 four-bit codes per second, more than its
+// integer pipe can turn into floats one by one, so the inner product of the codes of one
+// 32-column sub-block with x is taken in integers instead:
+//   x of a 32-column group is written as X * 2^e with a shared exponent and a 24-bit signed X
+//   (|X| <= 2^22, rounded to nearest: within one bit of f32 precision for the largest element), X is split into
+//   three bytes X = 65536 d2 + 256 d1 + d0, and  sum_l q_l X_l  is three dp4a chains over the
+//   packed codes (which are dp4a operands as they come out of the mask), exact in int32.
+// The exact integer S then enters the f32 algebra of the format:
+//   Q4_K  sum_l (d*sc*q_l - dmin*m) x_l = d*sc * 2^e S  -  dmin*m * sum_l x_l
+//   Q6_K  sum_l d*sc*(q_l - 32) x_l     = d*sc * (2^e S - 32 * sum_l x_l)
+//   Q8_0  sum_l d*q_l x_l               = d * 2^e S
+// with the per-16-column sums of x (f32, from the unrounded x) computed once per thread block.
+// Dense f32 matrices use plain f32 FMAs.
 #pragma once
 
 #include "dequant.cuh"
@@ -42,30 +51,96 @@ __device__ __forceinline__ uint16_t ldg_stream2(const void *p)
     return v;
 }
 
-// Byte k (0..3) of a word as float; unsigned and signed.
-__device__ __forceinline__ float u8f(uint32_t w, int k) { return (float)((w >> (8 * k)) & 0xffu); }
-__device__ __forceinline__ float s8f(uint32_t w, int k) { return (float)(int8_t)(w >> (8 * k)); }
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)  // a unsigned bytes, b signed bytes
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c)  // a signed bytes, b unsigned bytes
+{
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Integer -> f32 without the conversion unit (which runs at an eighth of the FP32 rate on this part):
+// adding the integer to the bit pattern of 2^23 (resp. 1.5 * 2^23) yields the float 2^23 + v exactly,
+// and one FP32 subtraction removes the offset.  Valid for 0 <= v < 2^23 (resp. |v| < 2^22).
+__device__ __forceinline__ float u2f(uint32_t v) { return __uint_as_float(v + 0x4b000000u) - 8388608.0f; }
+__device__ __forceinline__ float i2f(int v) { return __uint_as_float((uint32_t)v + 0x4b400000u) - 12582912.0f; }
+
+// 65536 s2 + 256 s1 + s0 as f32 for digit sums with 0 <= s0, s1 < 2^23 and |s2| < 2^22 (the top part may round).
+__device__ __forceinline__ float combine3(int s2, int s1, int s0)
+{
+    return fmaf(i2f(s2), 65536.0f, fmaf(u2f((uint32_t)s1), 256.0f, u2f((uint32_t)s0)));
+}
+// The same with signed low digits (|s0|, |s1| < 2^22).
+__device__ __forceinline__ float combine3s(int s2, int s1, int s0)
+{
+    return fmaf(i2f(s2), 65536.0f, fmaf(i2f(s1), 256.0f, i2f(s0)));
+}
+
+// Sign-extended byte k of a word, as f32.
+__device__ __forceinline__ float s8f(uint32_t w, int k) { return i2f((int)(w << (24 - 8 * k)) >> 24); }
 
 // ---------------------------------------------------------------------------------------------
-// Shared-memory image of the input vector.
-//   xs   : K floats, stored in 16-byte chunks at swizzled positions (swz<QT>(chunk))
-//   xsum : K/16 floats, sum of each run of 16 consecutive inputs
-// The swizzle permutes chunks inside aligned groups of 8 so that the 8 lanes served together
-// by one 128-bit shared load hit 8 different bank groups for the lane->column map of QT.
+// Shared-memory image of the input vector (built once per thread block by stage_x).
+//   quantised formats:  d0, d1, d2  K bytes each: the three byte digits of X, element order,
+//                                   16-byte chunks at swizzled positions (swz<QT>)
+//                       xscale      K/32 floats: 2^e of every 32-column group
+//                       xsum        K/16 floats: f32 sum of every 16 consecutive inputs
+//   f32:                xf          K floats
+// The swizzle permutes chunks inside aligned groups of 8 so that the 8 lanes served together by one
+// 128-bit shared load hit 8 different bank groups for the lane->column map of QT.
 // ---------------------------------------------------------------------------------------------
+struct XImage {
+    const uint4 *d0, *d1, *d2;
+    const float *xscale, *xsum, *xf;
+};
+
+__host__ __device__ constexpr size_t ximage_bytes(int qt, uint32_t K)
+{
+    return qt == WGB_F32 ? (size_t)K * 4 : 3 * (size_t)((K + 127) & ~127u) + (size_t)((K / 32 + 3) & ~3u) * 4 + (size_t)((K / 16 + 3) & ~3u) * 4;
+}
+
+__device__ __forceinline__ XImage ximage_carve(int qt, uint32_t K, void *smem)
+{
+    XImage im = {};
+    if (qt == WGB_F32) {
+        im.xf = reinterpret_cast<const float *>(smem);
+        return im;
+    }
+    const size_t plane = (K + 127) & ~127u;
+    uint8_t *p = reinterpret_cast<uint8_t *>(smem);
+    im.d0 = reinterpret_cast<const uint4 *>(p);
+    im.d1 = reinterpret_cast<const uint4 *>(p + plane);
+    im.d2 = reinterpret_cast<const uint4 *>(p + 2 * plane);
+    im.xscale = reinterpret_cast<const float *>(p + 3 * plane);
+    im.xsum = im.xscale + ((K / 32 + 3) & ~3u);
+    return im;
+}
+
+// Position of 16-element chunk c of a digit plane.
 template <int QT>
 __device__ __forceinline__ uint32_t swz(uint32_t c)
 {
-    if (QT == WGB_Q4_K) return c ^ ((c >> 4) & 7u);
-    if (QT == WGB_Q6_K) return c ^ (((c >> 6) & 1u) | (((c >> 5) & 1u) << 1));
-    if (QT == WGB_Q8_0) return c ^ ((c >> 3) & 7u);
+    if (QT == WGB_Q4_K) return c ^ ((c >> 3) & 3u);          // lanes (kb, g): c = kb*16 + g*4 + t
+    if (QT == WGB_Q6_K) return c ^ (((c >> 3) & 3u) << 1);   // lanes (kb, i, lb): c = kb*16 + i*8 + j*2 + lb
+    if (QT == WGB_Q8_0) return c ^ ((c >> 3) & 1u);          // lanes kb: c = kb*2 + t
     return c;
-}
-
-template <int QT>
-__device__ __forceinline__ float4 xs_chunk(const float *xs, uint32_t c)
-{
-    return reinterpret_cast<const float4 *>(xs)[swz<QT>(c)];
 }
 
 // Columns one warp step covers.
@@ -82,10 +157,30 @@ __host__ __device__ constexpr bool has_fast_path(int qt)
 }
 
 // ---------------------------------------------------------------------------------------------
-// Per-format step: `Raw` holds one row's bytes for one step; load() issues the global loads,
-// dot() consumes them.  `col0` is the first column of the step; lanes whose slice starts beyond
-// K contribute nothing (their loads are skipped).
+// Per-format step over rows staged in shared memory.  A step covers step_cols<QT>() columns; lane l
+// owns a fixed slice of them.  load_x() brings the lane's part of the input image into registers
+// (reused for every row of the step); dot() reads the lane's slice of one staged row -- `rowp[i]` is
+// the shared-memory address of the row's first byte in plane i -- and returns its partial sum.
 // ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr)
+{
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+
 template <int QT>
 struct Step;
 
@@ -93,42 +188,39 @@ struct Step;
 // (32 bytes of qs: low nibbles = first 32 columns, high nibbles = next 32).
 template <>
 struct Step<WGB_Q4_K> {
-    struct Raw { uint4 hdr, q0, q1; };
-    struct X { float lo[32], hi[32]; float slo, shi; };
+    struct X { uint4 d0[4], d1[4], d2[4]; float e_lo, e_hi, s_lo, s_hi; };
 
-    __device__ static __forceinline__ bool active(const QMat &m, uint32_t col0, int lane)
+    __device__ static __forceinline__ bool active(uint32_t bpr, uint32_t col0, int lane)
     {
-        return (col0 >> 8) + (lane >> 2) < m.bpr;
+        return (col0 >> 8) + (lane >> 2) < bpr;
     }
-    __device__ static __forceinline__ void load(Raw &r, const QMat &m, uint32_t row, uint32_t col0, int lane)
+    __device__ static __forceinline__ void load_x(X &x, const XImage &im, uint32_t col0, int lane)
     {
         const uint32_t kb = (col0 >> 8) + (lane >> 2), g = lane & 3;
-        const uint8_t *blk = m.p0 + ((size_t)row * m.bpr + kb) * 144;
-        r.hdr = ldg_stream(blk);
-        r.q0 = ldg_stream(blk + 16 + g * 32);
-        r.q1 = ldg_stream(blk + 32 + g * 32);
-    }
-    __device__ static __forceinline__ void load_x(X &x, const float *xs, const float *xsum, uint32_t col0, int lane)
-    {
-        const uint32_t kb = (col0 >> 8) + (lane >> 2), g = lane & 3;
-        const uint32_t c0 = kb * 64 + g * 16;
+        const uint32_t c0 = kb * 16 + g * 4;
 #pragma unroll
-        for (int t = 0; t < 8; t++) {
-            float4 a = xs_chunk<WGB_Q4_K>(xs, c0 + t), b = xs_chunk<WGB_Q4_K>(xs, c0 + 8 + t);
-            x.lo[4 * t] = a.x; x.lo[4 * t + 1] = a.y; x.lo[4 * t + 2] = a.z; x.lo[4 * t + 3] = a.w;
-            x.hi[4 * t] = b.x; x.hi[4 * t + 1] = b.y; x.hi[4 * t + 2] = b.z; x.hi[4 * t + 3] = b.w;
+        for (int t = 0; t < 4; t++) {
+            const uint32_t c = swz<WGB_Q4_K>(c0 + t);
+            x.d0[t] = im.d0[c];
+            x.d1[t] = im.d1[c];
+            x.d2[t] = im.d2[c];
         }
-        const float4 s = reinterpret_cast<const float4 *>(xsum)[kb * 4 + g];
-        x.slo = s.x + s.y;
-        x.shi = s.z + s.w;
+        const float2 e = reinterpret_cast<const float2 *>(im.xscale)[kb * 4 + g];
+        x.e_lo = e.x;
+        x.e_hi = e.y;
+        const float4 s = reinterpret_cast<const float4 *>(im.xsum)[kb * 4 + g];
+        x.s_lo = s.x + s.y;
+        x.s_hi = s.z + s.w;
     }
-    __device__ static __forceinline__ float dot(const Raw &r, const X &x, int lane)
+    __device__ static __forceinline__ float dot(const uint32_t (&rowp)[4], uint32_t col0, const X &x, int lane)
     {
-        const uint32_t g = lane & 3;
+        const uint32_t kb = (col0 >> 8) + (lane >> 2), g = lane & 3;
+        const uint32_t blk = rowp[0] + kb * 144;
+        const uint4 hdr = lds128(blk), q0 = lds128(blk + 16 + g * 32), q1 = lds128(blk + 32 + g * 32);
         // Six-bit scale / min of sub-blocks 2g and 2g+1 (get_scale_min_k4, quantization.rs:381-389),
         // two at a time in the 16-bit halves of a word.
         const uint32_t sh = (g & 1) * 16;
-        const uint32_t a = r.hdr.y >> sh, b = r.hdr.z >> sh, t = r.hdr.w >> sh;
+        const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, t = hdr.w >> sh;
         uint32_t sc16, m16;
         if (g < 2) {
             sc16 = a & 0x3f3fu;
@@ -137,20 +229,26 @@ struct Step<WGB_Q4_K> {
             sc16 = (t & 0x0f0fu) | ((a & 0xc0c0u) >> 2);
             m16 = ((t >> 4) & 0x0f0fu) | ((b & 0xc0c0u) >> 2);
         }
-        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&r.hdr.x));
-        float s_lo = 0.0f, s_hi = 0.0f;
-        const uint32_t q[8] = { r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w };
+        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+        const uint32_t q[8] = { q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w };
+        // columns 0..31 of the group sit in digit chunks 0,1 (low nibbles), 32..63 in chunks 2,3
+        const uint32_t *d0 = reinterpret_cast<const uint32_t *>(x.d0), *d1 = reinterpret_cast<const uint32_t *>(x.d1),
+                       *d2 = reinterpret_cast<const uint32_t *>(x.d2);
+        int l0 = 0, l1 = 0, l2 = 0, h0 = 0, h1 = 0, h2 = 0;
 #pragma unroll
         for (int w = 0; w < 8; w++) {
-            const uint32_t lo = q[w] & 0x0f0f0f0fu, hi = (q[w] >> 4) & 0x0f0f0f0fu;
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                s_lo = fmaf(u8f(lo, k), x.lo[4 * w + k], s_lo);
-                s_hi = fmaf(u8f(hi, k), x.hi[4 * w + k], s_hi);
-            }
+            // high nibbles stay in place (16 * code): the factor 1/16 is applied to the finished sum
+            const uint32_t lo = q[w] & 0x0f0f0f0fu, hi = q[w] & 0xf0f0f0f0u;
+            l0 = dp4a_uu(lo, d0[w], l0);
+            l1 = dp4a_uu(lo, d1[w], l1);
+            l2 = dp4a_us(lo, d2[w], l2);
+            h0 = dp4a_uu(hi, d0[8 + w], h0);
+            h1 = dp4a_uu(hi, d1[8 + w], h1);
+            h2 = dp4a_us(hi, d2[8 + w], h2);
         }
-        const float pos = (float)(sc16 & 0xffu) * s_lo + (float)(sc16 >> 8) * s_hi;
-        const float neg = (float)(m16 & 0xffu) * x.slo + (float)(m16 >> 8) * x.shi;
+        const float s_lo = combine3(l2, l1, l0) * x.e_lo, s_hi = combine3(h2, h1, h0) * (x.e_hi * 0.0625f);
+        const float pos = u2f(sc16 & 0xffu) * s_lo + u2f(sc16 >> 8) * s_hi;
+        const float neg = u2f(m16 & 0xffu) * x.s_lo + u2f(m16 >> 8) * x.s_hi;
         return dm.x * pos - dm.y * neg;
     }
 };
@@ -159,178 +257,177 @@ struct Step<WGB_Q4_K> {
 // l0 = 16*lb .. +15 of each of the four 32-column runs (ql[l], ql[l+32] nibbles + qh bit pairs).
 template <>
 struct Step<WGB_Q6_K> {
-    struct Raw { uint4 a, b, h; uint2 sc; uint16_t d; };
-    struct X { float v[4][16]; float s[4]; };
+    struct X { uint4 d0[4], d1[4], d2[4]; float e[4], s[4]; };
 
-    __device__ static __forceinline__ bool active(const QMat &m, uint32_t col0, int lane)
+    __device__ static __forceinline__ bool active(uint32_t bpr, uint32_t col0, int lane)
     {
-        return (col0 >> 8) + (lane >> 2) < m.bpr;
+        return (col0 >> 8) + (lane >> 2) < bpr;
     }
-    __device__ static __forceinline__ void load(Raw &r, const QMat &m, uint32_t row, uint32_t col0, int lane)
-    {
-        const uint32_t kb = (col0 >> 8) + (lane >> 2), i = (lane >> 1) & 1, lb = lane & 1;
-        const size_t blk = (size_t)row * m.bpr + kb;
-        const uint8_t *ql = m.p0 + blk * 128 + i * 64 + lb * 16;
-        r.a = ldg_stream(ql);
-        r.b = ldg_stream(ql + 32);
-        r.h = ldg_stream(m.p1 + blk * 64 + i * 32 + lb * 16);
-        r.sc = ldg_stream8(m.p2 + blk * 16 + i * 8);
-        r.d = ldg_stream2(m.p3 + blk * 2);
-    }
-    __device__ static __forceinline__ void load_x(X &x, const float *xs, const float *xsum, uint32_t col0, int lane)
+    __device__ static __forceinline__ void load_x(X &x, const XImage &im, uint32_t col0, int lane)
     {
         const uint32_t kb = (col0 >> 8) + (lane >> 2), i = (lane >> 1) & 1, lb = lane & 1;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const uint32_t c0 = kb * 64 + i * 32 + j * 8 + lb * 4;
-#pragma unroll
-            for (int t = 0; t < 4; t++) {
-                float4 a = xs_chunk<WGB_Q6_K>(xs, c0 + t);
-                x.v[j][4 * t] = a.x; x.v[j][4 * t + 1] = a.y; x.v[j][4 * t + 2] = a.z; x.v[j][4 * t + 3] = a.w;
-            }
-            x.s[j] = xsum[kb * 16 + i * 8 + j * 2 + lb];
+            const uint32_t c = swz<WGB_Q6_K>(kb * 16 + i * 8 + j * 2 + lb);
+            x.d0[j] = im.d0[c];
+            x.d1[j] = im.d1[c];
+            x.d2[j] = im.d2[c];
+            x.e[j] = im.xscale[kb * 8 + i * 4 + j];
+            x.s[j] = im.xsum[kb * 16 + i * 8 + j * 2 + lb];
         }
     }
-    __device__ static __forceinline__ float dot(const Raw &r, const X &x, int lane)
+    __device__ static __forceinline__ float dot(const uint32_t (&rowp)[4], uint32_t col0, const X &x, int lane)
     {
-        const uint32_t lb = lane & 1;
-        const uint32_t A[4] = { r.a.x, r.a.y, r.a.z, r.a.w }, B[4] = { r.b.x, r.b.y, r.b.z, r.b.w },
-                       H[4] = { r.h.x, r.h.y, r.h.z, r.h.w };
-        float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        const uint32_t kb = (col0 >> 8) + (lane >> 2), i = (lane >> 1) & 1, lb = lane & 1;
+        const uint32_t ql = rowp[0] + kb * 128 + i * 64 + lb * 16;
+        const uint4 ra = lds128(ql), rb = lds128(ql + 32), rh = lds128(rowp[1] + kb * 64 + i * 32 + lb * 16);
+        const uint2 rsc = lds64(rowp[2] + kb * 16 + i * 8);
+        const uint32_t rd = lds16(rowp[3] + kb * 2);
+        const uint32_t A[4] = { ra.x, ra.y, ra.z, ra.w }, B[4] = { rb.x, rb.y, rb.z, rb.w }, H[4] = { rh.x, rh.y, rh.z, rh.w };
+        const uint32_t *d0 = reinterpret_cast<const uint32_t *>(x.d0), *d1 = reinterpret_cast<const uint32_t *>(x.d1),
+                       *d2 = reinterpret_cast<const uint32_t *>(x.d2);
+        int s[4][3] = {};
 #pragma unroll
         for (int w = 0; w < 4; w++) {
-            const uint32_t q0 = (A[w] & 0x0f0f0f0fu) | ((H[w] << 4) & 0x30303030u);
-            const uint32_t q1 = (B[w] & 0x0f0f0f0fu) | ((H[w] << 2) & 0x30303030u);
-            const uint32_t q2 = ((A[w] >> 4) & 0x0f0f0f0fu) | (H[w] & 0x30303030u);
-            const uint32_t q3 = ((B[w] >> 4) & 0x0f0f0f0fu) | ((H[w] >> 2) & 0x30303030u);
+            uint32_t q[4];
+            q[0] = (A[w] & 0x0f0f0f0fu) | ((H[w] << 4) & 0x30303030u);
+            q[1] = (B[w] & 0x0f0f0f0fu) | ((H[w] << 2) & 0x30303030u);
+            q[2] = ((A[w] >> 4) & 0x0f0f0f0fu) | (H[w] & 0x30303030u);
+            q[3] = ((B[w] >> 4) & 0x0f0f0f0fu) | ((H[w] >> 2) & 0x30303030u);
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                s0 = fmaf(u8f(q0, k), x.v[0][4 * w + k], s0);
-                s1 = fmaf(u8f(q1, k), x.v[1][4 * w + k], s1);
-                s2 = fmaf(u8f(q2, k), x.v[2][4 * w + k], s2);
-                s3 = fmaf(u8f(q3, k), x.v[3][4 * w + k], s3);
+            for (int j = 0; j < 4; j++) {
+                s[j][0] = dp4a_uu(q[j], d0[4 * j + w], s[j][0]);
+                s[j][1] = dp4a_uu(q[j], d1[4 * j + w], s[j][1]);
+                s[j][2] = dp4a_us(q[j], d2[4 * j + w], s[j][2]);
             }
         }
         // int8 scales i*8 + lb + {0, 2, 4, 6}
-        const uint32_t lo = r.sc.x >> (8 * lb), hi = r.sc.y >> (8 * lb);
-        float acc = s8f(lo, 0) * (s0 - 32.0f * x.s[0]);
-        acc = fmaf(s8f(lo, 2), s1 - 32.0f * x.s[1], acc);
-        acc = fmaf(s8f(hi, 0), s2 - 32.0f * x.s[2], acc);
-        acc = fmaf(s8f(hi, 2), s3 - 32.0f * x.s[3], acc);
-        return __half2float(__ushort_as_half(r.d)) * acc;
+        const uint32_t lo = rsc.x >> (8 * lb), hi = rsc.y >> (8 * lb);
+        float acc = s8f(lo, 0) * (combine3(s[0][2], s[0][1], s[0][0]) * x.e[0] - 32.0f * x.s[0]);
+        acc = fmaf(s8f(lo, 2), combine3(s[1][2], s[1][1], s[1][0]) * x.e[1] - 32.0f * x.s[1], acc);
+        acc = fmaf(s8f(hi, 0), combine3(s[2][2], s[2][1], s[2][0]) * x.e[2] - 32.0f * x.s[2], acc);
+        acc = fmaf(s8f(hi, 2), combine3(s[3][2], s[3][1], s[3][0]) * x.e[3] - 32.0f * x.s[3], acc);
+        return __half2float(__ushort_as_half((uint16_t)rd)) * acc;
     }
 };
 
 // Q8_0, planar: one lane per 32-column block.
 template <>
 struct Step<WGB_Q8_0> {
-    struct Raw { uint4 q0, q1; uint16_t d; };
-    struct X { float v[32]; };
+    struct X { uint4 d0[2], d1[2], d2[2]; float e; };
 
-    __device__ static __forceinline__ bool active(const QMat &m, uint32_t col0, int lane)
+    __device__ static __forceinline__ bool active(uint32_t bpr, uint32_t col0, int lane)
     {
-        return (col0 >> 5) + lane < m.bpr;
+        return (col0 >> 5) + lane < bpr;
     }
-    __device__ static __forceinline__ void load(Raw &r, const QMat &m, uint32_t row, uint32_t col0, int lane)
-    {
-        const uint32_t kb = (col0 >> 5) + lane;
-        const uint8_t *qs = m.p0 + (size_t)row * m.ncols + kb * 32;
-        r.q0 = ldg_stream(qs);
-        r.q1 = ldg_stream(qs + 16);
-        r.d = ldg_stream2(m.p1 + ((size_t)row * m.bpr + kb) * 2);
-    }
-    __device__ static __forceinline__ void load_x(X &x, const float *xs, const float *, uint32_t col0, int lane)
+    __device__ static __forceinline__ void load_x(X &x, const XImage &im, uint32_t col0, int lane)
     {
         const uint32_t kb = (col0 >> 5) + lane;
 #pragma unroll
-        for (int t = 0; t < 8; t++) {
-            float4 a = xs_chunk<WGB_Q8_0>(xs, kb * 8 + t);
-            x.v[4 * t] = a.x; x.v[4 * t + 1] = a.y; x.v[4 * t + 2] = a.z; x.v[4 * t + 3] = a.w;
+        for (int t = 0; t < 2; t++) {
+            const uint32_t c = swz<WGB_Q8_0>(kb * 2 + t);
+            x.d0[t] = im.d0[c];
+            x.d1[t] = im.d1[c];
+            x.d2[t] = im.d2[c];
         }
+        x.e = im.xscale[kb];
     }
-    __device__ static __forceinline__ float dot(const Raw &r, const X &x, int)
+    __device__ static __forceinline__ float dot(const uint32_t (&rowp)[4], uint32_t col0, const X &x, int lane)
     {
-        const uint32_t q[8] = { r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w };
-        float s = 0.0f;
+        const uint32_t kb = (col0 >> 5) + lane;
+        const uint4 q0 = lds128(rowp[0] + kb * 32), q1 = lds128(rowp[0] + kb * 32 + 16);
+        const uint32_t rd = lds16(rowp[1] + kb * 2);
+        const uint32_t q[8] = { q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w };
+        const uint32_t *d0 = reinterpret_cast<const uint32_t *>(x.d0), *d1 = reinterpret_cast<const uint32_t *>(x.d1),
+                       *d2 = reinterpret_cast<const uint32_t *>(x.d2);
+        int s0 = 0, s1 = 0, s2 = 0;
 #pragma unroll
-        for (int w = 0; w < 8; w++)
-#pragma unroll
-            for (int k = 0; k < 4; k++) s = fmaf(s8f(q[w], k), x.v[4 * w + k], s);
-        return __half2float(__ushort_as_half(r.d)) * s;
+        for (int w = 0; w < 8; w++) {
+            s0 = dp4a_su(q[w], d0[w], s0);
+            s1 = dp4a_su(q[w], d1[w], s1);
+            s2 = dp4a_ss(q[w], d2[w], s2);
+        }
+        return __half2float(__ushort_as_half((uint16_t)rd)) * (combine3s(s2, s1, s0) * x.e);
     }
 };
 
-// Dense f32 (ncols a multiple of 4): one lane per 4 columns.
+// Dense f32 (ncols a multiple of 4): one lane per 4 columns.  `bpr` is the number of columns.
 template <>
 struct Step<WGB_F32> {
-    struct Raw { uint4 w; };
     struct X { float4 v; };
 
-    __device__ static __forceinline__ bool active(const QMat &m, uint32_t col0, int lane)
+    __device__ static __forceinline__ bool active(uint32_t ncols, uint32_t col0, int lane)
     {
-        return col0 + lane * 4 < m.ncols;
+        return col0 + lane * 4 < ncols;
     }
-    __device__ static __forceinline__ void load(Raw &r, const QMat &m, uint32_t row, uint32_t col0, int lane)
+    __device__ static __forceinline__ void load_x(X &x, const XImage &im, uint32_t col0, int lane)
     {
-        r.w = ldg_stream(m.p0 + ((size_t)row * m.ncols + col0 + lane * 4) * 4);
+        x.v = reinterpret_cast<const float4 *>(im.xf)[(col0 >> 2) + lane];
     }
-    __device__ static __forceinline__ void load_x(X &x, const float *xs, const float *, uint32_t col0, int lane)
+    __device__ static __forceinline__ float dot(const uint32_t (&rowp)[4], uint32_t col0, const X &x, int lane)
     {
-        x.v = xs_chunk<WGB_F32>(xs, (col0 >> 2) + lane);
-    }
-    __device__ static __forceinline__ float dot(const Raw &r, const X &x, int)
-    {
-        return __uint_as_float(r.w.x) * x.v.x + __uint_as_float(r.w.y) * x.v.y +
-               __uint_as_float(r.w.z) * x.v.z + __uint_as_float(r.w.w) * x.v.w;
+        const uint4 w = lds128(rowp[0] + (col0 + lane * 4) * 4);
+        return __uint_as_float(w.x) * x.v.x + __uint_as_float(w.y) * x.v.y + __uint_as_float(w.z) * x.v.z +
+               __uint_as_float(w.w) * x.v.w;
     }
 };
 
-// R rows (possibly of R different matrices of the same format and width) against xs.
-// `rows[r]` must be valid row indices of `mats[r]`.  Returns, in every lane, the R sums.
-template <int QT, int R>
-__device__ __forceinline__ void warp_dot_rows(const QMat *const (&mats)[R], const uint32_t (&rows)[R],
-                                              const float *xs, const float *xsum, float (&acc)[R])
-{
-    using S = Step<QT>;
-    const int lane = threadIdx.x & 31;
-    const QMat &m0 = *mats[0];
-#pragma unroll
-    for (int r = 0; r < R; r++) acc[r] = 0.0f;
-    for (uint32_t col0 = 0; col0 < m0.ncols; col0 += step_cols<QT>()) {
-        if (S::active(m0, col0, lane)) {
-            typename S::Raw raw[R];
-#pragma unroll
-            for (int r = 0; r < R; r++) S::load(raw[r], *mats[r], rows[r], col0, lane);
-            typename S::X x;
-            S::load_x(x, xs, xsum, col0, lane);
-#pragma unroll
-            for (int r = 0; r < R; r++) acc[r] += S::dot(raw[r], x, lane);
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < R; r++) acc[r] = warp_sum(acc[r]);
-}
-
-// Writes v[0..K) (already normalised / transformed by the caller through `f`) into the swizzled
-// shared image and builds the 16-column sums.  Called by all NT threads of the block; ends with a
-// barrier.  K must be a multiple of 4; `xsum` needs ceil(K/16) floats.
+// Builds the shared image of v[0..K) (already normalised / transformed by the caller: f(c) returns
+// the four values of float4 chunk c).  Called by threads 0..NT-1 of the block (NT a multiple of 32)
+// with converged warps; the caller synchronises those threads afterwards.  K must be a multiple of
+// 32 for the quantised formats, of 4 for f32.
 template <int QT, int NT, typename F>
-__device__ __forceinline__ void stage_x(float *xs, float *xsum, uint32_t K, F f)
+__device__ __forceinline__ void stage_x(void *smem, uint32_t K, F f)
 {
-    for (uint32_t c = threadIdx.x; c < K / 4; c += NT)
-        reinterpret_cast<float4 *>(xs)[swz<QT>(c)] = f(c);
-    __syncthreads();
-    if (QT == WGB_Q4_K || QT == WGB_Q6_K) {
-        for (uint32_t s = threadIdx.x; s < K / 16; s += NT) {
-            float t = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                float4 a = xs_chunk<QT>(xs, s * 4 + j);
-                t += (a.x + a.y) + (a.z + a.w);
-            }
-            xsum[s] = t;
+    if (QT == WGB_F32) {
+        float4 *xf = reinterpret_cast<float4 *>(smem);
+        for (uint32_t c = threadIdx.x; c < K / 4; c += NT) xf[c] = f(c);
+        return;
+    }
+    const size_t plane = (K + 127) & ~127u;
+    uint8_t *p = reinterpret_cast<uint8_t *>(smem);
+    uint32_t *d0 = reinterpret_cast<uint32_t *>(p), *d1 = reinterpret_cast<uint32_t *>(p + plane),
+             *d2 = reinterpret_cast<uint32_t *>(p + 2 * plane);
+    float *xscale = reinterpret_cast<float *>(p + 3 * plane);
+    float *xsum = xscale + ((K / 32 + 3) & ~3u);
+    // 8 consecutive lanes share a 32-column group (4 columns each); K/4 is a multiple of 8, so whole
+    // groups of 8 lanes are in or out of range together.
+    const uint32_t nchunk = K / 4;
+    for (uint32_t c0 = 0; c0 < nchunk; c0 += NT) {
+        const uint32_t c = c0 + threadIdx.x;
+        const bool in = c < nchunk;
+        const float4 v = in ? f(c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        float sum = (v.x + v.y) + (v.z + v.w);
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+        // |v| < 2^(ex-126) for the biased exponent ex of the group maximum, so X = v * 2^(148-ex) stays
+        // within +-2^22 after rounding and its third byte is a valid signed digit
+        uint32_t ex = (__float_as_uint(m) >> 23) & 0xffu;
+        ex = ex < 24u ? 24u : (ex > 253u ? 253u : ex);
+        const float up = __uint_as_float((275u - ex) << 23);    // 2^(148 - ex)
+        const float down = __uint_as_float((ex - 21u) << 23);   // 2^(ex - 148)
+        // round to nearest even through the 1.5 * 2^23 offset (|v * up| <= 2^22)
+        const int X0 = (int)(__float_as_uint(fmaf(v.x, up, 12582912.0f)) - 0x4b400000u),
+                  X1 = (int)(__float_as_uint(fmaf(v.y, up, 12582912.0f)) - 0x4b400000u),
+                  X2 = (int)(__float_as_uint(fmaf(v.z, up, 12582912.0f)) - 0x4b400000u),
+                  X3 = (int)(__float_as_uint(fmaf(v.w, up, 12582912.0f)) - 0x4b400000u);
+        if (in) {
+            // digit k of the four values packed into one word
+            const uint32_t a01 = __byte_perm(X0, X1, 0x5410), a23 = __byte_perm(X2, X3, 0x5410);  // bytes 0,1 of each
+            const uint32_t b01 = __byte_perm(X0, X1, 0x7632), b23 = __byte_perm(X2, X3, 0x7632);  // bytes 2,3 of each
+            const uint32_t w0 = __byte_perm(a01, a23, 0x6420), w1 = __byte_perm(a01, a23, 0x7531);
+            const uint32_t w2 = __byte_perm(b01, b23, 0x6420);
+            const uint32_t pos = swz<QT>(c >> 2) * 4 + (c & 3);
+            d0[pos] = w0;
+            d1[pos] = w1;
+            d2[pos] = w2;
+            if ((c & 7) == 0) xscale[c >> 3] = down;
+            if ((c & 3) == 0) xsum[c >> 2] = sum;
         }
-        __syncthreads();
     }
 }
 

@@ -43,8 +43,19 @@ struct GemvArgs {
     uint32_t kv_dim, head_size;
     int rope_variant;
     const float *rope_freq;     // head_size/2 inverse frequencies base^(-2j/head_size)
-    // optional copy of the normalised input (first block writes it); NULL to skip
-    float *x_norm_out;
+    // launch plan, filled by launch_gemv
+    uint32_t rs;            // rows per shared-memory stage
+    uint32_t ngroups;       // stages' worth of rows in the launch
+    uint32_t nstage;        // ring depth
+    uint32_t stage_bytes;
+    uint32_t ring_offset;   // of the ring inside dynamic shared memory (after the input image)
+    uint32_t wk;            // consumer warps along the columns (one slot)
+    uint32_t nslot;         // stage slots = stages in work at once
+    uint32_t rslots;        // row slots sharing the output units of one stage
+    uint32_t *err;          // device status word for expired waits
+#ifdef WGB_DBG_TIMING
+    unsigned long long *dbg;
+#endif
 };
 
 // Enqueues one fused kernel.  All matrices must share format and ncols and have a fast path;
@@ -53,6 +64,8 @@ struct GemvArgs {
 // weights before waiting for its predecessor).
 int launch_gemv(const GemvArgs &a, cudaStream_t stream, bool pdl);
 bool gemv_fast_supported(const QMat &m);
+// WGB_ERR_TIMEOUT if any bounded wait of a fused kernel expired since the last call (synchronises).
+int gemv_check_status();
 
 // Slow path for any format: one warp per row, dequantising with the exact block formulas.
 int launch_gemv_generic(const QMat &m, const float *x, float *out, cudaStream_t stream);

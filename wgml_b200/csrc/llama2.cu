@@ -711,5 +711,5 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
     for (size_t i = 0; i < total; i++) WGB_CUDA(cudaGraphLaunch(m->graph, s));
     WGB_CUDA(cudaMemcpyAsync(h_out_tokens, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
     WGB_CUDA(cudaStreamSynchronize(s));
-    return WGB_OK;
+    return gemv_check_status();
 }

@@ -1,6 +1,6 @@
 // Stand-alone operators of wgml's surface (norms, RoPE, softmax, SiLU, unary, op-assign, argmax)
 // plus the small device-resident helpers of the token loop (embedding gather, greedy step).
-#include "dequant.cuh"
+#include "qaccess.cuh"
 #include "kernels.h"
 
 #include <cmath>
@@ -215,37 +215,6 @@ __global__ void argmax_final_kernel(const unsigned long long *__restrict__ part,
 }
 
 // x = embedding row *d_token (+ position row *d_pos), dequantised exactly.
-template <int QT>
-__device__ __forceinline__ float embed_weight(const QMat &m, size_t row, uint32_t col)
-{
-    constexpr int BL = block_len(QT), BB = block_bytes(QT);
-    const uint32_t kb = col / BL, r = col % BL;
-    const size_t blk = row * m.bpr + kb;
-    if (QT == WGB_Q8_0 && m.planar) return q8_0_value(((const uint16_t *)m.p1)[blk], (int8_t)m.p0[row * (size_t)m.ncols + col]);
-    if (QT == WGB_Q6_K && m.planar)
-        return q6_k_value(m.p0 + blk * 128, m.p1 + blk * 64, (const int8_t *)(m.p2 + blk * 16), ((const uint16_t *)m.p3)[blk],
-                          r >> 5, r & 31);
-    return dequant_one<QT>(m.p0 + blk * BB, r >> 5, r & 31);
-}
-
-__device__ float embed_any(const QMat &m, size_t row, uint32_t col)
-{
-    switch (m.qtype) {
-    case WGB_F32: return embed_weight<WGB_F32>(m, row, col);
-    case WGB_F16: return embed_weight<WGB_F16>(m, row, col);
-    case WGB_Q4_0: return embed_weight<WGB_Q4_0>(m, row, col);
-    case WGB_Q4_1: return embed_weight<WGB_Q4_1>(m, row, col);
-    case WGB_Q5_0: return embed_weight<WGB_Q5_0>(m, row, col);
-    case WGB_Q5_1: return embed_weight<WGB_Q5_1>(m, row, col);
-    case WGB_Q8_0: return embed_weight<WGB_Q8_0>(m, row, col);
-    case WGB_Q4_K: return embed_weight<WGB_Q4_K>(m, row, col);
-    case WGB_Q5_K: return embed_weight<WGB_Q5_K>(m, row, col);
-    case WGB_Q6_K: return embed_weight<WGB_Q6_K>(m, row, col);
-    case WGB_Q8_K: return embed_weight<WGB_Q8_K>(m, row, col);
-    }
-    return 0.0f;
-}
-
 __global__ void embed_kernel(const __grid_constant__ QMat embd, const __grid_constant__ QMat pos_embd, int have_pos,
                              const uint32_t *__restrict__ d_token, const uint32_t *__restrict__ d_pos, float *__restrict__ x)
 {
@@ -254,8 +223,8 @@ __global__ void embed_kernel(const __grid_constant__ QMat embd, const __grid_con
     const uint32_t tok = *d_token;
     const uint32_t pos = have_pos ? *d_pos : 0;
     for (uint32_t c = blockIdx.x * blockDim.x + threadIdx.x; c < embd.ncols; c += gridDim.x * blockDim.x) {
-        float v = tok < embd.nrows ? embed_any(embd, tok, c) : 0.0f;
-        if (have_pos && pos < pos_embd.nrows) v += embed_any(pos_embd, pos, c);
+        float v = tok < embd.nrows ? qmat_weight_any(embd, tok, c) : 0.0f;
+        if (have_pos && pos < pos_embd.nrows) v += qmat_weight_any(pos_embd, pos, c);
         x[c] = v;
     }
 }

@@ -5,11 +5,12 @@
 //   raw     blocks in GGUF order, row-major [nrows][blocks_per_row][block_bytes].  Used as is for
 //           every format whose block size is a multiple of 16 bytes (Q4_K: 144, Q5_K: 176) and for
 //           the formats that only have the generic kernel.
-//   planar  the fields of each block split into planes so that every vector load is 16-byte
-//           aligned; byte count is unchanged.
-//             Q8_0: p0 = int8 codes  [nrows][ncols]            p1 = f16 scales [nrows][bpr]
-//             Q6_K: p0 = ql [nrows][bpr][128]  p1 = qh [nrows][bpr][64]
-//                   p2 = int8 scales [nrows][bpr][16]          p3 = f16 d [nrows][bpr]
+//   planar  the fields of each block split into planes so that every vector load and every bulk
+//           copy of whole rows is 16-byte aligned.  Every plane is row-major with a row pitch that
+//           is a multiple of 16 bytes (the 2-byte scale planes are padded up to it).
+//             Q8_0: p[0] = int8 codes  [nrows][ncols]          p[1] = f16 scales [nrows][bpr (+pad)]
+//             Q6_K: p[0] = ql [nrows][bpr][128]  p[1] = qh [nrows][bpr][64]
+//                   p[2] = int8 scales [nrows][bpr][16]        p[3] = f16 d [nrows][bpr (+pad)]
 #pragma once
 
 #include "common.cuh"
@@ -20,8 +21,30 @@ struct QMat {
     int qtype;
     int planar;
     uint32_t nrows, ncols, bpr;  // bpr = blocks per row = ncols / block_len(qtype)
-    const uint8_t *p0, *p1, *p2, *p3;
+    int nplanes;
+    uint32_t pitch[4];           // bytes per row of each plane
+    const uint8_t *p[4];
 };
+
+// Fills nplanes / pitch for a matrix of `bpr` blocks per row.
+__host__ __device__ inline void qmat_set_pitches(QMat &m)
+{
+    m.pitch[0] = m.pitch[1] = m.pitch[2] = m.pitch[3] = 0;
+    if (!m.planar) {
+        m.nplanes = 1;
+        m.pitch[0] = m.bpr * (uint32_t)block_bytes(m.qtype);
+    } else if (m.qtype == WGB_Q8_0) {
+        m.nplanes = 2;
+        m.pitch[0] = m.bpr * 32;
+        m.pitch[1] = (m.bpr * 2 + 15) & ~15u;
+    } else {  // Q6_K
+        m.nplanes = 4;
+        m.pitch[0] = m.bpr * 128;
+        m.pitch[1] = m.bpr * 64;
+        m.pitch[2] = m.bpr * 16;
+        m.pitch[3] = (m.bpr * 2 + 15) & ~15u;
+    }
+}
 
 }  // namespace wgb
 

@@ -1,6 +1,5 @@
 // Dequantisation kernels and the quantised-matrix object (upload, planar repack, row dequant).
-#include "dequant.cuh"
-#include "qmatrix.cuh"
+#include "qaccess.cuh"
 
 #include <new>
 
@@ -23,26 +22,6 @@ __global__ void dequant_raw_kernel(const uint8_t *__restrict__ blocks, size_t nw
     }
 }
 
-// Weight (row, col) of a matrix in either layout.
-template <int QT>
-__device__ __forceinline__ float qmat_weight(const QMat &m, size_t row, uint32_t col)
-{
-    constexpr int BL = block_len(QT), BB = block_bytes(QT);
-    const uint32_t kb = col / BL, r = col % BL;
-    const size_t blk = row * m.bpr + kb;
-    if (QT == WGB_Q8_0) {
-        if (m.planar) {
-            uint16_t s = ((const uint16_t *)m.p1)[blk];
-            return q8_0_value(s, (int8_t)m.p0[row * (size_t)m.ncols + col]);
-        }
-    } else if (QT == WGB_Q6_K) {
-        if (m.planar)
-            return q6_k_value(m.p0 + blk * 128, m.p1 + blk * 64, (const int8_t *)(m.p2 + blk * 16),
-                              ((const uint16_t *)m.p3)[blk], r >> 5, r & 31);
-    }
-    return dequant_one<QT>(m.p0 + blk * BB, r >> 5, r & 31);
-}
-
 // Rows [row0, row0+n) (or the single row *d_row when d_row != NULL) to dense f32.
 template <int QT>
 __global__ void dequant_rows_kernel(QMat m, size_t row0, size_t n, const uint32_t *d_row, float *__restrict__ out)
@@ -58,34 +37,36 @@ __global__ void dequant_rows_kernel(QMat m, size_t row0, size_t n, const uint32_
     }
 }
 
-// Raw Q8_0 blocks -> planes.  One thread per block.
-__global__ void repack_q8_0_kernel(const uint8_t *__restrict__ raw, size_t nblocks, uint8_t *__restrict__ qs,
-                                   uint16_t *__restrict__ d)
+// Raw Q8_0 blocks (row-major, bpr per row) -> planes.  One thread per block.
+__global__ void repack_q8_0_kernel(const uint8_t *__restrict__ raw, size_t nblocks, QMat m)
 {
     for (size_t b = blockIdx.x * (size_t)blockDim.x + threadIdx.x; b < nblocks;
          b += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = b / m.bpr, kb = b % m.bpr;
         const uint8_t *s = raw + b * 34;
-        d[b] = ld16(s);
-        uint32_t *dst = (uint32_t *)(qs + b * 32);
+        reinterpret_cast<uint16_t *>(const_cast<uint8_t *>(m.p[1]) + row * m.pitch[1])[kb] = ld16(s);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(const_cast<uint8_t *>(m.p[0]) + row * m.pitch[0] + kb * 32);
 #pragma unroll
         for (int i = 0; i < 8; i++) dst[i] = ld32(s + 2 + 4 * i);
     }
 }
 
 // Raw Q6_K blocks -> planes.  One thread per 4 bytes of a block's 208 data bytes + its d.
-__global__ void repack_q6_k_kernel(const uint8_t *__restrict__ raw, size_t nblocks, uint8_t *__restrict__ ql,
-                                   uint8_t *__restrict__ qh, uint8_t *__restrict__ sc, uint16_t *__restrict__ d)
+__global__ void repack_q6_k_kernel(const uint8_t *__restrict__ raw, size_t nblocks, QMat m)
 {
     const size_t total = nblocks * 53;  // 52 words of ql/qh/scales + one slot for d
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < total;
          e += (size_t)gridDim.x * blockDim.x) {
-        size_t b = e / 53;
-        int w = (int)(e % 53);
+        const size_t b = e / 53, row = b / m.bpr, kb = b % m.bpr;
+        const int w = (int)(e % 53);
         const uint8_t *s = raw + b * 210;
-        if (w < 32) ((uint32_t *)(ql + b * 128))[w] = ld32(s + 4 * w);
-        else if (w < 48) ((uint32_t *)(qh + b * 64))[w - 32] = ld32(s + 4 * w);
-        else if (w < 52) ((uint32_t *)(sc + b * 16))[w - 48] = ld32(s + 4 * w);
-        else d[b] = ld16(s + 208);
+        uint8_t *ql = const_cast<uint8_t *>(m.p[0]) + row * m.pitch[0] + kb * 128;
+        uint8_t *qh = const_cast<uint8_t *>(m.p[1]) + row * m.pitch[1] + kb * 64;
+        uint8_t *sc = const_cast<uint8_t *>(m.p[2]) + row * m.pitch[2] + kb * 16;
+        if (w < 32) reinterpret_cast<uint32_t *>(ql)[w] = ld32(s + 4 * w);
+        else if (w < 48) reinterpret_cast<uint32_t *>(qh)[w - 32] = ld32(s + 4 * w);
+        else if (w < 52) reinterpret_cast<uint32_t *>(sc)[w - 48] = ld32(s + 4 * w);
+        else reinterpret_cast<uint16_t *>(const_cast<uint8_t *>(m.p[3]) + row * m.pitch[3])[kb] = ld16(s + 208);
     }
 }
 
@@ -120,26 +101,15 @@ static bool is_supported(int qtype) { return block_bytes(qtype) != 0; }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Fills `view` plane pointers for a matrix of nrows x bpr blocks stored at `base`; returns bytes.
-static size_t layout_planes(int qtype, bool planar, size_t nrows, size_t bpr, uint8_t *base, QMat &v)
+// Fills the pitches and plane pointers of `v` (qtype, planar, bpr set) for `nrows` rows stored at `base`;
+// returns the bytes needed.
+static size_t layout_planes(size_t nrows, uint8_t *base, QMat &v)
 {
-    const size_t nb = nrows * bpr;
-    v.p1 = v.p2 = v.p3 = nullptr;
-    v.p0 = base;
-    if (!planar) return align_up(nb * block_bytes(qtype), 256);
+    qmat_set_pitches(v);
     size_t off = 0;
-    if (qtype == WGB_Q8_0) {
-        off = align_up(nb * 32, 256);
-        v.p1 = base + off;
-        off += align_up(nb * 2, 256);
-    } else {  // Q6_K
-        off = align_up(nb * 128, 256);
-        v.p1 = base + off;
-        off += align_up(nb * 64, 256);
-        v.p2 = base + off;
-        off += align_up(nb * 16, 256);
-        v.p3 = base + off;
-        off += align_up(nb * 2, 256);
+    for (int i = 0; i < 4; i++) {
+        v.p[i] = i < v.nplanes ? base + off : nullptr;
+        if (i < v.nplanes) off += align_up(nrows * (size_t)v.pitch[i], 256);
     }
     return off;
 }
@@ -147,10 +117,9 @@ static size_t layout_planes(int qtype, bool planar, size_t nrows, size_t bpr, ui
 static int repack_from_device_raw(int qtype, const uint8_t *d_raw, size_t nb, const QMat &v, cudaStream_t stream)
 {
     if (qtype == WGB_Q8_0) {
-        repack_q8_0_kernel<<<grid_for(nb, 256), 256, 0, stream>>>(d_raw, nb, (uint8_t *)v.p0, (uint16_t *)v.p1);
+        repack_q8_0_kernel<<<grid_for(nb, 256), 256, 0, stream>>>(d_raw, nb, v);
     } else {
-        repack_q6_k_kernel<<<grid_for(nb * 53, 256), 256, 0, stream>>>(d_raw, nb, (uint8_t *)v.p0, (uint8_t *)v.p1,
-                                                                         (uint8_t *)v.p2, (uint16_t *)v.p3);
+        repack_q6_k_kernel<<<grid_for(nb * 53, 256), 256, 0, stream>>>(d_raw, nb, v);
     }
     WGB_LAUNCH_CHECK("repack kernel");
     return WGB_OK;
@@ -176,10 +145,12 @@ int qmat_create_slice(int qtype, const void *h_blocks, size_t nrows, size_t ncol
     m->view.bpr = (uint32_t)bpr_keep;
     m->view.ncols = (uint32_t)(bpr_keep * bl);
     QMat tmp = m->view;
-    m->bytes = layout_planes(qtype, planar, nrows_keep, bpr_keep, nullptr, tmp);
+    m->bytes = layout_planes(nrows_keep, nullptr, tmp);
     cudaError_t e = cudaMalloc(&m->storage, m->bytes);
     if (e != cudaSuccess) { delete m; return cuda_fail(e, "cudaMalloc(quant matrix)"); }
-    layout_planes(qtype, planar, nrows_keep, bpr_keep, (uint8_t *)m->storage, m->view);
+    if (planar) e = cudaMemsetAsync(m->storage, 0, m->bytes, stream);  // pitch padding
+    if (e != cudaSuccess) { cudaFree(m->storage); delete m; return cuda_fail(e, "cudaMemset(quant matrix)"); }
+    layout_planes(nrows_keep, (uint8_t *)m->storage, m->view);
 
     const size_t raw_bytes = nrows_keep * bpr_keep * bb;
     uint8_t *d_raw = planar ? nullptr : (uint8_t *)m->storage;
@@ -223,10 +194,12 @@ int qmat_create(int qtype, const void *blocks, bool src_on_device, size_t nrows,
     m->view.bpr = (uint32_t)bpr;
     m->view.ncols = (uint32_t)ncols;
     QMat tmp = m->view;
-    m->bytes = layout_planes(qtype, planar, nrows, bpr, nullptr, tmp);
+    m->bytes = layout_planes(nrows, nullptr, tmp);
     cudaError_t e = cudaMalloc(&m->storage, m->bytes);
     if (e != cudaSuccess) { delete m; return cuda_fail(e, "cudaMalloc(quant matrix)"); }
-    layout_planes(qtype, planar, nrows, bpr, (uint8_t *)m->storage, m->view);
+    if (planar) e = cudaMemsetAsync(m->storage, 0, m->bytes, stream);  // pitch padding
+    if (e != cudaSuccess) { cudaFree(m->storage); delete m; return cuda_fail(e, "cudaMemset(quant matrix)"); }
+    layout_planes(nrows, (uint8_t *)m->storage, m->view);
     int rc = WGB_OK;
     if (planar) rc = repack_from_device_raw(qtype, (const uint8_t *)blocks, nrows * bpr, m->view, stream);
     else {
