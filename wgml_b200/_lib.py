@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libwgml_b200.so")
+LIB_PATH = os.environ.get("WGML_B200_LIB") or os.path.join(_HERE, "libwgml_b200.so")
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_PARSE, ERR_NOT_FOUND, ERR_TIMEOUT = range(7)
 STATUS_NAMES = ["OK", "ERR_INVALID", "ERR_UNSUPPORTED", "ERR_CUDA", "ERR_PARSE", "ERR_NOT_FOUND", "ERR_TIMEOUT"]

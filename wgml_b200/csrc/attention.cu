@@ -19,6 +19,7 @@ namespace wgb {
 constexpr int ATT_NT = 256;
 constexpr int ATT_WARPS = ATT_NT / 32;
 constexpr int ATT_CHUNK = 64;
+constexpr int ATT_TPW = ATT_CHUNK / ATT_WARPS;  // time steps per warp
 
 uint32_t attn_num_splits(uint32_t seq_len) { return (seq_len + ATT_CHUNK - 1) / ATT_CHUNK; }
 
@@ -65,26 +66,62 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
                           : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 
-    // Pass 1: scores of the chunk.
+    // Every warp owns ATT_TPW consecutive time steps.  All of their K and V rows are requested up front
+    // (independent loads, one DRAM round trip for the whole chunk), then consumed.
     const float *kbase = a.k_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
-    for (uint32_t tl = warp; tl < nt; tl += ATT_WARPS) {
-        float part[QH];
+    const float *vbase = a.v_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
+    float4 kr[ATT_TPW][VC], vr[ATT_TPW][VC];
 #pragma unroll
-        for (int j = 0; j < QH; j++) part[j] = 0.0f;
+    for (int i = 0; i < ATT_TPW; i++) {
+        const uint32_t tl = warp * ATT_TPW + i;
 #pragma unroll
         for (int c = 0; c < VC; c++) {
             const uint32_t ch = lane + 32 * c;
-            if (ch < nchunk) {
-                const float4 k = __ldcs(reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch);
+            const bool ok = tl < nt && ch < nchunk;
+            kr[i][c] = ok ? __ldcs(reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+            vr[i][c] = ok ? __ldcs(reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    // Pass 1: scores of the chunk.
 #pragma unroll
-                for (int j = 0; j < QH; j++)
-                    part[j] += q[j][c].x * k.x + q[j][c].y * k.y + q[j][c].z * k.z + q[j][c].w * k.w;
-            }
+    for (int j = 0; j < QH; j++) {
+        float part[ATT_TPW];
+#pragma unroll
+        for (int i = 0; i < ATT_TPW; i++) {
+            float p = 0.0f;
+#pragma unroll
+            for (int c = 0; c < VC; c++)
+                p += q[j][c].x * kr[i][c].x + q[j][c].y * kr[i][c].y + q[j][c].z * kr[i][c].z + q[j][c].w * kr[i][c].w;
+            part[i] = p;
+        }
+        // ATT_TPW sums over the warp at once: each halving step folds two partials into one lane half
+        // (8 -> 4 -> 2 -> 1 values per lane in 3 steps, then 2 plain steps): 7 + 2 shuffles instead of 40.
+        static_assert(ATT_TPW == 8, "the folding below is written for 8 time steps per warp");
+        float f4[4], f2[2], f1;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const bool up = lane & 16;
+            const float keep = up ? part[2 * i + 1] : part[2 * i], give = up ? part[2 * i] : part[2 * i + 1];
+            f4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
         }
 #pragma unroll
-        for (int j = 0; j < QH; j++) {
-            const float s = warp_sum(part[j]) / inv_sqrt;
-            if (lane == 0) s_score[j][tl] = s;
+        for (int i = 0; i < 2; i++) {
+            const bool up = lane & 8;
+            const float keep = up ? f4[2 * i + 1] : f4[2 * i], give = up ? f4[2 * i] : f4[2 * i + 1];
+            f2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+        }
+        {
+            const bool up = lane & 4;
+            const float keep = up ? f2[1] : f2[0], give = up ? f2[0] : f2[1];
+            f1 = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+        }
+        f1 += __shfl_xor_sync(0xffffffffu, f1, 2);
+        f1 += __shfl_xor_sync(0xffffffffu, f1, 1);
+        // lane l now holds the sum of time step i = (bit4 of l) + 2 * (bit3) + 4 * (bit2)
+        if ((lane & 3) == 0) {
+            const uint32_t i = ((lane >> 4) & 1) | (((lane >> 3) & 1) << 1) | (((lane >> 2) & 1) << 2);
+            const uint32_t tl = warp * ATT_TPW + i;
+            if (tl < nt) s_score[j][tl] = f1 / inv_sqrt;
         }
     }
     __syncthreads();
@@ -133,13 +170,13 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
     for (int j = 0; j < QH; j++)
 #pragma unroll
         for (int c = 0; c < VC; c++) acc[j][c] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float *vbase = a.v_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
-    for (uint32_t tl = warp; tl < nt; tl += ATT_WARPS) {
 #pragma unroll
-        for (int c = 0; c < VC; c++) {
-            const uint32_t ch = lane + 32 * c;
-            if (ch < nchunk) {
-                const float4 v = __ldcs(reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch);
+    for (int i = 0; i < ATT_TPW; i++) {
+        const uint32_t tl = warp * ATT_TPW + i;
+        if (tl < nt) {
+#pragma unroll
+            for (int c = 0; c < VC; c++) {
+                const float4 v = vr[i][c];
 #pragma unroll
                 for (int j = 0; j < QH; j++) {
                     const float p = s_score[j][tl];

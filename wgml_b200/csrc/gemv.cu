@@ -28,8 +28,17 @@
 
 namespace wgb {
 
-constexpr int GEMV_NCONS = 16;                      // consumer warps
-constexpr int GEMV_MAX_SLOTS = 8;                   // stages in work at once
+#ifndef WGB_GEMV_NCONS
+#define WGB_GEMV_NCONS 16
+#endif
+#ifndef WGB_GEMV_MINBLOCKS
+#define WGB_GEMV_MINBLOCKS 1
+#endif
+#ifndef WGB_GEMV_SMEM_KB
+#define WGB_GEMV_SMEM_KB 200
+#endif
+constexpr int GEMV_NCONS = WGB_GEMV_NCONS;          // consumer warps
+constexpr int GEMV_MAX_SLOTS = 8;                   // mini-slots of consumer warps
 constexpr int GEMV_CONS_THREADS = GEMV_NCONS * 32;
 constexpr int GEMV_NT = GEMV_CONS_THREADS + 32;     // + producer warp
 constexpr int GEMV_MAX_RS = 8;                      // rows per stage
@@ -247,7 +256,7 @@ __device__ __forceinline__ void group_epilogue(const GemvArgs &a, const Part (&p
 }
 
 template <int QT, int PRO, int EPI>
-__global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant__ GemvArgs a)
+__global__ void __launch_bounds__(GEMV_NT, WGB_GEMV_MINBLOCKS) gemv_kernel(const __grid_constant__ GemvArgs a)
 {
     using S = Step<QT>;
     constexpr int NPL = QT == WGB_Q6_K ? 4 : (QT == WGB_Q8_0 ? 2 : 1);   // planes of the format
@@ -585,12 +594,12 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
     for (int i = 0; i < a.nmat; i++) total_rows += a.mat[i].nrows;
     const bool pairs = a.epilogue == EPI_SILU_PAIR || a.epilogue == EPI_QKV_ROPE;
     const size_t image = (ximage_bytes(m0.qtype, m0.ncols) + 127) & ~(size_t)127;
-    const size_t budget_max = 200 * 1024;
+    const size_t budget_max = (size_t)WGB_GEMV_SMEM_KB * 1024, budget_hard = 200 * 1024;
     const uint32_t nsteps = steps_of(m0.qtype, m0.ncols);
     const uint32_t wk = nsteps < (uint32_t)GEMV_NCONS ? nsteps : (uint32_t)GEMV_NCONS;
     uint32_t slots = GEMV_NCONS / wk;             // mini-slots of wk warps
     if (slots > GEMV_MAX_SLOTS) slots = GEMV_MAX_SLOTS;
-    const uint32_t nslot = slots >= 8 ? 2 : 1;      // stage slots
+    const uint32_t nslot = slots >= 4 ? 2 : 1;      // stage slots
     const uint32_t rslots = slots / nslot;          // row slots per stage
     uint32_t best_rs = 0;
     double best_score = -1.0;
@@ -598,7 +607,7 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
         if (pairs && (rs & 1)) continue;
         const size_t stage = ((size_t)rs * row_bytes + 127) & ~(size_t)127;
         if (image + (nslot + 3) * stage > budget_max && rs > (pairs ? 2u : 1u)) continue;   // ring: stages in work + 3 in flight
-        if (image + 2 * stage > budget_max) continue;
+        if (image + 2 * stage > budget_hard) continue;
         if (a.epilogue == EPI_QKV_ROPE) {
             bool ok = true;
             for (int i = 0; i < 3; i++) ok = ok && a.mat[i].nrows % rs == 0;
@@ -622,7 +631,8 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
     a.stage_bytes = (uint32_t)(((size_t)best_rs * row_bytes + 127) & ~(size_t)127);
     grid = a.ngroups < sms ? a.ngroups : sms;
     const uint32_t per_block = (a.ngroups + grid - 1) / grid;
-    uint32_t ns = (uint32_t)((budget_max - image) / a.stage_bytes);
+    const size_t budget = image + (nslot + 3) * (size_t)a.stage_bytes > budget_max ? budget_hard : budget_max;
+    uint32_t ns = (uint32_t)((budget - image) / a.stage_bytes);
     if (ns > GEMV_MAX_STAGES) ns = GEMV_MAX_STAGES;
     if (ns > per_block) ns = per_block;
     if (ns < 1) ns = 1;
@@ -635,6 +645,38 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
     return true;
 }
 
+template <int QT>
+static int set_smem_attr()
+{
+    const int bytes = 200 * 1024;
+#define WGB_ATTR(PRO, EPI) WGB_CUDA(cudaFuncSetAttribute(gemv_kernel<QT, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))
+    WGB_ATTR(PRO_NONE, EPI_STORE);
+    WGB_ATTR(PRO_RMS, EPI_STORE);
+    WGB_ATTR(PRO_LN, EPI_STORE);
+    WGB_ATTR(PRO_NONE, EPI_RESIDUAL);
+    WGB_ATTR(PRO_RMS, EPI_SILU_PAIR);
+    WGB_ATTR(PRO_LN, EPI_GELU);
+    WGB_ATTR(PRO_RMS, EPI_QKV_ROPE);
+    WGB_ATTR(PRO_LN, EPI_QKV_SPLIT);
+#undef WGB_ATTR
+    return WGB_OK;
+}
+
+// One-time set-up of the fused kernels on the current device: the status word and the opt-in to
+// large dynamic shared memory.  Must first run outside stream capture (model creation does).
+int gemv_global_init()
+{
+    static bool done = false;
+    if (done) return WGB_OK;
+    int rc = ensure_err();
+    if (rc) return rc;
+    if ((rc = set_smem_attr<WGB_Q4_K>()) || (rc = set_smem_attr<WGB_Q6_K>()) || (rc = set_smem_attr<WGB_Q8_0>()) ||
+        (rc = set_smem_attr<WGB_F32>()))
+        return rc;
+    done = true;
+    return WGB_OK;
+}
+
 template <int QT, int PRO, int EPI>
 static int launch_one(GemvArgs &a, cudaStream_t stream, bool pdl)
 {
@@ -642,7 +684,7 @@ static int launch_one(GemvArgs &a, cudaStream_t stream, bool pdl)
     size_t smem = 0;
     uint32_t grid = 0;
     if (!plan(a, smem, grid)) return fail(WGB_ERR_UNSUPPORTED, "matrix shape does not fit the fused kernel");
-    int rc = ensure_err();
+    int rc = gemv_global_init();
     if (rc) return rc;
     a.err = g_err;
 #ifdef WGB_DBG_TIMING
@@ -656,11 +698,6 @@ static int launch_one(GemvArgs &a, cudaStream_t stream, bool pdl)
     }
     a.dbg = dbg;
 #endif
-    static thread_local size_t configured = 0;  // per instantiation and thread
-    if (smem > 48 * 1024 && smem > configured) {
-        WGB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured = 200 * 1024;
-    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(GEMV_NT);

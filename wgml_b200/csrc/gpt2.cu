@@ -242,6 +242,7 @@ WGB_EXPORT int wgb_gpt2_create(const wgb_gpt2_params *params, wgb_gpt2 **out)
     const uint32_t hs = p.n_embd / p.n_head;
     WGB_REQUIRE(hs % 4 == 0 && hs <= 256, "head size %u unsupported (multiple of 4, at most 256)", hs);
     WGB_REQUIRE(p.attn_b == 0 || p.attn_b == 3 * p.n_embd, "attn_b %u is not 3 * n_embd", p.attn_b);
+    { const int rc0 = gemv_global_init(); if (rc0) return rc0; }
     wgb_gpt2 *m = new (std::nothrow) wgb_gpt2();
     if (!m) return fail(WGB_ERR_INVALID, "out of host memory");
     m->p = p;

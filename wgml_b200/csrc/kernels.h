@@ -64,6 +64,8 @@ struct GemvArgs {
 // weights before waiting for its predecessor).
 int launch_gemv(const GemvArgs &a, cudaStream_t stream, bool pdl);
 bool gemv_fast_supported(const QMat &m);
+// One-time per-process set-up of the fused kernels (call outside stream capture).
+int gemv_global_init();
 // WGB_ERR_TIMEOUT if any bounded wait of a fused kernel expired since the last call (synchronises).
 int gemv_check_status();
 

@@ -313,6 +313,7 @@ WGB_EXPORT int wgb_llama2_create(const wgb_llama2_config *cfg, int model_type, i
     WGB_REQUIRE(hs % 4 == 0 && hs <= 256, "head size %u unsupported (multiple of 4, at most 256)", hs);
     WGB_REQUIRE(c.dim % 4 == 0 && c.hidden_dim % 4 == 0, "dimensions must be multiples of 4");
     WGB_REQUIRE(c.n_kv_heads % tp_size == 0, "n_kv_heads %u is not a multiple of the tensor-parallel size %d", c.n_kv_heads, tp_size);
+    { const int rc0 = gemv_global_init(); if (rc0) return rc0; }
     wgb_llama2 *m = new (std::nothrow) wgb_llama2();
     if (!m) return fail(WGB_ERR_INVALID, "out of host memory");
     m->cfg = c;
