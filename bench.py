@@ -148,8 +148,11 @@ def token_bytes(cfg: dict, pos: int, tp: int = 1) -> float:
     return total + launch_bytes(cfg, "logits", -1, pos, tp)[0]
 
 
-def build_gpu_model(cfg: dict, seed: int, tp_rank: int = 0, tp_size: int = 1):
-    """Generates the tensors layer by layer (host memory stays bounded) and uploads them."""
+def build_gpu_model(cfg: dict, seed: int, tp_rank: int = 0, tp_size: int = 1, distinct_layers: int | None = None):
+    """Generates the tensors layer by layer (host memory stays bounded) and uploads them.  With
+    `distinct_layers` = d < n_layers only the tensors of layers 0..d-1 are generated and layer l gets
+    those of layer l % d: every layer still owns its copy in HBM, the host just draws fewer random
+    blocks (the 70B-class model would otherwise spend minutes in the generator on every rank)."""
     import ctypes as C
 
     from wgml_b200 import _lib, synth
@@ -161,15 +164,22 @@ def build_gpu_model(cfg: dict, seed: int, tp_rank: int = 0, tp_size: int = 1):
     kv = c.kv_dim
     shapes = {"attn_q": (c.dim, c.dim), "attn_k": (kv, c.dim), "attn_v": (kv, c.dim), "attn_output": (c.dim, c.dim),
               "ffn_gate": (c.hidden_dim, c.dim), "ffn_up": (c.hidden_dim, c.dim), "ffn_down": (c.dim, c.hidden_dim)}
+    d = c.n_layers if not distinct_layers else min(distinct_layers, c.n_layers)
+    cache = {}
     for l in range(c.n_layers):
-        t = synth.llama_tensors(cfg, seed, layers=[l])
+        src = l % d
+        if src not in cache:
+            cache[src] = synth.llama_tensors(cfg, seed, layers=[src], model_tensors=(l == 0))
+        t = cache[src]
         for i, nm in enumerate(LLAMA_MATS):
-            qt, arr = t[f"blk.{l}.{nm}.weight"]
+            qt, arr = t[f"blk.{src}.{nm}.weight"]
             raw = np.ascontiguousarray(arr).view(np.uint8).reshape(-1)
             _lib.check(lib.wgb_llama2_set_matrix(m._h, l, i, qt, raw.ctypes.data, *shapes[nm]))
         for i, nm in enumerate(("attn_norm.weight", "ffn_norm.weight")):
-            v = np.ascontiguousarray(t[f"blk.{l}.{nm}"][1], dtype=np.float32)
+            v = np.ascontiguousarray(t[f"blk.{src}.{nm}"][1], dtype=np.float32)
             _lib.check(lib.wgb_llama2_set_vector(m._h, l, i, v.ctypes.data, v.size))
+        if d == c.n_layers:
+            del cache[src]
         if l == 0:
             for which, key in ((0, "token_embd.weight"), (1, "output.weight")):
                 qt, arr = t[key]
@@ -177,7 +187,6 @@ def build_gpu_model(cfg: dict, seed: int, tp_rank: int = 0, tp_size: int = 1):
                 _lib.check(lib.wgb_llama2_set_matrix(m._h, -1, which, qt, raw.ctypes.data, c.vocab_size, c.dim))
             v = np.ascontiguousarray(t["output_norm.weight"][1], dtype=np.float32)
             _lib.check(lib.wgb_llama2_set_vector(m._h, -1, 0, v.ctypes.data, v.size))
-        del t
     return m
 
 
@@ -266,10 +275,12 @@ def run_b200(args):
     K, W = args.steps, args.warmup
     cfg = model_cfg(workload, prompt_len + W + 2 * K + 8)
     from wgml_b200 import synth
-    model = build_gpu_model(cfg, args.seed, rank, world)
+    distinct = 2 if workload == "llama2-70b" else None
+    model = build_gpu_model(cfg, args.seed, rank, world, distinct)
     if world > 1:
         from wgml_b200 import tp
-        tp.attach(model)
+        comm = tp.init_from_torch_distributed()
+        tp.attach(model, comm)
     prompt = synth.prompt(prompt_len, cfg["vocab_size"], args.seed)
 
     def barrier():
@@ -352,7 +363,11 @@ def run_b200(args):
         "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "prompt_len": prompt_len, "decode_steps": K, "batch": 1,
-                   "parallelism": f"tp{world}" if world > 1 else "single GPU", "weights_gb": None,
+                   "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                   "weights_gb": sum(matrix_bytes(cfg, l, n)[0] for l in range(cfg["n_layers"]) for n in
+                                     ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")) / 1e9
+                                 + matrix_bytes(cfg, -1, "output")[0] / 1e9,
+                   "synthetic_layers": "all distinct" if not distinct else f"layers cycle through {distinct} generated tensor sets",
                    "timing": "CUDA events on the launch stream; the weights (far larger than the 126 MB L2) are re-read every token"},
         "e2e": {"value": K / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
                 "ms_per_step": ms_e2e / K, "wall_ms_per_step": 1e3 * wall_e2e / K,

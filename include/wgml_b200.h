@@ -260,8 +260,9 @@ int wgb_llama2_set_matrix(wgb_llama2 *m, int layer, int which, int qtype, const 
 int wgb_llama2_set_vector(wgb_llama2 *m, int layer, int which, const float *h_data, size_t n);
 /* Llama2Weights::from_gguf (transformer.rs:151-268): same tensor names. */
 int wgb_llama2_load_gguf(wgb_llama2 *m, const wgb_gguf *g);
-/* Optional: share an NCCL communicator (an `ncclComm_t` passed as void *) for tp_size > 1. */
-int wgb_llama2_set_comm(wgb_llama2 *m, void *nccl_comm);
+/* Required for tp_size > 1: the communicator of the tensor-parallel group (see wgb_comm_create below);
+ * `comm` is a `wgb_comm *`.  The model does not own it. */
+int wgb_llama2_set_comm(wgb_llama2 *m, void *comm);
 /* 1 (default): fused kernels (norm + matrix product + RoPE / KV append / SiLU / residual in one
  * launch each).  0: one launch per reference dispatch, in the order of Llama2::dispatch
  * (transformer.rs:310-427); also what is used when a layer mixes block formats that have no fused
@@ -295,6 +296,26 @@ int wgb_llama2_kernels_per_token(const wgb_llama2 *m);
  * At most `cap` entries are written; *n_out is their number. */
 int wgb_llama2_profile_step(wgb_llama2 *m, uint32_t token, uint32_t pos, void *stream, int cap,
                             int *kinds, int *layers, float *ms, int *n_out);
+
+/* ---- Tensor-parallel group ----
+ * No counterpart in the reference, which runs on one device (crates/wgml-bench/src/main.rs:23-36 picks
+ * a single adapter); this is what lets Llama-2-70B-sized weights be sharded over several GPUs.  One
+ * process per GPU.  Rank 0 makes an id, the host program hands it to the other ranks (MPI,
+ * torch.distributed, a file), then every rank calls wgb_comm_create with its device current.
+ * Sharding: Q/K/V, gate and up keep the rows of their heads / hidden slice; attn_output and ffn_down
+ * keep the matching columns and their partial products are summed over the group (NCCL all-reduce,
+ * the residual added by rank 0 before the sum); embeddings, norms and the output matrix are replicated. */
+#define WGB_COMM_ID_BYTES 128
+typedef struct wgb_comm wgb_comm;
+int wgb_comm_unique_id(void *id_out /* WGB_COMM_ID_BYTES */);
+int wgb_comm_create(const void *id, int rank, int size, wgb_comm **out);
+int wgb_comm_destroy(wgb_comm *c);
+int wgb_comm_rank(const wgb_comm *c);
+int wgb_comm_size(const wgb_comm *c);
+/* d_recv[i] = sum over ranks of d_send[i]; in place when d_send == d_recv. */
+int wgb_comm_all_reduce_sum(wgb_comm *c, const float *d_send, float *d_recv, size_t n, void *stream);
+/* d_recv[r * n_per_rank + i] = rank r's d_send[i]. */
+int wgb_comm_all_gather(wgb_comm *c, const float *d_send, float *d_recv, size_t n_per_rank, void *stream);
 
 /* ---- GPT-2 ---- */
 

@@ -122,6 +122,13 @@ SIGNATURES = {
     "wgb_llama2_decode": (_i, [_vp, _vp, _sz, _sz, _u32, _vp, _vp]),
     "wgb_llama2_kernels_per_token": (_i, [_vp]),
     "wgb_llama2_profile_step": (_i, [_vp, _u32, _u32, _vp, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_f), C.POINTER(_i)]),
+    "wgb_comm_unique_id": (_i, [_vp]),
+    "wgb_comm_create": (_i, [_vp, _i, _i, _pp]),
+    "wgb_comm_destroy": (_i, [_vp]),
+    "wgb_comm_rank": (_i, [_vp]),
+    "wgb_comm_size": (_i, [_vp]),
+    "wgb_comm_all_reduce_sum": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "wgb_comm_all_gather": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "wgb_gpt2_params_from_gguf": (_i, [_vp, C.POINTER(Gpt2ParamsC)]),
     "wgb_gpt2_create": (_i, [C.POINTER(Gpt2ParamsC), _pp]),
     "wgb_gpt2_destroy": (_i, [_vp]),

@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "csrc", "build")
 LIB = os.path.join(HERE, "libwgml_b200.so")
 
-SOURCES = ["api.cpp", "gguf.cpp", "quant.cu", "gemv.cu", "attention.cu", "ops.cu", "llama2.cu", "gpt2.cu"]
+SOURCES = ["api.cpp", "gguf.cpp", "quant.cu", "gemv.cu", "attention.cu", "ops.cu", "llama2.cu", "gpt2.cu", "comm.cpp"]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-fvisibility=hidden",
@@ -60,7 +60,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if r.returncode != 0:
                     raise RuntimeError("nvcc failed for " + cmd[-3])
     if jobs or force or _stale(LIB, objs):
-        cmd = [nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart"]
+        cmd = [nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or r.returncode != 0:
             sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)

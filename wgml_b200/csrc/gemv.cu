@@ -1,22 +1,27 @@
 // Matrix-vector kernels: the fused, TMA-fed kernel used by the models and by GemvQuant, and the
 // generic per-format fallback.
 //
-// Fused kernel.  One persistent block per SM: eight consumer warps and one producer warp.
-//   * Rows are taken in groups of `rs` (2..8) that lie contiguously in HBM.  The producer streams
+// Fused kernel.  One persistent block per SM with three roles: sixteen consumer warps, a producer
+// warp and an epilogue warp.
+//   * Rows are taken in groups of `rs` (1..8) that lie contiguously in HBM.  The producer streams
 //     group after group into a ring of shared-memory stages with one bulk asynchronous copy
 //     (cp.async.bulk, completion on an mbarrier) per plane of the group, running as many stages
-//     ahead as the ring holds.  It starts before the kernel waits for its predecessor in the stream
-//     (programmatic dependent launch): weights never depend on activations, so a kernel fills its
-//     ring -- the whole matrix, for the small ones -- while the previous kernel is still finishing.
-//   * The consumers build the shared image of the (normalised) input vector once.  They are split
-//     into slots of `wk` warps; the warps of a slot each own one column step of the matrix (so their
-//     part of the input stays in registers for the whole kernel) and together take every nslot-th
-//     stage.  The per-row partial sums of the column steps meet in shared memory behind a barrier
-//     private to the slot; the slot's first warp adds them and runs the epilogue (bias, residual,
-//     SiLU gate, GELU, RoPE + KV-cache append), one lane per output row.  Slots never wait for each
-//     other, so several stages are in work at any time.
+//     ahead as the ring holds and handling several stages per pass, one per group of lanes.  It
+//     starts before the kernel waits for its predecessor in the stream (programmatic dependent
+//     launch): weights never depend on activations.
+//   * The consumers build the shared image of the (normalised) input vector once.  Consumer warp w
+//     owns column part w % kp of the matrix for the whole kernel, so its share of the input stays in
+//     registers; the warps of one column part form ncl = 16 / kp "lanes" that take the (stage, row
+//     part) tasks of the block in turn.  A task is `rrows` rows of one stage: the warp computes the
+//     partial dot products, folds them across its lanes with a transposing butterfly (9 shuffles for
+//     up to 8 rows), writes them to shared memory and arrives on the stage's `done` barrier.
+//     Consumers never wait for each other or for the epilogue.
+//   * The epilogue warp waits for `done`, adds the column parts of every row in a fixed order,
+//     releases the stage to the producer and applies the epilogue (bias, residual, SiLU gate, GELU,
+//     RoPE + KV-cache append), one lane per output unit.  Its global loads (bias, residual, position)
+//     are issued before the wait, so they overlap the consumers' work on the stage.
 //   * Group g belongs to block g % gridDim.x, so every SM gets the same number of groups to within
-//     one; rs is chosen per launch for the best balance.
+//     one; rs and the row split are chosen per launch (see plan()).
 // Every mbarrier wait is bounded: after ~2^22 polls a waiter records an error code in the launch's
 // status word and carries on with whatever is in shared memory, so the kernel always terminates.
 #include "gemv_core.cuh"
@@ -28,22 +33,16 @@
 
 namespace wgb {
 
-#ifndef WGB_GEMV_NCONS
-#define WGB_GEMV_NCONS 16
-#endif
-#ifndef WGB_GEMV_MINBLOCKS
-#define WGB_GEMV_MINBLOCKS 1
-#endif
-#ifndef WGB_GEMV_SMEM_KB
-#define WGB_GEMV_SMEM_KB 200
-#endif
-constexpr int GEMV_NCONS = WGB_GEMV_NCONS;          // consumer warps
-constexpr int GEMV_MAX_SLOTS = 8;                   // mini-slots of consumer warps
+constexpr int GEMV_NCONS = 16;                      // consumer warps
 constexpr int GEMV_CONS_THREADS = GEMV_NCONS * 32;
-constexpr int GEMV_NT = GEMV_CONS_THREADS + 32;     // + producer warp
+constexpr int GEMV_PRODUCER = GEMV_NCONS;           // warp index of the producer
+constexpr int GEMV_EPILOGUE = GEMV_NCONS + 1;       // warp index of the epilogue warp
+constexpr int GEMV_NT = (GEMV_EPILOGUE + 1) * 32;
 constexpr int GEMV_MAX_RS = 8;                      // rows per stage
-constexpr int GEMV_MAX_STAGES = 16;
+constexpr int GEMV_MAX_STAGES = 24;
 constexpr uint32_t GEMV_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t GEMV_ROPE_TAB = 128;             // pair indices with a precomputed rotation
+constexpr size_t GEMV_SMEM_BUDGET = 200 * 1024;     // dynamic shared memory per block
 
 __device__ __forceinline__ float4 ld_act4(const float *p)
 {
@@ -51,13 +50,8 @@ __device__ __forceinline__ float4 ld_act4(const float *p)
 }
 
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_CONS_THREADS) : "memory"); }
-// Barrier among the `nthreads` threads of consumer slot `slot` (named barriers 2..2+GEMV_MAX_SLOTS-1).
-__device__ __forceinline__ void slot_sync(uint32_t slot, uint32_t nthreads)
-{
-    asm volatile("bar.sync %0, %1;" ::"r"(slot + 2), "r"(nthreads) : "memory");
-}
 
-// Sum / max over the 256 consumer threads (named barrier 1); every consumer gets the result.
+// Sum over the consumer threads (named barrier 1); every consumer gets the result.
 __device__ __forceinline__ float cons_sum(float v, float *red)
 {
     v = warp_sum(v);
@@ -68,6 +62,29 @@ __device__ __forceinline__ float cons_sum(float v, float *red)
     float t = (lane < GEMV_NCONS) ? red[lane] : 0.0f;
     static_assert(GEMV_NCONS <= 32, "one partial per consumer warp");
     return warp_sum(t);
+}
+
+// Sums acc[0..8) over the lanes of the warp.  Lane l returns the total of row
+// 4 * bit4(l) + 2 * bit3(l) + bit2(l); the four lanes that share bits 2..4 hold the same value.
+__device__ __forceinline__ float warp_sum8(const float (&acc)[8], int lane)
+{
+    float a4[4], a2[2];
+    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float keep = h16 ? acc[i + 4] : acc[i], send = h16 ? acc[i] : acc[i + 4];
+        a4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const float keep = h8 ? a4[i + 2] : a4[i], send = h8 ? a4[i] : a4[i + 2];
+        a2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    const float keep = h4 ? a2[1] : a2[0], send = h4 ? a2[0] : a2[1];
+    float v = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v;
 }
 
 // ---- mbarrier / bulk-copy primitives ---------------------------------------------------------
@@ -110,6 +127,19 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uin
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
+}
+
+// Stages per pass of the epilogue warp and of the producer warp.  The lanes of a warp may be held at a
+// reconvergence point until all of them have left their wait, so a pass must be assumed to finish only
+// when every stage in it has: the epilogue pass that frees a slot must never contain a stage whose copy
+// the producer can only issue in a pass that needs that very slot.  epilogue_batch + producer_batch <=
+// nstage + 1 rules the cycle out; the producer also leaves half of the ring queued while it waits.
+__host__ __device__ inline uint32_t epilogue_batch(uint32_t nstage) { return nstage >= 8 ? 4u : (nstage >= 4 ? 2u : 1u); }
+__host__ __device__ inline uint32_t producer_batch(uint32_t nstage, uint32_t copies_per_stage)
+{
+    uint32_t b = nstage / 2;
+    if (b > 32 / copies_per_stage) b = 32 / copies_per_stage;
+    return b < 1 ? 1 : b;
 }
 
 // ---- groups ------------------------------------------------------------------------------------
@@ -161,18 +191,6 @@ __device__ __forceinline__ float gelu_f32(float x)
     return 0.5f * x * (1.0f + tanhf(SQRT_2_OVER_PI * x * (1.0f + GELU_COEF_A * x * x)));
 }
 
-// RoPE (ops/rope.wgsl:36-77): angle = pos * base^(-(2i % head_size) / head_size) for pair (r0, r1).
-__device__ __forceinline__ void rope_pair(const GemvArgs &a, uint32_t r0, uint32_t pos, float &y0, float &y1)
-{
-    const uint32_t half = a.head_size / 2;
-    const uint32_t fi = (a.rope_variant == WGB_ROPE_NEOX) ? (r0 % a.head_size) : ((r0 / 2) % half);
-    float sn, cs;
-    sincosf((float)pos * a.rope_freq[fi], &sn, &cs);
-    const float t0 = cs * y0 - sn * y1, t1 = sn * y0 + cs * y1;
-    y0 = t0;
-    y1 = t1;
-}
-
 // Output units of a group (a unit = the stage rows that make one output: a row, or a pair) and the
 // stage rows of unit u.
 template <int EPI>
@@ -189,133 +207,219 @@ __device__ __forceinline__ void unit_rows(const Part (&parts)[2], int nparts, ui
     else { ra = u; rb = u; }
 }
 
-// Row slot that owns stage row j (the slot of the unit the row belongs to).
-template <int EPI>
-__device__ __forceinline__ uint32_t row_slot_of(const Part (&parts)[2], int nparts, uint32_t n, uint32_t j, uint32_t rsl)
-{
-    uint32_t u;
-    if (EPI == EPI_SILU_PAIR || (EPI == EPI_QKV_ROPE && nparts == 2)) u = j >= n ? j - n : j;
-    else if (EPI == EPI_QKV_ROPE && parts[0].mat < 2) u = j / 2;
-    else u = j;
-    return u % rsl;
-}
+// What the epilogue of one output unit needs besides the dot products; gathered before the unit's
+// sums are ready so that the global loads overlap the consumers' work.
+struct EpiCtx {
+    bool on;            // the lane has a unit
+    uint32_t r0, r1;    // output rows of the unit (matrix row indices)
+    float b0, b1;       // bias of r0 / r1, or the residual in b1 for EPI_RESIDUAL
+    float sn, cs;       // RoPE rotation
+    float *dst;         // EPI_QKV_*: where the rows of the unit go
+};
 
-// Epilogue of output unit t of a group; `sum(r)` gives the finished dot product of stage row r.
-template <int EPI, typename SumF>
-__device__ __forceinline__ void group_epilogue(const GemvArgs &a, const Part (&parts)[2], int nparts, uint32_t n, uint32_t t, SumF sum)
+template <int EPI>
+__device__ __forceinline__ EpiCtx epi_prepare(const GemvArgs &a, const Part (&parts)[2], int nparts, uint32_t n, uint32_t t,
+                                              uint32_t nunits, const float2 *rope_tab)
 {
+    EpiCtx c = {};
+    c.on = t < nunits;
+    if (!c.on) return c;
     if (EPI == EPI_STORE || EPI == EPI_RESIDUAL || EPI == EPI_GELU) {
-        if (t < n) {
-            const uint32_t row = parts[0].row0 + t;
-            float y = sum(t);
-            if (a.bias) y += a.bias[row];
-            if (EPI == EPI_RESIDUAL) y = a.residual[row] + y;
-            if (EPI == EPI_GELU) y = gelu_f32(y);
-            a.out[row] = y;
-        }
+        c.r0 = parts[0].row0 + t;
+        if (a.bias) c.b0 = a.bias[c.r0];
+        if (EPI == EPI_RESIDUAL) c.b1 = a.residual[c.r0];
     } else if (EPI == EPI_SILU_PAIR) {
-        if (t < n) {
-            const float g = sum(t), u = sum(n + t);
-            a.out[parts[0].row0 + t] = u * (g / (1.0f + expf(-g)));
-        }
+        c.r0 = parts[0].row0 + t;
     } else if (EPI == EPI_QKV_ROPE) {
         const int s = parts[0].mat;
         const float *bias = s == 0 ? a.bias : (s == 1 ? a.bias_k : a.bias_v);
         const uint32_t pos = *a.pos;
-        float *dst = s == 0 ? a.out : ((s == 1 ? a.k_cache : a.v_cache) + (size_t)pos * a.kv_dim);
+        c.dst = s == 0 ? a.out : ((s == 1 ? a.k_cache : a.v_cache) + (size_t)pos * a.kv_dim);
         if (s == 2) {
-            if (t < n) {
-                const uint32_t row = parts[0].row0 + t;
-                dst[row] = sum(t) + (bias ? bias[row] : 0.0f);
+            c.r0 = c.r1 = parts[0].row0 + t;
+        } else if (nparts == 2) {   // Neox: pairs (r0 + t, r0 + t + head_size / 2)
+            c.r0 = parts[0].row0 + t;
+            c.r1 = parts[1].row0 + t;
+        } else {                    // Original: adjacent pairs
+            c.r0 = parts[0].row0 + 2 * t;
+            c.r1 = c.r0 + 1;
+        }
+        if (bias) {
+            c.b0 = bias[c.r0];
+            c.b1 = bias[c.r1];
+        }
+        if (s < 2) {
+            // RoPE (ops/rope.wgsl:36-77): angle = pos * base^(-(2i % head_size) / head_size) for pair (r0, r1)
+            const uint32_t half = a.head_size / 2;
+            const uint32_t fi = (a.rope_variant == WGB_ROPE_NEOX) ? (c.r0 % a.head_size) : ((c.r0 / 2) % half);
+            if (half <= GEMV_ROPE_TAB) {
+                const float2 r = rope_tab[fi];
+                c.cs = r.x;
+                c.sn = r.y;
+            } else {
+                sincosf((float)pos * a.rope_freq[fi], &c.sn, &c.cs);
             }
-        } else if (nparts == 2) {  // Neox: pairs (r0 + t, r0 + t + head_size/2)
-            if (t < n) {
-                const uint32_t r0 = parts[0].row0 + t, r1 = parts[1].row0 + t;
-                float y0 = sum(t) + (bias ? bias[r0] : 0.0f), y1 = sum(n + t) + (bias ? bias[r1] : 0.0f);
-                rope_pair(a, r0, pos, y0, y1);
-                dst[r0] = y0;
-                dst[r1] = y1;
-            }
-        } else if (t < n / 2) {  // Original: adjacent pairs
-            const uint32_t r0 = parts[0].row0 + 2 * t;
-            float y0 = sum(2 * t) + (bias ? bias[r0] : 0.0f), y1 = sum(2 * t + 1) + (bias ? bias[r0 + 1] : 0.0f);
-            rope_pair(a, r0, pos, y0, y1);
-            dst[r0] = y0;
-            dst[r0 + 1] = y1;
         }
     } else if (EPI == EPI_QKV_SPLIT) {
-        if (t < n) {
-            const uint32_t row = parts[0].row0 + t, d = a.kv_dim, pos = *a.pos;
-            float y = sum(t);
-            if (a.bias) y += a.bias[row];
-            if (row < d) a.out[row] = y;
-            else if (row < 2 * d) a.k_cache[(size_t)pos * d + (row - d)] = y;
-            else a.v_cache[(size_t)pos * d + (row - 2 * d)] = y;
+        const uint32_t row = parts[0].row0 + t, d = a.kv_dim, pos = *a.pos;
+        c.r0 = row;
+        if (a.bias) c.b0 = a.bias[row];
+        if (row < d) c.dst = a.out + row;
+        else if (row < 2 * d) c.dst = a.k_cache + (size_t)pos * d + (row - d);
+        else c.dst = a.v_cache + (size_t)pos * d + (row - 2 * d);
+    }
+    return c;
+}
+
+// ya / yb: finished dot products of the unit's first / second stage row.
+template <int EPI>
+__device__ __forceinline__ void epi_finish(const GemvArgs &a, const Part (&parts)[2], const EpiCtx &c, float ya, float yb)
+{
+    if (!c.on) return;
+    if (EPI == EPI_STORE || EPI == EPI_RESIDUAL || EPI == EPI_GELU) {
+        float y = ya;
+        if (a.bias) y += c.b0;
+        if (EPI == EPI_RESIDUAL) y = c.b1 + y;
+        if (EPI == EPI_GELU) y = gelu_f32(y);
+        a.out[c.r0] = y;
+    } else if (EPI == EPI_SILU_PAIR) {
+        a.out[c.r0] = yb * (ya / (1.0f + expf(-ya)));
+    } else if (EPI == EPI_QKV_ROPE) {
+        if (parts[0].mat == 2) {
+            c.dst[c.r0] = ya + c.b0;
+        } else {
+            const float y0 = ya + c.b0, y1 = yb + c.b1;
+            c.dst[c.r0] = c.cs * y0 - c.sn * y1;
+            c.dst[c.r1] = c.sn * y0 + c.cs * y1;
         }
+    } else if (EPI == EPI_QKV_SPLIT) {
+        *c.dst = ya + c.b0;
     }
 }
 
 template <int QT, int PRO, int EPI>
-__global__ void __launch_bounds__(GEMV_NT, WGB_GEMV_MINBLOCKS) gemv_kernel(const __grid_constant__ GemvArgs a)
+__global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant__ GemvArgs a)
 {
     using S = Step<QT>;
     constexpr int NPL = QT == WGB_Q6_K ? 4 : (QT == WGB_Q8_0 ? 2 : 1);   // planes of the format
     extern __shared__ uint4 smem4[];
     __shared__ float red[32];
-    __shared__ float part[GEMV_MAX_STAGES][GEMV_MAX_RS][GEMV_NCONS];
-    __shared__ __align__(8) unsigned long long bars[2 * GEMV_MAX_STAGES];
+    __shared__ float part[GEMV_MAX_STAGES][GEMV_NCONS][GEMV_MAX_RS];    // [stage][column part][stage row]
+    __shared__ __align__(8) unsigned long long bars[3 * GEMV_MAX_STAGES];
+    __shared__ float2 rope_tab[EPI == EPI_QKV_ROPE ? GEMV_ROPE_TAB : 1];     // (cos, sin) per pair index of a head
 
     const uint32_t K = a.mat[0].ncols;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t nstage = a.nstage;
     uint8_t *smem = reinterpret_cast<uint8_t *>(smem4);
     const uint32_t ring = smem_addr(smem + a.ring_offset);
-    const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[GEMV_MAX_STAGES]);
+    const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[GEMV_MAX_STAGES]),
+                   done0 = smem_addr(&bars[2 * GEMV_MAX_STAGES]);
+    const uint32_t kp = a.kparts, rparts = a.rparts;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < nstage; s++) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, a.wk * a.rslots);
+            mbar_init(empty0 + 8 * s, 1);
+            mbar_init(done0 + 8 * s, kp * rparts);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-#ifndef WGB_DBG_NOPDL
     pdl_launch_dependents();
-#endif
 
-    // bytes per row over all planes, and the offset of each plane inside a part of n rows
+    // bytes per row over all planes
     uint32_t row_bytes = 0;
 #pragma unroll
     for (int i = 0; i < 4; i++) row_bytes += a.mat[0].pitch[i];
+    // stages of this block (the grid never exceeds the number of groups)
+    const uint32_t nst = (a.ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x;
 
-    if (warp == GEMV_NCONS) {
+    if (warp == GEMV_PRODUCER) {
         // ------------------------------ producer ------------------------------
-        const int nplanes = a.mat[0].nplanes;
-        uint32_t it = 0, s = 0, phase = 1;   // parity of the previous use of ring slot s
-        for (uint32_t gi = blockIdx.x; gi < a.ngroups; gi += gridDim.x, it++, s = (s + 1 == nstage) ? 0 : s + 1, phase ^= (s == 0)) {
-            if (it >= nstage) mbar_wait(empty0 + 8 * s, phase, a.err, 2);
+        // Waiting for a free slot, arming its barrier and issuing a copy is a dependent chain of several
+        // hundred cycles, so the warp runs it for several stages at once: the lanes form groups of `cps`
+        // (copies per stage), one group per stage of a pass; the first lane of a group waits and arms,
+        // every lane issues one copy.
+        const uint32_t nplanes = (uint32_t)a.mat[0].nplanes;
+        const uint32_t cps = nplanes * ((EPI == EPI_SILU_PAIR || EPI == EPI_QKV_ROPE) ? 2u : 1u);   // 1, 2, 4 or 8
+        // One pass takes about as long as 24 KB of streaming at full HBM rate: no more stages per pass
+        // than that needs, so that the ring stays as full as possible.
+        uint32_t spb = (24576u + a.stage_bytes - 1) / a.stage_bytes;
+        if (spb > producer_batch(nstage, cps)) spb = producer_batch(nstage, cps);
+        const uint32_t sb = (uint32_t)lane / cps, ci = (uint32_t)lane % cps;
+        const uint32_t gmask = (cps == 32 ? 0xffffffffu : ((1u << cps) - 1u)) << (sb * cps);
+        if (sb >= spb) return;
+        for (uint32_t it = sb; it < nst; it += spb) {
+            const uint32_t s = it % nstage;
             Part parts[2];
             uint32_t n = 0;
-            const int nparts = group_parts<EPI>(a, gi, parts, n);
-            const uint32_t stage = ring + s * a.stage_bytes;
-            if (lane == 0) mbar_expect_tx(full0 + 8 * s, nparts * n * row_bytes);
-            __syncwarp();
-            if (lane < nparts * nplanes) {
-                const int pi = lane / nplanes, pl = lane % nplanes;
+            const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
+            if (ci == 0) {
+                if (it >= nstage) mbar_wait(empty0 + 8 * s, ((it / nstage) - 1) & 1, a.err, 2);
+                mbar_expect_tx(full0 + 8 * s, nparts * n * row_bytes);
+            }
+            __syncwarp(gmask);
+            if (ci < (uint32_t)nparts * nplanes) {
+                const uint32_t pi = ci / nplanes, pl = ci % nplanes;
                 const QMat &m = a.mat[parts[pi].mat];
                 uint32_t off = pi * n * row_bytes;
-                for (int q = 0; q < pl; q++) off += n * m.pitch[q];
-                bulk_copy_g2s(stage + off, m.p[pl] + (size_t)parts[pi].row0 * m.pitch[pl], n * m.pitch[pl], full0 + 8 * s);
+                for (uint32_t q = 0; q < pl; q++) off += n * m.pitch[q];
+                bulk_copy_g2s(ring + s * a.stage_bytes + off, m.p[pl] + (size_t)parts[pi].row0 * m.pitch[pl], n * m.pitch[pl],
+                              full0 + 8 * s);
             }
         }
         return;
     }
 
+    if (warp == GEMV_EPILOGUE) {
+        // ------------------------------ epilogue ------------------------------
+        // Up to four stages per pass: lanes 8k..8k+7 take stage it0 + k, one lane per output unit.
+        pdl_wait();
+        if (EPI == EPI_QKV_ROPE) {
+            // rotation of every pair index of a head at this position (ops/rope.wgsl:36-77)
+            const uint32_t half = a.head_size / 2;
+            if (half <= GEMV_ROPE_TAB) {
+                const float pos = (float)*a.pos;
+                for (uint32_t i = lane; i < half; i += 32) {
+                    float sn, cs;
+                    sincosf(pos * a.rope_freq[i], &sn, &cs);
+                    rope_tab[i] = make_float2(cs, sn);
+                }
+            }
+            __syncwarp();
+        }
+        const uint32_t nb = epilogue_batch(nstage);
+        const uint32_t sub = (uint32_t)lane >> 3, ul = (uint32_t)lane & 7;
+        const uint32_t gmask = 0xffu << (8 * sub);
+        for (uint32_t it0 = 0; it0 < nst; it0 += nb) {
+            const uint32_t it = it0 + sub;
+            if (sub >= nb || it >= nst) continue;
+            const uint32_t s = it % nstage, phase = (it / nstage) & 1;
+            Part parts[2];
+            uint32_t n = 0;
+            const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
+            const uint32_t nunits = group_units<EPI>(parts, nparts, n);
+            const EpiCtx c = epi_prepare<EPI>(a, parts, nparts, n, ul, nunits, rope_tab);
+            uint32_t ra = 0, rb = 0;
+            if (c.on) unit_rows<EPI>(parts, nparts, n, ul, ra, rb);
+            mbar_wait(done0 + 8 * s, phase, a.err, 3);
+            float ya = 0.0f, yb = 0.0f;
+            if (c.on) {
+                for (uint32_t k = 0; k < kp; k++) {
+                    ya += part[s][k][ra];
+                    yb += part[s][k][rb];
+                }
+            }
+            __syncwarp(gmask);
+            if (ul == 0) mbar_arrive(empty0 + 8 * s);   // stage and partial sums may be overwritten
+            epi_finish<EPI>(a, parts, c, ya, yb);
+        }
+        return;
+    }
+
     // ------------------------------ consumers ------------------------------
-#ifndef WGB_DBG_NOPDL
     pdl_wait();
-#endif
     float mean = 0.0f, scale = 1.0f;
     if (PRO == PRO_RMS) {
         float ss = 0.0f;
@@ -356,151 +460,73 @@ __global__ void __launch_bounds__(GEMV_NT, WGB_GEMV_MINBLOCKS) gemv_kernel(const
     });
     cons_sync();
 
+    const uint32_t ncl = GEMV_NCONS / kp;                 // lanes of warps per column part
+    if ((uint32_t)warp >= kp * ncl) return;               // warps left over when 16 % kp != 0
     const XImage im = ximage_carve(QT, K, smem);
     const uint32_t kunits = QT == WGB_F32 ? K : a.mat[0].bpr;   // what Step::active() compares against
     const uint32_t nsteps = (K + step_cols<QT>() - 1) / step_cols<QT>();
-    // Mini-slots of wk warps: `nss` stage slots (stages in work at once) x `rsl` row slots (shares of
-    // a stage's output units).
-    const uint32_t wk = a.wk, nss = a.nslot, rsl = a.rslots;
-    const uint32_t kw = warp % wk, slot = warp / wk;
-    const uint32_t sslot = slot / rsl, rslot = slot % rsl;
-    const bool working = (uint32_t)warp < wk * nss * rsl;
-    const bool single = nsteps <= wk;   // this warp's only column step: keep its x in registers
+    const uint32_t kw = (uint32_t)warp % kp, cl = (uint32_t)warp / kp;
+    const uint32_t R = a.rrows;
     typename S::X x;
-    if (working && single && S::active(kunits, kw * step_cols<QT>(), lane)) S::load_x(x, im, kw * step_cols<QT>(), lane);
+    uint32_t held = ~0u;   // column step whose part of the input is in `x`
 
-    if (!working) return;
-
-    // Stage slot `sslot` takes every nss-th stage of this block.
-    uint32_t s = sslot % nstage, phase = (sslot / nstage) & 1;   // ring slot and parity of stage `it`
-    for (uint32_t it = sslot, gi = blockIdx.x + sslot * gridDim.x; gi < a.ngroups;
-         it += nss, gi += nss * gridDim.x, s += nss, phase ^= (s >= nstage), s -= (s >= nstage) ? nstage : 0) {
+    // Tasks (stage it, row part rp) with it * rparts + rp = cl, cl + ncl, ...
+    for (uint32_t t = cl; t < nst * rparts; t += ncl) {
+        const uint32_t it = t / rparts, rp = t - it * rparts;
+        const uint32_t s = it % nstage, phase = (it / nstage) & 1;
         Part parts[2];
         uint32_t n = 0;
-        const int nparts = group_parts<EPI>(a, gi, parts, n);
+        const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
         const uint32_t nrows = nparts * n;
-        const uint32_t nunits = group_units<EPI>(parts, nparts, n);
-        const bool paired = EPI == EPI_SILU_PAIR || (EPI == EPI_QKV_ROPE && parts[0].mat < 2);
+        const uint32_t j0 = rp * R;
         const uint32_t stage = ring + s * a.stage_bytes;
-#ifdef WGB_DBG_TIMING
-        long long t0 = clock64();
-#endif
+        float acc[GEMV_MAX_RS];
+#pragma unroll
+        for (int j = 0; j < GEMV_MAX_RS; j++) acc[j] = 0.0f;
         mbar_wait(full0 + 8 * s, phase, a.err, 1);
-#ifdef WGB_DBG_TIMING
-        long long t1 = clock64();
-#endif
-#ifndef WGB_DBG_NOCOMPUTE
-        // first shared-memory byte of row 0 of each part in each plane
-        uint32_t base[2][NPL];
+        if (j0 < nrows) {
+            // first shared-memory byte of row 0 of each part in each plane
+            uint32_t base[2][NPL];
 #pragma unroll
-        for (int pi = 0; pi < 2; pi++) {
-            uint32_t off = stage + pi * n * row_bytes;
+            for (int pi = 0; pi < 2; pi++) {
+                uint32_t off = stage + pi * n * row_bytes;
 #pragma unroll
-            for (int q = 0; q < NPL; q++) {
-                base[pi][q] = off;
-                off += n * a.mat[0].pitch[q];
-            }
-        }
-        if (single) {
-            // Two rows at a time (the two rows of a pair unit, or two single-row units): independent
-            // chains for the scheduler to interleave.
-            const uint32_t col0 = kw * step_cols<QT>();
-            const bool act = S::active(kunits, col0, lane);
-            for (uint32_t u = rslot; u < nunits; u += paired ? rsl : 2 * rsl) {
-                uint32_t j, j1;
-                if (paired) unit_rows<EPI>(parts, nparts, n, u, j, j1);
-                else { j = u; j1 = min(u + rsl, nunits - 1); if (u + rsl >= nunits) j1 = j; }
-                float v0 = 0.0f, v1 = 0.0f;
-                if (act) {
-                    uint32_t r0[4], r1[4];
-                    const uint32_t p0 = j >= n ? 1 : 0, p1 = j1 >= n ? 1 : 0;
-#pragma unroll
-                    for (int q = 0; q < NPL; q++) {
-                        r0[q] = base[p0][q] + (j - p0 * n) * a.mat[0].pitch[q];
-                        r1[q] = base[p1][q] + (j1 - p1 * n) * a.mat[0].pitch[q];
-                    }
-                    v0 = S::dot(r0, col0, x, lane);
-                    v1 = S::dot(r1, col0, x, lane);
+                for (int q = 0; q < NPL; q++) {
+                    base[pi][q] = off;
+                    off += n * a.mat[0].pitch[q];
                 }
-#ifdef WGB_DBG_NOSUM
-                if (v0 + v1 == 1.2345e-30f) part[s][j][kw] = v0;
-#else
-                v0 = warp_sum(v0);
-                v1 = warp_sum(v1);
-                if (lane == 0) {
-                    part[s][j][kw] = v0;
-                    part[s][j1][kw] = v1;
-                }
-#endif
             }
-        } else {
-            float acc[GEMV_MAX_RS];
-#pragma unroll
-            for (int j = 0; j < GEMV_MAX_RS; j++) acc[j] = 0.0f;
-            for (uint32_t ks = kw; ks < nsteps; ks += wk) {
+            for (uint32_t ks = kw; ks < nsteps; ks += kp) {
                 const uint32_t col0 = ks * step_cols<QT>();
-                if (S::active(kunits, col0, lane)) {
+                if (!S::active(kunits, col0, lane)) continue;
+                if (held != ks) {
                     S::load_x(x, im, col0, lane);
+                    held = ks;
+                }
+                // two rows at a time: independent chains for the scheduler to interleave
 #pragma unroll
-                    for (int j = 0; j < GEMV_MAX_RS; j++) {
-                        if ((uint32_t)j < nrows && row_slot_of<EPI>(parts, nparts, n, j, rsl) == rslot) {
-                            const uint32_t pi = (uint32_t)j >= n ? 1 : 0;
-                            uint32_t rowp[4];
+                for (int jj = 0; jj < GEMV_MAX_RS / 2; jj++) {
+                    const uint32_t ja = j0 + 2 * jj, jb = ja + 1;
+                    if ((uint32_t)(2 * jj) < R && ja < nrows) {
+                        const bool two = (uint32_t)(2 * jj + 1) < R && jb < nrows;
+                        const uint32_t pa = ja >= n ? 1 : 0, pb = jb >= n ? 1 : 0;
+                        uint32_t r0[4], r1[4];
 #pragma unroll
-                            for (int q = 0; q < NPL; q++) rowp[q] = base[pi][q] + (j - pi * n) * a.mat[0].pitch[q];
-                            acc[j] += S::dot(rowp, col0, x, lane);
+                        for (int q = 0; q < NPL; q++) {
+                            r0[q] = base[pa][q] + (ja - pa * n) * a.mat[0].pitch[q];
+                            r1[q] = base[pb][q] + (jb - pb * n) * a.mat[0].pitch[q];
                         }
+                        acc[2 * jj] += S::dot(r0, col0, x, lane);
+                        if (two) acc[2 * jj + 1] += S::dot(r1, col0, x, lane);
                     }
                 }
             }
-#pragma unroll
-            for (int j = 0; j < GEMV_MAX_RS; j++) {
-                if ((uint32_t)j < nrows && row_slot_of<EPI>(parts, nparts, n, j, rsl) == rslot) {
-                    const float v = warp_sum(acc[j]);
-                    if (lane == 0) part[s][j][kw] = v;
-                }
-            }
         }
-#endif
-#ifdef WGB_DBG_TIMING
-        long long t2 = clock64();
-#endif
-        // hand the partial sums of the column steps to the slot's first warp
-        (void)nrows;
-#ifndef WGB_DBG_NOSYNC
-        if (wk > 1) slot_sync(slot, wk * 32);
-        else __syncwarp();
-#endif
-        if (kw == 0) {
-            // Read the partial sums first, release the stage, then write the outputs: the release must
-            // not wait for the global stores of the epilogue.
-            const uint32_t u = rslot + (uint32_t)lane * rsl;
-            uint32_t ra = 0, rb = 0;
-            float ya = 0.0f, yb = 0.0f;
-            if (u < nunits) {
-                unit_rows<EPI>(parts, nparts, n, u, ra, rb);
-                for (uint32_t k = 0; k < wk; k++) {
-                    ya += part[s][ra][k];
-                    yb += part[s][rb][k];
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8 * s);
-#ifndef WGB_DBG_NOEPI
-            group_epilogue<EPI>(a, parts, nparts, n, u, [&](uint32_t r) { return r == ra ? ya : yb; });
-#endif
-        } else if (lane == 0) {
-            mbar_arrive(empty0 + 8 * s);   // this warp is done with the stage and its partial sums
-        }
-#ifdef WGB_DBG_TIMING
-        long long t3 = clock64();
-        if (lane == 0 && a.dbg) {
-            atomicAdd(a.dbg + 0, (unsigned long long)(t1 - t0));
-            atomicAdd(a.dbg + 1, (unsigned long long)(t2 - t1));
-            atomicAdd(a.dbg + 2, (unsigned long long)(t3 - t2));
-            atomicAdd(a.dbg + 3, 1ull);
-        }
-#endif
+        const float v = warp_sum8(acc, lane);
+        const uint32_t rr = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+        if ((lane & 3) == 0 && rr < R && j0 + rr < nrows) part[s][kw][j0 + rr] = v;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(done0 + 8 * s);
     }
 }
 
@@ -554,6 +580,7 @@ bool gemv_fast_supported(const QMat &m)
 // Device status word shared by all launches of the process: 0, or the code of the first bounded
 // wait that expired (1 consumer, 2 producer).
 static uint32_t *g_err = nullptr;
+static bool g_trace_plan = false;   // WGML_B200_TRACE_PLAN=1 prints the plan of every launch to stderr
 static int ensure_err()
 {
     if (g_err) return WGB_OK;
@@ -581,74 +608,96 @@ static uint32_t steps_of(int qt, uint32_t K)
     return (K + sc - 1) / sc;
 }
 
-// Chooses rows per stage, ring depth and grid; fills the plan fields of `a`.  Returns false when the
-// shapes do not fit the kernel's assumptions.
+// Chooses rows per stage, the row split, ring depth and grid; fills the plan fields of `a`.  Returns
+// false when the shapes do not fit the kernel's assumptions.
+//
+// Candidates are (rs rows per stage, rparts row parts per stage); a consumer task is rrows = rs / rparts
+// rows of one column part.  The score multiplies
+//   * the balance of groups over the SMs,
+//   * how much of the ~80 KB per SM that must be in flight to cover HBM latency at full bandwidth the
+//     ring can hold beyond the stages the consumers are working on, and
+//   * the share of a task spent in dot products rather than in the per-task reduction and hand-off.
 static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
 {
     const QMat &m0 = a.mat[0];
     uint32_t row_bytes = 0;
     for (int i = 0; i < m0.nplanes; i++) row_bytes += m0.pitch[i];
     const uint32_t sms = (uint32_t)sm_count();
-    // rows (or pairs of rows) that must stay together
     uint32_t total_rows = 0;
     for (int i = 0; i < a.nmat; i++) total_rows += a.mat[i].nrows;
     const bool pairs = a.epilogue == EPI_SILU_PAIR || a.epilogue == EPI_QKV_ROPE;
     const size_t image = (ximage_bytes(m0.qtype, m0.ncols) + 127) & ~(size_t)127;
-    const size_t budget_max = (size_t)WGB_GEMV_SMEM_KB * 1024, budget_hard = 200 * 1024;
+    if (image + 256 > GEMV_SMEM_BUDGET) return false;
     const uint32_t nsteps = steps_of(m0.qtype, m0.ncols);
-    const uint32_t wk = nsteps < (uint32_t)GEMV_NCONS ? nsteps : (uint32_t)GEMV_NCONS;
-    uint32_t slots = GEMV_NCONS / wk;             // mini-slots of wk warps
-    if (slots > GEMV_MAX_SLOTS) slots = GEMV_MAX_SLOTS;
-    const uint32_t nslot = slots >= 4 ? 2 : 1;      // stage slots
-    const uint32_t rslots = slots / nslot;          // row slots per stage
-    uint32_t best_rs = 0;
+    const uint32_t kp = nsteps < (uint32_t)GEMV_NCONS ? nsteps : (uint32_t)GEMV_NCONS;
+    const uint32_t ncl = GEMV_NCONS / kp;
+    const double want_in_flight = 80.0 * 1024;
+
+    auto groups_of = [&](uint32_t rs) -> uint32_t {
+        if (a.epilogue == EPI_SILU_PAIR) return (m0.nrows + rs / 2 - 1) / (rs / 2);
+        if (a.epilogue == EPI_QKV_ROPE) return total_rows / rs;
+        return (m0.nrows + rs - 1) / rs;
+    };
+
+    uint32_t best_rs = 0, best_rp = 0, best_ns = 0;
     double best_score = -1.0;
     for (uint32_t rs = GEMV_MAX_RS; rs >= 1; rs--) {
         if (pairs && (rs & 1)) continue;
         const size_t stage = ((size_t)rs * row_bytes + 127) & ~(size_t)127;
-        if (image + (nslot + 3) * stage > budget_max && rs > (pairs ? 2u : 1u)) continue;   // ring: stages in work + 3 in flight
-        if (image + 2 * stage > budget_hard) continue;
+        if (image + 2 * stage > GEMV_SMEM_BUDGET && rs > (pairs ? 2u : 1u)) continue;
+        if (image + stage > GEMV_SMEM_BUDGET) continue;
         if (a.epilogue == EPI_QKV_ROPE) {
             bool ok = true;
             for (int i = 0; i < 3; i++) ok = ok && a.mat[i].nrows % rs == 0;
             if (a.rope_variant == WGB_ROPE_NEOX) ok = ok && (a.head_size / 2) % (rs / 2) == 0;
             if (!ok) continue;
         }
-        uint32_t groups;
-        if (a.epilogue == EPI_SILU_PAIR) groups = (m0.nrows + rs / 2 - 1) / (rs / 2);
-        else if (a.epilogue == EPI_QKV_ROPE) groups = total_rows / rs;
-        else groups = (m0.nrows + rs - 1) / rs;
-        const uint32_t per = (groups + sms - 1) / sms;
-        // balance across SMs, discounted for small stages (fixed cost per stage ~ 2 KB of streaming)
-        const double score = (double)groups / ((double)per * sms) * ((double)stage / ((double)stage + 2048.0));
-        if (score > best_score + 1e-9) { best_score = score; best_rs = rs; }
+        const uint32_t groups = groups_of(rs);
+        const uint32_t g = groups < sms ? groups : sms;
+        const uint32_t per = (groups + g - 1) / g;
+        uint32_t ns = (uint32_t)((GEMV_SMEM_BUDGET - image) / stage);
+        if (ns > GEMV_MAX_STAGES) ns = GEMV_MAX_STAGES;
+        if (ns > per) ns = per;
+        for (uint32_t rparts = 1; rparts <= 4; rparts *= 2) {
+            if (rs % rparts) continue;
+            const uint32_t rrows = rs / rparts;
+            const uint32_t in_work = (ncl + rparts - 1) / rparts + 1;   // stages the consumers hold at a time
+            double flight;
+            if (ns >= per) flight = 1.0;                                // the block's whole share fits in the ring
+            else {
+                const double bytes = ns > in_work ? (double)(ns - in_work) * stage : 0.25 * stage;
+                flight = bytes >= want_in_flight ? 1.0 : bytes / want_in_flight;
+            }
+            const double balance = (double)groups / ((double)per * g);
+            const double work = (double)rrows / ((double)rrows + 0.5);
+            const double copy = (double)stage / ((double)stage + 512.0);
+            const double score = balance * flight * work * copy;
+            if (score > best_score + 1e-9) {
+                best_score = score;
+                best_rs = rs;
+                best_rp = rparts;
+                best_ns = ns;
+            }
+        }
     }
     if (!best_rs) return false;
     a.rs = best_rs;
-    if (a.epilogue == EPI_SILU_PAIR) a.ngroups = (m0.nrows + best_rs / 2 - 1) / (best_rs / 2);
-    else if (a.epilogue == EPI_QKV_ROPE) a.ngroups = total_rows / best_rs;
-    else a.ngroups = (m0.nrows + best_rs - 1) / best_rs;
+    a.rparts = best_rp;
+    a.rrows = best_rs / best_rp;
+    a.kparts = kp;
+    a.ngroups = groups_of(best_rs);
     a.stage_bytes = (uint32_t)(((size_t)best_rs * row_bytes + 127) & ~(size_t)127);
     grid = a.ngroups < sms ? a.ngroups : sms;
-    const uint32_t per_block = (a.ngroups + grid - 1) / grid;
-    const size_t budget = image + (nslot + 3) * (size_t)a.stage_bytes > budget_max ? budget_hard : budget_max;
-    uint32_t ns = (uint32_t)((budget - image) / a.stage_bytes);
-    if (ns > GEMV_MAX_STAGES) ns = GEMV_MAX_STAGES;
-    if (ns > per_block) ns = per_block;
-    if (ns < 1) ns = 1;
-    a.nstage = ns;
+    a.nstage = best_ns < 1 ? 1 : best_ns;
     a.ring_offset = (uint32_t)image;
-    a.wk = wk;
-    a.nslot = nslot;
-    a.rslots = rslots;
-    smem_bytes = image + (size_t)ns * a.stage_bytes;
+    smem_bytes = image + (size_t)a.nstage * a.stage_bytes;
     return true;
 }
 
 template <int QT>
 static int set_smem_attr()
 {
-    const int bytes = 200 * 1024;
+    const int bytes = (int)GEMV_SMEM_BUDGET;
 #define WGB_ATTR(PRO, EPI) WGB_CUDA(cudaFuncSetAttribute(gemv_kernel<QT, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))
     WGB_ATTR(PRO_NONE, EPI_STORE);
     WGB_ATTR(PRO_RMS, EPI_STORE);
@@ -670,6 +719,8 @@ int gemv_global_init()
     if (done) return WGB_OK;
     int rc = ensure_err();
     if (rc) return rc;
+    const char *tp = getenv("WGML_B200_TRACE_PLAN");
+    g_trace_plan = tp && tp[0] == '1';
     if ((rc = set_smem_attr<WGB_Q4_K>()) || (rc = set_smem_attr<WGB_Q6_K>()) || (rc = set_smem_attr<WGB_Q8_0>()) ||
         (rc = set_smem_attr<WGB_F32>()))
         return rc;
@@ -687,17 +738,6 @@ static int launch_one(GemvArgs &a, cudaStream_t stream, bool pdl)
     int rc = gemv_global_init();
     if (rc) return rc;
     a.err = g_err;
-#ifdef WGB_DBG_TIMING
-    static unsigned long long *dbg = nullptr;
-    if (!dbg) { cudaMalloc((void **)&dbg, 64); cudaMemset(dbg, 0, 64); }
-    if (getenv("WGB_DBG_DUMP")) {
-        unsigned long long h[4];
-        cudaMemcpy(h, dbg, 32, cudaMemcpyDeviceToHost);
-        if (h[3]) fprintf(stderr, "timing: stages=%llu wait=%.0f compute=%.0f tail=%.0f cycles/stage/warp\n", h[3], (double)h[0] / h[3], (double)h[1] / h[3], (double)h[2] / h[3]);
-        cudaMemset(dbg, 0, 64);
-    }
-    a.dbg = dbg;
-#endif
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(GEMV_NT);
@@ -710,9 +750,9 @@ static int launch_one(GemvArgs &a, cudaStream_t stream, bool pdl)
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    if (getenv("WGB_DBG_PLAN"))
-        fprintf(stderr, "gemv plan: qt=%d rows=%u K=%u rs=%u ngroups=%u nstage=%u stage=%u ring_off=%u wk=%u grid=%u smem=%zu\n", QT,
-                a.mat[0].nrows, a.mat[0].ncols, a.rs, a.ngroups, a.nstage, a.stage_bytes, a.ring_offset, a.wk * 10000 + a.nslot * 100 + a.rslots, grid, smem);
+    if (g_trace_plan)
+        fprintf(stderr, "gemv plan: qt=%d rows=%u K=%u rs=%u rparts=%u kparts=%u ngroups=%u nstage=%u stage=%u grid=%u smem=%zu\n", QT,
+                a.mat[0].nrows, a.mat[0].ncols, a.rs, a.rparts, a.kparts, a.ngroups, a.nstage, a.stage_bytes, grid, smem);
     WGB_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
     return WGB_OK;
 }

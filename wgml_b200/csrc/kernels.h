@@ -49,13 +49,10 @@ struct GemvArgs {
     uint32_t nstage;        // ring depth
     uint32_t stage_bytes;
     uint32_t ring_offset;   // of the ring inside dynamic shared memory (after the input image)
-    uint32_t wk;            // consumer warps along the columns (one slot)
-    uint32_t nslot;         // stage slots = stages in work at once
-    uint32_t rslots;        // row slots sharing the output units of one stage
+    uint32_t kparts;        // column parts = consumer warps that share one row
+    uint32_t rparts;        // row parts per stage
+    uint32_t rrows;         // rows per consumer task = rs / rparts
     uint32_t *err;          // device status word for expired waits
-#ifdef WGB_DBG_TIMING
-    unsigned long long *dbg;
-#endif
 };
 
 // Enqueues one fused kernel.  All matrices must share format and ncols and have a fast path;

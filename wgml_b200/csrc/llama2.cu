@@ -166,6 +166,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
     const uint32_t *d_token = m->scalars, *d_pos = m->scalars + 1;
     const bool fused = m->fused && fusable(m);
     const bool pdl = m->use_pdl && !m->profiling;
+    const bool tp = m->tp_size > 1;
     const int variant = m->model_type == WGB_QWEN2 ? WGB_ROPE_NEOX : WGB_ROPE_ORIGINAL;
     int n = 0;
     int rc = launch_embed(m->token_embd->view, nullptr, d_token, d_pos, m->x, s);
@@ -219,10 +220,13 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             o.mat[0] = w.m[WGB_L_ATTN_OUTPUT]->view;
             o.nmat = 1;
             o.x = m->xb;
-            o.epilogue = EPI_RESIDUAL;
+            // Tensor parallel: the rank holds a column slice, so its product is a partial sum over the
+            // group; rank 0 folds the residual in and the all-reduce leaves the new x on every rank.
+            o.epilogue = (!tp || m->tp_rank == 0) ? EPI_RESIDUAL : EPI_STORE;
             o.residual = m->x;
-            o.out = m->x;
+            o.out = tp ? m->xb2 : m->x;
             if ((rc = launch_gemv(o, s, pdl))) return rc;
+            if (tp && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->x, c.dim, s))) return rc;
             mark(m, s, K_OPROJ, l);
             GemvArgs f = {};
             f.mat[0] = w.m[WGB_L_FFN_GATE]->view;
@@ -240,10 +244,11 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             d.mat[0] = w.m[WGB_L_FFN_DOWN]->view;
             d.nmat = 1;
             d.x = m->hb;
-            d.epilogue = EPI_RESIDUAL;
+            d.epilogue = (!tp || m->tp_rank == 0) ? EPI_RESIDUAL : EPI_STORE;
             d.residual = m->x;
-            d.out = m->x;
+            d.out = tp ? m->xb2 : m->x;
             if ((rc = launch_gemv(d, s, pdl))) return rc;
+            if (tp && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->x, c.dim, s))) return rc;
             mark(m, s, K_DOWN, l);
             n += 5;
         } else {
@@ -258,12 +263,14 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             WGB_LAUNCH_CHECK("qkv_finish_kernel");
             if ((rc = launch_attention(at, s, false))) return rc;
             if ((rc = mat_vec(w.m[WGB_L_ATTN_OUTPUT]->view, m->xb, m->xb2, s))) return rc;
+            if (tp && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->xb2, c.dim, s))) return rc;
             if ((rc = wgb_op_assign(WGB_ASSIGN_ADD, m->x, m->xb2, c.dim, s))) return rc;
             if ((rc = wgb_rms_norm(m->xb, m->x, w.v[WGB_L_FFN_NORM], c.dim, c.rms_norm_eps, s))) return rc;
             if ((rc = mat_vec(w.m[WGB_L_FFN_GATE]->view, m->xb, m->hb, s))) return rc;
             if ((rc = mat_vec(w.m[WGB_L_FFN_UP]->view, m->xb, m->hb2, s))) return rc;
             if ((rc = wgb_silu(m->hb, m->hb2, m->hidden, s))) return rc;
             if ((rc = mat_vec(w.m[WGB_L_FFN_DOWN]->view, m->hb, m->xb2, s))) return rc;
+            if (tp && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->xb2, c.dim, s))) return rc;
             if ((rc = wgb_op_assign(WGB_ASSIGN_ADD, m->x, m->xb2, c.dim, s))) return rc;
             mark(m, s, K_OTHER, l);
             n += 14;
@@ -560,10 +567,12 @@ WGB_EXPORT int wgb_llama2_load_gguf(wgb_llama2 *m, const wgb_gguf *g)
     return WGB_OK;
 }
 
-WGB_EXPORT int wgb_llama2_set_comm(wgb_llama2 *m, void *nccl_comm)
+WGB_EXPORT int wgb_llama2_set_comm(wgb_llama2 *m, void *comm)
 {
     WGB_REQUIRE(m, "null argument");
-    m->comm = nccl_comm;
+    WGB_REQUIRE(!comm || (wgb_comm_size((wgb_comm *)comm) == m->tp_size && wgb_comm_rank((wgb_comm *)comm) == m->tp_rank),
+                "communicator rank/size does not match the model's tensor-parallel rank %d of %d", m->tp_rank, m->tp_size);
+    m->comm = comm;
     drop_graph(m);
     return WGB_OK;
 }

@@ -70,8 +70,10 @@ def vector(n: int, seed: int, name: str, mean: float = 0.0) -> tuple:
     return F32, (np.float32(mean) + rng.standard_normal(n, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
 
 
-def llama_tensors(cfg: dict, seed: int = 0, biases: bool = False, scale: float = 0.01, layers=None) -> dict:
-    """All tensors of a Llama-architecture model, GGUF names -> (qtype, array)."""
+def llama_tensors(cfg: dict, seed: int = 0, biases: bool = False, scale: float = 0.01, layers=None,
+                  model_tensors: bool = True) -> dict:
+    """All tensors of a Llama-architecture model, GGUF names -> (qtype, array).  `layers` restricts the
+    blocks generated; `model_tensors=False` leaves out token_embd / output / output_norm."""
     dim, hid, vocab = cfg["dim"], cfg["hidden_dim"], cfg["vocab_size"]
     kv_dim = dim * cfg["n_kv_heads"] // cfg["n_q_heads"]
     qt = cfg.get("default_qtype", Q4_K)
@@ -92,9 +94,10 @@ def llama_tensors(cfg: dict, seed: int = 0, biases: bool = False, scale: float =
             t[p + "attn_q.bias"] = vector(dim, seed, p + "attn_q.bias")
             t[p + "attn_k.bias"] = vector(kv_dim, seed, p + "attn_k.bias")
             t[p + "attn_v.bias"] = vector(kv_dim, seed, p + "attn_v.bias")
-    t["token_embd.weight"] = matrix(qt, vocab, dim, seed, "token_embd", scale)
-    t["output.weight"] = matrix(Q6_K if mix == "q4_k_m" else qt, vocab, dim, seed, "output", scale)
-    t["output_norm.weight"] = vector(dim, seed, "output_norm", 1.0)
+    if model_tensors:
+        t["token_embd.weight"] = matrix(qt, vocab, dim, seed, "token_embd", scale)
+        t["output.weight"] = matrix(Q6_K if mix == "q4_k_m" else qt, vocab, dim, seed, "output", scale)
+        t["output_norm.weight"] = vector(dim, seed, "output_norm", 1.0)
     return t
 
 
