@@ -1,0 +1,39 @@
+"""Tensor-parallel Llama-2 on 2 GPUs against the same model on one GPU: identical greedy tokens and
+logits within 1e-3 relative / 1e-4 absolute (absolute term scaled by the largest logit).  Needs two
+devices; skipped otherwise.  The ranks are separate processes over NCCL, as in production."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ATOL, RTOL, assert_close
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp2_matches_single_gpu(tmp_path):
+    out = str(tmp_path / "tp.npz")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py"), out]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = np.load(out)
+    for name in ("gqa_q4k", "tiny_f32"):
+        ref_t, ref_l = res[f"{name}/ref_tokens"], res[f"{name}/ref_logits"]
+        for fused in (1, 0):
+            assert np.array_equal(res[f"{name}/{fused}/tp_tokens"], ref_t), f"{name} fused={fused}: tokens differ"
+            scale = max(1.0, float(np.abs(ref_l).max()))
+            assert_close(res[f"{name}/{fused}/tp_logits"], ref_l, RTOL, ATOL * scale, f"{name} fused={fused} logits")
