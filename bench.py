@@ -274,6 +274,8 @@ def run_b200(args):
     prompt_len = args.prompt_len or (512 if workload == "llama2-7b" else 4096)
     K, W = args.steps, args.warmup
     cfg = model_cfg(workload, prompt_len + W + 2 * K + 8)
+    if args.layers:
+        cfg["n_layers"] = args.layers
     from wgml_b200 import synth
     distinct = 2 if workload == "llama2-70b" else None
     model = build_gpu_model(cfg, args.seed, rank, world, distinct)
@@ -364,6 +366,7 @@ def run_b200(args):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "prompt_len": prompt_len, "decode_steps": K, "batch": 1,
                    "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                   **({"truncated_to_layers": args.layers, "valid": False} if args.layers else {}),
                    "weights_gb": sum(matrix_bytes(cfg, l, n)[0] for l in range(cfg["n_layers"]) for n in
                                      ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")) / 1e9
                                  + matrix_bytes(cfg, -1, "output")[0] / 1e9,
@@ -393,6 +396,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "llama2-7b", "llama2-70b", "tiny-llama"])
     ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="truncate the model to this many layers (profiler captures only: the line it prints is not a benchmark result)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU oracle work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
