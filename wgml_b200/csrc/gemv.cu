@@ -33,7 +33,10 @@
 
 namespace wgb {
 
-constexpr int GEMV_NCONS = 16;                      // consumer warps
+#ifndef WGB_GEMV_NCONS
+#define WGB_GEMV_NCONS 16
+#endif
+constexpr int GEMV_NCONS = WGB_GEMV_NCONS;          // consumer warps
 constexpr int GEMV_CONS_THREADS = GEMV_NCONS * 32;
 constexpr int GEMV_PRODUCER = GEMV_NCONS;           // warp index of the producer
 constexpr int GEMV_EPILOGUE = GEMV_NCONS + 1;       // warp index of the epilogue warp
@@ -317,23 +320,18 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
                    done0 = smem_addr(&bars[2 * GEMV_MAX_STAGES]);
     const uint32_t kp = a.kparts, rparts = a.rparts;
 
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < nstage; s++) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
-            mbar_init(done0 + 8 * s, kp * rparts);
-        }
+    // one thread per barrier: initialising them one after the other would cost a microsecond
+    if (threadIdx.x < 3 * nstage) {
+        const uint32_t kind = threadIdx.x / nstage, s = threadIdx.x - kind * nstage;
+        mbar_init((kind == 0 ? full0 : (kind == 1 ? empty0 : done0)) + 8 * s, kind == 2 ? kp * rparts : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     pdl_launch_dependents();
 
-    // bytes per row over all planes
-    uint32_t row_bytes = 0;
-#pragma unroll
-    for (int i = 0; i < 4; i++) row_bytes += a.mat[0].pitch[i];
+    const uint32_t row_bytes = a.row_bytes;
     // stages of this block (the grid never exceeds the number of groups)
-    const uint32_t nst = (a.ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    const uint32_t nst = a.per_block - ((a.rem_blocks != 0 && blockIdx.x >= a.rem_blocks) ? 1u : 0u);
 
     if (warp == GEMV_PRODUCER) {
         // ------------------------------ producer ------------------------------
@@ -341,33 +339,32 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
         // hundred cycles, so the warp runs it for several stages at once: the lanes form groups of `cps`
         // (copies per stage), one group per stage of a pass; the first lane of a group waits and arms,
         // every lane issues one copy.
-        const uint32_t nplanes = (uint32_t)a.mat[0].nplanes;
-        const uint32_t cps = nplanes * ((EPI == EPI_SILU_PAIR || EPI == EPI_QKV_ROPE) ? 2u : 1u);   // 1, 2, 4 or 8
-        // One pass takes about as long as 24 KB of streaming at full HBM rate: no more stages per pass
-        // than that needs, so that the ring stays as full as possible.
-        uint32_t spb = (24576u + a.stage_bytes - 1) / a.stage_bytes;
-        if (spb > producer_batch(nstage, cps)) spb = producer_batch(nstage, cps);
-        const uint32_t sb = (uint32_t)lane / cps, ci = (uint32_t)lane % cps;
-        const uint32_t gmask = (cps == 32 ? 0xffffffffu : ((1u << cps) - 1u)) << (sb * cps);
+        const uint32_t nplanes = (uint32_t)NPL;
+        const uint32_t cps = 1u << a.cps_log2;                   // copies per stage: 1, 2, 4 or 8
+        const uint32_t spb = a.spb;                              // stages per pass
+        const uint32_t sb = (uint32_t)lane >> a.cps_log2, ci = (uint32_t)lane & (cps - 1);
+        const uint32_t gmask = ((1u << cps) - 1u) << (sb * cps);
         if (sb >= spb) return;
+        uint32_t s = sb % nstage, round = sb / nstage;           // ring slot of stage `it` and its use count
         for (uint32_t it = sb; it < nst; it += spb) {
-            const uint32_t s = it % nstage;
             Part parts[2];
             uint32_t n = 0;
             const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
             if (ci == 0) {
-                if (it >= nstage) mbar_wait(empty0 + 8 * s, ((it / nstage) - 1) & 1, a.err, 2);
+                if (round) mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.err, 2);
                 mbar_expect_tx(full0 + 8 * s, nparts * n * row_bytes);
             }
             __syncwarp(gmask);
             if (ci < (uint32_t)nparts * nplanes) {
-                const uint32_t pi = ci / nplanes, pl = ci % nplanes;
+                const uint32_t pi = ci / nplanes, pl = ci % nplanes;   // nplanes is a compile-time power of two
                 const QMat &m = a.mat[parts[pi].mat];
                 uint32_t off = pi * n * row_bytes;
                 for (uint32_t q = 0; q < pl; q++) off += n * m.pitch[q];
                 bulk_copy_g2s(ring + s * a.stage_bytes + off, m.p[pl] + (size_t)parts[pi].row0 * m.pitch[pl], n * m.pitch[pl],
                               full0 + 8 * s);
             }
+            s += spb;
+            while (s >= nstage) { s -= nstage; round++; }
         }
         return;
     }
@@ -420,11 +417,24 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
 
     // ------------------------------ consumers ------------------------------
     pdl_wait();
+    // The thread's first XC chunks of the input are requested at once and stay in registers for the
+    // normalisation passes and the staging (one trip to L2 instead of up to three, one after the other).
+    constexpr uint32_t XC = 3;
+    float4 xc[XC];
+#pragma unroll
+    for (uint32_t i = 0; i < XC; i++) {
+        const uint32_t c = threadIdx.x + i * GEMV_CONS_THREADS;
+        xc[i] = c < K / 4 ? ld_act4(a.x + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    auto chunk = [&](uint32_t c) {
+        const uint32_t i = c / GEMV_CONS_THREADS;   // c = threadIdx.x + i * GEMV_CONS_THREADS
+        return i == 0 ? xc[0] : (i == 1 ? xc[1] : (i == 2 ? xc[2] : ld_act4(a.x + 4 * c)));
+    };
     float mean = 0.0f, scale = 1.0f;
     if (PRO == PRO_RMS) {
         float ss = 0.0f;
         for (uint32_t c = threadIdx.x; c < K / 4; c += GEMV_CONS_THREADS) {
-            float4 v = ld_act4(a.x + 4 * c);
+            float4 v = chunk(c);
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
         ss = cons_sum(ss, red);
@@ -432,13 +442,13 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     } else if (PRO == PRO_LN) {
         float s = 0.0f;
         for (uint32_t c = threadIdx.x; c < K / 4; c += GEMV_CONS_THREADS) {
-            float4 v = ld_act4(a.x + 4 * c);
+            float4 v = chunk(c);
             s += (v.x + v.y) + (v.z + v.w);
         }
         mean = cons_sum(s, red) / (float)K;
         float ss = 0.0f;
         for (uint32_t c = threadIdx.x; c < K / 4; c += GEMV_CONS_THREADS) {
-            float4 v = ld_act4(a.x + 4 * c);
+            float4 v = chunk(c);
             v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
@@ -446,7 +456,7 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
         scale = 1.0f / sqrtf(ss / (float)K + 1.0e-5f);
     }
     stage_x<QT, GEMV_CONS_THREADS>(smem, K, [&](uint32_t c) {
-        float4 v = ld_act4(a.x + 4 * c);
+        float4 v = chunk(c);
         if (PRO == PRO_RMS) {
             const float4 w = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + c);
             v.x = (v.x * scale) * w.x; v.y = (v.y * scale) * w.y; v.z = (v.z * scale) * w.z; v.w = (v.w * scale) * w.w;
@@ -612,11 +622,12 @@ static uint32_t steps_of(int qt, uint32_t K)
 // false when the shapes do not fit the kernel's assumptions.
 //
 // Candidates are (rs rows per stage, rparts row parts per stage); a consumer task is rrows = rs / rparts
-// rows of one column part.  The score multiplies
-//   * the balance of groups over the SMs,
-//   * how much of the ~80 KB per SM that must be in flight to cover HBM latency at full bandwidth the
-//     ring can hold beyond the stages the consumers are working on, and
-//   * the share of a task spent in dot products rather than in the per-task reduction and hand-off.
+// rows of one column part, and the ncl = 16 / kparts warps of a column part take the tasks of the block
+// in turn.  The time of the launch is that of its fullest block: ceil(tasks / ncl) rounds of
+// (rrows + 1/2) row products, the half row standing for the wait, reduction and hand-off of a task.
+// That is divided by how much of the ~80 KB per SM that must be in flight to cover HBM latency at full
+// bandwidth the ring can hold beyond the stages the consumers are working on, and by a mild preference
+// for larger copies.
 static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
 {
     const QMat &m0 = a.mat[0];
@@ -640,7 +651,7 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
     };
 
     uint32_t best_rs = 0, best_rp = 0, best_ns = 0;
-    double best_score = -1.0;
+    double best_cost = 1e300;
     for (uint32_t rs = GEMV_MAX_RS; rs >= 1; rs--) {
         if (pairs && (rs & 1)) continue;
         const size_t stage = ((size_t)rs * row_bytes + 127) & ~(size_t)127;
@@ -658,7 +669,7 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
         uint32_t ns = (uint32_t)((GEMV_SMEM_BUDGET - image) / stage);
         if (ns > GEMV_MAX_STAGES) ns = GEMV_MAX_STAGES;
         if (ns > per) ns = per;
-        for (uint32_t rparts = 1; rparts <= 4; rparts *= 2) {
+        for (uint32_t rparts = 1; rparts <= 8; rparts *= 2) {
             if (rs % rparts) continue;
             const uint32_t rrows = rs / rparts;
             const uint32_t in_work = (ncl + rparts - 1) / rparts + 1;   // stages the consumers hold at a time
@@ -668,12 +679,11 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
                 const double bytes = ns > in_work ? (double)(ns - in_work) * stage : 0.25 * stage;
                 flight = bytes >= want_in_flight ? 1.0 : bytes / want_in_flight;
             }
-            const double balance = (double)groups / ((double)per * g);
-            const double work = (double)rrows / ((double)rrows + 0.5);
+            const uint32_t rounds = (per * rparts + ncl - 1) / ncl;
             const double copy = (double)stage / ((double)stage + 512.0);
-            const double score = balance * flight * work * copy;
-            if (score > best_score + 1e-9) {
-                best_score = score;
+            const double cost = (double)rounds * ((double)rrows + 0.5) / (flight * copy);
+            if (cost < best_cost - 1e-9) {
+                best_cost = cost;
                 best_rs = rs;
                 best_rp = rparts;
                 best_ns = ns;
@@ -690,6 +700,15 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
     grid = a.ngroups < sms ? a.ngroups : sms;
     a.nstage = best_ns < 1 ? 1 : best_ns;
     a.ring_offset = (uint32_t)image;
+    a.row_bytes = row_bytes;
+    a.per_block = (a.ngroups + grid - 1) / grid;
+    a.rem_blocks = a.ngroups % grid;
+    const uint32_t cps = (uint32_t)m0.nplanes * (pairs ? 2u : 1u);
+    a.cps_log2 = cps == 1 ? 0 : (cps == 2 ? 1 : (cps == 4 ? 2 : 3));
+    // One producer pass takes about as long as 24 KB of streaming at full HBM rate: no more stages per
+    // pass than that needs, so that the ring stays as full as possible.
+    a.spb = (24576u + a.stage_bytes - 1) / a.stage_bytes;
+    if (a.spb > producer_batch(a.nstage, cps)) a.spb = producer_batch(a.nstage, cps);
     smem_bytes = image + (size_t)a.nstage * a.stage_bytes;
     return true;
 }

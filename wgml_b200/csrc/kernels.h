@@ -52,6 +52,11 @@ struct GemvArgs {
     uint32_t kparts;        // column parts = consumer warps that share one row
     uint32_t rparts;        // row parts per stage
     uint32_t rrows;         // rows per consumer task = rs / rparts
+    uint32_t row_bytes;     // bytes of one row over all planes
+    uint32_t per_block;     // groups of blocks 0 .. rem_blocks-1; the other blocks have one fewer
+    uint32_t rem_blocks;    //   (0: every block has per_block)
+    uint32_t cps_log2;      // log2 of the copies per stage (planes x parts)
+    uint32_t spb;           // stages per producer pass
     uint32_t *err;          // device status word for expired waits
 };
 
