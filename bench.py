@@ -34,6 +34,9 @@ if ROOT not in sys.path:
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 BPE = {0: 4.0, 8: 34 / 32, 12: 144 / 256, 14: 210 / 256}  # algorithmic bytes per weight
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/gemv_q4k_gate_up_7b_ncu_full.txt (7B shapes); classes without a capture report null.
+NCU_TRAFFIC = {("llama2-7b", "gate_up_silu/q4_k"): 50.88e6 + 0.16e6}
 
 
 def measured_peaks():
@@ -355,7 +358,9 @@ def run_b200(args):
     if dom:
         d = classes[dom]
         roofline = {"bound": "hbm", "kernel": f"gemv_kernel [{dom}]", "achieved": d["gbs"], "peak": peak, "unit": "GB/s",
-                    "frac": d["gbs"] / peak, "traffic": None, "peak_source": peak_src,
+                    "frac": d["gbs"] / peak, "traffic": NCU_TRAFFIC.get((workload, dom)) if world == 1 else None,
+                    "traffic_source": "ncu capture, profiles/gemv_q4k_gate_up_7b_ncu_full.txt" if (workload, dom) in NCU_TRAFFIC else None,
+                    "peak_source": peak_src,
                     "bytes_per_launch": d["bytes"] / d["launches"], "us_per_launch": d["us_per_launch"],
                     "how": "algorithmic bytes / CUDA-event time per launch, eager replay of the step with an event after every launch",
                     "whole_step": {"bytes_per_token": bytes_tok, "achieved": bytes_tok * tok_s / 1e9,
