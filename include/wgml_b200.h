@@ -135,6 +135,26 @@ typedef struct {
  * the reference's single-kernel path, batched_multiquery_attention.wgsl:48,66). */
 int wgb_attention(const wgb_attn_params *p, const float *d_q, const float *d_key_cache,
                   const float *d_value_cache, float *d_attn, float *d_xb, void *stream);
+
+/* wgb_attention without any device allocation.  No counterpart in the reference; it exists for hosts
+ * that cannot have cudaMalloc / cudaFree on the call path: a server that has given the whole device to
+ * its own memory pool, or a latency-critical loop in which the device-wide synchronisation of an
+ * allocation would stall the other streams.  The split-K partial results live in a fixed array that is
+ * part of the library image (one copy per device, 8 MiB), so
+ *   - shapes that need more are refused with WGB_ERR_INVALID and a message naming the limit:
+ *     n_heads * ceil(seq_len / 64) * (head_size + 4) <= WGB_ATTENTION_STATIC_MAX_SCRATCH_FLOATS and
+ *     n_heads <= WGB_ATTENTION_STATIC_MAX_HEADS (a 7B-class 32 x 128 head layout fits up to 31 744 cached
+ *     positions; 64 heads up to 15 872);
+ *   - the first call on a device looks the array up (cudaGetSymbolAddress, with that device current);
+ *     make that first call before the stream is put into capture mode;
+ *   - two calls that may run at the same time (different streams, or different host threads on one
+ *     device) share the array and race: keep calls on one device in one stream order.
+ * Every call clears its tickets first, so an earlier launch that was cut short cannot disturb it.
+ * Results are identical to wgb_attention with d_attn == NULL. */
+#define WGB_ATTENTION_STATIC_MAX_SCRATCH_FLOATS (2 * 1024 * 1024)
+#define WGB_ATTENTION_STATIC_MAX_HEADS 256
+int wgb_attention_static(const wgb_attn_params *p, const float *d_q, const float *d_key_cache,
+                         const float *d_value_cache, float *d_xb, void *stream);
 /* SoftMax::dispatch (ops/softmax.rs:18-30, softmax.wgsl:31-92): every column of a column-major
  * nrows x ncols matrix (column j starts at d_mat + j * col_stride) replaced by its softmax. */
 int wgb_softmax(float *d_mat, size_t nrows, size_t ncols, size_t col_stride, void *stream);

@@ -80,6 +80,7 @@ SIGNATURES = {
     "wgb_layernorm": (_i, [_vp, _vp, _sz, _vp]),
     "wgb_rope": (_i, [_i, C.POINTER(RopeConfig), _vp, _sz, _vp, _sz, _vp]),
     "wgb_attention": (_i, [C.POINTER(AttnParams), _vp, _vp, _vp, _vp, _vp, _vp]),
+    "wgb_attention_static": (_i, [C.POINTER(AttnParams), _vp, _vp, _vp, _vp, _vp]),
     "wgb_softmax": (_i, [_vp, _sz, _sz, _sz, _vp]),
     "wgb_silu": (_i, [_vp, _vp, _sz, _vp]),
     "wgb_unary": (_i, [_i, _vp, _vp, _sz, C.POINTER(_f), _vp]),

@@ -14,6 +14,8 @@
 // probabilities are materialised in the caller's [n_heads][seq_len] buffer.
 #include "kernels.h"
 
+#include <mutex>
+
 namespace wgb {
 
 constexpr int ATT_NT = 256;
@@ -370,4 +372,93 @@ WGB_EXPORT int wgb_attention(const wgb_attn_params *p, const float *d_q, const f
     a.scratch = g_scratch;
     a.counters = g_counters;
     return launch_attention(a, as_stream(stream), false);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Attention entry point that never allocates.
+//
+// wgb_attention keeps its split-K scratch in device memory that it allocates (and regrows) on demand.
+// Some hosts cannot have that on the call path: a server that has handed the whole device to its own
+// memory pool has nothing left for cudaMalloc to take, and in a latency-critical loop the device-wide
+// synchronisation inside cudaMalloc / cudaFree stalls every other stream.  This variant runs the same
+// kernels on scratch that is part of the loaded module: two file-scope __device__ arrays of fixed size.
+// Shapes whose scratch would not fit are rejected, never served from another buffer.
+// ---------------------------------------------------------------------------------------------
+#define WGB_ATTN_STATIC_DEVICES 64
+
+static __device__ __align__(256) float g_static_scratch[WGB_ATTENTION_STATIC_MAX_SCRATCH_FLOATS];
+static __device__ __align__(256) uint32_t g_static_counters[WGB_ATTENTION_STATIC_MAX_HEADS];
+
+namespace {
+
+struct StaticScratch {
+    float *scratch = nullptr;
+    uint32_t *counters = nullptr;
+};
+StaticScratch g_static[WGB_ATTN_STATIC_DEVICES];   // per device: every device has its own copy of the arrays
+std::mutex g_static_mutex;
+
+__global__ void clear_words_kernel(uint32_t *p, uint32_t n)
+{
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) p[i] = 0;
+}
+
+// Resolves the arrays' addresses on the current device the first time the device is seen.
+int static_scratch(StaticScratch *out)
+{
+    int dev = -1;
+    WGB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= WGB_ATTN_STATIC_DEVICES) return fail(WGB_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static[dev].scratch) {
+        float *s = nullptr;
+        uint32_t *c = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&s, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(attention scratch)");
+        e = cudaGetSymbolAddress((void **)&c, g_static_counters);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(attention counters)");
+        g_static[dev].scratch = s;
+        g_static[dev].counters = c;
+    }
+    *out = g_static[dev];
+    return WGB_OK;
+}
+
+}  // namespace
+
+WGB_EXPORT int wgb_attention_static(const wgb_attn_params *p, const float *d_q, const float *d_key_cache,
+                                    const float *d_value_cache, float *d_xb, void *stream)
+{
+    WGB_REQUIRE(p && d_q && d_key_cache && d_value_cache && d_xb, "null argument");
+    WGB_REQUIRE(p->pos < p->seq_len, "pos %u outside a cache of %u positions", p->pos, p->seq_len);
+    WGB_REQUIRE(p->kv_mul > 0 && p->n_heads % p->kv_mul == 0 && p->kv_dim == (p->n_heads / p->kv_mul) * p->head_size,
+                "inconsistent attention parameters");
+    WGB_REQUIRE(p->head_size % 4 == 0 && p->head_size <= 256 && p->head_size > 0, "head_size %u unsupported", p->head_size);
+    const size_t need = attn_scratch_floats(p->n_heads, p->head_size, p->seq_len);
+    if (need > (size_t)WGB_ATTENTION_STATIC_MAX_SCRATCH_FLOATS)
+        return fail(WGB_ERR_INVALID,
+                    "wgb_attention_static: %u heads x %u positions x head size %u need %zu scratch floats, the built-in "
+                    "scratch holds %d; use wgb_attention",
+                    p->n_heads, p->seq_len, p->head_size, need, WGB_ATTENTION_STATIC_MAX_SCRATCH_FLOATS);
+    if (p->n_heads > (uint32_t)WGB_ATTENTION_STATIC_MAX_HEADS)
+        return fail(WGB_ERR_INVALID, "wgb_attention_static: %u heads, the built-in scratch serves at most %d; use wgb_attention",
+                    p->n_heads, WGB_ATTENTION_STATIC_MAX_HEADS);
+    StaticScratch ss;
+    int rc = static_scratch(&ss);
+    if (rc) return rc;
+    cudaStream_t s = as_stream(stream);
+    // The tickets must start at zero.  The kernel leaves them there, but a launch that was cut short
+    // (a failed launch further up the stream, a process that reuses the context) must not poison this one.
+    clear_words_kernel<<<1, 256, 0, s>>>(ss.counters, p->n_heads);
+    WGB_LAUNCH_CHECK("clear_words_kernel");
+    AttnArgs a = {};
+    a.p = *p;
+    a.pos = nullptr;
+    a.q = d_q;
+    a.k_cache = d_key_cache;
+    a.v_cache = d_value_cache;
+    a.xb = d_xb;
+    a.scratch = ss.scratch;
+    a.counters = ss.counters;
+    return launch_attention(a, s, false);
 }
