@@ -334,7 +334,7 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_dev, ms_e2e = float(t[0]), float(t[1])
 
-    # ---- per-launch breakdown (eager, events after every launch) ----------------------------------
+    # ---- per-launch breakdown (graph replay with an event after every launch) -----------------------
     peak, peak_src = measured_peaks()
     classes = {}
     for rep in range(6):
@@ -362,7 +362,7 @@ def run_b200(args):
                     "traffic_source": "ncu capture, profiles/gemv_q4k_gate_up_7b_ncu_full.txt" if (workload, dom) in NCU_TRAFFIC else None,
                     "peak_source": peak_src,
                     "bytes_per_launch": d["bytes"] / d["launches"], "us_per_launch": d["us_per_launch"],
-                    "how": "algorithmic bytes / CUDA-event time per launch, eager replay of the step with an event after every launch",
+                    "how": "algorithmic bytes / time the launch adds to the step: the decode graph is replayed with every launch writing its end time (%globaltimer) to device memory, time = own end - predecessor's end (tensor-parallel runs: CUDA events after every launch instead)",
                     "whole_step": {"bytes_per_token": bytes_tok, "achieved": bytes_tok * tok_s / 1e9,
                                    "frac": bytes_tok * tok_s / 1e9 / peak, "frac_of_8TBs": bytes_tok * tok_s / 8e12}}
     line = {

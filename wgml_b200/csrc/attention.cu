@@ -41,19 +41,41 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
     __shared__ uint32_t s_last;
 
     pdl_launch_dependents();
-    pdl_wait();
-
+    // The position and every cache row before it were written by earlier steps, so they are read before the
+    // wait for the preceding launch (which produces q and the cache row of this position): the DRAM round
+    // trip of the chunk overlaps the hand-over between the launches.
     const uint32_t pos = a.pos ? *a.pos : a.p.pos;
     const uint32_t hs = a.p.head_size, kv_dim = a.p.kv_dim, kv_mul = a.p.kv_mul;
     const uint32_t split = blockIdx.x, kvh = blockIdx.y;
     const uint32_t t0 = split * ATT_CHUNK;
-    if (t0 > pos) return;
+    if (t0 > pos) {
+        if (threadIdx.x == 0) stamp_end(a.stamp);
+        return;
+    }
     const uint32_t nt = min((uint32_t)ATT_CHUNK, pos + 1 - t0);
     const uint32_t nsplit_active = pos / ATT_CHUNK + 1;
     const uint32_t max_splits = gridDim.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t nchunk = hs / 4;  // float4 chunks per head
     const float inv_sqrt = sqrtf((float)hs);
+
+    // Every warp owns ATT_TPW consecutive time steps.  All of their K and V rows are requested up front
+    // (independent loads, one DRAM round trip for the whole chunk), then consumed.
+    const float *kbase = a.k_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
+    const float *vbase = a.v_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
+    float4 kr[ATT_TPW][VC], vr[ATT_TPW][VC];
+#pragma unroll
+    for (int i = 0; i < ATT_TPW; i++) {
+        const uint32_t tl = warp * ATT_TPW + i;
+#pragma unroll
+        for (int c = 0; c < VC; c++) {
+            const uint32_t ch = lane + 32 * c;
+            const bool ok = t0 + tl < pos && ch < nchunk;   // rows of earlier steps only
+            kr[i][c] = ok ? __ldcs(reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+            vr[i][c] = ok ? __ldcs(reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    pdl_wait();
 
     // query heads of this KV head: h = kvh * kv_mul + j, j = hq0 .. hq0 + QH - 1 (looped by caller grid.z)
     const uint32_t hq0 = blockIdx.z * QH;
@@ -67,21 +89,19 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
                           ? __ldcg(reinterpret_cast<const float4 *>(a.q + (size_t)(kvh * kv_mul + hq0 + j) * hs) + ch)
                           : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-
-    // Every warp owns ATT_TPW consecutive time steps.  All of their K and V rows are requested up front
-    // (independent loads, one DRAM round trip for the whole chunk), then consumed.
-    const float *kbase = a.k_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
-    const float *vbase = a.v_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
-    float4 kr[ATT_TPW][VC], vr[ATT_TPW][VC];
+    // the row of this position, written by the preceding launch
 #pragma unroll
     for (int i = 0; i < ATT_TPW; i++) {
         const uint32_t tl = warp * ATT_TPW + i;
+        if (t0 + tl == pos) {
 #pragma unroll
-        for (int c = 0; c < VC; c++) {
-            const uint32_t ch = lane + 32 * c;
-            const bool ok = tl < nt && ch < nchunk;
-            kr[i][c] = ok ? __ldcs(reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
-            vr[i][c] = ok ? __ldcs(reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < VC; c++) {
+                const uint32_t ch = lane + 32 * c;
+                if (ch < nchunk) {
+                    kr[i][c] = __ldcg(reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch);
+                    vr[i][c] = __ldcg(reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch);
+                }
+            }
         }
     }
     // Pass 1: scores of the chunk.
@@ -229,23 +249,78 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
         if (s_last) *counter = 0;  // ready for the next launch
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) {
+        if (threadIdx.x == 0) stamp_end(a.stamp);
+        return;
+    }
     __threadfence();
+    // Merge of the chunks, spread over the block: the chunk maxima first (one thread per chunk), then warp w
+    // folds chunks w, w + 8, ... for every output element, and the eight partial results meet in shared
+    // memory.  The chunk -> warp assignment is fixed, so the result does not depend on timing.
+    __shared__ float s_M[QH];
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        float m = -INFINITY;
+        if (hq0 + j < kv_mul) {
+            const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
+            for (uint32_t sp = threadIdx.x; sp < nsplit_active; sp += ATT_NT) m = fmaxf(m, __ldcg(base + (size_t)sp * (hs + 4) + hs));
+        }
+        m = warp_max(m);
+        if (lane == 0) s_red[j][warp] = m;
+    }
+    __syncthreads();
+    if (threadIdx.x < QH) {
+        float m = s_red[threadIdx.x][0];
+#pragma unroll
+        for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, s_red[threadIdx.x][w]);
+        s_M[threadIdx.x] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        if (hq0 + j >= kv_mul) continue;   // uniform over the block
+        const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
+        const float M = s_M[j];
+        float4 o[VC];
+#pragma unroll
+        for (int c = 0; c < VC; c++) o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.0f;
+        for (uint32_t sp = warp; sp < nsplit_active; sp += ATT_WARPS) {
+            const float *row = base + (size_t)sp * (hs + 4);
+            const float w = expf(__ldcg(row + hs) - M);
+            L = fmaf(__ldcg(row + hs + 1), w, L);
+#pragma unroll
+            for (int c = 0; c < VC; c++) {
+                const uint32_t ch = lane + 32 * c;
+                if (ch < nchunk) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(row) + ch);
+                    o[c].x = fmaf(v.x, w, o[c].x);
+                    o[c].y = fmaf(v.y, w, o[c].y);
+                    o[c].z = fmaf(v.z, w, o[c].z);
+                    o[c].w = fmaf(v.w, w, o[c].w);
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < VC; c++) {
+            const uint32_t ch = lane + 32 * c;
+            if (ch < nchunk) reinterpret_cast<float4 *>(&s_acc[warp][j][0])[ch] = o[c];
+        }
+        if (lane == 0) s_red[j][warp] = L;
+    }
+    __syncthreads();
     for (uint32_t e = threadIdx.x; e < QH * hs; e += ATT_NT) {
         const uint32_t j = e / hs, i = e % hs;
         if (hq0 + j >= kv_mul) continue;
-        const uint32_t h = kvh * kv_mul + hq0 + j;
-        const float *base = a.scratch + (size_t)h * max_splits * (hs + 4);
-        float M = -INFINITY;
-        for (uint32_t s = 0; s < nsplit_active; s++) M = fmaxf(M, __ldcg(base + (size_t)s * (hs + 4) + hs));
         float L = 0.0f, o = 0.0f;
-        for (uint32_t s = 0; s < nsplit_active; s++) {
-            const float w = expf(__ldcg(base + (size_t)s * (hs + 4) + hs) - M);
-            L = fmaf(__ldcg(base + (size_t)s * (hs + 4) + hs + 1), w, L);
-            o = fmaf(__ldcg(base + (size_t)s * (hs + 4) + i), w, o);
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) {
+            L += s_red[j][w];
+            o += s_acc[w][j][i];
         }
-        a.xb[(size_t)h * hs + i] = o / L;
+        a.xb[(size_t)(kvh * kv_mul + hq0 + j) * hs + i] = o / L;
     }
+    if (threadIdx.x == 0) stamp_end(a.stamp);
 }
 
 // One block per query head; writes the attention weights.

@@ -101,6 +101,16 @@ __device__ __forceinline__ float block_max(float v, float *red)
 // stream has completed and its writes are visible; `pdl_launch_dependents` lets the following
 // kernel start its independent prologue.  Both are no-ops for a kernel launched without the
 // programmatic-serialization attribute.
+// End-of-launch time stamp for per-launch timing inside a graph replay: the latest %globaltimer (ns) over
+// the blocks of a launch.  Called by one thread per block after its last store; a NULL slot costs a branch.
+__device__ __forceinline__ void stamp_end(unsigned long long *slot)
+{
+    if (!slot) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    atomicMax(slot, t);
+}
+
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 #endif

@@ -412,6 +412,7 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             if (ul == 0) mbar_arrive(empty0 + 8 * s);   // stage and partial sums may be overwritten
             epi_finish<EPI>(a, parts, c, ya, yb);
         }
+        if (lane == 0) stamp_end(a.stamp);
         return;
     }
 
@@ -599,16 +600,21 @@ static int ensure_err()
     return WGB_OK;
 }
 
+uint32_t *gemv_status_word() { return g_err; }
+
+int gemv_report_status(uint32_t v)
+{
+    if (!v) return WGB_OK;
+    if (g_err) cudaMemset(g_err, 0, sizeof(uint32_t));
+    return fail(WGB_ERR_TIMEOUT, "a bounded wait inside a matrix-vector kernel expired (code %u)", v);
+}
+
 int gemv_check_status()
 {
     if (!g_err) return WGB_OK;
     uint32_t v = 0;
     WGB_CUDA(cudaMemcpy(&v, g_err, sizeof(v), cudaMemcpyDeviceToHost));
-    if (v) {
-        cudaMemset(g_err, 0, sizeof(uint32_t));
-        return fail(WGB_ERR_TIMEOUT, "a bounded wait inside a matrix-vector kernel expired (code %u)", v);
-    }
-    return WGB_OK;
+    return gemv_report_status(v);
 }
 
 static uint32_t steps_of(int qt, uint32_t K)

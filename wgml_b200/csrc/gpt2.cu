@@ -9,6 +9,7 @@
 #include "kernels.h"
 
 #include <cstdlib>
+#include <cstring>
 #include <new>
 #include <string>
 #include <vector>
@@ -31,6 +32,8 @@ struct wgb_gpt2 {
     float *attn_scratch = nullptr;
     uint32_t *attn_counters = nullptr, *scalars = nullptr, *argmax_scratch = nullptr, *d_prompt = nullptr, *d_out = nullptr;
     size_t prompt_cap = 0, out_cap = 0;
+    uint32_t *h_pinned = nullptr;            // pinned staging of a decode call: [0] status word, [1..] token ids
+    size_t pinned_cap = 0;
     bool fused = true, use_pdl = true;
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_n_prompt = 0;
@@ -286,6 +289,7 @@ WGB_EXPORT int wgb_gpt2_destroy(wgb_gpt2 *m)
     for (float *b : bufs) if (b) cudaFree(b);
     uint32_t *ubufs[] = { m->attn_counters, m->scalars, m->argmax_scratch, m->d_prompt, m->d_out };
     for (uint32_t *b : ubufs) if (b) cudaFree(b);
+    if (m->h_pinned) cudaFreeHost(m->h_pinned);
     delete m;
     return WGB_OK;
 }
@@ -486,7 +490,15 @@ WGB_EXPORT int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_p
         WGB_CUDA(cudaMalloc((void **)&m->d_out, total * 4));
         m->out_cap = total;
     }
-    WGB_CUDA(cudaMemcpyAsync(m->d_prompt, h_prompt, n_prompt * 4, cudaMemcpyHostToDevice, s));
+    if (total + 1 > m->pinned_cap) {
+        if (m->h_pinned) cudaFreeHost(m->h_pinned);
+        m->h_pinned = nullptr;
+        m->pinned_cap = 0;
+        WGB_CUDA(cudaMallocHost((void **)&m->h_pinned, (total + 1) * 4));
+        m->pinned_cap = total + 1;
+    }
+    // the first token travels as a kernel argument; the rest of the prompt is only read when there is one
+    if (n_prompt > 1) WGB_CUDA(cudaMemcpyAsync(m->d_prompt, h_prompt, n_prompt * 4, cudaMemcpyHostToDevice, s));
     set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, h_prompt[0], start_pos, 0);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
     LoopState ls = {};
@@ -517,7 +529,11 @@ WGB_EXPORT int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_p
         m->graph_n_prompt = (uint32_t)n_prompt;
     }
     for (size_t i = 0; i < total; i++) WGB_CUDA(cudaGraphLaunch(m->graph, s));
-    WGB_CUDA(cudaMemcpyAsync(h_out_tokens, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
+    // One wait for the ids and the kernels' status word, both through pinned memory.
+    WGB_CUDA(cudaMemcpyAsync(m->h_pinned + 1, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
+    m->h_pinned[0] = 0;
+    if (gemv_status_word()) WGB_CUDA(cudaMemcpyAsync(m->h_pinned, gemv_status_word(), 4, cudaMemcpyDeviceToHost, s));
     WGB_CUDA(cudaStreamSynchronize(s));
-    return gemv_check_status();
+    memcpy(h_out_tokens, m->h_pinned + 1, total * 4);
+    return gemv_report_status(m->h_pinned[0]);
 }

@@ -58,6 +58,7 @@ struct GemvArgs {
     uint32_t cps_log2;      // log2 of the copies per stage (planes x parts)
     uint32_t spb;           // stages per producer pass
     uint32_t *err;          // device status word for expired waits
+    unsigned long long *stamp;   // optional: receives the launch's end time (stamp_end)
 };
 
 // Enqueues one fused kernel.  All matrices must share format and ncols and have a fast path;
@@ -70,6 +71,10 @@ bool gemv_fast_supported(const QMat &m);
 int gemv_global_init();
 // WGB_ERR_TIMEOUT if any bounded wait of a fused kernel expired since the last call (synchronises).
 int gemv_check_status();
+// The device status word itself (NULL before gemv_global_init) and the error for a value read from it
+// (clears the word when v != 0): lets a caller fold the read into its own device-to-host copy.
+uint32_t *gemv_status_word();
+int gemv_report_status(uint32_t v);
 
 // Slow path for any format: one warp per row, dequantising with the exact block formulas.
 int launch_gemv_generic(const QMat &m, const float *x, float *out, cudaStream_t stream);
@@ -82,6 +87,7 @@ struct AttnArgs {
     float *xb;
     float *scratch;             // attn_scratch_floats() floats
     uint32_t *counters;         // n_kv_heads counters, zero before the first launch
+    unsigned long long *stamp;  // optional: receives the launch's end time (stamp_end)
 };
 size_t attn_scratch_floats(uint32_t n_heads, uint32_t head_size, uint32_t seq_len);
 uint32_t attn_num_splits(uint32_t seq_len);

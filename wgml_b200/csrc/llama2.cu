@@ -12,6 +12,7 @@
 
 #include <cmath>
 #include <cstdlib>
+#include <cstring>
 #include <new>
 #include <vector>
 
@@ -46,6 +47,8 @@ struct wgb_llama2 {
     uint32_t *argmax_scratch = nullptr;
     uint32_t *d_prompt = nullptr, *d_out = nullptr;
     size_t prompt_cap = 0, out_cap = 0;
+    uint32_t *h_pinned = nullptr;            // pinned staging of a decode call: [0] status word, [1..] token ids
+    size_t pinned_cap = 0;
     bool fused = true, use_pdl = true;
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_n_prompt = 0;
@@ -53,11 +56,17 @@ struct wgb_llama2 {
     int kernels_per_token = 0;
     // per-launch timing of wgb_llama2_profile_step: one event after every launch
     bool profiling = false;
+    // per-launch timing inside a graph replay: end-time slot per launch ([0] = start of the step)
+    unsigned long long *stamps = nullptr;
+    size_t stamps_cap = 0;
+    bool stamping = false;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_kind, prof_layer;
 };
 
 namespace {
+
+__global__ void stamp_kernel(unsigned long long *slot) { stamp_end(slot); }
 
 __global__ void set_scalars_kernel(uint32_t *s, uint32_t token, uint32_t pos, uint32_t step)
 {
@@ -149,6 +158,11 @@ int mat_vec(const QMat &w, const float *x, float *out, cudaStream_t s)
 enum { K_EMBED = 0, K_QKV, K_ATTN, K_OPROJ, K_GATE_UP, K_DOWN, K_HEAD, K_OTHER };
 int mark(wgb_llama2 *m, cudaStream_t s, int kind, int layer)
 {
+    if (m->stamping) {   // the launch wrote its own end time; only its tag is kept
+        m->prof_kind.push_back(kind);
+        m->prof_layer.push_back(layer);
+        return WGB_OK;
+    }
     if (!m->profiling) return WGB_OK;
     cudaEvent_t e;
     WGB_CUDA(cudaEventCreate(&e));
@@ -169,10 +183,17 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
     const bool tp = m->tp_size > 1;
     const int variant = m->model_type == WGB_QWEN2 ? WGB_ROPE_NEOX : WGB_ROPE_ORIGINAL;
     int n = 0;
+    // stamping: slot 0 takes the start of the step, slot i the end of the i-th marked launch
+    size_t next_stamp = 0;
+    auto stamp_slot = [&]() -> unsigned long long * { return m->stamping ? m->stamps + next_stamp++ : nullptr; };
+    if (m->stamping) {
+        stamp_kernel<<<1, 1, 0, s>>>(stamp_slot());
+        WGB_LAUNCH_CHECK("stamp_kernel");
+    }
     int rc = launch_embed(m->token_embd->view, nullptr, d_token, d_pos, m->x, s);
     if (rc) return rc;
     n++;
-    mark(m, s, K_EMBED, -1);
+    if (!m->stamping) mark(m, s, K_EMBED, -1);
     const size_t cache_stride = (size_t)c.seq_len * m->kv_dim;
     AttnArgs at = {};
     at.p.seq_len = c.seq_len;
@@ -212,8 +233,10 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             a.head_size = m->head_size;
             a.rope_variant = variant;
             a.rope_freq = m->rope_freq;
+            a.stamp = stamp_slot();
             if ((rc = launch_gemv(a, s, pdl))) return rc;
             mark(m, s, K_QKV, l);
+            at.stamp = stamp_slot();
             if ((rc = launch_attention(at, s, pdl))) return rc;
             mark(m, s, K_ATTN, l);
             GemvArgs o = {};
@@ -225,6 +248,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             o.epilogue = (!tp || m->tp_rank == 0) ? EPI_RESIDUAL : EPI_STORE;
             o.residual = m->x;
             o.out = tp ? m->xb2 : m->x;
+            o.stamp = stamp_slot();
             if ((rc = launch_gemv(o, s, pdl))) return rc;
             if (tp && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->x, c.dim, s))) return rc;
             mark(m, s, K_OPROJ, l);
@@ -238,6 +262,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             f.eps = c.rms_norm_eps;
             f.epilogue = EPI_SILU_PAIR;
             f.out = m->hb;
+            f.stamp = stamp_slot();
             if ((rc = launch_gemv(f, s, pdl))) return rc;
             mark(m, s, K_GATE_UP, l);
             GemvArgs d = {};
@@ -247,6 +272,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             d.epilogue = (!tp || m->tp_rank == 0) ? EPI_RESIDUAL : EPI_STORE;
             d.residual = m->x;
             d.out = tp ? m->xb2 : m->x;
+            d.stamp = stamp_slot();
             if ((rc = launch_gemv(d, s, pdl))) return rc;
             if (tp && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->x, c.dim, s))) return rc;
             mark(m, s, K_DOWN, l);
@@ -287,6 +313,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
         a.eps = c.rms_norm_eps;
         a.epilogue = EPI_STORE;
         a.out = m->logits;
+        a.stamp = stamp_slot();
         if ((rc = launch_gemv(a, s, pdl))) return rc;
         mark(m, s, K_HEAD, -1);
         n += 1;
@@ -390,8 +417,10 @@ WGB_EXPORT int wgb_llama2_destroy(wgb_llama2 *m)
     float *bufs[] = { m->output_norm, m->x, m->xb, m->xb2, m->hb, m->hb2, m->q, m->tk, m->tv, m->logits, m->key_cache,
                       m->value_cache, m->attn_scratch, m->rope_freq };
     for (float *b : bufs) if (b) cudaFree(b);
+    if (m->stamps) cudaFree(m->stamps);
     uint32_t *ubufs[] = { m->attn_counters, m->scalars, m->argmax_scratch, m->d_prompt, m->d_out };
     for (uint32_t *b : ubufs) if (b) cudaFree(b);
+    if (m->h_pinned) cudaFreeHost(m->h_pinned);
     delete m;
     return WGB_OK;
 }
@@ -599,6 +628,119 @@ WGB_EXPORT int wgb_llama2_forward(wgb_llama2 *m, uint32_t token, uint32_t pos, v
     return enqueue_forward(m, s, &m->kernels_per_token);
 }
 
+// One forward with an event after every launch.  `as_graph`: the launches and event records are captured
+// into a CUDA graph and replayed once, so that the gaps between launches are the device's, not the time the
+// host needs to issue a launch; otherwise they are issued one by one.
+static int profile_once(wgb_llama2 *m, cudaStream_t s, bool as_graph, int cap, int *kinds, int *layers, float *ms, int *n_out)
+{
+    m->profiling = true;
+    m->prof_events.clear();
+    m->prof_kind.clear();
+    m->prof_layer.clear();
+    cudaEvent_t start = nullptr;
+    cudaError_t e = cudaEventCreate(&start);
+    int rc = WGB_OK;
+    if (e == cudaSuccess && as_graph) {
+        cudaStream_t cs = nullptr;
+        cudaGraph_t graph = nullptr;
+        cudaGraphExec_t exec = nullptr;
+        e = cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal);
+        if (e == cudaSuccess) {
+            e = cudaEventRecord(start, cs);
+            if (e == cudaSuccess) rc = enqueue_forward(m, cs, nullptr);
+            cudaError_t e2 = cudaStreamEndCapture(cs, &graph);
+            if (e == cudaSuccess) e = e2;
+        }
+        if (e == cudaSuccess && rc == WGB_OK) e = cudaGraphInstantiate(&exec, graph, 0);
+        if (e == cudaSuccess && rc == WGB_OK) e = cudaGraphLaunch(exec, s);
+        if (e == cudaSuccess && rc == WGB_OK) e = cudaStreamSynchronize(s);
+        if (exec) cudaGraphExecDestroy(exec);
+        if (graph) cudaGraphDestroy(graph);
+        if (cs) cudaStreamDestroy(cs);
+    } else if (e == cudaSuccess) {
+        e = cudaEventRecord(start, s);
+        if (e == cudaSuccess) rc = enqueue_forward(m, s, nullptr);
+        cudaError_t e2 = cudaStreamSynchronize(s);
+        if (e == cudaSuccess) e = e2;
+    }
+    m->profiling = false;
+    int n = 0;
+    cudaEvent_t prev = start;
+    for (size_t i = 0; i < m->prof_events.size(); i++) {
+        if (rc == WGB_OK && e == cudaSuccess && n < cap) {
+            float t = 0.0f;
+            e = cudaEventElapsedTime(&t, prev, m->prof_events[i]);
+            kinds[n] = m->prof_kind[i];
+            layers[n] = m->prof_layer[i];
+            ms[n] = t;
+            n++;
+        }
+        if (prev != start) cudaEventDestroy(prev);
+        prev = m->prof_events[i];
+    }
+    if (prev != start && prev) cudaEventDestroy(prev);
+    if (start) cudaEventDestroy(start);
+    m->prof_events.clear();
+    *n_out = n;
+    if (rc) return rc;
+    if (e != cudaSuccess) { cudaGetLastError(); return cuda_fail(e, "profile step"); }
+    return WGB_OK;
+}
+
+// The fused schedule exactly as a decode step runs it (one CUDA graph, programmatic dependent launch), each
+// launch leaving its end time in device memory; a launch's time is the distance to its predecessor's end,
+// which is what it adds to the step (the embedding copy is counted with the first launch).
+static int profile_stamped(wgb_llama2 *m, cudaStream_t s, int cap, int *kinds, int *layers, float *ms, int *n_out)
+{
+    const size_t need = 5 * (size_t)m->cfg.n_layers + 2;
+    if (need > m->stamps_cap) {
+        if (m->stamps) cudaFree(m->stamps);
+        m->stamps = nullptr;
+        m->stamps_cap = 0;
+        WGB_CUDA(cudaMalloc((void **)&m->stamps, need * sizeof(unsigned long long)));
+        m->stamps_cap = need;
+    }
+    m->stamping = true;
+    m->prof_kind.clear();
+    m->prof_layer.clear();
+    cudaStream_t cs = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int rc = WGB_OK;
+    cudaError_t e = cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+        rc = enqueue_forward(m, cs, nullptr);
+        e = cudaStreamEndCapture(cs, &graph);
+    }
+    m->stamping = false;
+    if (e == cudaSuccess && rc == WGB_OK) e = cudaGraphInstantiate(&exec, graph, 0);
+    std::vector<unsigned long long> h(need, 0);
+    for (int rep = 0; rep < 2 && e == cudaSuccess && rc == WGB_OK; rep++) {   // the second replay is the one read
+        e = cudaMemsetAsync(m->stamps, 0, need * sizeof(unsigned long long), s);
+        if (e == cudaSuccess) e = cudaGraphLaunch(exec, s);
+    }
+    if (e == cudaSuccess && rc == WGB_OK) e = cudaMemcpyAsync(h.data(), m->stamps, need * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess && rc == WGB_OK) e = cudaStreamSynchronize(s);
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    if (cs) cudaStreamDestroy(cs);
+    int n = 0;
+    if (e == cudaSuccess && rc == WGB_OK) {
+        for (size_t i = 0; i < m->prof_kind.size() && i + 1 < need && n < cap; i++) {
+            kinds[n] = m->prof_kind[i];
+            layers[n] = m->prof_layer[i];
+            ms[n] = h[i + 1] > h[i] ? (float)((double)(h[i + 1] - h[i]) * 1e-6) : 0.0f;
+            n++;
+        }
+    }
+    *n_out = n;
+    if (rc) return rc;
+    if (e != cudaSuccess) return cuda_fail(e, "stamped profile step");
+    return WGB_OK;
+}
+
 WGB_EXPORT int wgb_llama2_profile_step(wgb_llama2 *m, uint32_t token, uint32_t pos, void *stream, int cap, int *kinds,
                                        int *layers, float *ms, int *n_out)
 {
@@ -609,37 +751,14 @@ WGB_EXPORT int wgb_llama2_profile_step(wgb_llama2 *m, uint32_t token, uint32_t p
     cudaStream_t s = as_stream(stream);
     set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
-    m->profiling = true;
-    m->prof_events.clear();
-    m->prof_kind.clear();
-    m->prof_layer.clear();
-    cudaEvent_t start;
-    WGB_CUDA(cudaEventCreate(&start));
-    WGB_CUDA(cudaEventRecord(start, s));
-    rc = enqueue_forward(m, s, nullptr);
-    m->profiling = false;
-    cudaError_t e = cudaStreamSynchronize(s);
-    int n = 0;
-    cudaEvent_t prev = start;
-    for (size_t i = 0; i < m->prof_events.size(); i++) {
-        if (rc == WGB_OK && e == cudaSuccess && n < cap) {
-            float t = 0.0f;
-            cudaEventElapsedTime(&t, prev, m->prof_events[i]);
-            kinds[n] = m->prof_kind[i];
-            layers[n] = m->prof_layer[i];
-            ms[n] = t;
-            n++;
-        }
-        if (prev != start) cudaEventDestroy(prev);
-        prev = m->prof_events[i];
+    if (m->fused && fusable(m) && m->tp_size == 1) return profile_stamped(m, s, cap, kinds, layers, ms, n_out);
+    rc = profile_once(m, s, true, cap, kinds, layers, ms, n_out);
+    if (rc == WGB_ERR_CUDA) {   // events inside a captured graph unavailable: issue the launches one by one
+        set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
+        WGB_LAUNCH_CHECK("set_scalars_kernel");
+        rc = profile_once(m, s, false, cap, kinds, layers, ms, n_out);
     }
-    if (prev != start) cudaEventDestroy(prev);
-    cudaEventDestroy(start);
-    m->prof_events.clear();
-    *n_out = n;
-    if (rc) return rc;
-    if (e != cudaSuccess) return cuda_fail(e, "profile step");
-    return WGB_OK;
+    return rc;
 }
 
 WGB_EXPORT const float *wgb_llama2_logits(const wgb_llama2 *m) { return m ? m->logits : nullptr; }
@@ -685,7 +804,15 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
         WGB_CUDA(cudaMalloc((void **)&m->d_out, total * 4));
         m->out_cap = total;
     }
-    WGB_CUDA(cudaMemcpyAsync(m->d_prompt, h_prompt, n_prompt * 4, cudaMemcpyHostToDevice, s));
+    if (total + 1 > m->pinned_cap) {
+        if (m->h_pinned) cudaFreeHost(m->h_pinned);
+        m->h_pinned = nullptr;
+        m->pinned_cap = 0;
+        WGB_CUDA(cudaMallocHost((void **)&m->h_pinned, (total + 1) * 4));
+        m->pinned_cap = total + 1;
+    }
+    // the first token travels as a kernel argument; the rest of the prompt is only read when there is one
+    if (n_prompt > 1) WGB_CUDA(cudaMemcpyAsync(m->d_prompt, h_prompt, n_prompt * 4, cudaMemcpyHostToDevice, s));
     set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, h_prompt[0], start_pos, 0);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
 
@@ -719,7 +846,11 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
         m->graph_n_prompt = (uint32_t)n_prompt;
     }
     for (size_t i = 0; i < total; i++) WGB_CUDA(cudaGraphLaunch(m->graph, s));
-    WGB_CUDA(cudaMemcpyAsync(h_out_tokens, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
+    // One wait for the ids and the kernels' status word, both through pinned memory.
+    WGB_CUDA(cudaMemcpyAsync(m->h_pinned + 1, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
+    m->h_pinned[0] = 0;
+    if (gemv_status_word()) WGB_CUDA(cudaMemcpyAsync(m->h_pinned, gemv_status_word(), 4, cudaMemcpyDeviceToHost, s));
     WGB_CUDA(cudaStreamSynchronize(s));
-    return gemv_check_status();
+    memcpy(h_out_tokens, m->h_pinned + 1, total * 4);
+    return gemv_report_status(m->h_pinned[0]);
 }
