@@ -285,7 +285,7 @@ def run_b200(args):
     if world > 1:
         from wgml_b200 import tp
         comm = tp.init_from_torch_distributed()
-        tp.attach(model, comm)
+        tp.attach(model, comm, direct=(args.exchange == "peer"))
     prompt = synth.prompt(prompt_len, cfg["vocab_size"], args.seed)
 
     def barrier():
@@ -371,6 +371,8 @@ def run_b200(args):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload, "prompt_len": prompt_len, "decode_steps": K, "batch": 1,
                    "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                   **({"exchange": "kernels store partial products into the peers' memory over NVLink, flags instead of a collective"
+                       if args.exchange == "peer" else "NCCL all-reduce"} if world > 1 else {}),
                    **({"truncated_to_layers": args.layers, "valid": False} if args.layers else {}),
                    "weights_gb": sum(matrix_bytes(cfg, l, n)[0] for l in range(cfg["n_layers"]) for n in
                                      ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")) / 1e9
@@ -401,6 +403,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "llama2-7b", "llama2-70b", "tiny-llama"])
     ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="tensor-parallel runs: partial products exchanged by the kernels through peer memory (default) "
+                         "or by an NCCL all-reduce")
     ap.add_argument("--layers", type=int, default=None,
                     help="truncate the model to this many layers (profiler captures only: the line it prints is not a benchmark result)")
     ap.add_argument("--seed", type=int, default=0)

@@ -339,6 +339,19 @@ int wgb_comm_size(const wgb_comm *c);
 int wgb_comm_all_reduce_sum(wgb_comm *c, const float *d_send, float *d_recv, size_t n, void *stream);
 /* d_recv[r * n_per_rank + i] = rank r's d_send[i]. */
 int wgb_comm_all_gather(wgb_comm *c, const float *d_send, float *d_recv, size_t n_per_rank, void *stream);
+/* A zero-filled device buffer of `bytes` on every rank, each mapped into every other rank's address space
+ * (CUDA IPC between the processes; peer access over NVLink).  peers_out[p] (size entries, at most
+ * WGB_COMM_MAX_PEERS) is rank p's buffer as seen from this rank, peers_out[rank] the local one.
+ * Collective; the buffers live as long as the communicator. */
+#define WGB_COMM_MAX_PEERS 8
+int wgb_comm_shared_alloc(wgb_comm *c, size_t bytes, void **peers_out);
+/* Tensor-parallel models exchange the partial products of attn_output / ffn_down either with one NCCL
+ * all-reduce each (mode 0, default) or directly (mode 1): the matrix-vector kernel's epilogue stores its
+ * partial rows into every rank's mailbox over NVLink and raises a flag, and the next kernel's prologue
+ * waits for the tp flags (bounded) and adds the tp partials in rank order while it normalises its input.
+ * No collective library call and no extra launch remain on the token path.  Call after
+ * wgb_llama2_set_comm and before the first forward; collective (every rank, same mode). */
+int wgb_llama2_set_exchange(wgb_llama2 *m, int mode);
 
 /* ---- GPT-2 ---- */
 

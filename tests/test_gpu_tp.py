@@ -1,6 +1,7 @@
 """Tensor-parallel Llama-2 on 2 GPUs against the same model on one GPU: identical greedy tokens and
-logits within 1e-3 relative / 1e-4 absolute (absolute term scaled by the largest logit).  Needs two
-devices; skipped otherwise.  The ranks are separate processes over NCCL, as in production."""
+logits within 1e-3 relative / 1e-4 absolute (absolute term scaled by the largest logit), for the direct
+exchange of partial products through peer memory and for the NCCL all-reduce.  Needs two devices; skipped
+otherwise.  The ranks are separate processes over NCCL, as in production."""
 import os
 import socket
 import subprocess
@@ -33,7 +34,10 @@ def test_tp2_matches_single_gpu(tmp_path):
     res = np.load(out)
     for name in ("gqa_q4k", "tiny_f32"):
         ref_t, ref_l = res[f"{name}/ref_tokens"], res[f"{name}/ref_logits"]
-        for fused in (1, 0):
-            assert np.array_equal(res[f"{name}/{fused}/tp_tokens"], ref_t), f"{name} fused={fused}: tokens differ"
+        for mode in ("11", "10", "00"):   # fused + direct exchange, fused + NCCL, dispatch by dispatch + NCCL
+            assert np.array_equal(res[f"{name}/{mode}/tp_tokens"], ref_t), f"{name} mode {mode}: tokens differ"
             scale = max(1.0, float(np.abs(ref_l).max()))
-            assert_close(res[f"{name}/{fused}/tp_logits"], ref_l, RTOL, ATOL * scale, f"{name} fused={fused} logits")
+            assert_close(res[f"{name}/{mode}/tp_logits"], ref_l, RTOL, ATOL * scale, f"{name} mode {mode} logits")
+            ref_x = res[f"{name}/ref_x"]
+            assert_close(res[f"{name}/{mode}/tp_x"], ref_x, RTOL, ATOL * max(1.0, float(np.abs(ref_x).max())),
+                         f"{name} mode {mode} residual stream")

@@ -37,19 +37,23 @@ def main():
         c = Llama2Config(cfg["dim"], cfg["hidden_dim"], cfg["n_layers"], cfg["n_q_heads"], cfg["n_kv_heads"], cfg["vocab_size"],
                          cfg["seq_len"], cfg["rope_base_freq"], cfg["rms_norm_eps"])
         prompt = synth.prompt(8, cfg["vocab_size"], seed=5)
-        for fused in (True, False):
+        # (fused schedule, direct exchange through peer memory): direct needs the fused schedule
+        for fused, direct in ((True, True), (True, False), (False, False)):
             m = Llama2(c, tp_rank=rank, tp_size=world)
             m.load_tensors(t)
             m.set_fused(fused)
-            tp.attach(m, comm)
+            tp.attach(m, comm, direct=direct)
             toks = m.decode(prompt, 24)
             m.dispatch(int(toks[-1]), len(toks))      # one eager step after the graph replays
             logits = m.logits().cpu().numpy()
+            x = m.x().cpu().numpy()
             torch.cuda.synchronize()
             dist.barrier()
             if rank == 0:
-                res[f"{name}/{int(fused)}/tp_tokens"] = toks
-                res[f"{name}/{int(fused)}/tp_logits"] = logits
+                key = f"{name}/{int(fused)}{int(direct)}"
+                res[key + "/tp_tokens"] = toks
+                res[key + "/tp_logits"] = logits
+                res[key + "/tp_x"] = x
             m.close()
         if rank == 0:
             m = Llama2(c)
@@ -58,6 +62,7 @@ def main():
             m.dispatch(int(toks[-1]), len(toks))
             res[f"{name}/ref_tokens"] = toks
             res[f"{name}/ref_logits"] = m.logits().cpu().numpy()
+            res[f"{name}/ref_x"] = m.x().cpu().numpy()
             m.close()
         dist.barrier()
     if rank == 0:

@@ -130,6 +130,8 @@ SIGNATURES = {
     "wgb_comm_size": (_i, [_vp]),
     "wgb_comm_all_reduce_sum": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "wgb_comm_all_gather": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "wgb_comm_shared_alloc": (_i, [_vp, _sz, _pp]),
+    "wgb_llama2_set_exchange": (_i, [_vp, _i]),
     "wgb_gpt2_params_from_gguf": (_i, [_vp, C.POINTER(Gpt2ParamsC)]),
     "wgb_gpt2_create": (_i, [C.POINTER(Gpt2ParamsC), _pp]),
     "wgb_gpt2_destroy": (_i, [_vp]),

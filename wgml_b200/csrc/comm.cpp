@@ -8,6 +8,7 @@
 #include <nccl.h>
 
 #include <mutex>
+#include <vector>
 
 namespace {
 
@@ -78,6 +79,11 @@ int nccl_fail(ncclResult_t r, const char *what, ncclComm_t comm)
 struct wgb_comm {
     ncclComm_t comm = nullptr;
     int rank = 0, size = 1;
+    struct Shared {
+        void *local;
+        void *peer[WGB_COMM_MAX_PEERS];
+    };
+    std::vector<Shared> shared;   // buffers opened on the peers (wgb_comm_shared_alloc)
 };
 
 static_assert(sizeof(ncclUniqueId) == WGB_COMM_ID_BYTES, "id size in the public header");
@@ -118,6 +124,11 @@ WGB_EXPORT int wgb_comm_create(const void *id, int rank, int size, wgb_comm **ou
 WGB_EXPORT int wgb_comm_destroy(wgb_comm *c)
 {
     if (!c) return WGB_OK;
+    for (auto &sh : c->shared) {
+        for (int p = 0; p < c->size; p++)
+            if (p != c->rank && sh.peer[p]) cudaIpcCloseMemHandle(sh.peer[p]);
+        if (sh.local) cudaFree(sh.local);
+    }
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     delete c;
     return WGB_OK;
@@ -139,5 +150,49 @@ WGB_EXPORT int wgb_comm_all_gather(wgb_comm *c, const float *d_send, float *d_re
     WGB_REQUIRE(c && d_send && d_recv, "null argument");
     ncclResult_t r = g_nccl.AllGather(d_send, d_recv, n_per_rank, ncclFloat32, c->comm, wgb::as_stream(stream));
     if (r != ncclSuccess) return nccl_fail(r, "ncclAllGather", c->comm);
+    return WGB_OK;
+}
+
+// A zero-filled device buffer of `bytes` on every rank, each mapped into every other rank's address space
+// (CUDA IPC; the ranks are separate processes on GPUs of one node with peer access over NVLink).
+// peers_out[p] is rank p's buffer as seen from this rank; peers_out[rank] is the local one.  Collective:
+// every rank calls it with the same size.  The buffers belong to the communicator.
+WGB_EXPORT int wgb_comm_shared_alloc(wgb_comm *c, size_t bytes, void **peers_out)
+{
+    WGB_REQUIRE(c && peers_out && bytes > 0, "null argument");
+    WGB_REQUIRE(c->size <= WGB_COMM_MAX_PEERS, "shared buffers support at most %d ranks", WGB_COMM_MAX_PEERS);
+    wgb_comm::Shared sh = {};
+    WGB_CUDA(cudaMalloc(&sh.local, bytes));
+    cudaError_t e = cudaMemset(sh.local, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaIpcMemHandle_t mine;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine, sh.local);
+    unsigned char *d_send = nullptr, *d_recv = nullptr;
+    std::vector<cudaIpcMemHandle_t> all((size_t)c->size);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&d_send, sizeof(mine));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&d_recv, sizeof(mine) * (size_t)c->size);
+    if (e == cudaSuccess) e = cudaMemcpy(d_send, &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    int rc = WGB_OK;
+    if (e == cudaSuccess) {
+        // the zero fill above is complete on every rank before any rank learns a handle
+        ncclResult_t r = g_nccl.AllGather(d_send, d_recv, sizeof(mine), ncclUint8, c->comm, (cudaStream_t)0);
+        if (r != ncclSuccess) rc = nccl_fail(r, "ncclAllGather(ipc handles)", c->comm);
+    }
+    if (e == cudaSuccess && rc == WGB_OK) e = cudaStreamSynchronize((cudaStream_t)0);
+    if (e == cudaSuccess && rc == WGB_OK) e = cudaMemcpy(all.data(), d_recv, sizeof(mine) * (size_t)c->size, cudaMemcpyDeviceToHost);
+    if (d_send) cudaFree(d_send);
+    if (d_recv) cudaFree(d_recv);
+    for (int p = 0; p < c->size && e == cudaSuccess && rc == WGB_OK; p++) {
+        if (p == c->rank) sh.peer[p] = sh.local;
+        else e = cudaIpcOpenMemHandle(&sh.peer[p], all[(size_t)p], cudaIpcMemLazyEnablePeerAccess);
+    }
+    if (e != cudaSuccess || rc != WGB_OK) {
+        for (int p = 0; p < c->size; p++)
+            if (p != c->rank && sh.peer[p]) cudaIpcCloseMemHandle(sh.peer[p]);
+        cudaFree(sh.local);
+        return rc != WGB_OK ? rc : wgb::cuda_fail(e, "shared buffer set-up (CUDA IPC)");
+    }
+    c->shared.push_back(sh);
+    for (int p = 0; p < c->size; p++) peers_out[p] = sh.peer[p];
     return WGB_OK;
 }

@@ -284,7 +284,11 @@ __device__ __forceinline__ void epi_finish(const GemvArgs &a, const Part (&parts
         if (a.bias) y += c.b0;
         if (EPI == EPI_RESIDUAL) y = c.b1 + y;
         if (EPI == EPI_GELU) y = gelu_f32(y);
-        a.out[c.r0] = y;
+        if ((EPI == EPI_STORE || EPI == EPI_RESIDUAL) && a.peer_out.n) {
+            for (uint32_t p = 0; p < a.peer_out.n; p++) a.peer_out.mail[p][c.r0] = y;   // every rank's mailbox, own included
+        } else {
+            a.out[c.r0] = y;
+        }
     } else if (EPI == EPI_SILU_PAIR) {
         a.out[c.r0] = yb * (ya / (1.0f + expf(-ya)));
     } else if (EPI == EPI_QKV_ROPE) {
@@ -412,6 +416,23 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             if (ul == 0) mbar_arrive(empty0 + 8 * s);   // stage and partial sums may be overwritten
             epi_finish<EPI>(a, parts, c, ya, yb);
         }
+        if ((EPI == EPI_STORE || EPI == EPI_RESIDUAL) && a.peer_out.n) {
+            // The block's partial rows are on their way to the peers; the last block of the launch raises
+            // this rank's flag everywhere once every block's stores are visible system-wide.
+            __threadfence_system();
+            __syncwarp();
+            uint32_t last = 0;
+            if (lane == 0) {
+                const uint32_t t = atomicAdd(a.peer_out.ticket, 1u);
+                last = (t == gridDim.x - 1);
+                if (last) *a.peer_out.ticket = 0;   // ready for the next step
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence_system();
+                if ((uint32_t)lane < a.peer_out.n) atomicAdd_system(a.peer_out.flag[lane], 1u);
+            }
+        }
         if (lane == 0) stamp_end(a.stamp);
         return;
     }
@@ -422,14 +443,41 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     // normalisation passes and the staging (one trip to L2 instead of up to three, one after the other).
     constexpr uint32_t XC = 3;
     float4 xc[XC];
+    const bool gather = PRO == PRO_RMS && a.peer_in.n != 0;
+    if (gather) {
+        // Partial products from every rank: wait for the flags (bounded), then add in rank order.
+        if (threadIdx.x < a.peer_in.n) {
+            const uint32_t want = __ldcg(a.peer_in.epoch);
+            const uint32_t *f = a.peer_in.flag + threadIdx.x;
+            bool ok = false;
+            for (uint32_t i = 0; i < GEMV_WAIT_LIMIT && !ok; i++) {
+                uint32_t v;
+                asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                ok = (int32_t)(v - want) >= 0;
+            }
+            if (!ok && a.err) atomicExch(a.err, 6u);
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
+        }
+        cons_sync();
+    }
+    auto load_chunk = [&](uint32_t c) {
+        if (!gather) return ld_act4(a.x + 4 * c);
+        float4 v = __ldcg(reinterpret_cast<const float4 *>(a.peer_in.mail) + c);
+        for (uint32_t r = 1; r < a.peer_in.n; r++) {
+            const float4 w = __ldcg(reinterpret_cast<const float4 *>(a.peer_in.mail + (size_t)r * K) + c);
+            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+        }
+        if (blockIdx.x == 0) reinterpret_cast<float4 *>(a.peer_in.x_out)[c] = v;
+        return v;
+    };
 #pragma unroll
     for (uint32_t i = 0; i < XC; i++) {
         const uint32_t c = threadIdx.x + i * GEMV_CONS_THREADS;
-        xc[i] = c < K / 4 ? ld_act4(a.x + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        xc[i] = c < K / 4 ? load_chunk(c) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     auto chunk = [&](uint32_t c) {
         const uint32_t i = c / GEMV_CONS_THREADS;   // c = threadIdx.x + i * GEMV_CONS_THREADS
-        return i == 0 ? xc[0] : (i == 1 ? xc[1] : (i == 2 ? xc[2] : ld_act4(a.x + 4 * c)));
+        return i == 0 ? xc[0] : (i == 1 ? xc[1] : (i == 2 ? xc[2] : load_chunk(c)));
     };
     float mean = 0.0f, scale = 1.0f;
     if (PRO == PRO_RMS) {
@@ -589,7 +637,7 @@ bool gemv_fast_supported(const QMat &m)
 }
 
 // Device status word shared by all launches of the process: 0, or the code of the first bounded
-// wait that expired (1 consumer, 2 producer).
+// wait that expired (1 consumer, 2 producer, 3 epilogue, 6 flags of the tensor-parallel peers).
 static uint32_t *g_err = nullptr;
 static bool g_trace_plan = false;   // WGML_B200_TRACE_PLAN=1 prints the plan of every launch to stderr
 static int ensure_err()

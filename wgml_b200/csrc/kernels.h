@@ -23,6 +23,25 @@ enum Epilogue {
     EPI_QKV_SPLIT = 5  // one fused qkv matrix (+bias): rows [0,n) -> out, [n,2n) -> k cache, [2n,3n) -> v cache
 };
 
+// Direct exchange of partial products between the ranks of a tensor-parallel group (no collective call):
+// the sender's epilogue stores its partial rows into every rank's mailbox (plain stores to peer memory
+// over NVLink) and, once per launch, adds one to its flag on every rank; the receiver's prologue waits
+// until all `n` flags have reached the step count and adds the `n` partials in rank order.
+constexpr int PEER_MAX = 8;
+struct PeerOut {
+    uint32_t n;                   // ranks (0: write to `out` as usual)
+    float *mail[PEER_MAX];        // on rank p: where this rank's partial of this exchange goes
+    uint32_t *flag[PEER_MAX];     // on rank p: this rank's flag for this exchange (counts steps)
+    uint32_t *ticket;             // local: blocks of this launch that have finished
+};
+struct PeerIn {
+    uint32_t n;                   // ranks (0: read `x` as usual)
+    const float *mail;            // local mailbox of this exchange: [n][ncols]
+    const uint32_t *flag;         // local flags of this exchange: [n]
+    const uint32_t *epoch;        // device scalar: steps so far = the value every flag must have reached
+    float *x_out;                 // where block 0 leaves the sum (the residual stream)
+};
+
 struct GemvArgs {
     QMat mat[3];
     int nmat;
@@ -59,6 +78,8 @@ struct GemvArgs {
     uint32_t spb;           // stages per producer pass
     uint32_t *err;          // device status word for expired waits
     unsigned long long *stamp;   // optional: receives the launch's end time (stamp_end)
+    PeerOut peer_out;            // EPI_STORE / EPI_RESIDUAL only
+    PeerIn peer_in;              // PRO_RMS only
 };
 
 // Enqueues one fused kernel.  All matrices must share format and ncols and have a fast path;

@@ -53,6 +53,12 @@ struct wgb_llama2 {
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_n_prompt = 0;
     void *comm = nullptr;
+    // direct exchange of partial products between the ranks (wgb_llama2_set_exchange)
+    int exchange = 0;
+    float *mail_peer[PEER_MAX] = {};         // rank p's mailbox as seen from here: [2 * n_layers][tp][dim] floats
+    uint32_t *flag_peer[PEER_MAX] = {};      // rank p's flags: [2 * n_layers][tp]
+    uint32_t *tickets = nullptr;             // local: one per exchange
+    uint32_t *tp_epoch = nullptr;            // local: forwards so far
     int kernels_per_token = 0;
     // per-launch timing of wgb_llama2_profile_step: one event after every launch
     bool profiling = false;
@@ -65,6 +71,8 @@ struct wgb_llama2 {
 };
 
 namespace {
+
+__global__ void bump_kernel(uint32_t *p) { *p += 1; }
 
 __global__ void stamp_kernel(unsigned long long *slot) { stamp_end(slot); }
 
@@ -190,6 +198,33 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
         stamp_kernel<<<1, 1, 0, s>>>(stamp_slot());
         WGB_LAUNCH_CHECK("stamp_kernel");
     }
+    // Direct exchange between the ranks (fused schedule only): exchange 2l follows attn_output of layer l,
+    // 2l + 1 its ffn_down; the next normalising kernel (gate/up, the next layer's q/k/v, the logits) adds
+    // the partials.  `pending` is the exchange whose sum the next such kernel has to form.
+    const bool direct = tp && m->exchange == 1 && fused;
+    int pending = -1;
+    auto send_to_peers = [&](GemvArgs &g, int e) {
+        g.peer_out.n = (uint32_t)m->tp_size;
+        for (int p = 0; p < m->tp_size; p++) {
+            g.peer_out.mail[p] = m->mail_peer[p] + ((size_t)e * m->tp_size + m->tp_rank) * c.dim;
+            g.peer_out.flag[p] = m->flag_peer[p] + (size_t)e * m->tp_size + m->tp_rank;
+        }
+        g.peer_out.ticket = m->tickets + e;
+        pending = e;
+    };
+    auto receive_pending = [&](GemvArgs &g) {
+        if (pending < 0) return;
+        g.peer_in.n = (uint32_t)m->tp_size;
+        g.peer_in.mail = m->mail_peer[m->tp_rank] + (size_t)pending * m->tp_size * c.dim;
+        g.peer_in.flag = m->flag_peer[m->tp_rank] + (size_t)pending * m->tp_size;
+        g.peer_in.epoch = m->tp_epoch;
+        g.peer_in.x_out = m->x;
+        pending = -1;
+    };
+    if (direct) {
+        bump_kernel<<<1, 1, 0, s>>>(m->tp_epoch);
+        WGB_LAUNCH_CHECK("bump_kernel");
+    }
     int rc = launch_embed(m->token_embd->view, nullptr, d_token, d_pos, m->x, s);
     if (rc) return rc;
     n++;
@@ -234,6 +269,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             a.rope_variant = variant;
             a.rope_freq = m->rope_freq;
             a.stamp = stamp_slot();
+            receive_pending(a);
             if ((rc = launch_gemv(a, s, pdl))) return rc;
             mark(m, s, K_QKV, l);
             at.stamp = stamp_slot();
@@ -249,8 +285,9 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             o.residual = m->x;
             o.out = tp ? m->xb2 : m->x;
             o.stamp = stamp_slot();
+            if (direct) send_to_peers(o, 2 * (int)l);
             if ((rc = launch_gemv(o, s, pdl))) return rc;
-            if (tp && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->x, c.dim, s))) return rc;
+            if (tp && !direct && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->x, c.dim, s))) return rc;
             mark(m, s, K_OPROJ, l);
             GemvArgs f = {};
             f.mat[0] = w.m[WGB_L_FFN_GATE]->view;
@@ -263,6 +300,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             f.epilogue = EPI_SILU_PAIR;
             f.out = m->hb;
             f.stamp = stamp_slot();
+            receive_pending(f);
             if ((rc = launch_gemv(f, s, pdl))) return rc;
             mark(m, s, K_GATE_UP, l);
             GemvArgs d = {};
@@ -273,8 +311,9 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             d.residual = m->x;
             d.out = tp ? m->xb2 : m->x;
             d.stamp = stamp_slot();
+            if (direct) send_to_peers(d, 2 * (int)l + 1);
             if ((rc = launch_gemv(d, s, pdl))) return rc;
-            if (tp && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->x, c.dim, s))) return rc;
+            if (tp && !direct && (rc = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, m->xb2, m->x, c.dim, s))) return rc;
             mark(m, s, K_DOWN, l);
             n += 5;
         } else {
@@ -314,6 +353,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
         a.epilogue = EPI_STORE;
         a.out = m->logits;
         a.stamp = stamp_slot();
+        receive_pending(a);
         if ((rc = launch_gemv(a, s, pdl))) return rc;
         mark(m, s, K_HEAD, -1);
         n += 1;
@@ -418,6 +458,8 @@ WGB_EXPORT int wgb_llama2_destroy(wgb_llama2 *m)
                       m->value_cache, m->attn_scratch, m->rope_freq };
     for (float *b : bufs) if (b) cudaFree(b);
     if (m->stamps) cudaFree(m->stamps);
+    if (m->tickets) cudaFree(m->tickets);
+    if (m->tp_epoch) cudaFree(m->tp_epoch);
     uint32_t *ubufs[] = { m->attn_counters, m->scalars, m->argmax_scratch, m->d_prompt, m->d_out };
     for (uint32_t *b : ubufs) if (b) cudaFree(b);
     if (m->h_pinned) cudaFreeHost(m->h_pinned);
@@ -606,6 +648,37 @@ WGB_EXPORT int wgb_llama2_set_comm(wgb_llama2 *m, void *comm)
     return WGB_OK;
 }
 
+WGB_EXPORT int wgb_llama2_set_exchange(wgb_llama2 *m, int mode)
+{
+    WGB_REQUIRE(m && (mode == 0 || mode == 1), "bad argument");
+    if (m->tp_size == 1 || mode == 0) {
+        m->exchange = 0;
+        drop_graph(m);
+        return WGB_OK;
+    }
+    WGB_REQUIRE(m->comm, "set the communicator first");
+    WGB_REQUIRE(m->tp_size <= PEER_MAX, "direct exchange supports at most %d ranks", PEER_MAX);
+    if (!m->mail_peer[0]) {
+        const size_t n_ex = 2 * (size_t)m->cfg.n_layers;
+        const size_t mail_bytes = n_ex * m->tp_size * m->cfg.dim * sizeof(float);
+        const size_t flag_bytes = n_ex * m->tp_size * sizeof(uint32_t);
+        void *peers[PEER_MAX] = {};
+        int rc = wgb_comm_shared_alloc((wgb_comm *)m->comm, mail_bytes + flag_bytes, peers);
+        if (rc) return rc;
+        for (int p = 0; p < m->tp_size; p++) {
+            m->mail_peer[p] = (float *)peers[p];
+            m->flag_peer[p] = (uint32_t *)((char *)peers[p] + mail_bytes);
+        }
+        WGB_CUDA(cudaMalloc((void **)&m->tickets, n_ex * sizeof(uint32_t)));
+        WGB_CUDA(cudaMemset(m->tickets, 0, n_ex * sizeof(uint32_t)));
+        WGB_CUDA(cudaMalloc((void **)&m->tp_epoch, sizeof(uint32_t)));
+        WGB_CUDA(cudaMemset(m->tp_epoch, 0, sizeof(uint32_t)));
+    }
+    m->exchange = 1;
+    drop_graph(m);
+    return WGB_OK;
+}
+
 WGB_EXPORT int wgb_llama2_set_fused(wgb_llama2 *m, int enable)
 {
     WGB_REQUIRE(m, "null argument");
@@ -696,6 +769,8 @@ static int profile_stamped(wgb_llama2 *m, cudaStream_t s, int cap, int *kinds, i
     const size_t need = 5 * (size_t)m->cfg.n_layers + 2;
     if (need > m->stamps_cap) {
         if (m->stamps) cudaFree(m->stamps);
+    if (m->tickets) cudaFree(m->tickets);
+    if (m->tp_epoch) cudaFree(m->tp_epoch);
         m->stamps = nullptr;
         m->stamps_cap = 0;
         WGB_CUDA(cudaMalloc((void **)&m->stamps, need * sizeof(unsigned long long)));

@@ -119,6 +119,11 @@ class Llama2:
     def set_comm(self, comm_ptr: int) -> None:
         check(_lib.load().wgb_llama2_set_comm(self._h, comm_ptr))
 
+    def set_exchange(self, mode: int) -> None:
+        """0: NCCL all-reduce after attn_output / ffn_down; 1: partial products stored straight into the peers'
+        mailboxes by the kernels (collective call: every rank, same mode)."""
+        check(_lib.load().wgb_llama2_set_exchange(self._h, int(mode)))
+
     def dispatch(self, token: int, pos: int) -> None:
         """Llama2::dispatch for one token (enqueued on the current stream; logits stay on the device)."""
         check(_lib.load().wgb_llama2_forward(self._h, token, pos, torch.cuda.current_stream().cuda_stream))

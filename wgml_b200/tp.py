@@ -130,7 +130,9 @@ def init_from_torch_distributed() -> Comm:
     return Comm(box[0], rank, size)
 
 
-def attach(model, comm: Comm) -> None:
-    """Gives a tensor-parallel ``Llama2`` its group; must precede the first forward."""
+def attach(model, comm: Comm, direct: bool = True) -> None:
+    """Gives a tensor-parallel ``Llama2`` its group; must precede the first forward.  `direct`: the kernels
+    exchange partial products through peer memory themselves instead of calling NCCL's all-reduce."""
     model.set_comm(comm.handle)
     model._comm = comm   # keep it alive as long as the model
+    model.set_exchange(1 if direct else 0)
