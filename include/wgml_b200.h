@@ -310,10 +310,10 @@ int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t n_prompt, 
 int wgb_llama2_kernels_per_token(const wgb_llama2 *m);
 /* Measurement aid, the counterpart of wgcore's GpuTimestamps around a pass
  * (crates/wgml-bench/src/main.rs:201,226-241): the time each launch of one forward adds to the step.
- * Fused schedule on one GPU: the step is replayed from a CUDA graph exactly as wgb_llama2_decode runs it
+ * Fused schedule on one GPU, or tensor parallel with the direct exchange: the step is replayed from a CUDA graph exactly as wgb_llama2_decode runs it
  * (programmatic dependent launch included) and every launch leaves its end time (%globaltimer) in device
  * memory; a launch's time is the distance from its predecessor's end to its own (the embedding copy is
- * counted with the first launch).  Otherwise (unfused schedule, tensor parallel): a CUDA event after every
+ * counted with the first launch).  Otherwise (unfused schedule, NCCL exchange): a CUDA event after every
  * launch.  Reports per launch its kind (0 embedding, 1 norm+QKV+RoPE, 2 attention, 3 output projection,
  * 4 norm+gate/up+SiLU, 5 down projection, 6 norm+logits, 7 unfused layer), its layer (-1 outside layers)
  * and the milliseconds.  At most `cap` entries are written; *n_out is their number. */

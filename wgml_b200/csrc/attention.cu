@@ -32,7 +32,9 @@ size_t attn_scratch_floats(uint32_t n_heads, uint32_t head_size, uint32_t seq_le
 
 // QH = query heads per KV head handled at once; VC = float4 chunks of a head per lane (1: head
 // sizes up to 128, 2: up to 256).
-template <int QH, int VC>
+// MULTI: a block may get several chunks (long contexts, few heads) and keeps a running softmax over them;
+// otherwise every block has exactly one chunk and the loop below collapses.
+template <int QH, int VC, bool MULTI>
 __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constant__ AttnArgs a)
 {
     __shared__ float s_score[QH][ATT_CHUNK];
@@ -43,38 +45,62 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
     pdl_launch_dependents();
     // The position and every cache row before it were written by earlier steps, so they are read before the
     // wait for the preceding launch (which produces q and the cache row of this position): the DRAM round
-    // trip of the chunk overlaps the hand-over between the launches.
+    // trip of the first chunk overlaps the hand-over between the launches.
     const uint32_t pos = a.pos ? *a.pos : a.p.pos;
     const uint32_t hs = a.p.head_size, kv_dim = a.p.kv_dim, kv_mul = a.p.kv_mul;
     const uint32_t split = blockIdx.x, kvh = blockIdx.y;
-    const uint32_t t0 = split * ATT_CHUNK;
-    if (t0 > pos) {
+    // The grid has a fixed number of splits (chosen so that all blocks are resident at once); the chunks of
+    // ATT_CHUNK positions up to `pos` are dealt to them in runs of `cpb`.
+    const uint32_t nchunks_active = pos / ATT_CHUNK + 1;
+    const uint32_t max_splits = gridDim.x;
+    const uint32_t cpb = MULTI ? (nchunks_active + max_splits - 1) / max_splits : 1u;
+    const uint32_t nsplit_active = (nchunks_active + cpb - 1) / cpb;
+    if (split >= nsplit_active) {
         if (threadIdx.x == 0) stamp_end(a.stamp);
         return;
     }
-    const uint32_t nt = min((uint32_t)ATT_CHUNK, pos + 1 - t0);
-    const uint32_t nsplit_active = pos / ATT_CHUNK + 1;
-    const uint32_t max_splits = gridDim.x;
+    const uint32_t ck_begin = split * cpb, ck_end = MULTI ? min(ck_begin + cpb, nchunks_active) : ck_begin + 1;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t nchunk = hs / 4;  // float4 chunks per head
     const float inv_sqrt = sqrtf((float)hs);
 
-    // Every warp owns ATT_TPW consecutive time steps.  All of their K and V rows are requested up front
-    // (independent loads, one DRAM round trip for the whole chunk), then consumed.
-    const float *kbase = a.k_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
-    const float *vbase = a.v_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
+    // Every warp owns ATT_TPW consecutive time steps of a chunk.  All of their K and V rows are requested up
+    // front (independent loads, one DRAM round trip for the whole chunk), then consumed.
     float4 kr[ATT_TPW][VC], vr[ATT_TPW][VC];
+    auto load_rows = [&](uint32_t t0, bool before_wait) {
+        const float *kbase = a.k_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
+        const float *vbase = a.v_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
 #pragma unroll
-    for (int i = 0; i < ATT_TPW; i++) {
-        const uint32_t tl = warp * ATT_TPW + i;
+        for (int i = 0; i < ATT_TPW; i++) {
+            const uint32_t tl = warp * ATT_TPW + i;
 #pragma unroll
-        for (int c = 0; c < VC; c++) {
-            const uint32_t ch = lane + 32 * c;
-            const bool ok = t0 + tl < pos && ch < nchunk;   // rows of earlier steps only
-            kr[i][c] = ok ? __ldcs(reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
-            vr[i][c] = ok ? __ldcs(reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < VC; c++) {
+                const uint32_t ch = lane + 32 * c;
+                const float4 *kp = reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch;
+                const float4 *vp = reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch;
+                if (before_wait) {   // rows of earlier steps only
+                    const bool ok = t0 + tl < pos && ch < nchunk;
+                    kr[i][c] = ok ? __ldcs(kp) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    vr[i][c] = ok ? __ldcs(vp) : make_float4(0.f, 0.f, 0.f, 0.f);
+                } else if (ch < nchunk) {
+                    if (t0 + tl < pos) {
+                        kr[i][c] = __ldcs(kp);
+                        vr[i][c] = __ldcs(vp);
+                    } else if (t0 + tl == pos) {   // the row of this position, written by the preceding launch
+                        kr[i][c] = __ldcg(kp);
+                        vr[i][c] = __ldcg(vp);
+                    } else {
+                        kr[i][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        vr[i][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                } else {
+                    kr[i][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    vr[i][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
         }
-    }
+    };
+    load_rows(ck_begin * ATT_CHUNK, true);
     pdl_wait();
 
     // query heads of this KV head: h = kvh * kv_mul + j, j = hq0 .. hq0 + QH - 1 (looped by caller grid.z)
@@ -89,126 +115,153 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
                           ? __ldcg(reinterpret_cast<const float4 *>(a.q + (size_t)(kvh * kv_mul + hq0 + j) * hs) + ch)
                           : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-    // the row of this position, written by the preceding launch
-#pragma unroll
-    for (int i = 0; i < ATT_TPW; i++) {
-        const uint32_t tl = warp * ATT_TPW + i;
-        if (t0 + tl == pos) {
-#pragma unroll
-            for (int c = 0; c < VC; c++) {
-                const uint32_t ch = lane + 32 * c;
-                if (ch < nchunk) {
-                    kr[i][c] = __ldcg(reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch);
-                    vr[i][c] = __ldcg(reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch);
-                }
-            }
-        }
-    }
-    // Pass 1: scores of the chunk.
-#pragma unroll
-    for (int j = 0; j < QH; j++) {
-        float part[ATT_TPW];
-#pragma unroll
-        for (int i = 0; i < ATT_TPW; i++) {
-            float p = 0.0f;
-#pragma unroll
-            for (int c = 0; c < VC; c++)
-                p += q[j][c].x * kr[i][c].x + q[j][c].y * kr[i][c].y + q[j][c].z * kr[i][c].z + q[j][c].w * kr[i][c].w;
-            part[i] = p;
-        }
-        // ATT_TPW sums over the warp at once: each halving step folds two partials into one lane half
-        // (8 -> 4 -> 2 -> 1 values per lane in 3 steps, then 2 plain steps): 7 + 2 shuffles instead of 40.
-        static_assert(ATT_TPW == 8, "the folding below is written for 8 time steps per warp");
-        float f4[4], f2[2], f1;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const bool up = lane & 16;
-            const float keep = up ? part[2 * i + 1] : part[2 * i], give = up ? part[2 * i] : part[2 * i + 1];
-            f4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
-        }
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const bool up = lane & 8;
-            const float keep = up ? f4[2 * i + 1] : f4[2 * i], give = up ? f4[2 * i] : f4[2 * i + 1];
-            f2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
-        }
-        {
-            const bool up = lane & 4;
-            const float keep = up ? f2[1] : f2[0], give = up ? f2[0] : f2[1];
-            f1 = keep + __shfl_xor_sync(0xffffffffu, give, 4);
-        }
-        f1 += __shfl_xor_sync(0xffffffffu, f1, 2);
-        f1 += __shfl_xor_sync(0xffffffffu, f1, 1);
-        // lane l now holds the sum of time step i = (bit4 of l) + 2 * (bit3) + 4 * (bit2)
-        if ((lane & 3) == 0) {
-            const uint32_t i = ((lane >> 4) & 1) | (((lane >> 3) & 1) << 1) | (((lane >> 2) & 1) << 2);
-            const uint32_t tl = warp * ATT_TPW + i;
-            if (tl < nt) s_score[j][tl] = f1 / inv_sqrt;
-        }
-    }
-    __syncthreads();
 
-    // Chunk maximum per query head, then exponentials and their sum.
-    float mx[QH], sum[QH];
-#pragma unroll
-    for (int j = 0; j < QH; j++) {
-        float m = -INFINITY;
-        for (uint32_t tl = threadIdx.x; tl < nt; tl += ATT_NT) m = fmaxf(m, s_score[j][tl]);
-        m = warp_max(m);
-        if (lane == 0) s_red[j][warp] = m;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < QH; j++) {
-        float m = s_red[j][0];
-#pragma unroll
-        for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, s_red[j][w]);
-        mx[j] = m;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < QH; j++) {
-        float s = 0.0f;
-        for (uint32_t tl = threadIdx.x; tl < nt; tl += ATT_NT) {
-            const float e = expf(s_score[j][tl] - mx[j]);
-            s_score[j][tl] = e;
-            s += e;
-        }
-        s = warp_sum(s);
-        if (lane == 0) s_red[j][warp] = s;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < QH; j++) {
-        float s = 0.0f;
-#pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) s += s_red[j][w];
-        sum[j] = s;
-    }
-
-    // Pass 2: weighted sum of the value rows.
+    // Running softmax state over the block's chunks (rescaled whenever the maximum grows).
+    float M[QH], L[QH];
     float4 acc[QH][VC];
 #pragma unroll
-    for (int j = 0; j < QH; j++)
+    for (int j = 0; j < QH; j++) {
+        M[j] = -INFINITY;
+        L[j] = 0.0f;
 #pragma unroll
         for (int c = 0; c < VC; c++) acc[j][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+
+    for (uint32_t ck = ck_begin; ck < ck_end; ck++) {
+        const uint32_t t0 = ck * ATT_CHUNK;
+        const uint32_t nt = min((uint32_t)ATT_CHUNK, pos + 1 - t0);
+        if (MULTI && ck != ck_begin) {
+            load_rows(t0, false);
+        } else {
+            // the first chunk was requested before the wait; fetch the row of this position if it lies here
 #pragma unroll
-    for (int i = 0; i < ATT_TPW; i++) {
-        const uint32_t tl = warp * ATT_TPW + i;
-        if (tl < nt) {
+            for (int i = 0; i < ATT_TPW; i++) {
+                const uint32_t tl = warp * ATT_TPW + i;
+                if (t0 + tl == pos) {
 #pragma unroll
-            for (int c = 0; c < VC; c++) {
-                const float4 v = vr[i][c];
-#pragma unroll
-                for (int j = 0; j < QH; j++) {
-                    const float p = s_score[j][tl];
-                    acc[j][c].x = fmaf(p, v.x, acc[j][c].x);
-                    acc[j][c].y = fmaf(p, v.y, acc[j][c].y);
-                    acc[j][c].z = fmaf(p, v.z, acc[j][c].z);
-                    acc[j][c].w = fmaf(p, v.w, acc[j][c].w);
+                    for (int c = 0; c < VC; c++) {
+                        const uint32_t ch = lane + 32 * c;
+                        if (ch < nchunk) {
+                            kr[i][c] = __ldcg(reinterpret_cast<const float4 *>(a.k_cache + (size_t)pos * kv_dim + (size_t)kvh * hs) + ch);
+                            vr[i][c] = __ldcg(reinterpret_cast<const float4 *>(a.v_cache + (size_t)pos * kv_dim + (size_t)kvh * hs) + ch);
+                        }
+                    }
                 }
             }
         }
+        // Pass 1: scores of the chunk.
+#pragma unroll
+        for (int j = 0; j < QH; j++) {
+            float part[ATT_TPW];
+#pragma unroll
+            for (int i = 0; i < ATT_TPW; i++) {
+                float p = 0.0f;
+#pragma unroll
+                for (int c = 0; c < VC; c++)
+                    p += q[j][c].x * kr[i][c].x + q[j][c].y * kr[i][c].y + q[j][c].z * kr[i][c].z + q[j][c].w * kr[i][c].w;
+                part[i] = p;
+            }
+            // ATT_TPW sums over the warp at once: each halving step folds two partials into one lane half
+            // (8 -> 4 -> 2 -> 1 values per lane in 3 steps, then 2 plain steps): 7 + 2 shuffles instead of 40.
+            static_assert(ATT_TPW == 8, "the folding below is written for 8 time steps per warp");
+            float f4[4], f2[2], f1;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const bool up = lane & 16;
+                const float keep = up ? part[2 * i + 1] : part[2 * i], give = up ? part[2 * i] : part[2 * i + 1];
+                f4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const bool up = lane & 8;
+                const float keep = up ? f4[2 * i + 1] : f4[2 * i], give = up ? f4[2 * i] : f4[2 * i + 1];
+                f2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+            }
+            {
+                const bool up = lane & 4;
+                const float keep = up ? f2[1] : f2[0], give = up ? f2[0] : f2[1];
+                f1 = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+            }
+            f1 += __shfl_xor_sync(0xffffffffu, f1, 2);
+            f1 += __shfl_xor_sync(0xffffffffu, f1, 1);
+            // lane l now holds the sum of time step i = (bit4 of l) + 2 * (bit3) + 4 * (bit2)
+            if ((lane & 3) == 0) {
+                const uint32_t i = ((lane >> 4) & 1) | (((lane >> 3) & 1) << 1) | (((lane >> 2) & 1) << 2);
+                const uint32_t tl = warp * ATT_TPW + i;
+                if (tl < nt) s_score[j][tl] = f1 / inv_sqrt;
+            }
+        }
+        __syncthreads();
+
+        // Chunk maximum per query head, then exponentials against the running maximum and their sum.
+#pragma unroll
+        for (int j = 0; j < QH; j++) {
+            float m = -INFINITY;
+            for (uint32_t tl = threadIdx.x; tl < nt; tl += ATT_NT) m = fmaxf(m, s_score[j][tl]);
+            m = warp_max(m);
+            if (lane == 0) s_red[j][warp] = m;
+        }
+        __syncthreads();
+        float rescale[QH];
+#pragma unroll
+        for (int j = 0; j < QH; j++) {
+            float m = s_red[j][0];
+#pragma unroll
+            for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, s_red[j][w]);
+            const float mn = MULTI ? fmaxf(M[j], m) : m;
+            rescale[j] = MULTI ? expf(M[j] - mn) : 0.0f;   // 0 for the first chunk (M = -inf)
+            M[j] = mn;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < QH; j++) {
+            float sm = 0.0f;
+            for (uint32_t tl = threadIdx.x; tl < nt; tl += ATT_NT) {
+                const float e = expf(s_score[j][tl] - M[j]);
+                s_score[j][tl] = e;
+                sm += e;
+            }
+            sm = warp_sum(sm);
+            if (lane == 0) s_red[j][warp] = sm;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < QH; j++) {
+            float sm = 0.0f;
+#pragma unroll
+            for (int w = 0; w < ATT_WARPS; w++) sm += s_red[j][w];
+            L[j] = MULTI ? fmaf(L[j], rescale[j], sm) : sm;
+            if (MULTI) {
+#pragma unroll
+                for (int c = 0; c < VC; c++) {
+                    acc[j][c].x *= rescale[j];
+                    acc[j][c].y *= rescale[j];
+                    acc[j][c].z *= rescale[j];
+                    acc[j][c].w *= rescale[j];
+                }
+            }
+        }
+
+        // Pass 2: weighted sum of the value rows.
+#pragma unroll
+        for (int i = 0; i < ATT_TPW; i++) {
+            const uint32_t tl = warp * ATT_TPW + i;
+            if (tl < nt) {
+#pragma unroll
+                for (int c = 0; c < VC; c++) {
+                    const float4 v = vr[i][c];
+#pragma unroll
+                    for (int j = 0; j < QH; j++) {
+                        const float p = s_score[j][tl];
+                        acc[j][c].x = fmaf(p, v.x, acc[j][c].x);
+                        acc[j][c].y = fmaf(p, v.y, acc[j][c].y);
+                        acc[j][c].z = fmaf(p, v.z, acc[j][c].z);
+                        acc[j][c].w = fmaf(p, v.w, acc[j][c].w);
+                    }
+                }
+            }
+        }
+        if (MULTI) __syncthreads();   // the scores and the reduction scratch are reused by the next chunk
     }
 #pragma unroll
     for (int j = 0; j < QH; j++)
@@ -219,24 +272,24 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
         }
     __syncthreads();
 
-    // Partial result of this chunk -> scratch [head][split][hs + 4] = {vector, max, sum}.
+    // Partial result of this block -> scratch [head][split][hs + 4] = {vector, max, sum}.
     for (uint32_t e = threadIdx.x; e < QH * hs; e += ATT_NT) {
         const uint32_t j = e / hs, i = e % hs;
         if (hq0 + j >= kv_mul) continue;
-        float s = 0.0f;
+        float sv = 0.0f;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) s += s_acc[w][j][i];
+        for (int w = 0; w < ATT_WARPS; w++) sv += s_acc[w][j][i];
         const uint32_t h = kvh * kv_mul + hq0 + j;
-        a.scratch[((size_t)h * max_splits + split) * (hs + 4) + i] = s;
+        a.scratch[((size_t)h * max_splits + split) * (hs + 4) + i] = sv;
     }
     if (threadIdx.x < QH && hq0 + threadIdx.x < kv_mul) {
         const uint32_t h = kvh * kv_mul + hq0 + threadIdx.x;
         float *dst = a.scratch + ((size_t)h * max_splits + split) * (hs + 4) + hs;
-        float m = mx[0], s = sum[0];
+        float m = M[0], sm = L[0];
 #pragma unroll
-        for (int j = 1; j < QH; j++) { m = (threadIdx.x == j) ? mx[j] : m; s = (threadIdx.x == j) ? sum[j] : s; }
+        for (int j = 1; j < QH; j++) { m = (threadIdx.x == j) ? M[j] : m; sm = (threadIdx.x == j) ? L[j] : sm; }
         dst[0] = m;
-        dst[1] = s;
+        dst[1] = sm;
     }
 
     // Ticket: the last block of this (KV head, query-head group) merges all chunks.
@@ -362,10 +415,27 @@ __global__ void __launch_bounds__(ATT_NT) attn_full_kernel(const __grid_constant
 }
 
 template <int QH, int VC>
-static int launch_split(const AttnArgs &a, uint32_t nsplits, uint32_t n_kv, uint32_t zgroups, cudaStream_t stream, bool pdl)
+static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t n_kv, uint32_t zgroups, cudaStream_t stream, bool pdl)
 {
+    // One chunk per block while all blocks of such a grid are resident at once (a second wave would double
+    // the latency); beyond that, as many splits as fit and several chunks per block.
+    static int per_sm_single = 0, per_sm_multi = 0;
+    if (!per_sm_single) {
+        WGB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_single, attn_split_kernel<QH, VC, false>, ATT_NT, 0));
+        WGB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_multi, attn_split_kernel<QH, VC, true>, ATT_NT, 0));
+        if (per_sm_single < 1) per_sm_single = 1;
+        if (per_sm_multi < 1) per_sm_multi = 1;
+    }
+    const uint32_t heads = n_kv * zgroups;
+    const bool multi = (uint64_t)nchunks * heads > (uint64_t)per_sm_single * (uint32_t)sm_count();
+    uint32_t splits = nchunks;
+    if (multi) {
+        splits = (uint32_t)per_sm_multi * (uint32_t)sm_count() / heads;
+        if (splits < 1) splits = 1;
+        if (splits > nchunks) splits = nchunks;
+    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(nsplits, n_kv, zgroups);
+    cfg.gridDim = dim3(splits, n_kv, zgroups);
     cfg.blockDim = dim3(ATT_NT);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -375,25 +445,27 @@ static int launch_split(const AttnArgs &a, uint32_t nsplits, uint32_t n_kv, uint
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    WGB_CUDA(cudaLaunchKernelEx(&cfg, attn_split_kernel<QH, VC>, a));
+    if (multi) WGB_CUDA(cudaLaunchKernelEx(&cfg, attn_split_kernel<QH, VC, true>, a));
+    else WGB_CUDA(cudaLaunchKernelEx(&cfg, attn_split_kernel<QH, VC, false>, a));
     return WGB_OK;
 }
 
-// `a.counters` must hold n_kv_heads * ceil(kv_mul / QH) zeroed words (QH as chosen below).
+// `a.counters` must hold n_kv_heads * ceil(kv_mul / QH) zeroed words (QH as chosen below) and `a.scratch`
+// attn_scratch_floats() floats.
 int launch_attention(const AttnArgs &a, cudaStream_t stream, bool pdl)
 {
     const wgb_attn_params &p = a.p;
     WGB_REQUIRE(p.head_size % 4 == 0 && p.head_size <= 256 && p.head_size > 0, "head_size %u unsupported", p.head_size);
     WGB_REQUIRE(p.kv_mul > 0 && p.n_heads % p.kv_mul == 0, "n_heads %u not a multiple of kv_mul %u", p.n_heads, p.kv_mul);
     const uint32_t n_kv = p.n_heads / p.kv_mul;
-    const uint32_t nsplits = attn_num_splits(p.seq_len);
+    const uint32_t nchunks = attn_num_splits(p.seq_len);
     const bool big = p.head_size > 128;
     // query heads per block: the largest of 4 / 2 / 1 that divides nothing away (tail heads masked)
     const uint32_t qh = p.kv_mul >= 4 ? 4 : (p.kv_mul >= 2 ? 2 : 1);
     const uint32_t zg = (p.kv_mul + qh - 1) / qh;
-    if (qh == 4) return big ? launch_split<4, 2>(a, nsplits, n_kv, zg, stream, pdl) : launch_split<4, 1>(a, nsplits, n_kv, zg, stream, pdl);
-    if (qh == 2) return big ? launch_split<2, 2>(a, nsplits, n_kv, zg, stream, pdl) : launch_split<2, 1>(a, nsplits, n_kv, zg, stream, pdl);
-    return big ? launch_split<1, 2>(a, nsplits, n_kv, zg, stream, pdl) : launch_split<1, 1>(a, nsplits, n_kv, zg, stream, pdl);
+    if (qh == 4) return big ? launch_split<4, 2>(a, nchunks, n_kv, zg, stream, pdl) : launch_split<4, 1>(a, nchunks, n_kv, zg, stream, pdl);
+    if (qh == 2) return big ? launch_split<2, 2>(a, nchunks, n_kv, zg, stream, pdl) : launch_split<2, 1>(a, nchunks, n_kv, zg, stream, pdl);
+    return big ? launch_split<1, 2>(a, nchunks, n_kv, zg, stream, pdl) : launch_split<1, 1>(a, nchunks, n_kv, zg, stream, pdl);
 }
 
 }  // namespace wgb

@@ -826,7 +826,7 @@ WGB_EXPORT int wgb_llama2_profile_step(wgb_llama2 *m, uint32_t token, uint32_t p
     cudaStream_t s = as_stream(stream);
     set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
-    if (m->fused && fusable(m) && m->tp_size == 1) return profile_stamped(m, s, cap, kinds, layers, ms, n_out);
+    if (m->fused && fusable(m) && (m->tp_size == 1 || m->exchange == 1)) return profile_stamped(m, s, cap, kinds, layers, ms, n_out);
     rc = profile_once(m, s, true, cap, kinds, layers, ms, n_out);
     if (rc == WGB_ERR_CUDA) {   // events inside a captured graph unavailable: issue the launches one by one
         set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
