@@ -14,6 +14,7 @@
 // probabilities are materialised in the caller's [n_heads][seq_len] buffer.
 #include "kernels.h"
 
+#include <algorithm>
 #include <mutex>
 
 namespace wgb {
@@ -415,7 +416,8 @@ __global__ void __launch_bounds__(ATT_NT) attn_full_kernel(const __grid_constant
 }
 
 template <int QH, int VC>
-static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t n_kv, uint32_t zgroups, cudaStream_t stream, bool pdl)
+static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t nchunks_hint, uint32_t n_kv, uint32_t zgroups,
+                        cudaStream_t stream, bool pdl)
 {
     // One chunk per block while all blocks of such a grid are resident at once (a second wave would double
     // the latency); beyond that, as many splits as fit and several chunks per block.
@@ -427,7 +429,12 @@ static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t n_kv, uint
         if (per_sm_multi < 1) per_sm_multi = 1;
     }
     const uint32_t heads = n_kv * zgroups;
-    const bool multi = (uint64_t)nchunks * heads > (uint64_t)per_sm_single * (uint32_t)sm_count();
+    if (!a.q) {   // sizing query (attn_sizing_class): no launch
+        return (uint64_t)nchunks_hint * heads > (uint64_t)per_sm_single * (uint32_t)sm_count() ? 1 : 0;
+    }
+    // `nchunks_hint`: chunks up to the furthest position this launch is expected to serve (performance only:
+    // either kernel is correct for any position inside the cache).
+    const bool multi = (uint64_t)nchunks_hint * heads > (uint64_t)per_sm_single * (uint32_t)sm_count();
     uint32_t splits = nchunks;
     if (multi) {
         splits = (uint32_t)per_sm_multi * (uint32_t)sm_count() / heads;
@@ -459,13 +466,26 @@ int launch_attention(const AttnArgs &a, cudaStream_t stream, bool pdl)
     WGB_REQUIRE(p.kv_mul > 0 && p.n_heads % p.kv_mul == 0, "n_heads %u not a multiple of kv_mul %u", p.n_heads, p.kv_mul);
     const uint32_t n_kv = p.n_heads / p.kv_mul;
     const uint32_t nchunks = attn_num_splits(p.seq_len);
+    // With the position on the device, p.pos is the caller's bound on it (0: unknown, assume a short context).
+    const uint32_t nh = std::min(nchunks, p.pos / ATT_CHUNK + 1);
     const bool big = p.head_size > 128;
     // query heads per block: the largest of 4 / 2 / 1 that divides nothing away (tail heads masked)
     const uint32_t qh = p.kv_mul >= 4 ? 4 : (p.kv_mul >= 2 ? 2 : 1);
     const uint32_t zg = (p.kv_mul + qh - 1) / qh;
-    if (qh == 4) return big ? launch_split<4, 2>(a, nchunks, n_kv, zg, stream, pdl) : launch_split<4, 1>(a, nchunks, n_kv, zg, stream, pdl);
-    if (qh == 2) return big ? launch_split<2, 2>(a, nchunks, n_kv, zg, stream, pdl) : launch_split<2, 1>(a, nchunks, n_kv, zg, stream, pdl);
-    return big ? launch_split<1, 2>(a, nchunks, n_kv, zg, stream, pdl) : launch_split<1, 1>(a, nchunks, n_kv, zg, stream, pdl);
+    if (qh == 4) return big ? launch_split<4, 2>(a, nchunks, nh, n_kv, zg, stream, pdl) : launch_split<4, 1>(a, nchunks, nh, n_kv, zg, stream, pdl);
+    if (qh == 2) return big ? launch_split<2, 2>(a, nchunks, nh, n_kv, zg, stream, pdl) : launch_split<2, 1>(a, nchunks, nh, n_kv, zg, stream, pdl);
+    return big ? launch_split<1, 2>(a, nchunks, nh, n_kv, zg, stream, pdl) : launch_split<1, 1>(a, nchunks, nh, n_kv, zg, stream, pdl);
+}
+
+// 0 / 1: which of the two launch shapes launch_attention picks for positions up to p.pos (a caller that
+// records launches for later replay re-records when the class changes); negative on error.
+int attn_sizing_class(const wgb_attn_params &p)
+{
+    AttnArgs a = {};
+    a.p = p;
+    a.pos = reinterpret_cast<const uint32_t *>(&a);   // "position on the device": p.pos is the bound
+    const int r = launch_attention(a, nullptr, false);
+    return r > 1 ? -1 : r;
 }
 
 }  // namespace wgb

@@ -102,7 +102,7 @@ int launch_gemv_generic(const QMat &m, const float *x, float *out, cudaStream_t 
 
 // ---- attention ------------------------------------------------------------------------------
 struct AttnArgs {
-    wgb_attn_params p;          // p.pos is ignored when pos != NULL
+    wgb_attn_params p;          // with pos != NULL, p.pos is only a bound on the position used to size the launch
     const uint32_t *pos;        // device scalar or NULL
     const float *q, *k_cache, *v_cache;
     float *xb;
@@ -113,6 +113,7 @@ struct AttnArgs {
 size_t attn_scratch_floats(uint32_t n_heads, uint32_t head_size, uint32_t seq_len);
 uint32_t attn_num_splits(uint32_t seq_len);
 int launch_attention(const AttnArgs &a, cudaStream_t stream, bool pdl);
+int attn_sizing_class(const wgb_attn_params &p);
 
 // ---- small ops used by the models -------------------------------------------------------------
 // x[0..n) = row *d_token of the embedding matrix (+ row *d_pos of `pos_embd` when given).

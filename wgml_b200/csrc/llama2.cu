@@ -52,6 +52,8 @@ struct wgb_llama2 {
     bool fused = true, use_pdl = true;
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_n_prompt = 0;
+    uint32_t pos_bound = 0;                  // furthest position the launches being recorded will serve
+    uint32_t graph_attn_chunks = 0;          // attention launch shape (attn_sizing_class) the captured graph was built for
     void *comm = nullptr;
     // direct exchange of partial products between the ranks (wgb_llama2_set_exchange)
     int exchange = 0;
@@ -236,6 +238,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
     at.p.kv_mul = m->kv_mul;
     at.p.n_heads = m->n_q_local;
     at.p.head_size = m->head_size;
+    at.p.pos = m->pos_bound;
     at.pos = d_pos;
     at.q = m->q;
     at.xb = m->xb;
@@ -698,6 +701,7 @@ WGB_EXPORT int wgb_llama2_forward(wgb_llama2 *m, uint32_t token, uint32_t pos, v
     cudaStream_t s = as_stream(stream);
     set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
+    m->pos_bound = pos;
     return enqueue_forward(m, s, &m->kernels_per_token);
 }
 
@@ -826,6 +830,7 @@ WGB_EXPORT int wgb_llama2_profile_step(wgb_llama2 *m, uint32_t token, uint32_t p
     cudaStream_t s = as_stream(stream);
     set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
+    m->pos_bound = pos;
     if (m->fused && fusable(m) && (m->tp_size == 1 || m->exchange == 1)) return profile_stamped(m, s, cap, kinds, layers, ms, n_out);
     rc = profile_once(m, s, true, cap, kinds, layers, ms, n_out);
     if (rc == WGB_ERR_CUDA) {   // events inside a captured graph unavailable: issue the launches one by one
@@ -899,7 +904,19 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
     ls.n_prompt = (uint32_t)n_prompt;
     ls.out_tokens = m->d_out;
 
-    if (m->graph && m->graph_n_prompt != (uint32_t)n_prompt) drop_graph(m);
+    // The attention launch is sized for the furthest position of this call; the captured step is kept until
+    // that changes the shape of the launch (once in the life of a sequence).
+    m->pos_bound = (uint32_t)((size_t)start_pos + total - 1);
+    wgb_attn_params ap = {};
+    ap.seq_len = m->cfg.seq_len;
+    ap.kv_dim = m->kv_dim;
+    ap.kv_mul = m->kv_mul;
+    ap.n_heads = m->n_q_local;
+    ap.head_size = m->head_size;
+    ap.pos = m->pos_bound;
+    const int attn_class = attn_sizing_class(ap);
+    WGB_REQUIRE(attn_class >= 0, "attention sizing failed");
+    if (m->graph && (m->graph_n_prompt != (uint32_t)n_prompt || m->graph_attn_chunks != (uint32_t)attn_class)) drop_graph(m);
     if (!m->graph) {
         // Capture one step on a private stream (capturing on the legacy default stream is not allowed).
         cudaStream_t cs;
@@ -919,6 +936,7 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
         cudaStreamDestroy(cs);
         if (e != cudaSuccess) { m->graph = nullptr; return cuda_fail(e, "CUDA graph capture of a decode step"); }
         m->graph_n_prompt = (uint32_t)n_prompt;
+        m->graph_attn_chunks = (uint32_t)attn_class;
     }
     for (size_t i = 0; i < total; i++) WGB_CUDA(cudaGraphLaunch(m->graph, s));
     // One wait for the ids and the kernels' status word, both through pinned memory.
