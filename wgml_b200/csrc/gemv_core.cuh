@@ -1,12 +1,11 @@
-// Warp-level quantised dot products: R matrix rows against one input vector held in shared
-// memory.  These are the inner loops of every matrix-vector kernel of the library.
+// Warp-level quantised dot products: rows of a matrix staged in shared memory against one input vector
+// held in shared memory.  These are the inner loops of the fused matrix-vector kernel (gemv.cu).
 //
-// A warp owns R rows and walks the K dimension in steps; in each step every lane owns a fixed
-// slice of the columns (a run of codes that shares its sub-block scale), keeps the matching part
-// of x in registers and reuses it for all R rows.  Weight bytes are fetched with 128-bit loads
-// straight from HBM (each byte is used once, so nothing is staged); x comes from shared memory
-// through a bank-conflict-free swizzle.  Partial sums are f32 and are folded across the warp
-// with shuffles.
+// A warp walks the K dimension in steps; in each step every lane owns a fixed slice of the columns (a run
+// of codes that shares its sub-block scale), keeps the matching part of x in registers and reuses it for
+// every row it is given.  Weight bytes come from the stage the producer warp filled with bulk copies
+// (128-bit shared loads); x comes from the shared image through a bank-conflict-free swizzle.  Partial sums
+// are f32 and are folded across the warp by the caller.
 //
 // Arithmetic.  At 7.7 TB/s a B200 streams ~1.4e13 four-bit codes per second, more than its
 // integer pipe can turn into floats one by one, so the inner product of the codes of one
@@ -27,29 +26,6 @@
 #include "qmatrix.cuh"
 
 namespace wgb {
-
-__device__ __forceinline__ uint4 ldg_stream(const void *p)
-{
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-
-__device__ __forceinline__ uint2 ldg_stream8(const void *p)
-{
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-
-__device__ __forceinline__ uint16_t ldg_stream2(const void *p)
-{
-    uint16_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
-    return v;
-}
 
 __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
 {
