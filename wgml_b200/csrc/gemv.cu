@@ -165,7 +165,7 @@ __device__ __forceinline__ int group_parts(const GemvArgs &a, uint32_t gi, Part 
         parts[1] = { 1, r0 };
         return 2;
     } else if (EPI == EPI_QKV_ROPE) {
-        const uint32_t gq = a.mat[0].nrows / rs, gk = a.mat[1].nrows / rs;
+        const uint32_t gq = a.gq, gk = a.gk;
         const int s = gi < gq ? 0 : (gi < gq + gk ? 1 : 2);
         const uint32_t lg = gi - (s == 0 ? 0 : (s == 1 ? gq : gq + gk));
         if (s < 2 && a.rope_variant == WGB_ROPE_NEOX) {
@@ -393,10 +393,14 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
         const uint32_t nb = epilogue_batch(nstage);
         const uint32_t sub = (uint32_t)lane >> 3, ul = (uint32_t)lane & 7;
         const uint32_t gmask = 0xffu << (8 * sub);
-        for (uint32_t it0 = 0; it0 < nst; it0 += nb) {
+        uint32_t s = sub % nstage, phase = (sub / nstage) & 1;   // ring slot and parity of stage it0 + sub
+        for (uint32_t it0 = 0; it0 < nst; it0 += nb, s += nb) {
+            while (s >= nstage) {
+                s -= nstage;
+                phase ^= 1;
+            }
             const uint32_t it = it0 + sub;
             if (sub >= nb || it >= nst) continue;
-            const uint32_t s = it % nstage, phase = (it / nstage) & 1;
             Part parts[2];
             uint32_t n = 0;
             const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
@@ -529,10 +533,17 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     typename S::X x;
     uint32_t held = ~0u;   // column step whose part of the input is in `x`
 
-    // Tasks (stage it, row part rp) with it * rparts + rp = cl, cl + ncl, ...
+    // Tasks (stage it, row part rp) with it * rparts + rp = cl, cl + ncl, ...  The ring slot and parity of
+    // stage `it` are carried along instead of divided out: a task is only a few hundred instructions.
+    uint32_t s = 0, phase = 0, it_prev = 0;
     for (uint32_t t = cl; t < nst * rparts; t += ncl) {
-        const uint32_t it = t / rparts, rp = t - it * rparts;
-        const uint32_t s = it % nstage, phase = (it / nstage) & 1;
+        const uint32_t it = t >> a.rparts_log2, rp = t & (rparts - 1);
+        s += it - it_prev;
+        it_prev = it;
+        while (s >= nstage) {
+            s -= nstage;
+            phase ^= 1;
+        }
         Part parts[2];
         uint32_t n = 0;
         const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
@@ -747,6 +758,11 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
     if (!best_rs) return false;
     a.rs = best_rs;
     a.rparts = best_rp;
+    a.rparts_log2 = best_rp == 1 ? 0 : (best_rp == 2 ? 1 : (best_rp == 4 ? 2 : 3));
+    if (a.epilogue == EPI_QKV_ROPE) {
+        a.gq = a.mat[0].nrows / best_rs;
+        a.gk = a.mat[1].nrows / best_rs;
+    }
     a.rrows = best_rs / best_rp;
     a.kparts = kp;
     a.ngroups = groups_of(best_rs);

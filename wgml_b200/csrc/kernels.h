@@ -69,7 +69,9 @@ struct GemvArgs {
     uint32_t stage_bytes;
     uint32_t ring_offset;   // of the ring inside dynamic shared memory (after the input image)
     uint32_t kparts;        // column parts = consumer warps that share one row
-    uint32_t rparts;        // row parts per stage
+    uint32_t rparts;        // row parts per stage (a power of two)
+    uint32_t rparts_log2;
+    uint32_t gq, gk;        // EPI_QKV_ROPE: groups of the q and of the k matrix
     uint32_t rrows;         // rows per consumer task = rs / rparts
     uint32_t row_bytes;     // bytes of one row over all planes
     uint32_t per_block;     // groups of blocks 0 .. rem_blocks-1; the other blocks have one fewer
