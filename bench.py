@@ -395,13 +395,86 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_gpt2(args):
+    """GPT-2 124M in Q8_0 (a parity configuration, timed for the record): 64 forced prompt tokens, then K greedy
+    steps; the CPU oracle decodes a shorter sequence on the host cores for the baseline.  (Token parity for this
+    model family is the tests' job: with the prescribed weight scale the random 12-layer network amplifies f32
+    rounding differences by orders of magnitude per layer, so the tests use a smaller scale.)"""
+    import torch
+
+    import oracle
+    from wgml_b200 import synth
+    from wgml_b200.models import Gpt2, Gpt2Params
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(0)
+    cfg = dict(synth.CONFIGS["gpt2-124m"])
+    prompt_len = args.prompt_len or 64
+    K, W = args.steps, args.warmup
+    t = synth.gpt2_tensors(cfg, args.seed)
+    p = Gpt2Params(cfg["n_vocab"], cfg["n_seq"], cfg["n_embd"], cfg["n_head"], cfg["n_layer"], cfg["ff_len"], 3 * cfg["n_embd"], 7)
+    model = Gpt2(p)
+    model.load_tensors(t)
+    prompt = synth.prompt(prompt_len, cfg["n_vocab"], args.seed)
+    model.decode(prompt, 0)
+    pos = prompt_len - 1
+    last = np.array([prompt[-1]], np.uint32)
+    for _ in range(max(W, 1)):
+        last = model.decode(last, 1, start_pos=pos)
+        pos += 1
+    stream = torch.cuda.current_stream()
+    torch.cuda.synchronize()
+    with ClockSampler(0) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        out = model.decode(last, K, start_pos=pos)
+        e1.record(stream)
+        torch.cuda.synchronize()
+    ms_dev = e0.elapsed_time(e1)
+    pos += K
+    last = out[-1:]
+    n_e2e = min(K, cfg["n_seq"] - pos - 1)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        last = model.decode(last, 1, start_pos=pos)
+        pos += 1
+    torch.cuda.synchronize()
+    wall_e2e = time.perf_counter() - t0
+    n, ff = cfg["n_embd"], cfg["ff_len"]
+    weights = (cfg["n_layer"] * (3 * n * n + n * n + 2 * n * ff) + cfg["n_vocab"] * n) * BPE[8]
+    peak, peak_src = measured_peaks()
+    tok_s = K / (ms_dev * 1e-3)
+    line = {
+        "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_dev / K,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "gpt2-124m", "prompt_len": prompt_len, "decode_steps": K, "batch": 1, "parallelism": "single GPU",
+                   "weights_gb": weights / 1e9,
+                   "timing": "CUDA events on the launch stream; 131 MB of Q8_0 matrices per token fit the 126 MB L2 only partly"},
+        "e2e": {"value": n_e2e / wall_e2e, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
+                "ms_per_step": 1e3 * wall_e2e / n_e2e, "how": "wgb_gpt2_decode called once per token with host token ids"},
+        "gpu_launches": int(model.kernels_per_token()) * (K + n_e2e), "kernels_per_token": int(model.kernels_per_token()),
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": weights * tok_s / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": weights * tok_s / 1e9 / peak, "traffic": None, "peak_source": peak_src},
+    }
+    if not args.no_cpu_baseline:
+        cpu = oracle.Gpt2Oracle(cfg, t)
+        n_cpu = min(K, 64)
+        t0 = time.perf_counter()
+        cpu.decode(prompt, n_cpu)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": (prompt_len - 1 + n_cpu) / dt, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+                                "sample": f"{prompt_len - 1} prompt + {n_cpu} greedy steps of the whole model"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "llama2-7b", "llama2-70b", "tiny-llama"])
+    ap.add_argument("--workload", default=None, choices=[None, "llama2-7b", "llama2-70b", "tiny-llama", "gpt2-124m"])
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="tensor-parallel runs: partial products exchanged by the kernels through peer memory (default) "
@@ -414,6 +487,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "gpt2-124m":
+        run_gpt2(args)
     else:
         run_b200(args)
 
