@@ -43,3 +43,18 @@ def test_gpt2_124m_shapes_two_layers():
     compare_steps(gpu, cpu, prompt, what="gpt2-124m-2l")
     exp = cpu.decode(prompt[:3], 8, 0)  # overwrites positions 0.. of both caches identically
     assert np.array_equal(gpu.decode(prompt[:3], 8), exp)
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_gpt2_124m_full_depth(fused):
+    """The whole GPT-2 124M configuration (12 layers, Q8_0), weights scaled so that pre-activations stay of
+    order one (at the scale of the timing configuration a random 12-layer network amplifies f32 rounding
+    differences ~3x per layer and implementations cannot be compared): logits along the oracle's path,
+    caches, and 32 greedy tokens after a 16-token prompt."""
+    cfg = dict(synth.CONFIGS["gpt2-124m"])
+    gpu, cpu, _ = gpt2_pair(cfg, seed=3, fused=fused, scale=0.0005)
+    prompt = synth.prompt(16, cfg["n_vocab"], 3)
+    compare_steps(gpu, cpu, prompt[:8], what="gpt2-124m")
+    exp = cpu.decode(prompt, 32)
+    got = gpu.decode(prompt, 32)
+    assert np.array_equal(got, exp), f"first difference at {np.nonzero(got != exp)[0][:1]}"

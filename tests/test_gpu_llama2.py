@@ -151,3 +151,31 @@ def test_load_from_gguf_file(tmp_path):
     assert gpu.config.vocab_size == 1000 and gpu.config.n_kv_heads == 4 and abs(gpu.config.rms_norm_eps - 1e-5) < 1e-9
     cpu = oracle.Llama2Oracle(cfg, t)
     compare_steps(gpu, cpu, synth.prompt(5, 1000, 8), what="gguf")
+
+
+def test_llama2_7b_full_depth_greedy_tokens():
+    """The whole Llama-2-7B configuration (32 layers, Q4_K with Q6_K for the output matrix and every other
+    ffn_down) against the CPU transformer with on-the-fly dequantisation: logits at the first steps and the
+    first 32 greedy tokens after a 4-token prompt.  Weight scales are chosen so that pre-activations stay of
+    order one; at the scale of the timing configuration a random 32-layer network amplifies f32 rounding
+    differences until implementations cannot be compared token by token."""
+    cfg = dict(synth.CONFIGS["llama2-7b"], seq_len=48)
+    gpu, cpu, _ = llama_pair(cfg, seed=4, scale=1.0e-4)
+    prompt = synth.prompt(4, cfg["vocab_size"], 4)
+    exp_tokens, margin = cpu.decode(prompt, 32)
+    got_tokens = gpu.decode(prompt, 32)
+    diff = np.nonzero(got_tokens != exp_tokens)[0]
+    assert diff.size == 0, f"first difference at step {diff[0]}, top-2 margin there {margin[diff[0]]}"
+    gpu2, cpu2, _ = llama_pair(cfg, seed=4, scale=1.0e-4)
+    compare_steps(gpu2, cpu2, np.concatenate([prompt[:1], exp_tokens[:3]]), what="7b")
+
+
+def test_70b_shapes_two_layers_gqa():
+    """Llama-2-70B dimensions (dim 8192, 64 query / 8 KV heads of 128, FFN 28672, vocab 32000, Q4_K) with 2
+    layers: the long rows (K = 8192 and 28672) and the grouped-query attention path at the real sizes."""
+    cfg = dict(synth.CONFIGS["llama2-70b"], n_layers=2, seq_len=48)
+    gpu, cpu, _ = llama_pair(cfg, seed=6, scale=2.0e-4)
+    prompt = synth.prompt(4, cfg["vocab_size"], 6)
+    compare_steps(gpu, cpu, prompt, what="70b-2l")
+    exp, _ = cpu.decode(prompt, 8, 0)
+    assert np.array_equal(gpu.decode(prompt, 8), exp)
