@@ -923,7 +923,9 @@ static int gemv_dispatch(const QMat &m, const float *d_v, float *d_out, cudaStre
         a.prologue = PRO_NONE;
         a.epilogue = EPI_STORE;
         a.out = d_out;
-        return launch_gemv(a, stream, false);
+        // Programmatic dependent launch: the kernel streams its first weights while the previous launch in the
+        // stream is still draining, and waits for it (griddepcontrol.wait) before it reads d_v or writes d_out.
+        return launch_gemv(a, stream, true);
     }
     return launch_gemv_generic(m, d_v, d_out, stream);
 }
