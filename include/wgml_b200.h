@@ -292,8 +292,11 @@ int wgb_llama2_set_fused(wgb_llama2 *m, int enable);
  * crates/wgml-chat/src/chat_llama2.rs:155-213): one token at position pos; logits stay on the
  * device (wgb_llama2_logits). */
 int wgb_llama2_forward(wgb_llama2 *m, uint32_t token, uint32_t pos, void *stream);
-/* Device pointers into Llama2State (transformer.rs:17-45): logits [vocab_size], x [dim],
- * key / value cache of a layer [seq_len][kv_dim / tp_size]. */
+/* Device pointers into Llama2State (transformer.rs:17-45): logits [vocab_size], x [dim], key / value cache
+ * of a layer.  The caches are head-major, [n_kv_heads / tp_size][seq_len][head_size] (the reference keeps
+ * [seq_len][kv_dim], transformer.rs:75-80): the positions of one KV head are contiguous, so the attention
+ * kernel can move 64 of them with one bulk copy.  Element (pos, head, e) of the reference layout is element
+ * (head, pos, e) here. */
 const float *wgb_llama2_logits(const wgb_llama2 *m);
 const float *wgb_llama2_x(const wgb_llama2 *m);
 float *wgb_llama2_key_cache(wgb_llama2 *m, uint32_t layer);

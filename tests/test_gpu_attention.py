@@ -43,9 +43,33 @@ def test_split_kernel_shapes(case):
     run(*case, want_attn=False, seed=1)
 
 
+@pytest.mark.parametrize("case", [
+    (4224, 32, 128, 1, 4100),    # 7B heads, long context: one query head per block, 15 chunks per block
+    (4224, 32, 128, 1, 4095),    # last chunk exactly full
+    (4224, 32, 128, 4, 4100),    # four query heads per KV head
+    (4224, 32, 128, 2, 2049),    # two, last chunk of two positions
+    (4224, 40, 128, 5, 3000),    # five query heads share a block of eight
+    (4224, 96, 128, 12, 1500),   # twelve: two groups of eight (tail masked)
+    (8256, 64, 64, 8, 8200),     # head size 64: half of the lanes idle
+    (8256, 24, 96, 1, 5000),     # head size 96
+    (4224, 64, 128, 8, 0),       # only the first chunk holds anything, and only one position
+    (4224, 64, 128, 8, 63), (4224, 64, 128, 8, 64), (4224, 64, 128, 8, 130),
+])
+def test_streaming_kernel_shapes(case):
+    """Shapes whose chunks outnumber the resident blocks of the split kernel and take the streaming kernel
+    (head sizes up to 128): the position bound passed with a host-side `pos` is the position itself."""
+    run(*case, want_attn=False, seed=3)
+
+
 def test_repeated_calls_reuse_the_ticket_counters():
     a = run(512, 8, 64, 2, 300, False, seed=2)
     b = run(512, 8, 64, 2, 300, False, seed=2)
+    assert torch.equal(a, b)
+
+
+def test_repeated_streaming_calls_reuse_the_ticket_counters():
+    a = run(4224, 64, 128, 8, 4100, False, seed=4)
+    b = run(4224, 64, 128, 8, 4100, False, seed=4)
     assert torch.equal(a, b)
 
 

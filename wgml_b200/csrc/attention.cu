@@ -10,8 +10,12 @@
 // finishes last for a KV head (an atomic ticket, nobody waits) merges the chunks.  K and V rows
 // are read once for all kv_mul query heads.
 //
+// Long contexts (more chunks than blocks fit in one wave) take the streaming kernel further down: one block
+// per SM walks a run of chunks with a producer warp feeding K / V tiles through shared memory.
+//
 // Full kernel (API path that returns the attention weights): one block per query head, the
 // probabilities are materialised in the caller's [n_heads][seq_len] buffer.
+#include "async_copy.cuh"
 #include "kernels.h"
 
 #include <algorithm>
@@ -48,7 +52,8 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
     // wait for the preceding launch (which produces q and the cache row of this position): the DRAM round
     // trip of the first chunk overlaps the hand-over between the launches.
     const uint32_t pos = a.pos ? *a.pos : a.p.pos;
-    const uint32_t hs = a.p.head_size, kv_dim = a.p.kv_dim, kv_mul = a.p.kv_mul;
+    const uint32_t hs = a.p.head_size, kv_mul = a.p.kv_mul;
+    const uint32_t rstr = a.row_stride ? a.row_stride : a.p.kv_dim, hstr = a.row_stride ? a.head_stride : hs;
     const uint32_t split = blockIdx.x, kvh = blockIdx.y;
     // The grid has a fixed number of splits (chosen so that all blocks are resident at once); the chunks of
     // ATT_CHUNK positions up to `pos` are dealt to them in runs of `cpb`.
@@ -69,16 +74,16 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
     // front (independent loads, one DRAM round trip for the whole chunk), then consumed.
     float4 kr[ATT_TPW][VC], vr[ATT_TPW][VC];
     auto load_rows = [&](uint32_t t0, bool before_wait) {
-        const float *kbase = a.k_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
-        const float *vbase = a.v_cache + (size_t)t0 * kv_dim + (size_t)kvh * hs;
+        const float *kbase = a.k_cache + (size_t)t0 * rstr + (size_t)kvh * hstr;
+        const float *vbase = a.v_cache + (size_t)t0 * rstr + (size_t)kvh * hstr;
 #pragma unroll
         for (int i = 0; i < ATT_TPW; i++) {
             const uint32_t tl = warp * ATT_TPW + i;
 #pragma unroll
             for (int c = 0; c < VC; c++) {
                 const uint32_t ch = lane + 32 * c;
-                const float4 *kp = reinterpret_cast<const float4 *>(kbase + (size_t)tl * kv_dim) + ch;
-                const float4 *vp = reinterpret_cast<const float4 *>(vbase + (size_t)tl * kv_dim) + ch;
+                const float4 *kp = reinterpret_cast<const float4 *>(kbase + (size_t)tl * rstr) + ch;
+                const float4 *vp = reinterpret_cast<const float4 *>(vbase + (size_t)tl * rstr) + ch;
                 if (before_wait) {   // rows of earlier steps only
                     const bool ok = t0 + tl < pos && ch < nchunk;
                     kr[i][c] = ok ? __ldcs(kp) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -143,8 +148,8 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
                     for (int c = 0; c < VC; c++) {
                         const uint32_t ch = lane + 32 * c;
                         if (ch < nchunk) {
-                            kr[i][c] = __ldcg(reinterpret_cast<const float4 *>(a.k_cache + (size_t)pos * kv_dim + (size_t)kvh * hs) + ch);
-                            vr[i][c] = __ldcg(reinterpret_cast<const float4 *>(a.v_cache + (size_t)pos * kv_dim + (size_t)kvh * hs) + ch);
+                            kr[i][c] = __ldcg(reinterpret_cast<const float4 *>(a.k_cache + (size_t)pos * rstr + (size_t)kvh * hstr) + ch);
+                            vr[i][c] = __ldcg(reinterpret_cast<const float4 *>(a.v_cache + (size_t)pos * rstr + (size_t)kvh * hstr) + ch);
                         }
                     }
                 }
@@ -382,14 +387,15 @@ __global__ void __launch_bounds__(ATT_NT) attn_full_kernel(const __grid_constant
 {
     __shared__ float red[32];
     const uint32_t pos = a.pos ? *a.pos : a.p.pos;
-    const uint32_t hs = a.p.head_size, kv_dim = a.p.kv_dim;
+    const uint32_t hs = a.p.head_size;
+    const uint32_t rstr = a.row_stride ? a.row_stride : a.p.kv_dim, hstr = a.row_stride ? a.head_stride : hs;
     const uint32_t h = blockIdx.x, kvh = h / a.p.kv_mul;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float *att = attn + (size_t)h * a.p.seq_len;
     const float *qh = a.q + (size_t)h * hs;
     const float sq = sqrtf((float)hs);
     for (uint32_t t = warp; t <= pos; t += ATT_WARPS) {
-        const float *k = a.k_cache + (size_t)t * kv_dim + (size_t)kvh * hs;
+        const float *k = a.k_cache + (size_t)t * rstr + (size_t)kvh * hstr;
         float s = 0.0f;
         for (uint32_t i = lane; i < hs; i += 32) s = fmaf(qh[i], k[i], s);
         s = warp_sum(s);
@@ -410,9 +416,341 @@ __global__ void __launch_bounds__(ATT_NT) attn_full_kernel(const __grid_constant
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < hs; i += ATT_NT) {
         float o = 0.0f;
-        for (uint32_t t = 0; t <= pos; t++) o = fmaf(att[t], a.v_cache[(size_t)t * kv_dim + (size_t)kvh * hs + i], o);
+        for (uint32_t t = 0; t <= pos; t++) o = fmaf(att[t], a.v_cache[(size_t)t * rstr + (size_t)kvh * hstr + i], o);
         a.xb[(size_t)h * hs + i] = o;
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Streaming kernel (long contexts; head sizes up to 128).  Grid (splits, KV heads, query-head groups) with
+// one block per SM; a block owns a run of 64-position chunks of one KV head and all QH query heads that
+// share it.  A producer warp streams the K and V rows of chunk after chunk into a two-stage ring of shared
+// memory with bulk asynchronous copies (one per cache row, completion on an mbarrier), so the DRAM round
+// trip of the next chunk overlaps the arithmetic of the current one; eight consumer warps score the chunk
+// (8 positions per warp); each warp keeps its own running softmax and weighted value sum over its positions,
+// so nothing inside the loop synchronises the warps, and the eight are merged once at the end.  The block's
+// (vector, max, sum) goes to the scratch buffer and the last block of a head merges, as in the split kernel.
+// Every barrier wait is bounded (status codes 7 producer, 8 consumer).
+// ---------------------------------------------------------------------------------------------
+constexpr int ATS_STAGES = 2;
+constexpr int ATS_NT = ATT_NT + 32;   // consumer warps + the producer warp
+
+__device__ __forceinline__ void att_cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(ATT_NT) : "memory"); }
+
+template <int QH>
+__global__ void __launch_bounds__(ATS_NT, 1) attn_stream_kernel(const __grid_constant__ AttnArgs a)
+{
+    extern __shared__ uint4 ring4[];   // ATS_STAGES x (K tile | V tile), a tile = ATT_CHUNK rows of head_size floats
+    __shared__ float s_sc[ATT_WARPS][QH][ATT_TPW];   // a warp's scores of the chunk in work
+    __shared__ float s_red[QH][ATT_WARPS], s_sum[QH][ATT_WARPS];
+    __shared__ float s_M[QH];
+    __shared__ __align__(8) unsigned long long bars[2 * ATS_STAGES];
+    __shared__ uint32_t s_last;
+
+    const uint32_t pos = a.pos ? *a.pos : a.p.pos;   // written by an earlier step: readable before the wait
+    const uint32_t hs = a.p.head_size, kv_mul = a.p.kv_mul;
+    const uint32_t rstr = a.row_stride ? a.row_stride : a.p.kv_dim, hstr = a.row_stride ? a.head_stride : hs;
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y, hq0 = blockIdx.z * QH;
+    const uint32_t nchunks_active = pos / ATT_CHUNK + 1;
+    const uint32_t max_splits = gridDim.x;
+    const uint32_t cpb = (nchunks_active + max_splits - 1) / max_splits;
+    const uint32_t nsplit_active = (nchunks_active + cpb - 1) / cpb;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (split >= nsplit_active) {
+        if (threadIdx.x == 0) stamp_end(a.stamp);
+        return;
+    }
+    const uint32_t ck_begin = split * cpb, ck_end = min(ck_begin + cpb, nchunks_active);
+    const uint32_t full0 = smem_addr(&bars[0]), empty0 = smem_addr(&bars[ATS_STAGES]);
+    if (threadIdx.x < 2 * ATS_STAGES) {
+        mbar_init(smem_addr(&bars[threadIdx.x]), threadIdx.x < ATS_STAGES ? 1 : ATT_WARPS);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    const uint32_t row_bytes = hs * 4, tile_bytes = ATT_CHUNK * row_bytes, stage_bytes = 2 * tile_bytes;
+    const uint32_t ring = smem_addr(ring4);
+
+    if (warp == ATT_WARPS) {
+        // ------------------------------ producer ------------------------------
+        for (uint32_t ck = ck_begin, n = 0; ck < ck_end; ck++, n++) {
+            const uint32_t s = n % ATS_STAGES;
+            if (n >= ATS_STAGES) mbar_wait(empty0 + 8 * s, ((n / ATS_STAGES) - 1) & 1, a.err, 7);
+            const uint32_t t0 = ck * ATT_CHUNK;
+            const uint32_t nt = min((uint32_t)ATT_CHUNK, pos + 1 - t0);
+            // every row before `pos` was written by an earlier step; the row of `pos` by the preceding launch
+            if (t0 + nt - 1 == pos) pdl_wait();
+            if (lane == 0) mbar_expect_tx(full0 + 8 * s, 2 * nt * row_bytes);
+            __syncwarp();
+            const float *kbase = a.k_cache + (size_t)t0 * rstr + (size_t)kvh * hstr;
+            const float *vbase = a.v_cache + (size_t)t0 * rstr + (size_t)kvh * hstr;
+            const uint32_t dst = ring + s * stage_bytes;
+            if (rstr == hs) {
+                // head-major cache: the rows of the chunk are one contiguous run, one copy per tile
+                if (lane == 0) bulk_copy_g2s(dst, kbase, nt * row_bytes, full0 + 8 * s);
+                if (lane == 1) bulk_copy_g2s(dst + tile_bytes, vbase, nt * row_bytes, full0 + 8 * s);
+            } else {
+                for (uint32_t r = lane; r < nt; r += 32) {
+                    bulk_copy_g2s(dst + r * row_bytes, kbase + (size_t)r * rstr, row_bytes, full0 + 8 * s);
+                    bulk_copy_g2s(dst + tile_bytes + r * row_bytes, vbase + (size_t)r * rstr, row_bytes, full0 + 8 * s);
+                }
+            }
+        }
+        return;
+    }
+
+    // ------------------------------ consumers ------------------------------
+    // Every warp keeps its own running softmax over the positions it owns (8 per chunk), so the warps never
+    // synchronise inside the loop; their (max, sum, vector) triples are merged once at the end.
+    pdl_wait();
+    const uint32_t nchunk = hs / 4;  // float4 chunks per head (at most 32: one per lane)
+    const float inv_sqrt = sqrtf((float)hs);
+    const bool on = (uint32_t)lane < nchunk;
+    float4 q[QH];
+#pragma unroll
+    for (int j = 0; j < QH; j++)
+        q[j] = (on && hq0 + j < kv_mul) ? __ldcg(reinterpret_cast<const float4 *>(a.q + (size_t)(kvh * kv_mul + hq0 + j) * hs) + lane)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+    float M[QH], L[QH];
+    float4 acc[QH];
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        M[j] = -INFINITY;
+        L[j] = 0.0f;
+        acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const unsigned char *ringp = reinterpret_cast<const unsigned char *>(ring4);
+    float *my_sc = &s_sc[warp][0][0];
+
+    for (uint32_t ck = ck_begin, n = 0; ck < ck_end; ck++, n++) {
+        const uint32_t s = n % ATS_STAGES;
+        const uint32_t t0 = ck * ATT_CHUNK;
+        const uint32_t nt = min((uint32_t)ATT_CHUNK, pos + 1 - t0);
+        mbar_wait(full0 + 8 * s, (n / ATS_STAGES) & 1, a.err, 8);
+        const float4 *kt = reinterpret_cast<const float4 *>(ringp + (size_t)s * stage_bytes);
+        const float4 *vt = reinterpret_cast<const float4 *>(ringp + (size_t)s * stage_bytes + tile_bytes);
+        if ((uint32_t)warp * ATT_TPW < nt) {   // the warp has positions in this chunk
+            // scores of the warp's 8 positions for every query head -> the warp's corner of shared memory
+            float4 rows[ATT_TPW];
+#pragma unroll
+            for (int i = 0; i < ATT_TPW; i++) {
+                const uint32_t tl = warp * ATT_TPW + i;
+                rows[i] = (on && tl < nt) ? kt[tl * nchunk + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < QH; j++) {
+                float part[ATT_TPW];
+#pragma unroll
+                for (int i = 0; i < ATT_TPW; i++)
+                    part[i] = q[j].x * rows[i].x + q[j].y * rows[i].y + q[j].z * rows[i].z + q[j].w * rows[i].w;
+                // 8 sums over the warp at once (8 -> 4 -> 2 -> 1 values per lane, then two plain steps)
+                float f4[4], f2[2], f1;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const bool up = lane & 16;
+                    const float keep = up ? part[2 * i + 1] : part[2 * i], give = up ? part[2 * i] : part[2 * i + 1];
+                    f4[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+                }
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const bool up = lane & 8;
+                    const float keep = up ? f4[2 * i + 1] : f4[2 * i], give = up ? f4[2 * i] : f4[2 * i + 1];
+                    f2[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+                }
+                {
+                    const bool up = lane & 4;
+                    const float keep = up ? f2[1] : f2[0], give = up ? f2[0] : f2[1];
+                    f1 = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+                }
+                f1 += __shfl_xor_sync(0xffffffffu, f1, 2);
+                f1 += __shfl_xor_sync(0xffffffffu, f1, 1);
+                if ((lane & 3) == 0) {
+                    const uint32_t i = ((lane >> 4) & 1) | (((lane >> 3) & 1) << 1) | (((lane >> 2) & 1) << 2);
+                    my_sc[j * ATT_TPW + i] = (warp * ATT_TPW + i < nt) ? f1 / inv_sqrt : -INFINITY;
+                }
+            }
+            __syncwarp();
+            // the value rows take the registers of the key rows
+#pragma unroll
+            for (int i = 0; i < ATT_TPW; i++) {
+                const uint32_t tl = warp * ATT_TPW + i;
+                rows[i] = (on && tl < nt) ? vt[tl * nchunk + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < QH; j++) {
+                const float sv = my_sc[j * ATT_TPW + (lane & 7)];   // lane l looks after position l % 8
+                float m = sv;
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+                const float mn = fmaxf(M[j], m);          // finite: position 0 of the warp is valid
+                const float rs = expf(M[j] - mn);         // 0 at the warp's first chunk (M = -inf)
+                const float e = expf(sv - mn);            // 0 for positions past the end
+                M[j] = mn;
+                float psum = 0.0f;
+                acc[j].x *= rs;
+                acc[j].y *= rs;
+                acc[j].z *= rs;
+                acc[j].w *= rs;
+#pragma unroll
+                for (int i = 0; i < ATT_TPW; i++) {
+                    const float p = __shfl_sync(0xffffffffu, e, i);
+                    psum += p;
+                    acc[j].x = fmaf(p, rows[i].x, acc[j].x);
+                    acc[j].y = fmaf(p, rows[i].y, acc[j].y);
+                    acc[j].z = fmaf(p, rows[i].z, acc[j].z);
+                    acc[j].w = fmaf(p, rows[i].w, acc[j].w);
+                }
+                L[j] = fmaf(L[j], rs, psum);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * s);   // this warp is done with the stage
+    }
+
+    // Merge of the eight warps.  Every copy has landed and been consumed: the ring now holds their vectors.
+    float *s_acc = reinterpret_cast<float *>(ring4);   // [ATT_WARPS][QH][hs + 4]
+    const uint32_t astr = hs + 4;
+    att_cons_sync();
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        if (on) reinterpret_cast<float4 *>(s_acc + ((size_t)warp * QH + j) * astr)[lane] = acc[j];
+        if (lane == 0) {
+            s_red[j][warp] = M[j];
+            s_sum[j][warp] = L[j];
+        }
+    }
+    att_cons_sync();
+    for (uint32_t e = threadIdx.x; e < QH * hs; e += ATT_NT) {
+        const uint32_t j = e / hs, i = e % hs;
+        if (hq0 + j >= kv_mul) continue;
+        float mb = s_red[j][0];
+#pragma unroll
+        for (int w = 1; w < ATT_WARPS; w++) mb = fmaxf(mb, s_red[j][w]);
+        float sv = 0.0f, lb = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) {
+            const float f = expf(s_red[j][w] - mb);   // 0 for a warp that had no positions
+            sv = fmaf(s_acc[((size_t)w * QH + j) * astr + i], f, sv);
+            lb = fmaf(s_sum[j][w], f, lb);
+        }
+        float *dst = a.scratch + ((size_t)(kvh * kv_mul + hq0 + j) * max_splits + split) * (hs + 4);
+        dst[i] = sv;
+        if (i == 0) {
+            dst[hs] = mb;
+            dst[hs + 1] = lb;
+        }
+    }
+
+    // Ticket: the last block of this (KV head, query-head group) merges all splits.
+    __threadfence();
+    att_cons_sync();
+    uint32_t *counter = a.counters + kvh * gridDim.z + blockIdx.z;
+    if (threadIdx.x == 0) {
+        const uint32_t ticket = atomicAdd(counter, 1u);
+        s_last = (ticket == nsplit_active - 1);
+        if (s_last) *counter = 0;  // ready for the next launch
+    }
+    att_cons_sync();
+    if (!s_last) {
+        if (threadIdx.x == 0) stamp_end(a.stamp);
+        return;
+    }
+    __threadfence();
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        float m = -INFINITY;
+        if (hq0 + j < kv_mul) {
+            const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
+            for (uint32_t sp = threadIdx.x; sp < nsplit_active; sp += ATT_NT) m = fmaxf(m, __ldcg(base + (size_t)sp * (hs + 4) + hs));
+        }
+        m = warp_max(m);
+        if (lane == 0) s_red[j][warp] = m;
+    }
+    att_cons_sync();
+    if (threadIdx.x < QH) {
+        float m = s_red[threadIdx.x][0];
+#pragma unroll
+        for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, s_red[threadIdx.x][w]);
+        s_M[threadIdx.x] = m;
+    }
+    att_cons_sync();
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        if (hq0 + j >= kv_mul) continue;   // uniform over the block
+        const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
+        const float Mj = s_M[j];
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        float Lw = 0.0f;
+        for (uint32_t sp = warp; sp < nsplit_active; sp += ATT_WARPS) {
+            const float *row = base + (size_t)sp * (hs + 4);
+            const float w = expf(__ldcg(row + hs) - Mj);
+            Lw = fmaf(__ldcg(row + hs + 1), w, Lw);
+            if (on) {
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(row) + lane);
+                o.x = fmaf(v.x, w, o.x);
+                o.y = fmaf(v.y, w, o.y);
+                o.z = fmaf(v.z, w, o.z);
+                o.w = fmaf(v.w, w, o.w);
+            }
+        }
+        if (on) reinterpret_cast<float4 *>(s_acc + ((size_t)warp * QH + j) * astr)[lane] = o;
+        if (lane == 0) s_red[j][warp] = Lw;
+    }
+    att_cons_sync();
+    for (uint32_t e = threadIdx.x; e < QH * hs; e += ATT_NT) {
+        const uint32_t j = e / hs, i = e % hs;
+        if (hq0 + j >= kv_mul) continue;
+        float Lt = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) {
+            Lt += s_red[j][w];
+            o += s_acc[((size_t)w * QH + j) * astr + i];
+        }
+        a.xb[(size_t)(kvh * kv_mul + hq0 + j) * hs + i] = o / Lt;
+    }
+    if (threadIdx.x == 0) stamp_end(a.stamp);
+}
+
+template <int QH>
+static int launch_stream(const AttnArgs &a, uint32_t nchunks, uint32_t n_kv, uint32_t zgroups, cudaStream_t stream, bool pdl)
+{
+    const size_t smem = (size_t)ATS_STAGES * 2 * ATT_CHUNK * a.p.head_size * sizeof(float);
+    static bool ready = false;
+    if (!ready) {
+        WGB_CUDA(cudaFuncSetAttribute(attn_stream_kernel<QH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ATS_STAGES * 2 * ATT_CHUNK * 128 * sizeof(float))));
+        ready = true;
+    }
+    uint32_t splits = (uint32_t)sm_count() / (n_kv * zgroups);   // one block per SM
+    if (splits < 1) splits = 1;
+    if (splits > nchunks) splits = nchunks;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, n_kv, zgroups);
+    cfg.blockDim = dim3(ATS_NT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    WGB_CUDA(cudaLaunchKernelEx(&cfg, attn_stream_kernel<QH>, a));
+    return WGB_OK;
+}
+
+// Long contexts with head sizes up to 128: all query heads of a KV head (up to 8) in one streaming block.
+static int launch_stream_any(const AttnArgs &a, uint32_t nchunks, cudaStream_t stream, bool pdl)
+{
+    const uint32_t n_kv = a.p.n_heads / a.p.kv_mul;
+    const uint32_t qh = a.p.kv_mul >= 5 ? 8 : (a.p.kv_mul >= 3 ? 4 : (a.p.kv_mul >= 2 ? 2 : 1));
+    const uint32_t zg = (a.p.kv_mul + qh - 1) / qh;
+    if (qh == 8) return launch_stream<8>(a, nchunks, n_kv, zg, stream, pdl);
+    if (qh == 4) return launch_stream<4>(a, nchunks, n_kv, zg, stream, pdl);
+    if (qh == 2) return launch_stream<2>(a, nchunks, n_kv, zg, stream, pdl);
+    return launch_stream<1>(a, nchunks, n_kv, zg, stream, pdl);
 }
 
 template <int QH, int VC>
@@ -435,6 +773,7 @@ static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t nchunks_hi
     // `nchunks_hint`: chunks up to the furthest position this launch is expected to serve (performance only:
     // either kernel is correct for any position inside the cache).
     const bool multi = (uint64_t)nchunks_hint * heads > (uint64_t)per_sm_single * (uint32_t)sm_count();
+    if (multi && VC == 1) return launch_stream_any(a, nchunks, stream, pdl);
     uint32_t splits = nchunks;
     if (multi) {
         splits = (uint32_t)per_sm_multi * (uint32_t)sm_count() / heads;

@@ -24,6 +24,7 @@
 //     one; rs and the row split are chosen per launch (see plan()).
 // Every mbarrier wait is bounded: after ~2^22 polls a waiter records an error code in the launch's
 // status word and carries on with whatever is in shared memory, so the kernel always terminates.
+#include "async_copy.cuh"
 #include "gemv_core.cuh"
 #include "kernels.h"
 #include "qaccess.cuh"
@@ -43,7 +44,7 @@ constexpr int GEMV_EPILOGUE = GEMV_NCONS + 1;       // warp index of the epilogu
 constexpr int GEMV_NT = (GEMV_EPILOGUE + 1) * 32;
 constexpr int GEMV_MAX_RS = 8;                      // rows per stage
 constexpr int GEMV_MAX_STAGES = 24;
-constexpr uint32_t GEMV_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t GEMV_WAIT_LIMIT = ASYNC_WAIT_LIMIT;
 constexpr uint32_t GEMV_ROPE_TAB = 128;             // pair indices with a precomputed rotation
 constexpr size_t GEMV_SMEM_BUDGET = 200 * 1024;     // dynamic shared memory per block
 
@@ -88,48 +89,6 @@ __device__ __forceinline__ float warp_sum8(const float (&acc)[8], int lane)
     v += __shfl_xor_sync(0xffffffffu, v, 2);
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     return v;
-}
-
-// ---- mbarrier / bulk-copy primitives ---------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait; on expiry records `code` in *err and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *err, uint32_t code)
-{
-    for (uint32_t i = 0; i < GEMV_WAIT_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    if (err) atomicExch(err, code);
-    return false;
-}
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
 }
 
 // Stages per pass of the epilogue warp and of the producer warp.  The lanes of a warp may be held at a
@@ -215,6 +174,7 @@ __device__ __forceinline__ void unit_rows(const Part (&parts)[2], int nparts, ui
 struct EpiCtx {
     bool on;            // the lane has a unit
     uint32_t r0, r1;    // output rows of the unit (matrix row indices)
+    uint32_t d0, d1;    // EPI_QKV_ROPE: their offsets from `dst`
     float b0, b1;       // bias of r0 / r1, or the residual in b1 for EPI_RESIDUAL
     float sn, cs;       // RoPE rotation
     float *dst;         // EPI_QKV_*: where the rows of the unit go
@@ -237,7 +197,8 @@ __device__ __forceinline__ EpiCtx epi_prepare(const GemvArgs &a, const Part (&pa
         const int s = parts[0].mat;
         const float *bias = s == 0 ? a.bias : (s == 1 ? a.bias_k : a.bias_v);
         const uint32_t pos = *a.pos;
-        c.dst = s == 0 ? a.out : ((s == 1 ? a.k_cache : a.v_cache) + (size_t)pos * a.kv_dim);
+        const uint32_t rstr = a.kv_row_stride ? a.kv_row_stride : a.kv_dim;
+        c.dst = s == 0 ? a.out : ((s == 1 ? a.k_cache : a.v_cache) + (size_t)pos * rstr);
         if (s == 2) {
             c.r0 = c.r1 = parts[0].row0 + t;
         } else if (nparts == 2) {   // Neox: pairs (r0 + t, r0 + t + head_size / 2)
@@ -246,6 +207,13 @@ __device__ __forceinline__ EpiCtx epi_prepare(const GemvArgs &a, const Part (&pa
         } else {                    // Original: adjacent pairs
             c.r0 = parts[0].row0 + 2 * t;
             c.r1 = c.r0 + 1;
+        }
+        // where rows r0 / r1 land: q as is, k / v by (head, element) in the cache's layout
+        c.d0 = c.r0;
+        c.d1 = c.r1;
+        if (s != 0 && a.kv_row_stride) {
+            c.d0 = (c.r0 / a.head_size) * a.kv_head_stride + c.r0 % a.head_size;
+            c.d1 = (c.r1 / a.head_size) * a.kv_head_stride + c.r1 % a.head_size;
         }
         if (bias) {
             c.b0 = bias[c.r0];
@@ -293,11 +261,11 @@ __device__ __forceinline__ void epi_finish(const GemvArgs &a, const Part (&parts
         a.out[c.r0] = yb * (ya / (1.0f + expf(-ya)));
     } else if (EPI == EPI_QKV_ROPE) {
         if (parts[0].mat == 2) {
-            c.dst[c.r0] = ya + c.b0;
+            c.dst[c.d0] = ya + c.b0;
         } else {
             const float y0 = ya + c.b0, y1 = yb + c.b1;
-            c.dst[c.r0] = c.cs * y0 - c.sn * y1;
-            c.dst[c.r1] = c.sn * y0 + c.cs * y1;
+            c.dst[c.d0] = c.cs * y0 - c.sn * y1;
+            c.dst[c.d1] = c.sn * y0 + c.cs * y1;
         }
     } else if (EPI == EPI_QKV_SPLIT) {
         *c.dst = ya + c.b0;

@@ -126,6 +126,7 @@ int enqueue_forward(wgb_gpt2 *m, cudaStream_t s, int *nkernels)
     at.xb = m->curr_768;
     at.scratch = m->attn_scratch;
     at.counters = m->attn_counters;
+    at.err = gemv_status_word();
     for (uint32_t l = 0; l < p.n_layer; l++) {
         const wgb_gpt2::Layer &w = m->layers[l];
         float *kc = m->key_cache + l * cache_stride, *vc = m->value_cache + l * cache_stride;

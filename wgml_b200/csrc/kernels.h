@@ -57,7 +57,8 @@ struct GemvArgs {
     const float *bias_k, *bias_v;
     const float *residual;
     // EPI_QKV_*: KV cache rows and the position, read on the device
-    float *k_cache, *v_cache;   // [seq_len][kv_dim]
+    float *k_cache, *v_cache;   // element (pos, head, e) at pos * kv_row_stride + head * kv_head_stride + e
+    uint32_t kv_row_stride, kv_head_stride;   // 0, 0: the reference layout [seq_len][kv_dim] (kv_dim, head_size)
     const uint32_t *pos;        // device scalar
     uint32_t kv_dim, head_size;
     int rope_variant;
@@ -107,10 +108,15 @@ struct AttnArgs {
     wgb_attn_params p;          // with pos != NULL, p.pos is only a bound on the position used to size the launch
     const uint32_t *pos;        // device scalar or NULL
     const float *q, *k_cache, *v_cache;
+    // cache element (pos, KV head, e) at pos * row_stride + head * head_stride + e.  0, 0: the reference layout
+    // [seq_len][kv_dim] (kv_dim, head_size); head-major caches (head_size, seq_len * head_size) make the rows of a
+    // head contiguous, which is what the streaming kernel copies in one piece.
+    uint32_t row_stride, head_stride;
     float *xb;
     float *scratch;             // attn_scratch_floats() floats
     uint32_t *counters;         // n_kv_heads counters, zero before the first launch
     unsigned long long *stamp;  // optional: receives the launch's end time (stamp_end)
+    uint32_t *err;              // optional: status word for an expired wait of the streaming kernel
 };
 size_t attn_scratch_floats(uint32_t n_heads, uint32_t head_size, uint32_t seq_len);
 uint32_t attn_num_splits(uint32_t seq_len);

@@ -39,7 +39,8 @@ struct wgb_llama2 {
     // state (Llama2State, transformer.rs:17-45)
     float *x = nullptr, *xb = nullptr, *xb2 = nullptr, *hb = nullptr, *hb2 = nullptr, *q = nullptr, *logits = nullptr;
     float *tk = nullptr, *tv = nullptr;      // unfused path: K / V projections before RoPE + append
-    float *key_cache = nullptr, *value_cache = nullptr;  // [n_layers][seq_len][kv_dim]
+    // [n_layers][n_kv_local][seq_len][head_size]: head-major, so that the positions of one head are contiguous
+    float *key_cache = nullptr, *value_cache = nullptr;
     float *attn_scratch = nullptr;
     uint32_t *attn_counters = nullptr;
     float *rope_freq = nullptr;
@@ -90,7 +91,7 @@ __global__ void set_scalars_kernel(uint32_t *s, uint32_t token, uint32_t pos, ui
 __global__ void qkv_finish_kernel(float *__restrict__ q, const float *__restrict__ tk, const float *__restrict__ tv,
                                   const float *__restrict__ bq, const float *__restrict__ bk, const float *__restrict__ bv,
                                   float *__restrict__ k_cache, float *__restrict__ v_cache, const uint32_t *__restrict__ d_pos,
-                                  uint32_t q_dim, uint32_t kv_dim, uint32_t head_size, int variant,
+                                  uint32_t q_dim, uint32_t kv_dim, uint32_t head_size, uint32_t seq_len, int variant,
                                   const float *__restrict__ freq)
 {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;  // pair index over q
@@ -106,13 +107,16 @@ __global__ void qkv_finish_kernel(float *__restrict__ q, const float *__restrict
     q[ia] = cs * x - sn * y;
     q[ib] = sn * x + cs * y;
     if (2 * i < kv_dim) {
-        float *kc = k_cache + (size_t)pos * kv_dim, *vc = v_cache + (size_t)pos * kv_dim;
+        // head-major cache: element e of head h at position pos sits at (h * seq_len + pos) * head_size + e
+        float *kc = k_cache + (size_t)pos * head_size, *vc = v_cache + (size_t)pos * head_size;
+        const size_t da = (size_t)(ia / head_size) * seq_len * head_size + ia % head_size;
+        const size_t db = (size_t)(ib / head_size) * seq_len * head_size + ib % head_size;
         x = tk[ia] + (bk ? bk[ia] : 0.0f);
         y = tk[ib] + (bk ? bk[ib] : 0.0f);
-        kc[ia] = cs * x - sn * y;
-        kc[ib] = sn * x + cs * y;
-        vc[ia] = tv[ia] + (bv ? bv[ia] : 0.0f);
-        vc[ib] = tv[ib] + (bv ? bv[ib] : 0.0f);
+        kc[da] = cs * x - sn * y;
+        kc[db] = sn * x + cs * y;
+        vc[da] = tv[ia] + (bv ? bv[ia] : 0.0f);
+        vc[db] = tv[ib] + (bv ? bv[ib] : 0.0f);
     }
 }
 
@@ -240,10 +244,13 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
     at.p.head_size = m->head_size;
     at.p.pos = m->pos_bound;
     at.pos = d_pos;
+    at.row_stride = m->head_size;
+    at.head_stride = c.seq_len * m->head_size;
     at.q = m->q;
     at.xb = m->xb;
     at.scratch = m->attn_scratch;
     at.counters = m->attn_counters;
+    at.err = gemv_status_word();
     for (uint32_t l = 0; l < c.n_layers; l++) {
         const wgb_llama2::Layer &w = m->layers[l];
         float *kc = m->key_cache + l * cache_stride, *vc = m->value_cache + l * cache_stride;
@@ -269,6 +276,8 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             a.pos = d_pos;
             a.kv_dim = m->kv_dim;
             a.head_size = m->head_size;
+            a.kv_row_stride = m->head_size;
+            a.kv_head_stride = c.seq_len * m->head_size;
             a.rope_variant = variant;
             a.rope_freq = m->rope_freq;
             a.stamp = stamp_slot();
@@ -327,7 +336,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             if ((rc = mat_vec(w.m[WGB_L_ATTN_V]->view, m->xb, m->tv, s))) return rc;
             qkv_finish_kernel<<<(m->q_dim / 2 + 127) / 128, 128, 0, s>>>(
                 m->q, m->tk, m->tv, w.v[WGB_L_ATTN_Q_BIAS], w.v[WGB_L_ATTN_K_BIAS], w.v[WGB_L_ATTN_V_BIAS], kc, vc, d_pos,
-                m->q_dim, m->kv_dim, m->head_size, variant, m->rope_freq);
+                m->q_dim, m->kv_dim, m->head_size, c.seq_len, variant, m->rope_freq);
             WGB_LAUNCH_CHECK("qkv_finish_kernel");
             if ((rc = launch_attention(at, s, false))) return rc;
             if ((rc = mat_vec(w.m[WGB_L_ATTN_OUTPUT]->view, m->xb, m->xb2, s))) return rc;

@@ -136,13 +136,20 @@ class Llama2:
     def x(self) -> torch.Tensor:
         return _device_view(_lib.load().wgb_llama2_x(self._h), self.config.dim)
 
+    def _cache(self, ptr: int) -> torch.Tensor:
+        """The library keeps a layer's cache head-major, [n_kv_heads][seq_len][head_size]; this returns it in the
+        reference's [seq_len][kv_dim] order (a copy)."""
+        c = self.config
+        kv = c.kv_dim // self.tp_size
+        heads = kv // c.head_size
+        t = _device_view(ptr, c.seq_len * kv).view(heads, c.seq_len, c.head_size)
+        return t.permute(1, 0, 2).reshape(c.seq_len, kv)
+
     def key_cache(self, layer: int) -> torch.Tensor:
-        kv = self.config.kv_dim // self.tp_size
-        return _device_view(_lib.load().wgb_llama2_key_cache(self._h, layer), self.config.seq_len * kv).view(self.config.seq_len, kv)
+        return self._cache(_lib.load().wgb_llama2_key_cache(self._h, layer))
 
     def value_cache(self, layer: int) -> torch.Tensor:
-        kv = self.config.kv_dim // self.tp_size
-        return _device_view(_lib.load().wgb_llama2_value_cache(self._h, layer), self.config.seq_len * kv).view(self.config.seq_len, kv)
+        return self._cache(_lib.load().wgb_llama2_value_cache(self._h, layer))
 
     def decode(self, prompt, n_gen: int, start_pos: int = 0) -> np.ndarray:
         """The token loop (forced prompt tokens, then greedy).  Host ids in, host ids out."""
