@@ -773,7 +773,10 @@ static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t nchunks_hi
     // `nchunks_hint`: chunks up to the furthest position this launch is expected to serve (performance only:
     // either kernel is correct for any position inside the cache).
     const bool multi = (uint64_t)nchunks_hint * heads > (uint64_t)per_sm_single * (uint32_t)sm_count();
-    if (multi && VC == 1) return launch_stream_any(a, nchunks, stream, pdl);
+    // Up to two query heads per KV head the streaming kernel is bandwidth-bound and wins; with more, the
+    // arithmetic per cache byte grows (8 heads: 4 FMA per byte) and its eight consumer warps per SM hide
+    // less latency than two resident blocks of the chunk-walking split kernel.
+    if (multi && VC == 1 && a.p.kv_mul <= 2) return launch_stream_any(a, nchunks, stream, pdl);
     uint32_t splits = nchunks;
     if (multi) {
         splits = (uint32_t)per_sm_multi * (uint32_t)sm_count() / heads;
