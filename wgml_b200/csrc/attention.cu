@@ -741,16 +741,12 @@ static int launch_stream(const AttnArgs &a, uint32_t nchunks, uint32_t n_kv, uin
     return WGB_OK;
 }
 
-// Long contexts with head sizes up to 128: all query heads of a KV head (up to 8) in one streaming block.
+// Long contexts with head sizes up to 128 and at most two query heads per KV head.
 static int launch_stream_any(const AttnArgs &a, uint32_t nchunks, cudaStream_t stream, bool pdl)
 {
     const uint32_t n_kv = a.p.n_heads / a.p.kv_mul;
-    const uint32_t qh = a.p.kv_mul >= 5 ? 8 : (a.p.kv_mul >= 3 ? 4 : (a.p.kv_mul >= 2 ? 2 : 1));
-    const uint32_t zg = (a.p.kv_mul + qh - 1) / qh;
-    if (qh == 8) return launch_stream<8>(a, nchunks, n_kv, zg, stream, pdl);
-    if (qh == 4) return launch_stream<4>(a, nchunks, n_kv, zg, stream, pdl);
-    if (qh == 2) return launch_stream<2>(a, nchunks, n_kv, zg, stream, pdl);
-    return launch_stream<1>(a, nchunks, n_kv, zg, stream, pdl);
+    if (a.p.kv_mul == 2) return launch_stream<2>(a, nchunks, n_kv, 1, stream, pdl);
+    return launch_stream<1>(a, nchunks, n_kv, 1, stream, pdl);
 }
 
 template <int QH, int VC>
