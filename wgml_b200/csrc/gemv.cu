@@ -410,10 +410,24 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     }
 
     // ------------------------------ consumers ------------------------------
+    // The norm weights are parameters, not products of the launch before: their (cold, HBM-latency) loads
+    // are issued ahead of the dependency wait and are in registers by the time the input can be read.
+    constexpr uint32_t XC = PRO == PRO_NONE ? 6 : 4;
+    constexpr uint32_t WC = PRO == PRO_NONE ? 1 : XC;
+    float4 wc[WC], bc[PRO == PRO_LN ? WC : 1];
+    if (PRO != PRO_NONE) {
+#pragma unroll
+        for (uint32_t i = 0; i < WC; i++) {
+            const uint32_t c = threadIdx.x + i * GEMV_CONS_THREADS;
+            if (c < K / 4) {
+                wc[i] = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + c);
+                if (PRO == PRO_LN) bc[i] = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + c);
+            }
+        }
+    }
     pdl_wait();
     // The thread's first XC chunks of the input are requested at once and stay in registers for the
-    // normalisation passes and the staging (one trip to L2 instead of up to three, one after the other).
-    constexpr uint32_t XC = 3;
+    // normalisation passes and the staging (one trip to L2 instead of several, one after the other).
     float4 xc[XC];
     const bool gather = PRO == PRO_RMS && a.peer_in.n != 0;
     if (gather) {
@@ -449,7 +463,21 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     }
     auto chunk = [&](uint32_t c) {
         const uint32_t i = c / GEMV_CONS_THREADS;   // c = threadIdx.x + i * GEMV_CONS_THREADS
-        return i == 0 ? xc[0] : (i == 1 ? xc[1] : (i == 2 ? xc[2] : load_chunk(c)));
+        if (i >= XC) return load_chunk(c);
+        float4 v = xc[0];
+#pragma unroll
+        for (uint32_t j = 1; j < XC; j++)
+            if (i == j) v = xc[j];
+        return v;
+    };
+    auto held_param = [&](const float4 *regs, const float *p, uint32_t c) {
+        const uint32_t i = c / GEMV_CONS_THREADS;
+        if (i >= WC) return __ldg(reinterpret_cast<const float4 *>(p) + c);
+        float4 v = regs[0];
+#pragma unroll
+        for (uint32_t j = 1; j < WC; j++)
+            if (i == j) v = regs[j];
+        return v;
     };
     float mean = 0.0f, scale = 1.0f;
     if (PRO == PRO_RMS) {
@@ -479,11 +507,11 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     stage_x<QT, GEMV_CONS_THREADS>(smem, K, [&](uint32_t c) {
         float4 v = chunk(c);
         if (PRO == PRO_RMS) {
-            const float4 w = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + c);
+            const float4 w = held_param(wc, a.norm_w, c);
             v.x = (v.x * scale) * w.x; v.y = (v.y * scale) * w.y; v.z = (v.z * scale) * w.z; v.w = (v.w * scale) * w.w;
         } else if (PRO == PRO_LN) {
-            const float4 w = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + c);
-            const float4 b = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + c);
+            const float4 w = held_param(wc, a.norm_w, c);
+            const float4 b = held_param(bc, a.norm_b, c);
             v.x = ((v.x - mean) * scale) * w.x + b.x; v.y = ((v.y - mean) * scale) * w.y + b.y;
             v.z = ((v.z - mean) * scale) * w.z + b.z; v.w = ((v.w - mean) * scale) * w.w + b.w;
         }
