@@ -362,6 +362,8 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
         const uint32_t sub = (uint32_t)lane >> 3, ul = (uint32_t)lane & 7;
         const uint32_t gmask = 0xffu << (8 * sub);
         uint32_t s = sub % nstage, phase = (sub / nstage) & 1;   // ring slot and parity of stage it0 + sub
+        float rms_scale = 1.0f;
+        bool have_scale = false;
         for (uint32_t it0 = 0; it0 < nst; it0 += nb, s += nb) {
             while (s >= nstage) {
                 s -= nstage;
@@ -377,11 +379,23 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             uint32_t ra = 0, rb = 0;
             if (c.on) unit_rows<EPI>(parts, nparts, n, ul, ra, rb);
             mbar_wait(done0 + 8 * s, phase, a.err, 3);
+            if (PRO == PRO_RMS && !have_scale) {
+                // every consumer warp wrote its sum of squares before its first arrival on a `done` barrier
+                float ss = 0.0f;
+#pragma unroll
+                for (int w = 0; w < GEMV_NCONS; w++) ss += red[w];
+                rms_scale = 1.0f / sqrtf(ss / (float)K + a.eps);
+                have_scale = true;
+            }
             float ya = 0.0f, yb = 0.0f;
             if (c.on) {
                 for (uint32_t k = 0; k < kp; k++) {
                     ya += part[s][k][ra];
                     yb += part[s][k][rb];
+                }
+                if (PRO == PRO_RMS) {
+                    ya *= rms_scale;
+                    yb *= rms_scale;
                 }
             }
             __syncwarp(gmask);
@@ -410,6 +424,13 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     }
 
     // ------------------------------ consumers ------------------------------
+    // What the task loop needs and the input does not decide is worked out while the launch before drains.
+    const uint32_t ncl = GEMV_NCONS / kp;                 // lanes of warps per column part
+    const XImage im = ximage_carve(QT, K, smem);
+    const uint32_t kunits = QT == WGB_F32 ? K : a.mat[0].bpr;   // what Step::active() compares against
+    const uint32_t nsteps = (K + step_cols<QT>() - 1) / step_cols<QT>();
+    const uint32_t kw = (uint32_t)warp % kp, cl = (uint32_t)warp / kp;
+    const uint32_t R = a.rrows;
     // The norm weights are parameters, not products of the launch before: their (cold, HBM-latency) loads
     // are issued ahead of the dependency wait and are in registers by the time the input can be read.
     constexpr uint32_t XC = PRO == PRO_NONE ? 6 : 4;
@@ -486,8 +507,11 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             float4 v = chunk(c);
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
-        ss = cons_sum(ss, red);
-        scale = 1.0f / sqrtf(ss / (float)K + a.eps);
+        // The scale is one factor for the whole vector, so it commutes with the dot products: the input is
+        // staged as x * w, the warps' sums of squares go to `red`, and the epilogue warp multiplies every
+        // finished dot product by 1 / sqrt(mean square + eps).  No block-wide reduction ahead of the staging.
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
     } else if (PRO == PRO_LN) {
         float s = 0.0f;
         for (uint32_t c = threadIdx.x; c < K / 4; c += GEMV_CONS_THREADS) {
@@ -508,7 +532,7 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
         float4 v = chunk(c);
         if (PRO == PRO_RMS) {
             const float4 w = held_param(wc, a.norm_w, c);
-            v.x = (v.x * scale) * w.x; v.y = (v.y * scale) * w.y; v.z = (v.z * scale) * w.z; v.w = (v.w * scale) * w.w;
+            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
         } else if (PRO == PRO_LN) {
             const float4 w = held_param(wc, a.norm_w, c);
             const float4 b = held_param(bc, a.norm_b, c);
@@ -519,13 +543,7 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     });
     cons_sync();
 
-    const uint32_t ncl = GEMV_NCONS / kp;                 // lanes of warps per column part
     if ((uint32_t)warp >= kp * ncl) return;               // warps left over when 16 % kp != 0
-    const XImage im = ximage_carve(QT, K, smem);
-    const uint32_t kunits = QT == WGB_F32 ? K : a.mat[0].bpr;   // what Step::active() compares against
-    const uint32_t nsteps = (K + step_cols<QT>() - 1) / step_cols<QT>();
-    const uint32_t kw = (uint32_t)warp % kp, cl = (uint32_t)warp / kp;
-    const uint32_t R = a.rrows;
     typename S::X x;
     uint32_t held = ~0u;   // column step whose part of the input is in `x`
 
