@@ -96,6 +96,21 @@ int wgb_gemv_quant(const wgb_quant_matrix *m, const float *d_v, float *d_out, vo
 int wgb_gemv_quant_raw(int qtype, const void *d_blocks, size_t nrows, size_t ncols, const float *d_v,
                        float *d_out, void *stream);
 
+/* The same operator (GemvQuant::dispatch, ops/gemv_quant.rs:241-348) for Q4_K on the tcgen05 tensor-core
+ * path: weights kept tile-major (128 rows x one 256-column super-block per bulk copy), nibbles unpacked to
+ * bytes in shared memory, eight kind::i8 MMAs per tile and super-block against the three byte digits of
+ * the input, accumulators read back from tensor memory one lane per row.  nrows a multiple of 128, ncols a
+ * multiple of 256 up to 4096.  Same results as wgb_gemv_quant within f32 rounding.  Measured slower than
+ * wgb_gemv_quant for a single input vector (an MMA pays for loading its 128-row operand whatever the
+ * number of input columns); the models do not use it. */
+typedef struct wgb_q4k_tiles wgb_q4k_tiles;
+int wgb_q4k_tiles_create(const void *h_blocks, size_t nrows, size_t ncols, void *stream, wgb_q4k_tiles **out);
+int wgb_q4k_tiles_destroy(wgb_q4k_tiles *m);
+int wgb_gemv_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, float *d_out, void *stream);
+/* Waits for the device and returns WGB_ERR_TIMEOUT if a bounded wait inside a matrix-vector kernel has
+ * expired since the last report (stand-alone launches are asynchronous and cannot say so themselves). */
+int wgb_device_status(void);
+
 /* ---- normalisation, activations, elementwise ---- */
 
 /* RmsNorm::dispatch (ops/rms_norm.rs:24-53, rms_norm.wgsl:58-67), RmsNormConfig::nudge_factor

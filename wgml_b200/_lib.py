@@ -76,6 +76,10 @@ SIGNATURES = {
     "wgb_quant_matrix_dequantize_rows": (_i, [_vp, _sz, _sz, _vp, _vp]),
     "wgb_gemv_quant": (_i, [_vp, _vp, _vp, _vp]),
     "wgb_gemv_quant_raw": (_i, [_i, _vp, _sz, _sz, _vp, _vp, _vp]),
+    "wgb_q4k_tiles_create": (_i, [_vp, _sz, _sz, _vp, C.POINTER(_vp)]),
+    "wgb_q4k_tiles_destroy": (_i, [_vp]),
+    "wgb_gemv_q4k_tiles": (_i, [_vp, _vp, _vp, _vp]),
+    "wgb_device_status": (_i, []),
     "wgb_rms_norm": (_i, [_vp, _vp, _vp, _sz, _f, _vp]),
     "wgb_layernorm": (_i, [_vp, _vp, _sz, _vp]),
     "wgb_rope": (_i, [_i, C.POINTER(RopeConfig), _vp, _sz, _vp, _sz, _vp]),

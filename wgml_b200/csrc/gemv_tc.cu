@@ -1,0 +1,463 @@
+// Q4_K matrix-vector product on the fifth-generation tensor cores (tcgen05.mma kind::i8, accumulators in
+// tensor memory).  Same operator as GemvQuant::dispatch (crates/wgml/src/ops/gemv_quant.rs:241-348) for
+// Q4_K matrices whose row count is a multiple of 128 and whose column count is a multiple of 256 up to
+// TC_MAX_K; the weights are kept tile-major so that one bulk copy brings one super-block column of 128 rows.
+//
+// Decomposition.  The input vector is quantised once per block into three signed byte digits per element
+// with one power-of-two exponent per 32 columns (the same fixed-point image as the dp4a kernel, 23 bits).
+// For a tile of 128 rows and one super-block column (256 columns) the worker threads unpack the nibbles to
+// unsigned bytes in shared memory (A operand, 128 x 256, K-major canonical layout without swizzle), and one
+// thread issues eight MMAs, one per 32-column sub-block: D[128 rows x 16] = A[128 x 32] * B[32 x 16], where
+// columns 0..2 of B are the digits (columns 3..7 zero, 8..15 alias 0..7).  Worker thread r reads row r of
+// the eight results from tensor memory and applies, in FP32, the digit weights, the group exponent, the
+// six-bit sub-block scale and the min term (get_scale_min_k4, crates/wgml/src/quantization.rs:381-389).
+//
+// Pipeline per block: warp 0 streams (tile, column) units into a ring with bulk copies; warp 1 owns the
+// tensor memory allocation and issues the MMAs; eight worker warps form two groups that take alternate
+// units, so that one group unpacks while the other group's MMAs and read-back run.
+// Every wait is bounded; the first that expires records a code and every loop of the block winds down.
+#include "kernels.h"
+#include "async_copy.cuh"
+#include "gemv_core.cuh"
+
+namespace wgb {
+
+constexpr uint32_t TC_TILE_ROWS = 128;
+constexpr uint32_t TC_UNIT_BYTES = TC_TILE_ROWS * 144;        // one super-block column of a tile, raw
+constexpr uint32_t TC_A_BYTES = TC_TILE_ROWS * 256;           // the same, unpacked to bytes
+constexpr uint32_t TC_MAX_K = 4096;
+constexpr uint32_t TC_RING = 6;
+constexpr uint32_t TC_GROUPS = 2;
+constexpr uint32_t TC_WORKER_WARPS = 4 * TC_GROUPS;
+constexpr uint32_t TC_NT = 32 * (2 + TC_WORKER_WARPS);
+constexpr uint32_t TC_PARTS = 2;                              // a unit goes through in parts of 8 / TC_PARTS sub-blocks
+constexpr uint32_t TC_AHEAD = 1;                              // parts unpacked ahead of the one being finished
+constexpr uint32_t TC_CP = 4 / TC_PARTS;                      // 32-byte chunks (pairs of sub-blocks) per part
+constexpr uint32_t TC_TMEM_COLS = 256;                        // 128 per group: eight results of 16 columns
+
+// shared-memory map (dynamic, 1024-byte aligned by the launch)
+constexpr uint32_t TC_OFF_B = 0;                               // digits: K / 16 core matrices of 128 bytes
+constexpr uint32_t TC_OFF_E = TC_OFF_B + TC_MAX_K * 8;         // K / 32 exponents (odd ones carry the 1/16 of high nibbles)
+constexpr uint32_t TC_OFF_S = TC_OFF_E + TC_MAX_K / 32 * 4;    // K / 32 sums of the inputs
+constexpr uint32_t TC_OFF_A = TC_OFF_S + TC_MAX_K / 32 * 4;    // TC_GROUPS operand buffers
+constexpr uint32_t TC_OFF_RING = TC_OFF_A + TC_GROUPS * TC_A_BYTES;
+constexpr uint32_t TC_SMEM = TC_OFF_RING + TC_RING * TC_UNIT_BYTES;
+static_assert(TC_OFF_A % 1024 == 0 && TC_OFF_RING % 1024 == 0, "operand buffers on 1 KB boundaries");
+static_assert(TC_SMEM <= 220 * 1024, "shared memory budget");
+
+struct TcArgs {
+    const uint8_t *w;     // tile-major blocks: [tile][column][128 rows][144 bytes]
+    const float *x;
+    float *out;
+    uint32_t nrows, K;
+    uint32_t *err;
+};
+
+// 64-bit shared-memory operand descriptor, no swizzle, K-major operand: start address, the byte distance
+// between core matrices (8 rows x 16 bytes) adjacent along K ("leading" field) and the distance between
+// those adjacent along the rows ("stride" field).  Checked against the dp4a kernel on the device.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((leading_bytes & 0x3ffffu) >> 4) << 16;
+    d |= (uint64_t)((stride_bytes & 0x3ffffu) >> 4) << 32;
+    d |= (uint64_t)1 << 46;   // descriptor version of this architecture
+    return d;
+}
+// The same for a K-major operand in the 128-byte swizzled layout: rows of 128 bytes, groups of 8 rows
+// (1024 bytes, `group_bytes` apart), the 16-byte chunks of row i stored at chunk index ^ (i % 8).  A step
+// along K inside the 128 bytes is a plain byte offset on the start address (tile base on a 1 KB boundary).
+__device__ __forceinline__ uint64_t tc_smem_desc_sw128(uint32_t addr, uint32_t group_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((group_bytes & 0x3ffffu) >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;   // 128-byte swizzle
+    return d;
+}
+
+// kind::i8 instruction descriptor: D s32, A u8, B s8, both K-major, M = 128, N = 16.
+__device__ __forceinline__ uint32_t tc_idesc()
+{
+    return (2u << 4) | (0u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.u32 p, 0, 0;\n\t"   // do not accumulate: D = A * B
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld4(uint32_t taddr, int (&v)[4])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+// Bounded wait that also gives up when another thread of the block already has.
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *dead, uint32_t *err, uint32_t code)
+{
+    for (uint32_t i = 0; i < ASYNC_WAIT_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *dead) return false;
+    }
+    *dead = 1;
+    if (err) atomicExch(err, code);
+    return false;
+}
+
+// Unsigned byte k of a word as f32: the byte is placed in the mantissa of 2^23.
+__device__ __forceinline__ float byte2f(uint32_t w, int k)
+{
+    return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7440 + k)) - 8388608.0f;
+}
+
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Fixed-point image of the input: thread g quantises the 32 inputs of group g.
+__device__ __forceinline__ void tc_stage_group(uint8_t *smem, const float *x, uint32_t g)
+{
+    float v[32];
+    const float4 *src = reinterpret_cast<const float4 *>(x + 32 * g);
+    float m = 0.0f, sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float4 q = __ldcg(src + i);
+        v[4 * i] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(q.x), fabsf(q.y)), fmaxf(fabsf(q.z), fabsf(q.w))));
+        sum += (q.x + q.y) + (q.z + q.w);
+    }
+    // |v| < 2^(ex - 126), so X = v * 2^(148 - ex) stays within +-2^22 after rounding
+    uint32_t ex = (__float_as_uint(m) >> 23) & 0xffu;
+    ex = ex < 24u ? 24u : (ex > 253u ? 253u : ex);
+    const float up = __uint_as_float((275u - ex) << 23), down = __uint_as_float((ex - 21u) << 23);
+    uint32_t dig[3][8];
+#pragma unroll
+    for (int wd = 0; wd < 8; wd++) {
+        uint32_t d0 = 0, d1 = 0, d2 = 0;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            // round to nearest even through the 1.5 * 2^23 offset; with 0x8080 added, bytes 0 and 1 are
+            // the signed digits plus 128 and byte 2 is the signed top digit
+            const uint32_t y = __float_as_uint(fmaf(v[4 * wd + b], up, 12582912.0f)) - 0x4b400000u + 0x8080u;
+            d0 |= ((y & 0xffu) ^ 0x80u) << (8 * b);
+            d1 |= (((y >> 8) & 0xffu) ^ 0x80u) << (8 * b);
+            d2 |= ((y >> 16) & 0xffu) << (8 * b);
+        }
+        dig[0][wd] = d0; dig[1][wd] = d1; dig[2][wd] = d2;
+    }
+    const uint32_t base = smem_addr(smem + TC_OFF_B) + (2 * g) * 128;   // two 16-column core matrices per group
+#pragma unroll
+    for (int core = 0; core < 2; core++)
+#pragma unroll
+        for (int n = 0; n < 3; n++)
+            sts128(base + core * 128 + n * 16, dig[n][4 * core], dig[n][4 * core + 1], dig[n][4 * core + 2], dig[n][4 * core + 3]);
+    reinterpret_cast<float *>(smem + TC_OFF_E)[g] = (g & 1) ? down * 0.0625f : down;
+    reinterpret_cast<float *>(smem + TC_OFF_S)[g] = sum;
+}
+
+__global__ void __launch_bounds__(TC_NT, 1) gemv_q4k_tc_kernel(const __grid_constant__ TcArgs a)
+{
+    extern __shared__ uint8_t tc_smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[TC_GROUPS][2 * (TC_RING / TC_GROUPS) + 2 * TC_PARTS];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ uint32_t dead_flag;
+    uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    volatile uint32_t *dead = &dead_flag;
+    constexpr uint32_t SLOTS = TC_RING / TC_GROUPS;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t nkb = a.K / 256, ntiles = a.nrows / TC_TILE_ROWS;
+    auto bar_full = [&](uint32_t g, uint32_t s) { return smem_addr(&bars[g][s]); };
+    auto bar_empty = [&](uint32_t g, uint32_t s) { return smem_addr(&bars[g][SLOTS + s]); };
+    auto bar_ready = [&](uint32_t g, uint32_t p) { return smem_addr(&bars[g][2 * SLOTS + p]); };
+    auto bar_done = [&](uint32_t g, uint32_t p) { return smem_addr(&bars[g][2 * SLOTS + TC_PARTS + p]); };
+    // tiles of group g: blockIdx.x + (2 i + g) * gridDim.x
+    auto tiles_of = [&](uint32_t g) {
+        const uint32_t first = blockIdx.x + g * gridDim.x;
+        return first < ntiles ? (ntiles - first + 2 * gridDim.x - 1) / (2 * gridDim.x) : 0u;
+    };
+
+    if (threadIdx.x == 0) {
+        dead_flag = 0;
+        for (uint32_t g = 0; g < TC_GROUPS; g++) {
+            for (uint32_t s = 0; s < SLOTS; s++) {
+                mbar_init(bar_full(g, s), 1);
+                mbar_init(bar_empty(g, s), 128);
+            }
+            for (uint32_t p = 0; p < TC_PARTS; p++) {
+                mbar_init(bar_ready(g, p), 128);
+                mbar_init(bar_done(g, p), 1);
+            }
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // zero the digit operand (rows 3..7 of every core matrix stay zero)
+    for (uint32_t i = threadIdx.x; i < TC_MAX_K * 8 / 16; i += TC_NT) reinterpret_cast<uint4 *>(smem + TC_OFF_B)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            const uint32_t n0 = tiles_of(0), n1 = tiles_of(1);
+            uint32_t seq[TC_GROUPS] = { 0, 0 };
+            bool ok = true;
+            for (uint32_t i = 0; i < n0 && ok; i++) {
+                for (uint32_t kb = 0; kb < nkb && ok; kb++) {
+                    for (uint32_t g = 0; g < TC_GROUPS && ok; g++) {
+                        if (i >= (g == 0 ? n0 : n1)) continue;
+                        const uint32_t tile = blockIdx.x + (2 * i + g) * gridDim.x;
+                        const uint32_t n = seq[g]++, s = n % SLOTS, round = n / SLOTS;
+                        if (round) ok = tc_wait(bar_empty(g, s), (round - 1) & 1, dead, a.err, 11);
+                        if (!ok) break;
+                        mbar_expect_tx(bar_full(g, s), TC_UNIT_BYTES);
+                        bulk_copy_g2s(smem_addr(smem + TC_OFF_RING) + (g * SLOTS + s) * TC_UNIT_BYTES,
+                                      a.w + ((size_t)tile * nkb + kb) * TC_UNIT_BYTES, TC_UNIT_BYTES, bar_full(g, s));
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issue ------------------------------
+        // A unit goes through in two halves of four sub-blocks, each with its own operand buffer,
+        // accumulator columns and barriers, so that a group unpacks one half while the other multiplies.
+        // The thread serves whichever group has its next half ready.
+        if (lane == 0) {
+            const uint32_t idesc = tc_idesc();
+            const uint32_t total[TC_GROUPS] = { TC_PARTS * tiles_of(0) * nkb, TC_PARTS * tiles_of(1) * nkb };
+            uint32_t h[TC_GROUPS] = { 0, 0 };
+            uint32_t idle = 0;
+            while ((h[0] < total[0] || h[1] < total[1]) && idle < ASYNC_WAIT_LIMIT) {
+                bool served = false;
+#pragma unroll
+                for (uint32_t g = 0; g < TC_GROUPS; g++) {
+                    if (h[g] >= total[g]) continue;
+                    const uint32_t n = h[g] / TC_PARTS, p = h[g] % TC_PARTS, kb = n % nkb;
+                    if (!mbar_try_wait(bar_ready(g, p), n & 1)) continue;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t abuf = smem_addr(smem + TC_OFF_A) + g * TC_A_BYTES;
+                    const uint32_t bbuf = smem_addr(smem + TC_OFF_B) + kb * (256 / 16) * 128;
+#pragma unroll
+                    for (uint32_t q = 0; q < 2 * TC_CP; q++) {
+                        const uint32_t j = 2 * TC_CP * p + q;
+                        tc_mma(tmem_base + g * 128 + 16 * j, tc_smem_desc_sw128(abuf + (j >> 2) * 16384 + (j & 3) * 32, 1024),
+                               tc_smem_desc(bbuf + j * 256, 128, 0), idesc);
+                    }
+                    tc_commit(bar_done(g, p));
+                    h[g]++;
+                    served = true;
+                }
+                idle = served ? 0 : idle + 1;
+                if (!served && (idle & 255u) == 255u && *dead) break;
+            }
+            if (idle >= ASYNC_WAIT_LIMIT) {
+                *dead = 1;
+                if (a.err) atomicExch(a.err, 12u);
+            }
+        }
+    } else {
+        // ------------------------------ workers ------------------------------
+        const uint32_t w = warp - 2, g = w / 4, quarter = warp & 3, r = quarter * 32 + lane;
+        // the input image, once per block (both groups take part)
+        for (uint32_t grp = threadIdx.x - 64; grp < a.K / 32; grp += 32 * TC_WORKER_WARPS) tc_stage_group(smem, a.x, grp);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_WORKER_WARPS) : "memory");
+        const float *e = reinterpret_cast<const float *>(smem + TC_OFF_E), *xs = reinterpret_cast<const float *>(smem + TC_OFF_S);
+        const uint32_t abuf = smem_addr(smem + TC_OFF_A) + g * TC_A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + g * 128;
+        const uint32_t ring = smem_addr(smem + TC_OFF_RING) + g * SLOTS * TC_UNIT_BYTES + r * 144;
+        // Parts h = 4 n + p of the group's units n = 0, 1, ... (unit n = column n % nkb of the group's tile
+        // n / nkb; part p = 32-byte chunk p of every row = sub-blocks 2p and 2p + 1).  Step s unpacks part s
+        // and then finishes part s - TC_AHEAD, whose MMAs have had the steps in between to complete.
+        const uint32_t total = TC_PARTS * tiles_of(g) * nkb;
+        float rowacc = 0.0f;
+        bool ok = true;
+        for (uint32_t sidx = 0; sidx < total + TC_AHEAD && ok; sidx++) {
+            if (sidx < total) {
+                const uint32_t n = sidx / TC_PARTS, p = sidx % TC_PARTS, slot = n % SLOTS;
+                if (p == 0) ok = tc_wait(bar_full(g, slot), (n / SLOTS) & 1, dead, a.err, 13);
+                if (!ok) break;
+                const uint32_t raw = ring + slot * TC_UNIT_BYTES;
+                // nibbles -> bytes: low nibbles are sub-block 2c, high nibbles (left as 16 * code) sub-block
+                // 2c + 1; sub-block j lies in K panel j / 4 (16 KB) at bytes 32 (j % 4) .. + 31 of the row
+#pragma unroll
+                for (uint32_t cc = 0; cc < TC_CP; cc++) {
+                    const uint32_t c = TC_CP * p + cc;
+#pragma unroll
+                    for (uint32_t core = 0; core < 2; core++) {
+                        const uint4 q = lds128(raw + 16 + 32 * c + 16 * core);
+                        const uint32_t jl = 2 * c, jh = 2 * c + 1;
+                        sts128(abuf + (jl >> 2) * 16384 + (((2 * (jl & 3) + core) ^ (r & 7)) << 4),
+                               q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
+                        sts128(abuf + (jh >> 2) * 16384 + (((2 * (jh & 3) + core) ^ (r & 7)) << 4),
+                               q.x & 0xf0f0f0f0u, q.y & 0xf0f0f0f0u, q.z & 0xf0f0f0f0u, q.w & 0xf0f0f0f0u);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(bar_ready(g, p));
+            }
+            if (sidx >= TC_AHEAD) {
+                const uint32_t h = sidx - TC_AHEAD, n = h / TC_PARTS, p = h % TC_PARTS, slot = n % SLOTS;
+                const uint32_t kb = n % nkb;
+                const uint32_t raw = ring + slot * TC_UNIT_BYTES;
+                const uint4 hdr = lds128(raw);
+                const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, m_lo = hdr.z & 0x3f3f3f3fu;
+                const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+                const uint32_t m_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+                const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+                ok = tc_wait(bar_done(g, p), n & 1, dead, a.err, 14);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                int d[2 * TC_CP][4];
+#pragma unroll
+                for (uint32_t q = 0; q < 2 * TC_CP; q++) tc_ld4(taddr + 16 * (2 * TC_CP * p + q), d[q]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                float acc = 0.0f, neg = 0.0f;
+#pragma unroll
+                for (uint32_t cc = 0; cc < TC_CP; cc++) {
+                    // six-bit scales and mins of sub-blocks 2c, 2c + 1 in the low bytes of a word each
+                    const uint32_t c = TC_CP * p + cc, sh = (c & 1) * 16;
+                    const uint32_t scw = (c < 2 ? sc_lo : sc_hi) >> sh, mw = (c < 2 ? m_lo : m_hi) >> sh;
+                    const float2 e2 = reinterpret_cast<const float2 *>(e)[kb * 4 + c], s2 = reinterpret_cast<const float2 *>(xs)[kb * 4 + c];
+                    // |digit sum| <= 32 * 240 * 128 < 2^22: the offset conversion is exact
+                    const float f0 = fmaf(i2f(d[2 * cc][2]), 65536.0f, fmaf(i2f(d[2 * cc][1]), 256.0f, i2f(d[2 * cc][0])));
+                    const float f1 = fmaf(i2f(d[2 * cc + 1][2]), 65536.0f, fmaf(i2f(d[2 * cc + 1][1]), 256.0f, i2f(d[2 * cc + 1][0])));
+                    acc = fmaf(f0, byte2f(scw, 0) * e2.x, acc);
+                    acc = fmaf(f1, byte2f(scw, 1) * e2.y, acc);
+                    neg = fmaf(byte2f(mw, 0), s2.x, neg);
+                    neg = fmaf(byte2f(mw, 1), s2.y, neg);
+                }
+                rowacc += dm.x * acc - dm.y * neg;
+                if (p == TC_PARTS - 1) {
+                    mbar_arrive(bar_empty(g, slot));
+                    if (kb == nkb - 1) {
+                        const uint32_t tile = blockIdx.x + (2 * (n / nkb) + g) * gridDim.x;
+                        a.out[(size_t)tile * TC_TILE_ROWS + r] = rowacc;
+                        rowacc = 0.0f;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
+// Raw row-major Q4_K blocks -> [tile][column][row in tile][144 bytes].  One thread per 16 bytes.
+__global__ void q4k_tile_major_kernel(const uint4 *__restrict__ raw, uint4 *__restrict__ tiled, uint32_t nrows, uint32_t nkb)
+{
+    const size_t total = (size_t)nrows * nkb * 9;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t part = (uint32_t)(i % 9);
+        const size_t blk = i / 9;
+        const uint32_t kb = (uint32_t)(blk % nkb), row = (uint32_t)(blk / nkb);
+        const uint32_t tile = row / TC_TILE_ROWS, r = row % TC_TILE_ROWS;
+        tiled[(((size_t)tile * nkb + kb) * TC_TILE_ROWS + r) * 9 + part] = raw[i];
+    }
+}
+
+}  // namespace wgb
+
+using namespace wgb;
+
+struct wgb_q4k_tiles {
+    uint8_t *w;
+    uint32_t nrows, ncols;
+};
+
+WGB_EXPORT int wgb_q4k_tiles_create(const void *h_blocks, size_t nrows, size_t ncols, void *stream, wgb_q4k_tiles **out)
+{
+    WGB_REQUIRE(h_blocks && out, "null argument");
+    WGB_REQUIRE(nrows > 0 && nrows % TC_TILE_ROWS == 0, "the tensor-core path wants a multiple of %u rows, got %zu", TC_TILE_ROWS, nrows);
+    WGB_REQUIRE(ncols > 0 && ncols % 256 == 0 && ncols <= TC_MAX_K, "the tensor-core path wants a multiple of 256 columns up to %u, got %zu", TC_MAX_K, ncols);
+    int rc = gemv_global_init();
+    if (rc) return rc;
+    static bool attr_done = false;
+    if (!attr_done) {
+        WGB_CUDA(cudaFuncSetAttribute(gemv_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM + 1024)));
+        attr_done = true;
+    }
+    const size_t bytes = nrows * (ncols / 256) * 144;
+    cudaStream_t st = as_stream(stream);
+    wgb_q4k_tiles *m = new (std::nothrow) wgb_q4k_tiles();
+    if (!m) return fail(WGB_ERR_INVALID, "out of host memory");
+    uint8_t *d_raw = nullptr;
+    cudaError_t e = cudaMalloc((void **)&m->w, bytes);
+    if (e == cudaSuccess) e = cudaMalloc((void **)&d_raw, bytes);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_raw, h_blocks, bytes, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) {
+        q4k_tile_major_kernel<<<(unsigned)((bytes / 16 + 255) / 256 < 65535 * 16 ? (bytes / 16 + 255) / 256 : 65535 * 16), 256, 0, st>>>((const uint4 *)d_raw, (uint4 *)m->w, (uint32_t)nrows, (uint32_t)(ncols / 256));
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (d_raw) cudaFree(d_raw);
+    if (e != cudaSuccess) {
+        if (m->w) cudaFree(m->w);
+        delete m;
+        return cuda_fail(e, "Q4_K tile-major upload");
+    }
+    m->nrows = (uint32_t)nrows;
+    m->ncols = (uint32_t)ncols;
+    *out = m;
+    return WGB_OK;
+}
+
+
+WGB_EXPORT int wgb_q4k_tiles_destroy(wgb_q4k_tiles *m)
+{
+    if (!m) return WGB_OK;
+    cudaFree(m->w);
+    delete m;
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_gemv_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, float *d_out, void *stream)
+{
+    WGB_REQUIRE(m && d_v && d_out, "null argument");
+    TcArgs a = {};
+    a.w = m->w;
+    a.x = d_v;
+    a.out = d_out;
+    a.nrows = m->nrows;
+    a.K = m->ncols;
+    a.err = gemv_status_word();
+    const uint32_t ntiles = m->nrows / TC_TILE_ROWS;
+    const uint32_t grid = ntiles < (uint32_t)sm_count() ? ntiles : (uint32_t)sm_count();
+    gemv_q4k_tc_kernel<<<grid, TC_NT, TC_SMEM + 1024, as_stream(stream)>>>(a);
+    WGB_LAUNCH_CHECK("gemv_q4k_tc_kernel");
+    return WGB_OK;
+}
+
+// Waits for the device and reports whether a bounded wait inside any matrix-vector kernel has expired since
+// the last report (stand-alone launches are asynchronous and cannot return that themselves).
+WGB_EXPORT int wgb_device_status(void)
+{
+    WGB_CUDA(cudaDeviceSynchronize());
+    return gemv_check_status();
+}

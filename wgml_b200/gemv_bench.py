@@ -1,7 +1,7 @@
 """Quantised matrix-vector microbenchmark through the C ABI (`wgb_gemv_quant`).
 
     python -m wgml_b200.gemv_bench [--qtypes q4_k,q6_k,q8_0] [--shapes 4096x4096,...] [--reps 100]
-                                   [--eager N] [--json]
+                                   [--eager N] [--json] [--tensor]
 
 The shapes and value distributions are those of wgml-bench's GEMV sweep restricted to the transformer
 shapes of a 7B model (crates/wgml-bench/src/main.rs:186-248 times `GemvQuant::dispatch` on random block
@@ -12,6 +12,7 @@ times over), so each one streams from HBM.  `--reps` launches are captured in on
 is replayed three times between CUDA events.  The figure printed is algorithmic bytes
 (rows * cols * bytes-per-weight of the GGUF format + 4 * cols + 4 * rows) per second.
 `--eager N` instead issues N plain launches and exits; it exists for profilers, which want few launches.
+`--tensor` times the tcgen05 path (`wgb_gemv_q4k_tiles`, Q4_K, up to 4096 columns) instead of `wgb_gemv_quant`.
 """
 from __future__ import annotations
 
@@ -28,12 +29,14 @@ QT = {"q8_0": synth.Q8_0, "q4_k": synth.Q4_K, "q6_k": synth.Q6_K, "f32": synth.F
 BPE = {synth.F32: 4.0, synth.Q8_0: 34 / 32, synth.Q4_K: 144 / 256, synth.Q6_K: 210 / 256}
 
 
-def run(qtypes, shapes, reps, eager, peak_gbs):
+def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False):
     lib = _lib.load()
     out = []
     for name in qtypes:
         qt = QT[name]
         for (n, k) in shapes:
+            if tensor and (qt != synth.Q4_K or k > 4096 or n % 128):
+                continue
             nbytes = n * k * BPE[qt]
             ncopy = max(2, int(np.ceil(400e6 / nbytes)))
             rng = np.random.default_rng(1)
@@ -44,25 +47,29 @@ def run(qtypes, shapes, reps, eager, peak_gbs):
             mats = []
             for _ in range(ncopy):
                 h = C.c_void_p()
-                _lib.check(lib.wgb_quant_matrix_create(qt, raw.ctypes.data, n, k, None, C.byref(h)))
+                if tensor:
+                    _lib.check(lib.wgb_q4k_tiles_create(raw.ctypes.data, n, k, None, C.byref(h)))
+                else:
+                    _lib.check(lib.wgb_quant_matrix_create(qt, raw.ctypes.data, n, k, None, C.byref(h)))
                 mats.append(h)
+            gemv = lib.wgb_gemv_q4k_tiles if tensor else lib.wgb_gemv_quant
             x = torch.randn(k, device="cuda")
             y = torch.zeros(n, device="cuda")
             st = torch.cuda.current_stream().cuda_stream
             if eager:
                 for it in range(eager):
-                    _lib.check(lib.wgb_gemv_quant(mats[it % ncopy], x.data_ptr(), y.data_ptr(), st))
+                    _lib.check(gemv(mats[it % ncopy], x.data_ptr(), y.data_ptr(), st))
                 torch.cuda.synchronize()
                 out.append({"qtype": name, "rows": n, "cols": k, "eager_launches": eager})
             else:
                 for it in range(20):
-                    _lib.check(lib.wgb_gemv_quant(mats[it % ncopy], x.data_ptr(), y.data_ptr(), st))
+                    _lib.check(gemv(mats[it % ncopy], x.data_ptr(), y.data_ptr(), st))
                 torch.cuda.synchronize()
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     st2 = torch.cuda.current_stream().cuda_stream
                     for it in range(reps):
-                        _lib.check(lib.wgb_gemv_quant(mats[it % ncopy], x.data_ptr(), y.data_ptr(), st2))
+                        _lib.check(gemv(mats[it % ncopy], x.data_ptr(), y.data_ptr(), st2))
                 g.replay()
                 torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -73,10 +80,10 @@ def run(qtypes, shapes, reps, eager, peak_gbs):
                 torch.cuda.synchronize()
                 us = e0.elapsed_time(e1) * 1e3 / (3 * reps)
                 alg = nbytes + 4 * k + 4 * n
-                out.append({"qtype": name, "rows": n, "cols": k, "us": us, "bytes": alg, "gbs": alg / us / 1e3,
+                out.append({"qtype": name + ("/tcgen05" if tensor else ""), "rows": n, "cols": k, "us": us, "bytes": alg, "gbs": alg / us / 1e3,
                             "frac_of_measured_peak": alg / us / 1e3 / peak_gbs, "copies": ncopy})
             for h in mats:
-                lib.wgb_quant_matrix_destroy(h)
+                (lib.wgb_q4k_tiles_destroy if tensor else lib.wgb_quant_matrix_destroy)(h)
     return out
 
 
@@ -88,18 +95,19 @@ def main():
     ap.add_argument("--eager", type=int, default=0)
     ap.add_argument("--peak-gbs", type=float, default=6550.7, help="HBM copy bandwidth the fraction is taken of")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--tensor", action="store_true", help="time the tcgen05 path (Q4_K, up to 4096 columns)")
     a = ap.parse_args()
     shapes = [tuple(int(v) for v in s.split("x")) for s in a.shapes.split(",")]
-    res = run(a.qtypes.split(","), shapes, a.reps, a.eager, a.peak_gbs)
+    res = run(a.qtypes.split(","), shapes, a.reps, a.eager, a.peak_gbs, a.tensor)
     if a.json:
         print(json.dumps(res))
         return
     for r in res:
         if "us" in r:
-            print(f"{r['qtype']:5s} {r['rows']:6d}x{r['cols']:<6d} {r['us']:8.2f} us  {r['gbs']:8.1f} GB/s  "
+            print(f"{r['qtype']:12s} {r['rows']:6d}x{r['cols']:<6d} {r['us']:8.2f} us  {r['gbs']:8.1f} GB/s  "
                   f"{100 * r['frac_of_measured_peak']:5.1f}% of {a.peak_gbs:.0f} GB/s")
         else:
-            print(f"{r['qtype']:5s} {r['rows']:6d}x{r['cols']:<6d} {r['eager_launches']} eager launches")
+            print(f"{r['qtype']:12s} {r['rows']:6d}x{r['cols']:<6d} {r['eager_launches']} eager launches")
 
 
 if __name__ == "__main__":

@@ -115,6 +115,38 @@ class GemvQuant:
         check(_lib.load().wgb_gemv_quant_raw(qtype, raw.data_ptr(), nrows, ncols, _f32(v, "v"), _f32(out, "out"), _stream()))
 
 
+class Q4KTiles:
+    """A Q4_K matrix in the tile-major layout of the tensor-core matrix-vector kernel (nrows a multiple of
+    128, ncols a multiple of 256 up to 4096), built from raw GGUF blocks in host memory."""
+
+    def __init__(self, blocks, nrows: int, ncols: int):
+        require_device()
+        raw = np.ascontiguousarray(blocks).view(np.uint8).reshape(-1)
+        GpuQuantMatrix._check_size(Q4_K, raw.size, nrows, ncols)
+        self._h = C.c_void_p()
+        check(_lib.load().wgb_q4k_tiles_create(raw.ctypes.data, nrows, ncols, _stream(), C.byref(self._h)))
+        self.nrows, self.ncols = nrows, ncols
+
+    def gemv(self, out: torch.Tensor, v: torch.Tensor) -> None:
+        """GemvQuant::dispatch (crates/wgml/src/ops/gemv_quant.rs:241-348) on the tcgen05 path."""
+        if v.numel() != self.ncols or out.numel() != self.nrows:
+            raise WgbError(_lib.ERR_INVALID, "Gemv: dimension mismatch.")
+        check(_lib.load().wgb_gemv_q4k_tiles(self._h, _f32(v, "v"), _f32(out, "out"), _stream()))
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _lib.load().wgb_q4k_tiles_destroy(h)
+            except Exception:
+                pass
+
+
+def device_status() -> None:
+    """Waits for the device; raises if a bounded wait inside a matrix-vector kernel has expired."""
+    check(_lib.load().wgb_device_status())
+
+
 class RmsNormConfig:
     """RmsNormConfig (crates/wgml/src/ops/rms_norm.rs:17-21)."""
 
