@@ -13,8 +13,9 @@
 // six-bit sub-block scale and the min term (get_scale_min_k4, crates/wgml/src/quantization.rs:381-389).
 //
 // Pipeline per block: warp 0 streams (tile, column) units into a ring with bulk copies; warp 1 owns the
-// tensor memory allocation and issues the MMAs; eight worker warps form two groups that take alternate
-// units, so that one group unpacks while the other group's MMAs and read-back run.
+// tensor memory allocation and issues the MMAs; sixteen worker warps (four per quarter of the rows, one
+// 32-byte chunk of each row per thread) unpack unit n and then finish unit n - 1 while the MMAs of unit n
+// are issued and run (two operand buffers, two sets of accumulator columns).
 // Every wait is bounded; the first that expires records a code and every loop of the block winds down.
 #include "kernels.h"
 #include "async_copy.cuh"
@@ -27,20 +28,18 @@ constexpr uint32_t TC_UNIT_BYTES = TC_TILE_ROWS * 144;        // one super-block
 constexpr uint32_t TC_A_BYTES = TC_TILE_ROWS * 256;           // the same, unpacked to bytes
 constexpr uint32_t TC_MAX_K = 4096;
 constexpr uint32_t TC_RING = 6;
-constexpr uint32_t TC_GROUPS = 2;
-constexpr uint32_t TC_WORKER_WARPS = 4 * TC_GROUPS;
+constexpr uint32_t TC_WPQ = 4;                                // worker warps per quarter of the tile's rows
+constexpr uint32_t TC_CPT = 4 / TC_WPQ;                       // 32-byte chunks (pairs of sub-blocks) per thread
+constexpr uint32_t TC_WORKER_WARPS = 4 * TC_WPQ;
 constexpr uint32_t TC_NT = 32 * (2 + TC_WORKER_WARPS);
-constexpr uint32_t TC_PARTS = 2;                              // a unit goes through in parts of 8 / TC_PARTS sub-blocks
-constexpr uint32_t TC_AHEAD = 1;                              // parts unpacked ahead of the one being finished
-constexpr uint32_t TC_CP = 4 / TC_PARTS;                      // 32-byte chunks (pairs of sub-blocks) per part
-constexpr uint32_t TC_TMEM_COLS = 256;                        // 128 per group: eight results of 16 columns
+constexpr uint32_t TC_TMEM_COLS = 256;                        // 128 per unit in flight: eight results of 16 columns
 
 // shared-memory map (dynamic, 1024-byte aligned by the launch)
 constexpr uint32_t TC_OFF_B = 0;                               // digits: K / 16 core matrices of 128 bytes
 constexpr uint32_t TC_OFF_E = TC_OFF_B + TC_MAX_K * 8;         // K / 32 exponents (odd ones carry the 1/16 of high nibbles)
 constexpr uint32_t TC_OFF_S = TC_OFF_E + TC_MAX_K / 32 * 4;    // K / 32 sums of the inputs
-constexpr uint32_t TC_OFF_A = TC_OFF_S + TC_MAX_K / 32 * 4;    // TC_GROUPS operand buffers
-constexpr uint32_t TC_OFF_RING = TC_OFF_A + TC_GROUPS * TC_A_BYTES;
+constexpr uint32_t TC_OFF_A = TC_OFF_S + TC_MAX_K / 32 * 4;    // two operand buffers (units alternate)
+constexpr uint32_t TC_OFF_RING = TC_OFF_A + 2 * TC_A_BYTES;
 constexpr uint32_t TC_SMEM = TC_OFF_RING + TC_RING * TC_UNIT_BYTES;
 static_assert(TC_OFF_A % 1024 == 0 && TC_OFF_RING % 1024 == 0, "operand buffers on 1 KB boundaries");
 static_assert(TC_SMEM <= 220 * 1024, "shared memory budget");
@@ -174,36 +173,30 @@ __device__ __forceinline__ void tc_stage_group(uint8_t *smem, const float *x, ui
 __global__ void __launch_bounds__(TC_NT, 1) gemv_q4k_tc_kernel(const __grid_constant__ TcArgs a)
 {
     extern __shared__ uint8_t tc_smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[TC_GROUPS][2 * (TC_RING / TC_GROUPS) + 2 * TC_PARTS];
+    __shared__ __align__(8) unsigned long long bars[2 * TC_RING + 2];
+    __shared__ float rowpart[TC_WPQ][TC_TILE_ROWS];
     __shared__ uint32_t tmem_base_slot;
     __shared__ uint32_t dead_flag;
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
     volatile uint32_t *dead = &dead_flag;
-    constexpr uint32_t SLOTS = TC_RING / TC_GROUPS;
+
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t nkb = a.K / 256, ntiles = a.nrows / TC_TILE_ROWS;
-    auto bar_full = [&](uint32_t g, uint32_t s) { return smem_addr(&bars[g][s]); };
-    auto bar_empty = [&](uint32_t g, uint32_t s) { return smem_addr(&bars[g][SLOTS + s]); };
-    auto bar_ready = [&](uint32_t g, uint32_t p) { return smem_addr(&bars[g][2 * SLOTS + p]); };
-    auto bar_done = [&](uint32_t g, uint32_t p) { return smem_addr(&bars[g][2 * SLOTS + TC_PARTS + p]); };
-    // tiles of group g: blockIdx.x + (2 i + g) * gridDim.x
-    auto tiles_of = [&](uint32_t g) {
-        const uint32_t first = blockIdx.x + g * gridDim.x;
-        return first < ntiles ? (ntiles - first + 2 * gridDim.x - 1) / (2 * gridDim.x) : 0u;
-    };
+    auto bar_full = [&](uint32_t s) { return smem_addr(&bars[s]); };
+    auto bar_empty = [&](uint32_t s) { return smem_addr(&bars[TC_RING + s]); };
+    auto bar_done = [&](uint32_t u) { return smem_addr(&bars[2 * TC_RING + u]); };
+    // tiles of this block: blockIdx.x, blockIdx.x + gridDim.x, ...; unit n = column n % nkb of tile n / nkb
+    const uint32_t my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+    const uint32_t total = my_tiles * nkb;
 
     if (threadIdx.x == 0) {
         dead_flag = 0;
-        for (uint32_t g = 0; g < TC_GROUPS; g++) {
-            for (uint32_t s = 0; s < SLOTS; s++) {
-                mbar_init(bar_full(g, s), 1);
-                mbar_init(bar_empty(g, s), 128);
-            }
-            for (uint32_t p = 0; p < TC_PARTS; p++) {
-                mbar_init(bar_ready(g, p), 128);
-                mbar_init(bar_done(g, p), 1);
-            }
+        for (uint32_t s = 0; s < TC_RING; s++) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 32 * TC_WORKER_WARPS);
         }
+        mbar_init(bar_done(0), 1);
+        mbar_init(bar_done(1), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -220,125 +213,113 @@ __global__ void __launch_bounds__(TC_NT, 1) gemv_q4k_tc_kernel(const __grid_cons
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
-            const uint32_t n0 = tiles_of(0), n1 = tiles_of(1);
-            uint32_t seq[TC_GROUPS] = { 0, 0 };
             bool ok = true;
-            for (uint32_t i = 0; i < n0 && ok; i++) {
-                for (uint32_t kb = 0; kb < nkb && ok; kb++) {
-                    for (uint32_t g = 0; g < TC_GROUPS && ok; g++) {
-                        if (i >= (g == 0 ? n0 : n1)) continue;
-                        const uint32_t tile = blockIdx.x + (2 * i + g) * gridDim.x;
-                        const uint32_t n = seq[g]++, s = n % SLOTS, round = n / SLOTS;
-                        if (round) ok = tc_wait(bar_empty(g, s), (round - 1) & 1, dead, a.err, 11);
-                        if (!ok) break;
-                        mbar_expect_tx(bar_full(g, s), TC_UNIT_BYTES);
-                        bulk_copy_g2s(smem_addr(smem + TC_OFF_RING) + (g * SLOTS + s) * TC_UNIT_BYTES,
-                                      a.w + ((size_t)tile * nkb + kb) * TC_UNIT_BYTES, TC_UNIT_BYTES, bar_full(g, s));
-                    }
-                }
+            for (uint32_t n = 0; n < total && ok; n++) {
+                const uint32_t tile = blockIdx.x + (n / nkb) * gridDim.x, kb = n % nkb;
+                const uint32_t s = n % TC_RING, round = n / TC_RING;
+                if (round) ok = tc_wait(bar_empty(s), (round - 1) & 1, dead, a.err, 11);
+                if (!ok) break;
+                mbar_expect_tx(bar_full(s), TC_UNIT_BYTES);
+                bulk_copy_g2s(smem_addr(smem + TC_OFF_RING) + s * TC_UNIT_BYTES,
+                              a.w + ((size_t)tile * nkb + kb) * TC_UNIT_BYTES, TC_UNIT_BYTES, bar_full(s));
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issue ------------------------------
-        // A unit goes through in two halves of four sub-blocks, each with its own operand buffer,
-        // accumulator columns and barriers, so that a group unpacks one half while the other multiplies.
-        // The thread serves whichever group has its next half ready.
-        if (lane == 0) {
-            const uint32_t idesc = tc_idesc();
-            const uint32_t total[TC_GROUPS] = { TC_PARTS * tiles_of(0) * nkb, TC_PARTS * tiles_of(1) * nkb };
-            uint32_t h[TC_GROUPS] = { 0, 0 };
-            uint32_t idle = 0;
-            while ((h[0] < total[0] || h[1] < total[1]) && idle < ASYNC_WAIT_LIMIT) {
-                bool served = false;
+        // Unit n is complete in its operand buffer once all worker threads have arrived at hardware barrier
+        // 3 + n % 2 (they do not wait there); this warp does wait there, then one thread issues the unit's
+        // eight MMAs into accumulator columns 128 (n % 2) ... and commits them to the unit's barrier.
+        // The descriptors are worked out once: a single thread issues, and its own instruction stream is what
+        // bounds the rate.  The start-address field is the low 14 bits in units of 16 bytes; the offsets added
+        // below stay inside it (shared memory ends below 2^18).
+        const uint32_t idesc = tc_idesc();
+        const uint64_t adesc0 = tc_smem_desc_sw128(smem_addr(smem + TC_OFF_A), 1024);
+        const uint64_t bdesc0 = tc_smem_desc(smem_addr(smem + TC_OFF_B), 128, 0);
+        uint32_t kb = 0;
+        for (uint32_t n = 0; n < total; n++) {
+            const uint32_t u = n & 1;
+            if (u) asm volatile("bar.sync 4, %0;" ::"n"(32 * TC_WORKER_WARPS + 32) : "memory");
+            else asm volatile("bar.sync 3, %0;" ::"n"(32 * TC_WORKER_WARPS + 32) : "memory");
+            if (lane == 0 && !*dead) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t ad = adesc0 + (uint64_t)(u * (TC_A_BYTES >> 4));
+                const uint64_t bd = bdesc0 + (uint64_t)(kb * ((256 / 16) * 128 >> 4));
+                const uint32_t dcol = tmem_base + u * 128;
 #pragma unroll
-                for (uint32_t g = 0; g < TC_GROUPS; g++) {
-                    if (h[g] >= total[g]) continue;
-                    const uint32_t n = h[g] / TC_PARTS, p = h[g] % TC_PARTS, kb = n % nkb;
-                    if (!mbar_try_wait(bar_ready(g, p), n & 1)) continue;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t abuf = smem_addr(smem + TC_OFF_A) + g * TC_A_BYTES;
-                    const uint32_t bbuf = smem_addr(smem + TC_OFF_B) + kb * (256 / 16) * 128;
-#pragma unroll
-                    for (uint32_t q = 0; q < 2 * TC_CP; q++) {
-                        const uint32_t j = 2 * TC_CP * p + q;
-                        tc_mma(tmem_base + g * 128 + 16 * j, tc_smem_desc_sw128(abuf + (j >> 2) * 16384 + (j & 3) * 32, 1024),
-                               tc_smem_desc(bbuf + j * 256, 128, 0), idesc);
-                    }
-                    tc_commit(bar_done(g, p));
-                    h[g]++;
-                    served = true;
-                }
-                idle = served ? 0 : idle + 1;
-                if (!served && (idle & 255u) == 255u && *dead) break;
+                for (uint32_t j = 0; j < 8; j++)
+                    tc_mma(dcol + 16 * j, ad + (uint64_t)(((j >> 2) * 16384 + (j & 3) * 32) >> 4), bd + (uint64_t)((j * 256) >> 4), idesc);
+                tc_commit(bar_done(u));
             }
-            if (idle >= ASYNC_WAIT_LIMIT) {
-                *dead = 1;
-                if (a.err) atomicExch(a.err, 12u);
-            }
+            __syncwarp();
+            kb = kb + 1 == nkb ? 0 : kb + 1;
         }
     } else {
         // ------------------------------ workers ------------------------------
-        const uint32_t w = warp - 2, g = w / 4, quarter = warp & 3, r = quarter * 32 + lane;
-        // the input image, once per block (both groups take part)
+        // Thread (quarter, lane, sub): row r = 32 quarter + lane of the tile (the quarter of tensor memory
+        // its warp may read), 32-byte chunks sub * TC_CPT .. of that row (sub-blocks 2c and 2c + 1 each).
+        const uint32_t w = warp - 2, sub = w / 4, quarter = warp & 3, r = quarter * 32 + lane;
         for (uint32_t grp = threadIdx.x - 64; grp < a.K / 32; grp += 32 * TC_WORKER_WARPS) tc_stage_group(smem, a.x, grp);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("bar.sync 1, %0;" ::"n"(32 * TC_WORKER_WARPS) : "memory");
         const float *e = reinterpret_cast<const float *>(smem + TC_OFF_E), *xs = reinterpret_cast<const float *>(smem + TC_OFF_S);
-        const uint32_t abuf = smem_addr(smem + TC_OFF_A) + g * TC_A_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
-        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + g * 128;
-        const uint32_t ring = smem_addr(smem + TC_OFF_RING) + g * SLOTS * TC_UNIT_BYTES + r * 144;
-        // Parts h = 4 n + p of the group's units n = 0, 1, ... (unit n = column n % nkb of the group's tile
-        // n / nkb; part p = 32-byte chunk p of every row = sub-blocks 2p and 2p + 1).  Step s unpacks part s
-        // and then finishes part s - TC_AHEAD, whose MMAs have had the steps in between to complete.
-        const uint32_t total = TC_PARTS * tiles_of(g) * nkb;
+        const uint32_t arow = smem_addr(smem + TC_OFF_A) + (r >> 3) * 1024 + (r & 7) * 128;
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+        const uint32_t ring = smem_addr(smem + TC_OFF_RING) + r * 144;
+        // Step n unpacks unit n into operand buffer n % 2, tells the MMA warp (an arrival at a hardware
+        // barrier, without waiting), and goes on to finish unit n - 1, whose MMAs were issued a step ago.
+        // Buffer n % 2 is free again by then: finishing unit n - 2 waited for its MMAs.  The two barrier
+        // numbers alternate so that an early arrival for unit n + 1 cannot be counted for unit n.
         float rowacc = 0.0f;
         bool ok = true;
-        for (uint32_t sidx = 0; sidx < total + TC_AHEAD && ok; sidx++) {
-            if (sidx < total) {
-                const uint32_t n = sidx / TC_PARTS, p = sidx % TC_PARTS, slot = n % SLOTS;
-                if (p == 0) ok = tc_wait(bar_full(g, slot), (n / SLOTS) & 1, dead, a.err, 13);
-                if (!ok) break;
+        // After an expired wait (`ok` false, warp-uniform) the loop keeps its shape, so that every thread still
+        // meets every hardware barrier, but waits for nothing and computes nothing.
+        for (uint32_t n = 0; n <= total; n++) {
+            if (n < total) {
+                const uint32_t slot = n % TC_RING, u = n & 1;
+                if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_full(slot), (n / TC_RING) & 1, dead, a.err, 13));
                 const uint32_t raw = ring + slot * TC_UNIT_BYTES;
                 // nibbles -> bytes: low nibbles are sub-block 2c, high nibbles (left as 16 * code) sub-block
-                // 2c + 1; sub-block j lies in K panel j / 4 (16 KB) at bytes 32 (j % 4) .. + 31 of the row
+                // 2c + 1; sub-block j lies in K panel j / 4 (16 KB) at bytes 32 (j % 4) .. + 31 of the row,
+                // 16-byte chunks swizzled by the row index
 #pragma unroll
-                for (uint32_t cc = 0; cc < TC_CP; cc++) {
-                    const uint32_t c = TC_CP * p + cc;
+                for (uint32_t cc = 0; cc < (ok ? TC_CPT : 0u); cc++) {
+                    const uint32_t c = TC_CPT * sub + cc;
 #pragma unroll
                     for (uint32_t core = 0; core < 2; core++) {
                         const uint4 q = lds128(raw + 16 + 32 * c + 16 * core);
                         const uint32_t jl = 2 * c, jh = 2 * c + 1;
-                        sts128(abuf + (jl >> 2) * 16384 + (((2 * (jl & 3) + core) ^ (r & 7)) << 4),
+                        sts128(arow + u * TC_A_BYTES + (jl >> 2) * 16384 + (((2 * (jl & 3) + core) ^ (r & 7)) << 4),
                                q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
-                        sts128(abuf + (jh >> 2) * 16384 + (((2 * (jh & 3) + core) ^ (r & 7)) << 4),
+                        sts128(arow + u * TC_A_BYTES + (jh >> 2) * 16384 + (((2 * (jh & 3) + core) ^ (r & 7)) << 4),
                                q.x & 0xf0f0f0f0u, q.y & 0xf0f0f0f0u, q.z & 0xf0f0f0f0u, q.w & 0xf0f0f0f0u);
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(bar_ready(g, p));
+                if (u) asm volatile("bar.arrive 4, %0;" ::"n"(32 * TC_WORKER_WARPS + 32) : "memory");
+                else asm volatile("bar.arrive 3, %0;" ::"n"(32 * TC_WORKER_WARPS + 32) : "memory");
             }
-            if (sidx >= TC_AHEAD) {
-                const uint32_t h = sidx - TC_AHEAD, n = h / TC_PARTS, p = h % TC_PARTS, slot = n % SLOTS;
-                const uint32_t kb = n % nkb;
+            if (n >= 1) {
+                const uint32_t m = n - 1, slot = m % TC_RING, u = m & 1, kb = m % nkb;
                 const uint32_t raw = ring + slot * TC_UNIT_BYTES;
                 const uint4 hdr = lds128(raw);
                 const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, m_lo = hdr.z & 0x3f3f3f3fu;
                 const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
                 const uint32_t m_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
                 const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-                ok = tc_wait(bar_done(g, p), n & 1, dead, a.err, 14);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                int d[2 * TC_CP][4];
+                if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), (m >> 1) & 1, dead, a.err, 14));
+                int d[2 * TC_CPT][4] = {};
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (uint32_t q = 0; q < 2 * TC_CP; q++) tc_ld4(taddr + 16 * (2 * TC_CP * p + q), d[q]);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    for (uint32_t q = 0; q < 2 * TC_CPT; q++) tc_ld4(taddr + u * 128 + 16 * (2 * TC_CPT * sub + q), d[q]);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                }
                 float acc = 0.0f, neg = 0.0f;
 #pragma unroll
-                for (uint32_t cc = 0; cc < TC_CP; cc++) {
+                for (uint32_t cc = 0; cc < TC_CPT; cc++) {
                     // six-bit scales and mins of sub-blocks 2c, 2c + 1 in the low bytes of a word each
-                    const uint32_t c = TC_CP * p + cc, sh = (c & 1) * 16;
+                    const uint32_t c = TC_CPT * sub + cc, sh = (c & 1) * 16;
                     const uint32_t scw = (c < 2 ? sc_lo : sc_hi) >> sh, mw = (c < 2 ? m_lo : m_hi) >> sh;
                     const float2 e2 = reinterpret_cast<const float2 *>(e)[kb * 4 + c], s2 = reinterpret_cast<const float2 *>(xs)[kb * 4 + c];
                     // |digit sum| <= 32 * 240 * 128 < 2^22: the offset conversion is exact
@@ -350,13 +331,20 @@ __global__ void __launch_bounds__(TC_NT, 1) gemv_q4k_tc_kernel(const __grid_cons
                     neg = fmaf(byte2f(mw, 1), s2.y, neg);
                 }
                 rowacc += dm.x * acc - dm.y * neg;
-                if (p == TC_PARTS - 1) {
-                    mbar_arrive(bar_empty(g, slot));
-                    if (kb == nkb - 1) {
-                        const uint32_t tile = blockIdx.x + (2 * (n / nkb) + g) * gridDim.x;
-                        a.out[(size_t)tile * TC_TILE_ROWS + r] = rowacc;
-                        rowacc = 0.0f;
+                mbar_arrive(bar_empty(slot));
+                if (kb == nkb - 1) {
+                    // the row's total: its TC_WPQ threads' parts, added in a fixed order
+                    rowpart[sub][r] = rowacc;
+                    rowacc = 0.0f;
+                    asm volatile("bar.sync 2, %0;" ::"n"(32 * TC_WORKER_WARPS) : "memory");
+                    if (sub == 0 && ok) {
+                        float t = rowpart[0][r];
+#pragma unroll
+                        for (uint32_t q = 1; q < TC_WPQ; q++) t += rowpart[q][r];
+                        const uint32_t tile = blockIdx.x + (m / nkb) * gridDim.x;
+                        a.out[(size_t)tile * TC_TILE_ROWS + r] = t;
                     }
+                    asm volatile("bar.sync 2, %0;" ::"n"(32 * TC_WORKER_WARPS) : "memory");
                 }
             }
         }
