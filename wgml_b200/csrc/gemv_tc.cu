@@ -6,11 +6,15 @@
 // Decomposition.  The input vector is quantised once per block into three signed byte digits per element
 // with one power-of-two exponent per 32 columns (the same fixed-point image as the dp4a kernel, 23 bits).
 // For a tile of 128 rows and one super-block column (256 columns) the worker threads unpack the nibbles to
-// unsigned bytes in shared memory (A operand, 128 x 256, K-major canonical layout without swizzle), and one
-// thread issues eight MMAs, one per 32-column sub-block: D[128 rows x 16] = A[128 x 32] * B[32 x 16], where
-// columns 0..2 of B are the digits (columns 3..7 zero, 8..15 alias 0..7).  Worker thread r reads row r of
-// the eight results from tensor memory and applies, in FP32, the digit weights, the group exponent, the
-// six-bit sub-block scale and the min term (get_scale_min_k4, crates/wgml/src/quantization.rs:381-389).
+// unsigned bytes in shared memory (A operand, 128 x 256, K-major, 128-byte swizzle, two K panels of 16 KB),
+// and one thread issues eight MMAs, one per 32-column sub-block: D[128 rows x 16] = A[128 x 32] * B[32 x 16],
+// where columns 0..2 of B are the digits (columns 3..7 zero, 8..15 alias 0..7; B is K-major without
+// swizzle).  The threads of row r read that row of the eight results from tensor memory and apply, in FP32,
+// the digit weights, the group exponent, the six-bit sub-block scale and the min term (get_scale_min_k4,
+// crates/wgml/src/quantization.rs:381-389).
+//
+// Measured on a B200: one MMA of this shape takes about 190 cycles whatever N is, which caps this kernel at
+// about 3 TB/s of packed weights over 148 SMs, below the dp4a kernel; it pays only with many input vectors.
 //
 // Pipeline per block: warp 0 streams (tile, column) units into a ring with bulk copies; warp 1 owns the
 // tensor memory allocation and issues the MMAs; sixteen worker warps (four per quarter of the rows, one
