@@ -374,7 +374,7 @@ def run_b200(args):
                    **({"exchange": "kernels store partial products into the peers' memory over NVLink, flags instead of a collective"
                        if args.exchange == "peer" else "NCCL all-reduce",
                        "note": "the default single-GPU run of this script is the 7B configuration the metric is quoted on; this "
-                               "70B workload on one GPU (--workload llama2-70b --gpus 1) measured 57 tok/s, the figure strong "
+                               "70B workload on one GPU (--workload llama2-70b --gpus 1) measured 60 tok/s, the figure strong "
                                "scaling should be taken against"} if world > 1 else {}),
                    **({"truncated_to_layers": args.layers, "valid": False} if args.layers else {}),
                    "weights_gb": sum(matrix_bytes(cfg, l, n)[0] for l in range(cfg["n_layers"]) for n in
