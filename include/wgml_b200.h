@@ -370,6 +370,22 @@ int wgb_comm_shared_alloc(wgb_comm *c, size_t bytes, void **peers_out);
  * No collective library call and no extra launch remain on the token path.  Call after
  * wgb_llama2_set_comm and before the first forward; collective (every rank, same mode). */
 int wgb_llama2_set_exchange(wgb_llama2 *m, int mode);
+/* Direct exchange on buffers the host mapped itself (its own CUDA IPC, cuMem fabric or symmetric-memory
+ * allocator) instead of wgb_comm_shared_alloc: d_mail[p] / d_flags[p] are rank p's mailbox and flags as
+ * seen from this rank, of the sizes wgb_llama2_exchange_bytes gives, zero-filled, 16-byte aligned, valid
+ * for the life of the model; entry [tp_rank] is this rank's own.  Selects mode 1; no communicator is
+ * needed on the token path.  No counterpart in the reference (wgml runs on one adapter,
+ * crates/wgml-chat/src/chat_llama2.rs:168-213). */
+int wgb_llama2_exchange_bytes(const wgb_llama2 *m, size_t *mail_bytes, size_t *flag_bytes);
+int wgb_llama2_set_exchange_buffers(wgb_llama2 *m, void *const *d_mail, void *const *d_flags);
+/* How long a kernel waits for the flags of the other ranks before it gives up, in milliseconds (default
+ * 2000; it has to cover the skew between the ranks' host threads).  A wait that runs out leaves a code in
+ * the device's status word: the decode call in progress returns WGB_ERR_TIMEOUT within two batches of 64
+ * steps, and while the word is set no kernel waits for peers at all, so a missing rank costs one limit,
+ * not one per exchange.  After WGB_ERR_TIMEOUT the group's step counts no longer agree: rebuild the
+ * models of every rank.  Process-wide.  No counterpart in the reference. */
+int wgb_set_wait_limit_ms(unsigned ms);
+unsigned wgb_get_wait_limit_ms(void);
 
 /* ---- GPT-2 ---- */
 

@@ -130,3 +130,43 @@ def test_two_rank_layer_matches_unsharded(tmp_path):
     ref = _layer(x, _weights(), CFG["n_q_heads"], CFG["n_kv_heads"], kc, vc, lambda v: v, True)
     assert np.array_equal(ys[0], ys[1])
     np.testing.assert_allclose(ys[0], ref, rtol=1e-12, atol=1e-12)
+
+
+# ---- failure detection on the host: a rank that leaves between steps, a rank that dies silently ------------
+
+def _watch_main(rank, size, port, out_dir, mode):
+    """Three steps together; then rank 1 leaves (mode "leave": says good-bye; mode "vanish": just returns)."""
+    import datetime
+    import time
+    store = dist.TCPStore("127.0.0.1", port, size, rank == 0, timeout=datetime.timedelta(seconds=20))
+    watch = tp.PeerWatch(store, rank, size, timeout_s=1.0)
+    steps_done, error, waited = 0, "", 0.0
+    try:
+        for step in range(6):
+            if rank == 1 and step == 3:
+                if mode == "leave":
+                    watch.leave()
+                break
+            t0 = time.monotonic()
+            try:
+                watch.check()
+            finally:
+                waited = time.monotonic() - t0
+            steps_done += 1          # the launch would go here
+    except tp.PeerLost as e:
+        error = str(e)
+    with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+        f.write(f"{steps_done}|{error}|{waited:.3f}")
+    if rank == 0:
+        time.sleep(0.3)   # the store lives in rank 0: keep it up until rank 1 has written its good-bye
+
+
+@pytest.mark.parametrize("mode", ["leave", "vanish"])
+def test_rank_that_leaves_between_steps_is_an_error_not_a_wait(tmp_path, mode):
+    mp.spawn(_watch_main, args=(2, _free_port(), str(tmp_path), mode), nprocs=2, join=True)
+    r0 = open(tmp_path / "rank0.txt").read().split("|")
+    r1 = open(tmp_path / "rank1.txt").read().split("|")
+    assert r1[0] == "3" and r1[1] == ""                     # rank 1 did its three steps and left quietly
+    assert r0[0] == "3"                                      # rank 0 launched nothing after the peer was gone
+    assert ("left the group" if mode == "leave" else "did not reach step 3") in r0[1]
+    assert float(r0[2]) < (0.6 if mode == "leave" else 2.5)  # told at once / after the 1 s limit, never a hang

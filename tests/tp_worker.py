@@ -13,7 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from wgml_b200 import synth, tp  # noqa: E402
+from wgml_b200 import _lib, synth, tp  # noqa: E402
 from wgml_b200.models import Llama2, Llama2Config  # noqa: E402
 
 CASES = {
@@ -44,6 +44,14 @@ def main():
             m.set_fused(fused)
             tp.attach(m, comm, direct=direct)
             toks = m.decode(prompt, 24)
+            if fused:
+                # the per-launch timing path replays the step with time stamps (direct exchange) or events (NCCL);
+                # it must leave the exchange counters intact: decode the same sequence again afterwards
+                prof = m.profile_step(int(toks[-1]), len(toks))
+                assert len(prof) == 5 * cfg["n_layers"] + 1, len(prof)
+                again = m.decode(prompt, 24)
+                assert np.array_equal(again, toks), (name, fused, direct, again, toks)
+                assert _lib.load().wgb_device_status() == _lib.OK
             m.dispatch(int(toks[-1]), len(toks))      # one eager step after the graph replays
             logits = m.logits().cpu().numpy()
             x = m.x().cpu().numpy()

@@ -136,6 +136,10 @@ SIGNATURES = {
     "wgb_comm_all_gather": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "wgb_comm_shared_alloc": (_i, [_vp, _sz, _pp]),
     "wgb_llama2_set_exchange": (_i, [_vp, _i]),
+    "wgb_llama2_exchange_bytes": (_i, [_vp, C.POINTER(_sz), C.POINTER(_sz)]),
+    "wgb_llama2_set_exchange_buffers": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
+    "wgb_set_wait_limit_ms": (_i, [C.c_uint]),
+    "wgb_get_wait_limit_ms": (C.c_uint, []),
     "wgb_gpt2_params_from_gguf": (_i, [_vp, C.POINTER(Gpt2ParamsC)]),
     "wgb_gpt2_create": (_i, [C.POINTER(Gpt2ParamsC), _pp]),
     "wgb_gpt2_destroy": (_i, [_vp]),

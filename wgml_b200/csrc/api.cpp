@@ -1,9 +1,12 @@
 // Status handling and the device-memory helpers of the C ABI.
 #include "common.cuh"
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
+#include <new>
 
 namespace wgb {
 
@@ -26,17 +29,47 @@ int cuda_fail(cudaError_t e, const char *what)
     return WGB_ERR_CUDA;
 }
 
+static DeviceState *g_devices[MAX_DEVICES] = {};
+static std::mutex g_devices_mutex;
+static std::atomic<unsigned> g_peer_wait_ms{2000};
+
+int current_device()
+{
+    int dev = -1;
+    const cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { cuda_fail(e, "cudaGetDevice"); return -1; }
+    if (dev < 0 || dev >= MAX_DEVICES) { fail(WGB_ERR_UNSUPPORTED, "device ordinal %d outside 0..%d", dev, MAX_DEVICES - 1); return -1; }
+    return dev;
+}
+
+DeviceState *device_state()
+{
+    const int dev = current_device();
+    if (dev < 0) return nullptr;
+    std::lock_guard<std::mutex> lock(g_devices_mutex);
+    if (!g_devices[dev]) {
+        int n = 0;
+        const cudaError_t e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || n <= 0) { cuda_fail(e, "cudaDeviceGetAttribute(multiprocessor count)"); return nullptr; }
+        DeviceState *d = new (std::nothrow) DeviceState();
+        if (!d) { fail(WGB_ERR_INVALID, "out of host memory"); return nullptr; }
+        d->ordinal = dev;
+        d->sms = n;
+        g_devices[dev] = d;
+    }
+    return g_devices[dev];
+}
+
 int sm_count()
 {
-    static int cached = 0;
-    if (cached > 0) return cached;
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
-        cudaGetLastError();
-        return 148;  // B200; only reached when no device answers, and then every launch fails anyway
-    }
-    cached = n;
-    return n;
+    const DeviceState *d = device_state();
+    return d ? d->sms : 148;  // B200; the fallback is only reached when no device answers, and then every launch fails anyway
+}
+
+WaitLimits wait_limits()
+{
+    const unsigned long long peer = (unsigned long long)g_peer_wait_ms.load() * 1000000ull;
+    return { peer, peer + 2000000000ull };
 }
 
 }  // namespace wgb
@@ -44,7 +77,16 @@ int sm_count()
 using namespace wgb;
 
 WGB_EXPORT const char *wgb_last_error(void) { return g_error; }
-WGB_EXPORT const char *wgb_version(void) { return "wgml_b200 0.1 (sm_100a)"; }
+WGB_EXPORT const char *wgb_version(void) { return "wgml_b200 0.2 (sm_100a)"; }
+
+WGB_EXPORT int wgb_set_wait_limit_ms(unsigned ms)
+{
+    WGB_REQUIRE(ms >= 1 && ms <= 600000u, "wait limit of %u ms outside 1 ms .. 10 min", ms);
+    g_peer_wait_ms.store(ms);
+    return WGB_OK;
+}
+
+WGB_EXPORT unsigned wgb_get_wait_limit_ms(void) { return g_peer_wait_ms.load(); }
 
 WGB_EXPORT int wgb_malloc(void **d_ptr, size_t bytes)
 {

@@ -1,14 +1,22 @@
 // Shared-memory barriers with transaction counts and bulk asynchronous copies (global -> shared), the
 // plumbing of the producer / consumer pipelines of the matrix-vector and the streaming attention kernels.
-// Every wait is bounded: after ASYNC_WAIT_LIMIT polls a waiter records a code in the caller's status word
-// and returns, so a kernel always terminates.
+// Every wait is bounded in time (%globaltimer): a waiter that has run out records a code in the caller's
+// status word and returns, so a kernel always terminates, and it terminates within a known time.
 #pragma once
 
 #include "common.cuh"
 
 namespace wgb {
 
-constexpr uint32_t ASYNC_WAIT_LIMIT = 1u << 22;
+// Default limit of a wait inside one thread block; launches that know the configured limits pass their own.
+constexpr unsigned long long ASYNC_WAIT_NS = 4000000000ull;
+
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -36,12 +44,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait; on expiry records `code` in *err and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *err, uint32_t code)
+// Bounded wait; after `limit_ns` records `code` in *err (unless an earlier code is there) and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *err, uint32_t code,
+                                          unsigned long long limit_ns = ASYNC_WAIT_NS)
 {
-    for (uint32_t i = 0; i < ASYNC_WAIT_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    if (err) atomicExch(err, code);
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    do {
+#pragma unroll 1
+        for (int i = 0; i < 16; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+    } while (global_ns() - t0 < limit_ns);
+    if (err) atomicCAS(err, 0u, code);
     return false;
 }
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)

@@ -717,10 +717,12 @@ template <int QH>
 static int launch_stream(const AttnArgs &a, uint32_t nchunks, uint32_t n_kv, uint32_t zgroups, cudaStream_t stream, bool pdl)
 {
     const size_t smem = (size_t)ATS_STAGES * 2 * ATT_CHUNK * a.p.head_size * sizeof(float);
-    static bool ready = false;
-    if (!ready) {
+    static bool ready[MAX_DEVICES] = {};   // per instantiation and device
+    const int dev = current_device();
+    if (dev < 0) return WGB_ERR_CUDA;
+    if (!ready[dev]) {
         WGB_CUDA(cudaFuncSetAttribute(attn_stream_kernel<QH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(ATS_STAGES * 2 * ATT_CHUNK * 128 * sizeof(float))));
-        ready = true;
+        ready[dev] = true;
     }
     uint32_t splits = (uint32_t)sm_count() / (n_kv * zgroups);   // one block per SM
     if (splits < 1) splits = 1;
@@ -755,13 +757,17 @@ static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t nchunks_hi
 {
     // One chunk per block while all blocks of such a grid are resident at once (a second wave would double
     // the latency); beyond that, as many splits as fit and several chunks per block.
-    static int per_sm_single = 0, per_sm_multi = 0;
-    if (!per_sm_single) {
-        WGB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_single, attn_split_kernel<QH, VC, false>, ATT_NT, 0));
-        WGB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_multi, attn_split_kernel<QH, VC, true>, ATT_NT, 0));
-        if (per_sm_single < 1) per_sm_single = 1;
-        if (per_sm_multi < 1) per_sm_multi = 1;
+    static int occ_single[MAX_DEVICES] = {}, occ_multi[MAX_DEVICES] = {};   // per instantiation and device
+    const int dev = current_device();
+    if (dev < 0) return a.q ? WGB_ERR_CUDA : -1;
+    if (!occ_single[dev]) {
+        int one = 0, many = 0;
+        WGB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&one, attn_split_kernel<QH, VC, false>, ATT_NT, 0));
+        WGB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&many, attn_split_kernel<QH, VC, true>, ATT_NT, 0));
+        occ_multi[dev] = many < 1 ? 1 : many;
+        occ_single[dev] = one < 1 ? 1 : one;
     }
+    const int per_sm_single = occ_single[dev], per_sm_multi = occ_multi[dev];
     const uint32_t heads = n_kv * zgroups;
     if (!a.q) {   // sizing query (attn_sizing_class): no launch
         return (uint64_t)nchunks_hint * heads > (uint64_t)per_sm_single * (uint32_t)sm_count() ? 1 : 0;
@@ -830,12 +836,6 @@ int attn_sizing_class(const wgb_attn_params &p)
 
 using namespace wgb;
 
-// Scratch of the stand-alone op, grown on demand and kept for the life of the process.
-static float *g_scratch = nullptr;
-static size_t g_scratch_floats = 0;
-static uint32_t *g_counters = nullptr;
-static size_t g_ncounters = 0;
-
 WGB_EXPORT int wgb_attention(const wgb_attn_params *p, const float *d_q, const float *d_key_cache,
                              const float *d_value_cache, float *d_attn, float *d_xb, void *stream)
 {
@@ -856,26 +856,29 @@ WGB_EXPORT int wgb_attention(const wgb_attn_params *p, const float *d_q, const f
         return WGB_OK;
     }
     WGB_REQUIRE(p->head_size % 4 == 0 && p->head_size <= 256, "head_size %u unsupported", p->head_size);
+    // Scratch of the stand-alone op: per device, grown on demand and kept for the life of the process.
+    DeviceState *ds = device_state();
+    if (!ds) return WGB_ERR_CUDA;
     const size_t need = attn_scratch_floats(p->n_heads, p->head_size, p->seq_len);
-    if (need > g_scratch_floats) {
+    if (need > ds->attn_scratch_floats) {
         WGB_CUDA(cudaStreamSynchronize(as_stream(stream)));
-        if (g_scratch) cudaFree(g_scratch);
-        g_scratch = nullptr;
-        g_scratch_floats = 0;
-        WGB_CUDA(cudaMalloc((void **)&g_scratch, need * sizeof(float)));
-        g_scratch_floats = need;
+        if (ds->attn_scratch) cudaFree(ds->attn_scratch);
+        ds->attn_scratch = nullptr;
+        ds->attn_scratch_floats = 0;
+        WGB_CUDA(cudaMalloc((void **)&ds->attn_scratch, need * sizeof(float)));
+        ds->attn_scratch_floats = need;
     }
-    if (p->n_heads > g_ncounters) {
+    if (p->n_heads > ds->attn_ncounters) {
         WGB_CUDA(cudaStreamSynchronize(as_stream(stream)));
-        if (g_counters) cudaFree(g_counters);
-        g_counters = nullptr;
-        g_ncounters = 0;
-        WGB_CUDA(cudaMalloc((void **)&g_counters, p->n_heads * sizeof(uint32_t)));
-        WGB_CUDA(cudaMemset(g_counters, 0, p->n_heads * sizeof(uint32_t)));
-        g_ncounters = p->n_heads;
+        if (ds->attn_counters) cudaFree(ds->attn_counters);
+        ds->attn_counters = nullptr;
+        ds->attn_ncounters = 0;
+        WGB_CUDA(cudaMalloc((void **)&ds->attn_counters, p->n_heads * sizeof(uint32_t)));
+        WGB_CUDA(cudaMemset(ds->attn_counters, 0, p->n_heads * sizeof(uint32_t)));
+        ds->attn_ncounters = p->n_heads;
     }
-    a.scratch = g_scratch;
-    a.counters = g_counters;
+    a.scratch = ds->attn_scratch;
+    a.counters = ds->attn_counters;
     return launch_attention(a, as_stream(stream), false);
 }
 

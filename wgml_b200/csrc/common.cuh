@@ -37,8 +37,40 @@ int cuda_fail(cudaError_t e, const char *what);
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
-// Number of SMs of the current device (148 on B200); cached per process.
+// Per-device state.  Everything the library sets up once per device (the status word of the bounded waits,
+// opt-ins to large dynamic shared memory, occupancy figures, scratch of the stand-alone ops) hangs off the
+// current device's entry, so a process may drive several devices.  Entries are created under a mutex; the
+// calls of one device must still come from one host thread at a time (the C ABI is not thread-safe).
+constexpr int MAX_DEVICES = 64;
+struct DeviceState {
+    int ordinal = -1;
+    int sms = 0;
+    uint32_t *err = nullptr;              // device status word: 0, or the code of the first bounded wait that expired
+    bool gemv_attrs = false;              // fused matrix-vector kernels opted in to large dynamic shared memory
+    bool tiles_attrs = false;             // the same for the tensor-memory kernel
+    float *attn_scratch = nullptr;        // scratch of the stand-alone attention op, grown on demand
+    size_t attn_scratch_floats = 0;
+    uint32_t *attn_counters = nullptr;
+    size_t attn_ncounters = 0;
+    unsigned long long *argmax_part = nullptr;   // partial keys of the stand-alone argmax
+    float *sampler_scratch = nullptr;     // work area of the stand-alone sampler
+    size_t sampler_scratch_bytes = 0;
+};
+// Entry of the current device (created on first use), or NULL with the error recorded.
+DeviceState *device_state();
+// Ordinal of the current device in [0, MAX_DEVICES), or -1 with the error recorded.
+int current_device();
+
+// Number of SMs of the current device (148 on B200).
 int sm_count();
+
+// Limits of the device-side waits, in nanoseconds of %globaltimer.  `peer`: how long a kernel waits for the
+// flags of the other ranks of a tensor-parallel group (wgb_set_wait_limit_ms; default 2 s, which has to cover
+// the skew between the ranks' hosts).  `local`: waits inside one thread block (shared-memory barriers fed by
+// the block's own warps and bulk copies); longer than `peer`, because a block's warps may themselves be held
+// by a peer wait.
+struct WaitLimits { unsigned long long peer_ns, local_ns; };
+WaitLimits wait_limits();
 
 __host__ __device__ constexpr int block_bytes(int qtype)
 {

@@ -44,13 +44,19 @@ constexpr int GEMV_EPILOGUE = GEMV_NCONS + 1;       // warp index of the epilogu
 constexpr int GEMV_NT = (GEMV_EPILOGUE + 1) * 32;
 constexpr int GEMV_MAX_RS = 8;                      // rows per stage
 constexpr int GEMV_MAX_STAGES = 24;
-constexpr uint32_t GEMV_WAIT_LIMIT = ASYNC_WAIT_LIMIT;
 constexpr uint32_t GEMV_ROPE_TAB = 128;             // pair indices with a precomputed rotation
 constexpr size_t GEMV_SMEM_BUDGET = 200 * 1024;     // dynamic shared memory per block
 
 __device__ __forceinline__ float4 ld_act4(const float *p)
 {
     return __ldcg(reinterpret_cast<const float4 *>(p));
+}
+
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(GEMV_CONS_THREADS) : "memory"); }
@@ -323,7 +329,7 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             uint32_t n = 0;
             const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
             if (ci == 0) {
-                if (round) mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.err, 2);
+                if (round) mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.err, 2, a.wait_ns);
                 mbar_expect_tx(full0 + 8 * s, nparts * n * row_bytes);
             }
             __syncwarp(gmask);
@@ -378,7 +384,7 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             const EpiCtx c = epi_prepare<EPI>(a, parts, nparts, n, ul, nunits, rope_tab);
             uint32_t ra = 0, rb = 0;
             if (c.on) unit_rows<EPI>(parts, nparts, n, ul, ra, rb);
-            mbar_wait(done0 + 8 * s, phase, a.err, 3);
+            mbar_wait(done0 + 8 * s, phase, a.err, 3, a.wait_ns);
             if (PRO == PRO_RMS && !have_scale) {
                 // every consumer warp wrote its sum of squares before its first arrival on a `done` barrier
                 float ss = 0.0f;
@@ -452,17 +458,25 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     float4 xc[XC];
     const bool gather = PRO == PRO_RMS && a.peer_in.n != 0;
     if (gather) {
-        // Partial products from every rank: wait for the flags (bounded), then add in rank order.
+        // Partial products from every rank: wait for the flags, then add in rank order.  The wait is bounded
+        // in time (a.peer_wait_ns); a wait that runs out leaves code 6 in the status word, and while the word
+        // is non-zero no launch waits at all, so one missing rank costs one limit, not one per exchange.
         if (threadIdx.x < a.peer_in.n) {
             const uint32_t want = __ldcg(a.peer_in.epoch);
             const uint32_t *f = a.peer_in.flag + threadIdx.x;
-            bool ok = false;
-            for (uint32_t i = 0; i < GEMV_WAIT_LIMIT && !ok; i++) {
+            bool ok = false, give_up = a.err && ld_relaxed_u32(a.err) != 0;
+            unsigned long long t0 = 0;
+            for (uint32_t i = 0; !ok && !give_up; i++) {
                 uint32_t v;
                 asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
                 ok = (int32_t)(v - want) >= 0;
+                if (!ok && (i & 31u) == 31u) {
+                    const unsigned long long t = global_ns();
+                    if (!t0) t0 = t;
+                    give_up = t - t0 > a.peer_wait_ns || (a.err && ld_relaxed_u32(a.err) != 0);
+                }
             }
-            if (!ok && a.err) atomicExch(a.err, 6u);
+            if (!ok && a.err) atomicCAS(a.err, 0u, 6u);
             asm volatile("fence.acq_rel.sys;" ::: "memory");
         }
         cons_sync();
@@ -567,7 +581,7 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
         float acc[GEMV_MAX_RS];
 #pragma unroll
         for (int j = 0; j < GEMV_MAX_RS; j++) acc[j] = 0.0f;
-        mbar_wait(full0 + 8 * s, phase, a.err, 1);
+        mbar_wait(full0 + 8 * s, phase, a.err, 1, a.wait_ns);
         if (j0 < nrows) {
             // first shared-memory byte of row 0 of each part in each plane
             uint32_t base[2][NPL];
@@ -661,33 +675,68 @@ bool gemv_fast_supported(const QMat &m)
     return true;  // Q4_K raw
 }
 
-// Device status word shared by all launches of the process: 0, or the code of the first bounded
-// wait that expired (1 consumer, 2 producer, 3 epilogue, 6 flags of the tensor-parallel peers).
-static uint32_t *g_err = nullptr;
+// Device status word shared by all launches on one device: 0, or the code of the first bounded wait that
+// expired (1 consumer, 2 producer, 3 epilogue, 6 flags of the tensor-parallel peers, 7 / 8 streaming
+// attention, 16+ tensor-memory kernel).  While it is non-zero the kernels do not wait for peers at all.
 static bool g_trace_plan = false;   // WGML_B200_TRACE_PLAN=1 prints the plan of every launch to stderr
-static int ensure_err()
-{
-    if (g_err) return WGB_OK;
-    WGB_CUDA(cudaMalloc((void **)&g_err, sizeof(uint32_t)));
-    WGB_CUDA(cudaMemset(g_err, 0, sizeof(uint32_t)));
-    return WGB_OK;
-}
 
-uint32_t *gemv_status_word() { return g_err; }
+uint32_t *gemv_status_word()
+{
+    DeviceState *d = device_state();
+    return d ? d->err : nullptr;
+}
 
 int gemv_report_status(uint32_t v)
 {
     if (!v) return WGB_OK;
-    if (g_err) cudaMemset(g_err, 0, sizeof(uint32_t));
-    return fail(WGB_ERR_TIMEOUT, "a bounded wait inside a matrix-vector kernel expired (code %u)", v);
+    uint32_t *w = gemv_status_word();
+    if (w) cudaMemset(w, 0, sizeof(uint32_t));
+    return fail(WGB_ERR_TIMEOUT, "a bounded wait inside a kernel expired (code %u%s)", v,
+                v == 6 ? ": a rank of the tensor-parallel group did not deliver its partial products in time" : "");
 }
 
 int gemv_check_status()
 {
-    if (!g_err) return WGB_OK;
+    uint32_t *w = gemv_status_word();
+    if (!w) return WGB_OK;
     uint32_t v = 0;
-    WGB_CUDA(cudaMemcpy(&v, g_err, sizeof(v), cudaMemcpyDeviceToHost));
+    WGB_CUDA(cudaMemcpy(&v, w, sizeof(v), cudaMemcpyDeviceToHost));
     return gemv_report_status(v);
+}
+
+int replay_with_status(cudaGraphExec_t graph, size_t total, cudaStream_t stream, uint32_t *h_slots, StatusPoll &sp)
+{
+    uint32_t *word = gemv_status_word();
+    for (int k = 0; k < 2; k++)
+        if (!sp.ev[k]) WGB_CUDA(cudaEventCreateWithFlags(&sp.ev[k], cudaEventDisableTiming));
+    h_slots[0] = h_slots[1] = 0;
+    uint32_t seen = 0;
+    for (size_t i = 0; i < total && !seen; i++) {
+        if (word && i && i % STATUS_EVERY == 0) {
+            const int k = (int)((i / STATUS_EVERY) & 1);
+            if (i >= 2 * STATUS_EVERY) {
+                WGB_CUDA(cudaEventSynchronize(sp.ev[k]));
+                seen = h_slots[k];
+                if (seen) break;
+            }
+            WGB_CUDA(cudaMemcpyAsync(h_slots + k, word, 4, cudaMemcpyDeviceToHost, stream));
+            WGB_CUDA(cudaEventRecord(sp.ev[k], stream));
+        }
+        WGB_CUDA(cudaGraphLaunch(graph, stream));
+    }
+    if (seen) {
+        WGB_CUDA(cudaStreamSynchronize(stream));
+        return gemv_report_status(seen);
+    }
+    return WGB_OK;
+}
+
+void status_poll_destroy(StatusPoll &sp)
+{
+    for (int k = 0; k < 2; k++) {
+        if (sp.ev[k]) cudaEventDestroy(sp.ev[k]);
+        sp.ev[k] = nullptr;
+    }
 }
 
 static uint32_t steps_of(int qt, uint32_t K)
@@ -818,16 +867,20 @@ static int set_smem_attr()
 // large dynamic shared memory.  Must first run outside stream capture (model creation does).
 int gemv_global_init()
 {
-    static bool done = false;
-    if (done) return WGB_OK;
-    int rc = ensure_err();
-    if (rc) return rc;
+    DeviceState *d = device_state();
+    if (!d) return WGB_ERR_CUDA;
+    if (d->gemv_attrs) return WGB_OK;
+    if (!d->err) {
+        WGB_CUDA(cudaMalloc((void **)&d->err, sizeof(uint32_t)));
+        WGB_CUDA(cudaMemset(d->err, 0, sizeof(uint32_t)));
+    }
     const char *tp = getenv("WGML_B200_TRACE_PLAN");
     g_trace_plan = tp && tp[0] == '1';
+    int rc;
     if ((rc = set_smem_attr<WGB_Q4_K>()) || (rc = set_smem_attr<WGB_Q6_K>()) || (rc = set_smem_attr<WGB_Q8_0>()) ||
         (rc = set_smem_attr<WGB_F32>()))
         return rc;
-    done = true;
+    d->gemv_attrs = true;
     return WGB_OK;
 }
 
@@ -840,7 +893,10 @@ static int launch_one(GemvArgs &a, cudaStream_t stream, bool pdl)
     if (!plan(a, smem, grid)) return fail(WGB_ERR_UNSUPPORTED, "matrix shape does not fit the fused kernel");
     int rc = gemv_global_init();
     if (rc) return rc;
-    a.err = g_err;
+    a.err = gemv_status_word();
+    const WaitLimits wl = wait_limits();
+    a.wait_ns = wl.local_ns;
+    a.peer_wait_ns = wl.peer_ns;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(GEMV_NT);

@@ -109,15 +109,19 @@ __device__ __forceinline__ void tc_ld4(uint32_t taddr, int (&v)[4])
                  : "memory");
 }
 
-// Bounded wait that also gives up when another thread of the block already has.
+// Bounded wait (in time) that also gives up when another thread of the block already has.
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *dead, uint32_t *err, uint32_t code)
 {
-    for (uint32_t i = 0; i < ASYNC_WAIT_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *dead) return false;
-    }
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    do {
+#pragma unroll 1
+        for (int i = 0; i < 16; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*dead) return false;
+    } while (global_ns() - t0 < ASYNC_WAIT_NS);
     *dead = 1;
-    if (err) atomicExch(err, code);
+    if (err) atomicCAS(err, 0u, code);
     return false;
 }
 
@@ -390,10 +394,11 @@ WGB_EXPORT int wgb_q4k_tiles_create(const void *h_blocks, size_t nrows, size_t n
     WGB_REQUIRE(ncols > 0 && ncols % 256 == 0 && ncols <= TC_MAX_K, "the tensor-core path wants a multiple of 256 columns up to %u, got %zu", TC_MAX_K, ncols);
     int rc = gemv_global_init();
     if (rc) return rc;
-    static bool attr_done = false;
-    if (!attr_done) {
+    DeviceState *ds = device_state();
+    if (!ds) return WGB_ERR_CUDA;
+    if (!ds->tiles_attrs) {
         WGB_CUDA(cudaFuncSetAttribute(gemv_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TC_SMEM + 1024)));
-        attr_done = true;
+        ds->tiles_attrs = true;
     }
     const size_t bytes = nrows * (ncols / 256) * 144;
     cudaStream_t st = as_stream(stream);

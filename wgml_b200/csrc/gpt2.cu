@@ -32,8 +32,9 @@ struct wgb_gpt2 {
     float *attn_scratch = nullptr;
     uint32_t *attn_counters = nullptr, *scalars = nullptr, *argmax_scratch = nullptr, *d_prompt = nullptr, *d_out = nullptr;
     size_t prompt_cap = 0, out_cap = 0;
-    uint32_t *h_pinned = nullptr;            // pinned staging of a decode call: [0] status word, [1..] token ids
+    uint32_t *h_pinned = nullptr;            // pinned staging of a decode call: [0] status word, [1..2] status polls, [3..] token ids
     size_t pinned_cap = 0;
+    StatusPoll poll;
     bool fused = true, use_pdl = true;
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_n_prompt = 0;
@@ -291,6 +292,7 @@ WGB_EXPORT int wgb_gpt2_destroy(wgb_gpt2 *m)
     uint32_t *ubufs[] = { m->attn_counters, m->scalars, m->argmax_scratch, m->d_prompt, m->d_out };
     for (uint32_t *b : ubufs) if (b) cudaFree(b);
     if (m->h_pinned) cudaFreeHost(m->h_pinned);
+    status_poll_destroy(m->poll);
     delete m;
     return WGB_OK;
 }
@@ -491,12 +493,12 @@ WGB_EXPORT int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_p
         WGB_CUDA(cudaMalloc((void **)&m->d_out, total * 4));
         m->out_cap = total;
     }
-    if (total + 1 > m->pinned_cap) {
+    if (total + 3 > m->pinned_cap) {
         if (m->h_pinned) cudaFreeHost(m->h_pinned);
         m->h_pinned = nullptr;
         m->pinned_cap = 0;
-        WGB_CUDA(cudaMallocHost((void **)&m->h_pinned, (total + 1) * 4));
-        m->pinned_cap = total + 1;
+        WGB_CUDA(cudaMallocHost((void **)&m->h_pinned, (total + 3) * 4));
+        m->pinned_cap = total + 3;
     }
     // the first token travels as a kernel argument; the rest of the prompt is only read when there is one
     if (n_prompt > 1) WGB_CUDA(cudaMemcpyAsync(m->d_prompt, h_prompt, n_prompt * 4, cudaMemcpyHostToDevice, s));
@@ -529,12 +531,12 @@ WGB_EXPORT int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_p
         if (e != cudaSuccess) { m->graph = nullptr; return cuda_fail(e, "CUDA graph capture of a decode step"); }
         m->graph_n_prompt = (uint32_t)n_prompt;
     }
-    for (size_t i = 0; i < total; i++) WGB_CUDA(cudaGraphLaunch(m->graph, s));
+    if ((rc = replay_with_status(m->graph, total, s, m->h_pinned + 1, m->poll))) return rc;
     // One wait for the ids and the kernels' status word, both through pinned memory.
-    WGB_CUDA(cudaMemcpyAsync(m->h_pinned + 1, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
+    WGB_CUDA(cudaMemcpyAsync(m->h_pinned + 3, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
     m->h_pinned[0] = 0;
     if (gemv_status_word()) WGB_CUDA(cudaMemcpyAsync(m->h_pinned, gemv_status_word(), 4, cudaMemcpyDeviceToHost, s));
     WGB_CUDA(cudaStreamSynchronize(s));
-    memcpy(h_out_tokens, m->h_pinned + 1, total * 4);
+    memcpy(h_out_tokens, m->h_pinned + 3, total * 4);
     return gemv_report_status(m->h_pinned[0]);
 }

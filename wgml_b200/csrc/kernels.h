@@ -80,6 +80,7 @@ struct GemvArgs {
     uint32_t cps_log2;      // log2 of the copies per stage (planes x parts)
     uint32_t spb;           // stages per producer pass
     uint32_t *err;          // device status word for expired waits
+    unsigned long long wait_ns, peer_wait_ns;   // limits of the waits inside the block / for the peers' flags
     unsigned long long *stamp;   // optional: receives the launch's end time (stamp_end)
     PeerOut peer_out;            // EPI_STORE / EPI_RESIDUAL only
     PeerIn peer_in;              // PRO_RMS only
@@ -99,6 +100,18 @@ int gemv_check_status();
 // (clears the word when v != 0): lets a caller fold the read into its own device-to-host copy.
 uint32_t *gemv_status_word();
 int gemv_report_status(uint32_t v);
+
+// Replays a captured decode step `total` times on `stream` and reads the device status word every
+// STATUS_EVERY launches through `h_slots` (two words of pinned host memory) without draining the stream: the
+// copy issued after launch 64k is looked at before launch 64(k + 2) goes out.  When a wait has expired on the
+// device, stops launching, drains the stream, clears the word and returns WGB_ERR_TIMEOUT; the launches in
+// flight (at most 2 * STATUS_EVERY) finish quickly because kernels do not wait while the word is set.
+constexpr size_t STATUS_EVERY = 64;
+struct StatusPoll {
+    cudaEvent_t ev[2] = { nullptr, nullptr };
+};
+int replay_with_status(cudaGraphExec_t graph, size_t total, cudaStream_t stream, uint32_t *h_slots, StatusPoll &sp);
+void status_poll_destroy(StatusPoll &sp);
 
 // Slow path for any format: one warp per row, dequantising with the exact block formulas.
 int launch_gemv_generic(const QMat &m, const float *x, float *out, cudaStream_t stream);

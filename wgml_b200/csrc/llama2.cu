@@ -48,8 +48,9 @@ struct wgb_llama2 {
     uint32_t *argmax_scratch = nullptr;
     uint32_t *d_prompt = nullptr, *d_out = nullptr;
     size_t prompt_cap = 0, out_cap = 0;
-    uint32_t *h_pinned = nullptr;            // pinned staging of a decode call: [0] status word, [1..] token ids
+    uint32_t *h_pinned = nullptr;            // pinned staging of a decode call: [0] status word, [1..2] status polls, [3..] token ids
     size_t pinned_cap = 0;
+    StatusPoll poll;
     bool fused = true, use_pdl = true;
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_n_prompt = 0;
@@ -62,6 +63,7 @@ struct wgb_llama2 {
     uint32_t *flag_peer[PEER_MAX] = {};      // rank p's flags: [2 * n_layers][tp]
     uint32_t *tickets = nullptr;             // local: one per exchange
     uint32_t *tp_epoch = nullptr;            // local: forwards so far
+    bool exchange_external = false;          // mailboxes and flags were mapped by the caller (wgb_llama2_set_exchange_buffers)
     int kernels_per_token = 0;
     // per-launch timing of wgb_llama2_profile_step: one event after every launch
     bool profiling = false;
@@ -385,6 +387,21 @@ void drop_graph(wgb_llama2 *m)
     m->graph = nullptr;
 }
 
+// Local counters of the direct exchange: one ticket per exchange and the step count.
+int alloc_exchange_counters(wgb_llama2 *m)
+{
+    const size_t n_ex = 2 * (size_t)m->cfg.n_layers;
+    if (!m->tickets) {
+        WGB_CUDA(cudaMalloc((void **)&m->tickets, n_ex * sizeof(uint32_t)));
+        WGB_CUDA(cudaMemset(m->tickets, 0, n_ex * sizeof(uint32_t)));
+    }
+    if (!m->tp_epoch) {
+        WGB_CUDA(cudaMalloc((void **)&m->tp_epoch, sizeof(uint32_t)));
+        WGB_CUDA(cudaMemset(m->tp_epoch, 0, sizeof(uint32_t)));
+    }
+    return WGB_OK;
+}
+
 }  // namespace
 
 WGB_EXPORT int wgb_llama2_create(const wgb_llama2_config *cfg, int model_type, int tp_rank, int tp_size, wgb_llama2 **out)
@@ -472,6 +489,9 @@ WGB_EXPORT int wgb_llama2_destroy(wgb_llama2 *m)
     if (m->stamps) cudaFree(m->stamps);
     if (m->tickets) cudaFree(m->tickets);
     if (m->tp_epoch) cudaFree(m->tp_epoch);
+    m->stamps = nullptr;
+    m->tickets = m->tp_epoch = nullptr;
+    status_poll_destroy(m->poll);
     uint32_t *ubufs[] = { m->attn_counters, m->scalars, m->argmax_scratch, m->d_prompt, m->d_out };
     for (uint32_t *b : ubufs) if (b) cudaFree(b);
     if (m->h_pinned) cudaFreeHost(m->h_pinned);
@@ -668,12 +688,11 @@ WGB_EXPORT int wgb_llama2_set_exchange(wgb_llama2 *m, int mode)
         drop_graph(m);
         return WGB_OK;
     }
-    WGB_REQUIRE(m->comm, "set the communicator first");
     WGB_REQUIRE(m->tp_size <= PEER_MAX, "direct exchange supports at most %d ranks", PEER_MAX);
     if (!m->mail_peer[0]) {
-        const size_t n_ex = 2 * (size_t)m->cfg.n_layers;
-        const size_t mail_bytes = n_ex * m->tp_size * m->cfg.dim * sizeof(float);
-        const size_t flag_bytes = n_ex * m->tp_size * sizeof(uint32_t);
+        WGB_REQUIRE(m->comm, "set the communicator first (or map the buffers yourself: wgb_llama2_set_exchange_buffers)");
+        size_t mail_bytes = 0, flag_bytes = 0;
+        wgb_llama2_exchange_bytes(m, &mail_bytes, &flag_bytes);
         void *peers[PEER_MAX] = {};
         int rc = wgb_comm_shared_alloc((wgb_comm *)m->comm, mail_bytes + flag_bytes, peers);
         if (rc) return rc;
@@ -681,11 +700,39 @@ WGB_EXPORT int wgb_llama2_set_exchange(wgb_llama2 *m, int mode)
             m->mail_peer[p] = (float *)peers[p];
             m->flag_peer[p] = (uint32_t *)((char *)peers[p] + mail_bytes);
         }
-        WGB_CUDA(cudaMalloc((void **)&m->tickets, n_ex * sizeof(uint32_t)));
-        WGB_CUDA(cudaMemset(m->tickets, 0, n_ex * sizeof(uint32_t)));
-        WGB_CUDA(cudaMalloc((void **)&m->tp_epoch, sizeof(uint32_t)));
-        WGB_CUDA(cudaMemset(m->tp_epoch, 0, sizeof(uint32_t)));
     }
+    int rc = alloc_exchange_counters(m);
+    if (rc) return rc;
+    m->exchange = 1;
+    drop_graph(m);
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_exchange_bytes(const wgb_llama2 *m, size_t *mail_bytes, size_t *flag_bytes)
+{
+    WGB_REQUIRE(m && mail_bytes && flag_bytes, "null argument");
+    const size_t n_ex = 2 * (size_t)m->cfg.n_layers;
+    *mail_bytes = n_ex * m->tp_size * m->cfg.dim * sizeof(float);
+    *flag_bytes = n_ex * m->tp_size * sizeof(uint32_t);
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_set_exchange_buffers(wgb_llama2 *m, void *const *d_mail, void *const *d_flags)
+{
+    WGB_REQUIRE(m && d_mail && d_flags, "null argument");
+    WGB_REQUIRE(m->tp_size > 1 && m->tp_size <= PEER_MAX, "direct exchange wants 2..%d ranks, the model has %d", PEER_MAX, m->tp_size);
+    WGB_REQUIRE(!m->mail_peer[0] || m->exchange_external, "the exchange buffers of this model were already allocated through its communicator");
+    for (int p = 0; p < m->tp_size; p++) {
+        WGB_REQUIRE(d_mail[p] && d_flags[p], "rank %d: null buffer", p);
+        WGB_REQUIRE(((uintptr_t)d_mail[p] % 16) == 0 && ((uintptr_t)d_flags[p] % 4) == 0, "rank %d: misaligned buffer", p);
+    }
+    for (int p = 0; p < m->tp_size; p++) {
+        m->mail_peer[p] = (float *)d_mail[p];
+        m->flag_peer[p] = (uint32_t *)d_flags[p];
+    }
+    m->exchange_external = true;
+    int rc = alloc_exchange_counters(m);
+    if (rc) return rc;
     m->exchange = 1;
     drop_graph(m);
     return WGB_OK;
@@ -706,7 +753,7 @@ WGB_EXPORT int wgb_llama2_forward(wgb_llama2 *m, uint32_t token, uint32_t pos, v
     if (rc) return rc;
     WGB_REQUIRE(token < m->cfg.vocab_size, "token %u outside a vocabulary of %u", token, m->cfg.vocab_size);
     WGB_REQUIRE(pos < m->cfg.seq_len, "position %u outside a context of %u", pos, m->cfg.seq_len);
-    WGB_REQUIRE(m->tp_size == 1 || m->comm, "tensor-parallel model without a communicator");
+    WGB_REQUIRE(m->tp_size == 1 || m->comm || (m->exchange == 1 && m->exchange_external), "tensor-parallel model without a communicator");
     cudaStream_t s = as_stream(stream);
     set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, token, pos, 0);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
@@ -782,8 +829,6 @@ static int profile_stamped(wgb_llama2 *m, cudaStream_t s, int cap, int *kinds, i
     const size_t need = 5 * (size_t)m->cfg.n_layers + 2;
     if (need > m->stamps_cap) {
         if (m->stamps) cudaFree(m->stamps);
-    if (m->tickets) cudaFree(m->tickets);
-    if (m->tp_epoch) cudaFree(m->tp_epoch);
         m->stamps = nullptr;
         m->stamps_cap = 0;
         WGB_CUDA(cudaMalloc((void **)&m->stamps, need * sizeof(unsigned long long)));
@@ -875,7 +920,7 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
                 m->cfg.seq_len);
     for (size_t i = 0; i < n_prompt; i++)
         WGB_REQUIRE(h_prompt[i] < m->cfg.vocab_size, "prompt token %u outside a vocabulary of %u", h_prompt[i], m->cfg.vocab_size);
-    WGB_REQUIRE(m->tp_size == 1 || m->comm, "tensor-parallel model without a communicator");
+    WGB_REQUIRE(m->tp_size == 1 || m->comm || (m->exchange == 1 && m->exchange_external), "tensor-parallel model without a communicator");
     cudaStream_t s = as_stream(stream);
     if (n_prompt > m->prompt_cap) {
         if (m->d_prompt) cudaFree(m->d_prompt);
@@ -893,12 +938,12 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
         WGB_CUDA(cudaMalloc((void **)&m->d_out, total * 4));
         m->out_cap = total;
     }
-    if (total + 1 > m->pinned_cap) {
+    if (total + 3 > m->pinned_cap) {
         if (m->h_pinned) cudaFreeHost(m->h_pinned);
         m->h_pinned = nullptr;
         m->pinned_cap = 0;
-        WGB_CUDA(cudaMallocHost((void **)&m->h_pinned, (total + 1) * 4));
-        m->pinned_cap = total + 1;
+        WGB_CUDA(cudaMallocHost((void **)&m->h_pinned, (total + 3) * 4));
+        m->pinned_cap = total + 3;
     }
     // the first token travels as a kernel argument; the rest of the prompt is only read when there is one
     if (n_prompt > 1) WGB_CUDA(cudaMemcpyAsync(m->d_prompt, h_prompt, n_prompt * 4, cudaMemcpyHostToDevice, s));
@@ -947,12 +992,12 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
         m->graph_n_prompt = (uint32_t)n_prompt;
         m->graph_attn_chunks = (uint32_t)attn_class;
     }
-    for (size_t i = 0; i < total; i++) WGB_CUDA(cudaGraphLaunch(m->graph, s));
+    if ((rc = replay_with_status(m->graph, total, s, m->h_pinned + 1, m->poll))) return rc;
     // One wait for the ids and the kernels' status word, both through pinned memory.
-    WGB_CUDA(cudaMemcpyAsync(m->h_pinned + 1, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
+    WGB_CUDA(cudaMemcpyAsync(m->h_pinned + 3, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
     m->h_pinned[0] = 0;
     if (gemv_status_word()) WGB_CUDA(cudaMemcpyAsync(m->h_pinned, gemv_status_word(), 4, cudaMemcpyDeviceToHost, s));
     WGB_CUDA(cudaStreamSynchronize(s));
-    memcpy(h_out_tokens, m->h_pinned + 1, total * 4);
+    memcpy(h_out_tokens, m->h_pinned + 3, total * 4);
     return gemv_report_status(m->h_pinned[0]);
 }

@@ -348,13 +348,14 @@ WGB_EXPORT int wgb_op_assign(int kind, float *d_lhs, const float *d_rhs, size_t 
     return WGB_OK;
 }
 
-// Partial keys of the stand-alone argmax; allocated once per process.
-static unsigned long long *g_argmax_part = nullptr;
-
 WGB_EXPORT int wgb_argmax(const float *d_v, size_t n, uint32_t *d_index, void *stream)
 {
     WGB_REQUIRE(d_v && d_index && n > 0 && n <= 0xffffffffull, "bad argmax arguments");
-    if (!g_argmax_part) WGB_CUDA(cudaMalloc((void **)&g_argmax_part, ARGMAX_BLOCKS * sizeof(unsigned long long)));
+    // partial keys: allocated once per device
+    DeviceState *ds = device_state();
+    if (!ds) return WGB_ERR_CUDA;
+    if (!ds->argmax_part) WGB_CUDA(cudaMalloc((void **)&ds->argmax_part, ARGMAX_BLOCKS * sizeof(unsigned long long)));
+    unsigned long long *g_argmax_part = ds->argmax_part;
     argmax_partial_kernel<<<ARGMAX_BLOCKS, OPS_NT, 0, as_stream(stream)>>>(d_v, (uint32_t)n, g_argmax_part);
     WGB_LAUNCH_CHECK("argmax_partial_kernel");
     LoopState none = {};

@@ -124,6 +124,21 @@ class Llama2:
         mailboxes by the kernels (collective call: every rank, same mode)."""
         check(_lib.load().wgb_llama2_set_exchange(self._h, int(mode)))
 
+    def exchange_bytes(self) -> tuple[int, int]:
+        """Sizes (mailbox bytes, flag bytes) of one rank's exchange buffers for the direct exchange."""
+        a, b = C.c_size_t(), C.c_size_t()
+        check(_lib.load().wgb_llama2_exchange_bytes(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def set_exchange_buffers(self, mail_ptrs, flag_ptrs) -> None:
+        """Direct exchange over buffers the host mapped itself: entry p is rank p's mailbox / flag array as seen
+        from this process (device pointers as ints), entry [tp_rank] this rank's own."""
+        n = self.tp_size
+        assert len(mail_ptrs) == n and len(flag_ptrs) == n
+        mail = (C.c_void_p * n)(*[C.c_void_p(int(p)) for p in mail_ptrs])
+        flags = (C.c_void_p * n)(*[C.c_void_p(int(p)) for p in flag_ptrs])
+        check(_lib.load().wgb_llama2_set_exchange_buffers(self._h, mail, flags))
+
     def dispatch(self, token: int, pos: int) -> None:
         """Llama2::dispatch for one token (enqueued on the current stream; logits stay on the device)."""
         check(_lib.load().wgb_llama2_forward(self._h, token, pos, torch.cuda.current_stream().cuda_stream))
@@ -165,7 +180,9 @@ class Llama2:
     PROFILE_KINDS = ["embed", "qkv_rope", "attention", "attn_output", "gate_up_silu", "ffn_down", "logits", "unfused_layer"]
 
     def profile_step(self, token: int, pos: int):
-        """One eager forward with an event after every launch: list of (kind name, layer, milliseconds)."""
+        """Times every launch of one token forward: list of (kind name, layer, milliseconds).  The fused schedule
+        is replayed as the CUDA graph a decode step runs, each launch writing its end time to device memory
+        (time = distance to the predecessor's end); the other schedules get an event after every launch."""
         cap = 32 * self.config.n_layers + 16
         kinds, layers, ms, n = (C.c_int * cap)(), (C.c_int * cap)(), (C.c_float * cap)(), C.c_int()
         check(_lib.load().wgb_llama2_profile_step(self._h, token, pos, torch.cuda.current_stream().cuda_stream, cap,

@@ -130,6 +130,87 @@ def init_from_torch_distributed() -> Comm:
     return Comm(box[0], rank, size)
 
 
+def set_wait_limit_ms(ms: int) -> None:
+    """How long a kernel waits for the other ranks' flags before the decode call fails with a time-out
+    (process-wide; default 2000 ms)."""
+    check(_lib.load().wgb_set_wait_limit_ms(int(ms)))
+
+
+class PeerLost(RuntimeError):
+    """A rank of the group has left or stopped answering; raised on the host, before anything is launched."""
+
+
+class PeerWatch:
+    """Host-side liveness of a tensor-parallel group, checked between decode calls.
+
+    The kernels of the direct exchange wait for one another on the device, so a rank must never launch a
+    step that a peer will not join.  Every rank publishes the number of the step it is about to launch in a
+    key-value store shared by the group (any ``torch.distributed`` store: the TCPStore of the rendezvous, a
+    FileStore, ...) and, before launching, waits at most `timeout_s` for every peer to have published the same
+    step.  A rank that leaves in an orderly way says so (`leave`), and its peers learn of it at their next
+    check without waiting.  No device is involved; the device-side wait limit (`set_wait_limit_ms`) stays as
+    the second line of defence for a rank that dies in the middle of a step."""
+
+    def __init__(self, store, rank: int, size: int, timeout_s: float = 5.0, prefix: str = "wgb_tp"):
+        self.store, self.rank, self.size, self.timeout_s, self.prefix = store, rank, size, timeout_s, prefix
+        self.step = 0
+
+    def _key(self, kind: str, rank: int, step: int | None = None) -> str:
+        return f"{self.prefix}/{kind}/{rank}" + ("" if step is None else f"/{step}")
+
+    def check(self) -> int:
+        """Call before every launch (decode call).  Returns the step number; raises PeerLost."""
+        import datetime
+        step = self.step
+        try:
+            self.store.set(self._key("step", self.rank, step), b"1")
+            for p in range(self.size):
+                if p == self.rank:
+                    continue
+                if self.store.check([self._key("left", p)]):
+                    raise PeerLost(f"rank {p} left the group before step {step}")
+            keys = [self._key("step", p, step) for p in range(self.size) if p != self.rank]
+            if keys:
+                deadline = datetime.timedelta(seconds=self.timeout_s)
+                # poll in short slices so that a rank that says good-bye while we wait is noticed at once
+                import time
+                t_end = time.monotonic() + self.timeout_s
+                while True:
+                    try:
+                        self.store.wait(keys, min(deadline, datetime.timedelta(milliseconds=100)))
+                        break
+                    except PeerLost:
+                        raise
+                    except Exception:
+                        for p in range(self.size):
+                            if p != self.rank and self.store.check([self._key("left", p)]):
+                                raise PeerLost(f"rank {p} left the group before step {step}")
+                        if time.monotonic() >= t_end:
+                            missing = [p for p in range(self.size) if p != self.rank
+                                       and not self.store.check([self._key("step", p, step)])]
+                            raise PeerLost(f"ranks {missing} did not reach step {step} within {self.timeout_s} s")
+        except PeerLost:
+            raise
+        except Exception as e:   # the store itself is gone (its host rank died)
+            raise PeerLost(f"the group's store stopped answering at step {step}: {e}") from e
+        self.step += 1
+        return step
+
+    def leave(self) -> None:
+        """Tells the peers that this rank will launch nothing more (call between steps, nothing in flight)."""
+        try:
+            self.store.set(self._key("left", self.rank), b"1")
+        except Exception:
+            pass
+
+
+def guarded_decode(model, watch: PeerWatch, prompt, n_gen: int, start_pos: int = 0):
+    """``model.decode`` preceded by the group's liveness check: raises PeerLost instead of launching a step that
+    a peer will not join."""
+    watch.check()
+    return model.decode(prompt, n_gen, start_pos=start_pos)
+
+
 def attach(model, comm: Comm, direct: bool = True) -> None:
     """Gives a tensor-parallel ``Llama2`` its group; must precede the first forward.  `direct`: the kernels
     exchange partial products through peer memory themselves instead of calling NCCL's all-reduce."""
