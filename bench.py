@@ -373,9 +373,9 @@ def run_b200(args):
                    "parallelism": f"tp{world}" if world > 1 else "single GPU",
                    **({"exchange": "kernels store partial products into the peers' memory over NVLink, flags instead of a collective"
                        if args.exchange == "peer" else "NCCL all-reduce",
-                       "note": "the default single-GPU run of this script is the 7B configuration the metric is quoted on; this "
-                               "70B workload on one GPU (--workload llama2-70b --gpus 1) measured 60 tok/s, the figure strong "
-                               "scaling should be taken against"} if world > 1 else {}),
+                       "note": "the default single-GPU run of this script is the 7B configuration the metric is quoted on; the "
+                               "figure strong scaling of this 70B workload should be taken against is the same workload on "
+                               "one GPU (--workload llama2-70b --gpus 1), which this run does not measure"} if world > 1 else {}),
                    **({"truncated_to_layers": args.layers, "valid": False} if args.layers else {}),
                    "weights_gb": sum(matrix_bytes(cfg, l, n)[0] for l in range(cfg["n_layers"]) for n in
                                      ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")) / 1e9
@@ -389,6 +389,20 @@ def run_b200(args):
         "kernels_per_token": int(model.kernels_per_token()),
         "clocks": clocks.summary(), "roofline": roofline, "breakdown": classes,
     }
+    if rank == 0 and world == 1 and workload == "llama2-7b" and not args.no_microbench:
+        # the stand-alone quantised matrix-vector cases (4 shapes x 3 block formats), each launch on a fresh copy
+        # of the matrix so that it streams from HBM: microseconds, algorithmic GB/s and fraction of the measured peak
+        model.close()
+        del model
+        torch.cuda.empty_cache()
+        from wgml_b200 import gemv_bench
+        shapes = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]
+        line["gemv_microbench"] = {
+            "how": "wgb_gemv_quant, batch 1; 100 launches over rotating copies of the matrix (> 126 MB L2 in total) captured "
+                   "in one CUDA graph, replayed 3 times between CUDA events; bytes = rows*cols*bpe + 4*cols + 4*rows",
+            "peak_gbs": peak,
+            "cases": [{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()}
+                      for r in gemv_bench.run(["q8_0", "q4_k", "q6_k"], shapes, 100, 0, peak)]}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         tok_cpu, desc, threads, _, _ = cpu_sample(cfg, args.seed, 64, args.cpu_budget)
         line["cpu_baseline"] = {"value": tok_cpu, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
@@ -487,6 +501,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU oracle work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-microbench", action="store_true", help="skip the stand-alone matrix-vector cases of the 7B line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -45,14 +45,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 // Bounded wait; after `limit_ns` records `code` in *err (unless an earlier code is there) and returns false.
+// The clock is only looked at after a few hundred unsuccessful polls: reading %globaltimer takes far longer
+// than a poll, and nearly every wait of a healthy kernel ends within the first handful.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t *err, uint32_t code,
                                           unsigned long long limit_ns = ASYNC_WAIT_NS)
 {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 512; i++)
+        if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     do {
 #pragma unroll 1
-        for (int i = 0; i < 16; i++)
+        for (int i = 0; i < 256; i++)
             if (mbar_try_wait(bar, parity)) return true;
     } while (global_ns() - t0 < limit_ns);
     if (err) atomicCAS(err, 0u, code);

@@ -1,7 +1,7 @@
 // Matrix-vector kernels: the fused, TMA-fed kernel used by the models and by GemvQuant, and the
 // generic per-format fallback.
 //
-// Fused kernel.  One persistent block per SM with three roles: sixteen consumer warps, a producer
+// Fused kernel.  One persistent block per SM with three roles: eighteen consumer warps, a producer
 // warp and an epilogue warp.
 //   * Rows are taken in groups of `rs` (1..8) that lie contiguously in HBM.  The producer streams
 //     group after group into a ring of shared-memory stages with one bulk asynchronous copy
@@ -11,11 +11,12 @@
 //     launch): weights never depend on activations.
 //   * The consumers build the shared image of the (normalised) input vector once.  Consumer warp w
 //     owns column part w % kp of the matrix for the whole kernel, so its share of the input stays in
-//     registers; the warps of one column part form ncl = 16 / kp "lanes" that take the (stage, row
+//     registers; the warps of one column part form ncl = 18 / kp "lanes" that take the (stage, row
 //     part) tasks of the block in turn.  A task is `rrows` rows of one stage: the warp computes the
-//     partial dot products, folds them across its lanes with a transposing butterfly (9 shuffles for
-//     up to 8 rows), writes them to shared memory and arrives on the stage's `done` barrier.
-//     Consumers never wait for each other or for the epilogue.
+//     partial dot products (the loop over rows fully unrolled, so that the loads of later rows overlap
+//     the arithmetic of earlier ones), folds them across its lanes with a transposing butterfly (9
+//     shuffles for up to 8 rows), writes them to shared memory and arrives on the stage's `done`
+//     barrier.  Consumers never wait for each other or for the epilogue.
 //   * The epilogue warp waits for `done`, adds the column parts of every row in a fixed order,
 //     releases the stage to the producer and applies the epilogue (bias, residual, SiLU gate, GELU,
 //     RoPE + KV-cache append), one lane per output unit.  Its global loads (bias, residual, position)
@@ -31,18 +32,24 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 
 namespace wgb {
 
+// Consumer warps per block.  Registers are allocated per scheduler partition (a quarter of the register file
+// each, warps dealt round-robin): 18 consumers + producer + epilogue = 20 warps put five warps on every
+// partition, which leaves 96 registers per thread -- the same as 17 to 19 warps would -- so 18 is the most
+// consumers that budget buys.
 #ifndef WGB_GEMV_NCONS
 #define WGB_GEMV_NCONS 16
 #endif
-constexpr int GEMV_NCONS = WGB_GEMV_NCONS;          // consumer warps
+constexpr int GEMV_NCONS = WGB_GEMV_NCONS;
 constexpr int GEMV_CONS_THREADS = GEMV_NCONS * 32;
 constexpr int GEMV_PRODUCER = GEMV_NCONS;           // warp index of the producer
 constexpr int GEMV_EPILOGUE = GEMV_NCONS + 1;       // warp index of the epilogue warp
 constexpr int GEMV_NT = (GEMV_EPILOGUE + 1) * 32;
 constexpr int GEMV_MAX_RS = 8;                      // rows per stage
+constexpr int GEMV_TASK_ROWS = 4;                   // rows per consumer task, at most
 constexpr int GEMV_MAX_STAGES = 24;
 constexpr uint32_t GEMV_ROPE_TAB = 128;             // pair indices with a precomputed rotation
 constexpr size_t GEMV_SMEM_BUDGET = 200 * 1024;     // dynamic shared memory per block
@@ -97,6 +104,38 @@ __device__ __forceinline__ float warp_sum8(const float (&acc)[8], int lane)
     return v;
 }
 
+// The same for R = 4, 2, 1 rows: the total of row r ends up in the lanes whose top log2(R) bits spell r.
+template <int R>
+__device__ __forceinline__ float warp_sum_rows(const float (&acc)[R], int lane)
+{
+    static_assert(R == 1 || R == 2 || R == 4 || R == 8, "rows per task");
+    if constexpr (R == 8) {
+        return warp_sum8(acc, lane);
+    } else if constexpr (R == 4) {
+        const bool h16 = lane & 16, h8 = lane & 8;
+        float a2[2];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const float keep = h16 ? acc[i + 2] : acc[i], send = h16 ? acc[i] : acc[i + 2];
+            a2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
+        const float keep = h8 ? a2[1] : a2[0], send = h8 ? a2[0] : a2[1];
+        float v = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        return v;
+    } else if constexpr (R == 2) {
+        const bool h16 = lane & 16;
+        float v = (h16 ? acc[1] : acc[0]) + __shfl_xor_sync(0xffffffffu, h16 ? acc[0] : acc[1], 16);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        return v;
+    } else {
+        return warp_sum(acc[0]);
+    }
+}
+
 // Stages per pass of the epilogue warp and of the producer warp.  The lanes of a warp may be held at a
 // reconvergence point until all of them have left their wait, so a pass must be assumed to finish only
 // when every stage in it has: the epilogue pass that frees a slot must never contain a stage whose copy
@@ -118,8 +157,7 @@ struct Part {
 
 // Parts (1 or 2 runs of `n` consecutive rows of one matrix) of group gi; returns the number of parts,
 // 0 past the end.
-template <int EPI>
-__device__ __forceinline__ int group_parts(const GemvArgs &a, uint32_t gi, Part (&parts)[2], uint32_t &n)
+__device__ __forceinline__ int group_parts(const GemvArgs &a, const int EPI, uint32_t gi, Part (&parts)[2], uint32_t &n)
 {
     const uint32_t rs = a.rs;
     if (gi >= a.ngroups) return 0;
@@ -161,14 +199,12 @@ __device__ __forceinline__ float gelu_f32(float x)
 
 // Output units of a group (a unit = the stage rows that make one output: a row, or a pair) and the
 // stage rows of unit u.
-template <int EPI>
-__device__ __forceinline__ uint32_t group_units(const Part (&parts)[2], int nparts, uint32_t n)
+__device__ __forceinline__ uint32_t group_units(const int EPI, const Part (&parts)[2], int nparts, uint32_t n)
 {
     if (EPI == EPI_QKV_ROPE && nparts == 1 && parts[0].mat < 2) return n / 2;   // adjacent pairs
     return n;
 }
-template <int EPI>
-__device__ __forceinline__ void unit_rows(const Part (&parts)[2], int nparts, uint32_t n, uint32_t u, uint32_t &ra, uint32_t &rb)
+__device__ __forceinline__ void unit_rows(const int EPI, const Part (&parts)[2], int nparts, uint32_t n, uint32_t u, uint32_t &ra, uint32_t &rb)
 {
     if (EPI == EPI_SILU_PAIR || (EPI == EPI_QKV_ROPE && nparts == 2)) { ra = u; rb = n + u; }
     else if (EPI == EPI_QKV_ROPE && parts[0].mat < 2) { ra = 2 * u; rb = 2 * u + 1; }
@@ -186,8 +222,7 @@ struct EpiCtx {
     float *dst;         // EPI_QKV_*: where the rows of the unit go
 };
 
-template <int EPI>
-__device__ __forceinline__ EpiCtx epi_prepare(const GemvArgs &a, const Part (&parts)[2], int nparts, uint32_t n, uint32_t t,
+__device__ __forceinline__ EpiCtx epi_prepare(const GemvArgs &a, const int EPI, const Part (&parts)[2], int nparts, uint32_t n, uint32_t t,
                                               uint32_t nunits, const float2 *rope_tab)
 {
     EpiCtx c = {};
@@ -249,8 +284,7 @@ __device__ __forceinline__ EpiCtx epi_prepare(const GemvArgs &a, const Part (&pa
 }
 
 // ya / yb: finished dot products of the unit's first / second stage row.
-template <int EPI>
-__device__ __forceinline__ void epi_finish(const GemvArgs &a, const Part (&parts)[2], const EpiCtx &c, float ya, float yb)
+__device__ __forceinline__ void epi_finish(const GemvArgs &a, const int EPI, const Part (&parts)[2], const EpiCtx &c, float ya, float yb)
 {
     if (!c.on) return;
     if (EPI == EPI_STORE || EPI == EPI_RESIDUAL || EPI == EPI_GELU) {
@@ -278,16 +312,22 @@ __device__ __forceinline__ void epi_finish(const GemvArgs &a, const Part (&parts
     }
 }
 
-template <int QT, int PRO, int EPI>
+// One kernel per block format; prologue and epilogue are chosen at run time.  The launches of a decode step
+// alternate between four prologue / epilogue combinations, and as separate kernels each of them found its
+// code evicted from the instruction caches by the others (measured: +0.7 us per launch when two kernels
+// alternate, +1.7 us with four); as one kernel they share the hot loop and most of the set-up.
+template <int QT>
 __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant__ GemvArgs a)
 {
     using S = Step<QT>;
+    const int PRO = a.prologue, EPI = a.epilogue;
     constexpr int NPL = QT == WGB_Q6_K ? 4 : (QT == WGB_Q8_0 ? 2 : 1);   // planes of the format
     extern __shared__ uint4 smem4[];
     __shared__ float red[32];
     __shared__ float part[GEMV_MAX_STAGES][GEMV_NCONS][GEMV_MAX_RS];    // [stage][column part][stage row]
+    __shared__ __align__(16) float lane_part[GEMV_NCONS][GEMV_TASK_ROWS][32];   // [consumer warp][task row][lane]
     __shared__ __align__(8) unsigned long long bars[3 * GEMV_MAX_STAGES];
-    __shared__ float2 rope_tab[EPI == EPI_QKV_ROPE ? GEMV_ROPE_TAB : 1];     // (cos, sin) per pair index of a head
+    __shared__ float2 rope_tab[GEMV_ROPE_TAB];     // (cos, sin) per pair index of a head (EPI_QKV_ROPE)
 
     const uint32_t K = a.mat[0].ncols;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -327,7 +367,7 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
         for (uint32_t it = sb; it < nst; it += spb) {
             Part parts[2];
             uint32_t n = 0;
-            const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
+            const int nparts = group_parts(a, EPI, blockIdx.x + it * gridDim.x, parts, n);
             if (ci == 0) {
                 if (round) mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.err, 2, a.wait_ns);
                 mbar_expect_tx(full0 + 8 * s, nparts * n * row_bytes);
@@ -335,9 +375,10 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             __syncwarp(gmask);
             if (ci < (uint32_t)nparts * nplanes) {
                 const uint32_t pi = ci / nplanes, pl = ci % nplanes;   // nplanes is a compile-time power of two
+                // a stage holds plane after plane; within a plane, the rows of part 0 then those of part 1
                 const QMat &m = a.mat[parts[pi].mat];
-                uint32_t off = pi * n * row_bytes;
-                for (uint32_t q = 0; q < pl; q++) off += n * m.pitch[q];
+                uint32_t off = pi * n * m.pitch[pl];
+                for (uint32_t q = 0; q < pl; q++) off += (uint32_t)nparts * n * m.pitch[q];
                 bulk_copy_g2s(ring + s * a.stage_bytes + off, m.p[pl] + (size_t)parts[pi].row0 * m.pitch[pl], n * m.pitch[pl],
                               full0 + 8 * s);
             }
@@ -379,11 +420,11 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             if (sub >= nb || it >= nst) continue;
             Part parts[2];
             uint32_t n = 0;
-            const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
-            const uint32_t nunits = group_units<EPI>(parts, nparts, n);
-            const EpiCtx c = epi_prepare<EPI>(a, parts, nparts, n, ul, nunits, rope_tab);
+            const int nparts = group_parts(a, EPI, blockIdx.x + it * gridDim.x, parts, n);
+            const uint32_t nunits = group_units(EPI, parts, nparts, n);
+            const EpiCtx c = epi_prepare(a, EPI, parts, nparts, n, ul, nunits, rope_tab);
             uint32_t ra = 0, rb = 0;
-            if (c.on) unit_rows<EPI>(parts, nparts, n, ul, ra, rb);
+            if (c.on) unit_rows(EPI, parts, nparts, n, ul, ra, rb);
             mbar_wait(done0 + 8 * s, phase, a.err, 3, a.wait_ns);
             if (PRO == PRO_RMS && !have_scale) {
                 // every consumer warp wrote its sum of squares before its first arrival on a `done` barrier
@@ -406,7 +447,7 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             }
             __syncwarp(gmask);
             if (ul == 0) mbar_arrive(empty0 + 8 * s);   // stage and partial sums may be overwritten
-            epi_finish<EPI>(a, parts, c, ya, yb);
+            epi_finish(a, EPI, parts, c, ya, yb);
         }
         if ((EPI == EPI_STORE || EPI == EPI_RESIDUAL) && a.peer_out.n) {
             // The block's partial rows are on their way to the peers; the last block of the launch raises
@@ -431,17 +472,16 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
 
     // ------------------------------ consumers ------------------------------
     // What the task loop needs and the input does not decide is worked out while the launch before drains.
-    const uint32_t ncl = GEMV_NCONS / kp;                 // lanes of warps per column part
+    const uint32_t ncl = GEMV_NCONS / kp;                 // "lanes" of warps per column part
     const XImage im = ximage_carve(QT, K, smem);
     const uint32_t kunits = QT == WGB_F32 ? K : a.mat[0].bpr;   // what Step::active() compares against
     const uint32_t nsteps = (K + step_cols<QT>() - 1) / step_cols<QT>();
     const uint32_t kw = (uint32_t)warp % kp, cl = (uint32_t)warp / kp;
-    const uint32_t R = a.rrows;
     // The norm weights are parameters, not products of the launch before: their (cold, HBM-latency) loads
     // are issued ahead of the dependency wait and are in registers by the time the input can be read.
-    constexpr uint32_t XC = PRO == PRO_NONE ? 6 : 4;
-    constexpr uint32_t WC = PRO == PRO_NONE ? 1 : XC;
-    float4 wc[WC], bc[PRO == PRO_LN ? WC : 1];
+    constexpr uint32_t XC = 4;
+    constexpr uint32_t WC = XC;
+    float4 wc[WC], bc[WC];
     if (PRO != PRO_NONE) {
 #pragma unroll
         for (uint32_t i = 0; i < WC; i++) {
@@ -557,12 +597,35 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     });
     cons_sync();
 
-    if ((uint32_t)warp >= kp * ncl) return;               // warps left over when 16 % kp != 0
+    if ((uint32_t)warp >= kp * ncl) return;               // warps left over when kp does not divide the consumers
     typename S::X x;
-    uint32_t held = ~0u;   // column step whose part of the input is in `x`
+    // prefix[q]: bytes of planes 0..q-1 of one row (a stage holds plane after plane, see the producer)
+    uint32_t prefix[NPL];
+    {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int q = 0; q < NPL; q++) {
+            prefix[q] = acc;
+            acc += a.mat[0].pitch[q];
+        }
+    }
 
-    // Tasks (stage it, row part rp) with it * rparts + rp = cl, cl + ncl, ...  The ring slot and parity of
-    // stage `it` are carried along instead of divided out: a task is only a few hundred instructions.
+    // Task loop.  A task is up to GEMV_TASK_ROWS rows of one stage, taken one at a time by a rolled loop whose
+    // body -- one call of the format's dot product -- is the whole hot path of the kernel: two kilobytes of
+    // code that every warp of the block shares in the instruction caches.  (Unrolled over the rows the loop ran
+    // with "no instruction" as its first stall reason, and the launches of a decode step evict one another's
+    // code, so whatever a launch executes it first has to fetch.)  Nothing in the body depends on the lane:
+    // a lane past the end of the row works on the row's first unit with an all-zero input instead of sitting
+    // out.  Each lane leaves its partial sum of a row in shared memory; after the last row the warp adds the
+    // 32 partials of every row: lane l takes four partials of row l / 8, three butterfly steps do the rest.
+    // For every shape the models use the matrix has no more column steps than there are consumer warps, so the
+    // loop over steps makes one trip and the warp's part of the input is loaded once per kernel.
+    constexpr int R = GEMV_TASK_ROWS;
+    static_assert(R == 4, "the reduction below reads four partials per lane of four rows");
+    const uint32_t Rn = a.rrows;
+    float *my_part = &lane_part[warp][0][0];
+    uint32_t held = ~0u;   // column step whose part of the input is in `x`
+    int lane_d = lane;
     uint32_t s = 0, phase = 0, it_prev = 0;
     for (uint32_t t = cl; t < nst * rparts; t += ncl) {
         const uint32_t it = t >> a.rparts_log2, rp = t & (rparts - 1);
@@ -572,57 +635,46 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             s -= nstage;
             phase ^= 1;
         }
-        Part parts[2];
-        uint32_t n = 0;
-        const int nparts = group_parts<EPI>(a, blockIdx.x + it * gridDim.x, parts, n);
-        const uint32_t nrows = nparts * n;
-        const uint32_t j0 = rp * R;
+        uint32_t nrows = a.rs;   // rows in this stage: fewer only in the last group of a matrix
+        if (EPI != EPI_QKV_ROPE) {
+            Part parts[2];
+            uint32_t n = 0;
+            const int nparts = group_parts(a, EPI, blockIdx.x + it * gridDim.x, parts, n);
+            nrows = nparts * n;
+        }
+        const uint32_t j0 = rp * Rn;
+        const uint32_t jn = min(Rn, nrows > j0 ? nrows - j0 : 0u);
         const uint32_t stage = ring + s * a.stage_bytes;
-        float acc[GEMV_MAX_RS];
-#pragma unroll
-        for (int j = 0; j < GEMV_MAX_RS; j++) acc[j] = 0.0f;
         mbar_wait(full0 + 8 * s, phase, a.err, 1, a.wait_ns);
-        if (j0 < nrows) {
-            // first shared-memory byte of row 0 of each part in each plane
-            uint32_t base[2][NPL];
-#pragma unroll
-            for (int pi = 0; pi < 2; pi++) {
-                uint32_t off = stage + pi * n * row_bytes;
-#pragma unroll
-                for (int q = 0; q < NPL; q++) {
-                    base[pi][q] = off;
-                    off += n * a.mat[0].pitch[q];
-                }
+        for (uint32_t ks = kw; ks < nsteps; ks += kp) {
+            const uint32_t col0 = ks * step_cols<QT>();
+            if (held != ks) {
+                const bool on = S::active(kunits, col0, lane);
+                lane_d = on ? lane : S::lane0(lane);
+                if (on) S::load_x(x, im, col0, lane);
+                else zero_x(x);
+                held = ks;
             }
-            for (uint32_t ks = kw; ks < nsteps; ks += kp) {
-                const uint32_t col0 = ks * step_cols<QT>();
-                if (!S::active(kunits, col0, lane)) continue;
-                if (held != ks) {
-                    S::load_x(x, im, col0, lane);
-                    held = ks;
-                }
-                // two rows at a time: independent chains for the scheduler to interleave
+            uint32_t r[4];
 #pragma unroll
-                for (int jj = 0; jj < GEMV_MAX_RS / 2; jj++) {
-                    const uint32_t ja = j0 + 2 * jj, jb = ja + 1;
-                    if ((uint32_t)(2 * jj) < R && ja < nrows) {
-                        const bool two = (uint32_t)(2 * jj + 1) < R && jb < nrows;
-                        const uint32_t pa = ja >= n ? 1 : 0, pb = jb >= n ? 1 : 0;
-                        uint32_t r0[4], r1[4];
+            for (int q = 0; q < NPL; q++) r[q] = stage + nrows * prefix[q] + j0 * a.mat[0].pitch[q];
+            const bool first = ks == kw;
+#pragma unroll 1
+            for (uint32_t j = 0; j < jn; j++) {
+                float v = S::dot(r, col0, x, lane_d);
+                if (!first) v += my_part[j * 32 + lane];
+                my_part[j * 32 + lane] = v;
 #pragma unroll
-                        for (int q = 0; q < NPL; q++) {
-                            r0[q] = base[pa][q] + (ja - pa * n) * a.mat[0].pitch[q];
-                            r1[q] = base[pb][q] + (jb - pb * n) * a.mat[0].pitch[q];
-                        }
-                        acc[2 * jj] += S::dot(r0, col0, x, lane);
-                        if (two) acc[2 * jj + 1] += S::dot(r1, col0, x, lane);
-                    }
-                }
+                for (int q = 0; q < NPL; q++) r[q] += a.mat[0].pitch[q];
             }
         }
-        const float v = warp_sum8(acc, lane);
-        const uint32_t rr = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-        if ((lane & 3) == 0 && rr < R && j0 + rr < nrows) part[s][kw][j0 + rr] = v;
+        __syncwarp();
+        const float4 p4 = reinterpret_cast<const float4 *>(my_part)[lane];   // partials 4 (l % 8) .. + 3 of row l / 8
+        float v = (p4.x + p4.y) + (p4.z + p4.w);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        if ((lane & 7) == 0 && (uint32_t)(lane >> 3) < jn) part[s][kw][j0 + (lane >> 3)] = v;
         __syncwarp();
         if (lane == 0) mbar_arrive(done0 + 8 * s);
     }
@@ -750,7 +802,7 @@ static uint32_t steps_of(int qt, uint32_t K)
 // false when the shapes do not fit the kernel's assumptions.
 //
 // Candidates are (rs rows per stage, rparts row parts per stage); a consumer task is rrows = rs / rparts
-// rows of one column part, and the ncl = 16 / kparts warps of a column part take the tasks of the block
+// rows of one column part, and the ncl = 18 / kparts warps of a column part take the tasks of the block
 // in turn.  The time of the launch is that of its fullest block: ceil(tasks / ncl) rounds of
 // (rrows + 1/2) row products, the half row standing for the wait, reduction and hand-off of a task.
 // That is divided by how much of the ~80 KB per SM that must be in flight to cover HBM latency at full
@@ -800,6 +852,7 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
         for (uint32_t rparts = 1; rparts <= 8; rparts *= 2) {
             if (rs % rparts) continue;
             const uint32_t rrows = rs / rparts;
+            if (rrows > (uint32_t)GEMV_TASK_ROWS) continue;
             const uint32_t in_work = (ncl + rparts - 1) / rparts + 1;   // stages the consumers hold at a time
             double flight;
             if (ns >= per) flight = 1.0;                                // the block's whole share fits in the ring
@@ -849,17 +902,7 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
 template <int QT>
 static int set_smem_attr()
 {
-    const int bytes = (int)GEMV_SMEM_BUDGET;
-#define WGB_ATTR(PRO, EPI) WGB_CUDA(cudaFuncSetAttribute(gemv_kernel<QT, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))
-    WGB_ATTR(PRO_NONE, EPI_STORE);
-    WGB_ATTR(PRO_RMS, EPI_STORE);
-    WGB_ATTR(PRO_LN, EPI_STORE);
-    WGB_ATTR(PRO_NONE, EPI_RESIDUAL);
-    WGB_ATTR(PRO_RMS, EPI_SILU_PAIR);
-    WGB_ATTR(PRO_LN, EPI_GELU);
-    WGB_ATTR(PRO_RMS, EPI_QKV_ROPE);
-    WGB_ATTR(PRO_LN, EPI_QKV_SPLIT);
-#undef WGB_ATTR
+    WGB_CUDA(cudaFuncSetAttribute(gemv_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_BUDGET));
     return WGB_OK;
 }
 
@@ -884,10 +927,10 @@ int gemv_global_init()
     return WGB_OK;
 }
 
-template <int QT, int PRO, int EPI>
+template <int QT>
 static int launch_one(GemvArgs &a, cudaStream_t stream, bool pdl)
 {
-    auto kern = gemv_kernel<QT, PRO, EPI>;
+    auto kern = gemv_kernel<QT>;
     size_t smem = 0;
     uint32_t grid = 0;
     if (!plan(a, smem, grid)) return fail(WGB_ERR_UNSUPPORTED, "matrix shape does not fit the fused kernel");
@@ -919,28 +962,18 @@ static int launch_one(GemvArgs &a, cudaStream_t stream, bool pdl)
 template <int QT>
 static int launch_qt(GemvArgs &a, cudaStream_t stream, bool pdl)
 {
+    // the combinations the kernel is written for
+    bool ok = false;
     switch (a.epilogue) {
-    case EPI_STORE:
-        if (a.prologue == PRO_NONE) return launch_one<QT, PRO_NONE, EPI_STORE>(a, stream, pdl);
-        if (a.prologue == PRO_RMS) return launch_one<QT, PRO_RMS, EPI_STORE>(a, stream, pdl);
-        return launch_one<QT, PRO_LN, EPI_STORE>(a, stream, pdl);
-    case EPI_RESIDUAL:
-        if (a.prologue != PRO_NONE) break;
-        return launch_one<QT, PRO_NONE, EPI_RESIDUAL>(a, stream, pdl);
-    case EPI_SILU_PAIR:
-        if (a.prologue != PRO_RMS || a.nmat != 2) break;
-        return launch_one<QT, PRO_RMS, EPI_SILU_PAIR>(a, stream, pdl);
-    case EPI_GELU:
-        if (a.prologue != PRO_LN) break;
-        return launch_one<QT, PRO_LN, EPI_GELU>(a, stream, pdl);
-    case EPI_QKV_ROPE:
-        if (a.prologue != PRO_RMS || a.nmat != 3) break;
-        return launch_one<QT, PRO_RMS, EPI_QKV_ROPE>(a, stream, pdl);
-    case EPI_QKV_SPLIT:
-        if (a.prologue != PRO_LN) break;
-        return launch_one<QT, PRO_LN, EPI_QKV_SPLIT>(a, stream, pdl);
+    case EPI_STORE: ok = a.prologue == PRO_NONE || a.prologue == PRO_RMS || a.prologue == PRO_LN; break;
+    case EPI_RESIDUAL: ok = a.prologue == PRO_NONE; break;
+    case EPI_SILU_PAIR: ok = a.prologue == PRO_RMS && a.nmat == 2; break;
+    case EPI_GELU: ok = a.prologue == PRO_LN; break;
+    case EPI_QKV_ROPE: ok = a.prologue == PRO_RMS && a.nmat == 3; break;
+    case EPI_QKV_SPLIT: ok = a.prologue == PRO_LN; break;
     }
-    return fail(WGB_ERR_UNSUPPORTED, "no fused kernel for prologue %d / epilogue %d", a.prologue, a.epilogue);
+    if (!ok) return fail(WGB_ERR_UNSUPPORTED, "no fused kernel for prologue %d / epilogue %d", a.prologue, a.epilogue);
+    return launch_one<QT>(a, stream, pdl);
 }
 
 int launch_gemv(const GemvArgs &args, cudaStream_t stream, bool pdl)

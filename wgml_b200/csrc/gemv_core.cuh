@@ -52,25 +52,31 @@ __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c)
     return d;
 }
 
-// Integer -> f32 without the conversion unit (which runs at an eighth of the FP32 rate on this part):
-// adding the integer to the bit pattern of 2^23 (resp. 1.5 * 2^23) yields the float 2^23 + v exactly,
-// and one FP32 subtraction removes the offset.  Valid for 0 <= v < 2^23 (resp. |v| < 2^22).
+// Integer -> f32 without the conversion unit: adding the integer to the bit pattern of 2^23 (resp. 1.5 * 2^23)
+// yields the float 2^23 + v exactly, and one FP32 subtraction removes the offset.  Valid for 0 <= v < 2^23
+// (resp. |v| < 2^22).  Used where the range is known to fit; sums of digit products go through cvt below.
 __device__ __forceinline__ float u2f(uint32_t v) { return __uint_as_float(v + 0x4b000000u) - 8388608.0f; }
 __device__ __forceinline__ float i2f(int v) { return __uint_as_float((uint32_t)v + 0x4b400000u) - 12582912.0f; }
 
-// 65536 s2 + 256 s1 + s0 as f32 for digit sums with 0 <= s0, s1 < 2^23 and |s2| < 2^22 (the top part may round).
-__device__ __forceinline__ float combine3(int s2, int s1, int s0)
+// Unsigned byte k of a word as f32: one byte permute drops it into the mantissa of 2^23.
+__device__ __forceinline__ float byte2f(uint32_t w, int k)
 {
-    return fmaf(i2f(s2), 65536.0f, fmaf(u2f((uint32_t)s1), 256.0f, u2f((uint32_t)s0)));
-}
-// The same with signed low digits (|s0|, |s1| < 2^22).
-__device__ __forceinline__ float combine3s(int s2, int s1, int s0)
-{
-    return fmaf(i2f(s2), 65536.0f, fmaf(i2f(s1), 256.0f, i2f(s0)));
+    return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7440 + k)) - 8388608.0f;
 }
 
+// 65536 s2 + 256 s1 + s0 as f32 for the three digit sums of one scale group.  The two low digits are joined in
+// the integer unit (|256 s1 + s0| < 2^30 for every format here) and the conversion unit is used twice: its rate
+// (a sixteenth of the integer pipe's) is ample at two conversions per 32 or 64 weights, and the pair costs
+// four issue slots where the offset trick costs eight.  The result is the correctly rounded f32 of each part
+// and one fused multiply-add, i.e. within an ulp of the exact sum.
+__device__ __forceinline__ float combine3(int s2, int s1, int s0)
+{
+    return fmaf(__int2float_rn(s2), 65536.0f, __int2float_rn(s1 * 256 + s0));
+}
+__device__ __forceinline__ float combine3s(int s2, int s1, int s0) { return combine3(s2, s1, s0); }
+
 // Sign-extended byte k of a word, as f32.
-__device__ __forceinline__ float s8f(uint32_t w, int k) { return i2f((int)(w << (24 - 8 * k)) >> 24); }
+__device__ __forceinline__ float s8f(uint32_t w, int k) { return __int2float_rn((int)(signed char)(w >> (8 * k))); }
 
 // ---------------------------------------------------------------------------------------------
 // Shared-memory image of the input vector (built once per thread block by stage_x).
@@ -160,6 +166,15 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr)
 template <int QT>
 struct Step;
 
+// All-zero input registers: what a lane past the end of the row multiplies its (valid, in-row) weights by.
+template <typename X>
+__device__ __forceinline__ void zero_x(X &x)
+{
+    uint32_t *w = reinterpret_cast<uint32_t *>(&x);
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(X) / 4); i++) w[i] = 0u;
+}
+
 // Q4_K, raw 144-byte super-blocks: 4 lanes per super-block, lane g owns its 64-column group
 // (32 bytes of qs: low nibbles = first 32 columns, high nibbles = next 32).
 template <>
@@ -170,6 +185,8 @@ struct Step<WGB_Q4_K> {
     {
         return (col0 >> 8) + (lane >> 2) < bpr;
     }
+    // The lane of the step's first unit that plays the same part as `lane` (always inside the row).
+    __device__ static __forceinline__ int lane0(int lane) { return lane & 3; }
     __device__ static __forceinline__ void load_x(X &x, const XImage &im, uint32_t col0, int lane)
     {
         const uint32_t kb = (col0 >> 8) + (lane >> 2), g = lane & 3;
@@ -183,7 +200,7 @@ struct Step<WGB_Q4_K> {
         }
         const float2 e = reinterpret_cast<const float2 *>(im.xscale)[kb * 4 + g];
         x.e_lo = e.x;
-        x.e_hi = e.y;
+        x.e_hi = e.y * 0.0625f;   // the high nibbles enter the sums as 16 * code
         const float4 s = reinterpret_cast<const float4 *>(im.xsum)[kb * 4 + g];
         x.s_lo = s.x + s.y;
         x.s_hi = s.z + s.w;
@@ -193,18 +210,18 @@ struct Step<WGB_Q4_K> {
         const uint32_t kb = (col0 >> 8) + (lane >> 2), g = lane & 3;
         const uint32_t blk = rowp[0] + kb * 144;
         const uint4 hdr = lds128(blk), q0 = lds128(blk + 16 + g * 32), q1 = lds128(blk + 32 + g * 32);
-        // Six-bit scale / min of sub-blocks 2g and 2g+1 (get_scale_min_k4, quantization.rs:381-389),
-        // two at a time in the 16-bit halves of a word.
-        const uint32_t sh = (g & 1) * 16;
-        const uint32_t a = hdr.y >> sh, b = hdr.z >> sh, t = hdr.w >> sh;
-        uint32_t sc16, m16;
-        if (g < 2) {
-            sc16 = a & 0x3f3fu;
-            m16 = b & 0x3f3fu;
-        } else {
-            sc16 = (t & 0x0f0fu) | ((a & 0xc0c0u) >> 2);
-            m16 = ((t >> 4) & 0x0f0fu) | ((b & 0xc0c0u) >> 2);
-        }
+        // Six-bit scale / min of sub-blocks 2g and 2g+1 (get_scale_min_k4, quantization.rs:381-389) as the four
+        // bytes (sc_lo, sc_hi, m_lo, m_hi) of one word, without a branch: with j = 2g, 2g+1
+        //   g < 2:  sc = scales[j] & 63,                        m = scales[j+4] & 63
+        //   g >= 2: sc = (scales[j+4] & 15) | (scales[j-4] >> 6) << 4,  m = (scales[j+4] >> 4) | (scales[j] >> 6) << 4
+        // Both cases read bytes 2(g&1), 2(g&1)+1 of hdr.y (scales 0..3) and of hdr.z (4..7); the second also
+        // those bytes of hdr.w (8..11).  The selectors and masks depend on the lane only.
+        const uint32_t b0 = 2u * (g & 1u);
+        const uint32_t sel_yz = (b0) | ((b0 + 1u) << 4) | ((b0 + 4u) << 8) | ((b0 + 5u) << 12);   // (y[b0], y[b0+1], z[b0], z[b0+1])
+        const uint32_t yz = __byte_perm(hdr.y, hdr.z, sel_yz);
+        const uint32_t t2 = __byte_perm(hdr.w, hdr.w >> 4, sel_yz);                                 // (w[b0], w[b0+1], (w>>4)[b0], (w>>4)[b0+1])
+        const bool high = g >= 2;
+        const uint32_t scm = ((high ? t2 : yz) & (high ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((yz >> 2) & (high ? 0x30303030u : 0u));
         const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
         const uint32_t q[8] = { q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w };
         // columns 0..31 of the group sit in digit chunks 0,1 (low nibbles), 32..63 in chunks 2,3
@@ -222,10 +239,11 @@ struct Step<WGB_Q4_K> {
             h1 = dp4a_uu(hi, d1[8 + w], h1);
             h2 = dp4a_us(hi, d2[8 + w], h2);
         }
-        const float s_lo = combine3(l2, l1, l0) * x.e_lo, s_hi = combine3(h2, h1, h0) * (x.e_hi * 0.0625f);
-        const float pos = u2f(sc16 & 0xffu) * s_lo + u2f(sc16 >> 8) * s_hi;
-        const float neg = u2f(m16 & 0xffu) * x.s_lo + u2f(m16 >> 8) * x.s_hi;
-        return dm.x * pos - dm.y * neg;
+        // |256 l1 + l0| <= 257 * 32 * 15 * 255 < 2^25; the high-nibble sums are 16 times larger: < 2^29
+        const float s_lo = combine3(l2, l1, l0) * x.e_lo, s_hi = combine3(h2, h1, h0) * x.e_hi;   // e_hi holds 2^e / 16
+        const float pos = fmaf(byte2f(scm, 0), s_lo, byte2f(scm, 1) * s_hi);
+        const float neg = fmaf(byte2f(scm, 2), x.s_lo, byte2f(scm, 3) * x.s_hi);
+        return fmaf(dm.x, pos, -(dm.y * neg));
     }
 };
 
@@ -239,6 +257,7 @@ struct Step<WGB_Q6_K> {
     {
         return (col0 >> 8) + (lane >> 2) < bpr;
     }
+    __device__ static __forceinline__ int lane0(int lane) { return lane & 3; }
     __device__ static __forceinline__ void load_x(X &x, const XImage &im, uint32_t col0, int lane)
     {
         const uint32_t kb = (col0 >> 8) + (lane >> 2), i = (lane >> 1) & 1, lb = lane & 1;
@@ -296,6 +315,7 @@ struct Step<WGB_Q8_0> {
     {
         return (col0 >> 5) + lane < bpr;
     }
+    __device__ static __forceinline__ int lane0(int) { return 0; }
     __device__ static __forceinline__ void load_x(X &x, const XImage &im, uint32_t col0, int lane)
     {
         const uint32_t kb = (col0 >> 5) + lane;
@@ -336,6 +356,7 @@ struct Step<WGB_F32> {
     {
         return col0 + lane * 4 < ncols;
     }
+    __device__ static __forceinline__ int lane0(int) { return 0; }
     __device__ static __forceinline__ void load_x(X &x, const XImage &im, uint32_t col0, int lane)
     {
         x.v = reinterpret_cast<const float4 *>(im.xf)[(col0 >> 2) + lane];

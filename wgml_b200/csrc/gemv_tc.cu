@@ -112,23 +112,21 @@ __device__ __forceinline__ void tc_ld4(uint32_t taddr, int (&v)[4])
 // Bounded wait (in time) that also gives up when another thread of the block already has.
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *dead, uint32_t *err, uint32_t code)
 {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 512; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63) == 63 && *dead) return false;
+    }
     const unsigned long long t0 = global_ns();
     do {
 #pragma unroll 1
-        for (int i = 0; i < 16; i++)
+        for (int i = 0; i < 256; i++)
             if (mbar_try_wait(bar, parity)) return true;
         if (*dead) return false;
     } while (global_ns() - t0 < ASYNC_WAIT_NS);
     *dead = 1;
     if (err) atomicCAS(err, 0u, code);
     return false;
-}
-
-// Unsigned byte k of a word as f32: the byte is placed in the mantissa of 2^23.
-__device__ __forceinline__ float byte2f(uint32_t w, int k)
-{
-    return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7440 + k)) - 8388608.0f;
 }
 
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
