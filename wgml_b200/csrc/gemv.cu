@@ -312,15 +312,16 @@ __device__ __forceinline__ void epi_finish(const GemvArgs &a, const int EPI, con
     }
 }
 
-// One kernel per block format; prologue and epilogue are chosen at run time.  The launches of a decode step
-// alternate between four prologue / epilogue combinations, and as separate kernels each of them found its
-// code evicted from the instruction caches by the others (measured: +0.7 us per launch when two kernels
-// alternate, +1.7 us with four); as one kernel they share the hot loop and most of the set-up.
-template <int QT>
+// One kernel per block format, prologue and epilogue.  The launches of a decode step alternate between
+// kernels and evict one another's code from the instruction caches (measured: +0.7 us per launch when two
+// kernels alternate, +1.7 us with four), so what matters is how little code one launch executes: a single
+// kernel with the prologue and epilogue chosen at run time shares its hot loop between launches but was
+// measured 13 % slower over a 7B decode step (more code per launch, a worse register allocation).
+template <int QT, int PRO_T, int EPI_T>
 __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant__ GemvArgs a)
 {
     using S = Step<QT>;
-    const int PRO = a.prologue, EPI = a.epilogue;
+    constexpr int PRO = PRO_T, EPI = EPI_T;
     constexpr int NPL = QT == WGB_Q6_K ? 4 : (QT == WGB_Q8_0 ? 2 : 1);   // planes of the format
     extern __shared__ uint4 smem4[];
     __shared__ float red[32];
@@ -479,22 +480,23 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     const uint32_t kw = (uint32_t)warp % kp, cl = (uint32_t)warp / kp;
     // The norm weights are parameters, not products of the launch before: their (cold, HBM-latency) loads
     // are issued ahead of the dependency wait and are in registers by the time the input can be read.
-    constexpr uint32_t XC = 4;
-    constexpr uint32_t WC = XC;
+    // A thread owns float4 chunks c = threadIdx.x + i * GEMV_CONS_THREADS; the first XC of them (all of
+    // them up to 8192 columns) live in registers from one round of loads to the staging.
+    // (6 chunks where the kernel is compiled for one prologue and that is "none": nothing else is held then)
+    constexpr uint32_t XC = PRO_T == PRO_NONE ? 6 : 4, WC = PRO_T == PRO_NONE ? 1 : 4;
+    const uint32_t nchunk = K / 4;
     float4 wc[WC], bc[WC];
     if (PRO != PRO_NONE) {
 #pragma unroll
         for (uint32_t i = 0; i < WC; i++) {
             const uint32_t c = threadIdx.x + i * GEMV_CONS_THREADS;
-            if (c < K / 4) {
+            if (c < nchunk) {
                 wc[i] = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + c);
                 if (PRO == PRO_LN) bc[i] = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + c);
             }
         }
     }
     pdl_wait();
-    // The thread's first XC chunks of the input are requested at once and stay in registers for the
-    // normalisation passes and the staging (one trip to L2 instead of several, one after the other).
     float4 xc[XC];
     const bool gather = PRO == PRO_RMS && a.peer_in.n != 0;
     if (gather) {
@@ -534,31 +536,17 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
 #pragma unroll
     for (uint32_t i = 0; i < XC; i++) {
         const uint32_t c = threadIdx.x + i * GEMV_CONS_THREADS;
-        xc[i] = c < K / 4 ? load_chunk(c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        xc[i] = c < nchunk ? load_chunk(c) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    auto chunk = [&](uint32_t c) {
-        const uint32_t i = c / GEMV_CONS_THREADS;   // c = threadIdx.x + i * GEMV_CONS_THREADS
-        if (i >= XC) return load_chunk(c);
-        float4 v = xc[0];
-#pragma unroll
-        for (uint32_t j = 1; j < XC; j++)
-            if (i == j) v = xc[j];
-        return v;
-    };
-    auto held_param = [&](const float4 *regs, const float *p, uint32_t c) {
-        const uint32_t i = c / GEMV_CONS_THREADS;
-        if (i >= WC) return __ldg(reinterpret_cast<const float4 *>(p) + c);
-        float4 v = regs[0];
-#pragma unroll
-        for (uint32_t j = 1; j < WC; j++)
-            if (i == j) v = regs[j];
-        return v;
-    };
+    // Chunks past the ones held in registers (rows longer than 12288 columns) are read again where needed.
+    const uint32_t c_tail = threadIdx.x + XC * GEMV_CONS_THREADS;
     float mean = 0.0f, scale = 1.0f;
     if (PRO == PRO_RMS) {
         float ss = 0.0f;
-        for (uint32_t c = threadIdx.x; c < K / 4; c += GEMV_CONS_THREADS) {
-            float4 v = chunk(c);
+#pragma unroll
+        for (uint32_t i = 0; i < XC; i++) ss += xc[i].x * xc[i].x + xc[i].y * xc[i].y + xc[i].z * xc[i].z + xc[i].w * xc[i].w;
+        for (uint32_t c = c_tail; c < nchunk; c += GEMV_CONS_THREADS) {
+            const float4 v = load_chunk(c);
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
         // The scale is one factor for the whole vector, so it commutes with the dot products: the input is
@@ -567,34 +555,79 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
         ss = warp_sum(ss);
         if (lane == 0) red[warp] = ss;
     } else if (PRO == PRO_LN) {
-        float s = 0.0f;
-        for (uint32_t c = threadIdx.x; c < K / 4; c += GEMV_CONS_THREADS) {
-            float4 v = chunk(c);
-            s += (v.x + v.y) + (v.z + v.w);
+        float sm = 0.0f;
+#pragma unroll
+        for (uint32_t i = 0; i < XC; i++) sm += (xc[i].x + xc[i].y) + (xc[i].z + xc[i].w);   // chunks past the end are zero
+        for (uint32_t c = c_tail; c < nchunk; c += GEMV_CONS_THREADS) {
+            const float4 v = load_chunk(c);
+            sm += (v.x + v.y) + (v.z + v.w);
         }
-        mean = cons_sum(s, red) / (float)K;
+        mean = cons_sum(sm, red) / (float)K;
         float ss = 0.0f;
-        for (uint32_t c = threadIdx.x; c < K / 4; c += GEMV_CONS_THREADS) {
-            float4 v = chunk(c);
+#pragma unroll
+        for (uint32_t i = 0; i < XC; i++) {
+            if (threadIdx.x + i * GEMV_CONS_THREADS < nchunk) {
+                const float dx = xc[i].x - mean, dy = xc[i].y - mean, dz = xc[i].z - mean, dw = xc[i].w - mean;
+                ss += dx * dx + dy * dy + dz * dz + dw * dw;
+            }
+        }
+        for (uint32_t c = c_tail; c < nchunk; c += GEMV_CONS_THREADS) {
+            float4 v = load_chunk(c);
             v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
         ss = cons_sum(ss, red);
         scale = 1.0f / sqrtf(ss / (float)K + 1.0e-5f);
     }
-    stage_x<QT, GEMV_CONS_THREADS>(smem, K, [&](uint32_t c) {
-        float4 v = chunk(c);
-        if (PRO == PRO_RMS) {
-            const float4 w = held_param(wc, a.norm_w, c);
-            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
-        } else if (PRO == PRO_LN) {
-            const float4 w = held_param(wc, a.norm_w, c);
-            const float4 b = held_param(bc, a.norm_b, c);
-            v.x = ((v.x - mean) * scale) * w.x + b.x; v.y = ((v.y - mean) * scale) * w.y + b.y;
-            v.z = ((v.z - mean) * scale) * w.z + b.z; v.w = ((v.w - mean) * scale) * w.w + b.w;
+    {
+        const XWriter<QT> xw(smem, K);
+        auto transform = [&](float4 v, const float4 w, const float4 b) {
+            if (PRO == PRO_RMS) {
+                v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+            } else if (PRO == PRO_LN) {
+                v.x = ((v.x - mean) * scale) * w.x + b.x; v.y = ((v.y - mean) * scale) * w.y + b.y;
+                v.z = ((v.z - mean) * scale) * w.z + b.z; v.w = ((v.w - mean) * scale) * w.w + b.w;
+            }
+            return v;
+        };
+        // whole warps go round together (the writer shuffles): the bound is per warp, not per lane
+        const uint32_t warp_c0 = (uint32_t)warp * 32;
+#pragma unroll
+        for (uint32_t i = 0; i < XC; i++) {
+            if (warp_c0 + i * GEMV_CONS_THREADS < nchunk) {
+                const uint32_t c = threadIdx.x + i * GEMV_CONS_THREADS;
+                const bool in = c < nchunk;
+                float4 w = make_float4(0.f, 0.f, 0.f, 0.f), b = w;
+                if (i < WC) {
+                    w = wc[i];
+                    b = bc[i];
+                } else if (in) {
+                    if (PRO != PRO_NONE) w = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + c);
+                    if (PRO == PRO_LN) b = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + c);
+                }
+                xw.put(c, transform(xc[i], w, b), in);
+            }
         }
-        return v;
-    });
+        // the rest two chunks per trip, both requested before either is used (one trip to L2, not two)
+        for (uint32_t c0 = warp_c0 + XC * GEMV_CONS_THREADS; c0 < nchunk; c0 += 2 * GEMV_CONS_THREADS) {
+            const uint32_t ca = c0 + lane, cb = ca + GEMV_CONS_THREADS;
+            const bool ina = ca < nchunk, inb = cb < nchunk, second = c0 + GEMV_CONS_THREADS < nchunk;
+            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 va = z, vb = z, wa = z, wb = z, ba = z, bb = z;
+            if (ina) {
+                va = load_chunk(ca);
+                if (PRO != PRO_NONE) wa = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + ca);
+                if (PRO == PRO_LN) ba = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + ca);
+            }
+            if (inb) {
+                vb = load_chunk(cb);
+                if (PRO != PRO_NONE) wb = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + cb);
+                if (PRO == PRO_LN) bb = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + cb);
+            }
+            xw.put(ca, transform(va, wa, ba), ina);
+            if (second) xw.put(cb, transform(vb, wb, bb), inb);
+        }
+    }
     cons_sync();
 
     if ((uint32_t)warp >= kp * ncl) return;               // warps left over when kp does not divide the consumers
@@ -899,10 +932,17 @@ static bool plan(GemvArgs &a, size_t &smem_bytes, uint32_t &grid)
     return true;
 }
 
+// The prologue / epilogue combinations the models use, each its own kernel.
+#define WGB_GEMV_VARIANTS(F)                                                                                   \
+    F(PRO_NONE, EPI_STORE) F(PRO_RMS, EPI_STORE) F(PRO_LN, EPI_STORE) F(PRO_NONE, EPI_RESIDUAL) F(PRO_RMS, EPI_SILU_PAIR) \
+    F(PRO_LN, EPI_GELU) F(PRO_RMS, EPI_QKV_ROPE) F(PRO_LN, EPI_QKV_SPLIT)
+
 template <int QT>
 static int set_smem_attr()
 {
-    WGB_CUDA(cudaFuncSetAttribute(gemv_kernel<QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_BUDGET));
+#define WGB_ATTR(PRO, EPI) WGB_CUDA(cudaFuncSetAttribute(gemv_kernel<QT, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_BUDGET));
+    WGB_GEMV_VARIANTS(WGB_ATTR)
+#undef WGB_ATTR
     return WGB_OK;
 }
 
@@ -930,7 +970,11 @@ int gemv_global_init()
 template <int QT>
 static int launch_one(GemvArgs &a, cudaStream_t stream, bool pdl)
 {
-    auto kern = gemv_kernel<QT>;
+    void (*kern)(const GemvArgs) = nullptr;
+#define WGB_PICK(PRO, EPI) if (a.prologue == PRO && a.epilogue == EPI) kern = gemv_kernel<QT, PRO, EPI>;
+    WGB_GEMV_VARIANTS(WGB_PICK)
+#undef WGB_PICK
+    if (!kern) return fail(WGB_ERR_UNSUPPORTED, "no fused kernel for prologue %d / epilogue %d", a.prologue, a.epilogue);
     size_t smem = 0;
     uint32_t grid = 0;
     if (!plan(a, smem, grid)) return fail(WGB_ERR_UNSUPPORTED, "matrix shape does not fit the fused kernel");

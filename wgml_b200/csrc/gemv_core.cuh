@@ -369,31 +369,35 @@ struct Step<WGB_F32> {
     }
 };
 
-// Builds the shared image of v[0..K) (already normalised / transformed by the caller: f(c) returns
-// the four values of float4 chunk c).  Called by threads 0..NT-1 of the block (NT a multiple of 32)
-// with converged warps; the caller synchronises those threads afterwards.  K must be a multiple of
-// 32 for the quantised formats, of 4 for f32.
-template <int QT, int NT, typename F>
-__device__ __forceinline__ void stage_x(void *smem, uint32_t K, F f)
-{
-    if (QT == WGB_F32) {
-        float4 *xf = reinterpret_cast<float4 *>(smem);
-        for (uint32_t c = threadIdx.x; c < K / 4; c += NT) xf[c] = f(c);
-        return;
+// Writer of the shared image.  put(c, v, in) stores float4 chunk c (columns 4c .. 4c+3, already normalised /
+// transformed by the caller); it is called by whole warps (all 32 lanes, converged), lane l with chunk c0 + l, so
+// that 8 consecutive lanes hold one 32-column group; `in` is false for lanes past the end of the vector (whole
+// groups of 8 lanes are in or out together because K is a multiple of 32).  The caller synchronises the block
+// afterwards.  K must be a multiple of 32 for the quantised formats, of 4 for f32.
+template <int QT>
+struct XWriter {
+    uint32_t *d0, *d1, *d2;
+    float *xscale, *xsum;
+    float4 *xf;
+
+    __device__ __forceinline__ XWriter(void *smem, uint32_t K)
+    {
+        xf = reinterpret_cast<float4 *>(smem);
+        const size_t plane = (K + 127) & ~127u;
+        uint8_t *p = reinterpret_cast<uint8_t *>(smem);
+        d0 = reinterpret_cast<uint32_t *>(p);
+        d1 = reinterpret_cast<uint32_t *>(p + plane);
+        d2 = reinterpret_cast<uint32_t *>(p + 2 * plane);
+        xscale = reinterpret_cast<float *>(p + 3 * plane);
+        xsum = xscale + ((K / 32 + 3) & ~3u);
     }
-    const size_t plane = (K + 127) & ~127u;
-    uint8_t *p = reinterpret_cast<uint8_t *>(smem);
-    uint32_t *d0 = reinterpret_cast<uint32_t *>(p), *d1 = reinterpret_cast<uint32_t *>(p + plane),
-             *d2 = reinterpret_cast<uint32_t *>(p + 2 * plane);
-    float *xscale = reinterpret_cast<float *>(p + 3 * plane);
-    float *xsum = xscale + ((K / 32 + 3) & ~3u);
-    // 8 consecutive lanes share a 32-column group (4 columns each); K/4 is a multiple of 8, so whole
-    // groups of 8 lanes are in or out of range together.
-    const uint32_t nchunk = K / 4;
-    for (uint32_t c0 = 0; c0 < nchunk; c0 += NT) {
-        const uint32_t c = c0 + threadIdx.x;
-        const bool in = c < nchunk;
-        const float4 v = in ? f(c) : make_float4(0.f, 0.f, 0.f, 0.f);
+
+    __device__ __forceinline__ void put(uint32_t c, const float4 v, bool in) const
+    {
+        if (QT == WGB_F32) {
+            if (in) xf[c] = v;
+            return;
+        }
         float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
         float sum = (v.x + v.y) + (v.z + v.w);
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
@@ -406,7 +410,6 @@ __device__ __forceinline__ void stage_x(void *smem, uint32_t K, F f)
         uint32_t ex = (__float_as_uint(m) >> 23) & 0xffu;
         ex = ex < 24u ? 24u : (ex > 253u ? 253u : ex);
         const float up = __uint_as_float((275u - ex) << 23);    // 2^(148 - ex)
-        const float down = __uint_as_float((ex - 21u) << 23);   // 2^(ex - 148)
         // round to nearest even through the 1.5 * 2^23 offset (|v * up| <= 2^22)
         const int X0 = (int)(__float_as_uint(fmaf(v.x, up, 12582912.0f)) - 0x4b400000u),
                   X1 = (int)(__float_as_uint(fmaf(v.y, up, 12582912.0f)) - 0x4b400000u),
@@ -422,10 +425,10 @@ __device__ __forceinline__ void stage_x(void *smem, uint32_t K, F f)
             d0[pos] = w0;
             d1[pos] = w1;
             d2[pos] = w2;
-            if ((c & 7) == 0) xscale[c >> 3] = down;
+            if ((c & 7) == 0) xscale[c >> 3] = __uint_as_float((ex - 21u) << 23);   // 2^(ex - 148)
             if ((c & 3) == 0) xsum[c >> 2] = sum;
         }
     }
-}
+};
 
 }  // namespace wgb
