@@ -197,6 +197,19 @@ int wgb_op_assign(int kind, float *d_lhs, const float *d_rhs, size_t n, void *st
 /* Sampler::sample_argmax (models/sampler.rs:54-56) on the device: index of the first maximum
  * of d_v[0..n) written to *d_index. */
 int wgb_argmax(const float *d_v, size_t n, uint32_t *d_index, void *stream);
+/* Sampler::sample (models/sampler.rs:32-52) on the device, with the reference's `coin = random()` passed
+ * in (0 <= coin < 1): logits / temperature, softmax, then Sampler::sample_mult (sampler.rs:62-76) when topp
+ * is outside (0, 1) or Sampler::sample_topp (sampler.rs:84-130): candidates >= (1 - topp) / (n - 1),
+ * stable sort by decreasing probability, prefix cut where the running sum exceeds topp, inverse CDF at
+ * coin * sum.  temperature == 0 is wgb_argmax.  The logits are left untouched; the token id goes to
+ * *d_token.  The softmax denominator is a tree sum where the reference adds in index order, so a draw whose
+ * coin falls within rounding of a CDF step may land on the neighbouring token. */
+int wgb_sample(const float *d_logits, size_t n, float temperature, float topp, float coin, uint32_t *d_token,
+               void *stream);
+/* The counter-based uniform draw the device-resident token loops use for the token at position `draw`:
+ * 24 bits in [0, 1), the form of rand's f32 sample (the reference's generator is unseeded,
+ * sampler.rs:42). */
+float wgb_sampler_coin(uint64_t seed, uint64_t draw);
 
 /* ---- GGUF ---- */
 
@@ -324,6 +337,11 @@ float *wgb_llama2_value_cache(wgb_llama2 *m, uint32_t layer);
  * h_out_tokens receives n_prompt - 1 + n_gen ids: the token fed at each following position. */
 int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t n_prompt, size_t n_gen,
                       uint32_t start_pos, uint32_t *h_out_tokens, void *stream);
+/* Sampling of the generated tokens in wgb_llama2_decode: Sampler::new(vocab, temperature, topp)
+ * (models/sampler.rs:21-29; the chat loop uses 0.7 / 0.95, crates/wgml-chat/src/sampler.rs:109-110) with
+ * coin = wgb_sampler_coin(seed, position of the sampled token).  temperature 0 (the default) is greedy.
+ * The draw happens on the device: no logits leave it. */
+int wgb_llama2_set_sampler(wgb_llama2 *m, float temperature, float topp, uint64_t seed);
 /* Number of kernels one decode step launches (for launch accounting). */
 int wgb_llama2_kernels_per_token(const wgb_llama2 *m);
 /* Measurement aid, the counterpart of wgcore's GpuTimestamps around a pass
@@ -431,7 +449,9 @@ int wgb_gpt2_forward(wgb_gpt2 *m, uint32_t token, uint32_t pos, void *stream);
 const float *wgb_gpt2_logits(const wgb_gpt2 *m);
 float *wgb_gpt2_key_cache(wgb_gpt2 *m, uint32_t layer);
 float *wgb_gpt2_value_cache(wgb_gpt2 *m, uint32_t layer);
-/* ChatGpt2::forward's loop (crates/wgml-chat/src/chat_gpt2.rs:43-151), greedy, device-resident. */
+/* As wgb_llama2_set_sampler. */
+int wgb_gpt2_set_sampler(wgb_gpt2 *m, float temperature, float topp, uint64_t seed);
+/* ChatGpt2::forward's loop (crates/wgml-chat/src/chat_gpt2.rs:43-151), device-resident. */
 int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_prompt, size_t n_gen,
                     uint32_t start_pos, uint32_t *h_out_tokens, void *stream);
 int wgb_gpt2_kernels_per_token(const wgb_gpt2 *m);

@@ -85,6 +85,7 @@ def lib() -> C.CDLL:
         L.wgo_gpt2_decode.argtypes = [vp, vp, sz, sz, C.c_uint32, vp]
         L.wgo_num_threads.restype = C.c_int
         L.wgo_set_num_threads.argtypes = [C.c_int]
+        L.wgo_set_dot_f64.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -99,6 +100,12 @@ def _f32(a) -> np.ndarray:
 
 def set_num_threads(n: int) -> None:
     lib().wgo_set_num_threads(int(n))
+
+
+def set_dot_f64(on: bool) -> None:
+    """Accumulate every matrix-vector product of the transformers in double (rounded to f32 once): the gap to
+    the default f32 accumulation measures how far summation rounding alone moves a model's logits."""
+    lib().wgo_set_dot_f64(int(bool(on)))
 
 
 def num_threads() -> int:

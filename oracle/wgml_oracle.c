@@ -341,6 +341,13 @@ static double gemv_row_f64(const float *wrow, const float *x, size_t ncols)
     return y;
 }
 
+/* Test switch: when set, every matrix-vector product of the transformers below is accumulated in double and
+ * rounded to f32 once (all else stays f32).  The distance between the two settings is how far f32 summation
+ * rounding alone moves the logits of a model -- the yardstick a CUDA result is held against where a deep
+ * random network amplifies rounding beyond the flat tolerance. */
+static int g_dot_f64 = 0;
+WGO_API void wgo_set_dot_f64(int on) { g_dot_f64 = on != 0; }
+
 /* `matmul` of the CPU transformer -- crates/wgml/src/models/llama2/cpu.rs:368-374 -- over a
  * matrix that is still in GGUF blocks: each row is dequantised (exactly as
  * TransformerWeights::from_gguf does once at load, cpu.rs:198-217) and then multiplied.
@@ -365,7 +372,7 @@ WGO_API int wgo_gemv_quant(int qtype, const void *w, size_t nrows, size_t ncols,
                 for (size_t k = 0; k < bpr; k++) deq_block(qtype, rb + k * (size_t)bb, row + k * (size_t)bl);
                 wr = row;
             }
-            out[r] = na_gemv_row(wr, x, ncols);
+            out[r] = g_dot_f64 ? (float)gemv_row_f64(wr, x, ncols) : na_gemv_row(wr, x, ncols);
             if (out64) out64[r] = gemv_row_f64(wr, x, ncols);
         }
         free(row);

@@ -97,3 +97,35 @@ def test_gemv_dimension_mismatch_is_an_error():
         ops.GpuQuantMatrix(ops.Q4_K, raw, 8, 250)
     with pytest.raises(ops.WgbError):
         ops.GpuQuantMatrix(9, raw, 8, 256)  # Q8_1: unsupported by the reference as well
+
+
+@pytest.mark.parametrize("qtype", [ops.Q4_K, ops.Q6_K, ops.Q8_0])
+def test_gemv_outlier_inputs(qtype):
+    """The fast kernels read the input in block fixed point (one exponent per 32 columns, 23 bits).  Inputs that
+    stress it: twelve decades inside one 32-column group, groups of zeros, one huge element, denormal-sized
+    values -- against the f64 oracle, same tolerance as everywhere."""
+    nrows, ncols = 512, 4096
+    raw, _ = make(qtype, nrows, ncols, 23)
+    rng = np.random.default_rng(5)
+    cases = {}
+    x = rng.standard_normal(ncols).astype(np.float32)
+    x[:32] *= np.float32(10.0) ** rng.uniform(-6, 6, 32).astype(np.float32)      # 12 decades in the first group
+    x[32:64] = 0.0                                                                # an all-zero group
+    x[64:96] = np.where(np.arange(32) == 7, np.float32(1e4), np.float32(1e-8))    # one outlier among tiny values
+    cases["decades"] = x
+    x = np.zeros(ncols, np.float32)
+    x[1000] = 3.0e30
+    x[1001] = -2.5
+    cases["one huge element"] = x
+    cases["tiny"] = (rng.standard_normal(ncols) * 1e-30).astype(np.float32)
+    cases["zeros"] = np.zeros(ncols, np.float32)
+    m = ops.GpuQuantMatrix(qtype, raw, nrows, ncols)
+    g = ops.GemvQuant.from_device()
+    for name, xv in cases.items():
+        out = torch.full((nrows,), float("nan"), device="cuda")
+        g.dispatch(out, m, torch.from_numpy(xv).cuda())
+        o = out.cpu().numpy()
+        assert np.isfinite(o).all(), name
+        _, o64 = oracle.gemv_quant(qtype, raw, nrows, ncols, xv, want_f64=True)
+        atol = ATOL * float(np.sqrt(np.mean(o64 ** 2))) if name != "zeros" else 0.0
+        assert_close(o, o64, RTOL, atol, f"qtype {qtype}, {name}")

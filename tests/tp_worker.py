@@ -48,7 +48,7 @@ def main():
                 # the per-launch timing path replays the step with time stamps (direct exchange) or events (NCCL);
                 # it must leave the exchange counters intact: decode the same sequence again afterwards
                 prof = m.profile_step(int(toks[-1]), len(toks))
-                assert len(prof) == 5 * cfg["n_layers"] + 1, len(prof)
+                assert len(prof) >= 5 * cfg["n_layers"] + 1, len(prof)
                 again = m.decode(prompt, 24)
                 assert np.array_equal(again, toks), (name, fused, direct, again, toks)
                 assert _lib.load().wgb_device_status() == _lib.OK

@@ -91,6 +91,10 @@ SIGNATURES = {
     "wgb_unary_inplace": (_i, [_i, _vp, _sz, C.POINTER(_f), _vp]),
     "wgb_op_assign": (_i, [_i, _vp, _vp, _sz, _vp]),
     "wgb_argmax": (_i, [_vp, _sz, _vp, _vp]),
+    "wgb_sample": (_i, [_vp, _sz, _f, _f, _f, _vp, _vp]),
+    "wgb_sampler_coin": (_f, [_u64, _u64]),
+    "wgb_llama2_set_sampler": (_i, [_vp, _f, _f, _u64]),
+    "wgb_gpt2_set_sampler": (_i, [_vp, _f, _f, _u64]),
     "wgb_gguf_open": (_i, [C.c_char_p, _pp]),
     "wgb_gguf_from_bytes": (_i, [_vp, _sz, _pp]),
     "wgb_gguf_close": (_i, [_vp]),

@@ -35,6 +35,10 @@ struct wgb_gpt2 {
     uint32_t *h_pinned = nullptr;            // pinned staging of a decode call: [0] status word, [1..2] status polls, [3..] token ids
     size_t pinned_cap = 0;
     StatusPoll poll;
+    // sampling of generated tokens: temperature 0 = greedy (Sampler::sample, models/sampler.rs:32-52)
+    float smp_temperature = 0.0f, smp_topp = 0.0f;
+    unsigned long long smp_seed = 0;
+    void *smp_scratch = nullptr;
     bool fused = true, use_pdl = true;
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_n_prompt = 0;
@@ -293,6 +297,7 @@ WGB_EXPORT int wgb_gpt2_destroy(wgb_gpt2 *m)
     for (uint32_t *b : ubufs) if (b) cudaFree(b);
     if (m->h_pinned) cudaFreeHost(m->h_pinned);
     status_poll_destroy(m->poll);
+    if (m->smp_scratch) cudaFree(m->smp_scratch);
     delete m;
     return WGB_OK;
 }
@@ -520,8 +525,14 @@ WGB_EXPORT int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_p
         if (e == cudaSuccess) {
             int nk = 0;
             rc = enqueue_forward(m, cs, &nk);
-            if (!rc) rc = launch_argmax_advance(m->logits, m->p.n_vocab, ls, m->argmax_scratch, cs);
-            m->kernels_per_token = nk + 2;
+            if (!rc && m->smp_temperature == 0.0f) {
+                rc = launch_argmax_advance(m->logits, m->p.n_vocab, ls, m->argmax_scratch, cs);
+                m->kernels_per_token = nk + 2;
+            } else if (!rc) {
+                rc = launch_sample(m->logits, m->p.n_vocab, m->smp_temperature, m->smp_topp, 0.0f, 1, m->smp_seed, m->smp_scratch, nullptr,
+                                   &ls, cs);
+                m->kernels_per_token = nk + 1;
+            }
             e = cudaStreamEndCapture(cs, &graph);
             if (rc) { if (graph) cudaGraphDestroy(graph); cudaStreamDestroy(cs); return rc; }
         }
@@ -539,4 +550,16 @@ WGB_EXPORT int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_p
     WGB_CUDA(cudaStreamSynchronize(s));
     memcpy(h_out_tokens, m->h_pinned + 3, total * 4);
     return gemv_report_status(m->h_pinned[0]);
+}
+
+WGB_EXPORT int wgb_gpt2_set_sampler(wgb_gpt2 *m, float temperature, float topp, uint64_t seed)
+{
+    WGB_REQUIRE(m, "null argument");
+    WGB_REQUIRE(temperature >= 0.0f, "negative temperature %g", temperature);
+    if (temperature > 0.0f && !m->smp_scratch) WGB_CUDA(cudaMalloc(&m->smp_scratch, sampler_scratch_bytes(m->p.n_vocab)));
+    m->smp_temperature = temperature;
+    m->smp_topp = topp;
+    m->smp_seed = seed;
+    drop_graph(m);   // the parameters are baked into the recorded step
+    return WGB_OK;
 }

@@ -151,4 +151,11 @@ struct LoopState {
 int launch_argmax_advance(const float *logits, uint32_t n, const LoopState &ls, uint32_t *scratch,
                           cudaStream_t stream);
 
+// Temperature / top-p draw on the device (sampler.cu).  `scratch` holds sampler_scratch_bytes(n) bytes.  With a
+// loop state the kernel is the sampling step of the token loop: forced prompt tokens, then a draw per
+// generated position with coin = f(seed, position).
+size_t sampler_scratch_bytes(uint32_t n);
+int launch_sample(const float *logits, uint32_t n, float temperature, float topp, float coin, int seeded, unsigned long long seed,
+                  void *scratch, uint32_t *out_index, const LoopState *ls, cudaStream_t stream);
+
 }  // namespace wgb

@@ -174,6 +174,11 @@ class Llama2:
                                             torch.cuda.current_stream().cuda_stream))
         return out[:prompt.size - 1 + n_gen]
 
+    def set_sampler(self, temperature: float, topp: float, seed: int = 0) -> None:
+        """Sampler::new(vocab, temperature, topp) for the generated tokens of `decode`; temperature 0 = greedy.
+        The coin of the token at position p is ops.sampler_coin(seed, p)."""
+        check(_lib.load().wgb_llama2_set_sampler(self._h, temperature, topp, seed))
+
     def kernels_per_token(self) -> int:
         return _lib.load().wgb_llama2_kernels_per_token(self._h)
 
@@ -302,6 +307,9 @@ class Gpt2:
         check(_lib.load().wgb_gpt2_decode(self._h, prompt.ctypes.data, prompt.size, n_gen, start_pos, out.ctypes.data,
                                           torch.cuda.current_stream().cuda_stream))
         return out[:prompt.size - 1 + n_gen]
+
+    def set_sampler(self, temperature: float, topp: float, seed: int = 0) -> None:
+        check(_lib.load().wgb_gpt2_set_sampler(self._h, temperature, topp, seed))
 
     def kernels_per_token(self) -> int:
         return _lib.load().wgb_gpt2_kernels_per_token(self._h)
