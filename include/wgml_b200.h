@@ -202,8 +202,8 @@ int wgb_argmax(const float *d_v, size_t n, uint32_t *d_index, void *stream);
  * is outside (0, 1) or Sampler::sample_topp (sampler.rs:84-130): candidates >= (1 - topp) / (n - 1),
  * stable sort by decreasing probability, prefix cut where the running sum exceeds topp, inverse CDF at
  * coin * sum.  temperature == 0 is wgb_argmax.  The logits are left untouched; the token id goes to
- * *d_token.  The softmax denominator is a tree sum where the reference adds in index order, so a draw whose
- * coin falls within rounding of a CDF step may land on the neighbouring token. */
+ * *d_token.  The softmax denominator and the CDF are added in the reference's order (one thread, about 2 ns
+ * per vocabulary entry), so the same coin gives the same token up to the last bit of expf. */
 int wgb_sample(const float *d_logits, size_t n, float temperature, float topp, float coin, uint32_t *d_token,
                void *stream);
 /* The counter-based uniform draw the device-resident token loops use for the token at position `draw`:

@@ -86,6 +86,10 @@ def lib() -> C.CDLL:
         L.wgo_num_threads.restype = C.c_int
         L.wgo_set_num_threads.argtypes = [C.c_int]
         L.wgo_set_dot_f64.argtypes = [C.c_int]
+        L.wgo_sampler_coin.restype = C.c_float
+        L.wgo_sampler_coin.argtypes = [C.c_uint64, C.c_uint64]
+        L.wgo_sample.restype = C.c_size_t
+        L.wgo_sample.argtypes = [vp, sz, C.c_float, C.c_float, C.c_float, vp]
         _lib = L
     return _lib
 
@@ -188,6 +192,19 @@ def attention(seq_len, kv_dim, kv_mul, n_heads, head_size, pos, q, key_cache, va
     xb = np.zeros(n_heads * head_size, dtype=np.float32)
     lib().wgo_attention(_p(params), _p(q), _p(kc), _p(vc), _p(attn), _p(xb))
     return xb, attn
+
+
+def sampler_coin(seed: int, draw: int) -> float:
+    return float(lib().wgo_sampler_coin(seed, draw))
+
+
+def sample(logits, temperature: float, topp: float, coin: float):
+    """Sampler::sample (crates/wgml/src/models/sampler.rs:32-52).  Returns (token, slack): slack is how far the
+    deciding comparison was from its threshold, relative to the probability mass walked."""
+    a = _f32(logits).copy()
+    sl = np.zeros(1, np.float32)
+    tok = lib().wgo_sample(_p(a), a.size, float(temperature), float(topp), float(coin), _p(sl))
+    return int(tok), float(sl[0])
 
 
 def argmax(v) -> int:

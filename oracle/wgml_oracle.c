@@ -532,6 +532,91 @@ WGO_API void wgo_attention(const wgo_attn_params *p, const float *q, const float
     }
 }
 
+/* The counter-based uniform draw of the device token loops (not in the reference, whose generator is unseeded,
+ * crates/wgml/src/models/sampler.rs:42): splitmix64 of (seed, draw), top 24 bits, the form of rand's f32 sample. */
+WGO_API float wgo_sampler_coin(uint64_t seed, uint64_t draw)
+{
+    uint64_t z = seed + (draw + 1ull) * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+typedef struct { float prob; size_t index; } wgo_prob_index;
+/* `sort_by_key(|pid| OrderedFloat(-pid.prob))` is a stable sort: equal probabilities keep index order. */
+static int cmp_prob_desc(const void *a, const void *b)
+{
+    const wgo_prob_index *x = (const wgo_prob_index *)a, *y = (const wgo_prob_index *)b;
+    if (x->prob > y->prob) return -1;
+    if (x->prob < y->prob) return 1;
+    return x->index < y->index ? -1 : (x->index > y->index ? 1 : 0);
+}
+
+/* Sampler::sample -- crates/wgml/src/models/sampler.rs:32-52 with sample_mult :62-76 and sample_topp :84-130;
+ * `coin` stands for `random()`.  `logits` is overwritten with the probabilities, as in the reference.
+ * slack[0] receives the distance of the deciding comparison from its threshold, relative to the running sum:
+ * a draw whose slack is at rounding level may legitimately land on the neighbouring token elsewhere. */
+WGO_API size_t wgo_sample(float *logits, size_t n, float temperature, float topp, float coin, float *slack)
+{
+    if (slack) slack[0] = 1.0f;
+    if (temperature == 0.0f) {
+        size_t best = 0;
+        for (size_t i = 1; i < n; i++) if (logits[i] > logits[best]) best = i;
+        return best;
+    }
+    for (size_t i = 0; i < n; i++) logits[i] /= temperature;
+    wgo_softmax(logits, n);
+    if (topp <= 0.0f || topp >= 1.0f) {
+        float cdf = 0.0f;
+        for (size_t i = 0; i < n; i++) {
+            float before = cdf;
+            cdf += logits[i];
+            if (coin < cdf) {
+                if (slack) slack[0] = fminf(cdf - coin, i ? coin - before : 1.0f);
+                return i;
+            }
+        }
+        if (slack) slack[0] = 0.0f;
+        return n - 1;
+    }
+    wgo_prob_index *pi = (wgo_prob_index *)malloc(n * sizeof(wgo_prob_index));
+    size_t n0 = 0;
+    float cutoff = (1.0f - topp) / ((float)n - 1.0f);
+    for (size_t i = 0; i < n; i++) {
+        if (logits[i] >= cutoff) {
+            pi[n0].index = i;
+            pi[n0].prob = logits[i];
+            n0++;
+        }
+    }
+    qsort(pi, n0, sizeof(wgo_prob_index), cmp_prob_desc);
+    float cumulative = 0.0f;
+    size_t last = n0 - 1;
+    for (size_t i = 0; i < n0; i++) {
+        cumulative += pi[i].prob;
+        if (cumulative > topp) {
+            last = i;
+            break;
+        }
+    }
+    float r = coin * cumulative, cdf = 0.0f;
+    size_t pick = pi[last].index;
+    float sl = 0.0f;
+    for (size_t i = 0; i <= last; i++) {
+        float before = cdf;
+        cdf += pi[i].prob;
+        if (r < cdf) {
+            pick = pi[i].index;
+            sl = fminf(cdf - r, i ? r - before : 1.0f) / cumulative;
+            break;
+        }
+    }
+    if (slack) slack[0] = sl;
+    free(pi);
+    return pick;
+}
+
 /* Sampler::sample_argmax -- crates/wgml/src/models/sampler.rs:54-56; nalgebra `imax` keeps
  * the first of equal maxima. */
 WGO_API size_t wgo_argmax(const float *v, size_t n)

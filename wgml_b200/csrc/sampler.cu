@@ -10,11 +10,15 @@
 // generator; here it is a counter-based draw (seed, position), the same 24-bit form as rand's f32 sample, so a
 // sequence can be reproduced and resumed.
 //
-// One block does a whole draw: maximum, exponentials and their sum by tree reductions (the reference adds the
-// exponentials one after the other, so probabilities agree to rounding, not bit for bit); candidates compacted
-// in index order; a bitonic sort of 64-bit keys (probability bits descending, index ascending -- the order the
-// reference's stable sort produces) in shared memory for up to 4096 candidates, in global scratch beyond;
-// the two prefix walks by one thread in the reference's order of additions.
+// One block does a whole draw.  The maximum and the exponentials are computed in parallel; their sum is taken
+// by ONE thread in index order, as the reference does: a sequential f32 sum of 32000 to 50257 nearly equal terms
+// is off by up to 1e-4 relative (the rounding is biased, not random), every probability inherits that factor,
+// and a tree sum -- more accurate -- would move the draws of flat distributions to other tokens than the
+// reference's.  The sequential passes read the values through shared memory in double-buffered chunks filled
+// by the other warps (about 2 ns per term: 0.1 ms for a 50257-token vocabulary).  Candidates are compacted in
+// index order; a bitonic sort of 64-bit keys (probability bits descending, index ascending: the order the
+// reference's stable sort produces) runs in shared memory for up to 4096 candidates and in global scratch
+// beyond; the two prefix walks are done by one thread in the reference's order of additions.
 #include "kernels.h"
 
 namespace wgb {
@@ -71,6 +75,42 @@ __device__ void block_bitonic(unsigned long long *keys, uint32_t n)
     }
 }
 
+// Calls op(i, v[i]) for i = 0, 1, ... in order from thread 0 until it returns false or i reaches n; the other
+// warps stream v through the two halves of `buf` (2 * SEQ_CHUNK floats of shared memory).  Block-wide call.
+constexpr uint32_t SEQ_CHUNK = 4096;
+template <typename Op>
+__device__ void sequential_pass(const float *v, uint32_t n, float *buf, uint32_t *stop, Op op)
+{
+    const uint32_t nchunks = (n + SEQ_CHUNK - 1) / SEQ_CHUNK;
+    if (threadIdx.x == 0) *stop = 0;
+    __syncthreads();
+    for (uint32_t c = 0; c <= nchunks; c++) {
+        if (threadIdx.x >= 32 && c < nchunks) {
+            float *dst = buf + (c & 1) * SEQ_CHUNK;
+            const uint32_t base = c * SEQ_CHUNK;
+            for (uint32_t i = threadIdx.x - 32; i < SEQ_CHUNK; i += SMP_NT - 32)
+                dst[i] = base + i < n ? v[base + i] : 0.0f;
+        } else if (threadIdx.x == 0 && c > 0) {
+            const float *src = buf + ((c - 1) & 1) * SEQ_CHUNK;
+            const uint32_t base = (c - 1) * SEQ_CHUNK, cnt = min(SEQ_CHUNK, n - base);
+            bool go = true;
+            uint32_t i = 0;
+            for (; go && i + 8 <= cnt; i += 8) {
+                float t[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) t[k] = src[i + k];
+#pragma unroll
+                for (int k = 0; k < 8; k++) go = go && op(base + i + k, t[k]);
+            }
+            for (; go && i < cnt; i++) go = op(base + i, src[i]);
+            if (!go) *stop = 1;
+        }
+        __syncthreads();
+        if (*stop) break;
+    }
+    __syncthreads();
+}
+
 struct SampleArgs {
     const float *logits;
     uint32_t n;
@@ -89,8 +129,11 @@ __global__ void __launch_bounds__(SMP_NT) sample_kernel(const __grid_constant__ 
 {
     __shared__ float red[32];
     __shared__ uint32_t s_count[SMP_NT / 32];
-    __shared__ uint32_t s_n0, s_token;
-    __shared__ unsigned long long s_keys[SMP_SMEM_KEYS];
+    __shared__ uint32_t s_n0, s_token, s_stop;
+    __shared__ float s_sum;
+    __shared__ unsigned long long s_keys[SMP_SMEM_KEYS];   // also the chunk buffers of the sequential passes
+    static_assert(SMP_SMEM_KEYS * sizeof(unsigned long long) >= 2 * SEQ_CHUNK * sizeof(float), "chunk buffers alias the keys");
+    float *seq_buf = reinterpret_cast<float *>(s_keys);
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t n = a.n;
@@ -114,29 +157,32 @@ __global__ void __launch_bounds__(SMP_NT) sample_kernel(const __grid_constant__ 
     float m = -INFINITY;
     for (uint32_t i = threadIdx.x; i < n; i += SMP_NT) m = fmaxf(m, __ldcg(a.logits + i) / a.temperature);
     m = block_reduce_max(m, red);
-    float sum = 0.0f;
-    for (uint32_t i = threadIdx.x; i < n; i += SMP_NT) {
-        const float e = expf(__ldcg(a.logits + i) / a.temperature - m);
-        a.prob[i] = e;
-        sum += e;
-    }
-    sum = block_reduce_sum(sum, red);
+    for (uint32_t i = threadIdx.x; i < n; i += SMP_NT) a.prob[i] = expf(__ldcg(a.logits + i) / a.temperature - m);
     __syncthreads();
+    {
+        float acc = 0.0f;   // thread 0 only
+        sequential_pass(a.prob, n, seq_buf, &s_stop, [&](uint32_t, float e) {
+            acc += e;
+            return true;
+        });
+        if (threadIdx.x == 0) s_sum = acc;
+        __syncthreads();
+    }
+    const float sum = s_sum;
     const bool nucleus = a.topp > 0.0f && a.topp < 1.0f;
     if (!nucleus) {
         // sample_mult: inverse CDF in index order, the additions in the reference's order
-        if (threadIdx.x == 0) {
-            float cdf = 0.0f;
-            uint32_t pick = n - 1;
-            for (uint32_t i = 0; i < n; i++) {
-                cdf += a.prob[i] / sum;
-                if (coin < cdf) {
-                    pick = i;
-                    break;
-                }
+        float cdf = 0.0f;
+        uint32_t pick = n - 1;
+        sequential_pass(a.prob, n, seq_buf, &s_stop, [&](uint32_t i, float e) {
+            cdf += e / sum;
+            if (coin < cdf) {
+                pick = i;
+                return false;
             }
-            s_token = pick;
-        }
+            return true;
+        });
+        if (threadIdx.x == 0) s_token = pick;
     } else {
         // candidates p >= cutoff, compacted in index order: thread t owns the contiguous run [t * per, (t + 1) * per)
         const float cutoff = (1.0f - a.topp) / ((float)n - 1.0f);

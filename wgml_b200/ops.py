@@ -342,3 +342,24 @@ def sample_argmax(v: torch.Tensor) -> int:
     idx = torch.zeros(1, dtype=torch.int32, device=v.device)
     check(_lib.load().wgb_argmax(_f32(v, "v"), v.numel(), idx.data_ptr(), _stream()))
     return int(idx.item()) & 0xFFFFFFFF
+
+
+def sampler_coin(seed: int, draw: int) -> float:
+    """The uniform draw in [0, 1) the device-resident token loops use for the token at position `draw`."""
+    return float(_lib.load().wgb_sampler_coin(seed, draw))
+
+
+class Sampler:
+    """Sampler (crates/wgml/src/models/sampler.rs:14-52) evaluated on the device: the logits never leave it."""
+
+    def __init__(self, vocab_size: int, temperature: float, topp: float):
+        self.vocab_size, self.temperature, self.topp = vocab_size, temperature, topp
+        self._idx = None
+
+    def sample(self, logits: torch.Tensor, coin: float) -> int:
+        """One draw; `coin` in [0, 1) stands for the reference's `random()`."""
+        if self._idx is None or self._idx.device != logits.device:
+            self._idx = torch.zeros(1, dtype=torch.int32, device=logits.device)
+        check(_lib.load().wgb_sample(_f32(logits, "logits"), logits.numel(), self.temperature, self.topp, coin,
+                                     self._idx.data_ptr(), _stream()))
+        return int(self._idx.item()) & 0xFFFFFFFF
