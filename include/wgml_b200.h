@@ -263,6 +263,48 @@ typedef struct {
 int64_t wgb_gguf_tensor_find(const wgb_gguf *g, const char *name);
 int wgb_gguf_tensor_info(const wgb_gguf *g, uint64_t index, wgb_gguf_tensor *out);
 
+/* ---- Tokenizers and chat template (host only) ---- */
+
+/* LlamaTokenizer (models/llama2/tokenizer.rs:8-180) from the GGUF metadata keys tokenizer.ggml.tokens,
+ * .scores, .bos_token_id, .eos_token_id, .unknown_token_id (tokenizer.rs:23-34).  Text is UTF-8.
+ * encode (tokenizer.rs:75-164): spaces become U+2581, one token per character with byte fallback (byte b ->
+ * id b + 3), the "<s>" / "</s>" scans, then the best-scoring adjacent pair is merged until none is in the
+ * vocabulary.  With out_ids == NULL only *n_out is written (size query).
+ * decode (tokenizer.rs:166-177): the text of `token` after `prev_token` (leading white space dropped after
+ * id 1, "<0xHH>" pieces become the character of that byte value, U+2581 becomes a space). */
+typedef struct wgb_llama_tokenizer wgb_llama_tokenizer;
+int wgb_llama_tokenizer_from_gguf(const wgb_gguf *g, wgb_llama_tokenizer **out);
+int wgb_llama_tokenizer_destroy(wgb_llama_tokenizer *t);
+uint32_t wgb_llama_tokenizer_bos(const wgb_llama_tokenizer *t);
+uint32_t wgb_llama_tokenizer_eos(const wgb_llama_tokenizer *t);
+uint32_t wgb_llama_tokenizer_unk(const wgb_llama_tokenizer *t);
+size_t wgb_llama_tokenizer_vocab_size(const wgb_llama_tokenizer *t);
+int wgb_llama_tokenizer_encode(const wgb_llama_tokenizer *t, const char *text, size_t text_len, int bos, int eos,
+                               uint32_t *out_ids, size_t cap, size_t *n_out);
+int wgb_llama_tokenizer_decode(const wgb_llama_tokenizer *t, uint32_t prev_token, uint32_t token, char *buf, size_t cap,
+                               size_t *len);
+/* Gpt2Tokenizer (models/gpt2/tokenizer.rs:38-217) from tokenizer.ggml.tokens, .merges, .bos_token_id,
+ * .eos_token_id (tokenizer.rs:56-60): "<...>" spans are special tokens (tokenizer.rs:128-139, an unknown one
+ * is WGB_ERR_NOT_FOUND where the reference panics), the rest is split by the GPT-2 pattern (tokenizer.rs:75),
+ * mapped byte by byte to printable characters (bytes_to_unicode, tokenizer.rs:22-36) and merged by rank.
+ * \p{L} and \p{N} are decided exactly for ASCII and by the C library's UTF-8 character tables beyond it. */
+typedef struct wgb_gpt2_tokenizer wgb_gpt2_tokenizer;
+int wgb_gpt2_tokenizer_from_gguf(const wgb_gguf *g, wgb_gpt2_tokenizer **out);
+int wgb_gpt2_tokenizer_destroy(wgb_gpt2_tokenizer *t);
+uint32_t wgb_gpt2_tokenizer_bos(const wgb_gpt2_tokenizer *t);
+uint32_t wgb_gpt2_tokenizer_eos(const wgb_gpt2_tokenizer *t);
+int wgb_gpt2_tokenizer_encode(const wgb_gpt2_tokenizer *t, const char *text, size_t text_len, uint32_t *out_ids, size_t cap,
+                              size_t *n_out);
+int wgb_gpt2_tokenizer_decode(const wgb_gpt2_tokenizer *t, const uint32_t *tokens, size_t n, char *buf, size_t cap, size_t *len);
+/* ChatTemplate::apply (crates/wgml-chat/src/chat_template.rs:31-43) for the default template
+ * (LlamaTokenizer::CHAT_TEMPLATE, models/llama2/llama-2-chat.jinja) with minijinja configured as there
+ * (trim_blocks, bos_token / eos_token globals): roles[i] in {"system" (first only), "user", "assistant"},
+ * alternating from "user" (else WGB_ERR_INVALID with the template's own message).  The white space the
+ * template leaves between its tags is part of the rendering and is reproduced.  Templates carried by a GGUF
+ * (tokenizer.chat_template, chat_template.rs:22-29) are arbitrary Jinja and are not interpreted. */
+int wgb_chat_template_llama2(const char *const *roles, const char *const *contents, size_t n_messages, const char *bos,
+                             const char *eos, char *buf, size_t cap, size_t *len);
+
 /* ---- Llama-2 family ---- */
 
 /* Llama2Config (models/llama2/cpu.rs:46-67); usize fields are u32 here. */
@@ -337,6 +379,12 @@ float *wgb_llama2_value_cache(wgb_llama2 *m, uint32_t layer);
  * h_out_tokens receives n_prompt - 1 + n_gen ids: the token fed at each following position. */
 int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t n_prompt, size_t n_gen,
                       uint32_t start_pos, uint32_t *h_out_tokens, void *stream);
+/* Weight upload so far: bytes copied host -> device and the wall time the copies took (first byte taken to
+ * last repack kernel finished, summed over wgb_llama2_set_matrix calls and wgb_llama2_load_gguf).  The loader
+ * replaces the reference's eager element-by-element parse (gguf.rs:539-620, 671-681) by a pipeline: bytes go
+ * from the mapped file through a ring of pinned buffers to the device on a copy stream, the repack kernels of
+ * the planar formats run behind them, and nothing is waited for until the last tensor is enqueued. */
+int wgb_llama2_load_stats(const wgb_llama2 *m, size_t *bytes, double *seconds);
 /* Sampling of the generated tokens in wgb_llama2_decode: Sampler::new(vocab, temperature, topp)
  * (models/sampler.rs:21-29; the chat loop uses 0.7 / 0.95, crates/wgml-chat/src/sampler.rs:109-110) with
  * coin = wgb_sampler_coin(seed, position of the sampled token).  temperature 0 (the default) is greedy.

@@ -149,6 +149,8 @@ def test_load_from_gguf_file(tmp_path):
     g = Gguf.open(path)
     gpu = Llama2.from_gguf(g, LlamaModelType.Llama)
     assert gpu.config.vocab_size == 1000 and gpu.config.n_kv_heads == 4 and abs(gpu.config.rms_norm_eps - 1e-5) < 1e-9
+    nbytes, secs = gpu.load_stats()   # the pipelined upload moved every matrix once
+    assert nbytes == sum(np.asarray(a).nbytes for n_, (q_, a) in t.items() if n_.endswith(".weight") and "norm" not in n_) and secs > 0
     cpu = oracle.Llama2Oracle(cfg, t)
     compare_steps(gpu, cpu, synth.prompt(5, 1000, 8), what="gguf")
 

@@ -1,0 +1,176 @@
+"""Tokenizers and the default chat template (host code, no GPU): the C++ implementations behind the C ABI against
+the plain-Python restatement of the reference (oracle/tokenizers.py) on vocabularies written into GGUF metadata
+the way llama.cpp's converters do, plus a few hand-computed known answers."""
+import random
+
+import numpy as np
+import pytest
+
+from oracle import tokenizers as ref
+from wgml_b200.gguf import Gguf
+from wgml_b200.tokenizers import ChatTemplate, Gpt2Tokenizer, LlamaTokenizer
+
+
+def _write(path, arch, fill):
+    import gguf
+    w = gguf.GGUFWriter(path, arch)
+    fill(w)
+    w.add_tensor("dummy", np.zeros(4, np.float32))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+
+
+# ---- Llama ---------------------------------------------------------------------------------------------------
+def llama_vocab():
+    vocab = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)]
+    scores = [0.0] * len(vocab)
+    singles = list("▁abcdefghijklmnopqrstuvwxyz.,!?<>/[]INST'é")
+    for c in singles:
+        vocab.append(c)
+        scores.append(-1000.0)
+    merged = ["he", "ll", "hell", "hello", "▁hello", "or", "ld", "▁w", "▁wor", "▁world", "th", "▁th", "▁the", "in", "ing",
+              "▁a", "an", "▁an", "▁and", "er", "re", "on", "at", "en", "▁t", "▁s", "st", "es", "▁[", "IN", "ST", "INST", "▁▁", "▁h"]
+    for i, m in enumerate(merged):
+        vocab.append(m)
+        scores.append(-float(i) * 0.5 - 1.0)
+    return vocab, scores
+
+
+@pytest.fixture(scope="module")
+def llama_tok(tmp_path_factory):
+    vocab, scores = llama_vocab()
+    path = str(tmp_path_factory.mktemp("tok") / "llama.gguf")
+
+    def fill(w):
+        w.add_array("tokenizer.ggml.tokens", vocab)
+        w.add_array("tokenizer.ggml.scores", [float(s) for s in scores])
+        w.add_uint32("tokenizer.ggml.bos_token_id", 1)
+        w.add_uint32("tokenizer.ggml.eos_token_id", 2)
+        w.add_uint32("tokenizer.ggml.unknown_token_id", 0)
+    _write(path, "llama", fill)
+    g = Gguf.open(path)
+    return LlamaTokenizer.from_gguf(g), ref.LlamaTokenizer(vocab, scores, 1, 2, 0), vocab, g
+
+
+def test_llama_known_answers(llama_tok):
+    tok, _, vocab, _ = llama_tok
+    ix = {v: i for i, v in enumerate(vocab)}
+    assert (tok.bos, tok.eos, tok.unk) == (1, 2, 0)
+    # " hello" -> "▁hello" is one piece once the merges run: ▁ h e l l o -> ... -> ▁hello
+    assert tok.encode(" hello", True, False) == [1, ix["▁hello"]]
+    assert tok.encode("hello world", False, True) == [ix["hello"], ix["▁world"], 2]
+    # a character outside the vocabulary falls back to its UTF-8 bytes, ids byte + 3
+    assert tok.encode("日", False, False) == [b + 3 for b in "日".encode()]
+    # "<s>" and "</s>" spelled out in the text become the special ids
+    assert tok.encode("<s>hello</s>", False, False) == [1, ix["hello"], 2]
+    assert tok.encode("", True, True) == [1, 2]
+    # the trim after <s> runs before U+2581 becomes a space, so it only removes real white space (tokenizer.rs:168-176)
+    assert tok.decode(0, ix["▁hello"]) == " hello" and tok.decode(1, ix["▁hello"]) == " hello"
+    assert tok.decode(0, ord("A") + 3) == "A" and tok.decode(0, 0xE9 + 3) == "é"
+
+
+def test_llama_matches_the_restatement(llama_tok):
+    tok, oracle_tok, vocab, _ = llama_tok
+    rng = random.Random(3)
+    alphabet = list("abcdehlnorstw  .,!?<>/sé日") + ["hello", " world", " the", "ing", "<s>", "</s>", "[INST]", "  "]
+    for _ in range(300):
+        text = "".join(rng.choice(alphabet) for _ in range(rng.randint(0, 24)))
+        for bos, eos in ((True, False), (False, True)):
+            assert tok.encode(text, bos, eos) == oracle_tok.encode(text, bos, eos), repr(text)
+    for prev in (0, 1, 7):
+        for t in range(len(vocab)):
+            assert tok.decode(prev, t) == oracle_tok.decode(prev, t), (prev, t, vocab[t])
+
+
+# ---- GPT-2 ---------------------------------------------------------------------------------------------------
+def gpt2_vocab():
+    b2u = ref.bytes_to_unicode()
+    vocab = [b2u[b] for b in range(256)]
+    corpus = ("the quick brown fox jumps over the lazy dog and then the other dogs, isn't it? we'll see: 12345 times 67, "
+              "naïve café — it's the thing they're doing in 2024!\n\n  hello world hello there  ")
+    words = [[b2u[b] for b in w.encode()] for w in ref.Gpt2Tokenizer.PAT.findall(corpus)]
+    merges = []
+    for _ in range(120):   # plain BPE training: most frequent adjacent pair first, ties by first occurrence
+        counts = {}
+        for w in words:
+            for a, b in zip(w, w[1:]):
+                counts[(a, b)] = counts.get((a, b), 0) + 1
+        if not counts:
+            break
+        (a, b), c = max(counts.items(), key=lambda kv: kv[1])
+        if c < 2:
+            break
+        merges.append(f"{a} {b}")
+        vocab.append(a + b)
+        for w in words:
+            i = 0
+            while i + 1 < len(w):
+                if w[i] == a and w[i + 1] == b:
+                    w[i:i + 2] = [a + b]
+                else:
+                    i += 1
+    vocab += ["<|endoftext|>", "<pad>"]
+    return vocab, merges
+
+
+@pytest.fixture(scope="module")
+def gpt2_tok(tmp_path_factory):
+    vocab, merges = gpt2_vocab()
+    path = str(tmp_path_factory.mktemp("tok") / "gpt2.gguf")
+    eot = vocab.index("<|endoftext|>")
+
+    def fill(w):
+        w.add_array("tokenizer.ggml.tokens", vocab)
+        w.add_array("tokenizer.ggml.merges", merges)
+        w.add_uint32("tokenizer.ggml.bos_token_id", eot)
+        w.add_uint32("tokenizer.ggml.eos_token_id", eot)
+    _write(path, "gpt2", fill)
+    g = Gguf.open(path)
+    return Gpt2Tokenizer.from_gguf(g), ref.Gpt2Tokenizer(vocab, merges, eot, eot), vocab, g
+
+
+def test_gpt2_matches_the_restatement(gpt2_tok):
+    tok, oracle_tok, vocab, _ = gpt2_tok
+    assert tok.bos == tok.eos == vocab.index("<|endoftext|>")
+    texts = ["the quick brown fox", " the lazy dog", "isn't it? we'll see they're", "12345 times 67", "hello  world\n\nthere ",
+             "naïve café", "日本語 テキスト 123", "a<|endoftext|>b<pad>", "<|endoftext|>", "", "   ", "x'sy'llz 'd", "tabs\tand\r\nlines",
+             "punct!!! ...and—dashes", "MiXeD CaSe 9x9", "ünïcödé Ελληνικά кириллица"]
+    rng = random.Random(5)
+    pool = list("the quick brown fox 0123456789 '.,!?-\n\t") + ["'ll", "'s", " the", "é", "日", "<pad>", "  "]
+    texts += ["".join(rng.choice(pool) for _ in range(rng.randint(1, 40))) for _ in range(300)]
+    for text in texts:
+        got, exp = tok.encode(text), oracle_tok.encode(text)
+        assert got == exp, repr(text)
+        assert tok.decode(got) == oracle_tok.decode(exp), repr(text)
+    # ASCII text survives a round trip; merges are applied (fewer ids than bytes)
+    ids = tok.encode("the quick brown fox jumps over the lazy dog")
+    assert tok.decode(ids) == "the quick brown fox jumps over the lazy dog" and len(ids) < 43
+
+
+def test_gpt2_unknown_special_token_is_an_error(gpt2_tok):
+    tok = gpt2_tok[0]
+    with pytest.raises(Exception) as e:
+        tok.encode("a <nope> b")
+    assert "not in the vocabulary" in str(e.value)
+
+
+# ---- chat template -------------------------------------------------------------------------------------------
+def test_chat_template_matches_the_restatement():
+    convs = [
+        [("user", "Hello there")],
+        [("system", " Be brief. "), ("user", "Hi"), ("assistant", " Hello! "), ("user", "  What is 2+2?\n")],
+        [("user", "a"), ("assistant", "b"), ("user", "c"), ("assistant", "d")],
+        [("system", "s"), ("user", "u")],
+    ]
+    for conv in convs:
+        assert ChatTemplate.apply(conv, "<s>", "</s>") == ref.chat_template_llama2(conv, "<s>", "</s>")
+    one = ChatTemplate.apply([("system", "S"), ("user", " hi ")], "<s>", "</s>")
+    assert "<s>[INST] <<SYS>>\nS\n<</SYS>>\n\nhi [/INST]" in one
+    assert " ok </s>" in ChatTemplate.apply([("user", "q"), ("assistant", "ok")], "<s>", "</s>")
+    with pytest.raises(Exception) as e:
+        ChatTemplate.apply([("assistant", "first")], "<s>", "</s>")
+    assert "alternate" in str(e.value)
+    with pytest.raises(ValueError):
+        ref.chat_template_llama2([("user", "a"), ("user", "b")], "<s>", "</s>")

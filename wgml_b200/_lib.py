@@ -94,6 +94,7 @@ SIGNATURES = {
     "wgb_sample": (_i, [_vp, _sz, _f, _f, _f, _vp, _vp]),
     "wgb_sampler_coin": (_f, [_u64, _u64]),
     "wgb_llama2_set_sampler": (_i, [_vp, _f, _f, _u64]),
+    "wgb_llama2_load_stats": (_i, [_vp, C.POINTER(_sz), C.POINTER(C.c_double)]),
     "wgb_gpt2_set_sampler": (_i, [_vp, _f, _f, _u64]),
     "wgb_gguf_open": (_i, [C.c_char_p, _pp]),
     "wgb_gguf_from_bytes": (_i, [_vp, _sz, _pp]),
@@ -115,6 +116,21 @@ SIGNATURES = {
     "wgb_gguf_meta_arr_str": (_i, [_vp, _u64, _u64, C.POINTER(_vp), C.POINTER(_u64)]),
     "wgb_gguf_tensor_find": (_i64, [_vp, C.c_char_p]),
     "wgb_gguf_tensor_info": (_i, [_vp, _u64, C.POINTER(GgufTensorC)]),
+    "wgb_llama_tokenizer_from_gguf": (_i, [_vp, _pp]),
+    "wgb_llama_tokenizer_destroy": (_i, [_vp]),
+    "wgb_llama_tokenizer_bos": (_u32, [_vp]),
+    "wgb_llama_tokenizer_eos": (_u32, [_vp]),
+    "wgb_llama_tokenizer_unk": (_u32, [_vp]),
+    "wgb_llama_tokenizer_vocab_size": (_sz, [_vp]),
+    "wgb_llama_tokenizer_encode": (_i, [_vp, C.c_char_p, _sz, _i, _i, _vp, _sz, C.POINTER(_sz)]),
+    "wgb_llama_tokenizer_decode": (_i, [_vp, _u32, _u32, _vp, _sz, C.POINTER(_sz)]),
+    "wgb_gpt2_tokenizer_from_gguf": (_i, [_vp, _pp]),
+    "wgb_gpt2_tokenizer_destroy": (_i, [_vp]),
+    "wgb_gpt2_tokenizer_bos": (_u32, [_vp]),
+    "wgb_gpt2_tokenizer_eos": (_u32, [_vp]),
+    "wgb_gpt2_tokenizer_encode": (_i, [_vp, C.c_char_p, _sz, _vp, _sz, C.POINTER(_sz)]),
+    "wgb_gpt2_tokenizer_decode": (_i, [_vp, _vp, _sz, _vp, _sz, C.POINTER(_sz)]),
+    "wgb_chat_template_llama2": (_i, [C.POINTER(C.c_char_p), C.POINTER(C.c_char_p), _sz, C.c_char_p, C.c_char_p, _vp, _sz, C.POINTER(_sz)]),
     "wgb_llama2_config_from_gguf": (_i, [_vp, _i, C.POINTER(Llama2ConfigC)]),
     "wgb_llama2_create": (_i, [C.POINTER(Llama2ConfigC), _i, _i, _i, _pp]),
     "wgb_llama2_destroy": (_i, [_vp]),

@@ -51,6 +51,8 @@ struct wgb_llama2 {
     uint32_t *h_pinned = nullptr;            // pinned staging of a decode call: [0] status word, [1..2] status polls, [3..] token ids
     size_t pinned_cap = 0;
     StatusPoll poll;
+    Uploader up;                             // pipelined weight upload (set_matrix / load_gguf)
+    bool loading = false;                    // inside wgb_llama2_load_gguf: the uploads are waited for once, at the end
     // sampling of generated tokens: temperature 0 = greedy (Sampler::sample, models/sampler.rs:32-52)
     float smp_temperature = 0.0f, smp_topp = 0.0f;
     unsigned long long smp_seed = 0;
@@ -496,6 +498,7 @@ WGB_EXPORT int wgb_llama2_destroy(wgb_llama2 *m)
     m->stamps = nullptr;
     m->tickets = m->tp_epoch = nullptr;
     status_poll_destroy(m->poll);
+    m->up.destroy();
     if (m->smp_scratch) cudaFree(m->smp_scratch);
     uint32_t *ubufs[] = { m->attn_counters, m->scalars, m->argmax_scratch, m->d_prompt, m->d_out };
     for (uint32_t *b : ubufs) if (b) cudaFree(b);
@@ -540,9 +543,10 @@ WGB_EXPORT int wgb_llama2_set_matrix(wgb_llama2 *m, int layer, int which, int qt
     WGB_REQUIRE(nrows == exp_rows && ncols == exp_cols, "matrix is %zu x %zu, the model expects %zu x %zu", nrows, ncols, exp_rows, exp_cols);
     WGB_REQUIRE(ncols % bl == 0, "ncols %zu is not a multiple of the block length %d", ncols, bl);
     wgb_quant_matrix *q = nullptr;
-    const int rc = qmat_create_slice(qtype, h_blocks, nrows, ncols, row0, rows_keep, kb0, kb_keep, nullptr, &q);
+    int rc = qmat_create_slice_async(m->up, qtype, h_blocks, nrows, ncols, row0, rows_keep, kb0, kb_keep, &q);
     if (rc) return rc;
-    WGB_CUDA(cudaStreamSynchronize(nullptr));
+    // a caller of its own may release h_blocks on return; the GGUF loader keeps the file mapped until it has waited
+    if (!m->loading && (rc = m->up.finish())) { wgb_quant_matrix_destroy(q); return rc; }
     wgb_quant_matrix_destroy(*slot);
     *slot = q;
     drop_graph(m);
@@ -649,6 +653,13 @@ WGB_EXPORT int wgb_llama2_load_gguf(wgb_llama2 *m, const wgb_gguf *g)
         if (t.n_bytes != n * 4) return fail(WGB_ERR_INVALID, "tensor '%s' has %llu bytes, expected %zu", name.c_str(), (unsigned long long)t.n_bytes, n * 4);
         return wgb_llama2_set_vector(m, layer, which, (const float *)t.data, n);
     };
+    // Every tensor's bytes are enqueued on the upload stream (pinned ring, repack kernels) without waiting; one
+    // wait at the end.  The figures of the batch are kept for wgb_llama2_load_stats.
+    m->loading = true;
+    struct Done {
+        wgb_llama2 *m;
+        ~Done() { m->up.finish(); m->loading = false; }
+    } done{m};
     int rc;
     for (uint32_t l = 0; l < c.n_layers; l++) {
         const std::string p = "blk." + std::to_string(l) + ".";
@@ -1022,5 +1033,13 @@ WGB_EXPORT int wgb_llama2_set_sampler(wgb_llama2 *m, float temperature, float to
     m->smp_topp = topp;
     m->smp_seed = seed;
     drop_graph(m);   // the parameters are baked into the recorded step
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_load_stats(const wgb_llama2 *m, size_t *bytes, double *seconds)
+{
+    WGB_REQUIRE(m && bytes && seconds, "null argument");
+    *bytes = m->up.total_bytes;
+    *seconds = m->up.total_seconds;
     return WGB_OK;
 }

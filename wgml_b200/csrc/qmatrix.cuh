@@ -57,6 +57,34 @@ struct wgb_quant_matrix {
 
 namespace wgb {
 
+// Pipelined host -> device upload of tensor bytes that live in pageable memory (a memory-mapped GGUF file):
+// the bytes go through a small ring of pinned buffers, so that the host's copy out of the mapping (page
+// faults, file reads), the DMA of the buffer before and the repack kernel of the tensor before overlap on one
+// copy stream; nothing waits for a tensor until finish().  The counterpart of the reference's eager
+// element-by-element parse (crates/wgml/src/gguf.rs:539-620, read_array_unaligned :671-681).
+struct Uploader {
+    static constexpr int NBUF = 3;
+    static constexpr size_t BUF_BYTES = (size_t)64 << 20;
+    cudaStream_t stream = nullptr;
+    uint8_t *h_buf[NBUF] = {};
+    cudaEvent_t free_ev[NBUF] = {};
+    bool used[NBUF] = {};
+    int next = 0;
+    uint8_t *d_raw = nullptr;      // device staging of the raw blocks of a tensor that is repacked on the device
+    size_t d_raw_cap = 0;
+    size_t bytes = 0;              // uploaded since the last finish()
+    double t0 = 0.0;               // when the first byte of the batch was taken
+    size_t total_bytes = 0;        // over all finished batches
+    double total_seconds = 0.0;    //   and their wall time, first byte to finish()
+
+    int init();
+    void destroy();
+    // `rows` runs of `run_bytes` bytes, `src_stride` apart in host memory, laid end to end at d_dst.
+    int copy_rows(uint8_t *d_dst, const uint8_t *h_src, size_t run_bytes, size_t src_stride, size_t rows);
+    int reserve_raw(size_t n);
+    int finish();                  // waits for everything enqueued; closes the timing batch
+};
+
 // Builds a matrix from raw GGUF blocks.  `src_on_device` says where `blocks` lives.  Planar
 // formats are repacked on the device; the temporary raw copy is released before returning.
 int qmat_create(int qtype, const void *blocks, bool src_on_device, size_t nrows, size_t ncols,
@@ -66,6 +94,10 @@ int qmat_create(int qtype, const void *blocks, bool src_on_device, size_t nrows,
 int qmat_create_slice(int qtype, const void *h_blocks, size_t nrows, size_t ncols, size_t row0,
                       size_t nrows_keep, size_t kb0, size_t bpr_keep, cudaStream_t stream,
                       wgb_quant_matrix **out);
+// The same through an Uploader: returns as soon as the copies and the repack are enqueued on the uploader's
+// stream; the matrix may be used after up.finish() (or by work ordered after that stream).
+int qmat_create_slice_async(Uploader &up, int qtype, const void *h_blocks, size_t nrows, size_t ncols, size_t row0,
+                            size_t nrows_keep, size_t kb0, size_t bpr_keep, wgb_quant_matrix **out);
 int qmat_dequantize_rows(const QMat &m, size_t row0, size_t n, float *d_out, cudaStream_t stream);
 // Device-side variant whose first row is read from *d_row (token id kept on the device).
 int qmat_dequantize_row_indirect(const QMat &m, const uint32_t *d_row, float *d_out, cudaStream_t stream);

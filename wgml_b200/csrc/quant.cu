@@ -1,6 +1,9 @@
 // Dequantisation kernels and the quantised-matrix object (upload, planar repack, row dequant).
 #include "qaccess.cuh"
 
+#include <algorithm>
+#include <cstring>
+#include <ctime>
 #include <new>
 
 namespace wgb {
@@ -171,6 +174,149 @@ int qmat_create_slice(int qtype, const void *h_blocks, size_t nrows, size_t ncol
         cudaFree(d_raw);
     }
     if (rc != WGB_OK) { cudaFree(m->storage); delete m; return rc; }
+    *out = m;
+    return WGB_OK;
+}
+
+static double now_s()
+{
+    timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return (double)ts.tv_sec + 1e-9 * (double)ts.tv_nsec;
+}
+
+int Uploader::init()
+{
+    if (stream) return WGB_OK;
+    WGB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    for (int i = 0; i < NBUF; i++) {
+        WGB_CUDA(cudaMallocHost((void **)&h_buf[i], BUF_BYTES));
+        WGB_CUDA(cudaEventCreateWithFlags(&free_ev[i], cudaEventDisableTiming));
+    }
+    return WGB_OK;
+}
+
+void Uploader::destroy()
+{
+    if (stream) cudaStreamSynchronize(stream);
+    for (int i = 0; i < NBUF; i++) {
+        if (h_buf[i]) cudaFreeHost(h_buf[i]);
+        if (free_ev[i]) cudaEventDestroy(free_ev[i]);
+        h_buf[i] = nullptr;
+        free_ev[i] = nullptr;
+        used[i] = false;
+    }
+    if (d_raw) cudaFree(d_raw);
+    d_raw = nullptr;
+    d_raw_cap = 0;
+    if (stream) cudaStreamDestroy(stream);
+    stream = nullptr;
+}
+
+int Uploader::reserve_raw(size_t n)
+{
+    if (n <= d_raw_cap) return WGB_OK;
+    WGB_CUDA(cudaStreamSynchronize(stream));   // a repack may still read the old buffer
+    if (d_raw) cudaFree(d_raw);
+    d_raw = nullptr;
+    d_raw_cap = 0;
+    WGB_CUDA(cudaMalloc((void **)&d_raw, n));
+    d_raw_cap = n;
+    return WGB_OK;
+}
+
+int Uploader::copy_rows(uint8_t *d_dst, const uint8_t *h_src, size_t run_bytes, size_t src_stride, size_t rows)
+{
+    int rc = init();
+    if (rc) return rc;
+    if (bytes == 0) t0 = now_s();
+    // contiguous source: one long run
+    if (run_bytes == src_stride || rows == 1) {
+        run_bytes *= rows;
+        rows = 1;
+    }
+    size_t done_rows = 0, done_in_row = 0;   // progress: whole rows, plus bytes inside a row longer than a buffer
+    while (done_rows < rows) {
+        const int b = next;
+        next = (next + 1) % NBUF;
+        if (used[b]) WGB_CUDA(cudaEventSynchronize(free_ev[b]));
+        size_t fill = 0;
+        const size_t dst_off = done_rows * run_bytes + done_in_row;
+        if (run_bytes > BUF_BYTES) {
+            fill = std::min(BUF_BYTES, run_bytes - done_in_row);
+            memcpy(h_buf[b], h_src + done_rows * src_stride + done_in_row, fill);
+            done_in_row += fill;
+            if (done_in_row == run_bytes) {
+                done_in_row = 0;
+                done_rows++;
+            }
+        } else {
+            const size_t n = std::min(rows - done_rows, BUF_BYTES / run_bytes);
+            for (size_t r = 0; r < n; r++) memcpy(h_buf[b] + r * run_bytes, h_src + (done_rows + r) * src_stride, run_bytes);
+            fill = n * run_bytes;
+            done_rows += n;
+        }
+        WGB_CUDA(cudaMemcpyAsync(d_dst + dst_off, h_buf[b], fill, cudaMemcpyHostToDevice, stream));
+        WGB_CUDA(cudaEventRecord(free_ev[b], stream));
+        used[b] = true;
+        bytes += fill;
+    }
+    return WGB_OK;
+}
+
+int Uploader::finish()
+{
+    if (!stream) return WGB_OK;
+    WGB_CUDA(cudaStreamSynchronize(stream));
+    if (bytes) {
+        total_seconds += now_s() - t0;
+        total_bytes += bytes;
+        bytes = 0;
+    }
+    return WGB_OK;
+}
+
+int qmat_create_slice_async(Uploader &up, int qtype, const void *h_blocks, size_t nrows, size_t ncols, size_t row0,
+                            size_t nrows_keep, size_t kb0, size_t bpr_keep, wgb_quant_matrix **out)
+{
+    if (!is_supported(qtype)) return fail(WGB_ERR_UNSUPPORTED, "unsupported tensor type %d", qtype);
+    const int bl = block_len(qtype), bb = block_bytes(qtype);
+    WGB_REQUIRE(out && h_blocks, "null argument");
+    WGB_REQUIRE(ncols % bl == 0, "ncols %zu is not a multiple of the block length %d", ncols, bl);
+    const size_t bpr = ncols / bl;
+    WGB_REQUIRE(row0 + nrows_keep <= nrows && kb0 + bpr_keep <= bpr && nrows_keep > 0 && bpr_keep > 0,
+                "slice outside the matrix");
+    int rc = up.init();
+    if (rc) return rc;
+    const bool planar = (qtype == WGB_Q8_0 || qtype == WGB_Q6_K);
+    wgb_quant_matrix *m = new (std::nothrow) wgb_quant_matrix();
+    if (!m) return fail(WGB_ERR_INVALID, "out of host memory");
+    m->view.qtype = qtype;
+    m->view.planar = planar;
+    m->view.nrows = (uint32_t)nrows_keep;
+    m->view.bpr = (uint32_t)bpr_keep;
+    m->view.ncols = (uint32_t)(bpr_keep * bl);
+    QMat tmp = m->view;
+    m->bytes = layout_planes(nrows_keep, nullptr, tmp);
+    cudaError_t e = cudaMalloc(&m->storage, m->bytes);
+    if (e != cudaSuccess) { delete m; return cuda_fail(e, "cudaMalloc(quant matrix)"); }
+    layout_planes(nrows_keep, (uint8_t *)m->storage, m->view);
+    const size_t raw_bytes = nrows_keep * bpr_keep * bb;
+    uint8_t *d_raw = (uint8_t *)m->storage;
+    if (planar) {
+        rc = up.reserve_raw(raw_bytes);
+        if (rc == WGB_OK && (e = cudaMemsetAsync(m->storage, 0, m->bytes, up.stream)) != cudaSuccess) rc = cuda_fail(e, "cudaMemset(quant matrix)");
+        d_raw = up.d_raw;
+    }
+    const uint8_t *src = (const uint8_t *)h_blocks + (row0 * bpr + kb0) * bb;
+    if (rc == WGB_OK) rc = up.copy_rows(d_raw, src, bpr_keep * bb, bpr * bb, nrows_keep);
+    if (rc == WGB_OK && planar) rc = repack_from_device_raw(qtype, d_raw, nrows_keep * bpr_keep, m->view, up.stream);
+    if (rc != WGB_OK) {
+        cudaStreamSynchronize(up.stream);
+        cudaFree(m->storage);
+        delete m;
+        return rc;
+    }
     *out = m;
     return WGB_OK;
 }

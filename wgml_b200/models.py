@@ -113,6 +113,12 @@ class Llama2:
         v = np.ascontiguousarray(tensors["output_norm.weight"][1], dtype=np.float32)
         check(lib.wgb_llama2_set_vector(self._h, -1, 0, v.ctypes.data, v.size))
 
+    def load_stats(self) -> tuple[int, float]:
+        """(bytes uploaded, seconds the uploads took) so far."""
+        b, t = C.c_size_t(), C.c_double()
+        check(_lib.load().wgb_llama2_load_stats(self._h, C.byref(b), C.byref(t)))
+        return b.value, t.value
+
     def set_fused(self, enable: bool) -> None:
         check(_lib.load().wgb_llama2_set_fused(self._h, int(enable)))
 
