@@ -167,7 +167,8 @@ def test_chat_template_matches_the_restatement():
     for conv in convs:
         assert ChatTemplate.apply(conv, "<s>", "</s>") == ref.chat_template_llama2(conv, "<s>", "</s>")
     one = ChatTemplate.apply([("system", "S"), ("user", " hi ")], "<s>", "</s>")
-    assert "<s>[INST] <<SYS>>\nS\n<</SYS>>\n\nhi [/INST]" in one
+    # the trim applies to system text + user text as one string: the user's own leading space survives
+    assert "<s>[INST] <<SYS>>\nS\n<</SYS>>\n\n hi [/INST]" in one
     assert " ok </s>" in ChatTemplate.apply([("user", "q"), ("assistant", "ok")], "<s>", "</s>")
     with pytest.raises(Exception) as e:
         ChatTemplate.apply([("assistant", "first")], "<s>", "</s>")
