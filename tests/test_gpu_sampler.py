@@ -4,8 +4,9 @@
 Token ids must be identical, draw by draw.  The device adds the softmax denominator and walks the CDF in the
 reference's order, so the only licence left is the last bit of expf (CUDA's and the host's differ on some
 arguments): a draw whose coin falls within 1e-5 of a CDF step or of the nucleus boundary (the oracle reports the
-distance, relative to the probability mass walked) may land on a neighbouring token.  Such draws are counted and
-must be rare."""
+distance, relative to the probability mass walked) may land on a neighbouring token, and so may a draw that picks
+among candidates whose probabilities agree to 2e-6 relative (their order in the sorted list is decided by that
+last bit).  Such draws are counted and must be rare."""
 import numpy as np
 import pytest
 import torch
@@ -42,7 +43,10 @@ def test_sample_matches_the_oracle_draw_by_draw(n, temperature, topp):
             got = s.sample(d, coin)
             total += 1
             if got != exp:
-                assert slack < 1e-5, f"{name} draw {i}: token {got} vs {exp} with the coin {slack:.3g} away from a CDF step"
+                z = logits.astype(np.float32) / np.float32(temperature) if temperature else logits
+                tied = abs(float(np.exp(np.float64(z[got]) - np.float64(z[exp]))) - 1.0) < 2e-6
+                assert slack < 1e-5 or tied, (f"{name} draw {i}: token {got} vs {exp} with the coin {slack:.3g} away from a "
+                                              f"CDF step and logits {z[got]!r} / {z[exp]!r}")
                 excused += 1
         assert torch.equal(d.cpu(), torch.from_numpy(logits)), "the logits were modified"
     assert total >= 256 and excused <= max(1, total // 100), f"{excused} of {total} draws fell on a rounding boundary"

@@ -480,24 +480,27 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     const uint32_t kw = (uint32_t)warp % kp, cl = (uint32_t)warp / kp;
     // The norm weights are parameters, not products of the launch before: their (cold, HBM-latency) loads
     // are issued ahead of the dependency wait and are in registers by the time the input can be read.
-    // A thread owns float4 chunks c = threadIdx.x + i * GEMV_CONS_THREADS; the first XC of them (all of
-    // them up to 8192 columns) live in registers from one round of loads to the staging.
-    // (6 chunks where the kernel is compiled for one prologue and that is "none": nothing else is held then)
-    constexpr uint32_t XC = PRO_T == PRO_NONE ? 6 : 4, WC = PRO_T == PRO_NONE ? 1 : 4;
-    const uint32_t nchunk = K / 4;
-    float4 wc[WC], bc[WC];
+    // A thread owns units of eight consecutive inputs (two float4 chunks), u = threadIdx.x + i * GEMV_CONS_THREADS;
+    // the first XU of them live in registers from one round of loads to the staging: all of them up to 8192
+    // columns, up to 12288 where the kernel has no norm parameters to hold.
+    constexpr uint32_t XU = PRO_T == PRO_NONE ? 3 : 2, WU = PRO_T == PRO_NONE ? 1 : 2;
+    const uint32_t nchunk = K / 4, nunit = (nchunk + 1) / 2;
+    float4 wc[2 * WU], bc[2 * WU];
     if (PRO != PRO_NONE) {
 #pragma unroll
-        for (uint32_t i = 0; i < WC; i++) {
-            const uint32_t c = threadIdx.x + i * GEMV_CONS_THREADS;
-            if (c < nchunk) {
-                wc[i] = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + c);
-                if (PRO == PRO_LN) bc[i] = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + c);
+        for (uint32_t i = 0; i < WU; i++) {
+            const uint32_t c = 2 * (threadIdx.x + i * GEMV_CONS_THREADS);
+#pragma unroll
+            for (uint32_t h = 0; h < 2; h++) {
+                if (c + h < nchunk) {
+                    wc[2 * i + h] = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + c + h);
+                    if (PRO == PRO_LN) bc[2 * i + h] = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + c + h);
+                }
             }
         }
     }
     pdl_wait();
-    float4 xc[XC];
+    float4 xc[2 * XU];
     const bool gather = PRO == PRO_RMS && a.peer_in.n != 0;
     if (gather) {
         // Partial products from every rank: wait for the flags, then add in rank order.  The wait is bounded
@@ -533,21 +536,25 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
         if (blockIdx.x == 0) reinterpret_cast<float4 *>(a.peer_in.x_out)[c] = v;
         return v;
     };
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (uint32_t i = 0; i < XC; i++) {
-        const uint32_t c = threadIdx.x + i * GEMV_CONS_THREADS;
-        xc[i] = c < nchunk ? load_chunk(c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t i = 0; i < XU; i++) {
+        const uint32_t c = 2 * (threadIdx.x + i * GEMV_CONS_THREADS);
+        xc[2 * i] = c < nchunk ? load_chunk(c) : zero4;
+        xc[2 * i + 1] = c + 1 < nchunk ? load_chunk(c + 1) : zero4;
     }
-    // Chunks past the ones held in registers (rows longer than 12288 columns) are read again where needed.
-    const uint32_t c_tail = threadIdx.x + XC * GEMV_CONS_THREADS;
+    // Units past the ones held in registers (longer rows) are read again where needed.
+    const uint32_t u_tail = threadIdx.x + XU * GEMV_CONS_THREADS;
     float mean = 0.0f, scale = 1.0f;
     if (PRO == PRO_RMS) {
         float ss = 0.0f;
 #pragma unroll
-        for (uint32_t i = 0; i < XC; i++) ss += xc[i].x * xc[i].x + xc[i].y * xc[i].y + xc[i].z * xc[i].z + xc[i].w * xc[i].w;
-        for (uint32_t c = c_tail; c < nchunk; c += GEMV_CONS_THREADS) {
-            const float4 v = load_chunk(c);
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        for (uint32_t i = 0; i < 2 * XU; i++) ss += xc[i].x * xc[i].x + xc[i].y * xc[i].y + xc[i].z * xc[i].z + xc[i].w * xc[i].w;
+        for (uint32_t u = u_tail; u < nunit; u += GEMV_CONS_THREADS) {
+            for (uint32_t c = 2 * u; c < min(2 * u + 2, nchunk); c++) {
+                const float4 v = load_chunk(c);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
         }
         // The scale is one factor for the whole vector, so it commutes with the dot products: the input is
         // staged as x * w, the warps' sums of squares go to `red`, and the epilogue warp multiplies every
@@ -557,24 +564,28 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
     } else if (PRO == PRO_LN) {
         float sm = 0.0f;
 #pragma unroll
-        for (uint32_t i = 0; i < XC; i++) sm += (xc[i].x + xc[i].y) + (xc[i].z + xc[i].w);   // chunks past the end are zero
-        for (uint32_t c = c_tail; c < nchunk; c += GEMV_CONS_THREADS) {
-            const float4 v = load_chunk(c);
-            sm += (v.x + v.y) + (v.z + v.w);
+        for (uint32_t i = 0; i < 2 * XU; i++) sm += (xc[i].x + xc[i].y) + (xc[i].z + xc[i].w);   // chunks past the end are zero
+        for (uint32_t u = u_tail; u < nunit; u += GEMV_CONS_THREADS) {
+            for (uint32_t c = 2 * u; c < min(2 * u + 2, nchunk); c++) {
+                const float4 v = load_chunk(c);
+                sm += (v.x + v.y) + (v.z + v.w);
+            }
         }
         mean = cons_sum(sm, red) / (float)K;
         float ss = 0.0f;
 #pragma unroll
-        for (uint32_t i = 0; i < XC; i++) {
-            if (threadIdx.x + i * GEMV_CONS_THREADS < nchunk) {
+        for (uint32_t i = 0; i < 2 * XU; i++) {
+            if (2 * (threadIdx.x + (i / 2) * GEMV_CONS_THREADS) + (i & 1) < nchunk) {
                 const float dx = xc[i].x - mean, dy = xc[i].y - mean, dz = xc[i].z - mean, dw = xc[i].w - mean;
                 ss += dx * dx + dy * dy + dz * dz + dw * dw;
             }
         }
-        for (uint32_t c = c_tail; c < nchunk; c += GEMV_CONS_THREADS) {
-            float4 v = load_chunk(c);
-            v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        for (uint32_t u = u_tail; u < nunit; u += GEMV_CONS_THREADS) {
+            for (uint32_t c = 2 * u; c < min(2 * u + 2, nchunk); c++) {
+                float4 v = load_chunk(c);
+                v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
         }
         ss = cons_sum(ss, red);
         scale = 1.0f / sqrtf(ss / (float)K + 1.0e-5f);
@@ -590,42 +601,36 @@ __global__ void __launch_bounds__(GEMV_NT, 1) gemv_kernel(const __grid_constant_
             }
             return v;
         };
+        auto param = [&](const float *p, uint32_t c, bool in) {
+            return in ? __ldg(reinterpret_cast<const float4 *>(p) + c) : zero4;
+        };
         // whole warps go round together (the writer shuffles): the bound is per warp, not per lane
-        const uint32_t warp_c0 = (uint32_t)warp * 32;
+        const uint32_t warp_u0 = (uint32_t)warp * 32;
 #pragma unroll
-        for (uint32_t i = 0; i < XC; i++) {
-            if (warp_c0 + i * GEMV_CONS_THREADS < nchunk) {
-                const uint32_t c = threadIdx.x + i * GEMV_CONS_THREADS;
-                const bool in = c < nchunk;
-                float4 w = make_float4(0.f, 0.f, 0.f, 0.f), b = w;
-                if (i < WC) {
-                    w = wc[i];
-                    b = bc[i];
-                } else if (in) {
-                    if (PRO != PRO_NONE) w = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + c);
-                    if (PRO == PRO_LN) b = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + c);
+        for (uint32_t i = 0; i < XU; i++) {
+            if (warp_u0 + i * GEMV_CONS_THREADS < nunit) {
+                const uint32_t u = threadIdx.x + i * GEMV_CONS_THREADS, c = 2 * u;
+                const bool in = c < nchunk, inb = c + 1 < nchunk;
+                float4 w0 = zero4, w1 = zero4, b0 = zero4, b1 = zero4;
+                if (i < WU) {
+                    w0 = wc[2 * i]; w1 = wc[2 * i + 1];
+                    b0 = bc[2 * i]; b1 = bc[2 * i + 1];
+                } else if (PRO != PRO_NONE) {
+                    w0 = param(a.norm_w, c, in); w1 = param(a.norm_w, c + 1, inb);
+                    if (PRO == PRO_LN) { b0 = param(a.norm_b, c, in); b1 = param(a.norm_b, c + 1, inb); }
                 }
-                xw.put(c, transform(xc[i], w, b), in);
+                xw.put8(u, transform(xc[2 * i], w0, b0), transform(xc[2 * i + 1], w1, b1), in, inb);
             }
         }
-        // the rest two chunks per trip, both requested before either is used (one trip to L2, not two)
-        for (uint32_t c0 = warp_c0 + XC * GEMV_CONS_THREADS; c0 < nchunk; c0 += 2 * GEMV_CONS_THREADS) {
-            const uint32_t ca = c0 + lane, cb = ca + GEMV_CONS_THREADS;
-            const bool ina = ca < nchunk, inb = cb < nchunk, second = c0 + GEMV_CONS_THREADS < nchunk;
-            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-            float4 va = z, vb = z, wa = z, wb = z, ba = z, bb = z;
-            if (ina) {
-                va = load_chunk(ca);
-                if (PRO != PRO_NONE) wa = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + ca);
-                if (PRO == PRO_LN) ba = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + ca);
-            }
-            if (inb) {
-                vb = load_chunk(cb);
-                if (PRO != PRO_NONE) wb = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + cb);
-                if (PRO == PRO_LN) bb = __ldg(reinterpret_cast<const float4 *>(a.norm_b) + cb);
-            }
-            xw.put(ca, transform(va, wa, ba), ina);
-            if (second) xw.put(cb, transform(vb, wb, bb), inb);
+        for (uint32_t u0 = warp_u0 + XU * GEMV_CONS_THREADS; u0 < nunit; u0 += GEMV_CONS_THREADS) {
+            const uint32_t u = u0 + lane, c = 2 * u;
+            const bool in = c < nchunk, inb = c + 1 < nchunk;
+            float4 va = zero4, vb = zero4, w0 = zero4, w1 = zero4, b0 = zero4, b1 = zero4;
+            if (in) va = load_chunk(c);
+            if (inb) vb = load_chunk(c + 1);
+            if (PRO != PRO_NONE) { w0 = param(a.norm_w, c, in); w1 = param(a.norm_w, c + 1, inb); }
+            if (PRO == PRO_LN) { b0 = param(a.norm_b, c, in); b1 = param(a.norm_b, c + 1, inb); }
+            xw.put8(u, transform(va, w0, b0), transform(vb, w1, b1), in, inb);
         }
     }
     cons_sync();

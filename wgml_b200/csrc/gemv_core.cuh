@@ -392,6 +392,45 @@ struct XWriter {
         xsum = xscale + ((K / 32 + 3) & ~3u);
     }
 
+    // Eight consecutive values at once: float4 chunks c = 2u (va) and 2u + 1 (vb) of the thread's unit u; lane l
+    // of a warp calls with unit u0 + l, so that four consecutive lanes hold one 32-column group and two hold a
+    // 16-column run.  Half the shuffles of put() per value and one 64-bit store per digit plane.  `inb`: chunk
+    // 2u + 1 exists (only a dense f32 vector can end in the middle of a unit).
+    __device__ __forceinline__ void put8(uint32_t u, const float4 va, const float4 vb, bool in, bool inb) const
+    {
+        const uint32_t c = 2 * u;
+        if (QT == WGB_F32) {
+            if (in) xf[c] = va;
+            if (in && inb) xf[c + 1] = vb;
+            return;
+        }
+        float m = fmaxf(fmaxf(fmaxf(fabsf(va.x), fabsf(va.y)), fmaxf(fabsf(va.z), fabsf(va.w))),
+                        fmaxf(fmaxf(fabsf(vb.x), fabsf(vb.y)), fmaxf(fabsf(vb.z), fabsf(vb.w))));
+        float sum = ((va.x + va.y) + (va.z + va.w)) + ((vb.x + vb.y) + (vb.z + vb.w));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        uint32_t ex = (__float_as_uint(m) >> 23) & 0xffu;
+        ex = ex < 24u ? 24u : (ex > 253u ? 253u : ex);
+        const float up = __uint_as_float((275u - ex) << 23);    // 2^(148 - ex), see put()
+        auto fix = [&](float v) { return (int)(__float_as_uint(fmaf(v, up, 12582912.0f)) - 0x4b400000u); };
+        const int A0 = fix(va.x), A1 = fix(va.y), A2 = fix(va.z), A3 = fix(va.w);
+        const int B0 = fix(vb.x), B1 = fix(vb.y), B2 = fix(vb.z), B3 = fix(vb.w);
+        if (in) {
+            const uint32_t a01 = __byte_perm(A0, A1, 0x5410), a23 = __byte_perm(A2, A3, 0x5410);
+            const uint32_t a01h = __byte_perm(A0, A1, 0x7632), a23h = __byte_perm(A2, A3, 0x7632);
+            const uint32_t b01 = __byte_perm(B0, B1, 0x5410), b23 = __byte_perm(B2, B3, 0x5410);
+            const uint32_t b01h = __byte_perm(B0, B1, 0x7632), b23h = __byte_perm(B2, B3, 0x7632);
+            // chunks 2u and 2u + 1 sit side by side inside one (swizzled) 16-byte chunk of every digit plane
+            const uint32_t pos = swz<QT>(c >> 2) * 4 + (c & 3);
+            *reinterpret_cast<uint2 *>(d0 + pos) = make_uint2(__byte_perm(a01, a23, 0x6420), __byte_perm(b01, b23, 0x6420));
+            *reinterpret_cast<uint2 *>(d1 + pos) = make_uint2(__byte_perm(a01, a23, 0x7531), __byte_perm(b01, b23, 0x7531));
+            *reinterpret_cast<uint2 *>(d2 + pos) = make_uint2(__byte_perm(a01h, a23h, 0x6420), __byte_perm(b01h, b23h, 0x6420));
+            if ((u & 3) == 0) xscale[u >> 2] = __uint_as_float((ex - 21u) << 23);   // 2^(ex - 148)
+            if ((u & 1) == 0) xsum[u >> 1] = sum;
+        }
+    }
+
     __device__ __forceinline__ void put(uint32_t c, const float4 v, bool in) const
     {
         if (QT == WGB_F32) {
