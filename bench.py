@@ -389,6 +389,28 @@ def run_b200(args):
         "kernels_per_token": int(model.kernels_per_token()),
         "clocks": clocks.summary(), "roofline": roofline, "breakdown": classes,
     }
+    if rank == 0 and world == 1 and not args.no_prefill and prompt_len >= 16:
+        # prompt throughput: the same prompt position by position through the token loop (what the reference does) and
+        # through the batched passes (eight positions per pass, Q4_K products on the tensor cores)
+        def time_prompt():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            model.decode(prompt, 0)
+            b.record(stream)
+            torch.cuda.synchronize()
+            return a.elapsed_time(b)
+        seq_ms = min(time_prompt() for _ in range(2))
+        model.set_prefill(True)
+        time_prompt()
+        before = model.prefill_positions()
+        bat_ms = min(time_prompt() for _ in range(2))
+        batched = (model.prefill_positions() - before) // 2
+        model.set_prefill(False)
+        line["prefill"] = {"prompt_positions": prompt_len - 1, "positions_in_batched_passes": batched,
+                           "sequential": {"ms": seq_ms, "tok_s": (prompt_len - 1) / (seq_ms * 1e-3)},
+                           "batched": {"ms": bat_ms, "tok_s": (prompt_len - 1) / (bat_ms * 1e-3)},
+                           "how": "wgb_llama2_decode(prompt, n_gen = 0) between CUDA events, best of 2; batched = after "
+                                  "wgb_llama2_set_prefill(1); formats other than Q4_K go position by position inside a pass"}
     if rank == 0 and world == 1 and workload == "llama2-7b" and not args.no_microbench:
         # the stand-alone quantised matrix-vector cases (4 shapes x 3 block formats), each launch on a fresh copy
         # of the matrix so that it streams from HBM: microseconds, algorithmic GB/s and fraction of the measured peak
@@ -493,6 +515,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "llama2-7b", "llama2-70b", "tiny-llama", "gpt2-124m"])
     ap.add_argument("--prompt-len", type=int, default=None)
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prompt-throughput measurement")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="tensor-parallel runs: partial products exchanged by the kernels through peer memory (default) "
                          "or by an NCCL all-reduce")

@@ -107,6 +107,11 @@ typedef struct wgb_q4k_tiles wgb_q4k_tiles;
 int wgb_q4k_tiles_create(const void *h_blocks, size_t nrows, size_t ncols, void *stream, wgb_q4k_tiles **out);
 int wgb_q4k_tiles_destroy(wgb_q4k_tiles *m);
 int wgb_gemv_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, float *d_out, void *stream);
+/* The same product for 1..8 input vectors at once, d_v [n_vec][ncols] -> d_out [n_vec][nrows]: the tensor-core
+ * kernel of the batched prompt prefill (wgb_llama2_set_prefill), any number of columns that is a multiple of
+ * 256.  In the reference a prompt costs one GemvQuant::dispatch per matrix and position
+ * (chat_llama2.rs:104-116); here eight positions share one pass over the weights.  Synchronises. */
+int wgb_gemm_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream);
 /* Waits for the device and returns WGB_ERR_TIMEOUT if a bounded wait inside a matrix-vector kernel has
  * expired since the last report (stand-alone launches are asynchronous and cannot say so themselves). */
 int wgb_device_status(void);
@@ -390,6 +395,18 @@ int wgb_llama2_load_stats(const wgb_llama2 *m, size_t *bytes, double *seconds);
  * coin = wgb_sampler_coin(seed, position of the sampled token).  temperature 0 (the default) is greedy.
  * The draw happens on the device: no logits leave it. */
 int wgb_llama2_set_sampler(wgb_llama2 *m, float temperature, float topp, uint64_t seed);
+/* Batched prompt prefill, no counterpart in the reference (its chat loop feeds the prompt one position per
+ * Llama2::dispatch, chat_llama2.rs:104-116,169-204, and drops the logits).  Once enabled, wgb_llama2_decode
+ * sends every prompt position but the last through passes of eight positions: the Q4_K layer matrices are
+ * multiplied on the tensor cores (tcgen05.mma kind::i8 on the same fixed-point image of the activations as the
+ * matrix-vector kernels, from tile-major copies of the weights made here, which doubles their memory), other
+ * formats through the matrix-vector kernel position by position; RMSNorm, RoPE, the cache rows and causal
+ * attention are computed per pass.  Cache rows and everything after the prompt agree with the
+ * position-by-position path to the order of the f32 additions.  One GPU per model only (WGB_ERR_UNSUPPORTED
+ * for a tensor-parallel rank); enable it after the weights are set (setting a matrix disables it). */
+int wgb_llama2_set_prefill(wgb_llama2 *m, int enable);
+/* Prompt positions that have gone through the batched passes since it was enabled. */
+int wgb_llama2_prefill_positions(const wgb_llama2 *m, size_t *positions);
 /* Number of kernels one decode step launches (for launch accounting). */
 int wgb_llama2_kernels_per_token(const wgb_llama2 *m);
 /* Measurement aid, the counterpart of wgcore's GpuTimestamps around a pass

@@ -55,6 +55,7 @@ def test_shapes_outside_the_path_are_refused():
     raw, _ = make(128, 256, 1)
     with pytest.raises(_lib.WgbError):
         ops.Q4KTiles(raw[: 100 * 144], 100, 256)            # rows not a multiple of 128
-    big, _ = make(128, 8192, 1)
-    with pytest.raises(_lib.WgbError):
-        ops.Q4KTiles(big, 128, 8192)                        # more columns than the shared-memory image holds
+    big, x = make(128, 8192, 1)
+    t = ops.Q4KTiles(big, 128, 8192)
+    with pytest.raises(_lib.WgbError):                      # more columns than the single-vector kernel's image holds
+        t.gemv(torch.zeros(128, device="cuda"), torch.from_numpy(x).cuda())

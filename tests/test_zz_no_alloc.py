@@ -44,6 +44,9 @@ def _run(fn_static, p, q, k, v):
     dict(seq_len=768, n_heads=32, kv_mul=1, head=128, pos=(540, 17)),      # 7B layout, two different depths
     dict(seq_len=4224, n_heads=64, kv_mul=8, head=128, pos=(4100, 4101)),  # 70B layout, grouped-query
     dict(seq_len=256, n_heads=6, kv_mul=1, head=48, pos=(0, 255)),         # tiny model: first and last position
+    # more chunks than one wave of blocks: the streaming kernel (then a short context on the same scratch)
+    dict(seq_len=8192, n_heads=32, kv_mul=1, head=128, pos=(8000, 70)),
+    dict(seq_len=8192, n_heads=32, kv_mul=2, head=128, pos=(8100, 8101)),  # two query heads per KV head
 ])
 def test_static_matches_allocating_entry_point_twice_in_a_row(shape):
     pos = shape.pop("pos")

@@ -79,6 +79,7 @@ SIGNATURES = {
     "wgb_q4k_tiles_create": (_i, [_vp, _sz, _sz, _vp, C.POINTER(_vp)]),
     "wgb_q4k_tiles_destroy": (_i, [_vp]),
     "wgb_gemv_q4k_tiles": (_i, [_vp, _vp, _vp, _vp]),
+    "wgb_gemm_q4k_tiles": (_i, [_vp, _vp, _sz, _vp, _vp]),
     "wgb_device_status": (_i, []),
     "wgb_rms_norm": (_i, [_vp, _vp, _vp, _sz, _f, _vp]),
     "wgb_layernorm": (_i, [_vp, _vp, _sz, _vp]),
@@ -95,6 +96,8 @@ SIGNATURES = {
     "wgb_sampler_coin": (_f, [_u64, _u64]),
     "wgb_llama2_set_sampler": (_i, [_vp, _f, _f, _u64]),
     "wgb_llama2_load_stats": (_i, [_vp, C.POINTER(_sz), C.POINTER(C.c_double)]),
+    "wgb_llama2_set_prefill": (_i, [_vp, _i]),
+    "wgb_llama2_prefill_positions": (_i, [_vp, C.POINTER(_sz)]),
     "wgb_gpt2_set_sampler": (_i, [_vp, _f, _f, _u64]),
     "wgb_gguf_open": (_i, [C.c_char_p, _pp]),
     "wgb_gguf_from_bytes": (_i, [_vp, _sz, _pp]),

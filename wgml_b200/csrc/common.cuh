@@ -48,6 +48,7 @@ struct DeviceState {
     uint32_t *err = nullptr;              // device status word: 0, or the code of the first bounded wait that expired
     bool gemv_attrs = false;              // fused matrix-vector kernels opted in to large dynamic shared memory
     bool tiles_attrs = false;             // the same for the tensor-memory kernel
+    bool prefill_attrs = false;           // the same for the batched tensor-memory kernel
     float *attn_scratch = nullptr;        // scratch of the stand-alone attention op, grown on demand
     size_t attn_scratch_floats = 0;
     uint32_t *attn_counters = nullptr;
@@ -133,6 +134,12 @@ __device__ __forceinline__ float block_max(float v, float *red)
 // stream has completed and its writes are visible; `pdl_launch_dependents` lets the following
 // kernel start its independent prologue.  Both are no-ops for a kernel launched without the
 // programmatic-serialization attribute.
+// Rule for every read placed BEFORE pdl_wait: it may touch only memory that no launch still in flight can
+// write -- weights, launch parameters, and KV-cache rows of positions earlier than this step's (the rows at the
+// current position are written by the step's own q/k/v launch and are read after the wait).  Activations,
+// the token / position scalars, flags, tickets and the status word are always read after the wait.  A kernel
+// launched with the attribute whose predecessor was launched with it too must itself wait before it exits,
+// otherwise its successor's wait no longer covers the predecessor.
 // End-of-launch time stamp for per-launch timing inside a graph replay: the latest %globaltimer (ns) over
 // the blocks of a launch.  Called by one thread per block after its last store; a NULL slot costs a branch.
 __device__ __forceinline__ void stamp_end(unsigned long long *slot)

@@ -22,14 +22,10 @@
 // are issued and run (two operand buffers, two sets of accumulator columns).
 // Every wait is bounded; the first that expires records a code and every loop of the block winds down.
 #include "kernels.h"
-#include "async_copy.cuh"
-#include "gemv_core.cuh"
+#include "tc_common.cuh"
 
 namespace wgb {
 
-constexpr uint32_t TC_TILE_ROWS = 128;
-constexpr uint32_t TC_UNIT_BYTES = TC_TILE_ROWS * 144;        // one super-block column of a tile, raw
-constexpr uint32_t TC_A_BYTES = TC_TILE_ROWS * 256;           // the same, unpacked to bytes
 constexpr uint32_t TC_MAX_K = 4096;
 constexpr uint32_t TC_RING = 6;
 constexpr uint32_t TC_WPQ = 4;                                // worker warps per quarter of the tile's rows
@@ -55,84 +51,6 @@ struct TcArgs {
     uint32_t nrows, K;
     uint32_t *err;
 };
-
-// 64-bit shared-memory operand descriptor, no swizzle, K-major operand: start address, the byte distance
-// between core matrices (8 rows x 16 bytes) adjacent along K ("leading" field) and the distance between
-// those adjacent along the rows ("stride" field).  Checked against the dp4a kernel on the device.
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
-    d |= (uint64_t)((leading_bytes & 0x3ffffu) >> 4) << 16;
-    d |= (uint64_t)((stride_bytes & 0x3ffffu) >> 4) << 32;
-    d |= (uint64_t)1 << 46;   // descriptor version of this architecture
-    return d;
-}
-// The same for a K-major operand in the 128-byte swizzled layout: rows of 128 bytes, groups of 8 rows
-// (1024 bytes, `group_bytes` apart), the 16-byte chunks of row i stored at chunk index ^ (i % 8).  A step
-// along K inside the 128 bytes is a plain byte offset on the start address (tile base on a 1 KB boundary).
-__device__ __forceinline__ uint64_t tc_smem_desc_sw128(uint32_t addr, uint32_t group_bytes)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3ffffu) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)((group_bytes & 0x3ffffu) >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;   // 128-byte swizzle
-    return d;
-}
-
-// kind::i8 instruction descriptor: D s32, A u8, B s8, both K-major, M = 128, N = 16.
-__device__ __forceinline__ uint32_t tc_idesc()
-{
-    return (2u << 4) | (0u << 7) | (1u << 10) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
-}
-
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.u32 p, 0, 0;\n\t"   // do not accumulate: D = A * B
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc)
-        : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_ld4(uint32_t taddr, int (&v)[4])
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
-                 : "r"(taddr)
-                 : "memory");
-}
-
-// Bounded wait (in time) that also gives up when another thread of the block already has.
-__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *dead, uint32_t *err, uint32_t code)
-{
-#pragma unroll 1
-    for (int i = 0; i < 512; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63) == 63 && *dead) return false;
-    }
-    const unsigned long long t0 = global_ns();
-    do {
-#pragma unroll 1
-        for (int i = 0; i < 256; i++)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*dead) return false;
-    } while (global_ns() - t0 < ASYNC_WAIT_NS);
-    *dead = 1;
-    if (err) atomicCAS(err, 0u, code);
-    return false;
-}
-
-__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
-{
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
 
 // Fixed-point image of the input: thread g quantises the 32 inputs of group g.
 __device__ __forceinline__ void tc_stage_group(uint8_t *smem, const float *x, uint32_t g)
@@ -238,7 +156,7 @@ __global__ void __launch_bounds__(TC_NT, 1) gemv_q4k_tc_kernel(const __grid_cons
         // The descriptors are worked out once: a single thread issues, and its own instruction stream is what
         // bounds the rate.  The start-address field is the low 14 bits in units of 16 bytes; the offsets added
         // below stay inside it (shared memory ends below 2^18).
-        const uint32_t idesc = tc_idesc();
+        const uint32_t idesc = tc_idesc(16);
         const uint64_t adesc0 = tc_smem_desc_sw128(smem_addr(smem + TC_OFF_A), 1024);
         const uint64_t bdesc0 = tc_smem_desc(smem_addr(smem + TC_OFF_B), 128, 0);
         uint32_t kb = 0;
@@ -389,7 +307,7 @@ WGB_EXPORT int wgb_q4k_tiles_create(const void *h_blocks, size_t nrows, size_t n
 {
     WGB_REQUIRE(h_blocks && out, "null argument");
     WGB_REQUIRE(nrows > 0 && nrows % TC_TILE_ROWS == 0, "the tensor-core path wants a multiple of %u rows, got %zu", TC_TILE_ROWS, nrows);
-    WGB_REQUIRE(ncols > 0 && ncols % 256 == 0 && ncols <= TC_MAX_K, "the tensor-core path wants a multiple of 256 columns up to %u, got %zu", TC_MAX_K, ncols);
+    WGB_REQUIRE(ncols > 0 && ncols % 256 == 0, "the tensor-core path wants a multiple of 256 columns, got %zu", ncols);
     int rc = gemv_global_init();
     if (rc) return rc;
     DeviceState *ds = device_state();
@@ -435,6 +353,8 @@ WGB_EXPORT int wgb_q4k_tiles_destroy(wgb_q4k_tiles *m)
 WGB_EXPORT int wgb_gemv_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, float *d_out, void *stream)
 {
     WGB_REQUIRE(m && d_v && d_out, "null argument");
+    WGB_REQUIRE(m->ncols <= TC_MAX_K, "the single-vector tensor-core kernel keeps the whole input image in shared memory: up to %u columns, got %u",
+                TC_MAX_K, m->ncols);
     TcArgs a = {};
     a.w = m->w;
     a.x = d_v;
@@ -447,6 +367,33 @@ WGB_EXPORT int wgb_gemv_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, floa
     gemv_q4k_tc_kernel<<<grid, TC_NT, TC_SMEM + 1024, as_stream(stream)>>>(a);
     WGB_LAUNCH_CHECK("gemv_q4k_tc_kernel");
     return WGB_OK;
+}
+
+// The same product for up to eight input vectors at once (the kernel of the batched prompt prefill, prefill.cu):
+// d_v [n_vec][ncols] -> d_out [n_vec][nrows].  Allocates its work areas per call (a test and measurement entry
+// point; the model keeps its own).
+WGB_EXPORT int wgb_gemm_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream)
+{
+    WGB_REQUIRE(m && d_v && d_out, "null argument");
+    WGB_REQUIRE(n_vec >= 1 && n_vec <= PF_TOK, "between 1 and %u input vectors, got %zu", PF_TOK, n_vec);
+    cudaStream_t st = as_stream(stream);
+    const uint32_t ns = prefill_gemm_splits(m->nrows, m->ncols);
+    uint8_t *image = nullptr;
+    float *part = nullptr;
+    cudaError_t e = cudaMalloc((void **)&image, prefill_image_bytes(m->ncols));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&part, (size_t)ns * PF_TOK * m->nrows * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemsetAsync(image, 0, prefill_image_bytes(m->ncols), st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d_out, 0, n_vec * m->nrows * sizeof(float), st);
+    int rc = e == cudaSuccess ? WGB_OK : cuda_fail(e, "work areas of the batched product");
+    // image of the inputs (they are not written: no slices are folded into them)
+    if (!rc) rc = launch_prefill_norm_image(const_cast<float *>(d_v), m->ncols, nullptr, 0, 0, nullptr, 0.0f, m->ncols, (uint32_t)n_vec, image, nullptr, 0, st);
+    if (!rc) rc = launch_gemm_q4k_tiles(m->w, m->nrows, m->ncols, image, (uint32_t)n_vec, part, m->nrows, ns, st);
+    // d_out (zero) += the slices
+    if (!rc) rc = launch_prefill_norm_image(d_out, m->nrows, part, ns, m->nrows, nullptr, 0.0f, m->nrows, (uint32_t)n_vec, nullptr, nullptr, 0, st);
+    if (!rc && (e = cudaStreamSynchronize(st)) != cudaSuccess) rc = cuda_fail(e, "batched product");
+    if (image) cudaFree(image);
+    if (part) cudaFree(part);
+    return rc;
 }
 
 // Waits for the device and reports whether a bounded wait inside any matrix-vector kernel has expired since

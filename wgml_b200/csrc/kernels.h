@@ -158,4 +158,39 @@ size_t sampler_scratch_bytes(uint32_t n);
 int launch_sample(const float *logits, uint32_t n, float temperature, float topp, float coin, int seeded, unsigned long long seed,
                   void *scratch, uint32_t *out_index, const LoopState *ls, cudaStream_t stream);
 
+
+// ---- batched prompt prefill (prefill.cu) --------------------------------------------------------------
+constexpr uint32_t PF_TOK = 8;         // prompt positions per pass
+constexpr uint32_t PF_MAX_SPLIT = 8;   // column slices of one product
+// Bytes of the fixed-point activation image of PF_TOK vectors of K elements (zero it once: the kernels never
+// write its padding rows).
+size_t prefill_image_bytes(uint32_t K);
+bool prefill_tileable(const QMat &m);
+// Tile-major copy of a Q4_K matrix for the tensor-core product (cudaMalloc'd, *out).
+int prefill_tile_major(const QMat &m, uint8_t **out, cudaStream_t stream);
+uint32_t prefill_gemm_splits(uint32_t nrows, uint32_t K);
+// out[slice][position][row] (out_stride floats per position) = the product of the tile-major matrix with the
+// `ntok` vectors whose image is `image`, the columns cut into `nsplit` slices.
+int launch_gemm_q4k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, const uint8_t *image, uint32_t ntok, float *out,
+                          uint32_t out_stride, uint32_t nsplit, cudaStream_t stream);
+// x[t] (+= the slices of `part` when given, written back); then optionally RMS-normalised with norm_w; the image
+// of the result and, with xn, the values.  With neither image nor xn only x is updated.
+int launch_prefill_norm_image(float *x, uint32_t x_stride, const float *part, uint32_t nsplit, uint32_t part_stride, const float *norm_w,
+                              float eps, uint32_t K, uint32_t ntok, uint8_t *image, float *xn, uint32_t xn_stride, cudaStream_t stream);
+int launch_prefill_silu_image(const float *gate, uint32_t gsplit, const float *up, uint32_t usplit, uint32_t stride, uint32_t K,
+                              uint32_t ntok, uint8_t *image, float *h, uint32_t h_stride, cudaStream_t stream);
+struct PrefillQkv {
+    const float *q, *k, *v;            // product slices: [split][PF_TOK][stride]
+    uint32_t q_split, k_split, v_split, q_stride, kv_stride;
+    const float *bq, *bk, *bv;         // optional biases
+    float *q_out;                      // [ntok][q_dim]
+    float *k_cache, *v_cache;          // one layer, head-major
+    uint32_t q_dim, kv_dim, head_size, seq_len, pos0;
+    int variant;
+    const float *freq;
+};
+int launch_prefill_rope_append(const PrefillQkv &a, uint32_t ntok, cudaStream_t stream);
+int launch_prefill_attention(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
+                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, cudaStream_t stream);
+
 }  // namespace wgb

@@ -10,6 +10,7 @@
 // once into a CUDA graph and replayed per token.
 #include "kernels.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -79,6 +80,16 @@ struct wgb_llama2 {
     bool stamping = false;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_kind, prof_layer;
+    // batched prompt prefill (wgb_llama2_set_prefill): tile-major copies of the Q4_K layer matrices for the
+    // tensor-core product, activation images and the buffers of a pass of PF_TOK positions
+    struct Prefill {
+        bool enabled = false;
+        std::vector<uint8_t *> tiles;        // [layer * 7 + matrix], NULL: no tensor-core path for that matrix
+        uint8_t *img_dim = nullptr, *img_q = nullptr, *img_hidden = nullptr;
+        float *x = nullptr, *xn = nullptr, *q = nullptr, *xb = nullptr, *h = nullptr;   // [PF_TOK][dim | q_dim | hidden]
+        float *part[3] = {};                 // product slices: [PF_MAX_SPLIT][PF_TOK][max(dim, q_dim, hidden)]
+        size_t positions = 0;                // prompt positions that went through it, over all decode calls
+    } pf;
 };
 
 namespace {
@@ -387,6 +398,94 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
     return WGB_OK;
 }
 
+void prefill_free(wgb_llama2 *m)
+{
+    for (uint8_t *t : m->pf.tiles) if (t) cudaFree(t);
+    m->pf.tiles.clear();
+    uint8_t *imgs[] = { m->pf.img_dim, m->pf.img_q, m->pf.img_hidden };
+    for (uint8_t *b : imgs) if (b) cudaFree(b);
+    float *bufs[] = { m->pf.x, m->pf.xn, m->pf.q, m->pf.xb, m->pf.h, m->pf.part[0], m->pf.part[1], m->pf.part[2] };
+    for (float *b : bufs) if (b) cudaFree(b);
+    m->pf = wgb_llama2::Prefill();
+}
+
+// One product of a prefill pass: W . (the `ntok` vectors whose image is `image` and whose values are xf), as
+// slices [slice][PF_TOK][stride] in `out`.  Matrices without a tile-major copy (any format but Q4_K) go through
+// the matrix-vector kernel once per position.
+int prefill_product(wgb_llama2 *m, uint32_t layer, int which, const uint8_t *image, const float *xf, uint32_t xf_stride, uint32_t ntok,
+                    float *out, uint32_t stride, uint32_t *nsplit, cudaStream_t s)
+{
+    const QMat &w = m->layers[layer].m[which]->view;
+    const uint8_t *tiles = m->pf.tiles[(size_t)layer * 7 + which];
+    if (tiles) {
+        *nsplit = prefill_gemm_splits(w.nrows, w.ncols);
+        return launch_gemm_q4k_tiles(tiles, w.nrows, w.ncols, image, ntok, out, stride, *nsplit, s);
+    }
+    *nsplit = 1;
+    for (uint32_t t = 0; t < ntok; t++) {
+        int rc = mat_vec(w, xf + (size_t)t * xf_stride, out + (size_t)t * stride, s);
+        if (rc) return rc;
+    }
+    return WGB_OK;
+}
+
+// Prompt positions pos0 .. pos0 + ntok - 1 (tokens d_tokens[0 .. ntok)) through the layer stack in one pass: the
+// work of ntok calls of Llama2::dispatch (models/llama2/transformer.rs:298-431) up to the last layer's cache
+// rows -- the logits of prompt positions are never looked at (chat_llama2.rs:169-204 samples only once the
+// prompt is through), so the final norm and the output matrix are left out.
+int prefill_pass(wgb_llama2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32_t pos0, uint32_t ntok)
+{
+    const wgb_llama2_config &c = m->cfg;
+    wgb_llama2::Prefill &pf = m->pf;
+    const int variant = m->model_type == WGB_QWEN2 ? WGB_ROPE_NEOX : WGB_ROPE_ORIGINAL;
+    const uint32_t dim = c.dim, q_dim = m->q_dim, kv_dim = m->kv_dim, hidden = m->hidden;
+    int rc;
+    for (uint32_t t = 0; t < ntok; t++)
+        if ((rc = launch_embed(m->token_embd->view, nullptr, d_tokens + t, m->scalars + 1, pf.x + (size_t)t * dim, s))) return rc;
+    const size_t cache_stride = (size_t)c.seq_len * kv_dim;
+    const float *pending = nullptr;   // slices of the last layer's ffn_down, folded into x by the next norm
+    uint32_t pending_split = 0;
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        const wgb_llama2::Layer &w = m->layers[l];
+        uint32_t nq, nk, nv, no, ng, nu, nd;
+        if ((rc = launch_prefill_norm_image(pf.x, dim, pending, pending_split, dim, w.v[WGB_L_ATTN_NORM], c.rms_norm_eps, dim, ntok, pf.img_dim,
+                                            pf.xn, dim, s)))
+            return rc;
+        if ((rc = prefill_product(m, l, WGB_L_ATTN_Q, pf.img_dim, pf.xn, dim, ntok, pf.part[0], q_dim, &nq, s))) return rc;
+        if ((rc = prefill_product(m, l, WGB_L_ATTN_K, pf.img_dim, pf.xn, dim, ntok, pf.part[1], kv_dim, &nk, s))) return rc;
+        if ((rc = prefill_product(m, l, WGB_L_ATTN_V, pf.img_dim, pf.xn, dim, ntok, pf.part[2], kv_dim, &nv, s))) return rc;
+        PrefillQkv qa = {};
+        qa.q = pf.part[0]; qa.k = pf.part[1]; qa.v = pf.part[2];
+        qa.q_split = nq; qa.k_split = nk; qa.v_split = nv;
+        qa.q_stride = q_dim; qa.kv_stride = kv_dim;
+        qa.bq = w.v[WGB_L_ATTN_Q_BIAS]; qa.bk = w.v[WGB_L_ATTN_K_BIAS]; qa.bv = w.v[WGB_L_ATTN_V_BIAS];
+        qa.q_out = pf.q;
+        qa.k_cache = m->key_cache + l * cache_stride;
+        qa.v_cache = m->value_cache + l * cache_stride;
+        qa.q_dim = q_dim; qa.kv_dim = kv_dim; qa.head_size = m->head_size; qa.seq_len = c.seq_len; qa.pos0 = pos0;
+        qa.variant = variant;
+        qa.freq = m->rope_freq;
+        if ((rc = launch_prefill_rope_append(qa, ntok, s))) return rc;
+        if ((rc = launch_prefill_attention(pf.q, qa.k_cache, qa.v_cache, pf.xb, m->n_q_local, m->head_size, m->kv_mul, c.seq_len, pos0, ntok, s)))
+            return rc;
+        if ((rc = launch_prefill_norm_image(pf.xb, q_dim, nullptr, 0, 0, nullptr, 0.0f, q_dim, ntok, pf.img_q, nullptr, 0, s))) return rc;
+        if ((rc = prefill_product(m, l, WGB_L_ATTN_OUTPUT, pf.img_q, pf.xb, q_dim, ntok, pf.part[0], dim, &no, s))) return rc;
+        if ((rc = launch_prefill_norm_image(pf.x, dim, pf.part[0], no, dim, w.v[WGB_L_FFN_NORM], c.rms_norm_eps, dim, ntok, pf.img_dim, pf.xn, dim,
+                                            s)))
+            return rc;
+        if ((rc = prefill_product(m, l, WGB_L_FFN_GATE, pf.img_dim, pf.xn, dim, ntok, pf.part[0], hidden, &ng, s))) return rc;
+        if ((rc = prefill_product(m, l, WGB_L_FFN_UP, pf.img_dim, pf.xn, dim, ntok, pf.part[1], hidden, &nu, s))) return rc;
+        if ((rc = launch_prefill_silu_image(pf.part[0], ng, pf.part[1], nu, hidden, hidden, ntok, pf.img_hidden, pf.h, hidden, s))) return rc;
+        if ((rc = prefill_product(m, l, WGB_L_FFN_DOWN, pf.img_hidden, pf.h, hidden, ntok, pf.part[2], dim, &nd, s))) return rc;
+        pending = pf.part[2];
+        pending_split = nd;
+    }
+    // leave the residual stream of the pass complete (nothing reads it; it keeps wgb_llama2_x meaningful for tests)
+    if ((rc = launch_prefill_norm_image(pf.x, dim, pending, pending_split, dim, nullptr, 0.0f, dim, ntok, nullptr, nullptr, 0, s))) return rc;
+    pf.positions += ntok;
+    return WGB_OK;
+}
+
 void drop_graph(wgb_llama2 *m)
 {
     if (m->graph) cudaGraphExecDestroy(m->graph);
@@ -483,6 +582,7 @@ WGB_EXPORT int wgb_llama2_destroy(wgb_llama2 *m)
 {
     if (!m) return WGB_OK;
     drop_graph(m);
+    prefill_free(m);
     for (auto &l : m->layers) {
         for (auto *q : l.m) wgb_quant_matrix_destroy(q);
         for (auto *v : l.v) if (v) cudaFree(v);
@@ -511,6 +611,7 @@ WGB_EXPORT int wgb_llama2_set_matrix(wgb_llama2 *m, int layer, int which, int qt
                                      size_t ncols)
 {
     WGB_REQUIRE(m && h_blocks, "null argument");
+    if (m->pf.enabled) prefill_free(m);   // its tile-major copies would go stale
     const wgb_llama2_config &c = m->cfg;
     const int bl = block_len(qtype);
     if (!bl) return fail(WGB_ERR_UNSUPPORTED, "unsupported tensor type %d", qtype);
@@ -963,7 +1064,21 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
     }
     // the first token travels as a kernel argument; the rest of the prompt is only read when there is one
     if (n_prompt > 1) WGB_CUDA(cudaMemcpyAsync(m->d_prompt, h_prompt, n_prompt * 4, cudaMemcpyHostToDevice, s));
-    set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, h_prompt[0], start_pos, 0);
+    // Batched prefill: every prompt position but the last (whose logits choose the first generated token) may go
+    // through passes of PF_TOK positions; a remainder shorter than half a pass stays with the token loop.
+    size_t done = 0;
+    if (m->pf.enabled && n_prompt - 1 >= PF_TOK) {
+        const size_t rem = (n_prompt - 1) % PF_TOK;
+        const size_t batched = n_prompt - 1 - (rem >= PF_TOK / 2 ? 0 : rem);
+        for (; done < batched; done += PF_TOK) {
+            const uint32_t nt = (uint32_t)(batched - done < PF_TOK ? batched - done : PF_TOK);
+            if ((rc = prefill_pass(m, s, m->d_prompt + done, start_pos + (uint32_t)done, nt))) return rc;
+        }
+        done = batched;
+        // the token loop reports prompt[i + 1] for step i < n_prompt - 1
+        WGB_CUDA(cudaMemcpyAsync(m->d_out, m->d_prompt + 1, done * 4, cudaMemcpyDeviceToDevice, s));
+    }
+    set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, h_prompt[done], start_pos + (uint32_t)done, (uint32_t)done);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
 
     LoopState ls = {};
@@ -1014,7 +1129,7 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
         m->graph_n_prompt = (uint32_t)n_prompt;
         m->graph_attn_chunks = (uint32_t)attn_class;
     }
-    if ((rc = replay_with_status(m->graph, total, s, m->h_pinned + 1, m->poll))) return rc;
+    if ((rc = replay_with_status(m->graph, total - done, s, m->h_pinned + 1, m->poll))) return rc;
     // One wait for the ids and the kernels' status word, both through pinned memory.
     WGB_CUDA(cudaMemcpyAsync(m->h_pinned + 3, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
     m->h_pinned[0] = 0;
@@ -1022,6 +1137,54 @@ WGB_EXPORT int wgb_llama2_decode(wgb_llama2 *m, const uint32_t *h_prompt, size_t
     WGB_CUDA(cudaStreamSynchronize(s));
     memcpy(h_out_tokens, m->h_pinned + 3, total * 4);
     return gemv_report_status(m->h_pinned[0]);
+}
+
+WGB_EXPORT int wgb_llama2_set_prefill(wgb_llama2 *m, int enable)
+{
+    WGB_REQUIRE(m, "null argument");
+    if (!enable) {
+        prefill_free(m);
+        return WGB_OK;
+    }
+    if (m->pf.enabled) return WGB_OK;
+    if (m->tp_size != 1) return fail(WGB_ERR_UNSUPPORTED, "batched prefill is built for one GPU per model; this model is rank %d of %d", m->tp_rank, m->tp_size);
+    int rc = check_complete(m);
+    if (rc) return rc;
+    if ((rc = gemv_global_init())) return rc;
+    const wgb_llama2_config &c = m->cfg;
+    WGB_REQUIRE(c.dim % 256 == 0 && m->q_dim % 256 == 0 && m->hidden % 256 == 0 && m->kv_dim % 4 == 0 && m->head_size % 4 == 0 && m->head_size <= 256,
+                "batched prefill wants widths that are multiples of 256 (dim %u, attention width %u, hidden %u) and a head size up to 256", c.dim,
+                m->q_dim, m->hidden);
+    wgb_llama2::Prefill &pf = m->pf;
+    pf.tiles.assign((size_t)c.n_layers * 7, nullptr);
+    auto bail = [&](int code) { prefill_free(m); return code; };
+    for (uint32_t l = 0; l < c.n_layers; l++)
+        for (int i = 0; i < 7; i++) {
+            const QMat &w = m->layers[l].m[i]->view;
+            if (prefill_tileable(w) && (rc = prefill_tile_major(w, &pf.tiles[(size_t)l * 7 + i], nullptr))) return bail(rc);
+        }
+    auto image = [&](uint8_t **p, uint32_t K) -> int {
+        WGB_CUDA(cudaMalloc((void **)p, prefill_image_bytes(K)));
+        WGB_CUDA(cudaMemset(*p, 0, prefill_image_bytes(K)));
+        return WGB_OK;
+    };
+    if ((rc = image(&pf.img_dim, c.dim)) || (rc = image(&pf.img_q, m->q_dim)) || (rc = image(&pf.img_hidden, m->hidden))) return bail(rc);
+    const size_t widest = std::max<size_t>(std::max<size_t>(c.dim, m->q_dim), m->hidden);
+    if ((rc = dalloc(&pf.x, (size_t)PF_TOK * c.dim)) || (rc = dalloc(&pf.xn, (size_t)PF_TOK * c.dim)) || (rc = dalloc(&pf.q, (size_t)PF_TOK * m->q_dim)) ||
+        (rc = dalloc(&pf.xb, (size_t)PF_TOK * m->q_dim)) || (rc = dalloc(&pf.h, (size_t)PF_TOK * m->hidden)))
+        return bail(rc);
+    for (int i = 0; i < 3; i++)
+        if ((rc = dalloc(&pf.part[i], (size_t)PF_MAX_SPLIT * PF_TOK * widest))) return bail(rc);
+    WGB_CUDA(cudaDeviceSynchronize());
+    pf.enabled = true;
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_prefill_positions(const wgb_llama2 *m, size_t *positions)
+{
+    WGB_REQUIRE(m && positions, "null argument");
+    *positions = m->pf.positions;
+    return WGB_OK;
 }
 
 WGB_EXPORT int wgb_llama2_set_sampler(wgb_llama2 *m, float temperature, float topp, uint64_t seed)

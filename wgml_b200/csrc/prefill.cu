@@ -1,0 +1,668 @@
+// Batched prompt prefill: up to eight prompt positions per pass through the layer stack, with the Q4_K
+// matrix products on the fifth-generation tensor cores.
+//
+// The reference feeds the prompt through its decode path one token at a time (wgml-chat/src/chat_llama2.rs:
+// 104-116, 169-204: every prompt position is a full Llama2::dispatch whose logits are thrown away).  Here a pass
+// takes eight positions: each weight is read once for the eight, and the products run as tcgen05.mma kind::i8
+// on the fixed-point image of the activations that the batch-1 kernels use (three signed byte digits per
+// element, one power-of-two exponent per 32 columns), so a prompt position costs what the reference's CPU twin
+// computes for it (models/llama2/cpu.rs:83-178) up to the order of the f32 additions.
+//
+// Matrix product (gemm_q4k_tc_kernel).  Weights tile-major as for the single-vector tensor-core kernel
+// (gemv_tc.cu).  Work item = (tile of 128 rows, slice of the super-block columns); an item's units (one
+// super-block column each: 18 KB of weights and the 8.5 KB slice of the activation image that goes with it)
+// stream through a ring of shared-memory stages.  Sixteen worker warps unpack the nibbles of a unit into the A
+// operand (128 x 256 bytes, 128-byte swizzle), one thread issues eight MMAs per unit (one per 32-column
+// sub-block; M = 128, N = 32: rows 8 d + t of the B operand hold digit d of position t, rows 24..31 are zero,
+// K = 32) into 256 columns of tensor memory (two such sets alternate), and the workers read the sums back
+// (tcgen05.ld), apply digit weights, exponents, six-bit scales and the min term in FP32 and keep one running
+// sum per position.  Each item leaves its partial rows in out[slice][position][row]; whoever consumes the
+// product adds the slices in a fixed order, so results do not depend on the schedule.
+// Every wait is bounded in time; after an expired wait the loops keep their shape (all hardware barriers are
+// still met) but do nothing, and a code is left in the device's status word.
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace wgb {
+
+constexpr uint32_t TB_IMG_DIGITS = 16 * 4 * 128;                          // 16 K-cores x 4 row groups x 128 bytes
+constexpr uint32_t TB_IMG_BYTES = TB_IMG_DIGITS + 2 * 8 * PF_TOK * 4;     // + exponents and sums [group][position]
+constexpr uint32_t TB_STAGE = TB_IMG_BYTES + TC_UNIT_BYTES;
+constexpr uint32_t TB_RING = 4;
+constexpr uint32_t TB_WORKER_WARPS = 16;
+constexpr uint32_t TB_NT = 32 * (2 + TB_WORKER_WARPS);
+constexpr uint32_t TB_TMEM_COLS = 512;                                    // two sets of eight 32-column results
+constexpr uint32_t TB_OFF_A = 0;                                          // two operand buffers (units alternate)
+constexpr uint32_t TB_OFF_RING = TB_OFF_A + 2 * TC_A_BYTES;
+constexpr uint32_t TB_SMEM = TB_OFF_RING + TB_RING * TB_STAGE;
+static_assert(PF_TOK == 8, "one core matrix (eight rows) per digit");
+static_assert(TB_STAGE % 128 == 0 && TB_IMG_BYTES % 16 == 0, "stages keep the operand alignment");
+static_assert(TB_SMEM + 1024 + 20 * 1024 <= 227 * 1024, "shared memory budget (dynamic + static)");
+
+size_t prefill_image_bytes(uint32_t K) { return (size_t)(K / 256) * TB_IMG_BYTES; }
+
+struct TbArgs {
+    const uint8_t *w;     // tile-major blocks: [tile][column][128 rows][144 bytes]
+    const uint8_t *img;   // activation image: [column][TB_IMG_BYTES]
+    float *out;           // [nsplit][PF_TOK][out_stride]
+    uint32_t nrows, nkb, nsplit, ntok, out_stride;
+    uint32_t *err;
+};
+
+// Units of a block: items blockIdx.x, blockIdx.x + gridDim.x, ...; item i = (tile i / nsplit, slice i % nsplit),
+// whose columns are [slice * nkb / nsplit, (slice + 1) * nkb / nsplit).
+struct UnitWalk {
+    uint32_t item, tile, sp, kb, kb_end;
+    __device__ __forceinline__ void set(uint32_t i, uint32_t nsplit, uint32_t nkb)
+    {
+        item = i;
+        tile = i / nsplit;
+        sp = i - tile * nsplit;
+        kb = sp * nkb / nsplit;
+        kb_end = (sp + 1) * nkb / nsplit;
+    }
+    __device__ __forceinline__ bool last() const { return kb + 1 == kb_end; }
+    __device__ __forceinline__ void next(uint32_t nsplit, uint32_t nkb, uint32_t stride)
+    {
+        if (++kb == kb_end) set(item + stride, nsplit, nkb);
+    }
+};
+
+__global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_constant__ TbArgs a)
+{
+    extern __shared__ uint8_t tb_smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * TB_RING + 2];
+    __shared__ float rowpart[4][PF_TOK][TC_TILE_ROWS];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ uint32_t dead_flag;
+    uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)tb_smem_raw + 1023) & ~(uintptr_t)1023);
+    volatile uint32_t *dead = &dead_flag;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t nkb = a.nkb, nsplit = a.nsplit, nitems = (a.nrows / TC_TILE_ROWS) * nsplit;
+    auto bar_full = [&](uint32_t s) { return smem_addr(&bars[s]); };
+    auto bar_empty = [&](uint32_t s) { return smem_addr(&bars[TB_RING + s]); };
+    auto bar_done = [&](uint32_t u) { return smem_addr(&bars[2 * TB_RING + u]); };
+    auto stage = [&](uint32_t s) { return smem_addr(smem + TB_OFF_RING) + s * TB_STAGE; };
+    uint32_t total = 0;
+    for (uint32_t i = blockIdx.x; i < nitems; i += gridDim.x) {
+        const uint32_t sp = i % nsplit;
+        total += (sp + 1) * nkb / nsplit - sp * nkb / nsplit;
+    }
+
+    if (threadIdx.x == 0) {
+        dead_flag = 0;
+        for (uint32_t s = 0; s < TB_RING; s++) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 32 * TB_WORKER_WARPS);
+        }
+        mbar_init(bar_done(0), 1);
+        mbar_init(bar_done(1), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)), "r"(TB_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0 && total) {
+            UnitWalk w;
+            w.set(blockIdx.x, nsplit, nkb);
+            bool ok = true;
+            for (uint32_t n = 0; n < total && ok; n++) {
+                const uint32_t s = n % TB_RING, round = n / TB_RING;
+                if (round) ok = tc_wait(bar_empty(s), (round - 1) & 1, dead, a.err, 21);
+                if (!ok) break;
+                mbar_expect_tx(bar_full(s), TB_STAGE);
+                bulk_copy_g2s(stage(s), a.img + (size_t)w.kb * TB_IMG_BYTES, TB_IMG_BYTES, bar_full(s));
+                bulk_copy_g2s(stage(s) + TB_IMG_BYTES, a.w + ((size_t)w.tile * nkb + w.kb) * TC_UNIT_BYTES, TC_UNIT_BYTES, bar_full(s));
+                w.next(nsplit, nkb, gridDim.x);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issue ------------------------------
+        // Unit n is complete in operand buffer n % 2 once all worker threads have arrived at hardware barrier
+        // 3 + n % 2 (they do not wait there); this warp waits there, then one thread issues the unit's eight
+        // MMAs into accumulator columns 256 (n % 2) ... and commits them to the unit's barrier.  The B operand
+        // is read in place from the unit's stage (K-major, no swizzle: core matrices of eight positions x 16
+        // columns, the four row groups of a K-core 128 bytes apart, K-cores 512 bytes apart).
+        const uint32_t idesc = tc_idesc(32);
+        const uint64_t adesc0 = tc_smem_desc_sw128(smem_addr(smem + TB_OFF_A), 1024);
+        for (uint32_t n = 0; n < total; n++) {
+            const uint32_t u = n & 1, s = n % TB_RING;
+            if (u) asm volatile("bar.sync 4, %0;" ::"n"(32 * TB_WORKER_WARPS + 32) : "memory");
+            else asm volatile("bar.sync 3, %0;" ::"n"(32 * TB_WORKER_WARPS + 32) : "memory");
+            if (lane == 0 && !*dead && tc_wait(bar_full(s), (n / TB_RING) & 1, dead, a.err, 22)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t ad = adesc0 + (uint64_t)(u * (TC_A_BYTES >> 4));
+                const uint64_t bd = tc_smem_desc(stage(s), 512, 128);
+                const uint32_t dcol = tmem_base + u * 256;
+#pragma unroll
+                for (uint32_t j = 0; j < 8; j++)
+                    tc_mma(dcol + 32 * j, ad + (uint64_t)(((j >> 2) * 16384 + (j & 3) * 32) >> 4), bd + (uint64_t)((j * 1024) >> 4), idesc);
+                tc_commit(bar_done(u));
+            }
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------ workers ------------------------------
+        // Thread (quarter, lane, sub): row r = 32 quarter + lane of the tile (the quarter of tensor memory its
+        // warp may read), 32-byte chunk `sub` of that row's nibbles (sub-blocks 2 sub and 2 sub + 1).
+        const uint32_t w = warp - 2, sub = w / 4, quarter = warp & 3, r = quarter * 32 + lane;
+        const uint32_t arow = smem_addr(smem + TB_OFF_A) + (r >> 3) * 1024 + (r & 7) * 128;
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+        float rowacc[PF_TOK];
+#pragma unroll
+        for (uint32_t t = 0; t < PF_TOK; t++) rowacc[t] = 0.0f;
+        bool ok = true;
+        UnitWalk fin;   // the unit being finished (one step behind the one being unpacked)
+        fin.set(blockIdx.x, nsplit, nkb);
+        // Step n unpacks unit n into operand buffer n % 2, tells the MMA warp (an arrival at a hardware barrier,
+        // without waiting), and goes on to finish unit n - 1, whose MMAs were issued a step ago.  Buffer n % 2 is
+        // free again by then: finishing unit n - 2 waited for its MMAs.  After an expired wait (`ok` false,
+        // warp-uniform) the loop keeps its shape, so that every thread still meets every hardware barrier.
+        for (uint32_t n = 0; n <= total; n++) {
+            if (n < total) {
+                const uint32_t slot = n % TB_RING, u = n & 1;
+                if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_full(slot), (n / TB_RING) & 1, dead, a.err, 23));
+                const uint32_t raw = stage(slot) + TB_IMG_BYTES + r * 144;
+                if (ok) {
+                    // nibbles -> bytes: low nibbles are sub-block 2 sub, high nibbles (left as 16 * code) sub-block
+                    // 2 sub + 1; sub-block j lies in K panel j / 4 (16 KB) at bytes 32 (j % 4) .. + 31 of the row,
+                    // 16-byte chunks swizzled by the row index
+#pragma unroll
+                    for (uint32_t core = 0; core < 2; core++) {
+                        const uint4 q = lds128(raw + 16 + 32 * sub + 16 * core);
+                        const uint32_t jl = 2 * sub, jh = 2 * sub + 1;
+                        sts128(arow + u * TC_A_BYTES + (jl >> 2) * 16384 + (((2 * (jl & 3) + core) ^ (r & 7)) << 4),
+                               q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
+                        sts128(arow + u * TC_A_BYTES + (jh >> 2) * 16384 + (((2 * (jh & 3) + core) ^ (r & 7)) << 4),
+                               q.x & 0xf0f0f0f0u, q.y & 0xf0f0f0f0u, q.z & 0xf0f0f0f0u, q.w & 0xf0f0f0f0u);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if (u) asm volatile("bar.arrive 4, %0;" ::"n"(32 * TB_WORKER_WARPS + 32) : "memory");
+                else asm volatile("bar.arrive 3, %0;" ::"n"(32 * TB_WORKER_WARPS + 32) : "memory");
+            }
+            if (n >= 1) {
+                const uint32_t m = n - 1, slot = m % TB_RING, u = m & 1;
+                const uint32_t img = stage(slot), raw = img + TB_IMG_BYTES + r * 144;
+                const uint4 hdr = lds128(raw);
+                const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, m_lo = hdr.z & 0x3f3f3f3fu;
+                const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+                const uint32_t m_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+                const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+                // six-bit scales and mins of sub-blocks 2 sub, 2 sub + 1 in the low bytes of a word each
+                const uint32_t sh = (sub & 1) * 16;
+                const uint32_t scw = (sub < 2 ? sc_lo : sc_hi) >> sh, mw = (sub < 2 ? m_lo : m_hi) >> sh;
+                if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), (m >> 1) & 1, dead, a.err, 24));
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    float acc[PF_TOK], neg[PF_TOK];
+#pragma unroll
+                    for (uint32_t q = 0; q < 2; q++) {
+                        int d[3][8];
+#pragma unroll
+                        for (uint32_t dg = 0; dg < 3; dg++) tc_ld8(taddr + u * 256 + 32 * (2 * sub + q) + 8 * dg, d[dg]);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        // exponents and sums of group 2 sub + q, one float per position
+                        const uint32_t eo = img + TB_IMG_DIGITS + (2 * sub + q) * PF_TOK * 4;
+                        const uint4 e0 = lds128(eo), e1 = lds128(eo + 16), s0 = lds128(eo + 8 * PF_TOK * 4), s1 = lds128(eo + 8 * PF_TOK * 4 + 16);
+                        const float ev[8] = { __uint_as_float(e0.x), __uint_as_float(e0.y), __uint_as_float(e0.z), __uint_as_float(e0.w),
+                                              __uint_as_float(e1.x), __uint_as_float(e1.y), __uint_as_float(e1.z), __uint_as_float(e1.w) };
+                        const float sv[8] = { __uint_as_float(s0.x), __uint_as_float(s0.y), __uint_as_float(s0.z), __uint_as_float(s0.w),
+                                              __uint_as_float(s1.x), __uint_as_float(s1.y), __uint_as_float(s1.z), __uint_as_float(s1.w) };
+                        const float sc = byte2f(scw, q), mn = byte2f(mw, q);
+#pragma unroll
+                        for (uint32_t t = 0; t < PF_TOK; t++) {
+                            // |digit sum| <= 32 * 240 * 128 < 2^22: the offset conversion is exact
+                            const float f = fmaf(i2f(d[2][t]), 65536.0f, fmaf(i2f(d[1][t]), 256.0f, i2f(d[0][t])));
+                            if (q == 0) {
+                                acc[t] = f * (sc * ev[t]);
+                                neg[t] = mn * sv[t];
+                            } else {
+                                acc[t] = fmaf(f, sc * ev[t], acc[t]);
+                                neg[t] = fmaf(mn, sv[t], neg[t]);
+                            }
+                        }
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (uint32_t t = 0; t < PF_TOK; t++) rowacc[t] += dm.x * acc[t] - dm.y * neg[t];
+                }
+                mbar_arrive(bar_empty(slot));
+                if (fin.last()) {
+                    // the rows' totals over this item's columns: the four threads of a row, in a fixed order
+#pragma unroll
+                    for (uint32_t t = 0; t < PF_TOK; t++) {
+                        rowpart[sub][t][r] = rowacc[t];
+                        rowacc[t] = 0.0f;
+                    }
+                    asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_WORKER_WARPS) : "memory");
+                    if (ok) {
+#pragma unroll
+                        for (uint32_t tt = 0; tt < 2; tt++) {
+                            const uint32_t t = 2 * sub + tt;
+                            if (t < a.ntok) {
+                                const float v = ((rowpart[0][t][r] + rowpart[1][t][r]) + rowpart[2][t][r]) + rowpart[3][t][r];
+                                a.out[((size_t)fin.sp * PF_TOK + t) * a.out_stride + (size_t)fin.tile * TC_TILE_ROWS + r] = v;
+                            }
+                        }
+                    }
+                    asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_WORKER_WARPS) : "memory");
+                }
+                fin.next(nsplit, nkb, gridDim.x);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TB_TMEM_COLS) : "memory");
+    }
+}
+
+// Column slices per tile: enough items to fill the machine, at least three units per item, and the count whose
+// last wave is fullest.
+uint32_t prefill_gemm_splits(uint32_t nrows, uint32_t K)
+{
+    const uint32_t ntiles = nrows / TC_TILE_ROWS, nkb = K / 256, sms = (uint32_t)sm_count();
+    uint32_t best = 1;
+    float best_cost = 1e30f;
+    for (uint32_t s = 1; s <= PF_MAX_SPLIT && (s == 1 || nkb / s >= 3); s++) {
+        const uint32_t items = ntiles * s, waves = (items + sms - 1) / sms;
+        // time ~ waves x (units per item + a fixed cost per item of about two units)
+        const float cost = (float)waves * ((float)((nkb + s - 1) / s) + 2.0f);
+        if (cost < best_cost - 1e-3f) { best_cost = cost; best = s; }
+    }
+    return best;
+}
+
+int launch_gemm_q4k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, const uint8_t *image, uint32_t ntok, float *out,
+                          uint32_t out_stride, uint32_t nsplit, cudaStream_t stream)
+{
+    WGB_REQUIRE(nrows % TC_TILE_ROWS == 0 && K % 256 == 0 && ntok >= 1 && ntok <= PF_TOK && nsplit >= 1 && nsplit <= K / 256,
+                "batched product: %u x %u, %u positions, %u slices", nrows, K, ntok, nsplit);
+    DeviceState *ds = device_state();
+    if (!ds) return WGB_ERR_CUDA;
+    if (!ds->prefill_attrs) {
+        WGB_CUDA(cudaFuncSetAttribute(gemm_q4k_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(TB_SMEM + 1024)));
+        ds->prefill_attrs = true;
+    }
+    TbArgs a = {};
+    a.w = w_tiles;
+    a.img = image;
+    a.out = out;
+    a.nrows = nrows;
+    a.nkb = K / 256;
+    a.nsplit = nsplit;
+    a.ntok = ntok;
+    a.out_stride = out_stride;
+    a.err = gemv_status_word();
+    const uint32_t items = nrows / TC_TILE_ROWS * nsplit, sms = (uint32_t)sm_count();
+    gemm_q4k_tc_kernel<<<items < sms ? items : sms, TB_NT, TB_SMEM + 1024, stream>>>(a);
+    WGB_LAUNCH_CHECK("gemm_q4k_tc_kernel");
+    return WGB_OK;
+}
+
+// ---- activation image ---------------------------------------------------------------------------------
+
+// One thread per (position, 32-column group): the value v of element i of the group is handed in by `get`.
+// Writes the three digits of the group's 32 values (two K-cores), its exponent (odd groups carry the 1/16 of the
+// high nibbles) and the sum of its values.
+template <typename Get>
+__device__ __forceinline__ void image_group(uint8_t *__restrict__ image, uint32_t t, uint32_t g, Get get)
+{
+    float v[32];
+    float m = 0.0f, sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        const float4 q = get(i);
+        v[i] = q.x; v[i + 1] = q.y; v[i + 2] = q.z; v[i + 3] = q.w;
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(q.x), fabsf(q.y)), fmaxf(fabsf(q.z), fabsf(q.w))));
+        sum += (q.x + q.y) + (q.z + q.w);
+    }
+    // |v| < 2^(ex - 126), so X = v * 2^(148 - ex) stays within +-2^22 after rounding
+    uint32_t ex = (__float_as_uint(m) >> 23) & 0xffu;
+    ex = ex < 24u ? 24u : (ex > 253u ? 253u : ex);
+    const float up = __uint_as_float((275u - ex) << 23), down = __uint_as_float((ex - 21u) << 23);
+    uint8_t *unit = image + (size_t)(g >> 3) * TB_IMG_BYTES;
+#pragma unroll
+    for (int core = 0; core < 2; core++) {
+        uint32_t dig[3][4];
+#pragma unroll
+        for (int wd = 0; wd < 4; wd++) {
+            uint32_t d0 = 0, d1 = 0, d2 = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                // round to nearest even through the 1.5 * 2^23 offset; with 0x8080 added, bytes 0 and 1 are the
+                // signed digits plus 128 and byte 2 is the signed top digit
+                const uint32_t y = __float_as_uint(fmaf(v[16 * core + 4 * wd + b], up, 12582912.0f)) - 0x4b400000u + 0x8080u;
+                d0 |= ((y & 0xffu) ^ 0x80u) << (8 * b);
+                d1 |= (((y >> 8) & 0xffu) ^ 0x80u) << (8 * b);
+                d2 |= ((y >> 16) & 0xffu) << (8 * b);
+            }
+            dig[0][wd] = d0; dig[1][wd] = d1; dig[2][wd] = d2;
+        }
+        uint8_t *kc = unit + ((g & 7) * 2 + core) * 512 + t * 16;
+#pragma unroll
+        for (int n = 0; n < 3; n++) *reinterpret_cast<uint4 *>(kc + n * 128) = make_uint4(dig[n][0], dig[n][1], dig[n][2], dig[n][3]);
+    }
+    float *es = reinterpret_cast<float *>(unit + TB_IMG_DIGITS);
+    es[(g & 7) * PF_TOK + t] = (g & 1) ? down * 0.0625f : down;
+    es[8 * PF_TOK + (g & 7) * PF_TOK + t] = sum;
+}
+
+// x = residual (+ the slices of a product); optionally written back; optionally RMS-normalised (RmsNorm,
+// ops/rms_norm.wgsl:36-67: (x * 1/sqrt(mean(x^2) + eps)) * w); its image, and optionally the values themselves.
+// One block per position; positions >= ntok get an all-zero image.
+__global__ void __launch_bounds__(256) prefill_norm_image_kernel(float *__restrict__ x, uint32_t x_stride, const float *__restrict__ part,
+                                                                 uint32_t nsplit, uint32_t part_stride, const float *__restrict__ norm_w,
+                                                                 float eps, uint32_t K, uint32_t ntok, uint8_t *__restrict__ image,
+                                                                 float *__restrict__ xn, uint32_t xn_stride)
+{
+    const uint32_t t = blockIdx.x;
+    __shared__ float red[8];
+    __shared__ float scale_s;
+    if (t >= ntok) {
+        for (uint32_t g = threadIdx.x; g < K / 32; g += 256) image_group(image, t, g, [](int) { return make_float4(0.f, 0.f, 0.f, 0.f); });
+        return;
+    }
+    float *xr = x + (size_t)t * x_stride;
+    float ss = 0.0f;
+    if (part || norm_w) {
+        for (uint32_t i = threadIdx.x * 4; i < K; i += 1024) {
+            float4 v = *reinterpret_cast<const float4 *>(xr + i);
+            for (uint32_t s = 0; s < (part ? nsplit : 0u); s++) {
+                const float4 p = *reinterpret_cast<const float4 *>(part + ((size_t)s * PF_TOK + t) * part_stride + i);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
+            if (part) *reinterpret_cast<float4 *>(xr + i) = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float tot = 0.0f;
+            for (int i = 0; i < 8; i++) tot += red[i];
+            scale_s = 1.0f / sqrtf(tot / (float)K + eps);
+        }
+        __syncthreads();
+    }
+    if (!image && !xn) return;
+    const float scale = norm_w ? scale_s : 1.0f;
+    for (uint32_t g = threadIdx.x; g < K / 32; g += 256) {
+        auto get = [&](int i) {
+            float4 v = *reinterpret_cast<const float4 *>(xr + 32 * g + i);
+            if (norm_w) {
+                const float4 w = *reinterpret_cast<const float4 *>(norm_w + 32 * g + i);
+                v.x = (v.x * scale) * w.x; v.y = (v.y * scale) * w.y; v.z = (v.z * scale) * w.z; v.w = (v.w * scale) * w.w;
+            }
+            if (xn) *reinterpret_cast<float4 *>(xn + (size_t)t * xn_stride + 32 * g + i) = v;
+            return v;
+        };
+        image_group(image, t, g, get);
+    }
+}
+
+// h = up * gate / (1 + exp(-gate)) (Silu, ops/silu.wgsl:19-27) from the slices of the two products; its image and,
+// optionally, the values.
+__global__ void __launch_bounds__(256) prefill_silu_image_kernel(const float *__restrict__ gate, uint32_t gsplit, const float *__restrict__ upv,
+                                                                 uint32_t usplit, uint32_t stride, uint32_t K, uint32_t ntok,
+                                                                 uint8_t *__restrict__ image, float *__restrict__ h, uint32_t h_stride)
+{
+    const uint32_t t = blockIdx.y, g = blockIdx.x * 256 + threadIdx.x;
+    if (g >= K / 32) return;
+    if (t >= ntok) {
+        image_group(image, t, g, [](int) { return make_float4(0.f, 0.f, 0.f, 0.f); });
+        return;
+    }
+    auto get = [&](int i) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+        for (uint32_t s = 0; s < gsplit; s++) {
+            const float4 p = *reinterpret_cast<const float4 *>(gate + ((size_t)s * PF_TOK + t) * stride + 32 * g + i);
+            a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
+        }
+        for (uint32_t s = 0; s < usplit; s++) {
+            const float4 p = *reinterpret_cast<const float4 *>(upv + ((size_t)s * PF_TOK + t) * stride + 32 * g + i);
+            b.x += p.x; b.y += p.y; b.z += p.z; b.w += p.w;
+        }
+        float4 v;
+        v.x = b.x * (a.x / (1.0f + expf(-a.x)));
+        v.y = b.y * (a.y / (1.0f + expf(-a.y)));
+        v.z = b.z * (a.z / (1.0f + expf(-a.z)));
+        v.w = b.w * (a.w / (1.0f + expf(-a.w)));
+        if (h) *reinterpret_cast<float4 *>(h + (size_t)t * h_stride + 32 * g + i) = v;
+        return v;
+    };
+    image_group(image, t, g, get);
+}
+
+int launch_prefill_norm_image(float *x, uint32_t x_stride, const float *part, uint32_t nsplit, uint32_t part_stride, const float *norm_w,
+                              float eps, uint32_t K, uint32_t ntok, uint8_t *image, float *xn, uint32_t xn_stride, cudaStream_t stream)
+{
+    WGB_REQUIRE(K % 32 == 0 && ntok <= PF_TOK, "activation image of %u columns, %u positions", K, ntok);
+    prefill_norm_image_kernel<<<image ? PF_TOK : ntok, 256, 0, stream>>>(x, x_stride, part, nsplit, part_stride, norm_w, eps, K, ntok, image, xn,
+                                                                          xn_stride);
+    WGB_LAUNCH_CHECK("prefill_norm_image_kernel");
+    return WGB_OK;
+}
+
+int launch_prefill_silu_image(const float *gate, uint32_t gsplit, const float *up, uint32_t usplit, uint32_t stride, uint32_t K,
+                              uint32_t ntok, uint8_t *image, float *h, uint32_t h_stride, cudaStream_t stream)
+{
+    WGB_REQUIRE(K % 32 == 0 && ntok <= PF_TOK, "activation image of %u columns, %u positions", K, ntok);
+    prefill_silu_image_kernel<<<dim3((K / 32 + 255) / 256, PF_TOK), 256, 0, stream>>>(gate, gsplit, up, usplit, stride, K, ntok, image, h,
+                                                                                        h_stride);
+    WGB_LAUNCH_CHECK("prefill_silu_image_kernel");
+    return WGB_OK;
+}
+
+// ---- RoPE + KV append for a batch of positions ------------------------------------------------------
+
+// The work of the OpAssign / RoPE dispatches of models/llama2/transformer.rs:343-365 and the write into the cache
+// rows, for positions pos0 .. pos0 + ntok - 1: q, k, v are sums of product slices (+ bias); q is rotated into
+// `q_out`, k rotated into the key cache, v copied into the value cache (head-major caches: element e of head h
+// at position p sits at (h * seq_len + p) * head_size + e).
+__global__ void __launch_bounds__(128) prefill_rope_append_kernel(PrefillQkv a)
+{
+    const uint32_t i = blockIdx.x * 128 + threadIdx.x, t = blockIdx.y;   // pair index over q
+    if (2 * i >= a.q_dim) return;
+    const uint32_t pos = a.pos0 + t, half = a.head_size / 2;
+    float sn, cs;
+    sincosf((float)pos * a.freq[i % half], &sn, &cs);
+    uint32_t ia, ib;
+    if (a.variant == WGB_ROPE_ORIGINAL) { ia = 2 * i; ib = ia + 1; }
+    else { ia = i + ((2 * i) / a.head_size) * half; ib = ia + half; }
+    auto gather = [&](const float *p, uint32_t nsplit, uint32_t stride, const float *bias, uint32_t idx) {
+        float v = 0.0f;
+        for (uint32_t s = 0; s < nsplit; s++) v += p[((size_t)s * PF_TOK + t) * stride + idx];
+        return v + (bias ? bias[idx] : 0.0f);
+    };
+    float x = gather(a.q, a.q_split, a.q_stride, a.bq, ia), y = gather(a.q, a.q_split, a.q_stride, a.bq, ib);
+    a.q_out[(size_t)t * a.q_dim + ia] = cs * x - sn * y;
+    a.q_out[(size_t)t * a.q_dim + ib] = sn * x + cs * y;
+    if (2 * i < a.kv_dim) {
+        float *kc = a.k_cache + (size_t)pos * a.head_size, *vc = a.v_cache + (size_t)pos * a.head_size;
+        const size_t da = (size_t)(ia / a.head_size) * a.seq_len * a.head_size + ia % a.head_size;
+        const size_t db = (size_t)(ib / a.head_size) * a.seq_len * a.head_size + ib % a.head_size;
+        x = gather(a.k, a.k_split, a.kv_stride, a.bk, ia);
+        y = gather(a.k, a.k_split, a.kv_stride, a.bk, ib);
+        kc[da] = cs * x - sn * y;
+        kc[db] = sn * x + cs * y;
+        vc[da] = gather(a.v, a.v_split, a.kv_stride, a.bv, ia);
+        vc[db] = gather(a.v, a.v_split, a.kv_stride, a.bv, ib);
+    }
+}
+
+int launch_prefill_rope_append(const PrefillQkv &a, uint32_t ntok, cudaStream_t stream)
+{
+    prefill_rope_append_kernel<<<dim3((a.q_dim / 2 + 127) / 128, ntok), 128, 0, stream>>>(a);
+    WGB_LAUNCH_CHECK("prefill_rope_append_kernel");
+    return WGB_OK;
+}
+
+// ---- causal attention of a batch of positions ----------------------------------------------------------
+
+// BatchedMultiqueryAttention (ops/batched_multiquery_attention.wgsl:42-122) for positions pos0 + t, t < ntok, each
+// attending to cache rows 0 .. pos0 + t.  One block per (query head, pair of positions); the block walks the
+// cache rows in chunks of 256 with a running maximum and sum (rescaled), one thread per row for the scores, one
+// thread per value column (times a quarter of the chunk's rows) for the weighted sum.
+constexpr uint32_t PA_TQ = 2;        // positions per block
+constexpr uint32_t PA_CHUNK = 256;
+__global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__restrict__ q, const float *__restrict__ k_cache,
+                                                                const float *__restrict__ v_cache, float *__restrict__ out, uint32_t q_dim,
+                                                                uint32_t head_size, uint32_t kv_mul, uint32_t seq_len, uint32_t pos0,
+                                                                uint32_t ntok)
+{
+    extern __shared__ float pa_smem[];
+    const uint32_t h = blockIdx.x, t0 = blockIdx.y * PA_TQ;
+    if (t0 >= ntok) return;
+    const uint32_t nq = ntok - t0 < PA_TQ ? ntok - t0 : PA_TQ;
+    float *qs = pa_smem;                          // [PA_TQ][head_size]
+    float *sc = qs + PA_TQ * head_size;           // [PA_TQ][PA_CHUNK]
+    float *accs = sc + PA_TQ * PA_CHUNK;          // [4][PA_TQ][head_size]
+    __shared__ float red[PA_TQ][8];
+    __shared__ float m_run[PA_TQ], l_run[PA_TQ], m_new[PA_TQ], resc[PA_TQ];
+    const float *kh = k_cache + (size_t)(h / kv_mul) * seq_len * head_size;
+    const float *vh = v_cache + (size_t)(h / kv_mul) * seq_len * head_size;
+    const float inv_sqrt = 1.0f / sqrtf((float)head_size);
+    for (uint32_t i = threadIdx.x; i < PA_TQ * head_size; i += 256) {
+        const uint32_t tq = i / head_size, e = i % head_size;
+        qs[i] = tq < nq ? q[(size_t)(t0 + tq) * q_dim + h * head_size + e] : 0.0f;
+    }
+    if (threadIdx.x < PA_TQ) { m_run[threadIdx.x] = -INFINITY; l_run[threadIdx.x] = 0.0f; }
+    // value columns: thread = (quarter of the chunk's rows, column group); head sizes up to 256 (four columns each)
+    const uint32_t cg = threadIdx.x & 63, rq = threadIdx.x >> 6;
+    float4 acc[PA_TQ];
+#pragma unroll
+    for (uint32_t tq = 0; tq < PA_TQ; tq++) acc[tq] = make_float4(0.f, 0.f, 0.f, 0.f);
+    __syncthreads();
+    const uint32_t last = pos0 + t0 + nq - 1;     // furthest row any of the block's positions attends to
+    for (uint32_t c0 = 0; c0 <= last; c0 += PA_CHUNK) {
+        // scores of row c0 + thread for the block's positions
+        const uint32_t row = c0 + threadIdx.x;
+        float s[PA_TQ];
+#pragma unroll
+        for (uint32_t tq = 0; tq < PA_TQ; tq++) s[tq] = 0.0f;
+        if (row <= last) {
+            const float4 *kr = reinterpret_cast<const float4 *>(kh + (size_t)row * head_size);
+            for (uint32_t e = 0; e < head_size / 4; e++) {
+                const float4 kv = kr[e];
+#pragma unroll
+                for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+                    const float4 qv = *reinterpret_cast<const float4 *>(qs + tq * head_size + 4 * e);
+                    s[tq] += kv.x * qv.x + kv.y * qv.y + kv.z * qv.z + kv.w * qv.w;
+                }
+            }
+        }
+#pragma unroll
+        for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+            const bool live = tq < nq && row <= pos0 + t0 + tq;
+            s[tq] = live ? s[tq] * inv_sqrt : -INFINITY;
+            const float mx = warp_max(s[tq]);
+            if ((threadIdx.x & 31) == 0) red[tq][threadIdx.x >> 5] = mx;
+        }
+        __syncthreads();
+        if (threadIdx.x < PA_TQ) {
+            float mx = m_run[threadIdx.x];
+            for (int i = 0; i < 8; i++) mx = fmaxf(mx, red[threadIdx.x][i]);
+            m_new[threadIdx.x] = mx;
+            resc[threadIdx.x] = mx == -INFINITY ? 1.0f : expf(m_run[threadIdx.x] - mx);
+            m_run[threadIdx.x] = mx;
+        }
+        __syncthreads();
+#pragma unroll
+        for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+            const float p = s[tq] == -INFINITY ? 0.0f : expf(s[tq] - m_new[tq]);
+            sc[tq * PA_CHUNK + threadIdx.x] = p;
+            const float ps = warp_sum(p);
+            if ((threadIdx.x & 31) == 0) red[tq][threadIdx.x >> 5] = ps;   // the maxima in red[] were consumed before the last barrier
+        }
+        __syncthreads();
+        if (threadIdx.x < PA_TQ) {
+            float tot = 0.0f;
+            for (int i = 0; i < 8; i++) tot += red[threadIdx.x][i];
+            l_run[threadIdx.x] = l_run[threadIdx.x] * resc[threadIdx.x] + tot;
+        }
+        // weighted values: rows c0 + 64 rq .. + 63 of the chunk, columns 4 cg .. + 3
+#pragma unroll
+        for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+            const float rs = resc[tq];
+            acc[tq].x *= rs; acc[tq].y *= rs; acc[tq].z *= rs; acc[tq].w *= rs;
+        }
+        if (4 * cg < head_size) {
+            const uint32_t r_end = min(c0 + 64 * (rq + 1), last + 1);
+            for (uint32_t rr = c0 + 64 * rq; rr < r_end; rr++) {
+                const float4 vv = *reinterpret_cast<const float4 *>(vh + (size_t)rr * head_size + 4 * cg);
+#pragma unroll
+                for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+                    const float p = sc[tq * PA_CHUNK + (rr - c0)];
+                    acc[tq].x = fmaf(p, vv.x, acc[tq].x); acc[tq].y = fmaf(p, vv.y, acc[tq].y);
+                    acc[tq].z = fmaf(p, vv.z, acc[tq].z); acc[tq].w = fmaf(p, vv.w, acc[tq].w);
+                }
+            }
+        }
+        __syncthreads();   // sc[], red[] and resc[] are rewritten by the next chunk
+    }
+    if (4 * cg < head_size) {
+#pragma unroll
+        for (uint32_t tq = 0; tq < PA_TQ; tq++) *reinterpret_cast<float4 *>(accs + ((size_t)rq * PA_TQ + tq) * head_size + 4 * cg) = acc[tq];
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < nq * head_size; i += 256) {
+        const uint32_t tq = i / head_size, e = i % head_size;
+        float v = 0.0f;
+        for (uint32_t r4 = 0; r4 < 4; r4++) v += accs[((size_t)r4 * PA_TQ + tq) * head_size + e];
+        out[(size_t)(t0 + tq) * q_dim + h * head_size + e] = v / l_run[tq];
+    }
+}
+
+int launch_prefill_attention(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
+                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, cudaStream_t stream)
+{
+    WGB_REQUIRE(head_size % 4 == 0 && head_size <= 256 && ntok >= 1 && ntok <= PF_TOK, "prompt attention: head size %u, %u positions", head_size,
+                ntok);
+    const size_t smem = (size_t)(PA_TQ * head_size + PA_TQ * PA_CHUNK + 4 * PA_TQ * head_size) * sizeof(float);
+    prefill_attention_kernel<<<dim3(n_heads, (ntok + PA_TQ - 1) / PA_TQ), 256, smem, stream>>>(q, k_cache, v_cache, out, n_heads * head_size,
+                                                                                                head_size, kv_mul, seq_len, pos0, ntok);
+    WGB_LAUNCH_CHECK("prefill_attention_kernel");
+    return WGB_OK;
+}
+
+// Raw row-major Q4_K blocks -> [tile][column][row in tile][144 bytes].  One thread per 16 bytes.
+__global__ void prefill_tile_major_kernel(const uint4 *__restrict__ raw, uint4 *__restrict__ tiled, uint32_t nrows, uint32_t nkb)
+{
+    const size_t total = (size_t)nrows * nkb * 9;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t part = (uint32_t)(i % 9);
+        const size_t blk = i / 9;
+        const uint32_t kb = (uint32_t)(blk % nkb), row = (uint32_t)(blk / nkb);
+        const uint32_t tile = row / TC_TILE_ROWS, r = row % TC_TILE_ROWS;
+        tiled[(((size_t)tile * nkb + kb) * TC_TILE_ROWS + r) * 9 + part] = raw[i];
+    }
+}
+
+int prefill_tile_major(const QMat &m, uint8_t **out, cudaStream_t stream)
+{
+    WGB_REQUIRE(m.qtype == WGB_Q4_K && !m.planar && m.nrows % TC_TILE_ROWS == 0 && m.ncols % 256 == 0, "not a tileable Q4_K matrix");
+    const size_t bytes = (size_t)m.nrows * m.bpr * 144;
+    WGB_CUDA(cudaMalloc((void **)out, bytes));
+    const size_t blocks = (bytes / 16 + 255) / 256;
+    prefill_tile_major_kernel<<<(unsigned)(blocks < 65535u * 16u ? blocks : 65535u * 16u), 256, 0, stream>>>((const uint4 *)m.p[0], (uint4 *)*out,
+                                                                                                             m.nrows, m.bpr);
+    WGB_LAUNCH_CHECK("prefill_tile_major_kernel");
+    return WGB_OK;
+}
+
+bool prefill_tileable(const QMat &m) { return m.qtype == WGB_Q4_K && !m.planar && m.nrows % TC_TILE_ROWS == 0 && m.ncols % 256 == 0; }
+
+}  // namespace wgb

@@ -180,6 +180,16 @@ class Llama2:
                                             torch.cuda.current_stream().cuda_stream))
         return out[:prompt.size - 1 + n_gen]
 
+    def set_prefill(self, enable: bool = True) -> None:
+        """Batched prompt prefill: `decode` sends the prompt through passes of eight positions with the Q4_K
+        products on the tensor cores (the reference feeds it position by position, chat_llama2.rs:104-116)."""
+        check(_lib.load().wgb_llama2_set_prefill(self._h, 1 if enable else 0))
+
+    def prefill_positions(self) -> int:
+        n = C.c_size_t()
+        check(_lib.load().wgb_llama2_prefill_positions(self._h, C.byref(n)))
+        return n.value
+
     def set_sampler(self, temperature: float, topp: float, seed: int = 0) -> None:
         """Sampler::new(vocab, temperature, topp) for the generated tokens of `decode`; temperature 0 = greedy.
         The coin of the token at position p is ops.sampler_coin(seed, p)."""

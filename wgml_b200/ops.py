@@ -116,8 +116,8 @@ class GemvQuant:
 
 
 class Q4KTiles:
-    """A Q4_K matrix in the tile-major layout of the tensor-core matrix-vector kernel (nrows a multiple of
-    128, ncols a multiple of 256 up to 4096), built from raw GGUF blocks in host memory."""
+    """A Q4_K matrix in the tile-major layout of the tensor-core kernels (nrows a multiple of 128, ncols a
+    multiple of 256; the single-vector kernel takes up to 4096 columns), built from raw GGUF blocks in host memory."""
 
     def __init__(self, blocks, nrows: int, ncols: int):
         require_device()
@@ -132,6 +132,12 @@ class Q4KTiles:
         if v.numel() != self.ncols or out.numel() != self.nrows:
             raise WgbError(_lib.ERR_INVALID, "Gemv: dimension mismatch.")
         check(_lib.load().wgb_gemv_q4k_tiles(self._h, _f32(v, "v"), _f32(out, "out"), _stream()))
+
+    def gemm(self, out: torch.Tensor, v: torch.Tensor) -> None:
+        """The product for 1..8 input vectors at once: v [n][ncols] -> out [n][nrows] (the batched prefill's kernel)."""
+        if v.dim() != 2 or out.dim() != 2 or v.shape[1] != self.ncols or out.shape[1] != self.nrows or v.shape[0] != out.shape[0]:
+            raise WgbError(_lib.ERR_INVALID, "Gemm: dimension mismatch.")
+        check(_lib.load().wgb_gemm_q4k_tiles(self._h, _f32(v, "v"), v.shape[0], _f32(out, "out"), _stream()))
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
