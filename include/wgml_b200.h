@@ -110,8 +110,10 @@ int wgb_gemv_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, float *d_out, v
 /* The same product for 1..8 input vectors at once, d_v [n_vec][ncols] -> d_out [n_vec][nrows]: the tensor-core
  * kernel of the batched prompt prefill (wgb_llama2_set_prefill), any number of columns that is a multiple of
  * 256.  In the reference a prompt costs one GemvQuant::dispatch per matrix and position
- * (chat_llama2.rs:104-116); here eight positions share one pass over the weights.  Synchronises. */
-int wgb_gemm_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream);
+ * (chat_llama2.rs:104-116); here eight positions share one pass over the weights.  Asynchronous like the other
+ * operators; the first call on a matrix allocates its work areas (make it outside stream capture), and calls on
+ * one matrix must be ordered on a stream. */
+int wgb_gemm_q4k_tiles(wgb_q4k_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream);
 /* Waits for the device and returns WGB_ERR_TIMEOUT if a bounded wait inside a matrix-vector kernel has
  * expired since the last report (stand-alone launches are asynchronous and cannot say so themselves). */
 int wgb_device_status(void);

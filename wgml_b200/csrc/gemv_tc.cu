@@ -301,6 +301,9 @@ using namespace wgb;
 struct wgb_q4k_tiles {
     uint8_t *w;
     uint32_t nrows, ncols;
+    // work areas of the batched product, made by its first call: activation image and product slices
+    uint8_t *image;
+    float *part;
 };
 
 WGB_EXPORT int wgb_q4k_tiles_create(const void *h_blocks, size_t nrows, size_t ncols, void *stream, wgb_q4k_tiles **out)
@@ -346,6 +349,8 @@ WGB_EXPORT int wgb_q4k_tiles_destroy(wgb_q4k_tiles *m)
 {
     if (!m) return WGB_OK;
     cudaFree(m->w);
+    if (m->image) cudaFree(m->image);
+    if (m->part) cudaFree(m->part);
     delete m;
     return WGB_OK;
 }
@@ -370,29 +375,34 @@ WGB_EXPORT int wgb_gemv_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, floa
 }
 
 // The same product for up to eight input vectors at once (the kernel of the batched prompt prefill, prefill.cu):
-// d_v [n_vec][ncols] -> d_out [n_vec][nrows].  Allocates its work areas per call (a test and measurement entry
-// point; the model keeps its own).
-WGB_EXPORT int wgb_gemm_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream)
+// d_v [n_vec][ncols] -> d_out [n_vec][nrows].  The first call on a matrix allocates its work areas (activation
+// image, product slices), so make it outside stream capture; calls on one matrix must be ordered on a stream.
+WGB_EXPORT int wgb_gemm_q4k_tiles(wgb_q4k_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream)
 {
     WGB_REQUIRE(m && d_v && d_out, "null argument");
     WGB_REQUIRE(n_vec >= 1 && n_vec <= PF_TOK, "between 1 and %u input vectors, got %zu", PF_TOK, n_vec);
     cudaStream_t st = as_stream(stream);
     const uint32_t ns = prefill_gemm_splits(m->nrows, m->ncols);
-    uint8_t *image = nullptr;
-    float *part = nullptr;
-    cudaError_t e = cudaMalloc((void **)&image, prefill_image_bytes(m->ncols));
-    if (e == cudaSuccess) e = cudaMalloc((void **)&part, (size_t)ns * PF_TOK * m->nrows * sizeof(float));
-    if (e == cudaSuccess) e = cudaMemsetAsync(image, 0, prefill_image_bytes(m->ncols), st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(d_out, 0, n_vec * m->nrows * sizeof(float), st);
-    int rc = e == cudaSuccess ? WGB_OK : cuda_fail(e, "work areas of the batched product");
+    if (!m->image) {
+        uint8_t *image = nullptr;
+        float *part = nullptr;
+        cudaError_t e = cudaMalloc((void **)&image, prefill_image_bytes(m->ncols));
+        if (e == cudaSuccess) e = cudaMalloc((void **)&part, (size_t)PF_MAX_SPLIT * PF_TOK * m->nrows * sizeof(float));
+        if (e == cudaSuccess) e = cudaMemset(image, 0, prefill_image_bytes(m->ncols));
+        if (e != cudaSuccess) {
+            if (image) cudaFree(image);
+            if (part) cudaFree(part);
+            return cuda_fail(e, "work areas of the batched product");
+        }
+        m->image = image;
+        m->part = part;
+    }
+    WGB_CUDA(cudaMemsetAsync(d_out, 0, n_vec * m->nrows * sizeof(float), st));
     // image of the inputs (they are not written: no slices are folded into them)
-    if (!rc) rc = launch_prefill_norm_image(const_cast<float *>(d_v), m->ncols, nullptr, 0, 0, nullptr, 0.0f, m->ncols, (uint32_t)n_vec, image, nullptr, 0, st);
-    if (!rc) rc = launch_gemm_q4k_tiles(m->w, m->nrows, m->ncols, image, (uint32_t)n_vec, part, m->nrows, ns, st);
+    int rc = launch_prefill_norm_image(const_cast<float *>(d_v), m->ncols, nullptr, 0, 0, nullptr, 0.0f, m->ncols, (uint32_t)n_vec, m->image, nullptr, 0, st);
+    if (!rc) rc = launch_gemm_q4k_tiles(m->w, m->nrows, m->ncols, m->image, (uint32_t)n_vec, m->part, m->nrows, ns, st);
     // d_out (zero) += the slices
-    if (!rc) rc = launch_prefill_norm_image(d_out, m->nrows, part, ns, m->nrows, nullptr, 0.0f, m->nrows, (uint32_t)n_vec, nullptr, nullptr, 0, st);
-    if (!rc && (e = cudaStreamSynchronize(st)) != cudaSuccess) rc = cuda_fail(e, "batched product");
-    if (image) cudaFree(image);
-    if (part) cudaFree(part);
+    if (!rc) rc = launch_prefill_norm_image(d_out, m->nrows, m->part, ns, m->nrows, nullptr, 0.0f, m->nrows, (uint32_t)n_vec, nullptr, nullptr, 0, st);
     return rc;
 }
 

@@ -204,13 +204,11 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                 if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), (m >> 1) & 1, dead, a.err, 24));
                 if (ok) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    float acc[PF_TOK], neg[PF_TOK];
 #pragma unroll
                     for (uint32_t q = 0; q < 2; q++) {
                         int d[3][8];
 #pragma unroll
                         for (uint32_t dg = 0; dg < 3; dg++) tc_ld8(taddr + u * 256 + 32 * (2 * sub + q) + 8 * dg, d[dg]);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         // exponents and sums of group 2 sub + q, one float per position
                         const uint32_t eo = img + TB_IMG_DIGITS + (2 * sub + q) * PF_TOK * 4;
                         const uint4 e0 = lds128(eo), e1 = lds128(eo + 16), s0 = lds128(eo + 8 * PF_TOK * 4), s1 = lds128(eo + 8 * PF_TOK * 4 + 16);
@@ -218,23 +216,18 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                                               __uint_as_float(e1.x), __uint_as_float(e1.y), __uint_as_float(e1.z), __uint_as_float(e1.w) };
                         const float sv[8] = { __uint_as_float(s0.x), __uint_as_float(s0.y), __uint_as_float(s0.z), __uint_as_float(s0.w),
                                               __uint_as_float(s1.x), __uint_as_float(s1.y), __uint_as_float(s1.z), __uint_as_float(s1.w) };
-                        const float sc = byte2f(scw, q), mn = byte2f(mw, q);
+                        // the block's d and dmin folded into the sub-block's scale and min once per unit
+                        const float sc = dm.x * byte2f(scw, q), mn = -dm.y * byte2f(mw, q);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (uint32_t t = 0; t < PF_TOK; t++) {
-                            // |digit sum| <= 32 * 240 * 128 < 2^22: the offset conversion is exact
-                            const float f = fmaf(i2f(d[2][t]), 65536.0f, fmaf(i2f(d[1][t]), 256.0f, i2f(d[0][t])));
-                            if (q == 0) {
-                                acc[t] = f * (sc * ev[t]);
-                                neg[t] = mn * sv[t];
-                            } else {
-                                acc[t] = fmaf(f, sc * ev[t], acc[t]);
-                                neg[t] = fmaf(mn, sv[t], neg[t]);
-                            }
+                            // the two low digit sums are joined in the integer unit (|.| < 2^31) and take one
+                            // conversion; the product with the exponent is exact (a power of two)
+                            const float f = fmaf(__int2float_rn(d[2][t]), 65536.0f, __int2float_rn(d[1][t] * 256 + d[0][t]));
+                            rowacc[t] = fmaf(f, sc * ev[t], fmaf(mn, sv[t], rowacc[t]));
                         }
                     }
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-#pragma unroll
-                    for (uint32_t t = 0; t < PF_TOK; t++) rowacc[t] += dm.x * acc[t] - dm.y * neg[t];
                 }
                 mbar_arrive(bar_empty(slot));
                 if (fin.last()) {
@@ -314,55 +307,50 @@ int launch_gemm_q4k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, co
 
 // ---- activation image ---------------------------------------------------------------------------------
 
-// One thread per (position, 32-column group): the value v of element i of the group is handed in by `get`.
-// Writes the three digits of the group's 32 values (two K-cores), its exponent (odd groups carry the 1/16 of the
-// high nibbles) and the sum of its values.
-template <typename Get>
-__device__ __forceinline__ void image_group(uint8_t *__restrict__ image, uint32_t t, uint32_t g, Get get)
+// Eight threads per (position, 32-column group), four consecutive values each (`v`): writes the three digits of
+// the values, and (first thread of the eight) the group's exponent -- odd groups carry the 1/16 of the high
+// nibbles -- and the sum of its values.  The eight threads are consecutive lanes of a warp and all take part.
+__device__ __forceinline__ void image_quad(uint8_t *__restrict__ image, uint32_t t, uint32_t g, uint32_t j, float4 v)
 {
-    float v[32];
-    float m = 0.0f, sum = 0.0f;
+    float m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    float sum = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-        const float4 q = get(i);
-        v[i] = q.x; v[i + 1] = q.y; v[i + 2] = q.z; v[i + 3] = q.w;
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(q.x), fabsf(q.y)), fmaxf(fabsf(q.z), fabsf(q.w))));
-        sum += (q.x + q.y) + (q.z + q.w);
+    for (int o = 1; o < 8; o <<= 1) {
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
     }
     // |v| < 2^(ex - 126), so X = v * 2^(148 - ex) stays within +-2^22 after rounding
     uint32_t ex = (__float_as_uint(m) >> 23) & 0xffu;
     ex = ex < 24u ? 24u : (ex > 253u ? 253u : ex);
     const float up = __uint_as_float((275u - ex) << 23), down = __uint_as_float((ex - 21u) << 23);
-    uint8_t *unit = image + (size_t)(g >> 3) * TB_IMG_BYTES;
+    const float vv[4] = { v.x, v.y, v.z, v.w };
+    uint32_t d0 = 0, d1 = 0, d2 = 0;
 #pragma unroll
-    for (int core = 0; core < 2; core++) {
-        uint32_t dig[3][4];
-#pragma unroll
-        for (int wd = 0; wd < 4; wd++) {
-            uint32_t d0 = 0, d1 = 0, d2 = 0;
-#pragma unroll
-            for (int b = 0; b < 4; b++) {
-                // round to nearest even through the 1.5 * 2^23 offset; with 0x8080 added, bytes 0 and 1 are the
-                // signed digits plus 128 and byte 2 is the signed top digit
-                const uint32_t y = __float_as_uint(fmaf(v[16 * core + 4 * wd + b], up, 12582912.0f)) - 0x4b400000u + 0x8080u;
-                d0 |= ((y & 0xffu) ^ 0x80u) << (8 * b);
-                d1 |= (((y >> 8) & 0xffu) ^ 0x80u) << (8 * b);
-                d2 |= ((y >> 16) & 0xffu) << (8 * b);
-            }
-            dig[0][wd] = d0; dig[1][wd] = d1; dig[2][wd] = d2;
-        }
-        uint8_t *kc = unit + ((g & 7) * 2 + core) * 512 + t * 16;
-#pragma unroll
-        for (int n = 0; n < 3; n++) *reinterpret_cast<uint4 *>(kc + n * 128) = make_uint4(dig[n][0], dig[n][1], dig[n][2], dig[n][3]);
+    for (int b = 0; b < 4; b++) {
+        // round to nearest even through the 1.5 * 2^23 offset; with 0x8080 added, bytes 0 and 1 are the signed
+        // digits plus 128 and byte 2 is the signed top digit
+        const uint32_t y = __float_as_uint(fmaf(vv[b], up, 12582912.0f)) - 0x4b400000u + 0x8080u;
+        d0 |= ((y & 0xffu) ^ 0x80u) << (8 * b);
+        d1 |= (((y >> 8) & 0xffu) ^ 0x80u) << (8 * b);
+        d2 |= ((y >> 16) & 0xffu) << (8 * b);
     }
-    float *es = reinterpret_cast<float *>(unit + TB_IMG_DIGITS);
-    es[(g & 7) * PF_TOK + t] = (g & 1) ? down * 0.0625f : down;
-    es[8 * PF_TOK + (g & 7) * PF_TOK + t] = sum;
+    // values 4 j .. 4 j + 3 of the group: K-core 2 (g % 8) + j / 4 of the unit, bytes 4 (j % 4) .. of row t
+    uint8_t *unit = image + (size_t)(g >> 3) * TB_IMG_BYTES;
+    uint8_t *kc = unit + ((g & 7) * 2 + (j >> 2)) * 512 + t * 16 + (j & 3) * 4;
+    *reinterpret_cast<uint32_t *>(kc) = d0;
+    *reinterpret_cast<uint32_t *>(kc + 128) = d1;
+    *reinterpret_cast<uint32_t *>(kc + 256) = d2;
+    if (j == 0) {
+        float *es = reinterpret_cast<float *>(unit + TB_IMG_DIGITS);
+        es[(g & 7) * PF_TOK + t] = (g & 1) ? down * 0.0625f : down;
+        es[8 * PF_TOK + (g & 7) * PF_TOK + t] = sum;
+    }
 }
 
 // x = residual (+ the slices of a product); optionally written back; optionally RMS-normalised (RmsNorm,
 // ops/rms_norm.wgsl:36-67: (x * 1/sqrt(mean(x^2) + eps)) * w); its image, and optionally the values themselves.
-// One block per position; positions >= ntok get an all-zero image.
+// One block per position; positions >= ntok get an all-zero image.  K is a multiple of 32, so the eight threads of
+// a group are always whole.
 __global__ void __launch_bounds__(256) prefill_norm_image_kernel(float *__restrict__ x, uint32_t x_stride, const float *__restrict__ part,
                                                                  uint32_t nsplit, uint32_t part_stride, const float *__restrict__ norm_w,
                                                                  float eps, uint32_t K, uint32_t ntok, uint8_t *__restrict__ image,
@@ -372,12 +360,12 @@ __global__ void __launch_bounds__(256) prefill_norm_image_kernel(float *__restri
     __shared__ float red[8];
     __shared__ float scale_s;
     if (t >= ntok) {
-        for (uint32_t g = threadIdx.x; g < K / 32; g += 256) image_group(image, t, g, [](int) { return make_float4(0.f, 0.f, 0.f, 0.f); });
+        for (uint32_t i = threadIdx.x; i < K / 4; i += 256) image_quad(image, t, i >> 3, i & 7, make_float4(0.f, 0.f, 0.f, 0.f));
         return;
     }
     float *xr = x + (size_t)t * x_stride;
-    float ss = 0.0f;
     if (part || norm_w) {
+        float ss = 0.0f;
         for (uint32_t i = threadIdx.x * 4; i < K; i += 1024) {
             float4 v = *reinterpret_cast<const float4 *>(xr + i);
             for (uint32_t s = 0; s < (part ? nsplit : 0u); s++) {
@@ -397,59 +385,52 @@ __global__ void __launch_bounds__(256) prefill_norm_image_kernel(float *__restri
         }
         __syncthreads();
     }
-    if (!image && !xn) return;
+    if (!image) return;
     const float scale = norm_w ? scale_s : 1.0f;
-    for (uint32_t g = threadIdx.x; g < K / 32; g += 256) {
-        auto get = [&](int i) {
-            float4 v = *reinterpret_cast<const float4 *>(xr + 32 * g + i);
-            if (norm_w) {
-                const float4 w = *reinterpret_cast<const float4 *>(norm_w + 32 * g + i);
-                v.x = (v.x * scale) * w.x; v.y = (v.y * scale) * w.y; v.z = (v.z * scale) * w.z; v.w = (v.w * scale) * w.w;
-            }
-            if (xn) *reinterpret_cast<float4 *>(xn + (size_t)t * xn_stride + 32 * g + i) = v;
-            return v;
-        };
-        image_group(image, t, g, get);
+    // the same thread reads back what it wrote above (element 4 (threadIdx.x + 256 k))
+    for (uint32_t i = threadIdx.x; i < K / 4; i += 256) {
+        float4 v = *reinterpret_cast<const float4 *>(xr + 4 * i);
+        if (norm_w) {
+            const float4 w = *reinterpret_cast<const float4 *>(norm_w + 4 * i);
+            v.x = (v.x * scale) * w.x; v.y = (v.y * scale) * w.y; v.z = (v.z * scale) * w.z; v.w = (v.w * scale) * w.w;
+        }
+        if (xn) *reinterpret_cast<float4 *>(xn + (size_t)t * xn_stride + 4 * i) = v;
+        image_quad(image, t, i >> 3, i & 7, v);
     }
 }
 
 // h = up * gate / (1 + exp(-gate)) (Silu, ops/silu.wgsl:19-27) from the slices of the two products; its image and,
-// optionally, the values.
+// optionally, the values.  One thread per four columns.
 __global__ void __launch_bounds__(256) prefill_silu_image_kernel(const float *__restrict__ gate, uint32_t gsplit, const float *__restrict__ upv,
                                                                  uint32_t usplit, uint32_t stride, uint32_t K, uint32_t ntok,
                                                                  uint8_t *__restrict__ image, float *__restrict__ h, uint32_t h_stride)
 {
-    const uint32_t t = blockIdx.y, g = blockIdx.x * 256 + threadIdx.x;
-    if (g >= K / 32) return;
-    if (t >= ntok) {
-        image_group(image, t, g, [](int) { return make_float4(0.f, 0.f, 0.f, 0.f); });
-        return;
-    }
-    auto get = [&](int i) {
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    const uint32_t t = blockIdx.y, i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= K / 4) return;   // K / 4 is a multiple of 8: the eight threads of a group leave together
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t < ntok) {
+        float4 a = v, b = v;
         for (uint32_t s = 0; s < gsplit; s++) {
-            const float4 p = *reinterpret_cast<const float4 *>(gate + ((size_t)s * PF_TOK + t) * stride + 32 * g + i);
+            const float4 p = *reinterpret_cast<const float4 *>(gate + ((size_t)s * PF_TOK + t) * stride + 4 * i);
             a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
         }
         for (uint32_t s = 0; s < usplit; s++) {
-            const float4 p = *reinterpret_cast<const float4 *>(upv + ((size_t)s * PF_TOK + t) * stride + 32 * g + i);
+            const float4 p = *reinterpret_cast<const float4 *>(upv + ((size_t)s * PF_TOK + t) * stride + 4 * i);
             b.x += p.x; b.y += p.y; b.z += p.z; b.w += p.w;
         }
-        float4 v;
         v.x = b.x * (a.x / (1.0f + expf(-a.x)));
         v.y = b.y * (a.y / (1.0f + expf(-a.y)));
         v.z = b.z * (a.z / (1.0f + expf(-a.z)));
         v.w = b.w * (a.w / (1.0f + expf(-a.w)));
-        if (h) *reinterpret_cast<float4 *>(h + (size_t)t * h_stride + 32 * g + i) = v;
-        return v;
-    };
-    image_group(image, t, g, get);
+        if (h) *reinterpret_cast<float4 *>(h + (size_t)t * h_stride + 4 * i) = v;
+    }
+    image_quad(image, t, i >> 3, i & 7, v);
 }
 
 int launch_prefill_norm_image(float *x, uint32_t x_stride, const float *part, uint32_t nsplit, uint32_t part_stride, const float *norm_w,
                               float eps, uint32_t K, uint32_t ntok, uint8_t *image, float *xn, uint32_t xn_stride, cudaStream_t stream)
 {
-    WGB_REQUIRE(K % 32 == 0 && ntok <= PF_TOK, "activation image of %u columns, %u positions", K, ntok);
+    WGB_REQUIRE(K % 128 == 0 && ntok <= PF_TOK, "activation image of %u columns (whole warps of four-column threads), %u positions", K, ntok);
     prefill_norm_image_kernel<<<image ? PF_TOK : ntok, 256, 0, stream>>>(x, x_stride, part, nsplit, part_stride, norm_w, eps, K, ntok, image, xn,
                                                                           xn_stride);
     WGB_LAUNCH_CHECK("prefill_norm_image_kernel");
@@ -459,8 +440,8 @@ int launch_prefill_norm_image(float *x, uint32_t x_stride, const float *part, ui
 int launch_prefill_silu_image(const float *gate, uint32_t gsplit, const float *up, uint32_t usplit, uint32_t stride, uint32_t K,
                               uint32_t ntok, uint8_t *image, float *h, uint32_t h_stride, cudaStream_t stream)
 {
-    WGB_REQUIRE(K % 32 == 0 && ntok <= PF_TOK, "activation image of %u columns, %u positions", K, ntok);
-    prefill_silu_image_kernel<<<dim3((K / 32 + 255) / 256, PF_TOK), 256, 0, stream>>>(gate, gsplit, up, usplit, stride, K, ntok, image, h,
+    WGB_REQUIRE(K % 128 == 0 && ntok <= PF_TOK, "activation image of %u columns (whole warps of four-column threads), %u positions", K, ntok);
+    prefill_silu_image_kernel<<<dim3((K / 4 + 255) / 256, PF_TOK), 256, 0, stream>>>(gate, gsplit, up, usplit, stride, K, ntok, image, h,
                                                                                         h_stride);
     WGB_LAUNCH_CHECK("prefill_silu_image_kernel");
     return WGB_OK;

@@ -1,7 +1,7 @@
 """Quantised matrix-vector microbenchmark through the C ABI (`wgb_gemv_quant`).
 
     python -m wgml_b200.gemv_bench [--qtypes q4_k,q6_k,q8_0] [--shapes 4096x4096,...] [--reps 100]
-                                   [--eager N] [--json] [--tensor]
+                                   [--eager N] [--json] [--tensor] [--batched N]
 
 The shapes and value distributions are those of wgml-bench's GEMV sweep restricted to the transformer
 shapes of a 7B model (crates/wgml-bench/src/main.rs:186-248 times `GemvQuant::dispatch` on random block
@@ -13,6 +13,8 @@ is replayed three times between CUDA events.  The figure printed is algorithmic 
 (rows * cols * bytes-per-weight of the GGUF format + 4 * cols + 4 * rows) per second.
 `--eager N` instead issues N plain launches and exits; it exists for profilers, which want few launches.
 `--tensor` times the tcgen05 path (`wgb_gemv_q4k_tiles`, Q4_K, up to 4096 columns) instead of `wgb_gemv_quant`.
+`--batched N` times the batched tcgen05 product of the prompt prefill (`wgb_gemm_q4k_tiles`, Q4_K, N = 1..8 input
+vectors per launch: image of the inputs, product, sum of the column slices).
 """
 from __future__ import annotations
 
@@ -29,13 +31,15 @@ QT = {"q8_0": synth.Q8_0, "q4_k": synth.Q4_K, "q6_k": synth.Q6_K, "f32": synth.F
 BPE = {synth.F32: 4.0, synth.Q8_0: 34 / 32, synth.Q4_K: 144 / 256, synth.Q6_K: 210 / 256}
 
 
-def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False):
+def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False, batched=0):
     lib = _lib.load()
     out = []
     for name in qtypes:
         qt = QT[name]
         for (n, k) in shapes:
             if tensor and (qt != synth.Q4_K or k > 4096 or n % 128):
+                continue
+            if batched and (qt != synth.Q4_K or k % 256 or n % 128):
                 continue
             nbytes = n * k * BPE[qt]
             ncopy = max(2, int(np.ceil(400e6 / nbytes)))
@@ -47,14 +51,17 @@ def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False):
             mats = []
             for _ in range(ncopy):
                 h = C.c_void_p()
-                if tensor:
+                if tensor or batched:
                     _lib.check(lib.wgb_q4k_tiles_create(raw.ctypes.data, n, k, None, C.byref(h)))
                 else:
                     _lib.check(lib.wgb_quant_matrix_create(qt, raw.ctypes.data, n, k, None, C.byref(h)))
                 mats.append(h)
             gemv = lib.wgb_gemv_q4k_tiles if tensor else lib.wgb_gemv_quant
-            x = torch.randn(k, device="cuda")
-            y = torch.zeros(n, device="cuda")
+            x = torch.randn(max(batched, 1), k, device="cuda")
+            y = torch.zeros(max(batched, 1), n, device="cuda")
+            if batched:
+                def gemv(h, xp, yp, stream):
+                    return lib.wgb_gemm_q4k_tiles(h, xp, batched, yp, stream)
             st = torch.cuda.current_stream().cuda_stream
             if eager:
                 for it in range(eager):
@@ -62,7 +69,7 @@ def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False):
                 torch.cuda.synchronize()
                 out.append({"qtype": name, "rows": n, "cols": k, "eager_launches": eager})
             else:
-                for it in range(20):
+                for it in range(max(20, ncopy)):   # also the first call on every copy (it may allocate)
                     _lib.check(gemv(mats[it % ncopy], x.data_ptr(), y.data_ptr(), st))
                 torch.cuda.synchronize()
                 g = torch.cuda.CUDAGraph()
@@ -80,10 +87,10 @@ def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False):
                 torch.cuda.synchronize()
                 us = e0.elapsed_time(e1) * 1e3 / (3 * reps)
                 alg = nbytes + 4 * k + 4 * n
-                out.append({"qtype": name + ("/tcgen05" if tensor else ""), "rows": n, "cols": k, "us": us, "bytes": alg, "gbs": alg / us / 1e3,
+                out.append({"qtype": name + ("/tcgen05" if tensor else f"/tcgen05 x{batched}" if batched else ""), "rows": n, "cols": k, "us": us, "bytes": alg, "gbs": alg / us / 1e3,
                             "frac_of_measured_peak": alg / us / 1e3 / peak_gbs, "copies": ncopy})
             for h in mats:
-                (lib.wgb_q4k_tiles_destroy if tensor else lib.wgb_quant_matrix_destroy)(h)
+                (lib.wgb_q4k_tiles_destroy if tensor or batched else lib.wgb_quant_matrix_destroy)(h)
     return out
 
 
@@ -96,9 +103,10 @@ def main():
     ap.add_argument("--peak-gbs", type=float, default=6550.7, help="HBM copy bandwidth the fraction is taken of")
     ap.add_argument("--json", action="store_true")
     ap.add_argument("--tensor", action="store_true", help="time the tcgen05 path (Q4_K, up to 4096 columns)")
+    ap.add_argument("--batched", type=int, default=0, help="time the batched tcgen05 product with this many input vectors (1..8)")
     a = ap.parse_args()
     shapes = [tuple(int(v) for v in s.split("x")) for s in a.shapes.split(",")]
-    res = run(a.qtypes.split(","), shapes, a.reps, a.eager, a.peak_gbs, a.tensor)
+    res = run(a.qtypes.split(","), shapes, a.reps, a.eager, a.peak_gbs, a.tensor, a.batched)
     if a.json:
         print(json.dumps(res))
         return
