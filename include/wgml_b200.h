@@ -114,6 +114,13 @@ int wgb_gemv_q4k_tiles(const wgb_q4k_tiles *m, const float *d_v, float *d_out, v
  * operators; the first call on a matrix allocates its work areas (make it outside stream capture), and calls on
  * one matrix must be ordered on a stream. */
 int wgb_gemm_q4k_tiles(wgb_q4k_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream);
+/* The batched product for Q6_K matrices (BlockQ6K, quantization.rs:225-264): the 16-column scales are folded
+ * into a two-plane integer weight operand and a super-block's sixteen MMAs accumulate in tensor memory, with one
+ * exponent per input vector and super-block.  h_blocks: raw GGUF blocks, nrows a multiple of 128, ncols of 256. */
+typedef struct wgb_q6k_tiles wgb_q6k_tiles;
+int wgb_q6k_tiles_create(const void *h_blocks, size_t nrows, size_t ncols, void *stream, wgb_q6k_tiles **out);
+int wgb_q6k_tiles_destroy(wgb_q6k_tiles *m);
+int wgb_gemm_q6k_tiles(wgb_q6k_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream);
 /* Waits for the device and returns WGB_ERR_TIMEOUT if a bounded wait inside a matrix-vector kernel has
  * expired since the last report (stand-alone launches are asynchronous and cannot say so themselves). */
 int wgb_device_status(void);
@@ -401,9 +408,9 @@ int wgb_llama2_set_sampler(wgb_llama2 *m, float temperature, float topp, uint64_
  * Llama2::dispatch, chat_llama2.rs:104-116,169-204, and drops the logits).  Once enabled, wgb_llama2_decode
  * sends every prompt position but the last through passes of eight positions: the Q4_K layer matrices are
  * multiplied on the tensor cores (tcgen05.mma kind::i8 on the same fixed-point image of the activations as the
- * matrix-vector kernels, from tile-major copies of the weights made here, which doubles their memory), other
- * formats through the matrix-vector kernel position by position; RMSNorm, RoPE, the cache rows and causal
- * attention are computed per pass.  Cache rows and everything after the prompt agree with the
+ * matrix-vector kernels, from tile-major copies of the weights made here, which doubles their memory), the Q6_K
+ * ones by a kernel of their own (scales folded into the weight operand), other formats through the matrix-vector
+ * kernel position by position; RMSNorm, RoPE, the cache rows and causal attention are computed per pass.  Cache rows and everything after the prompt agree with the
  * position-by-position path to the order of the f32 additions.  One GPU per model only (WGB_ERR_UNSUPPORTED
  * for a tensor-parallel rank); enable it after the weights are set (setting a matrix disables it). */
 int wgb_llama2_set_prefill(wgb_llama2 *m, int enable);

@@ -39,6 +39,44 @@ def test_batched_product_vs_oracle(shape):
         assert_close(got[i], o64, RTOL, atol, f"batched product {nrows}x{ncols}, vector {i} of {n_vec}")
 
 
+@pytest.mark.parametrize("shape", [(128, 256, 8), (256, 512, 3), (384, 768, 8), (4096, 4096, 8), (1408, 11008, 5), (4096, 11008, 8)])
+def test_batched_q6k_product_vs_oracle(shape):
+    """The Q6_K kernel (scales folded into a two-plane operand, one exponent per vector and super-block)."""
+    nrows, ncols, n_vec = shape
+    qt, arr = synth.matrix(ops.Q6_K, nrows, ncols, 9, "pf6")
+    raw = np.ascontiguousarray(arr).view(np.uint8)
+    x = np.random.default_rng(3).standard_normal((n_vec, ncols)).astype(np.float32)
+    x *= (10.0 ** np.arange(-3, -3 + n_vec))[:, None].astype(np.float32)
+    t = ops.Q6KTiles(raw, nrows, ncols)
+    out = torch.full((n_vec, nrows), float("nan"), device="cuda")
+    t.gemm(out, torch.from_numpy(x).cuda())
+    ops.device_status()
+    got = out.cpu().numpy()
+    for i in range(n_vec):
+        _, o64 = oracle.gemv_quant(ops.Q6_K, raw, nrows, ncols, x[i], want_f64=True)
+        atol = ATOL * float(np.sqrt(np.mean(o64 ** 2)))
+        assert_close(got[i], o64, RTOL, atol, f"batched Q6_K product {nrows}x{ncols}, vector {i} of {n_vec}")
+
+
+def test_batched_q6k_product_extreme_scales_and_codes():
+    """All-0x00 / all-0xFF code bytes and scales of -128 / 127: the largest magnitudes of the folded operand."""
+    nrows, ncols = 128, 512
+    rng = np.random.default_rng(4)
+    blocks = np.zeros((nrows * ncols // 256, 210), np.uint8)
+    blocks[:, :192] = rng.choice(np.array([0x00, 0xFF], np.uint8), size=(blocks.shape[0], 192))
+    blocks[:, 192:208] = rng.choice(np.array([0x80, 0x7F, 0x01, 0xFF], np.uint8), size=(blocks.shape[0], 16))
+    blocks[:, 208:210] = np.frombuffer(np.float16(0.01).tobytes(), np.uint8)
+    raw = blocks.reshape(-1)
+    x = rng.standard_normal((8, ncols)).astype(np.float32)
+    t = ops.Q6KTiles(raw, nrows, ncols)
+    out = torch.zeros(8, nrows, device="cuda")
+    t.gemm(out, torch.from_numpy(x).cuda())
+    ops.device_status()
+    for i in range(8):
+        _, o64 = oracle.gemv_quant(ops.Q6_K, raw, nrows, ncols, x[i], want_f64=True)
+        assert_close(out[i].cpu().numpy(), o64, RTOL, ATOL * float(np.sqrt(np.mean(o64 ** 2))), f"extreme Q6_K blocks, vector {i}")
+
+
 def test_batched_product_matches_the_single_vector_kernels():
     nrows, ncols = 4096, 4096
     raw, x = make(nrows, ncols, 11, 8)

@@ -44,6 +44,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint: a thread whose phase has not completed may be parked by the hardware for up
+// to about `hint_ns` before the instruction returns false, instead of coming back at once to poll again (polls
+// of parked warps take issue slots from the warps that have work).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait; after `limit_ns` records `code` in *err (unless an earlier code is there) and returns false.
 // The clock is only looked at after a few hundred unsuccessful polls: reading %globaltimer takes far longer
 // than a poll, and nearly every wait of a healthy kernel ends within the first handful.

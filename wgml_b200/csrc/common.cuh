@@ -49,6 +49,7 @@ struct DeviceState {
     bool gemv_attrs = false;              // fused matrix-vector kernels opted in to large dynamic shared memory
     bool tiles_attrs = false;             // the same for the tensor-memory kernel
     bool prefill_attrs = false;           // the same for the batched tensor-memory kernel
+    bool prefill6_attrs = false;          // the same for its Q6_K counterpart
     float *attn_scratch = nullptr;        // scratch of the stand-alone attention op, grown on demand
     size_t attn_scratch_floats = 0;
     uint32_t *attn_counters = nullptr;

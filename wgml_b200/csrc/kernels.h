@@ -179,6 +179,15 @@ int launch_prefill_norm_image(float *x, uint32_t x_stride, const float *part, ui
                               float eps, uint32_t K, uint32_t ntok, uint8_t *image, float *xn, uint32_t xn_stride, cudaStream_t stream);
 int launch_prefill_silu_image(const float *gate, uint32_t gsplit, const float *up, uint32_t usplit, uint32_t stride, uint32_t K,
                               uint32_t ntok, uint8_t *image, float *h, uint32_t h_stride, cudaStream_t stream);
+// The Q6_K counterparts (prefill_q6k.cu): the scale is folded into a two-plane weight operand and a super-block's
+// MMAs accumulate in tensor memory, which takes an image of the inputs with one exponent per vector and
+// super-block (launch_prefill_image6, from the values themselves).
+size_t prefill_image6_bytes(uint32_t K);
+bool prefill_tileable6(const QMat &m);
+int prefill_tile_major6(const QMat &m, uint8_t **out, cudaStream_t stream);
+int launch_prefill_image6(const float *x, uint32_t x_stride, uint32_t K, uint32_t ntok, uint8_t *image, cudaStream_t stream);
+int launch_gemm_q6k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, const uint8_t *image, uint32_t ntok, float *out,
+                          uint32_t out_stride, uint32_t nsplit, cudaStream_t stream);
 struct PrefillQkv {
     const float *q, *k, *v;            // product slices: [split][PF_TOK][stride]
     uint32_t q_split, k_split, v_split, q_stride, kv_stride;

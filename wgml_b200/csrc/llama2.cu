@@ -85,7 +85,9 @@ struct wgb_llama2 {
     struct Prefill {
         bool enabled = false;
         std::vector<uint8_t *> tiles;        // [layer * 7 + matrix], NULL: no tensor-core path for that matrix
+        std::vector<uint8_t> tiles_q6;       // same index: the copy is a Q6_K one (its own kernel and image)
         uint8_t *img_dim = nullptr, *img_q = nullptr, *img_hidden = nullptr;
+        uint8_t *img6 = nullptr;             // Q6_K image of the widest input
         float *x = nullptr, *xn = nullptr, *q = nullptr, *xb = nullptr, *h = nullptr;   // [PF_TOK][dim | q_dim | hidden]
         float *part[3] = {};                 // product slices: [PF_MAX_SPLIT][PF_TOK][max(dim, q_dim, hidden)]
         size_t positions = 0;                // prompt positions that went through it, over all decode calls
@@ -402,7 +404,7 @@ void prefill_free(wgb_llama2 *m)
 {
     for (uint8_t *t : m->pf.tiles) if (t) cudaFree(t);
     m->pf.tiles.clear();
-    uint8_t *imgs[] = { m->pf.img_dim, m->pf.img_q, m->pf.img_hidden };
+    uint8_t *imgs[] = { m->pf.img_dim, m->pf.img_q, m->pf.img_hidden, m->pf.img6 };
     for (uint8_t *b : imgs) if (b) cudaFree(b);
     float *bufs[] = { m->pf.x, m->pf.xn, m->pf.q, m->pf.xb, m->pf.h, m->pf.part[0], m->pf.part[1], m->pf.part[2] };
     for (float *b : bufs) if (b) cudaFree(b);
@@ -417,6 +419,12 @@ int prefill_product(wgb_llama2 *m, uint32_t layer, int which, const uint8_t *ima
 {
     const QMat &w = m->layers[layer].m[which]->view;
     const uint8_t *tiles = m->pf.tiles[(size_t)layer * 7 + which];
+    if (tiles && m->pf.tiles_q6[(size_t)layer * 7 + which]) {
+        *nsplit = prefill_gemm_splits(w.nrows, w.ncols);
+        int rc = launch_prefill_image6(xf, xf_stride, w.ncols, ntok, m->pf.img6, s);
+        if (rc) return rc;
+        return launch_gemm_q6k_tiles(tiles, w.nrows, w.ncols, m->pf.img6, ntok, out, stride, *nsplit, s);
+    }
     if (tiles) {
         *nsplit = prefill_gemm_splits(w.nrows, w.ncols);
         return launch_gemm_q4k_tiles(tiles, w.nrows, w.ncols, image, ntok, out, stride, *nsplit, s);
@@ -1157,11 +1165,16 @@ WGB_EXPORT int wgb_llama2_set_prefill(wgb_llama2 *m, int enable)
                 m->q_dim, m->hidden);
     wgb_llama2::Prefill &pf = m->pf;
     pf.tiles.assign((size_t)c.n_layers * 7, nullptr);
+    pf.tiles_q6.assign((size_t)c.n_layers * 7, 0);
     auto bail = [&](int code) { prefill_free(m); return code; };
     for (uint32_t l = 0; l < c.n_layers; l++)
         for (int i = 0; i < 7; i++) {
             const QMat &w = m->layers[l].m[i]->view;
             if (prefill_tileable(w) && (rc = prefill_tile_major(w, &pf.tiles[(size_t)l * 7 + i], nullptr))) return bail(rc);
+            if (prefill_tileable6(w)) {
+                if ((rc = prefill_tile_major6(w, &pf.tiles[(size_t)l * 7 + i], nullptr))) return bail(rc);
+                pf.tiles_q6[(size_t)l * 7 + i] = 1;
+            }
         }
     auto image = [&](uint8_t **p, uint32_t K) -> int {
         WGB_CUDA(cudaMalloc((void **)p, prefill_image_bytes(K)));
@@ -1170,6 +1183,7 @@ WGB_EXPORT int wgb_llama2_set_prefill(wgb_llama2 *m, int enable)
     };
     if ((rc = image(&pf.img_dim, c.dim)) || (rc = image(&pf.img_q, m->q_dim)) || (rc = image(&pf.img_hidden, m->hidden))) return bail(rc);
     const size_t widest = std::max<size_t>(std::max<size_t>(c.dim, m->q_dim), m->hidden);
+    WGB_CUDA(cudaMalloc((void **)&pf.img6, prefill_image6_bytes((uint32_t)widest)));
     if ((rc = dalloc(&pf.x, (size_t)PF_TOK * c.dim)) || (rc = dalloc(&pf.xn, (size_t)PF_TOK * c.dim)) || (rc = dalloc(&pf.q, (size_t)PF_TOK * m->q_dim)) ||
         (rc = dalloc(&pf.xb, (size_t)PF_TOK * m->q_dim)) || (rc = dalloc(&pf.h, (size_t)PF_TOK * m->hidden)))
         return bail(rc);

@@ -49,25 +49,6 @@ struct TbArgs {
     uint32_t *err;
 };
 
-// Units of a block: items blockIdx.x, blockIdx.x + gridDim.x, ...; item i = (tile i / nsplit, slice i % nsplit),
-// whose columns are [slice * nkb / nsplit, (slice + 1) * nkb / nsplit).
-struct UnitWalk {
-    uint32_t item, tile, sp, kb, kb_end;
-    __device__ __forceinline__ void set(uint32_t i, uint32_t nsplit, uint32_t nkb)
-    {
-        item = i;
-        tile = i / nsplit;
-        sp = i - tile * nsplit;
-        kb = sp * nkb / nsplit;
-        kb_end = (sp + 1) * nkb / nsplit;
-    }
-    __device__ __forceinline__ bool last() const { return kb + 1 == kb_end; }
-    __device__ __forceinline__ void next(uint32_t nsplit, uint32_t nkb, uint32_t stride)
-    {
-        if (++kb == kb_end) set(item + stride, nsplit, nkb);
-    }
-};
-
 __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_constant__ TbArgs a)
 {
     extern __shared__ uint8_t tb_smem_raw[];
@@ -204,30 +185,36 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                 if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), (m >> 1) & 1, dead, a.err, 24));
                 if (ok) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    // all six loads of the thread's two sub-blocks are issued before the one wait; the exponents and
+                    // sums of the two groups are fetched from the stage meanwhile
+                    int d[2][3][8];
+#pragma unroll
+                    for (uint32_t q = 0; q < 2; q++)
+#pragma unroll
+                        for (uint32_t dg = 0; dg < 3; dg++) tc_ld8(taddr + u * 256 + 32 * (2 * sub + q) + 8 * dg, d[q][dg]);
+                    float ev[2][8], sv[2][8];
 #pragma unroll
                     for (uint32_t q = 0; q < 2; q++) {
-                        int d[3][8];
-#pragma unroll
-                        for (uint32_t dg = 0; dg < 3; dg++) tc_ld8(taddr + u * 256 + 32 * (2 * sub + q) + 8 * dg, d[dg]);
-                        // exponents and sums of group 2 sub + q, one float per position
-                        const uint32_t eo = img + TB_IMG_DIGITS + (2 * sub + q) * PF_TOK * 4;
+                        const uint32_t eo = img + TB_IMG_DIGITS + (2 * sub + q) * PF_TOK * 4;   // one float per position
                         const uint4 e0 = lds128(eo), e1 = lds128(eo + 16), s0 = lds128(eo + 8 * PF_TOK * 4), s1 = lds128(eo + 8 * PF_TOK * 4 + 16);
-                        const float ev[8] = { __uint_as_float(e0.x), __uint_as_float(e0.y), __uint_as_float(e0.z), __uint_as_float(e0.w),
-                                              __uint_as_float(e1.x), __uint_as_float(e1.y), __uint_as_float(e1.z), __uint_as_float(e1.w) };
-                        const float sv[8] = { __uint_as_float(s0.x), __uint_as_float(s0.y), __uint_as_float(s0.z), __uint_as_float(s0.w),
-                                              __uint_as_float(s1.x), __uint_as_float(s1.y), __uint_as_float(s1.z), __uint_as_float(s1.w) };
-                        // the block's d and dmin folded into the sub-block's scale and min once per unit
-                        const float sc = dm.x * byte2f(scw, q), mn = -dm.y * byte2f(mw, q);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                        for (uint32_t t = 0; t < PF_TOK; t++) {
-                            // the two low digit sums are joined in the integer unit (|.| < 2^31) and take one
-                            // conversion; the product with the exponent is exact (a power of two)
-                            const float f = fmaf(__int2float_rn(d[2][t]), 65536.0f, __int2float_rn(d[1][t] * 256 + d[0][t]));
-                            rowacc[t] = fmaf(f, sc * ev[t], fmaf(mn, sv[t], rowacc[t]));
-                        }
+                        ev[q][0] = __uint_as_float(e0.x); ev[q][1] = __uint_as_float(e0.y); ev[q][2] = __uint_as_float(e0.z); ev[q][3] = __uint_as_float(e0.w);
+                        ev[q][4] = __uint_as_float(e1.x); ev[q][5] = __uint_as_float(e1.y); ev[q][6] = __uint_as_float(e1.z); ev[q][7] = __uint_as_float(e1.w);
+                        sv[q][0] = __uint_as_float(s0.x); sv[q][1] = __uint_as_float(s0.y); sv[q][2] = __uint_as_float(s0.z); sv[q][3] = __uint_as_float(s0.w);
+                        sv[q][4] = __uint_as_float(s1.x); sv[q][5] = __uint_as_float(s1.y); sv[q][6] = __uint_as_float(s1.z); sv[q][7] = __uint_as_float(s1.w);
                     }
+                    // the block's d and dmin folded into the sub-blocks' scales and mins once per unit
+                    const float sc0 = dm.x * byte2f(scw, 0), sc1 = dm.x * byte2f(scw, 1), mn0 = -dm.y * byte2f(mw, 0), mn1 = -dm.y * byte2f(mw, 1);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (uint32_t t = 0; t < PF_TOK; t++) {
+                        // the two low digit sums are joined in the integer unit (|.| < 2^31) and take one conversion;
+                        // the product of scale and exponent is exact in the exponent (a power of two)
+                        const float f0 = fmaf(__int2float_rn(d[0][2][t]), 65536.0f, __int2float_rn(d[0][1][t] * 256 + d[0][0][t]));
+                        const float f1 = fmaf(__int2float_rn(d[1][2][t]), 65536.0f, __int2float_rn(d[1][1][t] * 256 + d[1][0][t]));
+                        const float mins = fmaf(mn0, sv[0][t], mn1 * sv[1][t]);
+                        rowacc[t] += fmaf(f0, sc0 * ev[0][t], fmaf(f1, sc1 * ev[1][t], mins));
+                    }
                 }
                 mbar_arrive(bar_empty(slot));
                 if (fin.last()) {
