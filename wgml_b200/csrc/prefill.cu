@@ -23,6 +23,8 @@
 #include "kernels.h"
 #include "tc_common.cuh"
 
+#include <cstdlib>
+
 namespace wgb {
 
 constexpr uint32_t TB_IMG_DIGITS = 16 * 4 * 128;                          // 16 K-cores x 4 row groups x 128 bytes
@@ -38,6 +40,15 @@ constexpr uint32_t TB_SMEM = TB_OFF_RING + TB_RING * TB_STAGE;
 static_assert(PF_TOK == 8, "one core matrix (eight rows) per digit");
 static_assert(TB_STAGE % 128 == 0 && TB_IMG_BYTES % 16 == 0, "stages keep the operand alignment");
 static_assert(TB_SMEM + 1024 + 20 * 1024 <= 227 * 1024, "shared memory budget (dynamic + static)");
+
+bool pdl_enabled()
+{
+    static const bool on = [] {
+        const char *env = getenv("WGB_NO_PDL");
+        return !(env && env[0] == '1');
+    }();
+    return on;
+}
 
 size_t prefill_image_bytes(uint32_t K) { return (size_t)(K / 256) * TB_IMG_BYTES; }
 
@@ -59,6 +70,7 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)tb_smem_raw + 1023) & ~(uintptr_t)1023);
     volatile uint32_t *dead = &dead_flag;
 
+    pdl_launch_dependents();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t nkb = a.nkb, nsplit = a.nsplit, nitems = (a.nrows / TC_TILE_ROWS) * nsplit;
     auto bar_full = [&](uint32_t s) { return smem_addr(&bars[s]); };
@@ -89,6 +101,8 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
+    // barriers and tensor memory are set up while the preceding launch (which writes the image) still runs
+    pdl_wait();
 
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
@@ -287,8 +301,7 @@ int launch_gemm_q4k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, co
     a.out_stride = out_stride;
     a.err = gemv_status_word();
     const uint32_t items = nrows / TC_TILE_ROWS * nsplit, sms = (uint32_t)sm_count();
-    gemm_q4k_tc_kernel<<<items < sms ? items : sms, TB_NT, TB_SMEM + 1024, stream>>>(a);
-    WGB_LAUNCH_CHECK("gemm_q4k_tc_kernel");
+    WGB_CUDA(launch_pdl(gemm_q4k_tc_kernel, dim3(items < sms ? items : sms), dim3(TB_NT), TB_SMEM + 1024, stream, a));
     return WGB_OK;
 }
 
@@ -343,6 +356,8 @@ __global__ void __launch_bounds__(256) prefill_norm_image_kernel(float *__restri
                                                                  float eps, uint32_t K, uint32_t ntok, uint8_t *__restrict__ image,
                                                                  float *__restrict__ xn, uint32_t xn_stride)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t t = blockIdx.x;
     __shared__ float red[8];
     __shared__ float scale_s;
@@ -392,6 +407,8 @@ __global__ void __launch_bounds__(256) prefill_silu_image_kernel(const float *__
                                                                  uint32_t usplit, uint32_t stride, uint32_t K, uint32_t ntok,
                                                                  uint8_t *__restrict__ image, float *__restrict__ h, uint32_t h_stride)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t t = blockIdx.y, i = blockIdx.x * 256 + threadIdx.x;
     if (i >= K / 4) return;   // K / 4 is a multiple of 8: the eight threads of a group leave together
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -418,9 +435,8 @@ int launch_prefill_norm_image(float *x, uint32_t x_stride, const float *part, ui
                               float eps, uint32_t K, uint32_t ntok, uint8_t *image, float *xn, uint32_t xn_stride, cudaStream_t stream)
 {
     WGB_REQUIRE(K % 128 == 0 && ntok <= PF_TOK, "activation image of %u columns (whole warps of four-column threads), %u positions", K, ntok);
-    prefill_norm_image_kernel<<<image ? PF_TOK : ntok, 256, 0, stream>>>(x, x_stride, part, nsplit, part_stride, norm_w, eps, K, ntok, image, xn,
-                                                                          xn_stride);
-    WGB_LAUNCH_CHECK("prefill_norm_image_kernel");
+    WGB_CUDA(launch_pdl(prefill_norm_image_kernel, dim3(image ? PF_TOK : ntok), dim3(256), 0, stream, x, x_stride, part, nsplit, part_stride, norm_w,
+                        eps, K, ntok, image, xn, xn_stride));
     return WGB_OK;
 }
 
@@ -428,9 +444,8 @@ int launch_prefill_silu_image(const float *gate, uint32_t gsplit, const float *u
                               uint32_t ntok, uint8_t *image, float *h, uint32_t h_stride, cudaStream_t stream)
 {
     WGB_REQUIRE(K % 128 == 0 && ntok <= PF_TOK, "activation image of %u columns (whole warps of four-column threads), %u positions", K, ntok);
-    prefill_silu_image_kernel<<<dim3((K / 4 + 255) / 256, PF_TOK), 256, 0, stream>>>(gate, gsplit, up, usplit, stride, K, ntok, image, h,
-                                                                                        h_stride);
-    WGB_LAUNCH_CHECK("prefill_silu_image_kernel");
+    WGB_CUDA(launch_pdl(prefill_silu_image_kernel, dim3((K / 4 + 255) / 256, PF_TOK), dim3(256), 0, stream, gate, gsplit, up, usplit, stride, K, ntok,
+                        image, h, h_stride));
     return WGB_OK;
 }
 
@@ -442,6 +457,8 @@ int launch_prefill_silu_image(const float *gate, uint32_t gsplit, const float *u
 // at position p sits at (h * seq_len + p) * head_size + e).
 __global__ void __launch_bounds__(128) prefill_rope_append_kernel(PrefillQkv a)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t i = blockIdx.x * 128 + threadIdx.x, t = blockIdx.y;   // pair index over q
     if (2 * i >= a.q_dim) return;
     const uint32_t pos = a.pos0 + t, half = a.head_size / 2;
@@ -473,8 +490,7 @@ __global__ void __launch_bounds__(128) prefill_rope_append_kernel(PrefillQkv a)
 
 int launch_prefill_rope_append(const PrefillQkv &a, uint32_t ntok, cudaStream_t stream)
 {
-    prefill_rope_append_kernel<<<dim3((a.q_dim / 2 + 127) / 128, ntok), 128, 0, stream>>>(a);
-    WGB_LAUNCH_CHECK("prefill_rope_append_kernel");
+    WGB_CUDA(launch_pdl(prefill_rope_append_kernel, dim3((a.q_dim / 2 + 127) / 128, ntok), dim3(128), 0, stream, a));
     return WGB_OK;
 }
 
@@ -492,6 +508,8 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
                                                                 uint32_t ntok)
 {
     extern __shared__ float pa_smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t h = blockIdx.x, t0 = blockIdx.y * PA_TQ;
     if (t0 >= ntok) return;
     const uint32_t nq = ntok - t0 < PA_TQ ? ntok - t0 : PA_TQ;
@@ -600,9 +618,8 @@ int launch_prefill_attention(const float *q, const float *k_cache, const float *
     WGB_REQUIRE(head_size % 4 == 0 && head_size <= 256 && ntok >= 1 && ntok <= PF_TOK, "prompt attention: head size %u, %u positions", head_size,
                 ntok);
     const size_t smem = (size_t)(PA_TQ * head_size + PA_TQ * PA_CHUNK + 4 * PA_TQ * head_size) * sizeof(float);
-    prefill_attention_kernel<<<dim3(n_heads, (ntok + PA_TQ - 1) / PA_TQ), 256, smem, stream>>>(q, k_cache, v_cache, out, n_heads * head_size,
-                                                                                                head_size, kv_mul, seq_len, pos0, ntok);
-    WGB_LAUNCH_CHECK("prefill_attention_kernel");
+    WGB_CUDA(launch_pdl(prefill_attention_kernel, dim3(n_heads, (ntok + PA_TQ - 1) / PA_TQ), dim3(256), smem, stream, q, k_cache, v_cache, out,
+                        n_heads * head_size, head_size, kv_mul, seq_len, pos0, ntok));
     return WGB_OK;
 }
 

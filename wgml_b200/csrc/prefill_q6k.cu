@@ -62,6 +62,7 @@ __global__ void __launch_bounds__(T6_NT, 1) gemm_q6k_tc_kernel(const __grid_cons
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)t6_smem_raw + 1023) & ~(uintptr_t)1023);
     volatile uint32_t *dead = &dead_flag;
 
+    pdl_launch_dependents();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t nkb = a.nkb, nsplit = a.nsplit, nitems = (a.nrows / TC_TILE_ROWS) * nsplit;
     auto bar_full = [&](uint32_t s) { return smem_addr(&bars[s]); };
@@ -92,6 +93,8 @@ __global__ void __launch_bounds__(T6_NT, 1) gemm_q6k_tc_kernel(const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_slot;
+    // barriers and tensor memory are set up while the preceding launch (which writes the image) still runs
+    pdl_wait();
 
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
@@ -264,8 +267,7 @@ int launch_gemm_q6k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, co
     a.out_stride = out_stride;
     a.err = gemv_status_word();
     const uint32_t items = nrows / TC_TILE_ROWS * nsplit, sms = (uint32_t)sm_count();
-    gemm_q6k_tc_kernel<<<items < sms ? items : sms, T6_NT, T6_SMEM + 1024, stream>>>(a);
-    WGB_LAUNCH_CHECK("gemm_q6k_tc_kernel");
+    WGB_CUDA(launch_pdl(gemm_q6k_tc_kernel, dim3(items < sms ? items : sms), dim3(T6_NT), T6_SMEM + 1024, stream, a));
     return WGB_OK;
 }
 
@@ -274,6 +276,8 @@ int launch_gemm_q6k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, co
 __global__ void __launch_bounds__(256) prefill_image6_kernel(const float *__restrict__ x, uint32_t x_stride, uint32_t nkb, uint32_t ntok,
                                                              uint8_t *__restrict__ image)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t wid = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (wid >= nkb * PF_TOK) return;
     const uint32_t kb = wid / PF_TOK, t = wid % PF_TOK;
@@ -318,8 +322,7 @@ int launch_prefill_image6(const float *x, uint32_t x_stride, uint32_t K, uint32_
 {
     WGB_REQUIRE(K % 256 == 0 && ntok <= PF_TOK, "Q6_K activation image of %u columns, %u vectors", K, ntok);
     const uint32_t warps = K / 256 * PF_TOK;
-    prefill_image6_kernel<<<(warps * 32 + 255) / 256, 256, 0, stream>>>(x, x_stride, K / 256, ntok, image);
-    WGB_LAUNCH_CHECK("prefill_image6_kernel");
+    WGB_CUDA(launch_pdl(prefill_image6_kernel, dim3((warps * 32 + 255) / 256), dim3(256), 0, stream, x, x_stride, K / 256, ntok, image));
     return WGB_OK;
 }
 
