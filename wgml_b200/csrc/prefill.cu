@@ -351,7 +351,7 @@ __device__ __forceinline__ void image_quad(uint8_t *__restrict__ image, uint32_t
 // ops/rms_norm.wgsl:36-67: (x * 1/sqrt(mean(x^2) + eps)) * w); its image, and optionally the values themselves.
 // One block per position; positions >= ntok get an all-zero image.  K is a multiple of 32, so the eight threads of
 // a group are always whole.
-__global__ void __launch_bounds__(256) prefill_norm_image_kernel(float *__restrict__ x, uint32_t x_stride, const float *__restrict__ part,
+__global__ void __launch_bounds__(1024) prefill_norm_image_kernel(float *__restrict__ x, uint32_t x_stride, const float *__restrict__ part,
                                                                  uint32_t nsplit, uint32_t part_stride, const float *__restrict__ norm_w,
                                                                  float eps, uint32_t K, uint32_t ntok, uint8_t *__restrict__ image,
                                                                  float *__restrict__ xn, uint32_t xn_stride)
@@ -359,16 +359,16 @@ __global__ void __launch_bounds__(256) prefill_norm_image_kernel(float *__restri
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t t = blockIdx.x;
-    __shared__ float red[8];
+    __shared__ float red[32];
     __shared__ float scale_s;
     if (t >= ntok) {
-        for (uint32_t i = threadIdx.x; i < K / 4; i += 256) image_quad(image, t, i >> 3, i & 7, make_float4(0.f, 0.f, 0.f, 0.f));
+        for (uint32_t i = threadIdx.x; i < K / 4; i += 1024) image_quad(image, t, i >> 3, i & 7, make_float4(0.f, 0.f, 0.f, 0.f));
         return;
     }
     float *xr = x + (size_t)t * x_stride;
     if (part || norm_w) {
         float ss = 0.0f;
-        for (uint32_t i = threadIdx.x * 4; i < K; i += 1024) {
+        for (uint32_t i = threadIdx.x * 4; i < K; i += 4096) {
             float4 v = *reinterpret_cast<const float4 *>(xr + i);
             for (uint32_t s = 0; s < (part ? nsplit : 0u); s++) {
                 const float4 p = *reinterpret_cast<const float4 *>(part + ((size_t)s * PF_TOK + t) * part_stride + i);
@@ -382,15 +382,15 @@ __global__ void __launch_bounds__(256) prefill_norm_image_kernel(float *__restri
         __syncthreads();
         if (threadIdx.x == 0) {
             float tot = 0.0f;
-            for (int i = 0; i < 8; i++) tot += red[i];
+            for (int i = 0; i < 32; i++) tot += red[i];
             scale_s = 1.0f / sqrtf(tot / (float)K + eps);
         }
         __syncthreads();
     }
     if (!image) return;
     const float scale = norm_w ? scale_s : 1.0f;
-    // the same thread reads back what it wrote above (element 4 (threadIdx.x + 256 k))
-    for (uint32_t i = threadIdx.x; i < K / 4; i += 256) {
+    // the same thread reads back what it wrote above (element 4 (threadIdx.x + 1024 k))
+    for (uint32_t i = threadIdx.x; i < K / 4; i += 1024) {
         float4 v = *reinterpret_cast<const float4 *>(xr + 4 * i);
         if (norm_w) {
             const float4 w = *reinterpret_cast<const float4 *>(norm_w + 4 * i);
@@ -435,7 +435,7 @@ int launch_prefill_norm_image(float *x, uint32_t x_stride, const float *part, ui
                               float eps, uint32_t K, uint32_t ntok, uint8_t *image, float *xn, uint32_t xn_stride, cudaStream_t stream)
 {
     WGB_REQUIRE(K % 128 == 0 && ntok <= PF_TOK, "activation image of %u columns (whole warps of four-column threads), %u positions", K, ntok);
-    WGB_CUDA(launch_pdl(prefill_norm_image_kernel, dim3(image ? PF_TOK : ntok), dim3(256), 0, stream, x, x_stride, part, nsplit, part_stride, norm_w,
+    WGB_CUDA(launch_pdl(prefill_norm_image_kernel, dim3(image ? PF_TOK : ntok), dim3(1024), 0, stream, x, x_stride, part, nsplit, part_stride, norm_w,
                         eps, K, ntok, image, xn, xn_stride));
     return WGB_OK;
 }
