@@ -36,7 +36,7 @@ UNIT = "tok/s"
 BPE = {0: 4.0, 8: 34 / 32, 12: 144 / 256, 14: 210 / 256}  # algorithmic bytes per weight
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/gemv_q4k_gate_up_7b_ncu_full.txt (7B shapes); classes without a capture report null.
-NCU_TRAFFIC = {("llama2-7b", "gate_up_silu/q4_k"): 50.89e6 + 0.13e6}
+NCU_TRAFFIC = {("llama2-7b", "gate_up_silu/q4_k"): 50.83e6 + 0.02e6}
 
 
 def measured_peaks():
