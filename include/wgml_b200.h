@@ -411,8 +411,9 @@ int wgb_llama2_set_sampler(wgb_llama2 *m, float temperature, float topp, uint64_
  * matrix-vector kernels, from tile-major copies of the weights made here, which doubles their memory), the Q6_K
  * ones by a kernel of their own (scales folded into the weight operand), other formats through the matrix-vector
  * kernel position by position; RMSNorm, RoPE, the cache rows and causal attention are computed per pass.  Cache rows and everything after the prompt agree with the
- * position-by-position path to the order of the f32 additions.  One GPU per model only (WGB_ERR_UNSUPPORTED
- * for a tensor-parallel rank); enable it after the weights are set (setting a matrix disables it). */
+ * position-by-position path to the order of the f32 additions.  A tensor-parallel rank sums its partial attn_output
+ * and ffn_down products over the group with one all-reduce each per pass and layer (call wgb_llama2_set_comm first,
+ * else WGB_ERR_UNSUPPORTED); enable it after the weights are set (setting a matrix disables it). */
 int wgb_llama2_set_prefill(wgb_llama2 *m, int enable);
 /* Prompt positions that have gone through the batched passes since it was enabled. */
 int wgb_llama2_prefill_positions(const wgb_llama2 *m, size_t *positions);

@@ -167,7 +167,7 @@ def test_prefill_resumes_at_a_later_position_and_can_be_switched_off():
     assert np.array_equal(b.decode(p1, 3), ta[: 17 + 3])
 
 
-def test_prefill_refused_for_a_tensor_parallel_rank():
+def test_prefill_of_a_tensor_parallel_rank_wants_its_communicator():
     from wgml_b200.models import Llama2, Llama2Config
     cfg = SMALL_LLAMA
     c = Llama2Config(cfg["dim"], cfg["hidden_dim"], cfg["n_layers"], cfg["n_q_heads"], cfg["n_kv_heads"], cfg["vocab_size"],
@@ -176,4 +176,4 @@ def test_prefill_refused_for_a_tensor_parallel_rank():
     m.load_tensors(synth.llama_tensors(cfg, 1, scale=0.002))
     with pytest.raises(_lib.WgbError) as e:
         m.set_prefill(True)
-    assert e.value.status == _lib.ERR_UNSUPPORTED
+    assert e.value.status == _lib.ERR_UNSUPPORTED and "communicator" in e.value.message

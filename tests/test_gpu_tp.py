@@ -41,3 +41,9 @@ def test_tp2_matches_single_gpu(tmp_path):
             ref_x = res[f"{name}/ref_x"]
             assert_close(res[f"{name}/{mode}/tp_x"], ref_x, RTOL, ATOL * max(1.0, float(np.abs(ref_x).max())),
                          f"{name} mode {mode} residual stream")
+    # batched prompt passes on the sharded model against the unsharded position-by-position loop
+    ref_t, ref_l = res["gqa_q4k/prefill/ref_tokens"], res["gqa_q4k/prefill/ref_logits"]
+    for mode in ("1", "0"):
+        assert np.array_equal(res[f"gqa_q4k/prefill{mode}/tp_tokens"], ref_t), f"prefill, exchange {mode}: tokens differ"
+        assert_close(res[f"gqa_q4k/prefill{mode}/tp_logits"], ref_l, RTOL, ATOL * max(1.0, float(np.abs(ref_l).max())),
+                     f"prefill, exchange {mode}: logits after the last step")

@@ -63,6 +63,31 @@ def main():
                 res[key + "/tp_logits"] = logits
                 res[key + "/tp_x"] = x
             m.close()
+        if name == "gqa_q4k":
+            # batched prompt passes on the sharded model (partial products summed over the group by an all-reduce),
+            # for both exchanges of the token loop that follows them
+            long_prompt = synth.prompt(30, cfg["vocab_size"], seed=6)
+            for direct in (True, False):
+                m = Llama2(c, tp_rank=rank, tp_size=world)
+                m.load_tensors(t)
+                tp.attach(m, comm, direct=direct)
+                m.set_prefill(True)
+                toks = m.decode(long_prompt, 16)
+                assert m.prefill_positions() == 29, m.prefill_positions()   # 3 full passes and one of five positions
+                assert _lib.load().wgb_device_status() == _lib.OK
+                logits = m.logits().cpu().numpy()
+                torch.cuda.synchronize()
+                dist.barrier()
+                if rank == 0:
+                    res[f"{name}/prefill{int(direct)}/tp_tokens"] = toks
+                    res[f"{name}/prefill{int(direct)}/tp_logits"] = logits
+                m.close()
+            if rank == 0:
+                m = Llama2(c)
+                m.load_tensors(t)
+                res[f"{name}/prefill/ref_tokens"] = m.decode(long_prompt, 16)
+                res[f"{name}/prefill/ref_logits"] = m.logits().cpu().numpy()
+                m.close()
         if rank == 0:
             m = Llama2(c)
             m.load_tensors(t)

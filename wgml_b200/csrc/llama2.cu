@@ -90,6 +90,7 @@ struct wgb_llama2 {
         uint8_t *img6 = nullptr;             // Q6_K image of the widest input
         float *x = nullptr, *xn = nullptr, *q = nullptr, *xb = nullptr, *h = nullptr;   // [PF_TOK][dim | q_dim | hidden]
         float *part[3] = {};                 // product slices: [PF_MAX_SPLIT][PF_TOK][max(dim, q_dim, hidden)]
+        float *red = nullptr;                // tensor parallel: [PF_TOK][dim], a rank's partial product summed over the group
         size_t positions = 0;                // prompt positions that went through it, over all decode calls
     } pf;
 };
@@ -406,7 +407,7 @@ void prefill_free(wgb_llama2 *m)
     m->pf.tiles.clear();
     uint8_t *imgs[] = { m->pf.img_dim, m->pf.img_q, m->pf.img_hidden, m->pf.img6 };
     for (uint8_t *b : imgs) if (b) cudaFree(b);
-    float *bufs[] = { m->pf.x, m->pf.xn, m->pf.q, m->pf.xb, m->pf.h, m->pf.part[0], m->pf.part[1], m->pf.part[2] };
+    float *bufs[] = { m->pf.x, m->pf.xn, m->pf.q, m->pf.xb, m->pf.h, m->pf.part[0], m->pf.part[1], m->pf.part[2], m->pf.red };
     for (float *b : bufs) if (b) cudaFree(b);
     m->pf = wgb_llama2::Prefill();
 }
@@ -451,6 +452,19 @@ int prefill_pass(wgb_llama2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32
     for (uint32_t t = 0; t < ntok; t++)
         if ((rc = launch_embed(m->token_embd->view, nullptr, d_tokens + t, m->scalars + 1, pf.x + (size_t)t * dim, s))) return rc;
     const size_t cache_stride = (size_t)c.seq_len * kv_dim;
+    // Tensor parallel: a rank's attn_output / ffn_down products are partial sums over the group (column slices of
+    // the matrices); their slices are added up locally, summed over the ranks (one all-reduce of [ntok][dim] per
+    // product) and handed on as a single slice.  Every rank then adds the same sum to its copy of x.
+    auto across_ranks = [&](const float **part, uint32_t *nsplit) -> int {
+        if (m->tp_size == 1) return WGB_OK;
+        WGB_CUDA(cudaMemsetAsync(pf.red, 0, (size_t)PF_TOK * dim * sizeof(float), s));
+        int r = launch_prefill_norm_image(pf.red, dim, *part, *nsplit, dim, nullptr, 0.0f, dim, ntok, nullptr, nullptr, 0, s);
+        if (r) return r;
+        if ((r = wgb_comm_all_reduce_sum((wgb_comm *)m->comm, pf.red, pf.red, (size_t)PF_TOK * dim, s))) return r;
+        *part = pf.red;
+        *nsplit = 1;
+        return WGB_OK;
+    };
     const float *pending = nullptr;   // slices of the last layer's ffn_down, folded into x by the next norm
     uint32_t pending_split = 0;
     for (uint32_t l = 0; l < c.n_layers; l++) {
@@ -478,8 +492,9 @@ int prefill_pass(wgb_llama2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32
             return rc;
         if ((rc = launch_prefill_norm_image(pf.xb, q_dim, nullptr, 0, 0, nullptr, 0.0f, q_dim, ntok, pf.img_q, nullptr, 0, s))) return rc;
         if ((rc = prefill_product(m, l, WGB_L_ATTN_OUTPUT, pf.img_q, pf.xb, q_dim, ntok, pf.part[0], dim, &no, s))) return rc;
-        if ((rc = launch_prefill_norm_image(pf.x, dim, pf.part[0], no, dim, w.v[WGB_L_FFN_NORM], c.rms_norm_eps, dim, ntok, pf.img_dim, pf.xn, dim,
-                                            s)))
+        const float *opart = pf.part[0];
+        if ((rc = across_ranks(&opart, &no))) return rc;
+        if ((rc = launch_prefill_norm_image(pf.x, dim, opart, no, dim, w.v[WGB_L_FFN_NORM], c.rms_norm_eps, dim, ntok, pf.img_dim, pf.xn, dim, s)))
             return rc;
         if ((rc = prefill_product(m, l, WGB_L_FFN_GATE, pf.img_dim, pf.xn, dim, ntok, pf.part[0], hidden, &ng, s))) return rc;
         if ((rc = prefill_product(m, l, WGB_L_FFN_UP, pf.img_dim, pf.xn, dim, ntok, pf.part[1], hidden, &nu, s))) return rc;
@@ -487,6 +502,7 @@ int prefill_pass(wgb_llama2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32
         if ((rc = prefill_product(m, l, WGB_L_FFN_DOWN, pf.img_hidden, pf.h, hidden, ntok, pf.part[2], dim, &nd, s))) return rc;
         pending = pf.part[2];
         pending_split = nd;
+        if ((rc = across_ranks(&pending, &pending_split))) return rc;
     }
     // leave the residual stream of the pass complete (nothing reads it; it keeps wgb_llama2_x meaningful for tests)
     if ((rc = launch_prefill_norm_image(pf.x, dim, pending, pending_split, dim, nullptr, 0.0f, dim, ntok, nullptr, nullptr, 0, s))) return rc;
@@ -1155,7 +1171,9 @@ WGB_EXPORT int wgb_llama2_set_prefill(wgb_llama2 *m, int enable)
         return WGB_OK;
     }
     if (m->pf.enabled) return WGB_OK;
-    if (m->tp_size != 1) return fail(WGB_ERR_UNSUPPORTED, "batched prefill is built for one GPU per model; this model is rank %d of %d", m->tp_rank, m->tp_size);
+    if (m->tp_size != 1 && !m->comm)
+        return fail(WGB_ERR_UNSUPPORTED, "batched prefill of a tensor-parallel model sums its partial products with the communicator: call wgb_llama2_set_comm first (rank %d of %d)",
+                    m->tp_rank, m->tp_size);
     int rc = check_complete(m);
     if (rc) return rc;
     if ((rc = gemv_global_init())) return rc;
@@ -1189,6 +1207,7 @@ WGB_EXPORT int wgb_llama2_set_prefill(wgb_llama2 *m, int enable)
         return bail(rc);
     for (int i = 0; i < 3; i++)
         if ((rc = dalloc(&pf.part[i], (size_t)PF_MAX_SPLIT * PF_TOK * widest))) return bail(rc);
+    if (m->tp_size > 1 && (rc = dalloc(&pf.red, (size_t)PF_TOK * c.dim))) return bail(rc);
     WGB_CUDA(cudaDeviceSynchronize());
     pf.enabled = true;
     return WGB_OK;
