@@ -294,8 +294,24 @@ def run_b200(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    # prefill: the prompt goes through the decode path token by token, as the reference does
-    toks = model.decode(prompt, 0) if prompt_len > 1 else np.zeros(0, np.uint32)
+    # The prompt: position by position through the token loop on one GPU, as the reference does (the batched passes
+    # are measured separately below); tensor-parallel runs send it through the batched passes, which are what a
+    # 4096-token prompt is for, and report their rate beside the decode figures.
+    tp_prefill = None
+    if world > 1 and not args.no_prefill and prompt_len >= 16:
+        model.set_prefill(True)
+        barrier()
+        t0 = time.perf_counter()
+        toks = model.decode(prompt, 0)
+        barrier()
+        dt = time.perf_counter() - t0
+        tp_prefill = {"prompt_positions": prompt_len - 1, "positions_in_batched_passes": model.prefill_positions(),
+                      "batched": {"ms": dt * 1e3, "tok_s": (prompt_len - 1) / dt},
+                      "how": "wgb_llama2_decode(prompt, n_gen = 0) after wgb_llama2_set_prefill(1), wall clock between barriers; "
+                             "partial products summed over the ranks by NCCL all-reduce"}
+        model.set_prefill(False)
+    else:
+        toks = model.decode(prompt, 0) if prompt_len > 1 else np.zeros(0, np.uint32)
     pos = prompt_len - 1
     last = np.array([prompt[-1]], np.uint32)
     # warm-up decode steps (also builds the n_prompt=1 graph)
@@ -389,6 +405,8 @@ def run_b200(args):
         "kernels_per_token": int(model.kernels_per_token()),
         "clocks": clocks.summary(), "roofline": roofline, "breakdown": classes,
     }
+    if tp_prefill:
+        line["prefill"] = tp_prefill
     if rank == 0 and world == 1 and not args.no_prefill and prompt_len >= 16:
         # prompt throughput: the same prompt position by position through the token loop (what the reference does) and
         # through the batched passes (eight positions per pass, Q4_K products on the tensor cores)
