@@ -11,12 +11,13 @@
 // Matrix product (gemm_q4k_tc_kernel).  Weights tile-major as for the single-vector tensor-core kernel
 // (gemv_tc.cu).  Work item = (tile of 128 rows, slice of the super-block columns); an item's units (one
 // super-block column each: 18 KB of weights and the 8.5 KB slice of the activation image that goes with it)
-// stream through a ring of shared-memory stages.  Sixteen worker warps unpack the nibbles of a unit into the A
-// operand (128 x 256 bytes, 128-byte swizzle), one thread issues eight MMAs per unit (one per 32-column
-// sub-block; M = 128, N = 32: rows 8 d + t of the B operand hold digit d of position t, rows 24..31 are zero,
-// K = 32) into 256 columns of tensor memory (two such sets alternate), and the workers read the sums back
+// stream through a ring of shared-memory stages.  Eight warps unpack the nibbles of a unit into the A operand
+// (128 x 256 bytes, 128-byte swizzle), one thread issues eight MMAs per unit (one per 32-column sub-block;
+// M = 128, N = 32: rows 8 d + t of the B operand hold digit d of position t, rows 24..31 are zero, K = 32) into
+// 256 columns of tensor memory (two such sets alternate), and eight other warps read the sums back
 // (tcgen05.ld), apply digit weights, exponents, six-bit scales and the min term in FP32 and keep one running
-// sum per position.  Each item leaves its partial rows in out[slice][position][row]; whoever consumes the
+// sum per position.  The three roles only meet through barriers, so the unpacking of unit n + 1, the MMAs of
+// unit n and the finishing of unit n - 1 overlap.  Each item leaves its partial rows in out[slice][position][row]; whoever consumes the
 // product adds the slices in a fixed order, so results do not depend on the schedule.
 // Every wait is bounded in time; after an expired wait the loops keep their shape (all hardware barriers are
 // still met) but do nothing, and a code is left in the device's status word.
@@ -31,8 +32,9 @@ constexpr uint32_t TB_IMG_DIGITS = 16 * 4 * 128;                          // 16 
 constexpr uint32_t TB_IMG_BYTES = TB_IMG_DIGITS + 2 * 8 * PF_TOK * 4;     // + exponents and sums [group][position]
 constexpr uint32_t TB_STAGE = TB_IMG_BYTES + TC_UNIT_BYTES;
 constexpr uint32_t TB_RING = 4;
-constexpr uint32_t TB_WORKER_WARPS = 16;
-constexpr uint32_t TB_NT = 32 * (2 + TB_WORKER_WARPS);
+constexpr uint32_t TB_UNPACK_WARPS = 8;                                   // build the A operand of unit n
+constexpr uint32_t TB_FINISH_WARPS = 8;                                   // read unit n - 1's sums and apply scales
+constexpr uint32_t TB_NT = 32 * (2 + TB_UNPACK_WARPS + TB_FINISH_WARPS);
 constexpr uint32_t TB_TMEM_COLS = 512;                                    // two sets of eight 32-column results
 constexpr uint32_t TB_OFF_A = 0;                                          // two operand buffers (units alternate)
 constexpr uint32_t TB_OFF_RING = TB_OFF_A + 2 * TC_A_BYTES;
@@ -63,8 +65,8 @@ struct TbArgs {
 __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_constant__ TbArgs a)
 {
     extern __shared__ uint8_t tb_smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * TB_RING + 2];
-    __shared__ float rowpart[4][PF_TOK][TC_TILE_ROWS];
+    __shared__ __align__(8) unsigned long long bars[2 * TB_RING + 4];
+    __shared__ float rowpart[2][PF_TOK][TC_TILE_ROWS];
     __shared__ uint32_t tmem_base_slot;
     __shared__ uint32_t dead_flag;
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)tb_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -75,7 +77,8 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
     const uint32_t nkb = a.nkb, nsplit = a.nsplit, nitems = (a.nrows / TC_TILE_ROWS) * nsplit;
     auto bar_full = [&](uint32_t s) { return smem_addr(&bars[s]); };
     auto bar_empty = [&](uint32_t s) { return smem_addr(&bars[TB_RING + s]); };
-    auto bar_done = [&](uint32_t u) { return smem_addr(&bars[2 * TB_RING + u]); };
+    auto bar_done = [&](uint32_t u) { return smem_addr(&bars[2 * TB_RING + u]); };        // the unit's MMAs have completed
+    auto bar_tfree = [&](uint32_t u) { return smem_addr(&bars[2 * TB_RING + 2 + u]); };   // its accumulators have been read
     auto stage = [&](uint32_t s) { return smem_addr(smem + TB_OFF_RING) + s * TB_STAGE; };
     uint32_t total = 0;
     for (uint32_t i = blockIdx.x; i < nitems; i += gridDim.x) {
@@ -87,10 +90,12 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
         dead_flag = 0;
         for (uint32_t s = 0; s < TB_RING; s++) {
             mbar_init(bar_full(s), 1);
-            mbar_init(bar_empty(s), 32 * TB_WORKER_WARPS);
+            mbar_init(bar_empty(s), 32 * (TB_UNPACK_WARPS + TB_FINISH_WARPS));
         }
-        mbar_init(bar_done(0), 1);
-        mbar_init(bar_done(1), 1);
+        for (uint32_t u = 0; u < 2; u++) {
+            mbar_init(bar_done(u), 1);
+            mbar_init(bar_tfree(u), 32 * TB_FINISH_WARPS);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -122,94 +127,116 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issue ------------------------------
-        // Unit n is complete in operand buffer n % 2 once all worker threads have arrived at hardware barrier
-        // 3 + n % 2 (they do not wait there); this warp waits there, then one thread issues the unit's eight
-        // MMAs into accumulator columns 256 (n % 2) ... and commits them to the unit's barrier.  The B operand
-        // is read in place from the unit's stage (K-major, no swizzle: core matrices of eight positions x 16
-        // columns, the four row groups of a K-core 128 bytes apart, K-cores 512 bytes apart).
+        // Unit n is complete in operand buffer n % 2 once all unpacking threads have arrived at hardware barrier
+        // 3 + n % 2 (they do not wait there); this warp waits there, then one thread -- once the accumulators of
+        // unit n - 2 have been read -- issues the unit's eight MMAs into accumulator columns 256 (n % 2) ... and
+        // commits them to the unit's barrier.  The B operand is read in place from the unit's stage (K-major, no
+        // swizzle: core matrices of eight positions x 16 columns, the four row groups of a K-core 128 bytes apart,
+        // K-cores 512 bytes apart).
         const uint32_t idesc = tc_idesc(32);
         const uint64_t adesc0 = tc_smem_desc_sw128(smem_addr(smem + TB_OFF_A), 1024);
+        bool ok = true;
         for (uint32_t n = 0; n < total; n++) {
             const uint32_t u = n & 1, s = n % TB_RING;
-            if (u) asm volatile("bar.sync 4, %0;" ::"n"(32 * TB_WORKER_WARPS + 32) : "memory");
-            else asm volatile("bar.sync 3, %0;" ::"n"(32 * TB_WORKER_WARPS + 32) : "memory");
-            if (lane == 0 && !*dead && tc_wait(bar_full(s), (n / TB_RING) & 1, dead, a.err, 22)) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t ad = adesc0 + (uint64_t)(u * (TC_A_BYTES >> 4));
-                const uint64_t bd = tc_smem_desc(stage(s), 512, 128);
-                const uint32_t dcol = tmem_base + u * 256;
+            if (u) asm volatile("bar.sync 4, %0;" ::"n"(32 * TB_UNPACK_WARPS + 32) : "memory");
+            else asm volatile("bar.sync 3, %0;" ::"n"(32 * TB_UNPACK_WARPS + 32) : "memory");
+            if (lane == 0 && ok && !*dead) {
+                ok = tc_wait(bar_full(s), (n / TB_RING) & 1, dead, a.err, 22);
+                if (ok && n >= 2) ok = tc_wait(bar_tfree(u), ((n - 2) >> 1) & 1, dead, a.err, 25);
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t ad = adesc0 + (uint64_t)(u * (TC_A_BYTES >> 4));
+                    const uint64_t bd = tc_smem_desc(stage(s), 512, 128);
+                    const uint32_t dcol = tmem_base + u * 256;
 #pragma unroll
-                for (uint32_t j = 0; j < 8; j++)
-                    tc_mma(dcol + 32 * j, ad + (uint64_t)(((j >> 2) * 16384 + (j & 3) * 32) >> 4), bd + (uint64_t)((j * 1024) >> 4), idesc);
-                tc_commit(bar_done(u));
+                    for (uint32_t j = 0; j < 8; j++)
+                        tc_mma(dcol + 32 * j, ad + (uint64_t)(((j >> 2) * 16384 + (j & 3) * 32) >> 4), bd + (uint64_t)((j * 1024) >> 4), idesc);
+                    tc_commit(bar_done(u));
+                }
             }
             __syncwarp();
         }
-    } else {
-        // ------------------------------ workers ------------------------------
-        // Thread (quarter, lane, sub): row r = 32 quarter + lane of the tile (the quarter of tensor memory its
-        // warp may read), 32-byte chunk `sub` of that row's nibbles (sub-blocks 2 sub and 2 sub + 1).
-        const uint32_t w = warp - 2, sub = w / 4, quarter = warp & 3, r = quarter * 32 + lane;
+    } else if (warp < 2 + TB_UNPACK_WARPS) {
+        // ------------------------------ unpacking ------------------------------
+        // Thread (quarter, lane, half): row r = 32 quarter + lane of the tile, 32-byte chunks 2 half and 2 half + 1
+        // of that row's nibbles (chunk c = sub-blocks 2 c and 2 c + 1).  Unit n goes into operand buffer n % 2 as
+        // soon as its stage is full and the MMAs of unit n - 2 have read the buffer; the thread then tells the
+        // MMA warp (an arrival at a hardware barrier, without waiting) and is done with the stage.
+        const uint32_t half = (warp - 2) >> 2, r = (warp & 3) * 32 + lane;
         const uint32_t arow = smem_addr(smem + TB_OFF_A) + (r >> 3) * 1024 + (r & 7) * 128;
-        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
-        float rowacc[PF_TOK];
-#pragma unroll
-        for (uint32_t t = 0; t < PF_TOK; t++) rowacc[t] = 0.0f;
         bool ok = true;
-        UnitWalk fin;   // the unit being finished (one step behind the one being unpacked)
-        fin.set(blockIdx.x, nsplit, nkb);
-        // Step n unpacks unit n into operand buffer n % 2, tells the MMA warp (an arrival at a hardware barrier,
-        // without waiting), and goes on to finish unit n - 1, whose MMAs were issued a step ago.  Buffer n % 2 is
-        // free again by then: finishing unit n - 2 waited for its MMAs.  After an expired wait (`ok` false,
-        // warp-uniform) the loop keeps its shape, so that every thread still meets every hardware barrier.
-        for (uint32_t n = 0; n <= total; n++) {
-            if (n < total) {
-                const uint32_t slot = n % TB_RING, u = n & 1;
-                if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_full(slot), (n / TB_RING) & 1, dead, a.err, 23));
-                const uint32_t raw = stage(slot) + TB_IMG_BYTES + r * 144;
-                if (ok) {
-                    // nibbles -> bytes: low nibbles are sub-block 2 sub, high nibbles (left as 16 * code) sub-block
-                    // 2 sub + 1; sub-block j lies in K panel j / 4 (16 KB) at bytes 32 (j % 4) .. + 31 of the row,
-                    // 16-byte chunks swizzled by the row index
+        // After an expired wait (`ok` false, warp-uniform) the loop keeps its shape, so that every thread still meets
+        // every hardware barrier, but waits for nothing and computes nothing.
+        for (uint32_t n = 0; n < total; n++) {
+            const uint32_t slot = n % TB_RING, u = n & 1;
+            if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_full(slot), (n / TB_RING) & 1, dead, a.err, 23));
+            if (ok && n >= 2) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), ((n - 2) >> 1) & 1, dead, a.err, 26));
+            const uint32_t raw = stage(slot) + TB_IMG_BYTES + r * 144;
+            if (ok) {
+                // nibbles -> bytes: low nibbles are sub-block 2 c, high nibbles (left as 16 * code) sub-block 2 c + 1;
+                // sub-block j lies in K panel j / 4 (16 KB) at bytes 32 (j % 4) .. + 31 of the row, 16-byte chunks
+                // swizzled by the row index
+#pragma unroll
+                for (uint32_t cc = 0; cc < 2; cc++) {
+                    const uint32_t c = 2 * half + cc;
 #pragma unroll
                     for (uint32_t core = 0; core < 2; core++) {
-                        const uint4 q = lds128(raw + 16 + 32 * sub + 16 * core);
-                        const uint32_t jl = 2 * sub, jh = 2 * sub + 1;
+                        const uint4 q = lds128(raw + 16 + 32 * c + 16 * core);
+                        const uint32_t jl = 2 * c, jh = 2 * c + 1;
                         sts128(arow + u * TC_A_BYTES + (jl >> 2) * 16384 + (((2 * (jl & 3) + core) ^ (r & 7)) << 4),
                                q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
                         sts128(arow + u * TC_A_BYTES + (jh >> 2) * 16384 + (((2 * (jh & 3) + core) ^ (r & 7)) << 4),
                                q.x & 0xf0f0f0f0u, q.y & 0xf0f0f0f0u, q.z & 0xf0f0f0f0u, q.w & 0xf0f0f0f0u);
                     }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                if (u) asm volatile("bar.arrive 4, %0;" ::"n"(32 * TB_WORKER_WARPS + 32) : "memory");
-                else asm volatile("bar.arrive 3, %0;" ::"n"(32 * TB_WORKER_WARPS + 32) : "memory");
             }
-            if (n >= 1) {
-                const uint32_t m = n - 1, slot = m % TB_RING, u = m & 1;
-                const uint32_t img = stage(slot), raw = img + TB_IMG_BYTES + r * 144;
-                const uint4 hdr = lds128(raw);
-                const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, m_lo = hdr.z & 0x3f3f3f3fu;
-                const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
-                const uint32_t m_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
-                const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-                // six-bit scales and mins of sub-blocks 2 sub, 2 sub + 1 in the low bytes of a word each
-                const uint32_t sh = (sub & 1) * 16;
-                const uint32_t scw = (sub < 2 ? sc_lo : sc_hi) >> sh, mw = (sub < 2 ? m_lo : m_hi) >> sh;
-                if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), (m >> 1) & 1, dead, a.err, 24));
-                if (ok) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    // all six loads of the thread's two sub-blocks are issued before the one wait; the exponents and
-                    // sums of the two groups are fetched from the stage meanwhile
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (u) asm volatile("bar.arrive 4, %0;" ::"n"(32 * TB_UNPACK_WARPS + 32) : "memory");
+            else asm volatile("bar.arrive 3, %0;" ::"n"(32 * TB_UNPACK_WARPS + 32) : "memory");
+            mbar_arrive(bar_empty(slot));   // the stage is free once the finishing threads have arrived too
+        }
+    } else {
+        // ------------------------------ finishing ------------------------------
+        // Thread (quarter, lane, half): row r = 32 quarter + lane (the quarter of tensor memory its warp may read),
+        // sub-blocks 4 half .. 4 half + 3 of the unit.  It reads the row's digit sums of those sub-blocks for the
+        // eight positions, frees the accumulators for unit m + 2, and applies scales, exponents and mins.
+        const uint32_t half = (warp - 2 - TB_UNPACK_WARPS) >> 2, quarter = warp & 3, r = quarter * 32 + lane;
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+        float rowacc[PF_TOK];
+#pragma unroll
+        for (uint32_t t = 0; t < PF_TOK; t++) rowacc[t] = 0.0f;
+        bool ok = true;
+        UnitWalk fin;
+        fin.set(blockIdx.x, nsplit, nkb);
+        for (uint32_t m = 0; m < total; m++) {
+            const uint32_t slot = m % TB_RING, u = m & 1;
+            if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_full(slot), (m / TB_RING) & 1, dead, a.err, 27));
+            const uint32_t img = stage(slot), raw = img + TB_IMG_BYTES + r * 144;
+            uint4 hdr = make_uint4(0u, 0u, 0u, 0u);
+            if (ok) hdr = lds128(raw);
+            const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, m_lo = hdr.z & 0x3f3f3f3fu;
+            const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
+            const uint32_t m_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
+            const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+            // six-bit scales and mins of sub-blocks 4 half .. 4 half + 3, one per byte
+            const uint32_t scw = half ? sc_hi : sc_lo, mw = half ? m_hi : m_lo;
+            if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), (m >> 1) & 1, dead, a.err, 24));
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (uint32_t cc = 0; cc < 2; cc++) {
+                    // sub-blocks j0 = 4 half + 2 cc and j0 + 1: their six loads are issued before the one wait; the
+                    // exponents and sums of the two groups are fetched from the stage meanwhile
+                    const uint32_t j0 = 4 * half + 2 * cc;
                     int d[2][3][8];
 #pragma unroll
                     for (uint32_t q = 0; q < 2; q++)
 #pragma unroll
-                        for (uint32_t dg = 0; dg < 3; dg++) tc_ld8(taddr + u * 256 + 32 * (2 * sub + q) + 8 * dg, d[q][dg]);
+                        for (uint32_t dg = 0; dg < 3; dg++) tc_ld8(taddr + u * 256 + 32 * (j0 + q) + 8 * dg, d[q][dg]);
                     float ev[2][8], sv[2][8];
 #pragma unroll
                     for (uint32_t q = 0; q < 2; q++) {
-                        const uint32_t eo = img + TB_IMG_DIGITS + (2 * sub + q) * PF_TOK * 4;   // one float per position
+                        const uint32_t eo = img + TB_IMG_DIGITS + (j0 + q) * PF_TOK * 4;   // one float per position
                         const uint4 e0 = lds128(eo), e1 = lds128(eo + 16), s0 = lds128(eo + 8 * PF_TOK * 4), s1 = lds128(eo + 8 * PF_TOK * 4 + 16);
                         ev[q][0] = __uint_as_float(e0.x); ev[q][1] = __uint_as_float(e0.y); ev[q][2] = __uint_as_float(e0.z); ev[q][3] = __uint_as_float(e0.w);
                         ev[q][4] = __uint_as_float(e1.x); ev[q][5] = __uint_as_float(e1.y); ev[q][6] = __uint_as_float(e1.z); ev[q][7] = __uint_as_float(e1.w);
@@ -217,9 +244,14 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                         sv[q][4] = __uint_as_float(s1.x); sv[q][5] = __uint_as_float(s1.y); sv[q][6] = __uint_as_float(s1.z); sv[q][7] = __uint_as_float(s1.w);
                     }
                     // the block's d and dmin folded into the sub-blocks' scales and mins once per unit
-                    const float sc0 = dm.x * byte2f(scw, 0), sc1 = dm.x * byte2f(scw, 1), mn0 = -dm.y * byte2f(mw, 0), mn1 = -dm.y * byte2f(mw, 1);
+                    const float sc0 = dm.x * byte2f(scw, 2 * cc), sc1 = dm.x * byte2f(scw, 2 * cc + 1);
+                    const float mn0 = -dm.y * byte2f(mw, 2 * cc), mn1 = -dm.y * byte2f(mw, 2 * cc + 1);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    if (cc == 1) {
+                        // every accumulator column this thread reads is in registers: unit m + 2 may overwrite them
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        mbar_arrive(bar_tfree(u));
+                    }
 #pragma unroll
                     for (uint32_t t = 0; t < PF_TOK; t++) {
                         // the two low digit sums are joined in the integer unit (|.| < 2^31) and take one conversion;
@@ -230,29 +262,27 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                         rowacc[t] += fmaf(f0, sc0 * ev[0][t], fmaf(f1, sc1 * ev[1][t], mins));
                     }
                 }
-                mbar_arrive(bar_empty(slot));
-                if (fin.last()) {
-                    // the rows' totals over this item's columns: the four threads of a row, in a fixed order
-#pragma unroll
-                    for (uint32_t t = 0; t < PF_TOK; t++) {
-                        rowpart[sub][t][r] = rowacc[t];
-                        rowacc[t] = 0.0f;
-                    }
-                    asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_WORKER_WARPS) : "memory");
-                    if (ok) {
-#pragma unroll
-                        for (uint32_t tt = 0; tt < 2; tt++) {
-                            const uint32_t t = 2 * sub + tt;
-                            if (t < a.ntok) {
-                                const float v = ((rowpart[0][t][r] + rowpart[1][t][r]) + rowpart[2][t][r]) + rowpart[3][t][r];
-                                a.out[((size_t)fin.sp * PF_TOK + t) * a.out_stride + (size_t)fin.tile * TC_TILE_ROWS + r] = v;
-                            }
-                        }
-                    }
-                    asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_WORKER_WARPS) : "memory");
-                }
-                fin.next(nsplit, nkb, gridDim.x);
             }
+            mbar_arrive(bar_empty(slot));
+            if (fin.last()) {
+                // the rows' totals over this item's columns: the two threads of a row, in a fixed order
+#pragma unroll
+                for (uint32_t t = 0; t < PF_TOK; t++) {
+                    rowpart[half][t][r] = rowacc[t];
+                    rowacc[t] = 0.0f;
+                }
+                asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_FINISH_WARPS) : "memory");
+                if (ok) {
+#pragma unroll
+                    for (uint32_t tt = 0; tt < PF_TOK / 2; tt++) {
+                        const uint32_t t = (PF_TOK / 2) * half + tt;
+                        if (t < a.ntok)
+                            a.out[((size_t)fin.sp * PF_TOK + t) * a.out_stride + (size_t)fin.tile * TC_TILE_ROWS + r] = rowpart[0][t][r] + rowpart[1][t][r];
+                    }
+                }
+                asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_FINISH_WARPS) : "memory");
+            }
+            fin.next(nsplit, nkb, gridDim.x);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
