@@ -34,7 +34,9 @@ constexpr uint32_t TB_STAGE = TB_IMG_BYTES + TC_UNIT_BYTES;
 constexpr uint32_t TB_RING = 4;
 constexpr uint32_t TB_UNPACK_WARPS = 8;                                   // build the A operand of unit n
 constexpr uint32_t TB_FINISH_WARPS = 8;                                   // read unit n - 1's sums and apply scales
-constexpr uint32_t TB_NT = 32 * (2 + TB_UNPACK_WARPS + TB_FINISH_WARPS);
+constexpr uint32_t TB_NT = 32 * (2 + TB_UNPACK_WARPS + TB_FINISH_WARPS);     // 4 + 16 and 8 + 16 warps measured 4-8 % slower
+static_assert(16 % TB_UNPACK_WARPS == 0 && TB_UNPACK_WARPS % 4 == 0 && 32 % TB_FINISH_WARPS == 0 && TB_FINISH_WARPS % 4 == 0 && TB_FINISH_WARPS <= 16,
+              "whole chunks per unpacking thread, whole sub-block pairs per finishing thread, four warps per quarter of the rows");
 constexpr uint32_t TB_TMEM_COLS = 512;                                    // two sets of eight 32-column results
 constexpr uint32_t TB_OFF_A = 0;                                          // two operand buffers (units alternate)
 constexpr uint32_t TB_OFF_RING = TB_OFF_A + 2 * TC_A_BYTES;
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
 {
     extern __shared__ uint8_t tb_smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * TB_RING + 4];
-    __shared__ float rowpart[2][PF_TOK][TC_TILE_ROWS];
+    __shared__ float rowpart[TB_FINISH_WARPS / 4][PF_TOK][TC_TILE_ROWS];
     __shared__ uint32_t tmem_base_slot;
     __shared__ uint32_t dead_flag;
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)tb_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -177,8 +179,8 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                 // sub-block j lies in K panel j / 4 (16 KB) at bytes 32 (j % 4) .. + 31 of the row, 16-byte chunks
                 // swizzled by the row index
 #pragma unroll
-                for (uint32_t cc = 0; cc < 2; cc++) {
-                    const uint32_t c = 2 * half + cc;
+                for (uint32_t cc = 0; cc < 16 / TB_UNPACK_WARPS; cc++) {
+                    const uint32_t c = (16 / TB_UNPACK_WARPS) * half + cc;
 #pragma unroll
                     for (uint32_t core = 0; core < 2; core++) {
                         const uint4 q = lds128(raw + 16 + 32 * c + 16 * core);
@@ -218,16 +220,17 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
             const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u);
             const uint32_t m_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);
             const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
-            // six-bit scales and mins of sub-blocks 4 half .. 4 half + 3, one per byte
-            const uint32_t scw = half ? sc_hi : sc_lo, mw = half ? m_hi : m_lo;
             if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), (m >> 1) & 1, dead, a.err, 24));
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                constexpr uint32_t SPT = 32 / TB_FINISH_WARPS;   // sub-blocks per thread
 #pragma unroll
-                for (uint32_t cc = 0; cc < 2; cc++) {
-                    // sub-blocks j0 = 4 half + 2 cc and j0 + 1: their six loads are issued before the one wait; the
+                for (uint32_t cc = 0; cc < SPT / 2; cc++) {
+                    // sub-blocks j0 = SPT half + 2 cc and j0 + 1: their six loads are issued before the one wait; the
                     // exponents and sums of the two groups are fetched from the stage meanwhile
-                    const uint32_t j0 = 4 * half + 2 * cc;
+                    const uint32_t j0 = SPT * half + 2 * cc;
+                    // six-bit scales and mins of sub-blocks j0, j0 + 1 in the two low bytes
+                    const uint32_t scw = ((j0 & 4) ? sc_hi : sc_lo) >> (8 * (j0 & 3)), mw = ((j0 & 4) ? m_hi : m_lo) >> (8 * (j0 & 3));
                     int d[2][3][8];
 #pragma unroll
                     for (uint32_t q = 0; q < 2; q++)
@@ -244,10 +247,10 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                         sv[q][4] = __uint_as_float(s1.x); sv[q][5] = __uint_as_float(s1.y); sv[q][6] = __uint_as_float(s1.z); sv[q][7] = __uint_as_float(s1.w);
                     }
                     // the block's d and dmin folded into the sub-blocks' scales and mins once per unit
-                    const float sc0 = dm.x * byte2f(scw, 2 * cc), sc1 = dm.x * byte2f(scw, 2 * cc + 1);
-                    const float mn0 = -dm.y * byte2f(mw, 2 * cc), mn1 = -dm.y * byte2f(mw, 2 * cc + 1);
+                    const float sc0 = dm.x * byte2f(scw, 0), sc1 = dm.x * byte2f(scw, 1);
+                    const float mn0 = -dm.y * byte2f(mw, 0), mn1 = -dm.y * byte2f(mw, 1);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (cc == 1) {
+                    if (cc == SPT / 2 - 1) {
                         // every accumulator column this thread reads is in registers: unit m + 2 may overwrite them
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                         mbar_arrive(bar_tfree(u));
@@ -273,11 +276,14 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                 }
                 asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_FINISH_WARPS) : "memory");
                 if (ok) {
+                    constexpr uint32_t NP = TB_FINISH_WARPS / 4, TPT = PF_TOK / NP;   // parts of a row, positions per thread
 #pragma unroll
-                    for (uint32_t tt = 0; tt < PF_TOK / 2; tt++) {
-                        const uint32_t t = (PF_TOK / 2) * half + tt;
-                        if (t < a.ntok)
-                            a.out[((size_t)fin.sp * PF_TOK + t) * a.out_stride + (size_t)fin.tile * TC_TILE_ROWS + r] = rowpart[0][t][r] + rowpart[1][t][r];
+                    for (uint32_t tt = 0; tt < TPT; tt++) {
+                        const uint32_t t = TPT * half + tt;
+                        float v = rowpart[0][t][r];
+#pragma unroll
+                        for (uint32_t q = 1; q < NP; q++) v += rowpart[q][t][r];
+                        if (t < a.ntok) a.out[((size_t)fin.sp * PF_TOK + t) * a.out_stride + (size_t)fin.tile * TC_TILE_ROWS + r] = v;
                     }
                 }
                 asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_FINISH_WARPS) : "memory");
