@@ -173,6 +173,9 @@ uint32_t prefill_gemm_splits(uint32_t nrows, uint32_t K);
 // `ntok` vectors whose image is `image`, the columns cut into `nsplit` slices.
 int launch_gemm_q4k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, const uint8_t *image, uint32_t ntok, float *out,
                           uint32_t out_stride, uint32_t nsplit, cudaStream_t stream);
+// The same for up to three matrices that share the input (q / k / v, gate / up) in one launch; `nsplit` is common.
+int launch_gemm_q4k_tiles_multi(uint32_t nmat, const uint8_t *const *w_tiles, const uint32_t *nrows, uint32_t K, const uint8_t *image,
+                                uint32_t ntok, float *const *out, const uint32_t *out_stride, uint32_t nsplit, cudaStream_t stream);
 // x[t] (+= the slices of `part` when given, written back); then optionally RMS-normalised with norm_w; the image
 // of the result and, with xn, the values.  With neither image nor xn only x is updated.
 int launch_prefill_norm_image(float *x, uint32_t x_stride, const float *part, uint32_t nsplit, uint32_t part_stride, const float *norm_w,

@@ -438,6 +438,34 @@ int prefill_product(wgb_llama2 *m, uint32_t layer, int which, const uint8_t *ima
     return WGB_OK;
 }
 
+// Products of several matrices of a layer with the same input (q / k / v; gate / up), product i as slices in out[i]:
+// one launch when all of them have Q4_K tile-major copies, one product after the other otherwise.
+int prefill_products(wgb_llama2 *m, uint32_t layer, const int *which, uint32_t n, const uint8_t *image, const float *xf, uint32_t xf_stride,
+                     uint32_t ntok, float *const *out, const uint32_t *stride, uint32_t *nsplit, cudaStream_t s)
+{
+    bool together = n > 1;
+    uint32_t rows[3], total_rows = 0;
+    const uint8_t *tiles[3];
+    for (uint32_t i = 0; i < n; i++) {
+        const size_t idx = (size_t)layer * 7 + which[i];
+        const QMat &w = m->layers[layer].m[which[i]]->view;
+        tiles[i] = m->pf.tiles[idx];
+        rows[i] = w.nrows;
+        total_rows += w.nrows;
+        if (!tiles[i] || m->pf.tiles_q6[idx] || w.ncols != m->layers[layer].m[which[0]]->view.ncols) together = false;
+    }
+    if (together) {
+        const uint32_t K = m->layers[layer].m[which[0]]->view.ncols, ns = prefill_gemm_splits(total_rows, K);
+        for (uint32_t i = 0; i < n; i++) nsplit[i] = ns;
+        return launch_gemm_q4k_tiles_multi(n, tiles, rows, K, image, ntok, out, stride, ns, s);
+    }
+    for (uint32_t i = 0; i < n; i++) {
+        int rc = prefill_product(m, layer, which[i], image, xf, xf_stride, ntok, out[i], stride[i], &nsplit[i], s);
+        if (rc) return rc;
+    }
+    return WGB_OK;
+}
+
 // Prompt positions pos0 .. pos0 + ntok - 1 (tokens d_tokens[0 .. ntok)) through the layer stack in one pass: the
 // work of ntok calls of Llama2::dispatch (models/llama2/transformer.rs:298-431) up to the last layer's cache
 // rows -- the logits of prompt positions are never looked at (chat_llama2.rs:169-204 samples only once the
@@ -473,9 +501,16 @@ int prefill_pass(wgb_llama2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32
         if ((rc = launch_prefill_norm_image(pf.x, dim, pending, pending_split, dim, w.v[WGB_L_ATTN_NORM], c.rms_norm_eps, dim, ntok, pf.img_dim,
                                             pf.xn, dim, s)))
             return rc;
-        if ((rc = prefill_product(m, l, WGB_L_ATTN_Q, pf.img_dim, pf.xn, dim, ntok, pf.part[0], q_dim, &nq, s))) return rc;
-        if ((rc = prefill_product(m, l, WGB_L_ATTN_K, pf.img_dim, pf.xn, dim, ntok, pf.part[1], kv_dim, &nk, s))) return rc;
-        if ((rc = prefill_product(m, l, WGB_L_ATTN_V, pf.img_dim, pf.xn, dim, ntok, pf.part[2], kv_dim, &nv, s))) return rc;
+        {
+            // q and k (and v, unless the file keeps it in another format) in one launch
+            const int which[3] = { WGB_L_ATTN_Q, WGB_L_ATTN_K, WGB_L_ATTN_V };
+            const uint32_t strides[3] = { q_dim, kv_dim, kv_dim };
+            uint32_t ns[3];
+            const bool v_too = pf.tiles[(size_t)l * 7 + WGB_L_ATTN_V] && !pf.tiles_q6[(size_t)l * 7 + WGB_L_ATTN_V];
+            if ((rc = prefill_products(m, l, which, v_too ? 3 : 2, pf.img_dim, pf.xn, dim, ntok, pf.part, strides, ns, s))) return rc;
+            if (!v_too && (rc = prefill_product(m, l, WGB_L_ATTN_V, pf.img_dim, pf.xn, dim, ntok, pf.part[2], kv_dim, &ns[2], s))) return rc;
+            nq = ns[0]; nk = ns[1]; nv = ns[2];
+        }
         PrefillQkv qa = {};
         qa.q = pf.part[0]; qa.k = pf.part[1]; qa.v = pf.part[2];
         qa.q_split = nq; qa.k_split = nk; qa.v_split = nv;
@@ -496,8 +531,13 @@ int prefill_pass(wgb_llama2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32
         if ((rc = across_ranks(&opart, &no))) return rc;
         if ((rc = launch_prefill_norm_image(pf.x, dim, opart, no, dim, w.v[WGB_L_FFN_NORM], c.rms_norm_eps, dim, ntok, pf.img_dim, pf.xn, dim, s)))
             return rc;
-        if ((rc = prefill_product(m, l, WGB_L_FFN_GATE, pf.img_dim, pf.xn, dim, ntok, pf.part[0], hidden, &ng, s))) return rc;
-        if ((rc = prefill_product(m, l, WGB_L_FFN_UP, pf.img_dim, pf.xn, dim, ntok, pf.part[1], hidden, &nu, s))) return rc;
+        {
+            const int which[2] = { WGB_L_FFN_GATE, WGB_L_FFN_UP };
+            const uint32_t strides[2] = { hidden, hidden };
+            uint32_t ns[2];
+            if ((rc = prefill_products(m, l, which, 2, pf.img_dim, pf.xn, dim, ntok, pf.part, strides, ns, s))) return rc;
+            ng = ns[0]; nu = ns[1];
+        }
         if ((rc = launch_prefill_silu_image(pf.part[0], ng, pf.part[1], nu, hidden, hidden, ntok, pf.img_hidden, pf.h, hidden, s))) return rc;
         if ((rc = prefill_product(m, l, WGB_L_FFN_DOWN, pf.img_hidden, pf.h, hidden, ntok, pf.part[2], dim, &nd, s))) return rc;
         pending = pf.part[2];

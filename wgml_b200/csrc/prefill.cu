@@ -56,13 +56,22 @@ bool pdl_enabled()
 
 size_t prefill_image_bytes(uint32_t K) { return (size_t)(K / 256) * TB_IMG_BYTES; }
 
+// Up to three matrices with the same input (q / k / v, gate / up) share a launch: their tiles are numbered through.
 struct TbArgs {
-    const uint8_t *w;     // tile-major blocks: [tile][column][128 rows][144 bytes]
-    const uint8_t *img;   // activation image: [column][TB_IMG_BYTES]
-    float *out;           // [nsplit][PF_TOK][out_stride]
-    uint32_t nrows, nkb, nsplit, ntok, out_stride;
+    const uint8_t *w[3];      // tile-major blocks: [tile][column][128 rows][144 bytes]
+    float *out[3];            // [nsplit][PF_TOK][out_stride]
+    uint32_t tile0[3];        // first tile of each matrix in the launch's numbering (tile0[0] = 0)
+    uint32_t out_stride[3];
+    uint32_t nmat, ntiles;    // matrices, tiles over all of them
+    const uint8_t *img;       // activation image: [column][TB_IMG_BYTES]
+    uint32_t nkb, nsplit, ntok;
     uint32_t *err;
 };
+// Matrix of a tile in the launch's numbering.
+__device__ __forceinline__ uint32_t tb_matrix_of(const TbArgs &a, uint32_t tile)
+{
+    return (a.nmat > 2 && tile >= a.tile0[2]) ? 2u : (a.nmat > 1 && tile >= a.tile0[1]) ? 1u : 0u;
+}
 
 __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_constant__ TbArgs a)
 {
@@ -76,7 +85,7 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
 
     pdl_launch_dependents();
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t nkb = a.nkb, nsplit = a.nsplit, nitems = (a.nrows / TC_TILE_ROWS) * nsplit;
+    const uint32_t nkb = a.nkb, nsplit = a.nsplit, nitems = a.ntiles * nsplit;
     auto bar_full = [&](uint32_t s) { return smem_addr(&bars[s]); };
     auto bar_empty = [&](uint32_t s) { return smem_addr(&bars[TB_RING + s]); };
     auto bar_done = [&](uint32_t u) { return smem_addr(&bars[2 * TB_RING + u]); };        // the unit's MMAs have completed
@@ -123,7 +132,9 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                 if (!ok) break;
                 mbar_expect_tx(bar_full(s), TB_STAGE);
                 bulk_copy_g2s(stage(s), a.img + (size_t)w.kb * TB_IMG_BYTES, TB_IMG_BYTES, bar_full(s));
-                bulk_copy_g2s(stage(s) + TB_IMG_BYTES, a.w + ((size_t)w.tile * nkb + w.kb) * TC_UNIT_BYTES, TC_UNIT_BYTES, bar_full(s));
+                const uint32_t mi = tb_matrix_of(a, w.tile);
+                bulk_copy_g2s(stage(s) + TB_IMG_BYTES, a.w[mi] + ((size_t)(w.tile - a.tile0[mi]) * nkb + w.kb) * TC_UNIT_BYTES, TC_UNIT_BYTES,
+                              bar_full(s));
                 w.next(nsplit, nkb, gridDim.x);
             }
         }
@@ -277,13 +288,16 @@ __global__ void __launch_bounds__(TB_NT, 1) gemm_q4k_tc_kernel(const __grid_cons
                 asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_FINISH_WARPS) : "memory");
                 if (ok) {
                     constexpr uint32_t NP = TB_FINISH_WARPS / 4, TPT = PF_TOK / NP;   // parts of a row, positions per thread
+                    const uint32_t mi = tb_matrix_of(a, fin.tile);
+                    float *outp = a.out[mi] + (size_t)(fin.tile - a.tile0[mi]) * TC_TILE_ROWS + r;
+                    const uint32_t ostride = a.out_stride[mi];
 #pragma unroll
                     for (uint32_t tt = 0; tt < TPT; tt++) {
                         const uint32_t t = TPT * half + tt;
                         float v = rowpart[0][t][r];
 #pragma unroll
                         for (uint32_t q = 1; q < NP; q++) v += rowpart[q][t][r];
-                        if (t < a.ntok) a.out[((size_t)fin.sp * PF_TOK + t) * a.out_stride + (size_t)fin.tile * TC_TILE_ROWS + r] = v;
+                        if (t < a.ntok) outp[((size_t)fin.sp * PF_TOK + t) * ostride] = v;
                     }
                 }
                 asm volatile("bar.sync 2, %0;" ::"n"(32 * TB_FINISH_WARPS) : "memory");
@@ -315,11 +329,11 @@ uint32_t prefill_gemm_splits(uint32_t nrows, uint32_t K)
     return best;
 }
 
-int launch_gemm_q4k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, const uint8_t *image, uint32_t ntok, float *out,
-                          uint32_t out_stride, uint32_t nsplit, cudaStream_t stream)
+int launch_gemm_q4k_tiles_multi(uint32_t nmat, const uint8_t *const *w_tiles, const uint32_t *nrows, uint32_t K, const uint8_t *image,
+                                uint32_t ntok, float *const *out, const uint32_t *out_stride, uint32_t nsplit, cudaStream_t stream)
 {
-    WGB_REQUIRE(nrows % TC_TILE_ROWS == 0 && K % 256 == 0 && ntok >= 1 && ntok <= PF_TOK && nsplit >= 1 && nsplit <= K / 256,
-                "batched product: %u x %u, %u positions, %u slices", nrows, K, ntok, nsplit);
+    WGB_REQUIRE(nmat >= 1 && nmat <= 3 && K % 256 == 0 && ntok >= 1 && ntok <= PF_TOK && nsplit >= 1 && nsplit <= K / 256,
+                "batched product: %u matrices, %u columns, %u positions, %u slices", nmat, K, ntok, nsplit);
     DeviceState *ds = device_state();
     if (!ds) return WGB_ERR_CUDA;
     if (!ds->prefill_attrs) {
@@ -327,18 +341,29 @@ int launch_gemm_q4k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, co
         ds->prefill_attrs = true;
     }
     TbArgs a = {};
-    a.w = w_tiles;
+    for (uint32_t i = 0; i < nmat; i++) {
+        WGB_REQUIRE(nrows[i] > 0 && nrows[i] % TC_TILE_ROWS == 0, "batched product: %u rows", nrows[i]);
+        a.w[i] = w_tiles[i];
+        a.out[i] = out[i];
+        a.out_stride[i] = out_stride[i];
+        a.tile0[i] = a.ntiles;
+        a.ntiles += nrows[i] / TC_TILE_ROWS;
+    }
+    a.nmat = nmat;
     a.img = image;
-    a.out = out;
-    a.nrows = nrows;
     a.nkb = K / 256;
     a.nsplit = nsplit;
     a.ntok = ntok;
-    a.out_stride = out_stride;
     a.err = gemv_status_word();
-    const uint32_t items = nrows / TC_TILE_ROWS * nsplit, sms = (uint32_t)sm_count();
+    const uint32_t items = a.ntiles * nsplit, sms = (uint32_t)sm_count();
     WGB_CUDA(launch_pdl(gemm_q4k_tc_kernel, dim3(items < sms ? items : sms), dim3(TB_NT), TB_SMEM + 1024, stream, a));
     return WGB_OK;
+}
+
+int launch_gemm_q4k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, const uint8_t *image, uint32_t ntok, float *out,
+                          uint32_t out_stride, uint32_t nsplit, cudaStream_t stream)
+{
+    return launch_gemm_q4k_tiles_multi(1, &w_tiles, &nrows, K, image, ntok, &out, &out_stride, nsplit, stream);
 }
 
 // ---- activation image ---------------------------------------------------------------------------------
