@@ -92,7 +92,9 @@ int wgb_quant_matrix_dequantize_rows(const wgb_quant_matrix *m, size_t row0, siz
 /* GemvQuant::dispatch (ops/gemv_quant.rs:241-348): d_out[nrows] = m * d_v[ncols], f32 in and
  * out, f32 accumulation.  Any nrows (the reference needs nrows % 4 == 0). */
 int wgb_gemv_quant(const wgb_quant_matrix *m, const float *d_v, float *d_out, void *stream);
-/* The same product over raw GGUF blocks in device memory (no wgb_quant_matrix). */
+/* The same product over raw GGUF blocks in device memory (no wgb_quant_matrix).  The blocks may be produced by
+ * earlier work on the same stream: unlike wgb_gemv_quant on a matrix the library uploaded, this launch does not
+ * start reading weights before its predecessor in the stream has completed. */
 int wgb_gemv_quant_raw(int qtype, const void *d_blocks, size_t nrows, size_t ncols, const float *d_v,
                        float *d_out, void *stream);
 

@@ -1064,7 +1064,7 @@ int launch_gemv_generic(const QMat &m, const float *x, float *out, cudaStream_t 
 
 using namespace wgb;
 
-static int gemv_dispatch(const QMat &m, const float *d_v, float *d_out, cudaStream_t stream)
+static int gemv_dispatch(const QMat &m, const float *d_v, float *d_out, cudaStream_t stream, bool early_weights)
 {
     WGB_REQUIRE(d_v && d_out, "null argument");
     if (gemv_fast_supported(m) && ((uintptr_t)d_v % 16) == 0) {
@@ -1077,7 +1077,9 @@ static int gemv_dispatch(const QMat &m, const float *d_v, float *d_out, cudaStre
         a.out = d_out;
         // Programmatic dependent launch: the kernel streams its first weights while the previous launch in the
         // stream is still draining, and waits for it (griddepcontrol.wait) before it reads d_v or writes d_out.
-        return launch_gemv(a, stream, true);
+        // Only for matrices the library uploaded itself: blocks in caller memory may be the output of that
+        // previous launch and must not be read before it has completed.
+        return launch_gemv(a, stream, early_weights);
     }
     return launch_gemv_generic(m, d_v, d_out, stream);
 }
@@ -1085,7 +1087,7 @@ static int gemv_dispatch(const QMat &m, const float *d_v, float *d_out, cudaStre
 WGB_EXPORT int wgb_gemv_quant(const wgb_quant_matrix *m, const float *d_v, float *d_out, void *stream)
 {
     WGB_REQUIRE(m, "null matrix");
-    return gemv_dispatch(m->view, d_v, d_out, as_stream(stream));
+    return gemv_dispatch(m->view, d_v, d_out, as_stream(stream), m->storage != nullptr);
 }
 
 WGB_EXPORT int wgb_gemv_quant_raw(int qtype, const void *d_blocks, size_t nrows, size_t ncols, const float *d_v,
@@ -1102,5 +1104,5 @@ WGB_EXPORT int wgb_gemv_quant_raw(int qtype, const void *d_blocks, size_t nrows,
     m.bpr = (uint32_t)(ncols / bl);
     qmat_set_pitches(m);
     m.p[0] = (const uint8_t *)d_blocks;
-    return gemv_dispatch(m, d_v, d_out, as_stream(stream));
+    return gemv_dispatch(m, d_v, d_out, as_stream(stream), false);
 }

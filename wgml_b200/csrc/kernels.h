@@ -202,7 +202,10 @@ struct PrefillQkv {
     const float *freq;
 };
 int launch_prefill_rope_append(const PrefillQkv &a, uint32_t ntok, cudaStream_t stream);
+// With `image` (allowed when prefill_attention_writes_image(head_size)) the kernel also writes the activation image of
+// its output, the input of the output projection.
+bool prefill_attention_writes_image(uint32_t head_size);
 int launch_prefill_attention(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
-                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, cudaStream_t stream);
+                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, cudaStream_t stream);
 
 }  // namespace wgb

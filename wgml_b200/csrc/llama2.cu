@@ -523,9 +523,11 @@ int prefill_pass(wgb_llama2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32
         qa.variant = variant;
         qa.freq = m->rope_freq;
         if ((rc = launch_prefill_rope_append(qa, ntok, s))) return rc;
-        if ((rc = launch_prefill_attention(pf.q, qa.k_cache, qa.v_cache, pf.xb, m->n_q_local, m->head_size, m->kv_mul, c.seq_len, pos0, ntok, s)))
+        const bool attn_image = prefill_attention_writes_image(m->head_size);
+        if ((rc = launch_prefill_attention(pf.q, qa.k_cache, qa.v_cache, pf.xb, m->n_q_local, m->head_size, m->kv_mul, c.seq_len, pos0, ntok,
+                                           attn_image ? pf.img_q : nullptr, s)))
             return rc;
-        if ((rc = launch_prefill_norm_image(pf.xb, q_dim, nullptr, 0, 0, nullptr, 0.0f, q_dim, ntok, pf.img_q, nullptr, 0, s))) return rc;
+        if (!attn_image && (rc = launch_prefill_norm_image(pf.xb, q_dim, nullptr, 0, 0, nullptr, 0.0f, q_dim, ntok, pf.img_q, nullptr, 0, s))) return rc;
         if ((rc = prefill_product(m, l, WGB_L_ATTN_OUTPUT, pf.img_q, pf.xb, q_dim, ntok, pf.part[0], dim, &no, s))) return rc;
         const float *opart = pf.part[0];
         if ((rc = across_ranks(&opart, &no))) return rc;

@@ -566,13 +566,19 @@ constexpr uint32_t PA_CHUNK = 256;
 __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__restrict__ q, const float *__restrict__ k_cache,
                                                                 const float *__restrict__ v_cache, float *__restrict__ out, uint32_t q_dim,
                                                                 uint32_t head_size, uint32_t kv_mul, uint32_t seq_len, uint32_t pos0,
-                                                                uint32_t ntok)
+                                                                uint32_t ntok, uint8_t *__restrict__ image)
 {
     extern __shared__ float pa_smem[];
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t h = blockIdx.x, t0 = blockIdx.y * PA_TQ;
-    if (t0 >= ntok) return;
+    if (t0 >= ntok) {
+        // with an image the grid covers all PF_TOK positions: the unused ones get zero digits
+        if (image)
+            for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256)
+                image_quad(image, t0 + i / (head_size / 4), (h * head_size + 4 * (i % (head_size / 4))) >> 5, i & 7, make_float4(0.f, 0.f, 0.f, 0.f));
+        return;
+    }
     const uint32_t nq = ntok - t0 < PA_TQ ? ntok - t0 : PA_TQ;
     float *qs = pa_smem;                          // [PA_TQ][head_size]
     float *sc = qs + PA_TQ * head_size;           // [PA_TQ][PA_CHUNK]
@@ -602,6 +608,7 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
         for (uint32_t tq = 0; tq < PA_TQ; tq++) s[tq] = 0.0f;
         if (row <= last) {
             const float4 *kr = reinterpret_cast<const float4 *>(kh + (size_t)row * head_size);
+#pragma unroll 8
             for (uint32_t e = 0; e < head_size / 4; e++) {
                 const float4 kv = kr[e];
 #pragma unroll
@@ -648,6 +655,7 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
         }
         if (4 * cg < head_size) {
             const uint32_t r_end = min(c0 + 64 * (rq + 1), last + 1);
+#pragma unroll 4
             for (uint32_t rr = c0 + 64 * rq; rr < r_end; rr++) {
                 const float4 vv = *reinterpret_cast<const float4 *>(vh + (size_t)rr * head_size + 4 * cg);
 #pragma unroll
@@ -665,22 +673,36 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
         for (uint32_t tq = 0; tq < PA_TQ; tq++) *reinterpret_cast<float4 *>(accs + ((size_t)rq * PA_TQ + tq) * head_size + 4 * cg) = acc[tq];
     }
     __syncthreads();
-    for (uint32_t i = threadIdx.x; i < nq * head_size; i += 256) {
-        const uint32_t tq = i / head_size, e = i % head_size;
-        float v = 0.0f;
-        for (uint32_t r4 = 0; r4 < 4; r4++) v += accs[((size_t)r4 * PA_TQ + tq) * head_size + e];
-        out[(size_t)(t0 + tq) * q_dim + h * head_size + e] = v / l_run[tq];
+    // the block's output, four columns per thread; with `image` (head sizes that are multiples of 64, so that whole
+    // warps take part) also its slice of the activation image of the output projection's input
+    for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256) {
+        const uint32_t tq = i / (head_size / 4), e4 = i % (head_size / 4);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tq < nq) {
+            for (uint32_t r4 = 0; r4 < 4; r4++) {
+                const float4 p = *reinterpret_cast<const float4 *>(accs + ((size_t)r4 * PA_TQ + tq) * head_size + 4 * e4);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
+            const float l = l_run[tq];
+            v.x /= l; v.y /= l; v.z /= l; v.w /= l;
+            *reinterpret_cast<float4 *>(out + (size_t)(t0 + tq) * q_dim + h * head_size + 4 * e4) = v;
+        }
+        if (image) image_quad(image, t0 + tq, (h * head_size + 4 * e4) >> 5, e4 & 7, v);
     }
 }
 
+bool prefill_attention_writes_image(uint32_t head_size) { return head_size % 64 == 0; }
+
 int launch_prefill_attention(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
-                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, cudaStream_t stream)
+                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, cudaStream_t stream)
 {
+    WGB_REQUIRE(!image || prefill_attention_writes_image(head_size), "prompt attention writes the image only for head sizes that are multiples of 64, got %u",
+                head_size);
     WGB_REQUIRE(head_size % 4 == 0 && head_size <= 256 && ntok >= 1 && ntok <= PF_TOK, "prompt attention: head size %u, %u positions", head_size,
                 ntok);
     const size_t smem = (size_t)(PA_TQ * head_size + PA_TQ * PA_CHUNK + 4 * PA_TQ * head_size) * sizeof(float);
-    WGB_CUDA(launch_pdl(prefill_attention_kernel, dim3(n_heads, (ntok + PA_TQ - 1) / PA_TQ), dim3(256), smem, stream, q, k_cache, v_cache, out,
-                        n_heads * head_size, head_size, kv_mul, seq_len, pos0, ntok));
+    WGB_CUDA(launch_pdl(prefill_attention_kernel, dim3(n_heads, image ? PF_TOK / PA_TQ : (ntok + PA_TQ - 1) / PA_TQ), dim3(256), smem, stream, q, k_cache,
+                        v_cache, out, n_heads * head_size, head_size, kv_mul, seq_len, pos0, ntok, image));
     return WGB_OK;
 }
 
