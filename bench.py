@@ -298,8 +298,20 @@ def run_b200(args):
     # are measured separately below); tensor-parallel runs send it through the batched passes, which are what a
     # 4096-token prompt is for, and report their rate beside the decode figures.
     tp_prefill = None
-    if world > 1 and not args.no_prefill and prompt_len >= 16:
-        model.set_prefill(True)
+    batched_prompt = world > 1 and not args.no_prefill and prompt_len >= 16
+    if batched_prompt:
+        try:
+            model.set_prefill(True)
+        except Exception as e:   # e.g. slice widths the tensor-core path does not take: the token loop serves the prompt
+            print(f"rank {rank}: batched prompt passes not available ({e}); feeding the prompt position by position", file=sys.stderr)
+            batched_prompt = False
+        if world > 1:   # all ranks take the same path
+            flag = torch.tensor([1 if batched_prompt else 0], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if batched_prompt and int(flag[0]) == 0:
+                model.set_prefill(False)
+            batched_prompt = bool(int(flag[0]))
+    if batched_prompt:
         barrier()
         t0 = time.perf_counter()
         toks = model.decode(prompt, 0)

@@ -13,12 +13,12 @@
 // the largest magnitude among the 256 columns.  An element's error is below 2^-23 of that maximum, which keeps
 // a product within 1e-6 of its output RMS for inputs whose maximum is within a few thousand times their RMS.
 // The epilogue per super-block is small: hi and lo sums joined in the integer unit, three conversions, one FMA
-// with d * exponent per (row, input vector); the four threads of a row take two input vectors each, so a row's
+// with d * exponent per (row, input vector); one thread per row does it for the eight vectors, so a row's
 // running sums live in registers and go straight to the output at the end of an item.
 //
 // Pipeline as in the Q4_K kernel: producer warp (bulk copies into a ring of stages: the super-block's slice of
-// the image and 26 KB of weights), one warp issuing the MMAs, sixteen worker warps that build the two operand
-// planes of unit n and then finish unit n - 1.  Bounded waits throughout.
+// the image and 26 KB of weights), one warp issuing the MMAs, sixteen warps that build the two operand planes of
+// unit n, four warps that finish unit n - 1; the roles meet only through barriers.  Bounded waits throughout.
 #include "kernels.h"
 #include "tc_common.cuh"
 
@@ -32,8 +32,9 @@ constexpr uint32_t T6_IMG_DIGITS = 3 * 16 * 128;                        // 3 dig
 constexpr uint32_t T6_IMG_BYTES = T6_IMG_DIGITS + PF_TOK * 4;           // + one exponent per vector
 constexpr uint32_t T6_STAGE = T6_IMG_BYTES + T6_UNIT_BYTES;
 constexpr uint32_t T6_RING = 3;
-constexpr uint32_t T6_WORKER_WARPS = 16;
-constexpr uint32_t T6_NT = 32 * (2 + T6_WORKER_WARPS);
+constexpr uint32_t T6_WORKER_WARPS = 16;                                // build the two operand planes of unit n
+constexpr uint32_t T6_FINISH_WARPS = 4;                                 // one thread per row reads unit n - 1's sums
+constexpr uint32_t T6_NT = 32 * (2 + T6_WORKER_WARPS + T6_FINISH_WARPS);
 constexpr uint32_t T6_TMEM_COLS = 128;                                  // two units x (Dlo, Dhi) x 32 columns
 constexpr uint32_t T6_A_BYTES = 2 * TC_A_BYTES;                         // lo plane, hi plane
 constexpr uint32_t T6_OFF_RING = 2 * T6_A_BYTES;
@@ -56,7 +57,7 @@ struct T6Args {
 __global__ void __launch_bounds__(T6_NT, 1) gemm_q6k_tc_kernel(const __grid_constant__ T6Args a)
 {
     extern __shared__ uint8_t t6_smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * T6_RING + 2];
+    __shared__ __align__(8) unsigned long long bars[2 * T6_RING + 4];
     __shared__ uint32_t tmem_base_slot;
     __shared__ uint32_t dead_flag;
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)t6_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -67,7 +68,8 @@ __global__ void __launch_bounds__(T6_NT, 1) gemm_q6k_tc_kernel(const __grid_cons
     const uint32_t nkb = a.nkb, nsplit = a.nsplit, nitems = (a.nrows / TC_TILE_ROWS) * nsplit;
     auto bar_full = [&](uint32_t s) { return smem_addr(&bars[s]); };
     auto bar_empty = [&](uint32_t s) { return smem_addr(&bars[T6_RING + s]); };
-    auto bar_done = [&](uint32_t u) { return smem_addr(&bars[2 * T6_RING + u]); };
+    auto bar_done = [&](uint32_t u) { return smem_addr(&bars[2 * T6_RING + u]); };        // the unit's MMAs have completed
+    auto bar_tfree = [&](uint32_t u) { return smem_addr(&bars[2 * T6_RING + 2 + u]); };   // its accumulators have been read
     auto stage = [&](uint32_t s) { return smem_addr(smem + T6_OFF_RING) + s * T6_STAGE; };
     uint32_t total = 0;
     for (uint32_t i = blockIdx.x; i < nitems; i += gridDim.x) {
@@ -79,10 +81,12 @@ __global__ void __launch_bounds__(T6_NT, 1) gemm_q6k_tc_kernel(const __grid_cons
         dead_flag = 0;
         for (uint32_t s = 0; s < T6_RING; s++) {
             mbar_init(bar_full(s), 1);
-            mbar_init(bar_empty(s), 32 * T6_WORKER_WARPS);
+            mbar_init(bar_empty(s), 32 * (T6_WORKER_WARPS + T6_FINISH_WARPS));
         }
-        mbar_init(bar_done(0), 1);
-        mbar_init(bar_done(1), 1);
+        for (uint32_t u = 0; u < 2; u++) {
+            mbar_init(bar_done(u), 1);
+            mbar_init(bar_tfree(u), 32 * T6_FINISH_WARPS);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -125,7 +129,8 @@ __global__ void __launch_bounds__(T6_NT, 1) gemm_q6k_tc_kernel(const __grid_cons
             const uint32_t u = n & 1, s = n % T6_RING;
             if (u) asm volatile("bar.sync 4, %0;" ::"n"(32 * T6_WORKER_WARPS + 32) : "memory");
             else asm volatile("bar.sync 3, %0;" ::"n"(32 * T6_WORKER_WARPS + 32) : "memory");
-            if (lane == 0 && !*dead && tc_wait(bar_full(s), (n / T6_RING) & 1, dead, a.err, 32)) {
+            if (lane == 0 && !*dead && tc_wait(bar_full(s), (n / T6_RING) & 1, dead, a.err, 32) &&
+                (n < 2 || tc_wait(bar_tfree(u), ((n - 2) >> 1) & 1, dead, a.err, 35))) {   // the accumulators of unit n - 2 have been read
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t bd = tc_smem_desc(stage(s), 128, 2048);
                 const uint32_t dcol = tmem_base + u * 64;
@@ -141,100 +146,117 @@ __global__ void __launch_bounds__(T6_NT, 1) gemm_q6k_tc_kernel(const __grid_cons
             }
             __syncwarp();
         }
-    } else {
-        // ------------------------------ workers ------------------------------
-        // Thread (quarter, lane, sub): row r = 32 quarter + lane of the tile.  Operand: 32-weight groups sub and
-        // 4 + sub of the row's super-block (columns 32 sub .. of each 128-column half, the layout of
-        // BlockQ6K::dequantize).  Epilogue: input vectors 2 sub and 2 sub + 1 of the row.
+    } else if (warp < 2 + T6_WORKER_WARPS) {
+        // ------------------------------ operand ------------------------------
+        // Thread (quarter, lane, sub): row r = 32 quarter + lane of the tile, 32-weight groups sub and 4 + sub of the
+        // row's super-block (columns 32 sub .. of each 128-column half, the layout of BlockQ6K::dequantize).  Unit n
+        // goes into operand buffer n % 2 once its stage is full and the MMAs of unit n - 2 have read the buffer.
         const uint32_t w = warp - 2, sub = w / 4, quarter = warp & 3, r = quarter * 32 + lane;
         const uint32_t arow = smem_addr(smem) + (r >> 3) * 1024 + (r & 7) * 128;
-        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
         const uint32_t nib_shift = 4 * (sub >> 1), h_shift = 2 * sub;
-        float rowacc[2] = { 0.0f, 0.0f };
         bool ok = true;
-        UnitWalk fin;   // the unit being finished (one step behind the one whose operand is built)
-        fin.set(blockIdx.x, nsplit, nkb);
-        for (uint32_t n = 0; n <= total; n++) {
-            if (n < total) {
-                const uint32_t slot = n % T6_RING, u = n & 1;
-                if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_full(slot), (n / T6_RING) & 1, dead, a.err, 33));
-                const uint32_t wbase = stage(slot) + T6_IMG_BYTES;
-                if (ok) {
-                    const uint4 scq = lds128(wbase + T6_OFF_SC + r * 16);   // the row's sixteen int8 scales
+        // After an expired wait (`ok` false, warp-uniform) the loop keeps its shape, so that every thread still meets
+        // every hardware barrier, but waits for nothing and computes nothing.
+        for (uint32_t n = 0; n < total; n++) {
+            const uint32_t slot = n % T6_RING, u = n & 1;
+            if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_full(slot), (n / T6_RING) & 1, dead, a.err, 33));
+            if (ok && n >= 2) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), ((n - 2) >> 1) & 1, dead, a.err, 36));
+            const uint32_t wbase = stage(slot) + T6_IMG_BYTES;
+            if (ok) {
+                const uint4 scq = lds128(wbase + T6_OFF_SC + r * 16);   // the row's sixteen int8 scales
 #pragma unroll
-                    for (uint32_t half = 0; half < 2; half++) {
+                for (uint32_t half = 0; half < 2; half++) {
 #pragma unroll
-                        for (uint32_t c = 0; c < 2; c++) {
-                            // weights l = 16 c .. 16 c + 15 of group 4 half + sub: low or high nibbles of ql[64 half +
-                            // 32 (sub & 1) + l], two more bits from qh[32 half + l] >> 2 sub, scale 8 half + 2 sub + c
-                            const uint4 qlq = lds128(wbase + r * 128 + 64 * half + 32 * (sub & 1) + 16 * c);
-                            const uint4 qhq = lds128(wbase + T6_OFF_QH + r * 64 + 32 * half + 16 * c);
-                            // scale 8 half + 2 sub + c: word 2 half + sub / 2 of the sixteen, byte 2 (sub % 2) + c
-                            const uint32_t sw = (sub >> 1) ? (half ? scq.w : scq.y) : (half ? scq.z : scq.x);
-                            const int s = (int)(signed char)((sw >> (8 * (2 * (sub & 1) + c))) & 0xffu);
-                            const int cst = -0x00200020 * s;   // (q1 - 32, q0 - 32) * s = (q1, q0) * s - (32, 32) * s
-                            const uint32_t qlw[4] = { qlq.x, qlq.y, qlq.z, qlq.w }, qhw[4] = { qhq.x, qhq.y, qhq.z, qhq.w };
-                            uint32_t lo[4], hi[4];
+                    for (uint32_t c = 0; c < 2; c++) {
+                        // weights l = 16 c .. 16 c + 15 of group 4 half + sub: low or high nibbles of ql[64 half +
+                        // 32 (sub & 1) + l], two more bits from qh[32 half + l] >> 2 sub, scale 8 half + 2 sub + c
+                        const uint4 qlq = lds128(wbase + r * 128 + 64 * half + 32 * (sub & 1) + 16 * c);
+                        const uint4 qhq = lds128(wbase + T6_OFF_QH + r * 64 + 32 * half + 16 * c);
+                        // scale 8 half + 2 sub + c: word 2 half + sub / 2 of the sixteen, byte 2 (sub % 2) + c
+                        const uint32_t sw = (sub >> 1) ? (half ? scq.w : scq.y) : (half ? scq.z : scq.x);
+                        const int s = (int)(signed char)((sw >> (8 * (2 * (sub & 1) + c))) & 0xffu);
+                        const int cst = -0x00200020 * s;   // (q1 - 32, q0 - 32) * s = (q1, q0) * s - (32, 32) * s
+                        const uint32_t qlw[4] = { qlq.x, qlq.y, qlq.z, qlq.w }, qhw[4] = { qhq.x, qhq.y, qhq.z, qhq.w };
+                        uint32_t lo[4], hi[4];
 #pragma unroll
-                            for (uint32_t k = 0; k < 4; k++) {
-                                const uint32_t q = ((qlw[k] >> nib_shift) & 0x0f0f0f0fu) | (((qhw[k] >> h_shift) & 0x03030303u) << 4);
-                                // two 16-bit lanes per word: q0 | q1 << 16 and q2 | q3 << 16, times the scale; a negative low
-                                // lane has borrowed one from the high lane, which is given back
-                                int r0 = (int)__byte_perm(q, 0u, 0x4140) * s + cst, r1 = (int)__byte_perm(q, 0u, 0x4342) * s + cst;
-                                r0 += (r0 & 0x8000) << 1;
-                                r1 += (r1 & 0x8000) << 1;
-                                lo[k] = __byte_perm((uint32_t)r0, (uint32_t)r1, 0x6420);
-                                hi[k] = __byte_perm((uint32_t)r0, (uint32_t)r1, 0x7531);
-                            }
-                            // columns 128 half + 32 sub + 16 c ..: K panel `half`, 16-byte chunk 2 sub + c of the row (swizzled)
-                            const uint32_t off = u * T6_A_BYTES + half * 16384 + (((2 * sub + c) ^ (r & 7)) << 4);
-                            sts128(arow + off, lo[0], lo[1], lo[2], lo[3]);
-                            sts128(arow + off + TC_A_BYTES, hi[0], hi[1], hi[2], hi[3]);
+                        for (uint32_t k = 0; k < 4; k++) {
+                            const uint32_t q = ((qlw[k] >> nib_shift) & 0x0f0f0f0fu) | (((qhw[k] >> h_shift) & 0x03030303u) << 4);
+                            // two 16-bit lanes per word: q0 | q1 << 16 and q2 | q3 << 16, times the scale; a negative low
+                            // lane has borrowed one from the high lane, which is given back
+                            int r0 = (int)__byte_perm(q, 0u, 0x4140) * s + cst, r1 = (int)__byte_perm(q, 0u, 0x4342) * s + cst;
+                            r0 += (r0 & 0x8000) << 1;
+                            r1 += (r1 & 0x8000) << 1;
+                            lo[k] = __byte_perm((uint32_t)r0, (uint32_t)r1, 0x6420);
+                            hi[k] = __byte_perm((uint32_t)r0, (uint32_t)r1, 0x7531);
                         }
+                        // columns 128 half + 32 sub + 16 c ..: K panel `half`, 16-byte chunk 2 sub + c of the row (swizzled)
+                        const uint32_t off = u * T6_A_BYTES + half * 16384 + (((2 * sub + c) ^ (r & 7)) << 4);
+                        sts128(arow + off, lo[0], lo[1], lo[2], lo[3]);
+                        sts128(arow + off + TC_A_BYTES, hi[0], hi[1], hi[2], hi[3]);
                     }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                if (u) asm volatile("bar.arrive 4, %0;" ::"n"(32 * T6_WORKER_WARPS + 32) : "memory");
-                else asm volatile("bar.arrive 3, %0;" ::"n"(32 * T6_WORKER_WARPS + 32) : "memory");
             }
-            if (n >= 1) {
-                const uint32_t m = n - 1, slot = m % T6_RING, u = m & 1;
-                const uint32_t img = stage(slot), wbase = img + T6_IMG_BYTES;
-                // d of the row's block and the exponents of the thread's two input vectors
-                uint32_t dbits, e0, e1;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            if (u) asm volatile("bar.arrive 4, %0;" ::"n"(32 * T6_WORKER_WARPS + 32) : "memory");
+            else asm volatile("bar.arrive 3, %0;" ::"n"(32 * T6_WORKER_WARPS + 32) : "memory");
+            mbar_arrive(bar_empty(slot));   // the stage is free once the finishing threads have arrived too
+        }
+    } else {
+        // ------------------------------ finishing ------------------------------
+        // One thread per row (r = 32 quarter + lane, the quarter of tensor memory its warp may read): the row's lo and
+        // hi digit sums of unit m for the eight input vectors, joined, converted and added to the row's running sums.
+        const uint32_t quarter = warp & 3, r = quarter * 32 + lane;
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+        float rowacc[PF_TOK];
+#pragma unroll
+        for (uint32_t t = 0; t < PF_TOK; t++) rowacc[t] = 0.0f;
+        bool ok = true;
+        UnitWalk fin;
+        fin.set(blockIdx.x, nsplit, nkb);
+        for (uint32_t m = 0; m < total; m++) {
+            const uint32_t slot = m % T6_RING, u = m & 1;
+            if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_full(slot), (m / T6_RING) & 1, dead, a.err, 37));
+            const uint32_t img = stage(slot), wbase = img + T6_IMG_BYTES;
+            // d of the row's block and the exponents of the eight input vectors
+            uint32_t dbits = 0;
+            uint4 ea = make_uint4(0u, 0u, 0u, 0u), eb = ea;
+            if (ok) {
                 asm volatile("ld.shared.u16 %0, [%1];" : "=r"(dbits) : "r"(wbase + T6_OFF_D + r * 2));
-                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(e0), "=r"(e1) : "r"(img + T6_IMG_DIGITS + 8 * sub));
-                const float d = __half2float(__ushort_as_half((unsigned short)dbits));
-                if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), (m >> 1) & 1, dead, a.err, 34));
-                if (ok) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    int dl[3][2], dh[3][2];
-#pragma unroll
-                    for (uint32_t dg = 0; dg < 3; dg++) {
-                        tc_ld2(taddr + u * 64 + 8 * dg + 2 * sub, dl[dg]);
-                        tc_ld2(taddr + u * 64 + 32 + 8 * dg + 2 * sub, dh[dg]);
-                    }
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-#pragma unroll
-                    for (uint32_t tt = 0; tt < 2; tt++) {
-                        // |hi| <= 256 * 16 * 128 and |lo| <= 256 * 255 * 128: 256 hi + lo stays below 2^28
-                        const int t0 = dh[0][tt] * 256 + dl[0][tt], t1 = dh[1][tt] * 256 + dl[1][tt], t2 = dh[2][tt] * 256 + dl[2][tt];
-                        const float f = fmaf(__int2float_rn(t2), 65536.0f, fmaf(__int2float_rn(t1), 256.0f, __int2float_rn(t0)));
-                        rowacc[tt] = fmaf(f, d * __uint_as_float(tt ? e1 : e0), rowacc[tt]);
-                    }
-                }
-                mbar_arrive(bar_empty(slot));
-                if (fin.last()) {
-#pragma unroll
-                    for (uint32_t tt = 0; tt < 2; tt++) {
-                        const uint32_t t = 2 * sub + tt;
-                        if (ok && t < a.ntok) a.out[((size_t)fin.sp * PF_TOK + t) * a.out_stride + (size_t)fin.tile * TC_TILE_ROWS + r] = rowacc[tt];
-                        rowacc[tt] = 0.0f;
-                    }
-                }
-                fin.next(nsplit, nkb, gridDim.x);
+                ea = lds128(img + T6_IMG_DIGITS);
+                eb = lds128(img + T6_IMG_DIGITS + 16);
             }
+            const float d = __half2float(__ushort_as_half((unsigned short)dbits));
+            const float ev[PF_TOK] = { __uint_as_float(ea.x), __uint_as_float(ea.y), __uint_as_float(ea.z), __uint_as_float(ea.w),
+                                       __uint_as_float(eb.x), __uint_as_float(eb.y), __uint_as_float(eb.z), __uint_as_float(eb.w) };
+            if (ok) ok = __all_sync(0xffffffffu, tc_wait(bar_done(u), (m >> 1) & 1, dead, a.err, 34));
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                int dl[3][8], dh[3][8];
+#pragma unroll
+                for (uint32_t dg = 0; dg < 3; dg++) {
+                    tc_ld8(taddr + u * 64 + 8 * dg, dl[dg]);
+                    tc_ld8(taddr + u * 64 + 32 + 8 * dg, dh[dg]);
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(bar_tfree(u));   // unit m + 2 may overwrite the accumulators
+#pragma unroll
+                for (uint32_t t = 0; t < PF_TOK; t++) {
+                    // |hi| <= 256 * 16 * 128 and |lo| <= 256 * 255 * 128: 256 hi + lo stays below 2^28
+                    const int t0 = dh[0][t] * 256 + dl[0][t], t1 = dh[1][t] * 256 + dl[1][t], t2 = dh[2][t] * 256 + dl[2][t];
+                    const float f = fmaf(__int2float_rn(t2), 65536.0f, fmaf(__int2float_rn(t1), 256.0f, __int2float_rn(t0)));
+                    rowacc[t] = fmaf(f, d * ev[t], rowacc[t]);
+                }
+            }
+            mbar_arrive(bar_empty(slot));
+            if (fin.last()) {
+#pragma unroll
+                for (uint32_t t = 0; t < PF_TOK; t++) {
+                    if (ok && t < a.ntok) a.out[((size_t)fin.sp * PF_TOK + t) * a.out_stride + (size_t)fin.tile * TC_TILE_ROWS + r] = rowacc[t];
+                    rowacc[t] = 0.0f;
+                }
+            }
+            fin.next(nsplit, nkb, gridDim.x);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
