@@ -114,9 +114,11 @@ def _caches(gpu, n):
     dict(n_prompt=45, n_kv_heads=8, qwen=False, mixed=False),     # five full passes and a remainder of four (a short pass)
     dict(n_prompt=20, n_kv_heads=2, qwen=True, mixed=False),      # grouped-query heads, biases, Neox RoPE; remainder 3 stays sequential
     dict(n_prompt=34, n_kv_heads=8, qwen=False, mixed=True),      # a Q6_K and a Q8_0 matrix among the Q4_K ones
+    # a context of several 256-row chunks: the prompt attention of a (head, pair of positions) is shared by blocks
+    dict(n_prompt=700, n_kv_heads=4, qwen=False, mixed=False, seq_len=720, n_layers=2, n_gen=6),
 ])
 def test_prefill_matches_sequential_loop_and_oracle(case):
-    cfg = dict(SMALL_LLAMA, n_layers=3, n_kv_heads=case["n_kv_heads"])
+    cfg = dict(SMALL_LLAMA, n_layers=case.get("n_layers", 3), n_kv_heads=case["n_kv_heads"], seq_len=case.get("seq_len", SMALL_LLAMA["seq_len"]))
     tensors = synth.llama_tensors(cfg, 21, biases=case["qwen"], scale=0.002)
     if case["mixed"]:
         tensors["blk.0.attn_v.weight"] = synth.matrix(synth.Q6_K, 512, 512, 3, "v6", 0.002)
@@ -125,7 +127,7 @@ def test_prefill_matches_sequential_loop_and_oracle(case):
     seq, cpu, _ = llama_pair(cfg, biases=case["qwen"], qwen=case["qwen"], tensors=tensors)
     bat, _, _ = llama_pair(cfg, biases=case["qwen"], qwen=case["qwen"], tensors=tensors)
     bat.set_prefill(True)
-    n_prompt, n_gen = case["n_prompt"], 12
+    n_prompt, n_gen = case["n_prompt"], case.get("n_gen", 12)
     prompt = synth.prompt(n_prompt, cfg["vocab_size"], seed=5)
     tok_seq = seq.decode(prompt, n_gen)
     tok_bat = bat.decode(prompt, n_gen)

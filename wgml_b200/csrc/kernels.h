@@ -205,7 +205,12 @@ int launch_prefill_rope_append(const PrefillQkv &a, uint32_t ntok, cudaStream_t 
 // With `image` (allowed when prefill_attention_writes_image(head_size)) the kernel also writes the activation image of
 // its output, the input of the output projection.
 bool prefill_attention_writes_image(uint32_t head_size);
+// With scratch (prefill_attention_scratch_floats) and counters (prefill_attention_counters words, zero before the first
+// launch; the kernel leaves them zero) long contexts are split over several blocks per (head, pair of positions).
+size_t prefill_attention_scratch_floats(uint32_t n_heads, uint32_t head_size);
+size_t prefill_attention_counters(uint32_t n_heads);
 int launch_prefill_attention(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
-                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, cudaStream_t stream);
+                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, float *scratch,
+                             uint32_t *counters, cudaStream_t stream);
 
 }  // namespace wgb

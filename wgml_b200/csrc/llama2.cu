@@ -90,6 +90,8 @@ struct wgb_llama2 {
         uint8_t *img6 = nullptr;             // Q6_K image of the widest input
         float *x = nullptr, *xn = nullptr, *q = nullptr, *xb = nullptr, *h = nullptr;   // [PF_TOK][dim | q_dim | hidden]
         float *part[3] = {};                 // product slices: [PF_MAX_SPLIT][PF_TOK][max(dim, q_dim, hidden)]
+        float *attn_scratch = nullptr;       // prompt attention split over several blocks: partial sums
+        uint32_t *attn_counters = nullptr;   //   and arrival counters
         float *red = nullptr;                // tensor parallel: [PF_TOK][dim], a rank's partial product summed over the group
         size_t positions = 0;                // prompt positions that went through it, over all decode calls
     } pf;
@@ -407,7 +409,8 @@ void prefill_free(wgb_llama2 *m)
     m->pf.tiles.clear();
     uint8_t *imgs[] = { m->pf.img_dim, m->pf.img_q, m->pf.img_hidden, m->pf.img6 };
     for (uint8_t *b : imgs) if (b) cudaFree(b);
-    float *bufs[] = { m->pf.x, m->pf.xn, m->pf.q, m->pf.xb, m->pf.h, m->pf.part[0], m->pf.part[1], m->pf.part[2], m->pf.red };
+    float *bufs[] = { m->pf.x, m->pf.xn, m->pf.q, m->pf.xb, m->pf.h, m->pf.part[0], m->pf.part[1], m->pf.part[2], m->pf.red, m->pf.attn_scratch };
+    if (m->pf.attn_counters) cudaFree(m->pf.attn_counters);
     for (float *b : bufs) if (b) cudaFree(b);
     m->pf = wgb_llama2::Prefill();
 }
@@ -525,7 +528,7 @@ int prefill_pass(wgb_llama2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32
         if ((rc = launch_prefill_rope_append(qa, ntok, s))) return rc;
         const bool attn_image = prefill_attention_writes_image(m->head_size);
         if ((rc = launch_prefill_attention(pf.q, qa.k_cache, qa.v_cache, pf.xb, m->n_q_local, m->head_size, m->kv_mul, c.seq_len, pos0, ntok,
-                                           attn_image ? pf.img_q : nullptr, s)))
+                                           attn_image ? pf.img_q : nullptr, pf.attn_scratch, pf.attn_counters, s)))
             return rc;
         if (!attn_image && (rc = launch_prefill_norm_image(pf.xb, q_dim, nullptr, 0, 0, nullptr, 0.0f, q_dim, ntok, pf.img_q, nullptr, 0, s))) return rc;
         if ((rc = prefill_product(m, l, WGB_L_ATTN_OUTPUT, pf.img_q, pf.xb, q_dim, ntok, pf.part[0], dim, &no, s))) return rc;
@@ -1250,6 +1253,13 @@ WGB_EXPORT int wgb_llama2_set_prefill(wgb_llama2 *m, int enable)
     for (int i = 0; i < 3; i++)
         if ((rc = dalloc(&pf.part[i], (size_t)PF_MAX_SPLIT * PF_TOK * widest))) return bail(rc);
     if (m->tp_size > 1 && (rc = dalloc(&pf.red, (size_t)PF_TOK * c.dim))) return bail(rc);
+    if ((rc = dalloc(&pf.attn_scratch, prefill_attention_scratch_floats(m->n_q_local, m->head_size)))) return bail(rc);
+    {
+        const size_t nc = prefill_attention_counters(m->n_q_local);
+        cudaError_t e = cudaMalloc((void **)&pf.attn_counters, nc * 4);
+        if (e == cudaSuccess) e = cudaMemset(pf.attn_counters, 0, nc * 4);
+        if (e != cudaSuccess) { prefill_free(m); return cuda_fail(e, "cudaMalloc(prompt attention counters)"); }
+    }
     WGB_CUDA(cudaDeviceSynchronize());
     pf.enabled = true;
     return WGB_OK;

@@ -563,18 +563,21 @@ int launch_prefill_rope_append(const PrefillQkv &a, uint32_t ntok, cudaStream_t 
 // thread per value column (times a quarter of the chunk's rows) for the weighted sum.
 constexpr uint32_t PA_TQ = 2;        // positions per block
 constexpr uint32_t PA_CHUNK = 256;
+constexpr uint32_t PA_MAX_SPLIT = 8; // blocks that may share the rows of one (head, pair of positions)
 __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__restrict__ q, const float *__restrict__ k_cache,
                                                                 const float *__restrict__ v_cache, float *__restrict__ out, uint32_t q_dim,
                                                                 uint32_t head_size, uint32_t kv_mul, uint32_t seq_len, uint32_t pos0,
-                                                                uint32_t ntok, uint8_t *__restrict__ image)
+                                                                uint32_t ntok, uint8_t *__restrict__ image, float *__restrict__ scratch,
+                                                                uint32_t *__restrict__ counters)
 {
     extern __shared__ float pa_smem[];
     pdl_launch_dependents();
     pdl_wait();
-    const uint32_t h = blockIdx.x, t0 = blockIdx.y * PA_TQ;
+    // blockIdx.z: which of gridDim.z interleaved subsets of the 256-row chunks this block walks (long contexts)
+    const uint32_t h = blockIdx.x, t0 = blockIdx.y * PA_TQ, nz = gridDim.z, z = blockIdx.z;
     if (t0 >= ntok) {
         // with an image the grid covers all PF_TOK positions: the unused ones get zero digits
-        if (image)
+        if (image && z == 0)
             for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256)
                 image_quad(image, t0 + i / (head_size / 4), (h * head_size + 4 * (i % (head_size / 4))) >> 5, i & 7, make_float4(0.f, 0.f, 0.f, 0.f));
         return;
@@ -600,7 +603,7 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
     for (uint32_t tq = 0; tq < PA_TQ; tq++) acc[tq] = make_float4(0.f, 0.f, 0.f, 0.f);
     __syncthreads();
     const uint32_t last = pos0 + t0 + nq - 1;     // furthest row any of the block's positions attends to
-    for (uint32_t c0 = 0; c0 <= last; c0 += PA_CHUNK) {
+    for (uint32_t c0 = z * PA_CHUNK; c0 <= last; c0 += nz * PA_CHUNK) {
         // scores of row c0 + thread for the block's positions
         const uint32_t row = c0 + threadIdx.x;
         float s[PA_TQ];
@@ -673,6 +676,56 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
         for (uint32_t tq = 0; tq < PA_TQ; tq++) *reinterpret_cast<float4 *>(accs + ((size_t)rq * PA_TQ + tq) * head_size + 4 * cg) = acc[tq];
     }
     __syncthreads();
+    if (nz > 1) {
+        // Several blocks share the rows of this (head, pair of positions): each leaves its unnormalised sum, maximum
+        // and denominator in scratch, and the last to arrive (a counter that wraps back to zero) merges them in the
+        // order of blockIdx.z, so the result does not depend on which block that is.
+        __shared__ uint32_t s_last;
+        const uint32_t pstride = head_size + 4;   // per position: head_size sums, maximum, denominator
+        float *mine = scratch + (((size_t)h * gridDim.y + blockIdx.y) * nz + z) * PA_TQ * pstride;
+        for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256) {
+            const uint32_t tq = i / (head_size / 4), e4 = i % (head_size / 4);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t r4 = 0; r4 < 4; r4++) {
+                const float4 p = *reinterpret_cast<const float4 *>(accs + ((size_t)r4 * PA_TQ + tq) * head_size + 4 * e4);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
+            *reinterpret_cast<float4 *>(mine + tq * pstride + 4 * e4) = v;
+        }
+        if (threadIdx.x < PA_TQ) {
+            mine[threadIdx.x * pstride + head_size] = m_run[threadIdx.x];
+            mine[threadIdx.x * pstride + head_size + 1] = l_run[threadIdx.x];
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_last = atomicInc(counters + h * gridDim.y + blockIdx.y, nz - 1) == nz - 1;
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        const float *all = scratch + ((size_t)h * gridDim.y + blockIdx.y) * nz * PA_TQ * pstride;
+        for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256) {
+            const uint32_t tq = i / (head_size / 4), e4 = i % (head_size / 4);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (tq < nq) {
+                float mx = -INFINITY;
+                for (uint32_t zz = 0; zz < nz; zz++) mx = fmaxf(mx, __ldcg(all + ((size_t)zz * PA_TQ + tq) * pstride + head_size));
+                float den = 0.0f;
+                for (uint32_t zz = 0; zz < nz; zz++) {
+                    const float *p = all + ((size_t)zz * PA_TQ + tq) * pstride;
+                    const float mz = __ldcg(p + head_size);
+                    if (mz == -INFINITY) continue;   // a subset without a row this position attends to
+                    const float wgt = expf(mz - mx);
+                    const float4 a4 = __ldcg(reinterpret_cast<const float4 *>(p + 4 * e4));
+                    den = fmaf(wgt, __ldcg(p + head_size + 1), den);
+                    v.x = fmaf(wgt, a4.x, v.x); v.y = fmaf(wgt, a4.y, v.y); v.z = fmaf(wgt, a4.z, v.z); v.w = fmaf(wgt, a4.w, v.w);
+                }
+                v.x /= den; v.y /= den; v.z /= den; v.w /= den;
+                *reinterpret_cast<float4 *>(out + (size_t)(t0 + tq) * q_dim + h * head_size + 4 * e4) = v;
+            }
+            if (image) image_quad(image, t0 + tq, (h * head_size + 4 * e4) >> 5, e4 & 7, v);
+        }
+        return;
+    }
     // the block's output, four columns per thread; with `image` (head sizes that are multiples of 64, so that whole
     // warps take part) also its slice of the activation image of the output projection's input
     for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256) {
@@ -693,16 +746,33 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
 
 bool prefill_attention_writes_image(uint32_t head_size) { return head_size % 64 == 0; }
 
+size_t prefill_attention_scratch_floats(uint32_t n_heads, uint32_t head_size)
+{
+    return (size_t)n_heads * (PF_TOK / PA_TQ) * PA_MAX_SPLIT * PA_TQ * (head_size + 4);
+}
+size_t prefill_attention_counters(uint32_t n_heads) { return (size_t)n_heads * (PF_TOK / PA_TQ); }
+
 int launch_prefill_attention(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
-                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, cudaStream_t stream)
+                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, float *scratch,
+                             uint32_t *counters, cudaStream_t stream)
 {
     WGB_REQUIRE(!image || prefill_attention_writes_image(head_size), "prompt attention writes the image only for head sizes that are multiples of 64, got %u",
                 head_size);
     WGB_REQUIRE(head_size % 4 == 0 && head_size <= 256 && ntok >= 1 && ntok <= PF_TOK, "prompt attention: head size %u, %u positions", head_size,
                 ntok);
     const size_t smem = (size_t)(PA_TQ * head_size + PA_TQ * PA_CHUNK + 4 * PA_TQ * head_size) * sizeof(float);
-    WGB_CUDA(launch_pdl(prefill_attention_kernel, dim3(n_heads, image ? PF_TOK / PA_TQ : (ntok + PA_TQ - 1) / PA_TQ), dim3(256), smem, stream, q, k_cache,
-                        v_cache, out, n_heads * head_size, head_size, kv_mul, seq_len, pos0, ntok, image));
+    // Long contexts: the chunks of a (head, pair of positions) are dealt to several blocks, enough to fill the machine
+    // about twice, at most one block per chunk.
+    const uint32_t pairs = (ntok + PA_TQ - 1) / PA_TQ, chunks = (pos0 + ntok + PA_CHUNK - 1) / PA_CHUNK;
+    uint32_t nz = 1;
+    if (scratch && counters) {
+        const uint32_t want = (2u * (uint32_t)sm_count()) / (n_heads * pairs);
+        nz = want < 1 ? 1u : want;
+        if (nz > chunks) nz = chunks;
+        if (nz > PA_MAX_SPLIT) nz = PA_MAX_SPLIT;
+    }
+    WGB_CUDA(launch_pdl(prefill_attention_kernel, dim3(n_heads, image ? PF_TOK / PA_TQ : pairs, nz), dim3(256), smem, stream, q, k_cache, v_cache, out,
+                        n_heads * head_size, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters));
     return WGB_OK;
 }
 
