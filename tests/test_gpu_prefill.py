@@ -116,6 +116,8 @@ def _caches(gpu, n):
     dict(n_prompt=34, n_kv_heads=8, qwen=False, mixed=True),      # a Q6_K and a Q8_0 matrix among the Q4_K ones
     # a context of several 256-row chunks: the prompt attention of a (head, pair of positions) is shared by blocks
     dict(n_prompt=700, n_kv_heads=4, qwen=False, mixed=False, seq_len=720, n_layers=2, n_gen=6),
+    # eight chunks and more: eight positions per attention block
+    dict(n_prompt=1900, n_kv_heads=8, qwen=False, mixed=False, seq_len=1920, n_layers=1, n_gen=4),
 ])
 def test_prefill_matches_sequential_loop_and_oracle(case):
     cfg = dict(SMALL_LLAMA, n_layers=case.get("n_layers", 3), n_kv_heads=case["n_kv_heads"], seq_len=case.get("seq_len", SMALL_LLAMA["seq_len"]))

@@ -558,12 +558,13 @@ int launch_prefill_rope_append(const PrefillQkv &a, uint32_t ntok, cudaStream_t 
 // ---- causal attention of a batch of positions ----------------------------------------------------------
 
 // BatchedMultiqueryAttention (ops/batched_multiquery_attention.wgsl:42-122) for positions pos0 + t, t < ntok, each
-// attending to cache rows 0 .. pos0 + t.  One block per (query head, pair of positions); the block walks the
+// attending to cache rows 0 .. pos0 + t.  One block per (query head, group of TQ = 2, 4 or 8 positions); the block walks the
 // cache rows in chunks of 256 with a running maximum and sum (rescaled), one thread per row for the scores, one
 // thread per value column (times a quarter of the chunk's rows) for the weighted sum.
-constexpr uint32_t PA_TQ = 2;        // positions per block
+constexpr uint32_t PA_TQ_MIN = 2;    // positions per block: 2, 4 or 8 (more on longer contexts: a block's positions share its cache reads)
 constexpr uint32_t PA_CHUNK = 256;
 constexpr uint32_t PA_MAX_SPLIT = 8; // blocks that may share the rows of one (head, pair of positions)
+template <uint32_t TQ>
 __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__restrict__ q, const float *__restrict__ k_cache,
                                                                 const float *__restrict__ v_cache, float *__restrict__ out, uint32_t q_dim,
                                                                 uint32_t head_size, uint32_t kv_mul, uint32_t seq_len, uint32_t pos0,
@@ -574,62 +575,62 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
     pdl_launch_dependents();
     pdl_wait();
     // blockIdx.z: which of gridDim.z interleaved subsets of the 256-row chunks this block walks (long contexts)
-    const uint32_t h = blockIdx.x, t0 = blockIdx.y * PA_TQ, nz = gridDim.z, z = blockIdx.z;
+    const uint32_t h = blockIdx.x, t0 = blockIdx.y * TQ, nz = gridDim.z, z = blockIdx.z;
     if (t0 >= ntok) {
         // with an image the grid covers all PF_TOK positions: the unused ones get zero digits
         if (image && z == 0)
-            for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256)
+            for (uint32_t i = threadIdx.x; i < TQ * head_size / 4; i += 256)
                 image_quad(image, t0 + i / (head_size / 4), (h * head_size + 4 * (i % (head_size / 4))) >> 5, i & 7, make_float4(0.f, 0.f, 0.f, 0.f));
         return;
     }
-    const uint32_t nq = ntok - t0 < PA_TQ ? ntok - t0 : PA_TQ;
-    float *qs = pa_smem;                          // [PA_TQ][head_size]
-    float *sc = qs + PA_TQ * head_size;           // [PA_TQ][PA_CHUNK]
-    float *accs = sc + PA_TQ * PA_CHUNK;          // [4][PA_TQ][head_size]
-    __shared__ float red[PA_TQ][8];
-    __shared__ float m_run[PA_TQ], l_run[PA_TQ], m_new[PA_TQ], resc[PA_TQ];
+    const uint32_t nq = ntok - t0 < TQ ? ntok - t0 : TQ;
+    float *qs = pa_smem;                          // [TQ][head_size]
+    float *sc = qs + TQ * head_size;           // [TQ][PA_CHUNK]
+    float *accs = sc + TQ * PA_CHUNK;          // [4][TQ][head_size]
+    __shared__ float red[TQ][8];
+    __shared__ float m_run[TQ], l_run[TQ], m_new[TQ], resc[TQ];
     const float *kh = k_cache + (size_t)(h / kv_mul) * seq_len * head_size;
     const float *vh = v_cache + (size_t)(h / kv_mul) * seq_len * head_size;
     const float inv_sqrt = 1.0f / sqrtf((float)head_size);
-    for (uint32_t i = threadIdx.x; i < PA_TQ * head_size; i += 256) {
+    for (uint32_t i = threadIdx.x; i < TQ * head_size; i += 256) {
         const uint32_t tq = i / head_size, e = i % head_size;
         qs[i] = tq < nq ? q[(size_t)(t0 + tq) * q_dim + h * head_size + e] : 0.0f;
     }
-    if (threadIdx.x < PA_TQ) { m_run[threadIdx.x] = -INFINITY; l_run[threadIdx.x] = 0.0f; }
+    if (threadIdx.x < TQ) { m_run[threadIdx.x] = -INFINITY; l_run[threadIdx.x] = 0.0f; }
     // value columns: thread = (quarter of the chunk's rows, column group); head sizes up to 256 (four columns each)
     const uint32_t cg = threadIdx.x & 63, rq = threadIdx.x >> 6;
-    float4 acc[PA_TQ];
+    float4 acc[TQ];
 #pragma unroll
-    for (uint32_t tq = 0; tq < PA_TQ; tq++) acc[tq] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t tq = 0; tq < TQ; tq++) acc[tq] = make_float4(0.f, 0.f, 0.f, 0.f);
     __syncthreads();
     const uint32_t last = pos0 + t0 + nq - 1;     // furthest row any of the block's positions attends to
     for (uint32_t c0 = z * PA_CHUNK; c0 <= last; c0 += nz * PA_CHUNK) {
         // scores of row c0 + thread for the block's positions
         const uint32_t row = c0 + threadIdx.x;
-        float s[PA_TQ];
+        float s[TQ];
 #pragma unroll
-        for (uint32_t tq = 0; tq < PA_TQ; tq++) s[tq] = 0.0f;
+        for (uint32_t tq = 0; tq < TQ; tq++) s[tq] = 0.0f;
         if (row <= last) {
             const float4 *kr = reinterpret_cast<const float4 *>(kh + (size_t)row * head_size);
 #pragma unroll 8
             for (uint32_t e = 0; e < head_size / 4; e++) {
                 const float4 kv = kr[e];
 #pragma unroll
-                for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+                for (uint32_t tq = 0; tq < TQ; tq++) {
                     const float4 qv = *reinterpret_cast<const float4 *>(qs + tq * head_size + 4 * e);
                     s[tq] += kv.x * qv.x + kv.y * qv.y + kv.z * qv.z + kv.w * qv.w;
                 }
             }
         }
 #pragma unroll
-        for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+        for (uint32_t tq = 0; tq < TQ; tq++) {
             const bool live = tq < nq && row <= pos0 + t0 + tq;
             s[tq] = live ? s[tq] * inv_sqrt : -INFINITY;
             const float mx = warp_max(s[tq]);
             if ((threadIdx.x & 31) == 0) red[tq][threadIdx.x >> 5] = mx;
         }
         __syncthreads();
-        if (threadIdx.x < PA_TQ) {
+        if (threadIdx.x < TQ) {
             float mx = m_run[threadIdx.x];
             for (int i = 0; i < 8; i++) mx = fmaxf(mx, red[threadIdx.x][i]);
             m_new[threadIdx.x] = mx;
@@ -638,21 +639,21 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
         }
         __syncthreads();
 #pragma unroll
-        for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+        for (uint32_t tq = 0; tq < TQ; tq++) {
             const float p = s[tq] == -INFINITY ? 0.0f : expf(s[tq] - m_new[tq]);
             sc[tq * PA_CHUNK + threadIdx.x] = p;
             const float ps = warp_sum(p);
             if ((threadIdx.x & 31) == 0) red[tq][threadIdx.x >> 5] = ps;   // the maxima in red[] were consumed before the last barrier
         }
         __syncthreads();
-        if (threadIdx.x < PA_TQ) {
+        if (threadIdx.x < TQ) {
             float tot = 0.0f;
             for (int i = 0; i < 8; i++) tot += red[threadIdx.x][i];
             l_run[threadIdx.x] = l_run[threadIdx.x] * resc[threadIdx.x] + tot;
         }
         // weighted values: rows c0 + 64 rq .. + 63 of the chunk, columns 4 cg .. + 3
 #pragma unroll
-        for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+        for (uint32_t tq = 0; tq < TQ; tq++) {
             const float rs = resc[tq];
             acc[tq].x *= rs; acc[tq].y *= rs; acc[tq].z *= rs; acc[tq].w *= rs;
         }
@@ -662,7 +663,7 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
             for (uint32_t rr = c0 + 64 * rq; rr < r_end; rr++) {
                 const float4 vv = *reinterpret_cast<const float4 *>(vh + (size_t)rr * head_size + 4 * cg);
 #pragma unroll
-                for (uint32_t tq = 0; tq < PA_TQ; tq++) {
+                for (uint32_t tq = 0; tq < TQ; tq++) {
                     const float p = sc[tq * PA_CHUNK + (rr - c0)];
                     acc[tq].x = fmaf(p, vv.x, acc[tq].x); acc[tq].y = fmaf(p, vv.y, acc[tq].y);
                     acc[tq].z = fmaf(p, vv.z, acc[tq].z); acc[tq].w = fmaf(p, vv.w, acc[tq].w);
@@ -673,7 +674,7 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
     }
     if (4 * cg < head_size) {
 #pragma unroll
-        for (uint32_t tq = 0; tq < PA_TQ; tq++) *reinterpret_cast<float4 *>(accs + ((size_t)rq * PA_TQ + tq) * head_size + 4 * cg) = acc[tq];
+        for (uint32_t tq = 0; tq < TQ; tq++) *reinterpret_cast<float4 *>(accs + ((size_t)rq * TQ + tq) * head_size + 4 * cg) = acc[tq];
     }
     __syncthreads();
     if (nz > 1) {
@@ -682,17 +683,17 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
         // order of blockIdx.z, so the result does not depend on which block that is.
         __shared__ uint32_t s_last;
         const uint32_t pstride = head_size + 4;   // per position: head_size sums, maximum, denominator
-        float *mine = scratch + (((size_t)h * gridDim.y + blockIdx.y) * nz + z) * PA_TQ * pstride;
-        for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256) {
+        float *mine = scratch + (((size_t)h * gridDim.y + blockIdx.y) * nz + z) * TQ * pstride;
+        for (uint32_t i = threadIdx.x; i < TQ * head_size / 4; i += 256) {
             const uint32_t tq = i / (head_size / 4), e4 = i % (head_size / 4);
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             for (uint32_t r4 = 0; r4 < 4; r4++) {
-                const float4 p = *reinterpret_cast<const float4 *>(accs + ((size_t)r4 * PA_TQ + tq) * head_size + 4 * e4);
+                const float4 p = *reinterpret_cast<const float4 *>(accs + ((size_t)r4 * TQ + tq) * head_size + 4 * e4);
                 v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
             }
             *reinterpret_cast<float4 *>(mine + tq * pstride + 4 * e4) = v;
         }
-        if (threadIdx.x < PA_TQ) {
+        if (threadIdx.x < TQ) {
             mine[threadIdx.x * pstride + head_size] = m_run[threadIdx.x];
             mine[threadIdx.x * pstride + head_size + 1] = l_run[threadIdx.x];
         }
@@ -702,16 +703,16 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
         __syncthreads();
         if (!s_last) return;
         __threadfence();
-        const float *all = scratch + ((size_t)h * gridDim.y + blockIdx.y) * nz * PA_TQ * pstride;
-        for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256) {
+        const float *all = scratch + ((size_t)h * gridDim.y + blockIdx.y) * nz * TQ * pstride;
+        for (uint32_t i = threadIdx.x; i < TQ * head_size / 4; i += 256) {
             const uint32_t tq = i / (head_size / 4), e4 = i % (head_size / 4);
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (tq < nq) {
                 float mx = -INFINITY;
-                for (uint32_t zz = 0; zz < nz; zz++) mx = fmaxf(mx, __ldcg(all + ((size_t)zz * PA_TQ + tq) * pstride + head_size));
+                for (uint32_t zz = 0; zz < nz; zz++) mx = fmaxf(mx, __ldcg(all + ((size_t)zz * TQ + tq) * pstride + head_size));
                 float den = 0.0f;
                 for (uint32_t zz = 0; zz < nz; zz++) {
-                    const float *p = all + ((size_t)zz * PA_TQ + tq) * pstride;
+                    const float *p = all + ((size_t)zz * TQ + tq) * pstride;
                     const float mz = __ldcg(p + head_size);
                     if (mz == -INFINITY) continue;   // a subset without a row this position attends to
                     const float wgt = expf(mz - mx);
@@ -728,12 +729,12 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
     }
     // the block's output, four columns per thread; with `image` (head sizes that are multiples of 64, so that whole
     // warps take part) also its slice of the activation image of the output projection's input
-    for (uint32_t i = threadIdx.x; i < PA_TQ * head_size / 4; i += 256) {
+    for (uint32_t i = threadIdx.x; i < TQ * head_size / 4; i += 256) {
         const uint32_t tq = i / (head_size / 4), e4 = i % (head_size / 4);
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (tq < nq) {
             for (uint32_t r4 = 0; r4 < 4; r4++) {
-                const float4 p = *reinterpret_cast<const float4 *>(accs + ((size_t)r4 * PA_TQ + tq) * head_size + 4 * e4);
+                const float4 p = *reinterpret_cast<const float4 *>(accs + ((size_t)r4 * TQ + tq) * head_size + 4 * e4);
                 v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
             }
             const float l = l_run[tq];
@@ -748,9 +749,30 @@ bool prefill_attention_writes_image(uint32_t head_size) { return head_size % 64 
 
 size_t prefill_attention_scratch_floats(uint32_t n_heads, uint32_t head_size)
 {
-    return (size_t)n_heads * (PF_TOK / PA_TQ) * PA_MAX_SPLIT * PA_TQ * (head_size + 4);
+    return (size_t)n_heads * PF_TOK * PA_MAX_SPLIT * (head_size + 4);   // per (head, position, block): sums, maximum, denominator
 }
-size_t prefill_attention_counters(uint32_t n_heads) { return (size_t)n_heads * (PF_TOK / PA_TQ); }
+size_t prefill_attention_counters(uint32_t n_heads) { return (size_t)n_heads * (PF_TOK / PA_TQ_MIN); }
+
+template <uint32_t TQ>
+static int launch_prefill_attention_tq(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
+                                       uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, float *scratch,
+                                       uint32_t *counters, uint32_t chunks, cudaStream_t stream)
+{
+    const size_t smem = (size_t)(TQ * head_size + TQ * PA_CHUNK + 4 * TQ * head_size) * sizeof(float);
+    // Long contexts: the chunks of a (head, group of positions) are dealt to several blocks, enough to fill the machine
+    // about twice, at most one block per chunk.
+    const uint32_t groups = (ntok + TQ - 1) / TQ;
+    uint32_t nz = 1;
+    if (scratch && counters) {
+        const uint32_t want = (2u * (uint32_t)sm_count()) / (n_heads * groups);
+        nz = want < 1 ? 1u : want;
+        if (nz > chunks) nz = chunks;
+        if (nz > PA_MAX_SPLIT) nz = PA_MAX_SPLIT;
+    }
+    WGB_CUDA(launch_pdl(prefill_attention_kernel<TQ>, dim3(n_heads, image ? PF_TOK / TQ : groups, nz), dim3(256), smem, stream, q, k_cache, v_cache, out,
+                        n_heads * head_size, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters));
+    return WGB_OK;
+}
 
 int launch_prefill_attention(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
                              uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, float *scratch,
@@ -760,20 +782,15 @@ int launch_prefill_attention(const float *q, const float *k_cache, const float *
                 head_size);
     WGB_REQUIRE(head_size % 4 == 0 && head_size <= 256 && ntok >= 1 && ntok <= PF_TOK, "prompt attention: head size %u, %u positions", head_size,
                 ntok);
-    const size_t smem = (size_t)(PA_TQ * head_size + PA_TQ * PA_CHUNK + 4 * PA_TQ * head_size) * sizeof(float);
-    // Long contexts: the chunks of a (head, pair of positions) are dealt to several blocks, enough to fill the machine
-    // about twice, at most one block per chunk.
-    const uint32_t pairs = (ntok + PA_TQ - 1) / PA_TQ, chunks = (pos0 + ntok + PA_CHUNK - 1) / PA_CHUNK;
-    uint32_t nz = 1;
-    if (scratch && counters) {
-        const uint32_t want = (2u * (uint32_t)sm_count()) / (n_heads * pairs);
-        nz = want < 1 ? 1u : want;
-        if (nz > chunks) nz = chunks;
-        if (nz > PA_MAX_SPLIT) nz = PA_MAX_SPLIT;
-    }
-    WGB_CUDA(launch_pdl(prefill_attention_kernel, dim3(n_heads, image ? PF_TOK / PA_TQ : pairs, nz), dim3(256), smem, stream, q, k_cache, v_cache, out,
-                        n_heads * head_size, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters));
-    return WGB_OK;
+    // Positions per block: two on short contexts (most blocks), four and eight as the cache rows to read grow, provided
+    // the chunks can still be dealt to enough blocks.
+    const uint32_t chunks = (pos0 + ntok + PA_CHUNK - 1) / PA_CHUNK;
+    const bool split = scratch && counters;
+    if (split && chunks >= 8 && head_size <= 128)
+        return launch_prefill_attention_tq<8>(q, k_cache, v_cache, out, n_heads, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters, chunks, stream);
+    if (split && chunks >= 3)
+        return launch_prefill_attention_tq<4>(q, k_cache, v_cache, out, n_heads, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters, chunks, stream);
+    return launch_prefill_attention_tq<2>(q, k_cache, v_cache, out, n_heads, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters, chunks, stream);
 }
 
 // Raw row-major Q4_K blocks -> [tile][column][row in tile][144 bytes].  One thread per 16 bytes.
