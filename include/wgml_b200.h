@@ -123,6 +123,13 @@ typedef struct wgb_q6k_tiles wgb_q6k_tiles;
 int wgb_q6k_tiles_create(const void *h_blocks, size_t nrows, size_t ncols, void *stream, wgb_q6k_tiles **out);
 int wgb_q6k_tiles_destroy(wgb_q6k_tiles *m);
 int wgb_gemm_q6k_tiles(wgb_q6k_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream);
+/* The batched product for Q8_0 matrices (BlockQ8_0, quantization.rs:29-52): the signed byte codes are the tensor-core
+ * operand as they are, kept in HBM in the operand's shared-memory image (128-byte swizzle applied), so a bulk copy
+ * lands a unit where the MMAs read it.  h_blocks: raw GGUF blocks, nrows a multiple of 128, ncols of 256. */
+typedef struct wgb_q80_tiles wgb_q80_tiles;
+int wgb_q80_tiles_create(const void *h_blocks, size_t nrows, size_t ncols, void *stream, wgb_q80_tiles **out);
+int wgb_q80_tiles_destroy(wgb_q80_tiles *m);
+int wgb_gemm_q80_tiles(wgb_q80_tiles *m, const float *d_v, size_t n_vec, float *d_out, void *stream);
 /* Waits for the device and returns WGB_ERR_TIMEOUT if a bounded wait inside a matrix-vector kernel has
  * expired since the last report (stand-alone launches are asynchronous and cannot say so themselves). */
 int wgb_device_status(void);
@@ -411,7 +418,8 @@ int wgb_llama2_set_sampler(wgb_llama2 *m, float temperature, float topp, uint64_
  * sends every prompt position but the last through passes of eight positions: the Q4_K layer matrices are
  * multiplied on the tensor cores (tcgen05.mma kind::i8 on the same fixed-point image of the activations as the
  * matrix-vector kernels, from tile-major copies of the weights made here, which doubles their memory), the Q6_K
- * ones by a kernel of their own (scales folded into the weight operand), other formats through the matrix-vector
+ * and Q8_0 ones by kernels of their own (Q6_K: scales folded into the weight operand; Q8_0: the codes are the operand),
+ * other formats through the matrix-vector
  * kernel position by position; RMSNorm, RoPE, the cache rows and causal attention are computed per pass.  Cache rows and everything after the prompt agree with the
  * position-by-position path to the order of the f32 additions.  A tensor-parallel rank sums its partial attn_output
  * and ffn_down products over the group with one all-reduce each per pass and layer (call wgb_llama2_set_comm first,

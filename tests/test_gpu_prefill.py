@@ -58,6 +58,28 @@ def test_batched_q6k_product_vs_oracle(shape):
         assert_close(got[i], o64, RTOL, atol, f"batched Q6_K product {nrows}x{ncols}, vector {i} of {n_vec}")
 
 
+@pytest.mark.parametrize("shape", [(128, 256, 8), (256, 512, 3), (768, 768, 8), (3072, 768, 8), (768, 3072, 5), (4096, 4096, 8)])
+def test_batched_q80_product_vs_oracle(shape):
+    """The Q8_0 kernel (codes as the operand, read from the ring stage the copy landed them in)."""
+    nrows, ncols, n_vec = shape
+    qt, arr = synth.matrix(ops.Q8_0, nrows, ncols, 13, "pf8")
+    raw = np.ascontiguousarray(arr).view(np.uint8).reshape(-1).copy()
+    blocks = raw.reshape(-1, 34)
+    blocks[::7, 2:] = 0x80      # whole blocks of -128, the code the operand format must keep signed
+    blocks[3::11, 2:] = 0x7F
+    x = np.random.default_rng(5).standard_normal((n_vec, ncols)).astype(np.float32)
+    x *= (10.0 ** np.arange(-3, -3 + n_vec))[:, None].astype(np.float32)
+    t = ops.Q80Tiles(raw, nrows, ncols)
+    out = torch.full((n_vec, nrows), float("nan"), device="cuda")
+    t.gemm(out, torch.from_numpy(x).cuda())
+    ops.device_status()
+    got = out.cpu().numpy()
+    for i in range(n_vec):
+        _, o64 = oracle.gemv_quant(ops.Q8_0, raw, nrows, ncols, x[i], want_f64=True)
+        atol = ATOL * float(np.sqrt(np.mean(o64 ** 2)))
+        assert_close(got[i], o64, RTOL, atol, f"batched Q8_0 product {nrows}x{ncols}, vector {i} of {n_vec}")
+
+
 def test_batched_q6k_product_extreme_scales_and_codes():
     """All-0x00 / all-0xFF code bytes and scales of -128 / 127: the largest magnitudes of the folded operand."""
     nrows, ncols = 128, 512
@@ -126,6 +148,7 @@ def test_prefill_matches_sequential_loop_and_oracle(case):
         tensors["blk.0.attn_v.weight"] = synth.matrix(synth.Q6_K, 512, 512, 3, "v6", 0.002)
         tensors["blk.1.ffn_down.weight"] = synth.matrix(synth.Q6_K, 512, 1024, 3, "d6", 0.002)
         tensors["blk.2.ffn_up.weight"] = synth.matrix(synth.Q8_0, 1024, 512, 3, "up8", 0.002)
+        tensors["blk.1.attn_q.weight"] = synth.matrix(synth.Q5_K, 512, 512, 3, "q5", 0.002)   # no tensor-core path: position by position
     seq, cpu, _ = llama_pair(cfg, biases=case["qwen"], qwen=case["qwen"], tensors=tensors)
     bat, _, _ = llama_pair(cfg, biases=case["qwen"], qwen=case["qwen"], tensors=tensors)
     bat.set_prefill(True)
@@ -169,6 +192,24 @@ def test_prefill_resumes_at_a_later_position_and_can_be_switched_off():
     b.set_prefill(False)
     assert b.prefill_positions() == 0
     assert np.array_equal(b.decode(p1, 3), ta[: 17 + 3])
+
+
+def test_prefill_with_the_sampler_and_up_to_the_last_cache_row():
+    """Sampled generation after a batched prompt equals sampled generation after a position-by-position prompt (same
+    seed: the coin depends on the position only), and a sequence may end on the last row of the cache."""
+    cfg = dict(SMALL_LLAMA, n_layers=2, seq_len=64)
+    a, _, t = llama_pair(cfg, seed=12, scale=0.002)
+    b, _, _ = llama_pair(cfg, tensors=t)
+    b.set_prefill(True)
+    for m in (a, b):
+        m.set_sampler(0.9, 0.95, seed=77)
+    prompt = synth.prompt(41, cfg["vocab_size"], seed=3)
+    n_gen = cfg["seq_len"] - 40          # positions 0 .. 63: the last step writes cache row 63
+    ta, tb = a.decode(prompt, n_gen), b.decode(prompt, n_gen)
+    assert b.prefill_positions() == 40
+    assert np.array_equal(ta, tb)
+    with pytest.raises(_lib.WgbError):   # one step more would leave the cache
+        b.decode(prompt, n_gen + 1)
 
 
 def test_prefill_of_a_tensor_parallel_rank_wants_its_communicator():

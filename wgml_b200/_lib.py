@@ -83,6 +83,9 @@ SIGNATURES = {
     "wgb_q6k_tiles_create": (_i, [_vp, _sz, _sz, _vp, C.POINTER(_vp)]),
     "wgb_q6k_tiles_destroy": (_i, [_vp]),
     "wgb_gemm_q6k_tiles": (_i, [_vp, _vp, _sz, _vp, _vp]),
+    "wgb_q80_tiles_create": (_i, [_vp, _sz, _sz, _vp, C.POINTER(_vp)]),
+    "wgb_q80_tiles_destroy": (_i, [_vp]),
+    "wgb_gemm_q80_tiles": (_i, [_vp, _vp, _sz, _vp, _vp]),
     "wgb_device_status": (_i, []),
     "wgb_rms_norm": (_i, [_vp, _vp, _vp, _sz, _f, _vp]),
     "wgb_layernorm": (_i, [_vp, _vp, _sz, _vp]),

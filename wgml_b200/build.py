@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "csrc", "build")
 LIB = os.path.join(HERE, "libwgml_b200.so")
 
-SOURCES = ["api.cpp", "gguf.cpp", "tokenizer.cpp", "quant.cu", "gemv.cu", "gemv_tc.cu", "attention.cu", "ops.cu", "sampler.cu", "prefill.cu", "prefill_q6k.cu", "llama2.cu", "gpt2.cu", "comm.cpp"]
+SOURCES = ["api.cpp", "gguf.cpp", "tokenizer.cpp", "quant.cu", "gemv.cu", "gemv_tc.cu", "attention.cu", "ops.cu", "sampler.cu", "prefill.cu", "prefill_q6k.cu", "prefill_q80.cu", "llama2.cu", "gpt2.cu", "comm.cpp"]
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-fvisibility=hidden",

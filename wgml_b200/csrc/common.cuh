@@ -50,6 +50,7 @@ struct DeviceState {
     bool tiles_attrs = false;             // the same for the tensor-memory kernel
     bool prefill_attrs = false;           // the same for the batched tensor-memory kernel
     bool prefill6_attrs = false;          // the same for its Q6_K counterpart
+    bool prefill8_attrs = false;          // and its Q8_0 counterpart
     float *attn_scratch = nullptr;        // scratch of the stand-alone attention op, grown on demand
     size_t attn_scratch_floats = 0;
     uint32_t *attn_counters = nullptr;

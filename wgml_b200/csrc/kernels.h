@@ -162,6 +162,9 @@ int launch_sample(const float *logits, uint32_t n, float temperature, float topp
 // ---- batched prompt prefill (prefill.cu) --------------------------------------------------------------
 constexpr uint32_t PF_TOK = 8;         // prompt positions per pass
 constexpr uint32_t PF_MAX_SPLIT = 8;   // column slices of one product
+// Bytes of the activation image per 256-column unit: 16 K-cores x 4 row groups x 128 bytes of digits, then one exponent
+// and one sum per 32-column group and position.
+constexpr uint32_t prefill_image_unit_bytes() { return 16 * 4 * 128 + 2 * 8 * PF_TOK * 4; }
 // Bytes of the fixed-point activation image of PF_TOK vectors of K elements (zero it once: the kernels never
 // write its padding rows).
 size_t prefill_image_bytes(uint32_t K);
@@ -190,6 +193,12 @@ bool prefill_tileable6(const QMat &m);
 int prefill_tile_major6(const QMat &m, uint8_t **out, cudaStream_t stream);
 int launch_prefill_image6(const float *x, uint32_t x_stride, uint32_t K, uint32_t ntok, uint8_t *image, cudaStream_t stream);
 int launch_gemm_q6k_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, const uint8_t *image, uint32_t ntok, float *out,
+                          uint32_t out_stride, uint32_t nsplit, cudaStream_t stream);
+// The Q8_0 counterpart (prefill_q80.cu): the codes are the operand as they are, kept in HBM in the operand's
+// shared-memory image; it reads the same activation image as the Q4_K product.
+bool prefill_tileable8(const QMat &m);
+int prefill_tile_major8(const QMat &m, uint8_t **out, cudaStream_t stream);
+int launch_gemm_q80_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, const uint8_t *image, uint32_t ntok, float *out,
                           uint32_t out_stride, uint32_t nsplit, cudaStream_t stream);
 struct PrefillQkv {
     const float *q, *k, *v;            // product slices: [split][PF_TOK][stride]

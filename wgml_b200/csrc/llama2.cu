@@ -85,7 +85,7 @@ struct wgb_llama2 {
     struct Prefill {
         bool enabled = false;
         std::vector<uint8_t *> tiles;        // [layer * 7 + matrix], NULL: no tensor-core path for that matrix
-        std::vector<uint8_t> tiles_q6;       // same index: the copy is a Q6_K one (its own kernel and image)
+        std::vector<uint8_t> tiles_q6;       // same index: 0 a Q4_K copy, 1 a Q6_K one (its own kernel and image), 2 a Q8_0 one
         uint8_t *img_dim = nullptr, *img_q = nullptr, *img_hidden = nullptr;
         uint8_t *img6 = nullptr;             // Q6_K image of the widest input
         float *x = nullptr, *xn = nullptr, *q = nullptr, *xb = nullptr, *h = nullptr;   // [PF_TOK][dim | q_dim | hidden]
@@ -423,7 +423,11 @@ int prefill_product(wgb_llama2 *m, uint32_t layer, int which, const uint8_t *ima
 {
     const QMat &w = m->layers[layer].m[which]->view;
     const uint8_t *tiles = m->pf.tiles[(size_t)layer * 7 + which];
-    if (tiles && m->pf.tiles_q6[(size_t)layer * 7 + which]) {
+    if (tiles && m->pf.tiles_q6[(size_t)layer * 7 + which] == 2) {
+        *nsplit = prefill_gemm_splits(w.nrows, w.ncols);
+        return launch_gemm_q80_tiles(tiles, w.nrows, w.ncols, image, ntok, out, stride, *nsplit, s);
+    }
+    if (tiles && m->pf.tiles_q6[(size_t)layer * 7 + which] == 1) {
         *nsplit = prefill_gemm_splits(w.nrows, w.ncols);
         int rc = launch_prefill_image6(xf, xf_stride, w.ncols, ntok, m->pf.img6, s);
         if (rc) return rc;
@@ -1237,6 +1241,10 @@ WGB_EXPORT int wgb_llama2_set_prefill(wgb_llama2 *m, int enable)
             if (prefill_tileable6(w)) {
                 if ((rc = prefill_tile_major6(w, &pf.tiles[(size_t)l * 7 + i], nullptr))) return bail(rc);
                 pf.tiles_q6[(size_t)l * 7 + i] = 1;
+            }
+            if (prefill_tileable8(w)) {
+                if ((rc = prefill_tile_major8(w, &pf.tiles[(size_t)l * 7 + i], nullptr))) return bail(rc);
+                pf.tiles_q6[(size_t)l * 7 + i] = 2;
             }
         }
     auto image = [&](uint8_t **p, uint32_t K) -> int {

@@ -42,6 +42,7 @@ constexpr uint32_t TB_OFF_A = 0;                                          // two
 constexpr uint32_t TB_OFF_RING = TB_OFF_A + 2 * TC_A_BYTES;
 constexpr uint32_t TB_SMEM = TB_OFF_RING + TB_RING * TB_STAGE;
 static_assert(PF_TOK == 8, "one core matrix (eight rows) per digit");
+static_assert(TB_IMG_BYTES == prefill_image_unit_bytes(), "the image layout other kernels rely on");
 static_assert(TB_STAGE % 128 == 0 && TB_IMG_BYTES % 16 == 0, "stages keep the operand alignment");
 static_assert(TB_SMEM + 1024 + 20 * 1024 <= 227 * 1024, "shared memory budget (dynamic + static)");
 

@@ -175,6 +175,33 @@ class Q6KTiles:
                 pass
 
 
+class Q80Tiles:
+    """A Q8_0 matrix in the tile-major layout of the batched tensor-core product (nrows a multiple of 128, ncols
+    of 256), built from raw GGUF blocks in host memory."""
+
+    def __init__(self, blocks, nrows: int, ncols: int):
+        require_device()
+        raw = np.ascontiguousarray(blocks).view(np.uint8).reshape(-1)
+        GpuQuantMatrix._check_size(Q8_0, raw.size, nrows, ncols)
+        self._h = C.c_void_p()
+        check(_lib.load().wgb_q80_tiles_create(raw.ctypes.data, nrows, ncols, _stream(), C.byref(self._h)))
+        self.nrows, self.ncols = nrows, ncols
+
+    def gemm(self, out: torch.Tensor, v: torch.Tensor) -> None:
+        """The product for 1..8 input vectors at once: v [n][ncols] -> out [n][nrows]."""
+        if v.dim() != 2 or out.dim() != 2 or v.shape[1] != self.ncols or out.shape[1] != self.nrows or v.shape[0] != out.shape[0]:
+            raise WgbError(_lib.ERR_INVALID, "Gemm: dimension mismatch.")
+        check(_lib.load().wgb_gemm_q80_tiles(self._h, _f32(v, "v"), v.shape[0], _f32(out, "out"), _stream()))
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _lib.load().wgb_q80_tiles_destroy(h)
+            except Exception:
+                pass
+
+
 def device_status() -> None:
     """Waits for the device; raises if a bounded wait inside a matrix-vector kernel has expired."""
     check(_lib.load().wgb_device_status())
