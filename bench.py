@@ -440,7 +440,7 @@ def run_b200(args):
                            "sequential": {"ms": seq_ms, "tok_s": (prompt_len - 1) / (seq_ms * 1e-3)},
                            "batched": {"ms": bat_ms, "tok_s": (prompt_len - 1) / (bat_ms * 1e-3)},
                            "how": "wgb_llama2_decode(prompt, n_gen = 0) between CUDA events, best of 2; batched = after "
-                                  "wgb_llama2_set_prefill(1); Q4_K and Q6_K products on tcgen05, other formats position by position inside a pass"}
+                                  "wgb_llama2_set_prefill(1); Q4_K, Q6_K and Q8_0 products on tcgen05, other formats position by position inside a pass"}
     if rank == 0 and world == 1 and workload == "llama2-7b" and not args.no_microbench:
         # the stand-alone quantised matrix-vector cases (4 shapes x 3 block formats), each launch on a fresh copy
         # of the matrix so that it streams from HBM: microseconds, algorithmic GB/s and fraction of the measured peak

@@ -13,7 +13,7 @@ is replayed three times between CUDA events.  The figure printed is algorithmic 
 (rows * cols * bytes-per-weight of the GGUF format + 4 * cols + 4 * rows) per second.
 `--eager N` instead issues N plain launches and exits; it exists for profilers, which want few launches.
 `--tensor` times the tcgen05 path (`wgb_gemv_q4k_tiles`, Q4_K, up to 4096 columns) instead of `wgb_gemv_quant`.
-`--batched N` times the batched tcgen05 product of the prompt prefill (`wgb_gemm_q4k_tiles`, Q4_K, N = 1..8 input
+`--batched N` times the batched tcgen05 products of the prompt prefill (`wgb_gemm_q4k_tiles` / `_q6k_` / `_q80_`, N = 1..8 input
 vectors per launch: image of the inputs, product, sum of the column slices).
 """
 from __future__ import annotations
@@ -39,8 +39,11 @@ def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False, batched=0):
         for (n, k) in shapes:
             if tensor and (qt != synth.Q4_K or k > 4096 or n % 128):
                 continue
-            if batched and (qt != synth.Q4_K or k % 256 or n % 128):
+            if batched and (qt not in (synth.Q4_K, synth.Q6_K, synth.Q8_0) or k % 256 or n % 128):
                 continue
+            tiles = {synth.Q4_K: ("wgb_q4k_tiles_create", "wgb_gemm_q4k_tiles", "wgb_q4k_tiles_destroy"),
+                     synth.Q6_K: ("wgb_q6k_tiles_create", "wgb_gemm_q6k_tiles", "wgb_q6k_tiles_destroy"),
+                     synth.Q8_0: ("wgb_q80_tiles_create", "wgb_gemm_q80_tiles", "wgb_q80_tiles_destroy")}.get(qt)
             nbytes = n * k * BPE[qt]
             ncopy = max(2, int(np.ceil(400e6 / nbytes)))
             rng = np.random.default_rng(1)
@@ -51,7 +54,9 @@ def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False, batched=0):
             mats = []
             for _ in range(ncopy):
                 h = C.c_void_p()
-                if tensor or batched:
+                if batched:
+                    _lib.check(getattr(lib, tiles[0])(raw.ctypes.data, n, k, None, C.byref(h)))
+                elif tensor:
                     _lib.check(lib.wgb_q4k_tiles_create(raw.ctypes.data, n, k, None, C.byref(h)))
                 else:
                     _lib.check(lib.wgb_quant_matrix_create(qt, raw.ctypes.data, n, k, None, C.byref(h)))
@@ -60,8 +65,8 @@ def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False, batched=0):
             x = torch.randn(max(batched, 1), k, device="cuda")
             y = torch.zeros(max(batched, 1), n, device="cuda")
             if batched:
-                def gemv(h, xp, yp, stream):
-                    return lib.wgb_gemm_q4k_tiles(h, xp, batched, yp, stream)
+                def gemv(h, xp, yp, stream, _f=getattr(lib, tiles[1])):
+                    return _f(h, xp, batched, yp, stream)
             st = torch.cuda.current_stream().cuda_stream
             if eager:
                 for it in range(eager):
@@ -90,7 +95,7 @@ def run(qtypes, shapes, reps, eager, peak_gbs, tensor=False, batched=0):
                 out.append({"qtype": name + ("/tcgen05" if tensor else f"/tcgen05 x{batched}" if batched else ""), "rows": n, "cols": k, "us": us, "bytes": alg, "gbs": alg / us / 1e3,
                             "frac_of_measured_peak": alg / us / 1e3 / peak_gbs, "copies": ncopy})
             for h in mats:
-                (lib.wgb_q4k_tiles_destroy if tensor or batched else lib.wgb_quant_matrix_destroy)(h)
+                (getattr(lib, tiles[2]) if batched else lib.wgb_q4k_tiles_destroy if tensor else lib.wgb_quant_matrix_destroy)(h)
     return out
 
 
