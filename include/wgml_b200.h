@@ -536,6 +536,12 @@ float *wgb_gpt2_key_cache(wgb_gpt2 *m, uint32_t layer);
 float *wgb_gpt2_value_cache(wgb_gpt2 *m, uint32_t layer);
 /* As wgb_llama2_set_sampler. */
 int wgb_gpt2_set_sampler(wgb_gpt2 *m, float temperature, float topp, uint64_t seed);
+/* Batched prompt prefill as wgb_llama2_set_prefill, for Gpt2::dispatch (models/gpt2/transformer.rs:265-477): passes of
+ * eight positions with LayerNorm, the fused qkv product and its split into cache rows, causal attention, the
+ * projections and GELU computed per pass; Q8_0 / Q4_K / Q6_K matrices on the tensor cores.  The reference's loop
+ * (chat_gpt2.rs:43-151) feeds the prompt one position per dispatch. */
+int wgb_gpt2_set_prefill(wgb_gpt2 *m, int enable);
+int wgb_gpt2_prefill_positions(const wgb_gpt2 *m, size_t *positions);
 /* ChatGpt2::forward's loop (crates/wgml-chat/src/chat_gpt2.rs:43-151), device-resident. */
 int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_prompt, size_t n_gen,
                     uint32_t start_pos, uint32_t *h_out_tokens, void *stream);

@@ -7,7 +7,7 @@ import torch
 
 import oracle
 from conftest import ATOL, RTOL, assert_close
-from helpers import SMALL_LLAMA, llama_pair
+from helpers import SMALL_GPT2, SMALL_LLAMA, gpt2_pair, llama_pair
 from wgml_b200 import _lib, ops, synth
 
 pytestmark = pytest.mark.gpu
@@ -210,6 +210,39 @@ def test_prefill_with_the_sampler_and_up_to_the_last_cache_row():
     assert np.array_equal(ta, tb)
     with pytest.raises(_lib.WgbError):   # one step more would leave the cache
         b.decode(prompt, n_gen + 1)
+
+
+@pytest.mark.parametrize("case", [
+    dict(cfg=dict(SMALL_GPT2), n_prompt=45, qtype=synth.Q8_0),                                   # five passes and a short one
+    dict(cfg=dict(SMALL_GPT2), n_prompt=19, qtype=synth.Q5_1),                                   # no tensor-core copy: per position
+    dict(cfg=dict(synth.CONFIGS["gpt2-124m"], n_layer=2), n_prompt=300, qtype=synth.Q8_0),       # 124M widths, two chunks of context
+])
+def test_gpt2_prefill_matches_sequential_loop_and_oracle(case):
+    cfg = dict(case["cfg"], default_qtype=case["qtype"])
+    seq, cpu, _ = gpt2_pair(cfg, seed=31, scale=0.002)
+    bat, _, _ = gpt2_pair(cfg, seed=31, scale=0.002)
+    bat.set_prefill(True)
+    n_prompt, n_gen = case["n_prompt"], 10
+    prompt = synth.prompt(n_prompt, cfg["n_vocab"], seed=7)
+    tok_seq = seq.decode(prompt, n_gen)
+    tok_bat = bat.decode(prompt, n_gen)
+    rem = (n_prompt - 1) % 8
+    assert bat.prefill_positions() == n_prompt - 1 - (rem if rem < 4 else 0)
+    exp = cpu.decode(prompt, n_gen)
+    assert np.array_equal(tok_bat[: n_prompt - 1], prompt[1:])
+    assert np.array_equal(tok_bat, tok_seq), "greedy tokens differ between batched and sequential prefill"
+    assert np.array_equal(tok_bat, exp), "greedy tokens differ from the oracle"
+    n = n_prompt - 1 + n_gen
+    kc, vc = cpu.caches()
+    for l in range(bat.params.n_layer):
+        sk = max(1.0, float(np.abs(kc[l, :n]).max()))
+        sv = max(1.0, float(np.abs(vc[l, :n]).max()))
+        assert_close(bat.key_cache(l)[:n].cpu().numpy(), kc[l, :n], RTOL, ATOL * sk, f"key cache {l} vs oracle")
+        assert_close(bat.value_cache(l)[:n].cpu().numpy(), vc[l, :n], RTOL, ATOL * sv, f"value cache {l} vs oracle")
+    lb, ls_ = bat.logits().cpu().numpy(), seq.logits().cpu().numpy()
+    assert_close(lb, ls_.astype(np.float64), RTOL, ATOL * max(1.0, float(np.abs(ls_).max())), "final logits vs sequential")
+    bat.set_prefill(False)
+    assert np.array_equal(bat.decode(prompt, n_gen), tok_seq)
 
 
 def test_prefill_of_a_tensor_parallel_rank_wants_its_communicator():

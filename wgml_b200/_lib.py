@@ -103,6 +103,8 @@ SIGNATURES = {
     "wgb_llama2_set_sampler": (_i, [_vp, _f, _f, _u64]),
     "wgb_llama2_load_stats": (_i, [_vp, C.POINTER(_sz), C.POINTER(C.c_double)]),
     "wgb_llama2_set_prefill": (_i, [_vp, _i]),
+    "wgb_gpt2_set_prefill": (_i, [_vp, _i]),
+    "wgb_gpt2_prefill_positions": (_i, [_vp, C.POINTER(_sz)]),
     "wgb_llama2_prefill_positions": (_i, [_vp, C.POINTER(_sz)]),
     "wgb_gpt2_set_sampler": (_i, [_vp, _f, _f, _u64]),
     "wgb_gguf_open": (_i, [C.c_char_p, _pp]),

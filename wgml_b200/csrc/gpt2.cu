@@ -8,6 +8,7 @@
 //   unfused  one launch per reference dispatch.
 #include "kernels.h"
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -43,6 +44,19 @@ struct wgb_gpt2 {
     cudaGraphExec_t graph = nullptr;
     uint32_t graph_n_prompt = 0;
     int kernels_per_token = 0;
+    // batched prompt prefill (wgb_gpt2_set_prefill): tile-major copies of the layer matrices for the tensor-core
+    // products, activation images and the buffers of a pass of PF_TOK positions
+    struct Prefill {
+        bool enabled = false;
+        std::vector<uint8_t *> tiles;        // [layer * 4 + matrix], NULL: no tensor-core path for that matrix
+        std::vector<uint8_t> kind;           // same index: 0 a Q4_K copy, 1 a Q6_K one, 2 a Q8_0 one
+        uint8_t *img_e = nullptr, *img_a = nullptr, *img_h = nullptr, *img6 = nullptr;   // images of n_embd / n_embd / ff_len columns
+        float *x = nullptr, *xn = nullptr, *q = nullptr, *xb = nullptr, *h = nullptr;     // [PF_TOK][n_embd | ff_len]
+        float *part[3] = {};                 // product slices: [PF_MAX_SPLIT][PF_TOK][max(3 n_embd, ff_len)]
+        float *attn_scratch = nullptr;
+        uint32_t *attn_counters = nullptr, *pos = nullptr;   // pos: the PF_TOK positions of a pass
+        size_t positions = 0;
+    } pf;
 };
 
 namespace {
@@ -234,6 +248,89 @@ int enqueue_forward(wgb_gpt2 *m, cudaStream_t s, int *nkernels)
     return WGB_OK;
 }
 
+void prefill_free(wgb_gpt2 *m)
+{
+    for (uint8_t *t : m->pf.tiles) if (t) cudaFree(t);
+    uint8_t *imgs[] = { m->pf.img_e, m->pf.img_a, m->pf.img_h, m->pf.img6 };
+    for (uint8_t *b : imgs) if (b) cudaFree(b);
+    float *bufs[] = { m->pf.x, m->pf.xn, m->pf.q, m->pf.xb, m->pf.h, m->pf.part[0], m->pf.part[1], m->pf.part[2], m->pf.attn_scratch };
+    for (float *b : bufs) if (b) cudaFree(b);
+    if (m->pf.attn_counters) cudaFree(m->pf.attn_counters);
+    if (m->pf.pos) cudaFree(m->pf.pos);
+    m->pf = wgb_gpt2::Prefill();
+}
+
+// One product of a prefill pass: W . (the `ntok` vectors whose image is `image` and whose values are xf), as slices
+// [slice][PF_TOK][stride] in `out`; matrices without a tile-major copy go through the matrix-vector kernel per position.
+int prefill_product(wgb_gpt2 *m, uint32_t layer, int which, const uint8_t *image, const float *xf, uint32_t xf_stride, uint32_t ntok, float *out,
+                    uint32_t stride, uint32_t *nsplit, cudaStream_t s)
+{
+    const QMat &w = m->layers[layer].m[which]->view;
+    const size_t idx = (size_t)layer * 4 + which;
+    const uint8_t *tiles = m->pf.tiles[idx];
+    if (tiles) {
+        *nsplit = prefill_gemm_splits(w.nrows, w.ncols);
+        if (m->pf.kind[idx] == 2) return launch_gemm_q80_tiles(tiles, w.nrows, w.ncols, image, ntok, out, stride, *nsplit, s);
+        if (m->pf.kind[idx] == 1) {
+            int rc = launch_prefill_image6(xf, xf_stride, w.ncols, ntok, m->pf.img6, s);
+            return rc ? rc : launch_gemm_q6k_tiles(tiles, w.nrows, w.ncols, m->pf.img6, ntok, out, stride, *nsplit, s);
+        }
+        return launch_gemm_q4k_tiles(tiles, w.nrows, w.ncols, image, ntok, out, stride, *nsplit, s);
+    }
+    *nsplit = 1;
+    for (uint32_t t = 0; t < ntok; t++) {
+        int rc = mat_vec(w, xf + (size_t)t * xf_stride, out + (size_t)t * stride, s);
+        if (rc) return rc;
+    }
+    return WGB_OK;
+}
+
+// Prompt positions pos0 .. pos0 + ntok - 1 (tokens d_tokens[0 .. ntok)) through the layer stack in one pass: the work
+// of ntok calls of Gpt2::dispatch (models/gpt2/transformer.rs:265-477) up to the last layer's cache rows; the final
+// LayerNorm and the logits of prompt positions are never looked at (chat_gpt2.rs:43-151 samples after the prompt).
+int prefill_pass(wgb_gpt2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32_t pos0, uint32_t ntok)
+{
+    const wgb_gpt2_params &p = m->p;
+    wgb_gpt2::Prefill &pf = m->pf;
+    const uint32_t n = p.n_embd, ff = p.ff_len, hs = n / p.n_head;
+    int rc;
+    if ((rc = launch_prefill_positions(pf.pos, pos0, s))) return rc;
+    for (uint32_t t = 0; t < ntok; t++)
+        if ((rc = launch_embed(m->wte->view, &m->wpe->view, d_tokens + t, pf.pos + t, pf.x + (size_t)t * n, s))) return rc;
+    const size_t cache_stride = (size_t)p.n_seq * n;
+    const bool attn_image = prefill_attention_writes_image(hs);
+    const float *pending = nullptr, *pending_bias = nullptr;   // the last layer's second projection and its bias
+    uint32_t pending_split = 0;
+    for (uint32_t l = 0; l < p.n_layer; l++) {
+        const wgb_gpt2::Layer &w = m->layers[l];
+        float *kc = m->key_cache + l * cache_stride, *vc = m->value_cache + l * cache_stride;
+        uint32_t nq, no, nf, nd;
+        if ((rc = launch_prefill_ln_image(pf.x, n, pending, pending_split, n, pending_bias, w.v[WGB_G_LN_1_G], w.v[WGB_G_LN_1_B], n, ntok, pf.img_e, pf.xn,
+                                          n, s)))
+            return rc;
+        if ((rc = prefill_product(m, l, WGB_G_ATTN_QKV, pf.img_e, pf.xn, n, ntok, pf.part[0], 3 * n, &nq, s))) return rc;
+        if ((rc = launch_prefill_qkv_split(pf.part[0], nq, w.v[WGB_G_ATTN_QKV_B], pf.q, kc, vc, n, pos0, ntok, s))) return rc;
+        if ((rc = launch_prefill_attention(pf.q, kc, vc, pf.xb, p.n_head, hs, 1, n, hs, pos0, ntok, attn_image ? pf.img_a : nullptr, pf.attn_scratch,
+                                           pf.attn_counters, s)))
+            return rc;
+        if (!attn_image && (rc = launch_prefill_norm_image(pf.xb, n, nullptr, 0, 0, nullptr, 0.0f, n, ntok, pf.img_a, nullptr, 0, s))) return rc;
+        if ((rc = prefill_product(m, l, WGB_G_ATTN_PROJ, pf.img_a, pf.xb, n, ntok, pf.part[1], n, &no, s))) return rc;
+        if ((rc = launch_prefill_ln_image(pf.x, n, pf.part[1], no, n, w.v[WGB_G_ATTN_PROJ_B], w.v[WGB_G_LN_2_G], w.v[WGB_G_LN_2_B], n, ntok, pf.img_e,
+                                          pf.xn, n, s)))
+            return rc;
+        if ((rc = prefill_product(m, l, WGB_G_MLP_FC, pf.img_e, pf.xn, n, ntok, pf.part[0], ff, &nf, s))) return rc;
+        if ((rc = launch_prefill_gelu_image(pf.part[0], nf, ff, w.v[WGB_G_MLP_FC_B], ff, ntok, pf.img_h, pf.h, ff, s))) return rc;
+        if ((rc = prefill_product(m, l, WGB_G_MLP_PROJ, pf.img_h, pf.h, ff, ntok, pf.part[2], n, &nd, s))) return rc;
+        pending = pf.part[2];
+        pending_bias = w.v[WGB_G_MLP_PROJ_B];
+        pending_split = nd;
+    }
+    // leave the residual stream of the pass complete
+    if ((rc = launch_prefill_ln_image(pf.x, n, pending, pending_split, n, pending_bias, nullptr, nullptr, n, ntok, nullptr, nullptr, 0, s))) return rc;
+    pf.positions += ntok;
+    return WGB_OK;
+}
+
 void drop_graph(wgb_gpt2 *m)
 {
     if (m->graph) cudaGraphExecDestroy(m->graph);
@@ -284,6 +381,7 @@ WGB_EXPORT int wgb_gpt2_destroy(wgb_gpt2 *m)
 {
     if (!m) return WGB_OK;
     drop_graph(m);
+    prefill_free(m);
     for (auto &l : m->layers) {
         for (auto *q : l.m) wgb_quant_matrix_destroy(q);
         for (auto *v : l.v) if (v) cudaFree(v);
@@ -305,6 +403,7 @@ WGB_EXPORT int wgb_gpt2_destroy(wgb_gpt2 *m)
 WGB_EXPORT int wgb_gpt2_set_matrix(wgb_gpt2 *m, int layer, int which, int qtype, const void *h_blocks, size_t nrows, size_t ncols)
 {
     WGB_REQUIRE(m && h_blocks, "null argument");
+    if (m->pf.enabled) prefill_free(m);   // its tile-major copies would go stale
     const wgb_gpt2_params &p = m->p;
     size_t er, ec;
     wgb_quant_matrix **slot;
@@ -507,7 +606,20 @@ WGB_EXPORT int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_p
     }
     // the first token travels as a kernel argument; the rest of the prompt is only read when there is one
     if (n_prompt > 1) WGB_CUDA(cudaMemcpyAsync(m->d_prompt, h_prompt, n_prompt * 4, cudaMemcpyHostToDevice, s));
-    set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, h_prompt[0], start_pos, 0);
+    // Batched prefill: every prompt position but the last may go through passes of PF_TOK positions; a remainder
+    // shorter than half a pass stays with the token loop.
+    size_t done = 0;
+    if (m->pf.enabled && n_prompt - 1 >= PF_TOK) {
+        const size_t rem = (n_prompt - 1) % PF_TOK;
+        const size_t batched = n_prompt - 1 - (rem >= PF_TOK / 2 ? 0 : rem);
+        for (; done < batched; done += PF_TOK) {
+            const uint32_t nt = (uint32_t)(batched - done < PF_TOK ? batched - done : PF_TOK);
+            if ((rc = prefill_pass(m, s, m->d_prompt + done, start_pos + (uint32_t)done, nt))) return rc;
+        }
+        done = batched;
+        WGB_CUDA(cudaMemcpyAsync(m->d_out, m->d_prompt + 1, done * 4, cudaMemcpyDeviceToDevice, s));   // step i reports prompt[i + 1]
+    }
+    set_scalars_kernel<<<1, 1, 0, s>>>(m->scalars, h_prompt[done], start_pos + (uint32_t)done, (uint32_t)done);
     WGB_LAUNCH_CHECK("set_scalars_kernel");
     LoopState ls = {};
     ls.token = m->scalars;
@@ -542,7 +654,7 @@ WGB_EXPORT int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_p
         if (e != cudaSuccess) { m->graph = nullptr; return cuda_fail(e, "CUDA graph capture of a decode step"); }
         m->graph_n_prompt = (uint32_t)n_prompt;
     }
-    if ((rc = replay_with_status(m->graph, total, s, m->h_pinned + 1, m->poll))) return rc;
+    if ((rc = replay_with_status(m->graph, total - done, s, m->h_pinned + 1, m->poll))) return rc;
     // One wait for the ids and the kernels' status word, both through pinned memory.
     WGB_CUDA(cudaMemcpyAsync(m->h_pinned + 3, m->d_out, total * 4, cudaMemcpyDeviceToHost, s));
     m->h_pinned[0] = 0;
@@ -550,6 +662,71 @@ WGB_EXPORT int wgb_gpt2_decode(wgb_gpt2 *m, const uint32_t *h_prompt, size_t n_p
     WGB_CUDA(cudaStreamSynchronize(s));
     memcpy(h_out_tokens, m->h_pinned + 3, total * 4);
     return gemv_report_status(m->h_pinned[0]);
+}
+
+WGB_EXPORT int wgb_gpt2_set_prefill(wgb_gpt2 *m, int enable)
+{
+    WGB_REQUIRE(m, "null argument");
+    if (!enable) {
+        prefill_free(m);
+        return WGB_OK;
+    }
+    if (m->pf.enabled) return WGB_OK;
+    int rc = check_complete(m);
+    if (rc) return rc;
+    if ((rc = gemv_global_init())) return rc;
+    const wgb_gpt2_params &p = m->p;
+    const uint32_t n = p.n_embd, ff = p.ff_len, hs = n / p.n_head;
+    WGB_REQUIRE(n % 256 == 0 && ff % 256 == 0 && hs % 4 == 0 && hs <= 256, "batched prefill wants widths that are multiples of 256 (n_embd %u, ff_len %u)", n, ff);
+    wgb_gpt2::Prefill &pf = m->pf;
+    pf.tiles.assign((size_t)p.n_layer * 4, nullptr);
+    pf.kind.assign((size_t)p.n_layer * 4, 0);
+    auto bail = [&](int code) { prefill_free(m); return code; };
+    for (uint32_t l = 0; l < p.n_layer; l++)
+        for (int i = 0; i < 4; i++) {
+            const QMat &w = m->layers[l].m[i]->view;
+            const size_t idx = (size_t)l * 4 + i;
+            if (prefill_tileable(w) && (rc = prefill_tile_major(w, &pf.tiles[idx], nullptr))) return bail(rc);
+            if (prefill_tileable6(w)) {
+                if ((rc = prefill_tile_major6(w, &pf.tiles[idx], nullptr))) return bail(rc);
+                pf.kind[idx] = 1;
+            }
+            if (prefill_tileable8(w)) {
+                if ((rc = prefill_tile_major8(w, &pf.tiles[idx], nullptr))) return bail(rc);
+                pf.kind[idx] = 2;
+            }
+        }
+    auto image = [&](uint8_t **ptr, uint32_t K) -> int {
+        WGB_CUDA(cudaMalloc((void **)ptr, prefill_image_bytes(K)));
+        WGB_CUDA(cudaMemset(*ptr, 0, prefill_image_bytes(K)));
+        return WGB_OK;
+    };
+    if ((rc = image(&pf.img_e, n)) || (rc = image(&pf.img_a, n)) || (rc = image(&pf.img_h, ff))) return bail(rc);
+    const size_t widest = std::max<size_t>(3 * (size_t)n, ff);
+    if (cudaMalloc((void **)&pf.img6, prefill_image6_bytes((uint32_t)widest)) != cudaSuccess) return bail(fail(WGB_ERR_CUDA, "cudaMalloc(Q6_K image)"));
+    if ((rc = dalloc(&pf.x, (size_t)PF_TOK * n)) || (rc = dalloc(&pf.xn, (size_t)PF_TOK * n)) || (rc = dalloc(&pf.q, (size_t)PF_TOK * n)) ||
+        (rc = dalloc(&pf.xb, (size_t)PF_TOK * n)) || (rc = dalloc(&pf.h, (size_t)PF_TOK * ff)))
+        return bail(rc);
+    for (int i = 0; i < 3; i++)
+        if ((rc = dalloc(&pf.part[i], (size_t)PF_MAX_SPLIT * PF_TOK * widest))) return bail(rc);
+    if ((rc = dalloc(&pf.attn_scratch, prefill_attention_scratch_floats(p.n_head, hs)))) return bail(rc);
+    {
+        const size_t nc = prefill_attention_counters(p.n_head);
+        cudaError_t e = cudaMalloc((void **)&pf.attn_counters, nc * 4);
+        if (e == cudaSuccess) e = cudaMemset(pf.attn_counters, 0, nc * 4);
+        if (e == cudaSuccess) e = cudaMalloc((void **)&pf.pos, PF_TOK * 4);
+        if (e != cudaSuccess) { prefill_free(m); return cuda_fail(e, "cudaMalloc(prompt pass state)"); }
+    }
+    WGB_CUDA(cudaDeviceSynchronize());
+    pf.enabled = true;
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_gpt2_prefill_positions(const wgb_gpt2 *m, size_t *positions)
+{
+    WGB_REQUIRE(m && positions, "null argument");
+    *positions = m->pf.positions;
+    return WGB_OK;
 }
 
 WGB_EXPORT int wgb_gpt2_set_sampler(wgb_gpt2 *m, float temperature, float topp, uint64_t seed)

@@ -200,6 +200,16 @@ bool prefill_tileable8(const QMat &m);
 int prefill_tile_major8(const QMat &m, uint8_t **out, cudaStream_t stream);
 int launch_gemm_q80_tiles(const uint8_t *w_tiles, uint32_t nrows, uint32_t K, const uint8_t *image, uint32_t ntok, float *out,
                           uint32_t out_stride, uint32_t nsplit, cudaStream_t stream);
+// GPT-2 passes: LayerNorm (two passes, epsilon 1e-5) * gain + bias with the fold of the preceding product and its
+// bias; the split of the fused qkv product into q / cache rows ([seq][n] caches); GELU of a product plus bias.
+int launch_prefill_ln_image(float *x, uint32_t x_stride, const float *part, uint32_t nsplit, uint32_t part_stride, const float *fold_bias,
+                            const float *gain, const float *bias, uint32_t K, uint32_t ntok, uint8_t *image, float *xn, uint32_t xn_stride,
+                            cudaStream_t stream);
+int launch_prefill_qkv_split(const float *qkv, uint32_t nsplit, const float *bias, float *q_out, float *k_cache, float *v_cache, uint32_t n,
+                             uint32_t pos0, uint32_t ntok, cudaStream_t stream);
+int launch_prefill_gelu_image(const float *part, uint32_t nsplit, uint32_t stride, const float *bias, uint32_t K, uint32_t ntok, uint8_t *image,
+                              float *h, uint32_t h_stride, cudaStream_t stream);
+int launch_prefill_positions(uint32_t *positions, uint32_t pos0, cudaStream_t stream);
 struct PrefillQkv {
     const float *q, *k, *v;            // product slices: [split][PF_TOK][stride]
     uint32_t q_split, k_split, v_split, q_stride, kv_stride;
@@ -218,8 +228,9 @@ bool prefill_attention_writes_image(uint32_t head_size);
 // launch; the kernel leaves them zero) long contexts are split over several blocks per (head, pair of positions).
 size_t prefill_attention_scratch_floats(uint32_t n_heads, uint32_t head_size);
 size_t prefill_attention_counters(uint32_t n_heads);
+// Cache row p of KV head g lies at p * row_stride + g * head_stride floats.
 int launch_prefill_attention(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
-                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, float *scratch,
-                             uint32_t *counters, cudaStream_t stream);
+                             uint32_t kv_mul, uint32_t row_stride, uint32_t head_stride, uint32_t pos0, uint32_t ntok, uint8_t *image,
+                             float *scratch, uint32_t *counters, cudaStream_t stream);
 
 }  // namespace wgb

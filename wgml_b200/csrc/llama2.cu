@@ -531,7 +531,8 @@ int prefill_pass(wgb_llama2 *m, cudaStream_t s, const uint32_t *d_tokens, uint32
         qa.freq = m->rope_freq;
         if ((rc = launch_prefill_rope_append(qa, ntok, s))) return rc;
         const bool attn_image = prefill_attention_writes_image(m->head_size);
-        if ((rc = launch_prefill_attention(pf.q, qa.k_cache, qa.v_cache, pf.xb, m->n_q_local, m->head_size, m->kv_mul, c.seq_len, pos0, ntok,
+        if ((rc = launch_prefill_attention(pf.q, qa.k_cache, qa.v_cache, pf.xb, m->n_q_local, m->head_size, m->kv_mul, m->head_size,
+                                           c.seq_len * m->head_size, pos0, ntok,
                                            attn_image ? pf.img_q : nullptr, pf.attn_scratch, pf.attn_counters, s)))
             return rc;
         if (!attn_image && (rc = launch_prefill_norm_image(pf.xb, q_dim, nullptr, 0, 0, nullptr, 0.0f, q_dim, ntok, pf.img_q, nullptr, 0, s))) return rc;

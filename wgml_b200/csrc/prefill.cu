@@ -511,6 +511,162 @@ int launch_prefill_silu_image(const float *gate, uint32_t gsplit, const float *u
     return WGB_OK;
 }
 
+// ---- GPT-2 passes: LayerNorm, fused-qkv split, GELU ---------------------------------------------------------
+
+// x (+= the slices of a product and its bias, written back); then LayerNorm (ops/layernorm.wgsl:28-80: two passes,
+// epsilon 1e-5) times gain plus bias (the Mul / Add dispatches of models/gpt2/transformer.rs:295-310, 372-386);
+// its image and the values.  One 1024-thread block per position; positions >= ntok get an all-zero image.
+__global__ void __launch_bounds__(1024) prefill_ln_image_kernel(float *__restrict__ x, uint32_t x_stride, const float *__restrict__ part,
+                                                                uint32_t nsplit, uint32_t part_stride, const float *__restrict__ fold_bias,
+                                                                const float *__restrict__ gain, const float *__restrict__ bias, uint32_t K,
+                                                                uint32_t ntok, uint8_t *__restrict__ image, float *__restrict__ xn,
+                                                                uint32_t xn_stride)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t t = blockIdx.x;
+    __shared__ float red[32];
+    __shared__ float stat_s;
+    if (t >= ntok) {
+        for (uint32_t i = threadIdx.x; i < K / 4; i += 1024) image_quad(image, t, i >> 3, i & 7, make_float4(0.f, 0.f, 0.f, 0.f));
+        return;
+    }
+    float *xr = x + (size_t)t * x_stride;
+    auto block_total = [&](float v) {
+        v = warp_sum(v);
+        __syncthreads();   // red[] and stat_s of the previous use have been read
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float tot = 0.0f;
+            for (int i = 0; i < 32; i++) tot += red[i];
+            stat_s = tot;
+        }
+        __syncthreads();
+        return stat_s;
+    };
+    float sm = 0.0f;
+    for (uint32_t i = threadIdx.x * 4; i < K; i += 4096) {
+        float4 v = *reinterpret_cast<const float4 *>(xr + i);
+        if (part) {
+            for (uint32_t s = 0; s < nsplit; s++) {
+                const float4 p = *reinterpret_cast<const float4 *>(part + ((size_t)s * PF_TOK + t) * part_stride + i);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
+            if (fold_bias) {
+                const float4 b = *reinterpret_cast<const float4 *>(fold_bias + i);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            }
+            *reinterpret_cast<float4 *>(xr + i) = v;
+        }
+        sm += (v.x + v.y) + (v.z + v.w);
+    }
+    if (!image) return;   // only the fold was wanted
+    const float mean = block_total(sm) / (float)K;
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x * 4; i < K; i += 4096) {   // the same thread reads back what it wrote above
+        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+        const float dx = v.x - mean, dy = v.y - mean, dz = v.z - mean, dw = v.w - mean;
+        ss = fmaf(dx, dx, ss); ss = fmaf(dy, dy, ss); ss = fmaf(dz, dz, ss); ss = fmaf(dw, dw, ss);
+    }
+    const float scale = 1.0f / sqrtf(block_total(ss) / (float)K + 1.0e-5f);
+    for (uint32_t i = threadIdx.x; i < K / 4; i += 1024) {
+        float4 v = *reinterpret_cast<const float4 *>(xr + 4 * i);
+        const float4 g = *reinterpret_cast<const float4 *>(gain + 4 * i), b = *reinterpret_cast<const float4 *>(bias + 4 * i);
+        v.x = ((v.x - mean) * scale) * g.x + b.x; v.y = ((v.y - mean) * scale) * g.y + b.y;
+        v.z = ((v.z - mean) * scale) * g.z + b.z; v.w = ((v.w - mean) * scale) * g.w + b.w;
+        if (xn) *reinterpret_cast<float4 *>(xn + (size_t)t * xn_stride + 4 * i) = v;
+        image_quad(image, t, i >> 3, i & 7, v);
+    }
+}
+
+int launch_prefill_ln_image(float *x, uint32_t x_stride, const float *part, uint32_t nsplit, uint32_t part_stride, const float *fold_bias,
+                            const float *gain, const float *bias, uint32_t K, uint32_t ntok, uint8_t *image, float *xn, uint32_t xn_stride,
+                            cudaStream_t stream)
+{
+    WGB_REQUIRE(K % 128 == 0 && ntok <= PF_TOK && (!image || (gain && bias)), "LayerNorm image of %u columns, %u positions", K, ntok);
+    WGB_CUDA(launch_pdl(prefill_ln_image_kernel, dim3(image ? PF_TOK : ntok), dim3(1024), 0, stream, x, x_stride, part, nsplit, part_stride, fold_bias,
+                        gain, bias, K, ntok, image, xn, xn_stride));
+    return WGB_OK;
+}
+
+// The three Copy dispatches of models/gpt2/transformer.rs:329-353 for a batch of positions, with the bias of the fused
+// qkv product: rows [0, n) -> q_out[t], [n, 2n) -> key cache row pos0 + t, [2n, 3n) -> value cache row ([seq][n] caches).
+__global__ void __launch_bounds__(256) prefill_qkv_split_kernel(const float *__restrict__ qkv, uint32_t nsplit, const float *__restrict__ bias,
+                                                                float *__restrict__ q_out, float *__restrict__ k_cache,
+                                                                float *__restrict__ v_cache, uint32_t n, uint32_t pos0)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
+    if (i >= 3 * n) return;
+    float v = 0.0f;
+    for (uint32_t s = 0; s < nsplit; s++) v += qkv[((size_t)s * PF_TOK + t) * (3 * n) + i];
+    if (bias) v += bias[i];
+    if (i < n) q_out[(size_t)t * n + i] = v;
+    else if (i < 2 * n) k_cache[(size_t)(pos0 + t) * n + (i - n)] = v;
+    else v_cache[(size_t)(pos0 + t) * n + (i - 2 * n)] = v;
+}
+
+int launch_prefill_qkv_split(const float *qkv, uint32_t nsplit, const float *bias, float *q_out, float *k_cache, float *v_cache, uint32_t n,
+                             uint32_t pos0, uint32_t ntok, cudaStream_t stream)
+{
+    WGB_CUDA(launch_pdl(prefill_qkv_split_kernel, dim3((3 * n + 255) / 256, ntok), dim3(256), 0, stream, qkv, nsplit, bias, q_out, k_cache, v_cache, n,
+                        pos0));
+    return WGB_OK;
+}
+
+// h = gelu(product + bias) (Unary GELU, ops/unary.wgsl:50-52: 0.5 x (1 + tanh(0.7978846 x (1 + 0.044715 x^2)))) from
+// the slices of the product; its image and, optionally, the values.  One thread per four columns.
+__device__ __forceinline__ float gelu_ref(float x)
+{
+    return 0.5f * x * (1.0f + tanhf(0.7978846f * x * (1.0f + 0.044715f * x * x)));
+}
+__global__ void __launch_bounds__(256) prefill_gelu_image_kernel(const float *__restrict__ part, uint32_t nsplit, uint32_t stride,
+                                                                 const float *__restrict__ bias, uint32_t K, uint32_t ntok,
+                                                                 uint8_t *__restrict__ image, float *__restrict__ h, uint32_t h_stride)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t t = blockIdx.y, i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= K / 4) return;   // K / 4 is a multiple of 32: whole warps leave together
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t < ntok) {
+        for (uint32_t s = 0; s < nsplit; s++) {
+            const float4 p = *reinterpret_cast<const float4 *>(part + ((size_t)s * PF_TOK + t) * stride + 4 * i);
+            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        if (bias) {
+            const float4 b = *reinterpret_cast<const float4 *>(bias + 4 * i);
+            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        }
+        v.x = gelu_ref(v.x); v.y = gelu_ref(v.y); v.z = gelu_ref(v.z); v.w = gelu_ref(v.w);
+        if (h) *reinterpret_cast<float4 *>(h + (size_t)t * h_stride + 4 * i) = v;
+    }
+    image_quad(image, t, i >> 3, i & 7, v);
+}
+
+int launch_prefill_gelu_image(const float *part, uint32_t nsplit, uint32_t stride, const float *bias, uint32_t K, uint32_t ntok, uint8_t *image,
+                              float *h, uint32_t h_stride, cudaStream_t stream)
+{
+    WGB_REQUIRE(K % 128 == 0 && ntok <= PF_TOK, "activation image of %u columns (whole warps of four-column threads), %u positions", K, ntok);
+    WGB_CUDA(launch_pdl(prefill_gelu_image_kernel, dim3((K / 4 + 255) / 256, PF_TOK), dim3(256), 0, stream, part, nsplit, stride, bias, K, ntok, image, h,
+                        h_stride));
+    return WGB_OK;
+}
+
+// positions[t] = pos0 + t (the learned positional rows of a pass are looked up through device scalars)
+__global__ void prefill_positions_kernel(uint32_t *positions, uint32_t pos0)
+{
+    if (threadIdx.x < PF_TOK) positions[threadIdx.x] = pos0 + threadIdx.x;
+}
+int launch_prefill_positions(uint32_t *positions, uint32_t pos0, cudaStream_t stream)
+{
+    prefill_positions_kernel<<<1, 32, 0, stream>>>(positions, pos0);
+    WGB_LAUNCH_CHECK("prefill_positions_kernel");
+    return WGB_OK;
+}
+
 // ---- RoPE + KV append for a batch of positions ------------------------------------------------------
 
 // The work of the OpAssign / RoPE dispatches of models/llama2/transformer.rs:343-365 and the write into the cache
@@ -568,9 +724,9 @@ constexpr uint32_t PA_MAX_SPLIT = 8; // blocks that may share the rows of one (h
 template <uint32_t TQ>
 __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__restrict__ q, const float *__restrict__ k_cache,
                                                                 const float *__restrict__ v_cache, float *__restrict__ out, uint32_t q_dim,
-                                                                uint32_t head_size, uint32_t kv_mul, uint32_t seq_len, uint32_t pos0,
-                                                                uint32_t ntok, uint8_t *__restrict__ image, float *__restrict__ scratch,
-                                                                uint32_t *__restrict__ counters)
+                                                                uint32_t head_size, uint32_t kv_mul, uint32_t row_stride, uint32_t head_stride,
+                                                                uint32_t pos0, uint32_t ntok, uint8_t *__restrict__ image,
+                                                                float *__restrict__ scratch, uint32_t *__restrict__ counters)
 {
     extern __shared__ float pa_smem[];
     pdl_launch_dependents();
@@ -590,8 +746,10 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
     float *accs = sc + TQ * PA_CHUNK;          // [4][TQ][head_size]
     __shared__ float red[TQ][8];
     __shared__ float m_run[TQ], l_run[TQ], m_new[TQ], resc[TQ];
-    const float *kh = k_cache + (size_t)(h / kv_mul) * seq_len * head_size;
-    const float *vh = v_cache + (size_t)(h / kv_mul) * seq_len * head_size;
+    // cache row p of KV head g at p * row_stride + g * head_stride (head-major caches: head_size, seq_len * head_size;
+    // the reference layout [seq_len][kv_dim]: kv_dim, head_size)
+    const float *kh = k_cache + (size_t)(h / kv_mul) * head_stride;
+    const float *vh = v_cache + (size_t)(h / kv_mul) * head_stride;
     const float inv_sqrt = 1.0f / sqrtf((float)head_size);
     for (uint32_t i = threadIdx.x; i < TQ * head_size; i += 256) {
         const uint32_t tq = i / head_size, e = i % head_size;
@@ -612,7 +770,7 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
 #pragma unroll
         for (uint32_t tq = 0; tq < TQ; tq++) s[tq] = 0.0f;
         if (row <= last) {
-            const float4 *kr = reinterpret_cast<const float4 *>(kh + (size_t)row * head_size);
+            const float4 *kr = reinterpret_cast<const float4 *>(kh + (size_t)row * row_stride);
 #pragma unroll 8
             for (uint32_t e = 0; e < head_size / 4; e++) {
                 const float4 kv = kr[e];
@@ -662,7 +820,7 @@ __global__ void __launch_bounds__(256) prefill_attention_kernel(const float *__r
             const uint32_t r_end = min(c0 + 64 * (rq + 1), last + 1);
 #pragma unroll 4
             for (uint32_t rr = c0 + 64 * rq; rr < r_end; rr++) {
-                const float4 vv = *reinterpret_cast<const float4 *>(vh + (size_t)rr * head_size + 4 * cg);
+                const float4 vv = *reinterpret_cast<const float4 *>(vh + (size_t)rr * row_stride + 4 * cg);
 #pragma unroll
                 for (uint32_t tq = 0; tq < TQ; tq++) {
                     const float p = sc[tq * PA_CHUNK + (rr - c0)];
@@ -756,8 +914,8 @@ size_t prefill_attention_counters(uint32_t n_heads) { return (size_t)n_heads * (
 
 template <uint32_t TQ>
 static int launch_prefill_attention_tq(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
-                                       uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, float *scratch,
-                                       uint32_t *counters, uint32_t chunks, cudaStream_t stream)
+                                       uint32_t kv_mul, uint32_t row_stride, uint32_t head_stride, uint32_t pos0, uint32_t ntok, uint8_t *image,
+                                       float *scratch, uint32_t *counters, uint32_t chunks, cudaStream_t stream)
 {
     const size_t smem = (size_t)(TQ * head_size + TQ * PA_CHUNK + 4 * TQ * head_size) * sizeof(float);
     // Long contexts: the chunks of a (head, group of positions) are dealt to several blocks, enough to fill the machine
@@ -771,13 +929,13 @@ static int launch_prefill_attention_tq(const float *q, const float *k_cache, con
         if (nz > PA_MAX_SPLIT) nz = PA_MAX_SPLIT;
     }
     WGB_CUDA(launch_pdl(prefill_attention_kernel<TQ>, dim3(n_heads, image ? PF_TOK / TQ : groups, nz), dim3(256), smem, stream, q, k_cache, v_cache, out,
-                        n_heads * head_size, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters));
+                        n_heads * head_size, head_size, kv_mul, row_stride, head_stride, pos0, ntok, image, scratch, counters));
     return WGB_OK;
 }
 
 int launch_prefill_attention(const float *q, const float *k_cache, const float *v_cache, float *out, uint32_t n_heads, uint32_t head_size,
-                             uint32_t kv_mul, uint32_t seq_len, uint32_t pos0, uint32_t ntok, uint8_t *image, float *scratch,
-                             uint32_t *counters, cudaStream_t stream)
+                             uint32_t kv_mul, uint32_t row_stride, uint32_t head_stride, uint32_t pos0, uint32_t ntok, uint8_t *image,
+                             float *scratch, uint32_t *counters, cudaStream_t stream)
 {
     WGB_REQUIRE(!image || prefill_attention_writes_image(head_size), "prompt attention writes the image only for head sizes that are multiples of 64, got %u",
                 head_size);
@@ -788,10 +946,10 @@ int launch_prefill_attention(const float *q, const float *k_cache, const float *
     const uint32_t chunks = (pos0 + ntok + PA_CHUNK - 1) / PA_CHUNK;
     const bool split = scratch && counters;
     if (split && chunks >= 8 && head_size <= 128)
-        return launch_prefill_attention_tq<8>(q, k_cache, v_cache, out, n_heads, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters, chunks, stream);
+        return launch_prefill_attention_tq<8>(q, k_cache, v_cache, out, n_heads, head_size, kv_mul, row_stride, head_stride, pos0, ntok, image, scratch, counters, chunks, stream);
     if (split && chunks >= 3)
-        return launch_prefill_attention_tq<4>(q, k_cache, v_cache, out, n_heads, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters, chunks, stream);
-    return launch_prefill_attention_tq<2>(q, k_cache, v_cache, out, n_heads, head_size, kv_mul, seq_len, pos0, ntok, image, scratch, counters, chunks, stream);
+        return launch_prefill_attention_tq<4>(q, k_cache, v_cache, out, n_heads, head_size, kv_mul, row_stride, head_stride, pos0, ntok, image, scratch, counters, chunks, stream);
+    return launch_prefill_attention_tq<2>(q, k_cache, v_cache, out, n_heads, head_size, kv_mul, row_stride, head_stride, pos0, ntok, image, scratch, counters, chunks, stream);
 }
 
 // Raw row-major Q4_K blocks -> [tile][column][row in tile][144 bytes].  One thread per 16 bytes.

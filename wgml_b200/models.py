@@ -327,6 +327,16 @@ class Gpt2:
     def set_sampler(self, temperature: float, topp: float, seed: int = 0) -> None:
         check(_lib.load().wgb_gpt2_set_sampler(self._h, temperature, topp, seed))
 
+    def set_prefill(self, enable: bool = True) -> None:
+        """Batched prompt prefill: `decode` sends the prompt through passes of eight positions with the matrix
+        products on the tensor cores (the reference feeds it position by position, chat_gpt2.rs:43-151)."""
+        check(_lib.load().wgb_gpt2_set_prefill(self._h, 1 if enable else 0))
+
+    def prefill_positions(self) -> int:
+        n = C.c_size_t()
+        check(_lib.load().wgb_gpt2_prefill_positions(self._h, C.byref(n)))
+        return n.value
+
     def kernels_per_token(self) -> int:
         return _lib.load().wgb_gpt2_kernels_per_token(self._h)
 
