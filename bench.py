@@ -526,6 +526,24 @@ def run_gpt2(args):
         "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": weights * tok_s / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": weights * tok_s / 1e9 / peak, "traffic": None, "peak_source": peak_src},
     }
+    if not args.no_prefill and prompt_len >= 16:
+        def time_prompt():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            model.decode(prompt, 0)
+            b.record(stream)
+            torch.cuda.synchronize()
+            return a.elapsed_time(b)
+        seq_ms = min(time_prompt() for _ in range(2))
+        model.set_prefill(True)
+        time_prompt()
+        bat_ms = min(time_prompt() for _ in range(2))
+        model.set_prefill(False)
+        line["prefill"] = {"prompt_positions": prompt_len - 1,
+                           "sequential": {"ms": seq_ms, "tok_s": (prompt_len - 1) / (seq_ms * 1e-3)},
+                           "batched": {"ms": bat_ms, "tok_s": (prompt_len - 1) / (bat_ms * 1e-3)},
+                           "how": "wgb_gpt2_decode(prompt, n_gen = 0) between CUDA events, best of 2; batched = after wgb_gpt2_set_prefill(1), "
+                                  "Q8_0 products on tcgen05"}
     if not args.no_cpu_baseline:
         cpu = oracle.Gpt2Oracle(cfg, t)
         n_cpu = min(K, 64)
