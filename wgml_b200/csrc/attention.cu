@@ -39,8 +39,81 @@ size_t attn_scratch_floats(uint32_t n_heads, uint32_t head_size, uint32_t seq_le
 // sizes up to 128, 2: up to 256).
 // MULTI: a block may get several chunks (long contexts, few heads) and keeps a running softmax over them;
 // otherwise every block has exactly one chunk and the loop below collapses.
+// The merge of a head's chunks by its last block, kept out of line: its registers (a second set of running sums)
+// must not count towards the kernel's, whose blocks per SM decide how long a context runs in a single wave.
+template <int QH, int VC>
+__device__ __noinline__ void attn_merge_chunks(const AttnArgs &a, uint32_t kvh, uint32_t hq0, uint32_t kv_mul, uint32_t hs, uint32_t nchunk,
+                                               uint32_t max_splits, uint32_t nsplit_active, float (*s_red)[ATT_WARPS], float (*s_Mw)[ATT_WARPS],
+                                               float (*s_acc)[QH][VC * 128 + 4])
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // Merge of the chunks, spread over the block, in one pass over the scratch: warp w folds chunks w, w + 8, ...
+    // with a running maximum (a row's vector, maximum and denominator come in one round trip), and the eight warps'
+    // (vector, maximum, denominator) triples meet in shared memory.  The chunk -> warp assignment and the order of
+    // the additions are fixed, so the result does not depend on timing.
+#pragma unroll
+    for (int j = 0; j < QH; j++) {
+        if (hq0 + j >= kv_mul) continue;   // uniform over the block
+        const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
+        float4 o[VC];
+#pragma unroll
+        for (int c = 0; c < VC; c++) o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        float Mw = -INFINITY, Lw = 0.0f;
+        for (uint32_t sp = warp; sp < nsplit_active; sp += ATT_WARPS) {
+            const float *row = base + (size_t)sp * (hs + 4);
+            const float ms = __ldcg(row + hs), ls = __ldcg(row + hs + 1);
+            float4 v[VC];
+#pragma unroll
+            for (int c = 0; c < VC; c++) {
+                const uint32_t ch = lane + 32 * c;
+                v[c] = ch < nchunk ? __ldcg(reinterpret_cast<const float4 *>(row) + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            const float mn = fmaxf(Mw, ms);
+            const float rs = expf(Mw - mn), w = expf(ms - mn);   // rs = 0 at the warp's first chunk (Mw = -inf)
+            Mw = mn;
+            Lw = fmaf(Lw, rs, ls * w);
+#pragma unroll
+            for (int c = 0; c < VC; c++) {
+                o[c].x = fmaf(o[c].x, rs, v[c].x * w);
+                o[c].y = fmaf(o[c].y, rs, v[c].y * w);
+                o[c].z = fmaf(o[c].z, rs, v[c].z * w);
+                o[c].w = fmaf(o[c].w, rs, v[c].w * w);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < VC; c++) {
+            const uint32_t ch = lane + 32 * c;
+            if (ch < nchunk) reinterpret_cast<float4 *>(&s_acc[warp][j][0])[ch] = o[c];
+        }
+        if (lane == 0) {
+            s_Mw[j][warp] = Mw;
+            s_red[j][warp] = Lw;
+        }
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < QH * hs; e += ATT_NT) {
+        const uint32_t j = e / hs, i = e % hs;
+        if (hq0 + j >= kv_mul) continue;
+        float M = s_Mw[j][0];
+#pragma unroll
+        for (int w = 1; w < ATT_WARPS; w++) M = fmaxf(M, s_Mw[j][w]);
+        float L = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) {
+            const float f = expf(s_Mw[j][w] - M);   // 0 for a warp without a chunk
+            L = fmaf(s_red[j][w], f, L);
+            o = fmaf(s_acc[w][j][i], f, o);
+        }
+        a.xb[(size_t)(kvh * kv_mul + hq0 + j) * hs + i] = o / L;
+    }
+}
+
+// One query head per KV head and head sizes up to 128 (the 7B shape): three blocks per SM, so that the chunks of a
+// context of 800 positions are all resident at once.  (Left to itself the kernel takes 85 registers, two blocks per
+// SM, and a launch is 1.2 us shorter while its blocks fit one wave -- 576 positions for 32 heads -- but a second
+// wave costs 2.5 us, more than the streaming kernel.)
 template <int QH, int VC, bool MULTI>
-__global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constant__ AttnArgs a)
+__global__ void __launch_bounds__(ATT_NT, (QH == 1 && VC == 1) ? 3 : 1) attn_split_kernel(const __grid_constant__ AttnArgs a)
 {
     __shared__ float s_score[QH][ATT_CHUNK];
     __shared__ float s_red[QH][ATT_WARPS];
@@ -313,72 +386,8 @@ __global__ void __launch_bounds__(ATT_NT) attn_split_kernel(const __grid_constan
         return;
     }
     __threadfence();
-    // Merge of the chunks, spread over the block: the chunk maxima first (one thread per chunk), then warp w
-    // folds chunks w, w + 8, ... for every output element, and the eight partial results meet in shared
-    // memory.  The chunk -> warp assignment is fixed, so the result does not depend on timing.
-    __shared__ float s_M[QH];
-#pragma unroll
-    for (int j = 0; j < QH; j++) {
-        float m = -INFINITY;
-        if (hq0 + j < kv_mul) {
-            const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
-            for (uint32_t sp = threadIdx.x; sp < nsplit_active; sp += ATT_NT) m = fmaxf(m, __ldcg(base + (size_t)sp * (hs + 4) + hs));
-        }
-        m = warp_max(m);
-        if (lane == 0) s_red[j][warp] = m;
-    }
-    __syncthreads();
-    if (threadIdx.x < QH) {
-        float m = s_red[threadIdx.x][0];
-#pragma unroll
-        for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, s_red[threadIdx.x][w]);
-        s_M[threadIdx.x] = m;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int j = 0; j < QH; j++) {
-        if (hq0 + j >= kv_mul) continue;   // uniform over the block
-        const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
-        const float M = s_M[j];
-        float4 o[VC];
-#pragma unroll
-        for (int c = 0; c < VC; c++) o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-        float L = 0.0f;
-        for (uint32_t sp = warp; sp < nsplit_active; sp += ATT_WARPS) {
-            const float *row = base + (size_t)sp * (hs + 4);
-            const float w = expf(__ldcg(row + hs) - M);
-            L = fmaf(__ldcg(row + hs + 1), w, L);
-#pragma unroll
-            for (int c = 0; c < VC; c++) {
-                const uint32_t ch = lane + 32 * c;
-                if (ch < nchunk) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(row) + ch);
-                    o[c].x = fmaf(v.x, w, o[c].x);
-                    o[c].y = fmaf(v.y, w, o[c].y);
-                    o[c].z = fmaf(v.z, w, o[c].z);
-                    o[c].w = fmaf(v.w, w, o[c].w);
-                }
-            }
-        }
-#pragma unroll
-        for (int c = 0; c < VC; c++) {
-            const uint32_t ch = lane + 32 * c;
-            if (ch < nchunk) reinterpret_cast<float4 *>(&s_acc[warp][j][0])[ch] = o[c];
-        }
-        if (lane == 0) s_red[j][warp] = L;
-    }
-    __syncthreads();
-    for (uint32_t e = threadIdx.x; e < QH * hs; e += ATT_NT) {
-        const uint32_t j = e / hs, i = e % hs;
-        if (hq0 + j >= kv_mul) continue;
-        float L = 0.0f, o = 0.0f;
-#pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) {
-            L += s_red[j][w];
-            o += s_acc[w][j][i];
-        }
-        a.xb[(size_t)(kvh * kv_mul + hq0 + j) * hs + i] = o / L;
-    }
+    __shared__ float s_Mw[QH][ATT_WARPS];
+    attn_merge_chunks<QH, VC>(a, kvh, hq0, kv_mul, hs, nchunk, max_splits, nsplit_active, s_red, s_Mw, s_acc);
     if (threadIdx.x == 0) stamp_end(a.stamp);
 }
 
@@ -751,6 +760,15 @@ static int launch_stream_any(const AttnArgs &a, uint32_t nchunks, cudaStream_t s
     return launch_stream<1>(a, nchunks, n_kv, 1, stream, pdl);
 }
 
+static double single_wave_factor()
+{
+    static const double f = [] {
+        const char *env = getenv("WGB_ATTN_SINGLE_X");
+        return env ? atof(env) : 1.0;
+    }();
+    return f;
+}
+
 template <int QH, int VC>
 static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t nchunks_hint, uint32_t n_kv, uint32_t zgroups,
                         cudaStream_t stream, bool pdl)
@@ -770,11 +788,11 @@ static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t nchunks_hi
     const int per_sm_single = occ_single[dev], per_sm_multi = occ_multi[dev];
     const uint32_t heads = n_kv * zgroups;
     if (!a.q) {   // sizing query (attn_sizing_class): no launch
-        return (uint64_t)nchunks_hint * heads > (uint64_t)per_sm_single * (uint32_t)sm_count() ? 1 : 0;
+        return (double)nchunks_hint * heads > single_wave_factor() * per_sm_single * sm_count() ? 1 : 0;
     }
     // `nchunks_hint`: chunks up to the furthest position this launch is expected to serve (performance only:
     // either kernel is correct for any position inside the cache).
-    const bool multi = (uint64_t)nchunks_hint * heads > (uint64_t)per_sm_single * (uint32_t)sm_count();
+    const bool multi = (double)nchunks_hint * heads > single_wave_factor() * per_sm_single * sm_count();
     // Up to two query heads per KV head the streaming kernel is bandwidth-bound and wins; with more, the
     // arithmetic per cache byte grows (8 heads: 4 FMA per byte) and its eight consumer warps per SM hide
     // less latency than two resident blocks of the chunk-walking split kernel.
