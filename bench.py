@@ -12,6 +12,10 @@ launched by torchrun), 4096 forced prompt tokens.
 `value`  tokens/s with everything resident on the device (one C-ABI call decodes K tokens).
 `e2e`    tokens/s through the C ABI with host buffers, one call per token: the token id goes host ->
          device, the sampled id comes back device -> host and the host waits for it, every step.
+`prefill`  prompt positions per second, position by position through the token loop (what the reference does)
+         and through the batched passes of eight positions (tensor-core products); N > 1: the batched rate only,
+         which is how those runs feed their 4096-token prompt.
+`gemv_microbench`  the twelve stand-alone matrix-vector cases (N = 1, 7B workload).
 `--impl reference` times the reference's CPU transformer (the C restatement in oracle/, all host
 threads) on a bounded sample of the same workload and prints the same line with "impl": "reference".
 """
