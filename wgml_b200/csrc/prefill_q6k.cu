@@ -170,8 +170,10 @@ __global__ void __launch_bounds__(T6_NT, 1) gemm_q6k_tc_kernel(const __grid_cons
                     for (uint32_t c = 0; c < 2; c++) {
                         // weights l = 16 c .. 16 c + 15 of group 4 half + sub: low or high nibbles of ql[64 half +
                         // 32 (sub & 1) + l], two more bits from qh[32 half + l] >> 2 sub, scale 8 half + 2 sub + c
-                        const uint4 qlq = lds128(wbase + r * 128 + 64 * half + 32 * (sub & 1) + 16 * c);
-                        const uint4 qhq = lds128(wbase + T6_OFF_QH + r * 64 + 32 * half + 16 * c);
+                        // (the 16-byte pieces of a row's ql, and of a pair of rows' qh, are stored at piece index ^ row
+                        // bits, so that the eight lanes of a quarter warp read eight different bank groups)
+                        const uint4 qlq = lds128(wbase + r * 128 + (((4 * half + 2 * (sub & 1) + c) ^ (r & 7)) << 4));
+                        const uint4 qhq = lds128(wbase + T6_OFF_QH + (r >> 1) * 128 + (((4 * (r & 1) + 2 * half + c) ^ ((r >> 1) & 7)) << 4));
                         // scale 8 half + 2 sub + c: word 2 half + sub / 2 of the sixteen, byte 2 (sub % 2) + c
                         const uint32_t sw = (sub >> 1) ? (half ? scq.w : scq.y) : (half ? scq.z : scq.x);
                         const int s = (int)(signed char)((sw >> (8 * (2 * (sub & 1) + c))) & 0xffu);
@@ -348,7 +350,8 @@ int launch_prefill_image6(const float *x, uint32_t x_stride, uint32_t K, uint32_
     return WGB_OK;
 }
 
-// Planar Q6_K matrix (qmatrix.cuh) -> [tile][column][ql 128 x 128 | qh 128 x 64 | scales 128 x 16 | d 128 x 2].
+// Planar Q6_K matrix (qmatrix.cuh) -> [tile][column][ql 128 x 128 | qh 128 x 64 | scales 128 x 16 | d 128 x 2], the
+// 16-byte pieces of ql rows and qh row pairs permuted (piece index ^ row bits) for conflict-free shared-memory reads.
 __global__ void prefill_tile_major6_kernel(QMat m, uint8_t *__restrict__ tiled)
 {
     const uint32_t nkb = m.bpr;
@@ -364,9 +367,10 @@ __global__ void prefill_tile_major6_kernel(QMat m, uint8_t *__restrict__ tiled)
         const size_t row = (size_t)tile * TC_TILE_ROWS + r;
         uint8_t *dst = tiled + unit * T6_UNIT_BYTES;
         if (piece < 8)
-            reinterpret_cast<uint4 *>(dst + r * 128)[piece] = reinterpret_cast<const uint4 *>(m.p[0] + row * m.pitch[0] + (size_t)kb * 128)[piece];
+            reinterpret_cast<uint4 *>(dst + r * 128)[piece ^ (r & 7)] = reinterpret_cast<const uint4 *>(m.p[0] + row * m.pitch[0] + (size_t)kb * 128)[piece];
         else if (piece < 12)
-            reinterpret_cast<uint4 *>(dst + T6_OFF_QH + r * 64)[piece - 8] = reinterpret_cast<const uint4 *>(m.p[1] + row * m.pitch[1] + (size_t)kb * 64)[piece - 8];
+            reinterpret_cast<uint4 *>(dst + T6_OFF_QH + (r >> 1) * 128)[(4 * (r & 1) + piece - 8) ^ ((r >> 1) & 7)] =
+                reinterpret_cast<const uint4 *>(m.p[1] + row * m.pitch[1] + (size_t)kb * 64)[piece - 8];
         else if (piece == 12)
             *reinterpret_cast<uint4 *>(dst + T6_OFF_SC + r * 16) = *reinterpret_cast<const uint4 *>(m.p[2] + row * m.pitch[2] + (size_t)kb * 16);
         else
