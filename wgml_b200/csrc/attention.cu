@@ -39,14 +39,84 @@ size_t attn_scratch_floats(uint32_t n_heads, uint32_t head_size, uint32_t seq_le
 // sizes up to 128, 2: up to 256).
 // MULTI: a block may get several chunks (long contexts, few heads) and keeps a running softmax over them;
 // otherwise every block has exactly one chunk and the loop below collapses.
-// The merge of a head's chunks by its last block, kept out of line: its registers (a second set of running sums)
-// must not count towards the kernel's, whose blocks per SM decide how long a context runs in a single wave.
+// The merge of a head's chunks by its last block.
 template <int QH, int VC>
-__device__ __noinline__ void attn_merge_chunks(const AttnArgs &a, uint32_t kvh, uint32_t hq0, uint32_t kv_mul, uint32_t hs, uint32_t nchunk,
+__device__ __forceinline__ void attn_merge_chunks(const AttnArgs &a, uint32_t kvh, uint32_t hq0, uint32_t kv_mul, uint32_t hs, uint32_t nchunk,
                                                uint32_t max_splits, uint32_t nsplit_active, float (*s_red)[ATT_WARPS], float (*s_Mw)[ATT_WARPS],
                                                float (*s_acc)[QH][VC * 128 + 4])
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if constexpr (QH > 1 || VC > 1) {
+        // Grouped queries / wide heads (arithmetic-bound kernels whose register count decides their occupancy): two passes
+        // over the scratch, all maxima first, then independent weighted sums.
+        // Merge of the chunks, spread over the block: the chunk maxima first (one thread per chunk), then warp w
+        // folds chunks w, w + 8, ... for every output element, and the eight partial results meet in shared
+        // memory.  The chunk -> warp assignment is fixed, so the result does not depend on timing.
+        __shared__ float s_M[QH];
+    #pragma unroll
+        for (int j = 0; j < QH; j++) {
+            float m = -INFINITY;
+            if (hq0 + j < kv_mul) {
+                const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
+                for (uint32_t sp = threadIdx.x; sp < nsplit_active; sp += ATT_NT) m = fmaxf(m, __ldcg(base + (size_t)sp * (hs + 4) + hs));
+            }
+            m = warp_max(m);
+            if (lane == 0) s_red[j][warp] = m;
+        }
+        __syncthreads();
+        if (threadIdx.x < QH) {
+            float m = s_red[threadIdx.x][0];
+    #pragma unroll
+            for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, s_red[threadIdx.x][w]);
+            s_M[threadIdx.x] = m;
+        }
+        __syncthreads();
+    #pragma unroll
+        for (int j = 0; j < QH; j++) {
+            if (hq0 + j >= kv_mul) continue;   // uniform over the block
+            const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
+            const float M = s_M[j];
+            float4 o[VC];
+    #pragma unroll
+            for (int c = 0; c < VC; c++) o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+            float L = 0.0f;
+            for (uint32_t sp = warp; sp < nsplit_active; sp += ATT_WARPS) {
+                const float *row = base + (size_t)sp * (hs + 4);
+                const float w = expf(__ldcg(row + hs) - M);
+                L = fmaf(__ldcg(row + hs + 1), w, L);
+    #pragma unroll
+                for (int c = 0; c < VC; c++) {
+                    const uint32_t ch = lane + 32 * c;
+                    if (ch < nchunk) {
+                        const float4 v = __ldcg(reinterpret_cast<const float4 *>(row) + ch);
+                        o[c].x = fmaf(v.x, w, o[c].x);
+                        o[c].y = fmaf(v.y, w, o[c].y);
+                        o[c].z = fmaf(v.z, w, o[c].z);
+                        o[c].w = fmaf(v.w, w, o[c].w);
+                    }
+                }
+            }
+    #pragma unroll
+            for (int c = 0; c < VC; c++) {
+                const uint32_t ch = lane + 32 * c;
+                if (ch < nchunk) reinterpret_cast<float4 *>(&s_acc[warp][j][0])[ch] = o[c];
+            }
+            if (lane == 0) s_red[j][warp] = L;
+        }
+        __syncthreads();
+        for (uint32_t e = threadIdx.x; e < QH * hs; e += ATT_NT) {
+            const uint32_t j = e / hs, i = e % hs;
+            if (hq0 + j >= kv_mul) continue;
+            float L = 0.0f, o = 0.0f;
+    #pragma unroll
+            for (int w = 0; w < ATT_WARPS; w++) {
+                L += s_red[j][w];
+                o += s_acc[w][j][i];
+            }
+            a.xb[(size_t)(kvh * kv_mul + hq0 + j) * hs + i] = o / L;
+        }
+        return;
+    }
     // Merge of the chunks, spread over the block, in one pass over the scratch: warp w folds chunks w, w + 8, ...
     // with a running maximum (a row's vector, maximum and denominator come in one round trip), and the eight warps'
     // (vector, maximum, denominator) triples meet in shared memory.  The chunk -> warp assignment and the order of
@@ -113,7 +183,7 @@ __device__ __noinline__ void attn_merge_chunks(const AttnArgs &a, uint32_t kvh, 
 // SM, and a launch is 1.2 us shorter while its blocks fit one wave -- 576 positions for 32 heads -- but a second
 // wave costs 2.5 us, more than the streaming kernel.)
 template <int QH, int VC, bool MULTI>
-__global__ void __launch_bounds__(ATT_NT, (QH == 1 && VC == 1) ? 3 : 1) attn_split_kernel(const __grid_constant__ AttnArgs a)
+__global__ void __launch_bounds__(ATT_NT, (QH == 1 && VC == 1) ? 3 : 0) attn_split_kernel(const __grid_constant__ AttnArgs a)
 {
     __shared__ float s_score[QH][ATT_CHUNK];
     __shared__ float s_red[QH][ATT_WARPS];
