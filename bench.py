@@ -52,17 +52,46 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """SM clocks and throttle reasons while the timed region runs.
+
+    Two readers of the same driver counters: an NVML thread (a sample every 5 ms, so that a timed region of a few tens of
+    milliseconds still gets some) and the `nvidia-smi -lms 100` loop.  Both only read."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, index: int):
-        self.index, self.lines, self.proc = index, [], None
+    def __init__(self, device):
+        """`device`: a physical GPU index, or a GPU UUID as CUDA_VISIBLE_DEVICES may list it."""
+        self.device, self.lines, self.proc = str(device), [], None
+        self.nvml_samples, self.nvml_thread, self.stop = [], None, threading.Event()
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        if self.device.isdigit():
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(int(self.device))
+        return pynvml, pynvml.nvmlDeviceGetHandleByUUID(self.device)
+
+    def _nvml_loop(self, nv, h):
+        reasons_of = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        while not self.stop.is_set():
+            try:
+                self.nvml_samples.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), mx, int(reasons_of(h))))
+            except Exception:
+                break
+            self.stop.wait(0.005)
 
     def __enter__(self):
         try:
+            nv, h = self._nvml_handle()
+            self.nvml_thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.nvml_thread.start()
+        except Exception:
+            self.nvml_thread = None
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-i", self.device], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -74,8 +103,12 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def __exit__(self, *a):
+        self.stop.set()
+        if self.nvml_thread:
+            self.nvml_thread.join(timeout=2)
         if self.proc:
-            time.sleep(0.15)
+            if not self.nvml_samples:
+                time.sleep(0.15)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -97,9 +130,15 @@ class ClockSampler:
             for name, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
+        n_smi = len(sm)
+        for clock, top, bits in self.nvml_samples:
+            sm.append(clock)
+            mx.append(top)
+            reasons.update(name for name, bit in self.REASON_BITS.items() if bits & bit)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm),
+                "samples_nvidia_smi": n_smi, "samples_nvml": len(self.nvml_samples)}
 
 
 def model_cfg(workload: str, seq_len: int) -> dict:
@@ -335,7 +374,8 @@ def run_b200(args):
         last = model.decode(last, 1, start_pos=pos)
         pos += 1
     stream = torch.cuda.current_stream()
-    index = int(os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[local]) if os.environ.get("CUDA_VISIBLE_DEVICES") else local
+    visible = [v.strip() for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip()]
+    index = visible[local] if local < len(visible) else local
 
     # ---- device-resident: one call decodes K tokens --------------------------------------------
     barrier()
