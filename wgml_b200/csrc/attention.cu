@@ -47,13 +47,12 @@ __device__ __forceinline__ void attn_merge_chunks(const AttnArgs &a, uint32_t kv
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if constexpr (QH > 1 || VC > 1) {
-        // Grouped queries / wide heads (arithmetic-bound kernels whose register count decides their occupancy): two passes
-        // over the scratch, all maxima first, then independent weighted sums.
-        // Merge of the chunks, spread over the block: the chunk maxima first (one thread per chunk), then warp w
-        // folds chunks w, w + 8, ... for every output element, and the eight partial results meet in shared
-        // memory.  The chunk -> warp assignment is fixed, so the result does not depend on timing.
+        // Grouped queries / wide heads (kernels whose register count decides their blocks per SM): two passes over
+        // the scratch.  The chunk maxima first (one thread per chunk), then warp w folds chunks w, w + 8, ... for
+        // every output element, and the eight partial results meet in shared memory.  The chunk -> warp assignment
+        // is fixed, so the result does not depend on timing.
         __shared__ float s_M[QH];
-    #pragma unroll
+#pragma unroll
         for (int j = 0; j < QH; j++) {
             float m = -INFINITY;
             if (hq0 + j < kv_mul) {
@@ -66,25 +65,25 @@ __device__ __forceinline__ void attn_merge_chunks(const AttnArgs &a, uint32_t kv
         __syncthreads();
         if (threadIdx.x < QH) {
             float m = s_red[threadIdx.x][0];
-    #pragma unroll
+#pragma unroll
             for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, s_red[threadIdx.x][w]);
             s_M[threadIdx.x] = m;
         }
         __syncthreads();
-    #pragma unroll
+#pragma unroll
         for (int j = 0; j < QH; j++) {
             if (hq0 + j >= kv_mul) continue;   // uniform over the block
             const float *base = a.scratch + (size_t)(kvh * kv_mul + hq0 + j) * max_splits * (hs + 4);
             const float M = s_M[j];
             float4 o[VC];
-    #pragma unroll
+#pragma unroll
             for (int c = 0; c < VC; c++) o[c] = make_float4(0.f, 0.f, 0.f, 0.f);
             float L = 0.0f;
             for (uint32_t sp = warp; sp < nsplit_active; sp += ATT_WARPS) {
                 const float *row = base + (size_t)sp * (hs + 4);
                 const float w = expf(__ldcg(row + hs) - M);
                 L = fmaf(__ldcg(row + hs + 1), w, L);
-    #pragma unroll
+#pragma unroll
                 for (int c = 0; c < VC; c++) {
                     const uint32_t ch = lane + 32 * c;
                     if (ch < nchunk) {
@@ -96,7 +95,7 @@ __device__ __forceinline__ void attn_merge_chunks(const AttnArgs &a, uint32_t kv
                     }
                 }
             }
-    #pragma unroll
+#pragma unroll
             for (int c = 0; c < VC; c++) {
                 const uint32_t ch = lane + 32 * c;
                 if (ch < nchunk) reinterpret_cast<float4 *>(&s_acc[warp][j][0])[ch] = o[c];
@@ -108,7 +107,7 @@ __device__ __forceinline__ void attn_merge_chunks(const AttnArgs &a, uint32_t kv
             const uint32_t j = e / hs, i = e % hs;
             if (hq0 + j >= kv_mul) continue;
             float L = 0.0f, o = 0.0f;
-    #pragma unroll
+#pragma unroll
             for (int w = 0; w < ATT_WARPS; w++) {
                 L += s_red[j][w];
                 o += s_acc[w][j][i];
@@ -117,7 +116,7 @@ __device__ __forceinline__ void attn_merge_chunks(const AttnArgs &a, uint32_t kv
         }
         return;
     }
-    // Merge of the chunks, spread over the block, in one pass over the scratch: warp w folds chunks w, w + 8, ...
+    // One query head, head size <= 128: one pass over the scratch.  Warp w folds chunks w, w + 8, ...
     // with a running maximum (a row's vector, maximum and denominator come in one round trip), and the eight warps'
     // (vector, maximum, denominator) triples meet in shared memory.  The chunk -> warp assignment and the order of
     // the additions are fixed, so the result does not depend on timing.
@@ -830,15 +829,6 @@ static int launch_stream_any(const AttnArgs &a, uint32_t nchunks, cudaStream_t s
     return launch_stream<1>(a, nchunks, n_kv, 1, stream, pdl);
 }
 
-static double single_wave_factor()
-{
-    static const double f = [] {
-        const char *env = getenv("WGB_ATTN_SINGLE_X");
-        return env ? atof(env) : 1.0;
-    }();
-    return f;
-}
-
 template <int QH, int VC>
 static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t nchunks_hint, uint32_t n_kv, uint32_t zgroups,
                         cudaStream_t stream, bool pdl)
@@ -858,11 +848,11 @@ static int launch_split(const AttnArgs &a, uint32_t nchunks, uint32_t nchunks_hi
     const int per_sm_single = occ_single[dev], per_sm_multi = occ_multi[dev];
     const uint32_t heads = n_kv * zgroups;
     if (!a.q) {   // sizing query (attn_sizing_class): no launch
-        return (double)nchunks_hint * heads > single_wave_factor() * per_sm_single * sm_count() ? 1 : 0;
+        return (uint64_t)nchunks_hint * heads > (uint64_t)per_sm_single * (uint32_t)sm_count() ? 1 : 0;
     }
     // `nchunks_hint`: chunks up to the furthest position this launch is expected to serve (performance only:
     // either kernel is correct for any position inside the cache).
-    const bool multi = (double)nchunks_hint * heads > single_wave_factor() * per_sm_single * sm_count();
+    const bool multi = (uint64_t)nchunks_hint * heads > (uint64_t)per_sm_single * (uint32_t)sm_count();
     // Up to two query heads per KV head the streaming kernel is bandwidth-bound and wins; with more, the
     // arithmetic per cache byte grows (8 heads: 4 FMA per byte) and its eight consumer warps per SM hide
     // less latency than two resident blocks of the chunk-walking split kernel.
