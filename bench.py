@@ -148,6 +148,9 @@ def model_cfg(workload: str, seq_len: int) -> dict:
     return cfg
 
 
+HEAD_SHARDS = 1   # ranks the rows of the output matrix are dealt over (--vocab-shard); 1: every rank computes all logits
+
+
 def matrix_bytes(cfg: dict, layer: int, name: str) -> float:
     """Algorithmic bytes of one weight matrix (GGUF block sizes, whatever the device layout)."""
     from wgml_b200 import synth
@@ -180,7 +183,7 @@ def launch_bytes(cfg: dict, kind: str, layer: int, pos: int, tp: int = 1):
         return w / tp + 4 * hid / tp + 8 * dim, qt
     if kind == "logits":
         w, qt = matrix_bytes(cfg, -1, "output")
-        return w + 4 * dim * 2 + 4 * cfg["vocab_size"], qt
+        return w / HEAD_SHARDS + 4 * dim * 2 + 4 * cfg["vocab_size"] / HEAD_SHARDS, qt
     if kind == "attention":
         return 2.0 * (pos + 1) * kv * 4 / tp + 8 * dim / tp, 0
     return 0.0, 0
@@ -316,6 +319,9 @@ def run_b200(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if args.vocab_shard:
+            global HEAD_SHARDS
+            HEAD_SHARDS = world
     workload = args.workload or ("llama2-7b" if world == 1 else "llama2-70b")
     prompt_len = args.prompt_len or (512 if workload == "llama2-7b" else 4096)
     K, W = args.steps, args.warmup
@@ -328,7 +334,7 @@ def run_b200(args):
     if world > 1:
         from wgml_b200 import tp
         comm = tp.init_from_torch_distributed()
-        tp.attach(model, comm, direct=(args.exchange == "peer"))
+        tp.attach(model, comm, direct=(args.exchange == "peer"), vocab_shard=args.vocab_shard)
     prompt = synth.prompt(prompt_len, cfg["vocab_size"], args.seed)
 
     def barrier():
@@ -445,6 +451,7 @@ def run_b200(args):
                    "parallelism": f"tp{world}" if world > 1 else "single GPU",
                    **({"exchange": "kernels store partial products into the peers' memory over NVLink, flags instead of a collective"
                        if args.exchange == "peer" else "NCCL all-reduce",
+                       "output_head": "vocab_size / N rows per rank + one NCCL all-gather" if args.vocab_shard else "replicated",
                        "note": "the default single-GPU run of this script is the 7B configuration the metric is quoted on; the "
                                "figure strong scaling of this 70B workload should be taken against is the same workload on "
                                "one GPU (--workload llama2-70b --gpus 1), which this run does not measure"} if world > 1 else {}),
@@ -611,6 +618,8 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="tensor-parallel runs: partial products exchanged by the kernels through peer memory (default) "
                          "or by an NCCL all-reduce")
+    ap.add_argument("--vocab-shard", action="store_true",
+                    help="tensor-parallel runs: every rank computes vocab_size / N logits, an all-gather completes them")
     ap.add_argument("--layers", type=int, default=None,
                     help="truncate the model to this many layers (profiler captures only: the line it prints is not a benchmark result)")
     ap.add_argument("--seed", type=int, default=0)

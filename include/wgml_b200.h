@@ -473,6 +473,14 @@ int wgb_comm_shared_alloc(wgb_comm *c, size_t bytes, void **peers_out);
  * No collective library call and no extra launch remain on the token path.  Call after
  * wgb_llama2_set_comm and before the first forward; collective (every rank, same mode). */
 int wgb_llama2_set_exchange(wgb_llama2 *m, int mode);
+/* Vocabulary-sharded output head of a tensor-parallel model (off by default): every rank multiplies only rows
+ * [tp_rank, tp_rank + 1) * vocab_size / tp_size of the output matrix -- a view of the replicated matrix, no
+ * reload -- and one NCCL all-gather per token gives every rank all the logits, so that the argmax, the
+ * sampler and wgb_llama2_logits see what they see on one GPU.  Needs the communicator and a vocabulary that
+ * is a multiple of tp_size; no effect on a single-GPU model.  Collective: every rank, same setting, before
+ * the next forward.  No counterpart in the reference (one adapter; the head is the last `matmul` of
+ * crates/wgml/src/models/llama2/transformer.rs:310-427). */
+int wgb_llama2_set_vocab_shard(wgb_llama2 *m, int on);
 /* Direct exchange on buffers the host mapped itself (its own CUDA IPC, cuMem fabric or symmetric-memory
  * allocator) instead of wgb_comm_shared_alloc: d_mail[p] / d_flags[p] are rank p's mailbox and flags as
  * seen from this rank, of the sizes wgb_llama2_exchange_bytes gives, zero-filled, 16-byte aligned, valid

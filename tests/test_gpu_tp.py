@@ -1,6 +1,7 @@
 """Tensor-parallel Llama-2 on 2 GPUs against the same model on one GPU: identical greedy tokens and
 logits within 1e-3 relative / 1e-4 absolute (absolute term scaled by the largest logit), for the direct
-exchange of partial products through peer memory and for the NCCL all-reduce.  Needs two devices; skipped
+exchange of partial products through peer memory and for the NCCL all-reduce, with the replicated and the
+vocabulary-sharded output head.  Needs two devices; skipped
 otherwise.  The ranks are separate processes over NCCL, as in production."""
 import os
 import socket
@@ -41,6 +42,10 @@ def test_tp2_matches_single_gpu(tmp_path):
             ref_x = res[f"{name}/ref_x"]
             assert_close(res[f"{name}/{mode}/tp_x"], ref_x, RTOL, ATOL * max(1.0, float(np.abs(ref_x).max())),
                          f"{name} mode {mode} residual stream")
+        for mode in ("11", "00"):   # vocabulary-sharded head: same tokens, same full logits on rank 0
+            assert np.array_equal(res[f"{name}/vs{mode}/tp_tokens"], ref_t), f"{name} vocab shard {mode}: tokens differ"
+            assert_close(res[f"{name}/vs{mode}/tp_logits"], ref_l, RTOL, ATOL * max(1.0, float(np.abs(ref_l).max())),
+                         f"{name} vocab shard {mode} logits")
     # batched prompt passes on the sharded model against the unsharded position-by-position loop
     ref_t, ref_l = res["gqa_q4k/prefill/ref_tokens"], res["gqa_q4k/prefill/ref_logits"]
     for mode in ("1", "0"):

@@ -63,6 +63,27 @@ def main():
                 res[key + "/tp_logits"] = logits
                 res[key + "/tp_x"] = x
             m.close()
+        # vocabulary-sharded head: every rank computes half of the logits, an all-gather completes them; the tokens and the
+        # full logits must be those of the replicated head
+        for fused, direct in ((True, True), (False, False)):
+            m = Llama2(c, tp_rank=rank, tp_size=world)
+            m.load_tensors(t)
+            m.set_fused(fused)
+            tp.attach(m, comm, direct=direct, vocab_shard=True)
+            toks = m.decode(prompt, 24)
+            if fused:
+                prof = m.profile_step(int(toks[-1]), len(toks))
+                assert len(prof) >= 5 * cfg["n_layers"] + 1, len(prof)
+                assert np.array_equal(m.decode(prompt, 24), toks), (name, "vocab shard: decode after the profiled step")
+            m.dispatch(int(toks[-1]), len(toks))
+            logits = m.logits().cpu().numpy()
+            assert _lib.load().wgb_device_status() == _lib.OK
+            torch.cuda.synchronize()
+            dist.barrier()
+            if rank == 0:
+                res[f"{name}/vs{int(fused)}{int(direct)}/tp_tokens"] = toks
+                res[f"{name}/vs{int(fused)}{int(direct)}/tp_logits"] = logits
+            m.close()
         if name == "gqa_q4k":
             # batched prompt passes on the sharded model (partial products summed over the group by an all-reduce),
             # for both exchanges of the token loop that follows them

@@ -167,6 +167,7 @@ SIGNATURES = {
     "wgb_comm_all_gather": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "wgb_comm_shared_alloc": (_i, [_vp, _sz, _pp]),
     "wgb_llama2_set_exchange": (_i, [_vp, _i]),
+    "wgb_llama2_set_vocab_shard": (_i, [_vp, _i]),
     "wgb_llama2_exchange_bytes": (_i, [_vp, C.POINTER(_sz), C.POINTER(_sz)]),
     "wgb_llama2_set_exchange_buffers": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp)]),
     "wgb_set_wait_limit_ms": (_i, [C.c_uint]),

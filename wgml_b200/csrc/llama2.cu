@@ -71,6 +71,7 @@ struct wgb_llama2 {
     uint32_t *tickets = nullptr;             // local: one per exchange
     uint32_t *tp_epoch = nullptr;            // local: forwards so far
     bool exchange_external = false;          // mailboxes and flags were mapped by the caller (wgb_llama2_set_exchange_buffers)
+    bool vocab_shard = false;                // every rank computes vocab_size / tp_size logits, an all-gather completes them
     int kernels_per_token = 0;
     // per-launch timing of wgb_llama2_profile_step: one event after every launch
     bool profiling = false;
@@ -377,7 +378,21 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
             n += 14;
         }
     }
-    const QMat &outw = (m->output ? m->output : m->token_embd)->view;
+    // The output head.  Its matrix is replicated; with the vocabulary-sharded head a rank multiplies only its run of
+    // vocab_size / tp_size rows (a row-range view: every plane is row-major with 16-byte-aligned pitches) into its
+    // part of the logits, and an all-gather hands every rank all of them, so that the argmax / the sampler and
+    // wgb_llama2_logits see what they see on one GPU.
+    QMat outw = (m->output ? m->output : m->token_embd)->view;
+    float *head_out = m->logits;
+    const bool vshard = tp && m->vocab_shard;
+    const uint32_t vocab_local = vshard ? c.vocab_size / (uint32_t)m->tp_size : c.vocab_size;
+    if (vshard) {
+        WGB_REQUIRE(m->comm, "the vocabulary-sharded head needs a communicator (wgb_llama2_set_comm)");
+        const size_t row0 = (size_t)m->tp_rank * vocab_local;
+        for (int i = 0; i < outw.nplanes; i++) outw.p[i] += row0 * outw.pitch[i];
+        outw.nrows = vocab_local;
+        head_out += row0;
+    }
     if (fused) {
         GemvArgs a = {};
         a.mat[0] = outw;
@@ -387,7 +402,7 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
         a.norm_w = m->output_norm;
         a.eps = c.rms_norm_eps;
         a.epilogue = EPI_STORE;
-        a.out = m->logits;
+        a.out = head_out;
         a.stamp = stamp_slot();
         receive_pending(a);
         if ((rc = launch_gemv(a, s, pdl))) return rc;
@@ -395,10 +410,11 @@ int enqueue_forward(wgb_llama2 *m, cudaStream_t s, int *nkernels)
         n += 1;
     } else {
         if ((rc = wgb_rms_norm(m->xb, m->x, m->output_norm, c.dim, c.rms_norm_eps, s))) return rc;
-        if ((rc = mat_vec(outw, m->xb, m->logits, s))) return rc;
+        if ((rc = mat_vec(outw, m->xb, head_out, s))) return rc;
         mark(m, s, K_HEAD, -1);
         n += 2;
     }
+    if (vshard && (rc = wgb_comm_all_gather((wgb_comm *)m->comm, head_out, m->logits, vocab_local, s))) return rc;
     if (nkernels) *nkernels = n;
     return WGB_OK;
 }
@@ -867,6 +883,18 @@ WGB_EXPORT int wgb_llama2_set_comm(wgb_llama2 *m, void *comm)
     WGB_REQUIRE(!comm || (wgb_comm_size((wgb_comm *)comm) == m->tp_size && wgb_comm_rank((wgb_comm *)comm) == m->tp_rank),
                 "communicator rank/size does not match the model's tensor-parallel rank %d of %d", m->tp_rank, m->tp_size);
     m->comm = comm;
+    drop_graph(m);
+    return WGB_OK;
+}
+
+WGB_EXPORT int wgb_llama2_set_vocab_shard(wgb_llama2 *m, int on)
+{
+    WGB_REQUIRE(m, "null argument");
+    const bool want = on != 0 && m->tp_size > 1;
+    if (want)
+        WGB_REQUIRE(m->cfg.vocab_size % (uint32_t)m->tp_size == 0, "a vocabulary of %u rows does not split evenly over %d ranks",
+                    m->cfg.vocab_size, m->tp_size);
+    m->vocab_shard = want;
     drop_graph(m);
     return WGB_OK;
 }

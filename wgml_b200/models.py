@@ -130,6 +130,11 @@ class Llama2:
         mailboxes by the kernels (collective call: every rank, same mode)."""
         check(_lib.load().wgb_llama2_set_exchange(self._h, int(mode)))
 
+    def set_vocab_shard(self, enable: bool) -> None:
+        """Tensor-parallel models: every rank computes vocab_size / tp_size logits and one all-gather per token
+        completes them on every rank (collective call: every rank, same setting; needs the communicator)."""
+        check(_lib.load().wgb_llama2_set_vocab_shard(self._h, int(enable)))
+
     def exchange_bytes(self) -> tuple[int, int]:
         """Sizes (mailbox bytes, flag bytes) of one rank's exchange buffers for the direct exchange."""
         a, b = C.c_size_t(), C.c_size_t()

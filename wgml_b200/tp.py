@@ -211,9 +211,11 @@ def guarded_decode(model, watch: PeerWatch, prompt, n_gen: int, start_pos: int =
     return model.decode(prompt, n_gen, start_pos=start_pos)
 
 
-def attach(model, comm: Comm, direct: bool = True) -> None:
+def attach(model, comm: Comm, direct: bool = True, vocab_shard: bool = False) -> None:
     """Gives a tensor-parallel ``Llama2`` its group; must precede the first forward.  `direct`: the kernels
-    exchange partial products through peer memory themselves instead of calling NCCL's all-reduce."""
+    exchange partial products through peer memory themselves instead of calling NCCL's all-reduce.
+    `vocab_shard`: every rank computes its run of the logits and an all-gather completes them."""
     model.set_comm(comm.handle)
     model._comm = comm   # keep it alive as long as the model
     model.set_exchange(1 if direct else 0)
+    model.set_vocab_shard(vocab_shard)
