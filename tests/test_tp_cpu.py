@@ -1,6 +1,7 @@
 """Tensor-parallel host logic on CPU: the partition rule and a two-rank (gloo) run of the sharded
 layer algebra -- head-sharded attention, FFN sharded over the hidden dimension, partial products
-summed by all-reduce with the residual folded in by rank 0 -- against the unsharded layer."""
+summed by all-reduce with the residual folded in by rank 0, and the vocabulary-sharded head completed by an
+all-gather -- against the unsharded layer."""
 import os
 import socket
 
@@ -13,6 +14,7 @@ import torch.multiprocessing as mp
 from wgml_b200 import tp
 
 CFG = dict(dim=256, hidden_dim=1024, n_q_heads=8, n_kv_heads=4)
+VOCAB = 1000
 TENSORS = ["attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight", "ffn_gate.weight",
            "ffn_up.weight", "ffn_down.weight"]
 
@@ -54,6 +56,8 @@ def _weights(seed=7):
     w = {k: rng.standard_normal(s) / np.sqrt(s[1]) for k, s in shapes.items()}
     w["attn_norm.weight"] = 1.0 + 0.1 * rng.standard_normal(d)
     w["ffn_norm.weight"] = 1.0 + 0.1 * rng.standard_normal(d)
+    w["output_norm.weight"] = 1.0 + 0.1 * rng.standard_normal(d)
+    w["output.weight"] = rng.standard_normal((VOCAB, d)) / np.sqrt(d)
     return w
 
 
@@ -110,8 +114,14 @@ def _rank_main(rank, size, port, out):
         # every rank must end with the same replicated activations
         gathered = [torch.zeros(CFG["dim"], dtype=torch.float64) for _ in range(size)]
         dist.all_gather(gathered, torch.from_numpy(y))
+        # vocabulary-sharded head: a rank's run of the logits, completed by an all-gather
+        lo, hi = tp.head_rows(VOCAB, rank, size)
+        mine = full["output.weight"][lo:hi] @ _rms(y, full["output_norm.weight"])
+        runs = [torch.zeros(hi - lo, dtype=torch.float64) for _ in range(size)]
+        dist.all_gather(runs, torch.from_numpy(mine))
         if rank == 0:
             np.save(out, np.stack([g.numpy() for g in gathered]))
+            np.save(out + ".logits.npy", np.concatenate([r.numpy() for r in runs]))
     finally:
         dist.destroy_process_group()
 
@@ -130,6 +140,21 @@ def test_two_rank_layer_matches_unsharded(tmp_path):
     ref = _layer(x, _weights(), CFG["n_q_heads"], CFG["n_kv_heads"], kc, vc, lambda v: v, True)
     assert np.array_equal(ys[0], ys[1])
     np.testing.assert_allclose(ys[0], ref, rtol=1e-12, atol=1e-12)
+    w = _weights()
+    np.testing.assert_allclose(np.load(out + ".logits.npy"), w["output.weight"] @ _rms(ref, w["output_norm.weight"]),
+                               rtol=1e-10, atol=1e-10)
+
+
+def test_head_rows_tile_the_vocabulary():
+    for size in (1, 2, 4, 8):
+        runs = [tp.head_rows(32000, r, size) for r in range(size)]
+        assert runs[0][0] == 0 and runs[-1][1] == 32000
+        assert all(a[1] == b[0] for a, b in zip(runs, runs[1:]))
+        assert len({hi - lo for lo, hi in runs}) == 1
+    with pytest.raises(ValueError):
+        tp.head_rows(50257, 0, 2)
+    with pytest.raises(ValueError):
+        tp.head_rows(32000, 2, 2)
 
 
 # ---- failure detection on the host: a rank that leaves between steps, a rank that dies silently ------------

@@ -59,6 +59,17 @@ def partition(dim: int, hidden_dim: int, n_q_heads: int, n_kv_heads: int, rank: 
                      (rank * kv_local * head, (rank + 1) * kv_local * head), hid, q_local, kv_local)
 
 
+def head_rows(vocab_size: int, rank: int, size: int) -> tuple[int, int]:
+    """Rows of the output matrix (= entries of the logits) that rank `rank` computes under the vocabulary-sharded
+    head (``Llama2.set_vocab_shard``): equal contiguous runs, so that an all-gather completes the logits."""
+    if not (size >= 1 and 0 <= rank < size):
+        raise ValueError(f"bad rank {rank} of {size}")
+    if vocab_size % size != 0:
+        raise ValueError(f"a vocabulary of {vocab_size} rows does not split evenly over {size} ranks")
+    n = vocab_size // size
+    return rank * n, (rank + 1) * n
+
+
 def slice_tensor(name: str, full: np.ndarray, p: Partition) -> np.ndarray:
     """The part of a dense [rows, cols] layer tensor that rank p.rank keeps (by GGUF tensor suffix)."""
     if name.endswith("attn_q.weight"):
