@@ -22,7 +22,12 @@
  * own `dequantization` test (crates/wgml/src/ops/quantization.rs:79-222) evaluated with an
  * independent implementation of the same ggml formats (gguf-py `quants.dequantize`); see
  * tests/golden/.  No reference test stores numeric outputs for GEMV, attention or the
- * transformers: for those the parity is "unpinned" beyond this restatement.
+ * transformers: for those the parity is "unpinned" beyond this restatement.  What anchors the
+ * reading of the architectures instead is an implementation that shares no code with this one:
+ * tests/test_oracle_hf.py compares the Llama (Original RoPE), Qwen2 (Neox RoPE, biases) and
+ * GPT-2 forwards below with logits that Hugging Face `transformers` computes in float64 for
+ * the same seeded weights (tests/golden/make_hf_golden.py): they agree to 3e-6 on logits of
+ * order 3-9.  That check says nothing about wgml's summation order.
  */
 #include <math.h>
 #include <stdint.h>
