@@ -1,33 +1,110 @@
-"""Generates tests/golden/hf_forward_golden.npz: logits of small seeded Llama, Qwen2 and GPT-2 networks computed by
-an implementation that shares no code with this repository (Hugging Face `transformers`, float64, eager attention),
-with the weights stored under their GGUF names and in GGUF conventions.
+"""Generates tests/golden/hf_forward_golden.npz: logits of seeded Llama, Qwen2 and GPT-2 networks computed by an
+implementation that shares no code with this repository (Hugging Face `transformers`, float64, eager attention).
 
-The CPU oracle's transformer forwards (restated from wgml's models/llama2/cpu.rs and models/gpt2/cpu.rs) are checked
-against these logits in tests/test_oracle_hf.py: wgml's own tests hold no numeric vectors for the forward pass, so
-this is the independent anchor of the oracle's architecture reading -- RoPE pairing and frequencies, grouped-query
-head mapping, attention scaling, SwiGLU, biases, GPT-2's fused qkv, learned positions, tanh GELU and tied head.
-It does not pin wgml's summation order (nothing available offline does).
+The CPU oracle's transformer forwards (restated from wgml's models/llama2/cpu.rs and models/gpt2/cpu.rs) and the CUDA
+models are checked against these logits in tests/test_oracle_hf.py and tests/test_gpu_hf.py: wgml's own tests hold no
+numeric vectors for the forward pass, so this is the independent anchor of the architecture reading -- RoPE pairing
+and frequencies, grouped-query head mapping, attention scaling, SwiGLU, biases, GPT-2's fused qkv, learned positions,
+tanh GELU and tied head.  It does not pin wgml's summation order (nothing available offline does).
+
+The weights are not stored: `draw_llama` / `draw_gpt2` (numpy only) draw them from a seed under their GGUF names and
+in GGUF conventions, here and in the tests; the fixture holds token ids, logits and a checksum of the drawn weights,
+so that a change of numpy's random stream shows up as a checksum mismatch and not as a parity failure.  The shapes are
+those of the small networks the GPU parity tests already use (head sizes 48 and 64, grouped queries).
 
 Conventions.  A GGUF Llama file holds attn_q / attn_k with the rows of every head permuted so that RoPE pairs
-elements (2i, 2i+1) (wgml's RoPEVariant::Original); transformers pairs (i, i + head/2).  The generator draws the
-GGUF-convention matrices and un-permutes them for the Hugging Face model.  Qwen2 files keep the (i, i + head/2)
-pairing (RoPEVariant::Neox), so the matrices are shared as they are.  GPT-2's Conv1D weights are the transposes of
-the GGUF matrices.
+elements (2i, 2i+1) (wgml's RoPEVariant::Original); transformers pairs (i, i + head/2).  The generator un-permutes
+the GGUF-convention matrices for the Hugging Face model.  Qwen2 files keep the (i, i + head/2) pairing
+(RoPEVariant::Neox), so the matrices are shared as they are.  GPT-2's Conv1D weights are the transposes of the GGUF
+matrices.
 
 Run from the repository root:  python tests/golden/make_hf_golden.py
 """
 import os
 
+import zlib
+
 import numpy as np
-import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 T = 12   # positions per network
 
 
-def _h(a) -> np.ndarray:
-    """Rounds to values a 16-bit float holds exactly (the fixture stores the weights as f16) and returns them as f32."""
-    return np.asarray(a).astype(np.float16).astype(np.float32)
+SEEDS = {"llama": 101, "qwen2": 102, "gpt2": 103}
+LLAMA_CFGS = {
+    # tiny-llama widths (head 48) with grouped queries, two layers, a small vocabulary
+    "llama": dict(dim=288, hidden_dim=768, n_layers=2, n_q_heads=6, n_kv_heads=3, vocab_size=256, seq_len=32,
+                  rope_base_freq=10000.0, rms_norm_eps=1e-5),
+    # head 64, four query heads per KV head, biases, Qwen2's theta and epsilon
+    "qwen2": dict(dim=512, hidden_dim=1024, n_layers=2, n_q_heads=8, n_kv_heads=2, vocab_size=256, seq_len=32,
+                  rope_base_freq=1000000.0, rms_norm_eps=1e-6),
+}
+GPT2_CFG = dict(n_vocab=200, n_seq=32, n_embd=256, n_head=4, n_layer=2, ff_len=1024)
+
+
+def _f(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def draw_llama(kind: str):
+    """(config, {GGUF tensor name: f32 array}, token ids) of the seeded Llama-family network `kind`."""
+    cfg = dict(LLAMA_CFGS[kind])
+    rng = np.random.default_rng(SEEDS[kind])
+    dim, hid, L = cfg["dim"], cfg["hidden_dim"], cfg["n_layers"]
+    kv = cfg["n_kv_heads"] * (dim // cfg["n_q_heads"])
+
+    def mat(r, c):
+        return _f(rng.standard_normal((r, c)) / np.sqrt(c))
+
+    t = {"token_embd.weight": _f(rng.standard_normal((cfg["vocab_size"], dim)) * 0.5),
+         "output.weight": mat(cfg["vocab_size"], dim),
+         "output_norm.weight": _f(1.0 + 0.1 * rng.standard_normal(dim))}
+    for l in range(L):
+        p = f"blk.{l}."
+        t[p + "attn_q.weight"], t[p + "attn_k.weight"], t[p + "attn_v.weight"] = mat(dim, dim), mat(kv, dim), mat(kv, dim)
+        t[p + "attn_output.weight"] = mat(dim, dim)
+        t[p + "ffn_gate.weight"], t[p + "ffn_up.weight"], t[p + "ffn_down.weight"] = mat(hid, dim), mat(hid, dim), mat(dim, hid)
+        t[p + "attn_norm.weight"] = _f(1.0 + 0.1 * rng.standard_normal(dim))
+        t[p + "ffn_norm.weight"] = _f(1.0 + 0.1 * rng.standard_normal(dim))
+        if kind == "qwen2":
+            for n, sz in (("attn_q.bias", dim), ("attn_k.bias", kv), ("attn_v.bias", kv)):
+                t[p + n] = _f(0.2 * rng.standard_normal(sz))
+    tokens = rng.integers(0, cfg["vocab_size"], T).astype(np.uint32)
+    return cfg, t, tokens
+
+
+def draw_gpt2():
+    """(config, {GGUF tensor name: f32 array}, token ids) of the seeded GPT-2 network."""
+    cfg = dict(GPT2_CFG)
+    rng = np.random.default_rng(SEEDS["gpt2"])
+    n, ff, L = cfg["n_embd"], cfg["ff_len"], cfg["n_layer"]
+
+    def mat(r, c):
+        return _f(rng.standard_normal((r, c)) / np.sqrt(c))
+
+    def vec(sz, mean=0.0, sd=0.1):
+        return _f(mean + sd * rng.standard_normal(sz))
+
+    t = {"token_embd.weight": _f(rng.standard_normal((cfg["n_vocab"], n)) * 0.5),
+         "position_embd.weight": _f(rng.standard_normal((cfg["n_seq"], n)) * 0.2),
+         "output_norm.weight": vec(n, 1.0), "output_norm.bias": vec(n)}
+    for l in range(L):
+        p = f"blk.{l}."
+        t[p + "attn_qkv.weight"], t[p + "attn_output.weight"] = mat(3 * n, n), mat(n, n)
+        t[p + "ffn_up.weight"], t[p + "ffn_down.weight"] = mat(ff, n), mat(n, ff)
+        t[p + "attn_qkv.bias"], t[p + "attn_output.bias"], t[p + "ffn_up.bias"], t[p + "ffn_down.bias"] = vec(3 * n), vec(n), vec(ff), vec(n)
+        t[p + "attn_norm.weight"], t[p + "attn_norm.bias"] = vec(n, 1.0), vec(n)
+        t[p + "ffn_norm.weight"], t[p + "ffn_norm.bias"] = vec(n, 1.0), vec(n)
+    tokens = rng.integers(0, cfg["n_vocab"], T).astype(np.uint32)
+    return cfg, t, tokens
+
+
+def checksum(tensors: dict) -> int:
+    """CRC-32 over the bytes of all tensors in name order."""
+    c = 0
+    for k in sorted(tensors):
+        c = zlib.crc32(np.ascontiguousarray(tensors[k]).tobytes(), zlib.crc32(k.encode(), c))
+    return c
 
 
 def _unpermute_rope_rows(w: np.ndarray, n_heads: int) -> np.ndarray:
@@ -42,44 +119,29 @@ def _unpermute_rope_rows(w: np.ndarray, n_heads: int) -> np.ndarray:
     return out
 
 
-def llama_like(kind: str, seed: int):
+def _load(model, sd, may_miss):
+    import torch
+    missing, unexpected = model.load_state_dict({k: torch.from_numpy(np.ascontiguousarray(v, dtype=np.float64)) for k, v in sd.items()},
+                                                strict=False)
+    assert not unexpected and all(any(s in m for s in may_miss) for m in missing), (missing, unexpected)
+
+
+def hf_llama_logits(kind: str, cfg: dict, t: dict, tokens: np.ndarray) -> np.ndarray:
+    import torch
     from transformers import LlamaConfig, LlamaForCausalLM, Qwen2Config, Qwen2ForCausalLM
-    rng = np.random.default_rng(seed)
-    cfg = dict(dim=48, hidden_dim=96, n_layers=2, n_q_heads=4, n_kv_heads=2, vocab_size=64, seq_len=32,
-               rope_base_freq=10000.0 if kind == "llama" else 1000000.0, rms_norm_eps=1e-5 if kind == "llama" else 1e-6)
-    dim, hid, L = cfg["dim"], cfg["hidden_dim"], cfg["n_layers"]
-    head = dim // cfg["n_q_heads"]
-    kv = cfg["n_kv_heads"] * head
-
-    def mat(r, c):
-        return _h(rng.standard_normal((r, c)) / np.sqrt(c))
-
-    t = {"token_embd.weight": _h(rng.standard_normal((cfg["vocab_size"], dim)) * 0.5),
-         "output.weight": mat(cfg["vocab_size"], dim),
-         "output_norm.weight": _h(1.0 + 0.1 * rng.standard_normal(dim))}
-    for l in range(L):
-        p = f"blk.{l}."
-        t[p + "attn_q.weight"], t[p + "attn_k.weight"], t[p + "attn_v.weight"] = mat(dim, dim), mat(kv, dim), mat(kv, dim)
-        t[p + "attn_output.weight"] = mat(dim, dim)
-        t[p + "ffn_gate.weight"], t[p + "ffn_up.weight"], t[p + "ffn_down.weight"] = mat(hid, dim), mat(hid, dim), mat(dim, hid)
-        t[p + "attn_norm.weight"] = _h(1.0 + 0.1 * rng.standard_normal(dim))
-        t[p + "ffn_norm.weight"] = _h(1.0 + 0.1 * rng.standard_normal(dim))
-        if kind == "qwen2":
-            for n, sz in (("attn_q.bias", dim), ("attn_k.bias", kv), ("attn_v.bias", kv)):
-                t[p + n] = _h(0.2 * rng.standard_normal(sz))
-    common = dict(vocab_size=cfg["vocab_size"], hidden_size=dim, intermediate_size=hid, num_hidden_layers=L,
-                  num_attention_heads=cfg["n_q_heads"], num_key_value_heads=cfg["n_kv_heads"], hidden_act="silu",
-                  max_position_embeddings=cfg["seq_len"], rms_norm_eps=cfg["rms_norm_eps"], rope_theta=cfg["rope_base_freq"],
-                  tie_word_embeddings=False, attn_implementation="eager")
+    common = dict(vocab_size=cfg["vocab_size"], hidden_size=cfg["dim"], intermediate_size=cfg["hidden_dim"],
+                  num_hidden_layers=cfg["n_layers"], num_attention_heads=cfg["n_q_heads"], num_key_value_heads=cfg["n_kv_heads"],
+                  hidden_act="silu", max_position_embeddings=cfg["seq_len"], rms_norm_eps=cfg["rms_norm_eps"],
+                  rope_theta=cfg["rope_base_freq"], tie_word_embeddings=False, attn_implementation="eager")
     if kind == "llama":
         model = LlamaForCausalLM(LlamaConfig(attention_bias=False, mlp_bias=False, **common))
     else:
         model = Qwen2ForCausalLM(Qwen2Config(use_sliding_window=False, **common))
     model = model.double().eval()
-    fix = (lambda w, n: _unpermute_rope_rows(w, n)) if kind == "llama" else (lambda w, n: w)
+    fix = _unpermute_rope_rows if kind == "llama" else (lambda w, n: w)
     sd = {"model.embed_tokens.weight": t["token_embd.weight"], "lm_head.weight": t["output.weight"],
           "model.norm.weight": t["output_norm.weight"]}
-    for l in range(L):
+    for l in range(cfg["n_layers"]):
         p, h = f"blk.{l}.", f"model.layers.{l}."
         sd[h + "self_attn.q_proj.weight"] = fix(t[p + "attn_q.weight"], cfg["n_q_heads"])
         sd[h + "self_attn.k_proj.weight"] = fix(t[p + "attn_k.weight"], cfg["n_kv_heads"])
@@ -94,44 +156,21 @@ def llama_like(kind: str, seed: int):
             sd[h + "self_attn.q_proj.bias"] = t[p + "attn_q.bias"]
             sd[h + "self_attn.k_proj.bias"] = t[p + "attn_k.bias"]
             sd[h + "self_attn.v_proj.bias"] = t[p + "attn_v.bias"]
-    missing, unexpected = model.load_state_dict({k: torch.from_numpy(np.asarray(v, dtype=np.float64)) for k, v in sd.items()},
-                                                strict=False)
-    assert not unexpected and all("rotary" in m or "inv_freq" in m for m in missing), (missing, unexpected)
-    tokens = rng.integers(0, cfg["vocab_size"], T)
+    _load(model, sd, ("rotary", "inv_freq"))
     with torch.no_grad():
-        logits = model(torch.from_numpy(tokens)[None]).logits[0].numpy()
-    return cfg, t, tokens.astype(np.uint32), logits
+        return model(torch.from_numpy(tokens.astype(np.int64))[None]).logits[0].numpy()
 
 
-def gpt2(seed: int):
+def hf_gpt2_logits(cfg: dict, t: dict, tokens: np.ndarray) -> np.ndarray:
+    import torch
     from transformers import GPT2Config, GPT2LMHeadModel
-    rng = np.random.default_rng(seed)
-    cfg = dict(n_vocab=64, n_seq=32, n_embd=32, n_head=4, n_layer=2, ff_len=128)
-    n, ff, L = cfg["n_embd"], cfg["ff_len"], cfg["n_layer"]
-
-    def mat(r, c):
-        return _h(rng.standard_normal((r, c)) / np.sqrt(c))
-
-    def vec(sz, mean=0.0, sd=0.1):
-        return _h(mean + sd * rng.standard_normal(sz))
-
-    t = {"token_embd.weight": _h(rng.standard_normal((cfg["n_vocab"], n)) * 0.5),
-         "position_embd.weight": _h(rng.standard_normal((cfg["n_seq"], n)) * 0.2),
-         "output_norm.weight": vec(n, 1.0), "output_norm.bias": vec(n)}
-    for l in range(L):
-        p = f"blk.{l}."
-        t[p + "attn_qkv.weight"], t[p + "attn_output.weight"] = mat(3 * n, n), mat(n, n)
-        t[p + "ffn_up.weight"], t[p + "ffn_down.weight"] = mat(ff, n), mat(n, ff)
-        t[p + "attn_qkv.bias"], t[p + "attn_output.bias"], t[p + "ffn_up.bias"], t[p + "ffn_down.bias"] = vec(3 * n), vec(n), vec(ff), vec(n)
-        t[p + "attn_norm.weight"], t[p + "attn_norm.bias"] = vec(n, 1.0), vec(n)
-        t[p + "ffn_norm.weight"], t[p + "ffn_norm.bias"] = vec(n, 1.0), vec(n)
-    model = GPT2LMHeadModel(GPT2Config(vocab_size=cfg["n_vocab"], n_positions=cfg["n_seq"], n_embd=n, n_layer=L, n_head=cfg["n_head"],
-                                       n_inner=ff, activation_function="gelu_new", resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0,
-                                       layer_norm_epsilon=1e-5, attn_implementation="eager")).double().eval()
+    model = GPT2LMHeadModel(GPT2Config(vocab_size=cfg["n_vocab"], n_positions=cfg["n_seq"], n_embd=cfg["n_embd"], n_layer=cfg["n_layer"],
+                                       n_head=cfg["n_head"], n_inner=cfg["ff_len"], activation_function="gelu_new", resid_pdrop=0.0,
+                                       embd_pdrop=0.0, attn_pdrop=0.0, layer_norm_epsilon=1e-5, attn_implementation="eager")).double().eval()
     sd = {"transformer.wte.weight": t["token_embd.weight"], "transformer.wpe.weight": t["position_embd.weight"],
           "transformer.ln_f.weight": t["output_norm.weight"], "transformer.ln_f.bias": t["output_norm.bias"],
           "lm_head.weight": t["token_embd.weight"]}
-    for l in range(L):
+    for l in range(cfg["n_layer"]):
         p, h = f"blk.{l}.", f"transformer.h.{l}."
         sd[h + "attn.c_attn.weight"], sd[h + "attn.c_attn.bias"] = t[p + "attn_qkv.weight"].T, t[p + "attn_qkv.bias"]
         sd[h + "attn.c_proj.weight"], sd[h + "attn.c_proj.bias"] = t[p + "attn_output.weight"].T, t[p + "attn_output.bias"]
@@ -139,26 +178,24 @@ def gpt2(seed: int):
         sd[h + "mlp.c_proj.weight"], sd[h + "mlp.c_proj.bias"] = t[p + "ffn_down.weight"].T, t[p + "ffn_down.bias"]
         sd[h + "ln_1.weight"], sd[h + "ln_1.bias"] = t[p + "attn_norm.weight"], t[p + "attn_norm.bias"]
         sd[h + "ln_2.weight"], sd[h + "ln_2.bias"] = t[p + "ffn_norm.weight"], t[p + "ffn_norm.bias"]
-    missing, unexpected = model.load_state_dict({k: torch.from_numpy(np.ascontiguousarray(v, dtype=np.float64)) for k, v in sd.items()},
-                                                strict=False)
-    assert not unexpected and all(".attn.bias" in m or "masked_bias" in m for m in missing), (missing, unexpected)
-    tokens = rng.integers(0, cfg["n_vocab"], T)
+    _load(model, sd, (".attn.bias", "masked_bias"))
     with torch.no_grad():
-        logits = model(torch.from_numpy(tokens)[None]).logits[0].numpy()
-    return cfg, t, tokens.astype(np.uint32), logits
+        return model(torch.from_numpy(tokens.astype(np.int64))[None]).logits[0].numpy()
 
 
 def main():
     out = {}
-    for name, (cfg, t, tokens, logits) in (("llama", llama_like("llama", 101)), ("qwen2", llama_like("qwen2", 102)), ("gpt2", gpt2(103))):
-        for k, v in cfg.items():
-            out[f"{name}/cfg/{k}"] = np.float64(v)
-        for k, v in t.items():
-            assert np.array_equal(v.astype(np.float16).astype(np.float32), v), k
-            out[f"{name}/w/{k}"] = v.astype(np.float16)
+    for name in ("llama", "qwen2", "gpt2"):
+        if name == "gpt2":
+            cfg, t, tokens = draw_gpt2()
+            logits = hf_gpt2_logits(cfg, t, tokens)
+        else:
+            cfg, t, tokens = draw_llama(name)
+            logits = hf_llama_logits(name, cfg, t, tokens)
         out[f"{name}/tokens"] = tokens
         out[f"{name}/logits"] = logits.astype(np.float64)
-        print(name, "logits", logits.shape, "max |logit|", float(np.abs(logits).max()))
+        out[f"{name}/weights_crc32"] = np.uint32(checksum(t))
+        print(name, "logits", logits.shape, "max |logit|", float(np.abs(logits).max()), "crc", checksum(t))
     path = os.path.join(HERE, "hf_forward_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")
