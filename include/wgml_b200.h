@@ -183,8 +183,10 @@ int wgb_attention(const wgb_attn_params *p, const float *d_q, const float *d_key
  *     n_heads * ceil(seq_len / 64) * (head_size + 4) <= WGB_ATTENTION_STATIC_MAX_SCRATCH_FLOATS and
  *     n_heads <= WGB_ATTENTION_STATIC_MAX_HEADS (a 7B-class 32 x 128 head layout fits up to 31 744 cached
  *     positions; 64 heads up to 15 872);
- *   - the first call on a device looks the array up (cudaGetSymbolAddress, with that device current);
- *     make that first call before the stream is put into capture mode;
+ *   - the first call on a device looks the array up (cudaGetSymbolAddress, with that device current) and, like
+ *     the first wgb_attention there, sets the kernels up once (cudaFuncSetAttribute for the shared-memory
+ *     opt-in, cudaOccupancyMaxActiveBlocksPerMultiprocessor for the launch shapes): none of these may run while
+ *     a stream is capturing, so make that first call before the stream is put into capture mode;
  *   - two calls that may run at the same time (different streams, or different host threads on one
  *     device) share the array and race: keep calls on one device in one stream order.
  * Every call clears its tickets first, so an earlier launch that was cut short cannot disturb it.
