@@ -132,3 +132,47 @@ def test_big_endian_magic_is_accepted_like_the_reference():
     good = bytearray(open(os.path.join(GOLD, "ref_dummy.gguf"), "rb").read())
     good[0:4] = (0x47475546).to_bytes(4, "little")  # GGUF_FILE_MAGIC_BE, gguf.rs:20,477
     assert Gguf.from_bytes(bytes(good)).version == 3
+
+
+def test_mutated_files_parse_or_fail_cleanly():
+    """Random byte, word and length mutations of a valid file: every one either parses -- and then every tensor's
+    bytes and every metadata value can be read -- or is refused with a status; none may crash the process.  Strings that
+    are not UTF-8 come out with replacement characters, as the reference reads them (gguf.rs:660, from_utf8_lossy)."""
+    import random
+    good = open(os.path.join(GOLD, "ref_dummy.gguf"), "rb").read()
+    rng = random.Random(2024)
+    parsed = refused = 0
+    for _ in range(1500):
+        b = bytearray(good)
+        mode = rng.randrange(4)
+        if mode == 0:
+            for _ in range(rng.randint(1, 4)):
+                b[rng.randrange(len(b))] = rng.randrange(256)
+        elif mode == 1:
+            p = rng.randrange(0, min(len(b) - 8, 1400))
+            b[p:p + 8] = rng.choice([0, 1, 0xFF, 0xFFFF, 0xFFFFFFFF, 2**63, 2**64 - 1, rng.getrandbits(64)]).to_bytes(8, "little")
+        elif mode == 2:
+            b = b[:rng.randrange(len(b))]
+        else:
+            p = rng.randrange(0, min(len(b) - 4, 1400))
+            b[p:p + 4] = rng.getrandbits(32).to_bytes(4, "little")
+        try:
+            g = Gguf.from_bytes(bytes(b))
+        except WgbError as e:
+            assert e.status in (_lib.ERR_PARSE, _lib.ERR_UNSUPPORTED, _lib.ERR_INVALID), e.status
+            refused += 1
+            continue
+        for t in g.tensors.values():
+            d = t.data()
+            assert d.size == t.n_bytes or d.size == 0
+            if d.size:
+                int(d[0]) + int(d[-1])
+        repr(g.metadata)
+        g.close()
+        parsed += 1
+    assert parsed > 100 and refused > 100
+    # a tensor name that is not UTF-8
+    bad = bytearray(good)
+    bad[good.index(b"tensor")] = 0xFF
+    g = Gguf.from_bytes(bytes(bad))
+    assert any("\ufffd" in n for n in list(g.tensors) + list(g.metadata))

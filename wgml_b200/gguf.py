@@ -18,7 +18,7 @@ class GgufTensor:
     """GgufTensor (gguf.rs:297-315): dimensions, ggml type and a zero-copy view of the bytes."""
 
     def __init__(self, info: GgufTensorC, owner):
-        self.name = info.name.decode()
+        self.name = info.name.decode("utf-8", "replace")   # lossy, as the reference reads strings (gguf.rs:660)
         self.n_dims = info.n_dims
         self.dimensions = [int(d) for d in info.dims]
         self.type = int(info.type)
