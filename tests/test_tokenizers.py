@@ -252,3 +252,43 @@ def test_llama_matches_sentencepiece(llama_tok):
     texts += ["".join(rng.choice(alphabet) for _ in range(rng.randint(1, 24))) for _ in range(400)]
     for text in texts:
         assert tok.encode(text, True, False) == [1] + sp.encode(text), repr(text)
+
+
+# ---- arbitrary input ---------------------------------------------------------------------------------------------
+def test_arbitrary_bytes_and_ids_never_crash(llama_tok, gpt2_tok):
+    """The C entry points take raw bytes: malformed UTF-8, unbalanced `<`, empty and long inputs must come back as
+    token ids or as a status, and ids outside the vocabulary must decode to a status or to nothing."""
+    import ctypes as C
+
+    from wgml_b200 import _lib
+    from wgml_b200._lib import WgbError
+    lt, gt = llama_tok[0], gpt2_tok[0]
+    n_llama, n_gpt2 = len(llama_tok[2]), len(gpt2_tok[2])
+    lib = _lib.load()
+    rng = random.Random(77)
+    encoded = refused = 0
+    for _ in range(400):
+        n = rng.choice([0, 1, 2, 3, 7, 31, 200, 3000])
+        kind = rng.randrange(3)
+        if kind == 0:
+            raw = bytes(rng.randrange(256) for _ in range(n))
+        elif kind == 1:
+            raw = "".join(rng.choice(["<", ">", "a", " ", "é", "<s>", "</s>", "<pad>", "\n", "日", "\U0001F600", "'ll"]) for _ in range(n)).encode()
+        else:
+            raw = bytes(rng.choice(b"<>a \xc3\xa9\xe6\x97\xa5\xf0\x9f\x98\x80\xff\x80'") for _ in range(n))
+        cnt = C.c_size_t()
+        for call in (lambda out, cap: lib.wgb_llama_tokenizer_encode(lt._h, raw, len(raw), 1, 1, out, cap, C.byref(cnt)),
+                     lambda out, cap: lib.wgb_gpt2_tokenizer_encode(gt._h, raw, len(raw), out, cap, C.byref(cnt))):
+            if call(None, 0) != _lib.OK:
+                refused += 1
+                continue
+            out = np.zeros(max(cnt.value, 1), np.uint32)
+            assert call(out.ctypes.data, out.size) == _lib.OK
+            encoded += 1
+        for f in (lambda: gt.decode(np.array([rng.randrange(0, n_gpt2 + 5) for _ in range(rng.randint(0, 20))], np.uint32)),
+                  lambda: lt.decode(rng.randrange(0, n_llama + 5), rng.randrange(0, n_llama + 5))):
+            try:
+                f()
+            except WgbError:
+                pass
+    assert encoded > 400 and refused > 0
