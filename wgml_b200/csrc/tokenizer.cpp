@@ -14,6 +14,7 @@
 #include <locale.h>
 
 #include <climits>
+#include <cmath>
 #include <map>
 #include <new>
 #include <string>
