@@ -50,3 +50,34 @@ def test_argument_errors_are_statuses_not_aborts():
     assert "null" in _lib.last_error() or "unsupported" in _lib.last_error()
     assert lib.wgb_rope(0, None, None, 2, None, 2, None) == _lib.ERR_INVALID
     assert lib.wgb_gguf_open(b"/nonexistent/file.gguf", None) == _lib.ERR_INVALID  # null out pointer
+
+
+def test_header_is_plain_c_and_links_from_c(tmp_path):
+    """The boundary is a C ABI: the header compiles as pedantic C11 and as C++, and a C program with no other
+    dependency links against the library and calls into it (host-only entry points: no device needed)."""
+    import shutil
+    import subprocess
+    if not shutil.which("gcc"):
+        pytest.skip("no C compiler")
+    src = tmp_path / "user.c"
+    src.write_text('#include <stdio.h>\n#include <string.h>\n#include "wgml_b200.h"\n'
+                   "int main(void) {\n"
+                   "    wgb_gguf *g = NULL;\n"
+                   '    if (wgb_block_bytes(12) != 144 || wgb_block_len(12) != 256) return 1;\n'
+                   '    if (wgb_gguf_from_bytes("GGML", 4, &g) == WGB_OK) return 2;\n'
+                   '    if (!strlen(wgb_last_error()) || !strlen(wgb_version())) return 3;\n'
+                   '    puts(wgb_version());\n'
+                   "    return 0;\n}\n")
+    inc = os.path.join(ROOT, "include")
+    libdir = os.path.join(ROOT, "wgml_b200")
+    for cc, std, lang in (("gcc", "-std=c11", "c"), ("g++", "-std=c++17", "c++")):
+        if shutil.which(cc):
+            r = subprocess.run([cc, std, "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-x", lang, "-I", inc, str(src)],
+                               capture_output=True, text=True)
+            assert r.returncode == 0, r.stderr
+    exe = tmp_path / "user"
+    r = subprocess.run(["gcc", "-std=c11", "-I", inc, str(src), "-o", str(exe), "-L", libdir, "-lwgml_b200", f"-Wl,-rpath,{libdir}"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip(), (r.returncode, r.stdout, r.stderr)
