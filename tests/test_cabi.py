@@ -81,3 +81,26 @@ def test_header_is_plain_c_and_links_from_c(tmp_path):
     assert r.returncode == 0, r.stderr
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0 and r.stdout.strip(), (r.returncode, r.stdout, r.stderr)
+
+
+def _split_params(s: str):
+    s = s.strip()
+    if not s or s == "void":
+        return []
+    return [p.strip() for p in s.split(",")]
+
+
+def test_binding_excerpt_in_the_integration_notes_matches_the_header():
+    """Every `pub fn wgb_*` of the Rust excerpt names a declared entry point with the same number of parameters and the
+    same parameter names (the excerpt is what a maintainer would copy)."""
+    header = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "wgml_b200.h")).read(), flags=re.S)
+    c_decls = {m.group(1): _split_params(m.group(2))
+               for m in re.finditer(r"\b(wgb_[a-z0-9_]+)\s*\(([^()]*)\)\s*;", header)}
+    notes = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    rust = re.findall(r"pub fn (wgb_[a-z0-9_]+)\(([^()]*)\)", notes)
+    assert len(rust) >= 10
+    for name, params in rust:
+        assert name in c_decls, f"{name} is in the binding excerpt but not in the header"
+        r = [p.split(":")[0].strip() for p in _split_params(params)]
+        c = [re.findall(r"[A-Za-z_][A-Za-z0-9_]*", p)[-1] for p in c_decls[name]]
+        assert r == c, f"{name}: Rust excerpt has {r}, the header {c}"
