@@ -321,12 +321,12 @@ uint32_t wgb_gpt2_tokenizer_eos(const wgb_gpt2_tokenizer *t);
 int wgb_gpt2_tokenizer_encode(const wgb_gpt2_tokenizer *t, const char *text, size_t text_len, uint32_t *out_ids, size_t cap,
                               size_t *n_out);
 int wgb_gpt2_tokenizer_decode(const wgb_gpt2_tokenizer *t, const uint32_t *tokens, size_t n, char *buf, size_t cap, size_t *len);
-/* ChatTemplate::apply (crates/wgml-chat/src/chat_template.rs:31-43) for the default template
+/* ChatTemplate::apply (crates/wgml-chat/src/chat_template.rs:27-39) for the default template
  * (LlamaTokenizer::CHAT_TEMPLATE, models/llama2/llama-2-chat.jinja) with minijinja configured as there
  * (trim_blocks, bos_token / eos_token globals): roles[i] in {"system" (first only), "user", "assistant"},
  * alternating from "user" (else WGB_ERR_INVALID with the template's own message).  The white space the
  * template leaves between its tags is part of the rendering and is reproduced.  Templates carried by a GGUF
- * (tokenizer.chat_template, chat_template.rs:22-29) are arbitrary Jinja and are not interpreted. */
+ * (tokenizer.chat_template, chat_template.rs:18-25) are arbitrary Jinja and are not interpreted. */
 int wgb_chat_template_llama2(const char *const *roles, const char *const *contents, size_t n_messages, const char *bos,
                              const char *eos, char *buf, size_t cap, size_t *len);
 

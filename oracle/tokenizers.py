@@ -147,7 +147,7 @@ class Gpt2Tokenizer:
 
 
 def chat_template_llama2(messages, bos: str, eos: str) -> str:
-    """llama-2-chat.jinja under minijinja with trim_blocks (chat_template.rs:31-43).  The literal text of the
+    """llama-2-chat.jinja under minijinja with trim_blocks (chat_template.rs:27-39).  The literal text of the
     template between its tags (indentation, blank lines) is emitted exactly as written there, minus the one
     newline trim_blocks removes after each `{% ... %}`."""
     out = []

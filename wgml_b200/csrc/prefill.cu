@@ -714,7 +714,7 @@ int launch_prefill_rope_append(const PrefillQkv &a, uint32_t ntok, cudaStream_t 
 
 // ---- causal attention of a batch of positions ----------------------------------------------------------
 
-// BatchedMultiqueryAttention (ops/batched_multiquery_attention.wgsl:42-122) for positions pos0 + t, t < ntok, each
+// BatchedMultiqueryAttention (ops/batched_multiquery_attention.wgsl:38-99) for positions pos0 + t, t < ntok, each
 // attending to cache rows 0 .. pos0 + t.  One block per (query head, group of TQ = 2, 4 or 8 positions); the block walks the
 // cache rows in chunks of 256 with a running maximum and sum (rescaled), one thread per row for the scores, one
 // thread per value column (times a quarter of the chunk's rows) for the weighted sum.

@@ -4,7 +4,7 @@
 //                   fallback), the special-token scans, then greedy merging of the best-scoring adjacent pair
 //   Gpt2Tokenizer   crates/wgml/src/models/gpt2/tokenizer.rs:38-217   byte-level BPE over a pre-split by the GPT-2
 //                   pattern, with `<...>` spans looked up as special tokens
-//   chat template   crates/wgml-chat/src/chat_template.rs:11-44 + models/llama2/llama-2-chat.jinja
+//   chat template   crates/wgml-chat/src/chat_template.rs:10-40 + models/llama2/llama-2-chat.jinja
 //
 // All three work on what the GGUF metadata holds (tokenizer.ggml.tokens / scores / merges / *_token_id); no
 // vocabulary is built in.  Pure host code: nothing here touches a device.
@@ -508,7 +508,7 @@ std::string trim(const std::string &s)
 
 }  // namespace
 
-// ChatTemplate::apply (crates/wgml-chat/src/chat_template.rs:31-43) for the default template,
+// ChatTemplate::apply (crates/wgml-chat/src/chat_template.rs:27-39) for the default template,
 // LlamaTokenizer::CHAT_TEMPLATE = llama-2-chat.jinja, rendered as the reference configures minijinja:
 // trim_blocks on (the newline after a block tag is dropped), lstrip_blocks off (the indentation in front of a
 // tag stays), add_generation_prompt unused by this template.  The white space between the tags is therefore

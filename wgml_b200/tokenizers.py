@@ -103,7 +103,7 @@ class Gpt2Tokenizer:
 
 
 class ChatTemplate:
-    """ChatTemplate (chat_template.rs:5-44) for the default Llama-2 chat template."""
+    """ChatTemplate (chat_template.rs:5-40) for the default Llama-2 chat template."""
 
     @staticmethod
     def apply(messages: list[tuple[str, str]], bos: str, eos: str) -> str:
